@@ -1,0 +1,299 @@
+/*
+ * oasr_b200.h -- C-ABI of the B200 (sm_100a) encoder hot path.
+ *
+ * One shared library, liboasr_b200.so, exports every function below with C
+ * linkage, plain device pointers and sizes.  Each entry point replaces one
+ * TVM-FFI launcher of the reference (cited per function as <file>:<line> in
+ * the reference tree).  Conventions shared by all entry points, following
+ * the reference's launcher conventions (csrc/tvm_ffi_utils.h:36-168):
+ *
+ *   - the OUTPUT pointer comes first, inputs follow, optional tensors are
+ *     nullable pointers, scalars are int64_t / double / int;
+ *   - the caller owns and allocates every buffer; nothing is allocated per
+ *     call, so every entry point may be recorded into a CUDA graph;
+ *   - work is enqueued on the `stream` argument (a cudaStream_t passed as
+ *     void*; NULL means the legacy default stream) and the call returns
+ *     without synchronising;
+ *   - the return value is 0 on success or a negative OASR_ERR_* code; no
+ *     launch has happened when the code is negative.  The message for the
+ *     calling thread is available from oasr_b200_last_error();
+ *   - all pointers are device pointers unless the parameter comment says
+ *     "host"; tensors are dense row-major with the trailing dimension
+ *     contiguous;
+ *   - `dtype` is an oasr_dtype id naming the element type of the activation
+ *     tensors (and of weights unless stated otherwise).
+ */
+#ifndef OASR_B200_H_
+#define OASR_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define OASR_API __declspec(dllexport)
+#else
+#define OASR_API __attribute__((visibility("default")))
+#endif
+
+/* Element type ids. */
+enum oasr_dtype {
+  OASR_DT_F32 = 0,
+  OASR_DT_F16 = 1,
+  OASR_DT_BF16 = 2,
+  OASR_DT_FP8_E4M3 = 3,
+  OASR_DT_INT8 = 4
+};
+
+/* Activation ids: the reference's ActivationType (include/oasr/common/types.h:49-56,
+ * oasr/functionals/activation.py:13-25).  OASR_ACT_NONE has no reference id. */
+enum oasr_activation {
+  OASR_ACT_NONE = -1,
+  OASR_ACT_RELU = 0,
+  OASR_ACT_GELU_TANH = 1,
+  OASR_ACT_SWISH = 2,
+  OASR_ACT_GELU_ERF = 4
+};
+
+/* Status codes. */
+enum oasr_status {
+  OASR_OK = 0,
+  OASR_ERR_INVALID = -1,   /* bad shape / size / null pointer            */
+  OASR_ERR_DTYPE = -2,     /* element type not supported by this op      */
+  OASR_ERR_ALIGN = -3,     /* pointer or extent violates an alignment    */
+  OASR_ERR_CUDA = -4,      /* a CUDA runtime / driver call failed        */
+  OASR_ERR_UNSUPPORTED = -5,
+  OASR_ERR_DEVICE_WAIT = -6 /* a bounded device-side wait gave up        */
+};
+
+/* ---- library ---------------------------------------------------------- */
+
+/* "oasr_b200 <version> sm_100a" */
+OASR_API const char* oasr_b200_version(void);
+/* Message of the last failing call made by this thread ("" if none). */
+OASR_API const char* oasr_b200_last_error(void);
+/* Reads and clears the device-side status word that kernels with bounded
+ * waits (TMA / tcgen05 pipelines) write when a wait gives up.  Synchronises
+ * `stream`.  Returns 0 when no kernel reported a problem, else
+ * OASR_ERR_DEVICE_WAIT with the raw word in *word (nullable). */
+OASR_API int oasr_b200_device_status(uint32_t* word /*host*/, void* stream);
+/* Process-wide integer tunables.  "gemm_bn": 0 = heuristic tile width, or 64 /
+ * 128 / 256 to force it (no reference counterpart; the reference selects tiles
+ * through its JIT variant names, oasr/jit/gemm.py:863-880). */
+OASR_API int oasr_b200_set_tunable(const char* name, int value);
+
+/* ---- norms ------------------------------------------------------------ */
+/* rows = product of leading dims, hidden = trailing dim.  weight/bias and the
+ * batch-norm statistics have `hidden` elements of the activation dtype. */
+
+/* out = LN(in).  Replaces layernorm (csrc/norm_jit_binding.cu:9, kernel
+ * include/oasr/norm.cuh:28-93). */
+OASR_API int oasr_b200_layer_norm(void* out, const void* in, const void* weight,
+                                  const void* bias /*nullable*/, int64_t rows, int64_t hidden,
+                                  double eps, int dtype, void* stream);
+/* out = act(LN(in)).  Replaces layernorm_activation (csrc/norm_jit_binding.cu:28). */
+OASR_API int oasr_b200_layer_norm_activation(void* out, const void* in, const void* weight,
+                                             const void* bias /*nullable*/, int64_t rows,
+                                             int64_t hidden, double eps, int activation, int dtype,
+                                             void* stream);
+/* out = LN(residual + alpha*in), sum kept in fp32.  Replaces addlayernorm
+ * (csrc/norm_jit_binding.cu:17, kernel include/oasr/norm.cuh:307-382). */
+OASR_API int oasr_b200_add_layer_norm(void* out, const void* in, const void* residual,
+                                      const void* weight, const void* bias /*nullable*/,
+                                      int64_t rows, int64_t hidden, double eps, double alpha,
+                                      int dtype, void* stream);
+/* As above and residual_out = cast(residual + alpha*in), rounded once.
+ * Replaces addlayernorm_residual (csrc/norm_jit_binding.cu:19, kernel
+ * include/oasr/norm.cuh:396-484). */
+OASR_API int oasr_b200_add_layer_norm_residual(void* out, void* residual_out, const void* in,
+                                               const void* residual, const void* weight,
+                                               const void* bias /*nullable*/, int64_t rows,
+                                               int64_t hidden, double eps, double alpha, int dtype,
+                                               void* stream);
+/* out = RMSNorm(in) (+bias).  Replaces rmsnorm (csrc/norm_jit_binding.cu:11,
+ * kernel include/oasr/norm.cuh:99-147). */
+OASR_API int oasr_b200_rms_norm(void* out, const void* in, const void* weight,
+                                const void* bias /*nullable*/, int64_t rows, int64_t hidden,
+                                double eps, int dtype, void* stream);
+/* Replaces rmsnorm_activation (csrc/norm_jit_binding.cu:30). */
+OASR_API int oasr_b200_rms_norm_activation(void* out, const void* in, const void* weight,
+                                           const void* bias /*nullable*/, int64_t rows,
+                                           int64_t hidden, double eps, int activation, int dtype,
+                                           void* stream);
+/* Replaces addrmsnorm (csrc/norm_jit_binding.cu:22). */
+OASR_API int oasr_b200_add_rms_norm(void* out, const void* in, const void* residual,
+                                    const void* weight, const void* bias /*nullable*/, int64_t rows,
+                                    int64_t hidden, double eps, double alpha, int dtype,
+                                    void* stream);
+/* Replaces addrmsnorm_residual (csrc/norm_jit_binding.cu:24). */
+OASR_API int oasr_b200_add_rms_norm_residual(void* out, void* residual_out, const void* in,
+                                             const void* residual, const void* weight,
+                                             const void* bias /*nullable*/, int64_t rows,
+                                             int64_t hidden, double eps, double alpha, int dtype,
+                                             void* stream);
+/* Inference batch norm over channels-last rows, optional activation
+ * (activation = OASR_ACT_NONE for plain BN).  Replaces batchnorm1d,
+ * batchnorm_activation and batchnorm_swish (csrc/norm_jit_binding.cu:13,32,35;
+ * kernels include/oasr/norm.cuh:153-187,779-813). */
+OASR_API int oasr_b200_batch_norm(void* out, const void* in, const void* weight, const void* bias,
+                                  const void* running_mean, const void* running_var, int64_t rows,
+                                  int64_t channels, double eps, int activation, int dtype,
+                                  void* stream);
+
+/* ---- activations ------------------------------------------------------ */
+/* out[r, c] = in[r, c] * sigmoid(in[r, channels + c]); in has 2*channels
+ * columns.  Replaces glu (csrc/activation_jit_binding.cu:9, kernel
+ * include/oasr/activation.cuh:25-60). */
+OASR_API int oasr_b200_glu(void* out, const void* in, int64_t rows, int64_t channels, int dtype,
+                           void* stream);
+/* out = in * sigmoid(in).  Replaces swish (csrc/activation_jit_binding.cu:13,
+ * kernel include/oasr/activation.cuh:66-87). */
+OASR_API int oasr_b200_swish(void* out, const void* in, int64_t numel, int dtype, void* stream);
+
+/* ---- depthwise conv1d -------------------------------------------------- */
+/* in (batch, seq_len, channels), weight (kernel_size, channels), out
+ * (batch, out_len, channels) with out_len = seq_len + pad_left + pad_right -
+ * kernel_size + 1.  `mask` (nullable) is (batch, seq_len) in the activation
+ * dtype (mask_is_bool = 0) or one byte per frame (mask_is_bool = 1) and is
+ * applied to the input and to the output; add_input adds the (masked) input
+ * frame before the output mask (both need out_len == seq_len).  activation is
+ * OASR_ACT_NONE or OASR_ACT_SWISH.  Replaces depthwise_conv1d and
+ * depthwise_conv1d_silu (csrc/conv_jit_binding.cu:9-13, kernels
+ * include/oasr/conv/conv1d.cuh:23-181). */
+OASR_API int oasr_b200_depthwise_conv1d(void* out, const void* in, const void* weight,
+                                        const void* bias /*nullable*/, int64_t batch,
+                                        int64_t seq_len, int64_t channels, int64_t kernel_size,
+                                        int64_t pad_left, int64_t pad_right,
+                                        const void* mask /*nullable*/, int mask_is_bool,
+                                        int add_input, int activation, int dtype, void* stream);
+/* Streaming causal depthwise conv with a rolling state: in (batch, seq_len,
+ * channels), state (batch, kernel_size-1, channels) updated in place to the
+ * last kernel_size-1 frames of [state, in], weight (channels, kernel_size).
+ * Replaces causal_conv1d (csrc/conv_jit_binding.cu:14, kernels
+ * include/oasr/conv/conv1d.cuh:187-269,450-473). */
+OASR_API int oasr_b200_causal_conv1d(void* out, const void* in, void* state, const void* weight,
+                                     const void* bias /*nullable*/, int64_t batch, int64_t seq_len,
+                                     int64_t channels, int64_t kernel_size, int dtype,
+                                     void* stream);
+
+/* ---- GEMM family (tcgen05 / TMEM / TMA) -------------------------------- */
+/* D[M,N] = act(A[M,K] . B[N,K]^T + bias[N]); A, B, D row-major, fp16 or
+ * bf16, fp32 accumulation in tensor memory, one rounding on store.  N and K
+ * must be multiples of 8 and all pointers 16-byte aligned.  activation =
+ * OASR_ACT_NONE gives the plain GEMM.  Replaces gemm / gemm_activation
+ * (csrc/gemm_jit_binding.cu:9-16, launchers csrc/gemm.cu:40-115). */
+OASR_API int oasr_b200_gemm(void* D, const void* A, const void* B, const void* bias /*nullable*/,
+                            int64_t M, int64_t N, int64_t K, int activation, int dtype,
+                            void* stream);
+/* Residual form used by the fused encoder layer (no reference counterpart as
+ * an operator; it is the reference's `residual + alpha * Linear(x)` pair,
+ * oasr/models/conformer/model.py:722-751, with the sum kept in fp32):
+ * R_out[M,N] (fp32) = R_in[M,N] (fp32) + alpha * (A . B^T + bias).  R_out may
+ * alias R_in. */
+OASR_API int oasr_b200_gemm_residual_f32(float* R_out, const float* R_in, const void* A,
+                                         const void* B, const void* bias /*nullable*/, int64_t M,
+                                         int64_t N, int64_t K, double alpha, int dtype,
+                                         void* stream);
+/* GLU form: B has 2*N rows; D[M,N] = (A.B[:N]^T + bias[:N]) * sigmoid(A.B[N:]^T
+ * + bias[N:]).  Equals pointwise_conv1 followed by glu
+ * (oasr/models/conformer/model.py:191-192) without the (M, 2N) round trip. */
+OASR_API int oasr_b200_gemm_glu(void* D, const void* A, const void* B,
+                                const void* bias /*nullable*/, int64_t M, int64_t N, int64_t K,
+                                int dtype, void* stream);
+/* D[b] = A[b] . B[b]^T for b < batch; A (batch,M,K), B (batch,N,K).  Replaces
+ * bmm (csrc/bmm.cu, oasr/functionals/gemm.py:262-299). */
+OASR_API int oasr_b200_bmm(void* D, const void* A, const void* B, int64_t batch, int64_t M,
+                           int64_t N, int64_t K, int dtype, void* stream);
+/* Grouped GEMM: rows [offsets[g-1], offsets[g]) of A (L,K) times B[g] (N,K)^T.
+ * `offsets` is a DEVICE int32 array of `groups` cumulative END rows; it is
+ * read on the device (no host synchronisation, unlike the reference launcher
+ * csrc/group_gemm.cu:54-57).  Replaces group_gemm
+ * (csrc/group_gemm_jit_binding.cu:8-12). */
+OASR_API int oasr_b200_group_gemm(void* D, const void* A, const void* B, const int32_t* offsets,
+                                  int64_t L, int64_t groups, int64_t N, int64_t K, int dtype,
+                                  void* stream);
+/* CTC head: out[M,N] = log_softmax(A.B^T + bias) over N, logits never leave
+ * the chip.  out_dtype is OASR_DT_F32 or the activation dtype.  Replaces
+ * gemm_log_softmax (csrc/gemm_log_softmax_jit_binding.cu:8-11, kernel pair
+ * include/oasr/gemm/gemm_log_softmax.cuh:124-166).  `argmax` (nullable,
+ * int32[M]) receives the index of the first maximum of each row. */
+OASR_API int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B,
+                                        const void* bias /*nullable*/, int64_t M, int64_t N,
+                                        int64_t K, int dtype, int out_dtype,
+                                        int32_t* argmax /*nullable*/, void* stream);
+
+/* ---- attention --------------------------------------------------------- */
+/* Dense or paged multi-head attention, the reference's fmha
+ * (oasr/functionals/attention.py:369-551; kernel contract
+ * oasr/kernels/cute/attention/fmha_sm80.py:552, mask rules
+ * oasr/kernels/cute/mask.py:102-117):
+ *   out[b,h,i,:] = softmax_j(q[b,h,i,:].k[b,h/(H/Hkv),j,:]*scale + bias[b,h,i,j]) . v
+ * q, out (B,H,Tq,D); dense k, v (B,Hkv,Tk,D).  bias (nullable) is in the
+ * activation dtype with row stride bias_stride_q and head/batch strides
+ * bias_stride_h / bias_stride_b (elements).  seqlens / seqstarts (nullable,
+ * int32[B]) keep keys in [start, len); causal masks j > i.  Rows with no
+ * visible key produce zeros.  Paged mode (block_table != NULL): k, v are
+ * pools (num_blocks, block_size, Hkv, D), block_table is int32
+ * (B, blocks_per_seq) and Tk = blocks_per_seq * block_size. */
+OASR_API int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v,
+                            const void* bias /*nullable*/, int64_t bias_stride_b,
+                            int64_t bias_stride_h, int64_t bias_stride_q,
+                            const int32_t* seqlens /*nullable*/,
+                            const int32_t* seqstarts /*nullable*/,
+                            const int32_t* block_table /*nullable*/, int64_t blocks_per_seq,
+                            int64_t block_size, int64_t B, int64_t H, int64_t Hkv, int64_t Tq,
+                            int64_t Tk, int64_t D, double scale, int causal, int dtype,
+                            void* stream);
+/* Packed variable-length attention, the reference's fmha_varlen
+ * (oasr/functionals/attention.py:592-693): q, out (total_q,H,D); k, v
+ * (total_k,Hkv,D); cu_seqlens_* int32[S+1]; bias (nullable) flat, segment s is
+ * (H,Tq_s,Tk_s) row-major at bias_offsets[s] (int64[S+1] if
+ * bias_offsets_is_i64 else int32[S+1]). */
+OASR_API int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, const void* v,
+                                   const void* bias /*nullable*/,
+                                   const void* bias_offsets /*nullable*/, int bias_offsets_is_i64,
+                                   const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                   int64_t num_segs, int64_t max_seqlen_q, int64_t H, int64_t Hkv,
+                                   int64_t D, double scale, int dtype, void* stream);
+
+/* ---- paged KV cache ---------------------------------------------------- */
+/* Scatter a chunk of new keys/values into the page pools.  k_new, v_new are
+ * (B, Hkv, T, D) with element strides (sb, sh, st) and unit stride along D;
+ * logical position offsets[b] + t of stream b lands in physical row
+ * block_table[b, pos / block_size] * block_size + pos % block_size of the
+ * pools (num_blocks, block_size, Hkv, D).  Replaces
+ * PagedKVCache.write_kv_chunk / flat_write_index
+ * (oasr/cache/paged_kv.py:23-40,63-137).  elem_bytes is 1, 2 or 4. */
+OASR_API int oasr_b200_paged_kv_write(void* k_pool, void* v_pool, const void* k_new,
+                                      const void* v_new, const int32_t* block_table,
+                                      const int32_t* offsets, int64_t B, int64_t Hkv, int64_t T,
+                                      int64_t D, int64_t stride_b, int64_t stride_h,
+                                      int64_t stride_t, int64_t blocks_per_seq,
+                                      int64_t block_size, int64_t num_blocks, int elem_bytes,
+                                      void* stream);
+/* Gather pages into dense (B, Hkv, blocks_per_seq*block_size, D) tensors.
+ * Replaces gather_paged_kv (oasr/functionals/attention.py:153-178). */
+OASR_API int oasr_b200_paged_kv_gather(void* k_out, void* v_out, const void* k_pool,
+                                       const void* v_pool, const int32_t* block_table, int64_t B,
+                                       int64_t Hkv, int64_t D, int64_t blocks_per_seq,
+                                       int64_t block_size, int64_t num_blocks, int elem_bytes,
+                                       void* stream);
+
+/* ---- packed-layout glue ------------------------------------------------ */
+/* out[i, :] = in[index[i], :] for i < n_out (rows of `row_bytes` bytes,
+ * multiple of 16; index int64; a negative index writes zeros).  Covers
+ * pack_hidden / the gapped-conv gather (oasr/models/conformer/packing.py:222-232,
+ * oasr/models/conformer/model.py:223-233) and SlotTensor.gather
+ * (oasr/cache/state.py:88-94). */
+OASR_API int oasr_b200_gather_rows(void* out, const void* in, const int64_t* index, int64_t n_out,
+                                   int64_t row_bytes, void* stream);
+/* out[index[i], :] = in[i, :] for i < n_in (index_copy_ along rows). */
+OASR_API int oasr_b200_scatter_rows(void* out, const void* in, const int64_t* index, int64_t n_in,
+                                    int64_t row_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OASR_B200_H_ */

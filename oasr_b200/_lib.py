@@ -1,0 +1,124 @@
+"""ctypes binding of liboasr_b200.so (the C-ABI declared in include/oasr_b200.h).
+
+There is no fallback: if the shared library is missing or a symbol cannot be
+resolved, importing an operator raises.  Nothing in this module touches a GPU;
+loading the library and resolving symbols works on a machine without one.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+from ctypes import c_char_p, c_double, c_int, c_int64, c_void_p, POINTER, c_uint32
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "lib" / "liboasr_b200.so"
+
+# Status codes (include/oasr_b200.h: enum oasr_status)
+OK = 0
+ERR_INVALID = -1
+ERR_DTYPE = -2
+ERR_ALIGN = -3
+ERR_CUDA = -4
+ERR_UNSUPPORTED = -5
+ERR_DEVICE_WAIT = -6
+
+# dtype ids (enum oasr_dtype)
+DT_F32, DT_F16, DT_BF16, DT_FP8_E4M3, DT_INT8 = 0, 1, 2, 3, 4
+
+# activation ids (enum oasr_activation)
+ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_SWISH, ACT_GELU_ERF = -1, 0, 1, 2, 4
+
+P = c_void_p
+I = c_int64
+
+# name -> argtypes (restype is int for all of these)
+_SIGNATURES = {
+    "oasr_b200_device_status": [POINTER(c_uint32), P],
+    "oasr_b200_set_tunable": [c_char_p, c_int],
+    "oasr_b200_layer_norm": [P, P, P, P, I, I, c_double, c_int, P],
+    "oasr_b200_layer_norm_activation": [P, P, P, P, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_add_layer_norm": [P, P, P, P, P, I, I, c_double, c_double, c_int, P],
+    "oasr_b200_add_layer_norm_residual": [P, P, P, P, P, P, I, I, c_double, c_double, c_int, P],
+    "oasr_b200_rms_norm": [P, P, P, P, I, I, c_double, c_int, P],
+    "oasr_b200_rms_norm_activation": [P, P, P, P, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_add_rms_norm": [P, P, P, P, P, I, I, c_double, c_double, c_int, P],
+    "oasr_b200_add_rms_norm_residual": [P, P, P, P, P, P, I, I, c_double, c_double, c_int, P],
+    "oasr_b200_batch_norm": [P, P, P, P, P, P, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_glu": [P, P, I, I, c_int, P],
+    "oasr_b200_swish": [P, P, I, c_int, P],
+    "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
+    "oasr_b200_causal_conv1d": [P, P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_gemm": [P, P, P, P, I, I, I, c_int, c_int, P],
+    "oasr_b200_gemm_residual_f32": [P, P, P, P, P, I, I, I, c_double, c_int, P],
+    "oasr_b200_gemm_glu": [P, P, P, P, I, I, I, c_int, P],
+    "oasr_b200_bmm": [P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_group_gemm": [P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_gemm_log_softmax": [P, P, P, P, I, I, I, c_int, c_int, P, P],
+    "oasr_b200_fmha": [P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_fmha_varlen": [P, P, P, P, P, P, c_int, P, P, I, I, I, I, I, c_double, c_int, P],
+    "oasr_b200_paged_kv_write": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, c_int, P],
+    "oasr_b200_paged_kv_gather": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
+    "oasr_b200_gather_rows": [P, P, P, I, I, P],
+    "oasr_b200_scatter_rows": [P, P, P, I, I, P],
+}
+
+_STRING_FUNCS = ("oasr_b200_version", "oasr_b200_last_error")
+
+
+class OasrB200Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+@functools.cache
+def load() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m oasr_b200.build` "
+            "(needs nvcc); there is no fallback path."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name in _STRING_FUNCS:
+        fn = getattr(lib, name)
+        fn.restype = c_char_p
+        fn.argtypes = []
+    for name, argtypes in _SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:  # pragma: no cover - a broken build
+            raise RuntimeError(f"{LIB_PATH} does not export {name}") from e
+        fn.restype = c_int
+        fn.argtypes = argtypes
+    return lib
+
+
+def exported_names() -> list[str]:
+    return list(_STRING_FUNCS) + list(_SIGNATURES)
+
+
+def last_error() -> str:
+    return load().oasr_b200_last_error().decode()
+
+
+def check(code: int) -> None:
+    """Raise the reference-style exception for a failing status."""
+    if code == OK:
+        return
+    msg = last_error()
+    if code in (ERR_INVALID, ERR_ALIGN, ERR_DTYPE, ERR_UNSUPPORTED):
+        # The reference reports launcher validation failures as RuntimeError
+        # (TVM_FFI_ICHECK, csrc/tvm_ffi_utils.h:36-106).
+        raise OasrB200Error(code, msg)
+    raise OasrB200Error(code, msg)
+
+
+def call(name: str, *args) -> None:
+    check(getattr(load(), name)(*args))
+
+
+def version() -> str:
+    return load().oasr_b200_version().decode()

@@ -1,0 +1,124 @@
+// GLU and swish: pure-bandwidth elementwise kernels, 128-bit accesses,
+// grid sized as a multiple of the SM count.  Algorithmic bytes (16-bit type):
+// GLU 6C per output row of width C, swish 4 per element.
+#include "common.cuh"
+
+namespace ob {
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) glu_vec_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                      int64_t rows, int channels) {
+  constexpr int V = Elem<T>::kVec;
+  const int ppr = channels / V;
+  const int64_t total = rows * ppr;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < total; p += stride) {
+    const int64_t r = p / ppr;
+    const int c = static_cast<int>(p - r * ppr) * V;
+    const T* row = in + r * 2 * channels;
+    const Pack<T> a = ld128_stream(row + c);
+    const Pack<T> g = ld128_stream(row + channels + c);
+    Pack<T> o;
+#pragma unroll
+    for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(Elem<T>::to_f(a.v[i]) * sigmoid_f(Elem<T>::to_f(g.v[i])));
+    st128(out + r * channels + c, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) glu_scalar_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                         int64_t rows, int channels) {
+  const int64_t total = rows * channels;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / channels;
+    const int c = static_cast<int>(i - r * channels);
+    const float a = Elem<T>::to_f(in[r * 2 * channels + c]);
+    const float g = Elem<T>::to_f(in[r * 2 * channels + channels + c]);
+    out[i] = Elem<T>::from_f(a * sigmoid_f(g));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) swish_vec_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                        int64_t packs) {
+  constexpr int V = Elem<T>::kVec;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < packs; p += stride) {
+    const Pack<T> a = ld128_stream(in + p * V);
+    Pack<T> o;
+#pragma unroll
+    for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(apply_act<OASR_ACT_SWISH>(Elem<T>::to_f(a.v[i])));
+    st128(out + p * V, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) swish_scalar_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                           int64_t begin, int64_t numel) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < numel; i += stride) {
+    out[i] = Elem<T>::from_f(apply_act<OASR_ACT_SWISH>(Elem<T>::to_f(in[i])));
+  }
+}
+
+unsigned grid_for(int64_t work_items, int block) {
+  int64_t g = (work_items + block - 1) / block;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<unsigned>(g);
+}
+
+}  // namespace
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_glu(void* out, const void* in, int64_t rows, int64_t channels, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(out && in, OASR_ERR_INVALID, "glu: null pointer argument");
+  OB_REQUIRE(rows >= 0 && channels > 0 && channels < (1 << 24), OASR_ERR_INVALID,
+             "glu: bad shape rows=%lld channels=%lld", (long long)rows, (long long)channels);
+  if (rows == 0) return OASR_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int {
+    constexpr int V = Elem<T>::kVec;
+    if (channels % V == 0 && is_aligned(in, 16) && is_aligned(out, 16)) {
+      glu_vec_kernel<T><<<grid_for(rows * (channels / V), 256), 256, 0, s>>>(
+          static_cast<T*>(out), static_cast<const T*>(in), rows, (int)channels);
+    } else {
+      glu_scalar_kernel<T><<<grid_for(rows * channels, 256), 256, 0, s>>>(
+          static_cast<T*>(out), static_cast<const T*>(in), rows, (int)channels);
+    }
+    return check_launch("glu kernel launch");
+  });
+}
+
+int oasr_b200_swish(void* out, const void* in, int64_t numel, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(out && in, OASR_ERR_INVALID, "swish: null pointer argument");
+  OB_REQUIRE(numel >= 0, OASR_ERR_INVALID, "swish: negative element count");
+  if (numel == 0) return OASR_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int {
+    constexpr int V = Elem<T>::kVec;
+    int64_t vec_elems = 0;
+    if (is_aligned(in, 16) && is_aligned(out, 16)) {
+      const int64_t packs = numel / V;
+      vec_elems = packs * V;
+      if (packs > 0) {
+        swish_vec_kernel<T><<<grid_for(packs, 256), 256, 0, s>>>(static_cast<T*>(out),
+                                                                  static_cast<const T*>(in), packs);
+      }
+    }
+    if (vec_elems < numel) {
+      swish_scalar_kernel<T><<<grid_for(numel - vec_elems, 256), 256, 0, s>>>(
+          static_cast<T*>(out), static_cast<const T*>(in), vec_elems, numel);
+    }
+    return check_launch("swish kernel launch");
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,93 @@
+// Library-level entry points: version, per-thread error message, device status word.
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "device_status.cuh"
+
+namespace ob {
+
+static thread_local char g_err[1024] = {0};
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    return set_error(OASR_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  }
+  return OASR_OK;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// One status word per device, living in device memory for the life of the
+// library.  Kernels with bounded waits OR a code into it when a wait gives up.
+__device__ uint32_t g_device_status_word = 0;
+
+uint32_t* device_status_ptr() {
+  static uint32_t* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status_word) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<uint32_t*>(p);
+  }
+  return ptrs[dev];
+}
+
+namespace gemm { extern int g_force_bn; }
+
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_set_tunable(const char* name, int value) {
+  if (name && std::strcmp(name, "gemm_bn") == 0) {
+    if (value != 0 && value != 64 && value != 128 && value != 256)
+      return ob::set_error(OASR_ERR_INVALID, "gemm_bn must be 0, 64, 128 or 256 (got %d)", value);
+    ob::gemm::g_force_bn = value;
+    return OASR_OK;
+  }
+  return ob::set_error(OASR_ERR_INVALID, "unknown tunable '%s'", name ? name : "(null)");
+}
+
+const char* oasr_b200_version(void) { return "oasr_b200 0.1.0 sm_100a"; }
+
+const char* oasr_b200_last_error(void) { return ob::g_err; }
+
+int oasr_b200_device_status(uint32_t* word, void* stream) {
+  uint32_t* dptr = ob::device_status_ptr();
+  if (dptr == nullptr) return ob::set_error(OASR_ERR_CUDA, "device status word is not addressable");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t h = 0;
+  cudaError_t e = cudaMemcpyAsync(&h, dptr, sizeof(h), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return ob::set_error(OASR_ERR_CUDA, "device status read: %s", cudaGetErrorString(e));
+  if (word) *word = h;
+  if (h != 0) {
+    cudaMemsetAsync(dptr, 0, sizeof(h), s);
+    cudaStreamSynchronize(s);
+    return ob::set_error(OASR_ERR_DEVICE_WAIT, "a kernel gave up a bounded wait (status word 0x%08x)", h);
+  }
+  return OASR_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,365 @@
+// Depthwise conv1d over channels-last rows (padded batch or packed segments),
+// with optional per-channel affine (folded inference BatchNorm) and activation,
+// and the streaming causal form with a rolling state.
+//
+// HBM-bound.  Fast path: a thread owns a channel pair and a run of kTile
+// consecutive output frames; the K-frame input window slides through registers
+// so every input frame is loaded once per thread ((kTile+K-1)/kTile re-read
+// factor, served by L1/L2), weights live in registers, lanes of a warp touch
+// 32 adjacent channel pairs (128 contiguous bytes per frame).  Algorithmic
+// bytes per frame of C channels in a 16-bit type: 4C (+2KC weights once).
+// The reference kernel launches one CTA of C/8 threads per output frame and
+// re-reads all K taps and weights per frame (include/oasr/conv/conv1d.cuh:23-113).
+#include "common.cuh"
+
+namespace ob {
+namespace {
+
+template <typename T>
+struct Pair;
+template <>
+struct Pair<float> {
+  __device__ static float2 ld(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  __device__ static void st(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <>
+struct Pair<__half> {
+  __device__ static float2 ld(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+  __device__ static void st(__half* p, float a, float b) { *reinterpret_cast<__half2*>(p) = __floats2half2_rn(a, b); }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  __device__ static float2 ld(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  __device__ static void st(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+};
+
+struct DwArgs {
+  void* out;
+  const void* in;
+  const void* weight;        // (K, C)
+  const void* bias;          // nullable (C)
+  const float* post_scale;   // nullable (C) fp32: y = y*scale + shift applied after bias
+  const float* post_shift;   // nullable (C) fp32
+  const int32_t* cu_seqlens; // nullable: packed mode, (S+1)
+  int64_t batch;             // batch size or number of segments
+  int seq_len;               // padded mode: frames per batch row
+  int out_len;               // padded mode: output frames per batch row
+  int channels;
+  int kernel_size;
+  int pad_left;
+  int act;
+  // generic path only
+  const void* mask;
+  int mask_is_bool;
+  int add_input;
+};
+
+constexpr int kTile = 16;
+
+template <typename T, int K, bool kAffine, bool kAct>
+__global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
+  const int cp = blockIdx.x * blockDim.x + threadIdx.x;  // channel pair
+  const int C = a.channels;
+  if (cp * 2 >= C) return;
+  const int c = cp * 2;
+  const int64_t b = blockIdx.z;
+  int64_t in_row0, out_row0;
+  int TL, OL;
+  if (a.cu_seqlens) {
+    const int s0 = a.cu_seqlens[b], s1 = a.cu_seqlens[b + 1];
+    TL = s1 - s0;
+    OL = TL;
+    in_row0 = s0;
+    out_row0 = s0;
+  } else {
+    TL = a.seq_len;
+    OL = a.out_len;
+    in_row0 = b * a.seq_len;
+    out_row0 = b * a.out_len;
+  }
+  const int t0 = blockIdx.y * kTile;
+  if (t0 >= OL) return;
+  const T* in = static_cast<const T*>(a.in) + in_row0 * C + c;
+  T* out = static_cast<T*>(a.out) + out_row0 * C + c;
+  const T* w = static_cast<const T*>(a.weight) + c;
+
+  float w0[K], w1[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const float2 ww = Pair<T>::ld(w + static_cast<int64_t>(k) * C);
+    w0[k] = ww.x;
+    w1[k] = ww.y;
+  }
+  float b0 = 0.f, b1 = 0.f;
+  if (a.bias) {
+    const float2 bb = Pair<T>::ld(static_cast<const T*>(a.bias) + c);
+    b0 = bb.x;
+    b1 = bb.y;
+  }
+  float sc0 = 1.f, sc1 = 1.f, sh0 = 0.f, sh1 = 0.f;
+  if constexpr (kAffine) {
+    sc0 = a.post_scale[c];
+    sc1 = a.post_scale[c + 1];
+    sh0 = a.post_shift[c];
+    sh1 = a.post_shift[c + 1];
+  }
+
+  // window[k] holds input frame (t - pad_left + k) for the current output t.
+  float x0[K], x1[K];
+  const int first = t0 - a.pad_left;
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) {
+    const int ti = first + k;
+    float2 v = make_float2(0.f, 0.f);
+    if (ti >= 0 && ti < TL) v = Pair<T>::ld(in + static_cast<int64_t>(ti) * C);
+    x0[k] = v.x;
+    x1[k] = v.y;
+  }
+#pragma unroll
+  for (int j = 0; j < kTile; ++j) {
+    const int t = t0 + j;
+    if (t < OL) {
+      const int ti = first + j + K - 1;
+      float2 v = make_float2(0.f, 0.f);
+      if (ti >= 0 && ti < TL) v = Pair<T>::ld(in + static_cast<int64_t>(ti) * C);
+      x0[K - 1] = v.x;
+      x1[K - 1] = v.y;
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        acc0 = fmaf(x0[k], w0[k], acc0);
+        acc1 = fmaf(x1[k], w1[k], acc1);
+      }
+      acc0 += b0;
+      acc1 += b1;
+      if constexpr (kAffine) {
+        acc0 = fmaf(acc0, sc0, sh0);
+        acc1 = fmaf(acc1, sc1, sh1);
+      }
+      if constexpr (kAct) {
+        acc0 = apply_act_rt(acc0, a.act);
+        acc1 = apply_act_rt(acc1, a.act);
+      }
+      Pair<T>::st(out + static_cast<int64_t>(t) * C, acc0, acc1);
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k) {
+        x0[k] = x0[k + 1];
+        x1[k] = x1[k + 1];
+      }
+    }
+  }
+}
+
+// Any kernel size / channel count, optional mask and add_input
+// (include/oasr/conv/conv1d.cuh:23-113 semantics).  One thread per output element.
+template <typename T>
+__global__ void __launch_bounds__(256) dwconv_generic_kernel(DwArgs a) {
+  const int C = a.channels;
+  const int64_t total = a.batch * a.out_len * C;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const T* mask_t = static_cast<const T*>(a.mask);
+  const uint8_t* mask_b = static_cast<const uint8_t*>(a.mask);
+  auto mask_at = [&](int64_t b, int t) -> float {
+    if (!a.mask) return 1.f;
+    const int64_t i = b * a.seq_len + t;
+    return a.mask_is_bool ? (mask_b[i] ? 1.f : 0.f) : Elem<T>::to_f(mask_t[i]);
+  };
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = static_cast<int>(i % C);
+    const int t = static_cast<int>((i / C) % a.out_len);
+    const int64_t b = i / (static_cast<int64_t>(C) * a.out_len);
+    const T* in = static_cast<const T*>(a.in) + b * a.seq_len * C + c;
+    const T* w = static_cast<const T*>(a.weight) + c;
+    float acc = 0.f;
+    for (int k = 0; k < a.kernel_size; ++k) {
+      const int ti = t - a.pad_left + k;
+      if (ti < 0 || ti >= a.seq_len) continue;
+      float v = Elem<T>::to_f(in[static_cast<int64_t>(ti) * C]);
+      v *= mask_at(b, ti);
+      acc = fmaf(v, Elem<T>::to_f(w[static_cast<int64_t>(k) * C]), acc);
+    }
+    if (a.bias) acc += Elem<T>::to_f(static_cast<const T*>(a.bias)[c]);
+    if (a.post_scale) acc = fmaf(acc, a.post_scale[c], a.post_shift[c]);
+    if (a.add_input) acc += Elem<T>::to_f(in[static_cast<int64_t>(t) * C]) * mask_at(b, t);
+    if (a.mask) acc *= mask_at(b, t);
+    acc = apply_act_rt(acc, a.act);
+    static_cast<T*>(a.out)[i] = Elem<T>::from_f(acc);
+  }
+}
+
+template <typename T, int K>
+int launch_window(const DwArgs& a, int max_out_len, cudaStream_t s) {
+  dim3 block(128);
+  dim3 grid((a.channels / 2 + 127) / 128, (max_out_len + kTile - 1) / kTile, static_cast<unsigned>(a.batch));
+  const bool affine = a.post_scale != nullptr;
+  const bool act = a.act != OASR_ACT_NONE;
+  if (affine && act) dwconv_window_kernel<T, K, true, true><<<grid, block, 0, s>>>(a);
+  else if (affine) dwconv_window_kernel<T, K, true, false><<<grid, block, 0, s>>>(a);
+  else if (act) dwconv_window_kernel<T, K, false, true><<<grid, block, 0, s>>>(a);
+  else dwconv_window_kernel<T, K, false, false><<<grid, block, 0, s>>>(a);
+  return check_launch("depthwise_conv1d kernel launch");
+}
+
+template <typename T>
+int launch_dw(const DwArgs& a, int max_out_len, cudaStream_t s) {
+  const bool plain = a.mask == nullptr && !a.add_input;
+  const bool fast = plain && a.channels % 2 == 0 && is_aligned(a.in, 2 * sizeof(T)) &&
+                    is_aligned(a.out, 2 * sizeof(T)) && is_aligned(a.weight, 2 * sizeof(T)) &&
+                    (!a.bias || is_aligned(a.bias, 2 * sizeof(T))) && a.batch <= 65535 &&
+                    (max_out_len + kTile - 1) / kTile <= 65535;
+  if (fast) {
+    switch (a.kernel_size) {
+      case 3: return launch_window<T, 3>(a, max_out_len, s);
+      case 5: return launch_window<T, 5>(a, max_out_len, s);
+      case 7: return launch_window<T, 7>(a, max_out_len, s);
+      case 9: return launch_window<T, 9>(a, max_out_len, s);
+      case 11: return launch_window<T, 11>(a, max_out_len, s);
+      case 15: return launch_window<T, 15>(a, max_out_len, s);
+      case 31: return launch_window<T, 31>(a, max_out_len, s);
+      default: break;
+    }
+  }
+  if (a.cu_seqlens) {
+    return set_error(OASR_ERR_UNSUPPORTED,
+                     "packed depthwise conv supports kernel sizes 3/5/7/9/11/15/31 and even channel counts");
+  }
+  int64_t total = a.batch * a.out_len * a.channels;
+  int64_t g = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (g > cap) g = cap;
+  dwconv_generic_kernel<T><<<static_cast<unsigned>(g), 256, 0, s>>>(a);
+  return check_launch("depthwise_conv1d (generic) kernel launch");
+}
+
+// ---------------------------------------------------------------------------
+// Streaming causal conv with rolling state.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) causal_conv_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                          const T* __restrict__ state,
+                                                          const T* __restrict__ weight,  // (C, K)
+                                                          const T* __restrict__ bias, int64_t batch,
+                                                          int seq_len, int C, int K) {
+  const int64_t total = batch * seq_len * C;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int SL = K - 1;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = static_cast<int>(i % C);
+    const int t = static_cast<int>((i / C) % seq_len);
+    const int64_t b = i / (static_cast<int64_t>(C) * seq_len);
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int pos = t - SL + k;
+      const float v = pos < 0 ? Elem<T>::to_f(state[(b * SL + (SL + pos)) * C + c])
+                              : Elem<T>::to_f(in[(b * seq_len + pos) * C + c]);
+      acc = fmaf(v, Elem<T>::to_f(weight[static_cast<int64_t>(c) * K + k]), acc);
+    }
+    if (bias) acc += Elem<T>::to_f(bias[c]);
+    out[i] = Elem<T>::from_f(acc);
+  }
+}
+
+// One thread owns one (batch, channel) column of the state and walks it in
+// ascending order, so the in-place left shift reads every slot before it is
+// overwritten.
+template <typename T>
+__global__ void __launch_bounds__(256) causal_state_update_kernel(T* __restrict__ state,
+                                                                  const T* __restrict__ in, int64_t batch,
+                                                                  int seq_len, int C, int SL) {
+  const int64_t total = batch * C;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % C);
+  const int64_t b = i / C;
+  T* st = state + b * SL * C + c;
+  const T* x = in + b * seq_len * C + c;
+  if (seq_len >= SL) {
+    for (int s = 0; s < SL; ++s) st[static_cast<int64_t>(s) * C] = x[static_cast<int64_t>(seq_len - SL + s) * C];
+  } else {
+    const int shift = SL - seq_len;
+    for (int s = 0; s < shift; ++s) st[static_cast<int64_t>(s) * C] = st[static_cast<int64_t>(s + seq_len) * C];
+    for (int s = shift; s < SL; ++s) st[static_cast<int64_t>(s) * C] = x[static_cast<int64_t>(s - shift) * C];
+  }
+}
+
+}  // namespace
+
+// Internal (C++) entry used by the fused encoder: packed segments, "same"
+// padding, optional folded-BatchNorm affine and activation.
+int depthwise_conv1d_packed(void* out, const void* in, const void* weight, const void* bias,
+                            const float* post_scale, const float* post_shift, const int32_t* cu_seqlens,
+                            int64_t num_segs, int max_seg_len, int channels, int kernel_size, int act,
+                            int dtype, cudaStream_t stream) {
+  OB_REQUIRE(out && in && weight && cu_seqlens, OASR_ERR_INVALID, "packed depthwise conv: null pointer");
+  OB_REQUIRE(kernel_size % 2 == 1, OASR_ERR_INVALID, "packed depthwise conv needs an odd kernel size");
+  if (num_segs == 0 || max_seg_len == 0) return OASR_OK;
+  DwArgs a{};
+  a.out = out; a.in = in; a.weight = weight; a.bias = bias;
+  a.post_scale = post_scale; a.post_shift = post_shift; a.cu_seqlens = cu_seqlens;
+  a.batch = num_segs; a.seq_len = 0; a.out_len = 0; a.channels = channels;
+  a.kernel_size = kernel_size; a.pad_left = (kernel_size - 1) / 2; a.act = act;
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, max_seg_len, stream); });
+}
+
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_depthwise_conv1d(void* out, const void* in, const void* weight, const void* bias,
+                               int64_t batch, int64_t seq_len, int64_t channels, int64_t kernel_size,
+                               int64_t pad_left, int64_t pad_right, const void* mask, int mask_is_bool,
+                               int add_input, int activation, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "depthwise_conv1d: null pointer argument");
+  OB_REQUIRE(batch >= 0 && seq_len >= 0 && channels > 0 && kernel_size > 0 && pad_left >= 0 && pad_right >= 0,
+             OASR_ERR_INVALID, "depthwise_conv1d: bad shape");
+  OB_REQUIRE(channels < (1 << 24) && seq_len < (1 << 30) && kernel_size < (1 << 16), OASR_ERR_INVALID,
+             "depthwise_conv1d: extent too large");
+  const int64_t out_len = seq_len + pad_left + pad_right - kernel_size + 1;
+  OB_REQUIRE(out_len > 0, OASR_ERR_INVALID, "depthwise_conv1d has invalid output length %lld", (long long)out_len);
+  OB_REQUIRE(!(mask || add_input) || out_len == seq_len, OASR_ERR_INVALID,
+             "depthwise_conv1d: mask / add_input need out_len == seq_len");
+  OB_REQUIRE(activation == OASR_ACT_NONE || activation == OASR_ACT_SWISH, OASR_ERR_INVALID,
+             "depthwise_conv1d: activation must be none or swish");
+  if (batch == 0) return OASR_OK;
+  DwArgs a{};
+  a.out = out; a.in = in; a.weight = weight; a.bias = bias;
+  a.batch = batch; a.seq_len = (int)seq_len; a.out_len = (int)out_len; a.channels = (int)channels;
+  a.kernel_size = (int)kernel_size; a.pad_left = (int)pad_left; a.act = activation;
+  a.mask = mask; a.mask_is_bool = mask_is_bool; a.add_input = add_input;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, (int)out_len, s); });
+}
+
+int oasr_b200_causal_conv1d(void* out, const void* in, void* state, const void* weight, const void* bias,
+                            int64_t batch, int64_t seq_len, int64_t channels, int64_t kernel_size, int dtype,
+                            void* stream) {
+  using namespace ob;
+  OB_REQUIRE(out && in && state && weight, OASR_ERR_INVALID, "causal_conv1d: null pointer argument");
+  OB_REQUIRE(batch >= 0 && seq_len > 0 && channels > 0 && kernel_size > 1, OASR_ERR_INVALID,
+             "causal_conv1d: bad shape");
+  if (batch == 0) return OASR_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int {
+    const int64_t total = batch * seq_len * channels;
+    int64_t g = (total + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (g > cap) g = cap;
+    causal_conv_kernel<T><<<static_cast<unsigned>(g), 256, 0, s>>>(
+        static_cast<T*>(out), static_cast<const T*>(in), static_cast<const T*>(state),
+        static_cast<const T*>(weight), static_cast<const T*>(bias), batch, (int)seq_len, (int)channels,
+        (int)kernel_size);
+    if (int rc = check_launch("causal_conv1d kernel launch")) return rc;
+    const int64_t cols = batch * channels;
+    causal_state_update_kernel<T><<<static_cast<unsigned>((cols + 255) / 256), 256, 0, s>>>(
+        static_cast<T*>(state), static_cast<const T*>(in), batch, (int)seq_len, (int)channels,
+        (int)kernel_size - 1);
+    return check_launch("causal_conv1d state update launch");
+  });
+}
+
+}  // extern "C"

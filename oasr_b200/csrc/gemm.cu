@@ -1,0 +1,749 @@
+// GEMM family on the 5th-generation tensor cores:
+//   D[M,N] = epilogue(A[M,K] . B[N,K]^T + bias[N]),  A/B fp16 or bf16, fp32 accumulate.
+//
+// One persistent, warp-specialised kernel (192 threads, one CTA per SM):
+//   warp 0   TMA producer: streams 128x64 A tiles and BNx64 B tiles (128-byte
+//            swizzle) into a kStages-deep shared-memory ring, one mbarrier pair
+//            (full/empty) per stage;
+//   warp 1   MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN,
+//            K=16) four times per stage into a TMEM accumulator and commits the
+//            stage back to the producer; owns the TMEM allocation (2 x BN
+//            columns, so the epilogue of tile i overlaps the main loop of i+1);
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = row, 32 columns per
+//            load), apply bias / activation / residual / GLU / log-softmax in
+//            fp32 and store with one rounding.
+// Tensor-pipe bound; algorithmic flops 2*M*N*K.  No cluster launch and no TMA
+// multicast: every CTA loads its own operands.
+//
+// The reference reaches the same tensor cores through CUTLASS 3.x with one
+// fixed 128x128x128 tile (include/oasr/gemm/gemm.cuh:57-59,
+// oasr/jit/gemm.py:863-880); epilogue numerics follow its fusion functors
+// (include/oasr/common/epilogue_functors.h): fp32 accumulate, + bias in fp32,
+// activation in fp32, one rounding to the output type.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <type_traits>
+
+#include "common.cuh"
+#include "device_status.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.cuh"
+
+namespace ob {
+namespace gemm {
+
+constexpr int BM = 128;   // rows per tile (= UMMA M, = TMEM lanes)
+constexpr int BK = 64;    // K elements per stage (= 128 bytes = one swizzle row)
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+
+enum Epi { kEpiStore = 0, kEpiResid = 1, kEpiGlu = 2, kEpiLsm = 3 };
+enum Sched { kSchedDense = 0, kSchedGroup = 1, kSchedSweep = 2 };
+
+struct Params {
+  int M, N, K;            // per-problem extents (N = output columns)
+  int batch;              // dense: number of independent problems (bmm)
+  int num_m_tiles, num_n_tiles, num_k_blocks;
+  int groups;             // grouped: number of groups
+  const int32_t* offsets; // grouped: cumulative end rows (device)
+  void* D;                // output (T, or float for kEpiResid / fp32 log-probs)
+  const void* bias;       // nullable, T[N] (GLU: T[2N])
+  const float* R_in;      // kEpiResid
+  float alpha;
+  int act;
+  int out_f32;            // kEpiLsm: 1 = fp32 output, 0 = T output
+  int32_t* argmax;        // kEpiLsm: nullable
+  uint32_t* status;       // device status word (nullable)
+};
+
+struct Tile {
+  int a_row, a_batch;   // TMA coordinates of the A tile
+  int b_row, b_batch;   // TMA coordinates of the B tile
+  int64_t out_row;      // first output row of the tile
+  int64_t row_end;      // rows >= row_end are not stored
+  int n0;               // first output column
+  int pass, n_idx;      // sweep scheduler only
+};
+
+template <int kSched, int BN>
+struct Scheduler {
+  const Params& p;
+  __device__ explicit Scheduler(const Params& p_) : p(p_) {}
+  // iter-th work item of this CTA; false when the CTA has no more work.
+  __device__ bool get(int iter, Tile& t) const {
+    if constexpr (kSched == kSchedDense) {
+      const int64_t per_batch = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
+      const int64_t w = blockIdx.x + static_cast<int64_t>(iter) * gridDim.x;
+      if (w >= per_batch * p.batch) return false;
+      const int b = static_cast<int>(w / per_batch);
+      const int r = static_cast<int>(w - b * per_batch);
+      const int m = r / p.num_n_tiles, n = r - m * p.num_n_tiles;
+      t.a_row = m * BM; t.a_batch = b;
+      t.b_row = n * BN; t.b_batch = b;
+      t.out_row = static_cast<int64_t>(b) * p.M + m * BM;
+      t.row_end = static_cast<int64_t>(b) * p.M + p.M;
+      t.n0 = n * BN;
+      t.pass = 0; t.n_idx = n;
+      return true;
+    } else if constexpr (kSched == kSchedGroup) {
+      int64_t w = blockIdx.x + static_cast<int64_t>(iter) * gridDim.x;
+      int start = 0;
+      for (int g = 0; g < p.groups; ++g) {
+        const int end = p.offsets[g];
+        const int rows = end - start;
+        const int64_t tiles = static_cast<int64_t>((rows + BM - 1) / BM) * p.num_n_tiles;
+        if (w < tiles) {
+          const int m = static_cast<int>(w / p.num_n_tiles), n = static_cast<int>(w - static_cast<int64_t>(m) * p.num_n_tiles);
+          t.a_row = start + m * BM; t.a_batch = 0;
+          t.b_row = n * BN; t.b_batch = g;
+          t.out_row = t.a_row;
+          t.row_end = end;
+          t.n0 = n * BN;
+          t.pass = 0; t.n_idx = n;
+          return true;
+        }
+        w -= tiles;
+        start = end;
+      }
+      return false;
+    } else {
+      const int per_row_tile = 2 * p.num_n_tiles;
+      const int64_t m = blockIdx.x + static_cast<int64_t>(iter / per_row_tile) * gridDim.x;
+      if (m >= p.num_m_tiles) return false;
+      const int sub = iter % per_row_tile;
+      t.pass = sub / p.num_n_tiles;
+      t.n_idx = sub - t.pass * p.num_n_tiles;
+      t.a_row = static_cast<int>(m) * BM; t.a_batch = 0;
+      t.b_row = t.n_idx * BN; t.b_batch = 0;
+      t.out_row = m * BM;
+      t.row_end = p.M;
+      t.n0 = t.n_idx * BN;
+      return true;
+    }
+  }
+};
+
+template <int BN, int kStages>
+struct Smem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBarOffset = kStages * (kABytes + kBBytes);
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ float bits_f(uint32_t u) { return __uint_as_float(u); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 8 consecutive bias values as floats (T is 16-bit; p is 16-byte aligned).
+template <typename T>
+__device__ __forceinline__ void load_bias8(const T* p, float (&f)[8]) {
+  Pack<T> v = ld128_nc(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = Elem<T>::to_f(v.v[i]);
+}
+
+template <typename T, int BN, int kStages, int kSched, int kEpi>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const Params p) {
+  using S = Smem<BN, kStages>;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr uint32_t kIdesc = ptx::umma_idesc_f16(kBf16, BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kStages * S::kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&full_bar[i], 1);
+      ptx::mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&tfull_bar[i], 1);
+      ptx::mbar_init(&tempty_bar[i], kEpiWarps);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  Scheduler<kSched, BN> sched(p);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      Tile t;
+      bool ok = true;
+      for (int iter = 0; ok && sched.get(iter, t); ++iter) {
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          ptx::mbar_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
+          ptx::tma_load_3d(sA + stage * S::kABytes, &tmap_a, kb * BK, t.a_row, t.a_batch, &full_bar[stage]);
+          if constexpr (kEpi == kEpiGlu) {
+            // value rows [n0/2, +BN/2) and gate rows [N + n0/2, +BN/2) of the 2N-row weight
+            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * BK, t.b_row / 2, t.b_batch, &full_bar[stage]);
+            ptx::tma_load_3d(sB + stage * S::kBBytes + S::kBBytes / 2, &tmap_b, kb * BK, p.N + t.b_row / 2,
+                             t.b_batch, &full_bar[stage]);
+          } else {
+            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * BK, t.b_row, t.b_batch, &full_bar[stage]);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && p.status) atomicOr(p.status, kStatusGemmProducer);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      Tile t;
+      bool ok = true;
+      for (int iter = 0; ok && sched.get(iter, t); ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1u;
+        if (!ptx::mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(sA + stage * S::kABytes);
+          const uint32_t b_addr = ptx::smem_u32(sB + stage * S::kBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = ptx::smem_desc_kmajor_sw128(a_addr + k * UMMA_K * 2);
+            const uint64_t bdesc = ptx::smem_desc_kmajor_sw128(b_addr + k * UMMA_K * 2);
+            ptx::umma_f16(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::umma_commit(&tfull_bar[acc]);
+      }
+      if (!ok && p.status) atomicOr(p.status, kStatusGemmMma);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    Tile t;
+    bool ok = true;
+    // kEpiLsm running statistics of this thread's row
+    float run_max = -INFINITY, run_sum = 0.f, lse = 0.f;
+    int run_arg = 0;
+    for (int iter = 0; ok && sched.get(iter, t); ++iter) {
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1u;
+      if (!ptx::mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const int64_t row = t.out_row + q * 32 + lane;
+      const bool row_ok = row < t.row_end;
+      const uint32_t t_acc = tmem_base + lane_base + acc * BN;
+
+      if constexpr (kEpi == kEpiStore) {
+        T* drow = static_cast<T*>(p.D) + row * p.N;
+        const T* bias = static_cast<const T*>(p.bias);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + c0, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = t.n0 + c0 + g * 8;
+            if (col < p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g * 8 + i]);
+              if (bias) {
+                float bb[8];
+                load_bias8(bias + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += bb[i];
+              }
+              if (p.act != OASR_ACT_NONE) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = apply_act_rt(v[i], p.act);
+              }
+              if (row_ok) {
+                uint4 o;
+                o.x = pack2<T>(v[0], v[1]); o.y = pack2<T>(v[2], v[3]);
+                o.z = pack2<T>(v[4], v[5]); o.w = pack2<T>(v[6], v[7]);
+                *reinterpret_cast<uint4*>(drow + col) = o;
+              }
+            }
+          }
+        }
+      } else if constexpr (kEpi == kEpiResid) {
+        float* orow = static_cast<float*>(p.D) + row * p.N;
+        const float* rrow = p.R_in + row * p.N;
+        const T* bias = static_cast<const T*>(p.bias);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + c0, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = t.n0 + c0 + g * 8;
+            if (col < p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g * 8 + i]);
+              if (bias) {
+                float bb[8];
+                load_bias8(bias + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += bb[i];
+              }
+              if (row_ok) {
+                const float4 r0 = *reinterpret_cast<const float4*>(rrow + col);
+                const float4 r1 = *reinterpret_cast<const float4*>(rrow + col + 4);
+                float4 o0, o1;
+                o0.x = fmaf(p.alpha, v[0], r0.x); o0.y = fmaf(p.alpha, v[1], r0.y);
+                o0.z = fmaf(p.alpha, v[2], r0.z); o0.w = fmaf(p.alpha, v[3], r0.w);
+                o1.x = fmaf(p.alpha, v[4], r1.x); o1.y = fmaf(p.alpha, v[5], r1.y);
+                o1.z = fmaf(p.alpha, v[6], r1.z); o1.w = fmaf(p.alpha, v[7], r1.w);
+                *reinterpret_cast<float4*>(orow + col) = o0;
+                *reinterpret_cast<float4*>(orow + col + 4) = o1;
+              }
+            }
+          }
+        }
+      } else if constexpr (kEpi == kEpiGlu) {
+        // accumulator columns [0, BN/2) hold the value half, [BN/2, BN) the gate half
+        constexpr int HN = BN / 2;
+        const int n0 = t.n0 / 2;
+        T* drow = static_cast<T*>(p.D) + row * p.N;
+        const T* bias = static_cast<const T*>(p.bias);
+#pragma unroll 1
+        for (int c0 = 0; c0 < HN; c0 += 32) {
+          if (n0 + c0 >= p.N) break;
+          uint32_t rv[32], rg[32];
+          ptx::tmem_ld_32x32(t_acc + c0, rv);
+          ptx::tmem_ld_32x32(t_acc + HN + c0, rg);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = n0 + c0 + g * 8;
+            if (col < p.N) {
+              float v[8], gt[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { v[i] = bits_f(rv[g * 8 + i]); gt[i] = bits_f(rg[g * 8 + i]); }
+              if (bias) {
+                float bb[8];
+                load_bias8(bias + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += bb[i];
+                load_bias8(bias + p.N + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) gt[i] += bb[i];
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] *= sigmoid_f(gt[i]);
+              if (row_ok) {
+                uint4 o;
+                o.x = pack2<T>(v[0], v[1]); o.y = pack2<T>(v[2], v[3]);
+                o.z = pack2<T>(v[4], v[5]); o.w = pack2<T>(v[6], v[7]);
+                *reinterpret_cast<uint4*>(drow + col) = o;
+              }
+            }
+          }
+        }
+      } else {
+        // kEpiLsm.  Pass 0: running (max, sum of exp, argmax) of the row over all
+        // column tiles.  Pass 1: the same products again, written as logit - lse.
+        const T* bias = static_cast<const T*>(p.bias);
+        if (t.pass == 0 && t.n_idx == 0) { run_max = -INFINITY; run_sum = 0.f; run_arg = 0; }
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + c0, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = t.n0 + c0 + g * 8;
+            if (col < p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g * 8 + i]);
+              if (bias) {
+                float bb[8];
+                load_bias8(bias + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += bb[i];
+              }
+              if (t.pass == 0) {
+                float m8 = v[0];
+                int a8 = 0;
+#pragma unroll
+                for (int i = 1; i < 8; ++i) {
+                  if (v[i] > m8) { m8 = v[i]; a8 = i; }
+                }
+                if (m8 > run_max) {
+                  run_sum *= __expf(run_max - m8);  // exp(-inf) = 0 on the first group
+                  run_max = m8;
+                  run_arg = col + a8;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) run_sum += __expf(v[i] - run_max);
+              } else if (row_ok) {
+                if (p.out_f32) {
+                  float* orow = static_cast<float*>(p.D) + row * p.N + col;
+                  *reinterpret_cast<float4*>(orow) = make_float4(v[0] - lse, v[1] - lse, v[2] - lse, v[3] - lse);
+                  *reinterpret_cast<float4*>(orow + 4) = make_float4(v[4] - lse, v[5] - lse, v[6] - lse, v[7] - lse);
+                } else {
+                  uint4 o;
+                  o.x = pack2<T>(v[0] - lse, v[1] - lse); o.y = pack2<T>(v[2] - lse, v[3] - lse);
+                  o.z = pack2<T>(v[4] - lse, v[5] - lse); o.w = pack2<T>(v[6] - lse, v[7] - lse);
+                  *reinterpret_cast<uint4*>(static_cast<T*>(p.D) + row * p.N + col) = o;
+                }
+              }
+            }
+          }
+        }
+        if (t.pass == 0 && t.n_idx == p.num_n_tiles - 1) {
+          lse = run_max + __logf(run_sum);
+          if (row_ok && p.argmax) p.argmax[row] = run_arg;
+        }
+      }
+
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+    }
+    if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusGemmEpilogue);
+  }
+
+  // Teardown.  After an abandoned wait, give copies that may still be in
+  // flight time to land before shared memory and TMEM are released.
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Small / odd problems: plain CUDA-core kernel (one thread per output).  Keeps
+// every shape the reference accepts on the GPU; not a performance path.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(T* __restrict__ D, const T* __restrict__ A,
+                                                        const T* __restrict__ B, const T* __restrict__ bias,
+                                                        int64_t M, int N, int K, int act, int64_t strideA,
+                                                        int64_t strideB, int64_t strideD) {
+  const int64_t batch = blockIdx.z;
+  A += batch * strideA; B += batch * strideB; D += batch * strideD;
+  const int64_t total = M * N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t m = i / N;
+    const int n = static_cast<int>(i - m * N);
+    const T* a = A + m * K;
+    const T* b = B + static_cast<int64_t>(n) * K;
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc = fmaf(Elem<T>::to_f(a[k]), Elem<T>::to_f(b[k]), acc);
+    if (bias) acc += Elem<T>::to_f(bias[n]);
+    acc = apply_act_rt(acc, act);
+    D[i] = Elem<T>::from_f(acc);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+int g_force_bn = 0;  // 0 = heuristic; otherwise 64 / 128 / 256 (set through oasr_b200_set_tunable)
+
+template <typename T, int BN, int kStages, int kSched, int kEpi>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_t work_items, cudaStream_t s) {
+  using S = Smem<BN, kStages>;
+  auto kern = gemm_tcgen05_kernel<T, BN, kStages, kSched, kEpi>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+    if (e != cudaSuccess) return set_error(OASR_ERR_CUDA, "gemm: cannot reserve %d bytes of shared memory: %s",
+                                           S::kDynamic, cudaGetErrorString(e));
+    attr_done = true;
+  }
+  int64_t grid = work_items < sm_count() ? work_items : sm_count();
+  if (grid < 1) grid = 1;
+  kern<<<static_cast<unsigned>(grid), kThreads, S::kDynamic, s>>>(ta, tb, p);
+  return check_launch("tcgen05 gemm launch");
+}
+
+// stage counts: as deep as fits beside the barriers in ~200 KB
+template <int BN> struct StagesFor;
+template <> struct StagesFor<64> { static constexpr int v = 8; };   // 24 KB / stage
+template <> struct StagesFor<128> { static constexpr int v = 6; };  // 32 KB / stage
+template <> struct StagesFor<256> { static constexpr int v = 4; };  // 48 KB / stage
+
+int pick_bn(int64_t m_tiles_total, int64_t N) {
+  if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) return g_force_bn;
+  const int sms = sm_count();
+  double best = 1e30;
+  int best_bn = 128;
+  const int cand[3] = {256, 128, 64};
+  const double unit_cost[3] = {1.0, 1.08, 1.25};  // relative cost per output column of the narrower tiles
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    const int64_t tiles = m_tiles_total * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * bn * unit_cost[i];
+    if (cost < best) { best = cost; best_bn = bn; }
+  }
+  return best_bn;
+}
+
+struct Problem {
+  int sched, epi;
+  int64_t M, N, K, batch, groups;
+  const void *A, *B;
+  Params p;
+};
+
+template <typename T>
+int make_maps(const Problem& pr, int bn, int dtype, CUtensorMap* ta, CUtensorMap* tb) {
+  // A: (K, rows, batch); B: (K, rows, batch)
+  const int64_t a_rows = pr.sched == kSchedGroup ? pr.M : pr.M;
+  const int64_t a_batch = pr.sched == kSchedDense ? pr.batch : 1;
+  const int64_t b_rows = pr.epi == kEpiGlu ? 2 * pr.N : pr.N;
+  const int64_t b_batch = pr.sched == kSchedDense ? pr.batch : (pr.sched == kSchedGroup ? pr.groups : 1);
+  uint64_t adims[3] = {(uint64_t)pr.K, (uint64_t)a_rows, (uint64_t)a_batch};
+  uint64_t astr[3] = {0, (uint64_t)pr.K * 2, (uint64_t)pr.K * 2 * (uint64_t)a_rows};
+  uint32_t abox[3] = {BK, BM, 1};
+  if (int rc = make_tensor_map(ta, tma_dtype(dtype), 3, pr.A, adims, astr, abox)) return rc;
+  uint64_t bdims[3] = {(uint64_t)pr.K, (uint64_t)b_rows, (uint64_t)b_batch};
+  uint64_t bstr[3] = {0, (uint64_t)pr.K * 2, (uint64_t)pr.K * 2 * (uint64_t)b_rows};
+  uint32_t bbox[3] = {BK, (uint32_t)(pr.epi == kEpiGlu ? bn / 2 : bn), 1};
+  return make_tensor_map(tb, tma_dtype(dtype), 3, pr.B, bdims, bstr, bbox);
+}
+
+template <typename T, int kSched, int kEpi>
+int run_typed(Problem& pr, int dtype, cudaStream_t s) {
+  Params& p = pr.p;
+  int64_t m_tiles_total;
+  if (kSched == kSchedGroup) m_tiles_total = (pr.M + BM - 1) / BM + pr.groups;
+  else m_tiles_total = ((pr.M + BM - 1) / BM) * (kSched == kSchedDense ? pr.batch : 1);
+  const int64_t n_eff = kEpi == kEpiGlu ? 2 * pr.N : pr.N;  // accumulator columns
+  int bn = kEpi == kEpiLsm ? (g_force_bn ? g_force_bn : 256) : pick_bn(m_tiles_total, n_eff);
+  if (kEpi == kEpiGlu && bn < 128) bn = 128;  // half tiles of >= 64 columns
+  p.num_m_tiles = static_cast<int>((pr.M + BM - 1) / BM);
+  p.num_n_tiles = static_cast<int>((n_eff + bn - 1) / bn);
+  p.num_k_blocks = static_cast<int>((pr.K + BK - 1) / BK);
+  CUtensorMap ta, tb;
+  if (int rc = make_maps<T>(pr, bn, dtype, &ta, &tb)) return rc;
+  int64_t work;
+  if (kSched == kSchedSweep) work = p.num_m_tiles;
+  else work = m_tiles_total * p.num_n_tiles;
+  switch (bn) {
+    case 256: return launch<T, 256, StagesFor<256>::v, kSched, kEpi>(ta, tb, p, work, s);
+    case 128: return launch<T, 128, StagesFor<128>::v, kSched, kEpi>(ta, tb, p, work, s);
+    default: return launch<T, 64, StagesFor<64>::v, kSched, kEpi>(ta, tb, p, work, s);
+  }
+}
+
+template <int kSched, int kEpi>
+int run(Problem& pr, int dtype, cudaStream_t s) {
+  pr.p.status = device_status_ptr();
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int { return run_typed<T, kSched, kEpi>(pr, dtype, s); });
+}
+
+int validate_common(const char* op, const void* D, const void* A, const void* B, const void* bias, int64_t M,
+                    int64_t N, int64_t K) {
+  OB_REQUIRE(D && A && B, OASR_ERR_INVALID, "%s: null pointer argument", op);
+  OB_REQUIRE(M >= 0 && N > 0 && K > 0, OASR_ERR_INVALID, "%s: bad shape M=%lld N=%lld K=%lld", op, (long long)M,
+             (long long)N, (long long)K);
+  OB_REQUIRE(N % 8 == 0 && K % 8 == 0, OASR_ERR_ALIGN,
+             "%s needs both free dimensions 8-aligned, got N=%lld K=%lld. Pad the projection at the model layer "
+             "(align_out_features / pad_output_projection).",
+             op, (long long)N, (long long)K);
+  OB_REQUIRE(is_aligned(A, 16) && is_aligned(B, 16) && is_aligned(D, 16) && (!bias || is_aligned(bias, 16)),
+             OASR_ERR_ALIGN, "%s: operand pointers must be 16-byte aligned", op);
+  OB_REQUIRE(M < (int64_t(1) << 31) && N < (1 << 30) && K < (1 << 30), OASR_ERR_INVALID, "%s: extent too large", op);
+  return OASR_OK;
+}
+
+// Shapes the tensor-core kernel does not take: fewer than 16 columns of K.
+bool use_simt(int64_t M, int64_t N, int64_t K) { return K < 16 || M * N * K < 32 * 32 * 32; }
+
+template <typename T>
+int launch_simt(void* D, const void* A, const void* B, const void* bias, int64_t batch, int64_t M, int64_t N,
+                int64_t K, int act, cudaStream_t s) {
+  if (M == 0 || batch == 0) return OASR_OK;
+  int64_t g = (M * N + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (g > cap) g = cap;
+  dim3 grid(static_cast<unsigned>(g), 1, static_cast<unsigned>(batch));
+  gemm_simt_kernel<T><<<grid, 256, 0, s>>>(static_cast<T*>(D), static_cast<const T*>(A), static_cast<const T*>(B),
+                                           static_cast<const T*>(bias), M, (int)N, (int)K, act, M * K, N * K, M * N);
+  return check_launch("simt gemm launch");
+}
+
+}  // namespace gemm
+
+// Internal C++ entry: reference GEMM on CUDA cores (tests compare the
+// tensor-core kernel against it on the device).
+int gemm_simt_reference(void* D, const void* A, const void* B, const void* bias, int64_t M, int64_t N, int64_t K,
+                        int act, int dtype, cudaStream_t s) {
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+    return gemm::launch_simt<T>(D, A, B, bias, 1, M, N, K, act, s);
+  });
+}
+
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_gemm(void* D, const void* A, const void* B, const void* bias, int64_t M, int64_t N, int64_t K,
+                   int activation, int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("gemm", D, A, B, bias, M, N, K)) return rc;
+  OB_REQUIRE(act_is_known(activation), OASR_ERR_INVALID, "gemm: unknown activation id %d", activation);
+  if (M == 0) return OASR_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_simt(M, N, K)) return gemm_simt_reference(D, A, B, bias, M, N, K, activation, dtype, s);
+  Problem pr{};
+  pr.sched = kSchedDense; pr.epi = kEpiStore;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = 1; pr.A = A; pr.B = B;
+  pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
+  pr.p.D = D; pr.p.bias = bias; pr.p.act = activation; pr.p.alpha = 1.f;
+  return run<kSchedDense, kEpiStore>(pr, dtype, s);
+}
+
+int oasr_b200_gemm_residual_f32(float* R_out, const float* R_in, const void* A, const void* B, const void* bias,
+                                int64_t M, int64_t N, int64_t K, double alpha, int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("gemm_residual_f32", R_out, A, B, bias, M, N, K)) return rc;
+  OB_REQUIRE(R_in && is_aligned(R_in, 16), OASR_ERR_INVALID, "gemm_residual_f32: residual pointer null or unaligned");
+  if (M == 0) return OASR_OK;
+  Problem pr{};
+  pr.sched = kSchedDense; pr.epi = kEpiResid;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = 1; pr.A = A; pr.B = B;
+  pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
+  pr.p.D = R_out; pr.p.R_in = R_in; pr.p.bias = bias; pr.p.act = OASR_ACT_NONE; pr.p.alpha = (float)alpha;
+  return run<kSchedDense, kEpiResid>(pr, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_gemm_glu(void* D, const void* A, const void* B, const void* bias, int64_t M, int64_t N, int64_t K,
+                       int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("gemm_glu", D, A, B, bias, M, N, K)) return rc;
+  if (M == 0) return OASR_OK;
+  Problem pr{};
+  pr.sched = kSchedDense; pr.epi = kEpiGlu;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = 1; pr.A = A; pr.B = B;
+  pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
+  pr.p.D = D; pr.p.bias = bias; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
+  return run<kSchedDense, kEpiGlu>(pr, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_bmm(void* D, const void* A, const void* B, int64_t batch, int64_t M, int64_t N, int64_t K, int dtype,
+                  void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("bmm", D, A, B, nullptr, M, N, K)) return rc;
+  OB_REQUIRE(batch >= 0 && batch < 65536, OASR_ERR_INVALID, "bmm: bad batch %lld", (long long)batch);
+  if (M == 0 || batch == 0) return OASR_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_simt(M, N, K)) {
+    return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+      return launch_simt<T>(D, A, B, nullptr, batch, M, N, K, OASR_ACT_NONE, s);
+    });
+  }
+  Problem pr{};
+  pr.sched = kSchedDense; pr.epi = kEpiStore;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = batch; pr.A = A; pr.B = B;
+  pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = (int)batch;
+  pr.p.D = D; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
+  return run<kSchedDense, kEpiStore>(pr, dtype, s);
+}
+
+int oasr_b200_group_gemm(void* D, const void* A, const void* B, const int32_t* offsets, int64_t L, int64_t groups,
+                         int64_t N, int64_t K, int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("group_gemm", D, A, B, nullptr, L, N, K)) return rc;
+  OB_REQUIRE(offsets != nullptr && groups > 0 && groups < 65536, OASR_ERR_INVALID, "group_gemm: bad offsets/groups");
+  if (L == 0) return OASR_OK;
+  Problem pr{};
+  pr.sched = kSchedGroup; pr.epi = kEpiStore;
+  pr.M = L; pr.N = N; pr.K = K; pr.batch = 1; pr.groups = groups; pr.A = A; pr.B = B;
+  pr.p.M = (int)L; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1; pr.p.groups = (int)groups;
+  pr.p.offsets = offsets;
+  pr.p.D = D; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
+  return run<kSchedGroup, kEpiStore>(pr, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B, const void* bias, int64_t M, int64_t N,
+                               int64_t K, int dtype, int out_dtype, int32_t* argmax, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("gemm_log_softmax", out, A, B, bias, M, N, K)) return rc;
+  OB_REQUIRE(out_dtype == OASR_DT_F32 || out_dtype == dtype, OASR_ERR_DTYPE,
+             "gemm_log_softmax: out dtype must be fp32 or the activation dtype");
+  if (M == 0) return OASR_OK;
+  Problem pr{};
+  pr.sched = kSchedSweep; pr.epi = kEpiLsm;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = 1; pr.A = A; pr.B = B;
+  pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
+  pr.p.D = out; pr.p.bias = bias; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
+  pr.p.out_f32 = out_dtype == OASR_DT_F32 ? 1 : 0;
+  pr.p.argmax = argmax;
+  return run<kSchedSweep, kEpiLsm>(pr, dtype, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,429 @@
+// Row normalisation kernels: LayerNorm / RMSNorm with optional fused residual
+// add, optional activation, and inference BatchNorm over channels-last rows.
+//
+// HBM-bound.  Fast path: one warp owns one row, the whole row lives in
+// registers (one global read, one global write), statistics by warp shuffles,
+// 128-bit coalesced accesses (lane l of chunk c touches elements
+// [(c*32+l)*8, +8)).  Algorithmic bytes per row of width H in a 16-bit type:
+// LN 4H, add+LN+residual 8H (include/oasr/norm.cuh:28-93,396-484 in the
+// reference make 3-4 passes over the row from global memory instead).
+#include "common.cuh"
+
+namespace ob {
+namespace {
+
+constexpr int kGran = 8;  // elements per lane per chunk
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[kGran]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  } else {
+    Pack<T> v = ld128(p);
+#pragma unroll
+    for (int i = 0; i < kGran; ++i) f[i] = Elem<T>::to_f(v.v[i]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void load8_param(const T* p, float (&f)[kGran]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  } else {
+    Pack<T> v = ld128_nc(p);
+#pragma unroll
+    for (int i = 0; i < kGran; ++i) f[i] = Elem<T>::to_f(v.v[i]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[kGran]) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  } else {
+    Pack<T> v;
+#pragma unroll
+    for (int i = 0; i < kGran; ++i) v.v[i] = Elem<T>::from_f(f[i]);
+    st128(p, v);
+  }
+}
+
+struct NormArgs {
+  void* out;
+  void* res_out;      // nullable
+  const void* in;
+  const void* res;    // nullable
+  const void* weight;
+  const void* bias;   // nullable
+  int64_t rows;
+  int hidden;
+  float eps;
+  float alpha;
+  int act;
+};
+
+// TIn: type of in/residual; TOut: type of out/res_out; TW: type of weight/bias.
+template <typename TIn, typename TOut, typename TW, int kChunks, bool kRms, bool kAdd, bool kAct>
+__global__ void __launch_bounds__(128) norm_warp_rows_kernel(NormArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int H = a.hidden;
+  const TIn* in = static_cast<const TIn*>(a.in) + row * H;
+  const TIn* res = kAdd ? static_cast<const TIn*>(a.res) + row * H : nullptr;
+  TOut* out = static_cast<TOut*>(a.out) + row * H;
+  TOut* res_out = (kAdd && a.res_out) ? static_cast<TOut*>(a.res_out) + row * H : nullptr;
+
+  float x[kChunks][kGran];
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int e = (c * 32 + lane) * kGran;
+    if (e < H) {
+      load8(in + e, x[c]);
+      if constexpr (kAdd) {
+        float r[kGran];
+        load8(res + e, r);
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) x[c][i] = fmaf(a.alpha, x[c][i], r[i]);
+        if (res_out) store8(res_out + e, x[c]);
+      }
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) sum += kRms ? x[c][i] * x[c][i] : x[c][i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) x[c][i] = 0.f;
+    }
+  }
+  sum = warp_sum(sum);
+  float mean = 0.f, rstd;
+  if constexpr (kRms) {
+    rstd = rsqrtf(sum / H + a.eps);
+  } else {
+    mean = sum / H;
+    float sq = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int e = (c * 32 + lane) * kGran;
+      if (e < H) {
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) {
+          const float d = x[c][i] - mean;
+          sq = fmaf(d, d, sq);
+        }
+      }
+    }
+    sq = warp_sum(sq);
+    rstd = rsqrtf(sq / H + a.eps);
+  }
+  const TW* w = static_cast<const TW*>(a.weight);
+  const TW* b = static_cast<const TW*>(a.bias);
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int e = (c * 32 + lane) * kGran;
+    if (e < H) {
+      float g[kGran], y[kGran];
+      load8_param(w + e, g);
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) y[i] = (x[c][i] - mean) * rstd * g[i];
+      if (b) {
+        float bb[kGran];
+        load8_param(b + e, bb);
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) y[i] += bb[i];
+      }
+      if constexpr (kAct) {
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) y[i] = apply_act_rt(y[i], a.act);
+      }
+      store8(out + e, y);
+    }
+  }
+}
+
+// Any width: one block per row, scalar accesses, row re-read from global.
+template <typename TIn, typename TOut, typename TW, bool kRms, bool kAdd, bool kAct>
+__global__ void __launch_bounds__(256) norm_block_rows_kernel(NormArgs a) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int H = a.hidden;
+  const TIn* in = static_cast<const TIn*>(a.in) + row * H;
+  const TIn* res = kAdd ? static_cast<const TIn*>(a.res) + row * H : nullptr;
+  TOut* out = static_cast<TOut*>(a.out) + row * H;
+  TOut* res_out = (kAdd && a.res_out) ? static_cast<TOut*>(a.res_out) + row * H : nullptr;
+  auto value = [&](int i) -> float {
+    float v = Elem<TIn>::to_f(in[i]);
+    if constexpr (kAdd) v = fmaf(a.alpha, v, Elem<TIn>::to_f(res[i]));
+    return v;
+  };
+  float s = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = value(i);
+    s += kRms ? v * v : v;
+  }
+  s = block_sum(s, red);
+  float mean = 0.f, rstd;
+  if constexpr (kRms) {
+    rstd = rsqrtf(s / H + a.eps);
+  } else {
+    mean = s / H;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float d = value(i) - mean;
+      sq = fmaf(d, d, sq);
+    }
+    sq = block_sum(sq, red);
+    rstd = rsqrtf(sq / H + a.eps);
+  }
+  const TW* w = static_cast<const TW*>(a.weight);
+  const TW* b = static_cast<const TW*>(a.bias);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = value(i);
+    float y = (v - mean) * rstd * Elem<TW>::to_f(w[i]);
+    if (b) y += Elem<TW>::to_f(b[i]);
+    if constexpr (kAct) y = apply_act_rt(y, a.act);
+    // The sum is written after every read of in/res at this index by this
+    // thread, so res_out may alias in or res.
+    if (res_out) res_out[i] = Elem<TOut>::from_f(v);
+    out[i] = Elem<TOut>::from_f(y);
+  }
+}
+
+template <typename TIn, typename TOut, typename TW, bool kRms, bool kAdd, bool kAct>
+int launch_norm(const NormArgs& a, cudaStream_t stream) {
+  if (a.rows == 0) return OASR_OK;
+  const int H = a.hidden;
+  const bool fast = (H % kGran == 0) && H <= 16 * 32 * kGran && is_aligned(a.in, 16) &&
+                    is_aligned(a.out, 16) && is_aligned(a.weight, 16) &&
+                    (!a.bias || is_aligned(a.bias, 16)) && (!a.res || is_aligned(a.res, 16)) &&
+                    (!a.res_out || is_aligned(a.res_out, 16));
+  if (fast) {
+    const int packs = H / kGran;
+    const int chunks = (packs + 31) / 32;
+    const int warps = 4;
+    const unsigned grid = static_cast<unsigned>((a.rows + warps - 1) / warps);
+#define OB_NORM_CASE(C)                                                                          \
+  norm_warp_rows_kernel<TIn, TOut, TW, C, kRms, kAdd, kAct><<<grid, warps * 32, 0, stream>>>(a)
+    if (chunks <= 1) OB_NORM_CASE(1);
+    else if (chunks <= 2) OB_NORM_CASE(2);
+    else if (chunks <= 4) OB_NORM_CASE(4);
+    else if (chunks <= 8) OB_NORM_CASE(8);
+    else OB_NORM_CASE(16);
+#undef OB_NORM_CASE
+  } else {
+    norm_block_rows_kernel<TIn, TOut, TW, kRms, kAdd, kAct>
+        <<<static_cast<unsigned>(a.rows), 256, 0, stream>>>(a);
+  }
+  return check_launch("norm kernel launch");
+}
+
+int validate_norm(const void* out, const void* in, const void* weight, int64_t rows, int64_t hidden,
+                  int act) {
+  OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "norm: null pointer argument");
+  OB_REQUIRE(rows >= 0 && hidden > 0, OASR_ERR_INVALID, "norm: bad shape rows=%lld hidden=%lld",
+             (long long)rows, (long long)hidden);
+  OB_REQUIRE(hidden <= (1 << 24), OASR_ERR_INVALID, "norm: hidden=%lld is too large", (long long)hidden);
+  OB_REQUIRE(rows < (int64_t(1) << 31), OASR_ERR_INVALID, "norm: rows=%lld is too large", (long long)rows);
+  OB_REQUIRE(act_is_known(act), OASR_ERR_INVALID, "norm: unknown activation id %d", act);
+  return OASR_OK;
+}
+
+template <bool kRms>
+int norm_entry(void* out, void* res_out, const void* in, const void* res, const void* weight,
+               const void* bias, int64_t rows, int64_t hidden, double eps, double alpha, int act,
+               int dtype, bool add, void* stream) {
+  if (int rc = validate_norm(out, in, weight, rows, hidden, act)) return rc;
+  if (add) OB_REQUIRE(res != nullptr, OASR_ERR_INVALID, "add-norm: residual pointer is null");
+  NormArgs a{out, res_out, in, res, weight, bias, rows, (int)hidden, (float)eps, (float)alpha, act};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int {
+    if (add) {
+      if (act != OASR_ACT_NONE) return launch_norm<T, T, T, kRms, true, true>(a, s);
+      return launch_norm<T, T, T, kRms, true, false>(a, s);
+    }
+    if (act != OASR_ACT_NONE) return launch_norm<T, T, T, kRms, false, true>(a, s);
+    return launch_norm<T, T, T, kRms, false, false>(a, s);
+  });
+}
+
+// ---------------------------------------------------------------------------
+// BatchNorm (inference) over channels-last rows.
+// ---------------------------------------------------------------------------
+struct BnArgs {
+  void* out;
+  const void* in;
+  const void *w, *b, *mean, *var;
+  int64_t rows;
+  int channels;
+  float eps;
+  int act;
+};
+
+// Each thread keeps one 8-channel column group for the whole kernel, so the
+// per-channel scale/shift are computed once per thread.
+template <typename T, bool kAct>
+__global__ void __launch_bounds__(256) batch_norm_vec_kernel(BnArgs a) {
+  const int ppr = a.channels / kGran;  // packs per row
+  const int64_t total = a.rows * ppr;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;  // multiple of ppr
+  if (tid >= total) return;
+  const int c0 = static_cast<int>(tid % ppr) * kGran;
+  float g[kGran], bb[kGran], mu[kGran], vv[kGran], scale[kGran], shift[kGran];
+  load8_param(static_cast<const T*>(a.w) + c0, g);
+  load8_param(static_cast<const T*>(a.b) + c0, bb);
+  load8_param(static_cast<const T*>(a.mean) + c0, mu);
+  load8_param(static_cast<const T*>(a.var) + c0, vv);
+#pragma unroll
+  for (int i = 0; i < kGran; ++i) {
+    scale[i] = g[i] * rsqrtf(vv[i] + a.eps);
+    shift[i] = bb[i] - mu[i] * scale[i];
+  }
+  const T* in = static_cast<const T*>(a.in);
+  T* out = static_cast<T*>(a.out);
+  for (int64_t p = tid; p < total; p += nthreads) {
+    float x[kGran];
+    load8(in + p * kGran, x);
+#pragma unroll
+    for (int i = 0; i < kGran; ++i) {
+      x[i] = fmaf(x[i], scale[i], shift[i]);
+      if constexpr (kAct) x[i] = apply_act_rt(x[i], a.act);
+    }
+    store8(out + p * kGran, x);
+  }
+}
+
+template <typename T, bool kAct>
+__global__ void __launch_bounds__(256) batch_norm_scalar_kernel(BnArgs a) {
+  const int64_t total = a.rows * a.channels;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+    const int c = static_cast<int>(i % a.channels);
+    const float scale = Elem<T>::to_f(static_cast<const T*>(a.w)[c]) *
+                        rsqrtf(Elem<T>::to_f(static_cast<const T*>(a.var)[c]) + a.eps);
+    float y = (Elem<T>::to_f(static_cast<const T*>(a.in)[i]) - Elem<T>::to_f(static_cast<const T*>(a.mean)[c])) * scale +
+              Elem<T>::to_f(static_cast<const T*>(a.b)[c]);
+    if constexpr (kAct) y = apply_act_rt(y, a.act);
+    static_cast<T*>(a.out)[i] = Elem<T>::from_f(y);
+  }
+}
+
+int64_t gcd64(int64_t x, int64_t y) {
+  while (y) { int64_t t = x % y; x = y; y = t; }
+  return x;
+}
+
+template <typename T, bool kAct>
+int launch_bn(const BnArgs& a, cudaStream_t s) {
+  if (a.rows == 0) return OASR_OK;
+  const bool fast = a.channels % kGran == 0 && is_aligned(a.in, 16) && is_aligned(a.out, 16) &&
+                    is_aligned(a.w, 16) && is_aligned(a.b, 16) && is_aligned(a.mean, 16) &&
+                    is_aligned(a.var, 16);
+  const int block = 256;
+  if (fast) {
+    const int64_t ppr = a.channels / kGran;
+    const int64_t total = a.rows * ppr;
+    // grid*block must be a multiple of ppr so that a thread's column is fixed.
+    const int64_t unit = ppr / gcd64(ppr, block);  // grid must be a multiple of this
+    int64_t want = (total + block - 1) / block;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (want > cap) want = cap;
+    int64_t grid = ((want + unit - 1) / unit) * unit;
+    batch_norm_vec_kernel<T, kAct><<<static_cast<unsigned>(grid), block, 0, s>>>(a);
+  } else {
+    int64_t grid = (a.rows * a.channels + block - 1) / block;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (grid > cap) grid = cap;
+    batch_norm_scalar_kernel<T, kAct><<<static_cast<unsigned>(grid), block, 0, s>>>(a);
+  }
+  return check_launch("batch_norm kernel launch");
+}
+
+}  // namespace
+
+// Internal (C++) entry used by the fused encoder: fp32 rows in, 16-bit rows out.
+int layer_norm_f32_in(void* out, const float* in, const void* weight, const void* bias, int64_t rows,
+                      int64_t hidden, double eps, int out_dtype, cudaStream_t stream) {
+  if (int rc = validate_norm(out, in, weight, rows, hidden, OASR_ACT_NONE)) return rc;
+  NormArgs a{out, nullptr, in, nullptr, weight, bias, rows, (int)hidden, (float)eps, 1.f, OASR_ACT_NONE};
+  return OB_DISPATCH_HALF(out_dtype, T, [&]() -> int {
+    return launch_norm<float, T, T, false, false, false>(a, stream);
+  });
+}
+
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_layer_norm(void* out, const void* in, const void* weight, const void* bias, int64_t rows,
+                         int64_t hidden, double eps, int dtype, void* stream) {
+  return ob::norm_entry<false>(out, nullptr, in, nullptr, weight, bias, rows, hidden, eps, 1.0,
+                               OASR_ACT_NONE, dtype, false, stream);
+}
+int oasr_b200_layer_norm_activation(void* out, const void* in, const void* weight, const void* bias,
+                                    int64_t rows, int64_t hidden, double eps, int activation, int dtype,
+                                    void* stream) {
+  return ob::norm_entry<false>(out, nullptr, in, nullptr, weight, bias, rows, hidden, eps, 1.0, activation,
+                               dtype, false, stream);
+}
+int oasr_b200_add_layer_norm(void* out, const void* in, const void* residual, const void* weight,
+                             const void* bias, int64_t rows, int64_t hidden, double eps, double alpha,
+                             int dtype, void* stream) {
+  return ob::norm_entry<false>(out, nullptr, in, residual, weight, bias, rows, hidden, eps, alpha,
+                               OASR_ACT_NONE, dtype, true, stream);
+}
+int oasr_b200_add_layer_norm_residual(void* out, void* residual_out, const void* in, const void* residual,
+                                      const void* weight, const void* bias, int64_t rows, int64_t hidden,
+                                      double eps, double alpha, int dtype, void* stream) {
+  if (!residual_out) return ob::set_error(OASR_ERR_INVALID, "add_layer_norm_residual: residual_out is null");
+  return ob::norm_entry<false>(out, residual_out, in, residual, weight, bias, rows, hidden, eps, alpha,
+                               OASR_ACT_NONE, dtype, true, stream);
+}
+int oasr_b200_rms_norm(void* out, const void* in, const void* weight, const void* bias, int64_t rows,
+                       int64_t hidden, double eps, int dtype, void* stream) {
+  return ob::norm_entry<true>(out, nullptr, in, nullptr, weight, bias, rows, hidden, eps, 1.0, OASR_ACT_NONE,
+                              dtype, false, stream);
+}
+int oasr_b200_rms_norm_activation(void* out, const void* in, const void* weight, const void* bias,
+                                  int64_t rows, int64_t hidden, double eps, int activation, int dtype,
+                                  void* stream) {
+  return ob::norm_entry<true>(out, nullptr, in, nullptr, weight, bias, rows, hidden, eps, 1.0, activation,
+                              dtype, false, stream);
+}
+int oasr_b200_add_rms_norm(void* out, const void* in, const void* residual, const void* weight,
+                           const void* bias, int64_t rows, int64_t hidden, double eps, double alpha, int dtype,
+                           void* stream) {
+  return ob::norm_entry<true>(out, nullptr, in, residual, weight, bias, rows, hidden, eps, alpha,
+                              OASR_ACT_NONE, dtype, true, stream);
+}
+int oasr_b200_add_rms_norm_residual(void* out, void* residual_out, const void* in, const void* residual,
+                                    const void* weight, const void* bias, int64_t rows, int64_t hidden,
+                                    double eps, double alpha, int dtype, void* stream) {
+  if (!residual_out) return ob::set_error(OASR_ERR_INVALID, "add_rms_norm_residual: residual_out is null");
+  return ob::norm_entry<true>(out, residual_out, in, residual, weight, bias, rows, hidden, eps, alpha,
+                              OASR_ACT_NONE, dtype, true, stream);
+}
+
+int oasr_b200_batch_norm(void* out, const void* in, const void* weight, const void* bias,
+                         const void* running_mean, const void* running_var, int64_t rows, int64_t channels,
+                         double eps, int activation, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(out && in && weight && bias && running_mean && running_var, OASR_ERR_INVALID,
+             "batch_norm: null pointer argument");
+  OB_REQUIRE(rows >= 0 && channels > 0 && channels < (1 << 24), OASR_ERR_INVALID,
+             "batch_norm: bad shape rows=%lld channels=%lld", (long long)rows, (long long)channels);
+  OB_REQUIRE(act_is_known(activation), OASR_ERR_INVALID, "batch_norm: unknown activation id %d", activation);
+  BnArgs a{out, in, weight, bias, running_mean, running_var, rows, (int)channels, (float)eps, activation};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int {
+    if (activation != OASR_ACT_NONE) return launch_bn<T, true>(a, s);
+    return launch_bn<T, false>(a, s);
+  });
+}
+
+}  // extern "C"

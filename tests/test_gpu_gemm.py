@@ -1,0 +1,155 @@
+"""GPU parity: tcgen05 GEMM family vs the CPU oracle.
+
+Shapes follow the reference's tests (tests/test_gemm.py:33-101 gemm / bmm /
+group_gemm vs torch.matmul at rtol=atol=1e-2; tests/test_gemm_log_softmax.py:20-96
+fp32 log_softmax(linear) oracle, row logsumexp ~ 0, out= aliasing) and the
+GEMM shapes of the Conformer configs, plus ragged M/N/K tails.
+"""
+import pytest
+import torch
+
+import oasr_b200 as ob
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+HALF = [torch.bfloat16, torch.float16]
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def _check(got, want, dtype, rtol=1e-2, atol=1e-2):
+    got = got.float().cpu()
+    torch.testing.assert_close(got, want.to(dtype).float(), rtol=rtol, atol=atol)
+
+
+SHAPES = [
+    (128, 128, 64), (128, 256, 128), (256, 512, 512), (1000, 1536, 512), (708, 2048, 256), (333, 264, 72),
+    (1, 8, 16), (5, 5008, 256), (4096, 512, 2048), (129, 24, 200), (2000, 1024, 512), (64, 64, 64),
+    (17, 776, 520), (300, 8, 8),
+]
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm(dtype, M, N, K):
+    A, B, C = _rand((M, K), dtype, 1), _rand((N, K), dtype, 2, K ** -0.5), _rand((N,), dtype, 3)
+    _check(ob.gemm(A.cuda(), B.cuda(), C.cuda()), O.gemm(A, B, C), dtype)
+    _check(ob.gemm(A.cuda(), B.cuda()), O.gemm(A, B), dtype)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("M,N,K", [(1000, 1536, 512), (300, 520, 136), (128, 64, 64)])
+def test_gemm_every_tile_width(bn, M, N, K):
+    from oasr_b200 import tunables
+
+    dtype = torch.bfloat16
+    A, B, C = _rand((M, K), dtype, 1), _rand((N, K), dtype, 2, K ** -0.5), _rand((N,), dtype, 3)
+    tunables.set("gemm_bn", bn)
+    try:
+        _check(ob.gemm(A.cuda(), B.cuda(), C.cuda()), O.gemm(A, B, C), dtype)
+    finally:
+        tunables.set("gemm_bn", 0)
+
+
+def test_gemm_is_deterministic_and_leading_dims():
+    dtype = torch.bfloat16
+    A, B = _rand((3, 70, 512), dtype, 4), _rand((1024, 512), dtype, 5, 0.05)
+    y1 = ob.gemm(A.cuda(), B.cuda())
+    y2 = ob.gemm(A.cuda(), B.cuda())
+    assert y1.shape == (3, 70, 1024) and torch.equal(y1, y2)
+    out = torch.empty(3, 70, 1024, device="cuda", dtype=dtype)
+    assert ob.gemm(A.cuda(), B.cuda(), out=out) is out and torch.equal(out, y1)
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("act", [0, 1, 2, 4])
+def test_gemm_activation(dtype, act):
+    M, N, K = 700, 2048, 512
+    A, B, C = _rand((M, K), dtype, 6), _rand((N, K), dtype, 7, K ** -0.5), _rand((N,), dtype, 8)
+    _check(ob.gemm_activation(A.cuda(), B.cuda(), C.cuda(), act), O.gemm(A, B, C, act), dtype)
+
+
+def test_gemm_rejects_bad_inputs():
+    A = torch.randn(16, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):  # N not a multiple of 8 (reference CHECK_GEMM_ALIGNMENT)
+        ob.gemm(A, torch.randn(5002, 64, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):  # dtype mismatch
+        ob.gemm(A, torch.randn(8, 64, device="cuda", dtype=torch.float16))
+    with pytest.raises(RuntimeError):  # fp32 is not a GEMM dtype
+        ob.gemm(A.float(), torch.randn(8, 64, device="cuda"))
+    with pytest.raises(RuntimeError):  # K mismatch
+        ob.gemm(A, torch.randn(8, 32, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("M,N,K", [(1000, 512, 512), (333, 256, 256), (64, 1024, 1024), (130, 72, 264)])
+def test_gemm_glu(dtype, M, N, K):
+    A, B, C = _rand((M, K), dtype, 9), _rand((2 * N, K), dtype, 10, K ** -0.5), _rand((2 * N,), dtype, 11)
+    _check(ob.gemm_glu(A.cuda(), B.cuda(), C.cuda()), O.gemm_glu(A, B, C), dtype)
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("M,N,K,alpha", [(1000, 512, 2048, 0.5), (333, 256, 256, 1.0), (129, 1024, 520, 1.0)])
+def test_gemm_residual_f32(dtype, M, N, K, alpha):
+    A, B, C = _rand((M, K), dtype, 12), _rand((N, K), dtype, 13, K ** -0.5), _rand((N,), dtype, 14)
+    R = _rand((M, N), torch.float32, 15)
+    got = ob.gemm_residual_f32(R.cuda(), A.cuda(), B.cuda(), C.cuda(), alpha)
+    want = R + alpha * O.gemm(A, B, C)
+    torch.testing.assert_close(got.cpu(), want, rtol=1e-4, atol=1e-4)
+    Rg = R.cuda()
+    assert ob.gemm_residual_f32(Rg, A.cuda(), B.cuda(), C.cuda(), alpha, out=Rg) is Rg  # in place
+    torch.testing.assert_close(Rg.cpu(), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("b,M,N,K", [(16, 200, 200, 64), (3, 130, 72, 136), (256, 16, 272, 64), (2, 1, 8, 16)])
+def test_bmm(dtype, b, M, N, K):
+    A, B = _rand((b, M, K), dtype, 16), _rand((b, N, K), dtype, 17, K ** -0.5)
+    _check(ob.bmm(A.cuda(), B.cuda()), O.bmm(A, B), dtype)
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("sizes", [[128, 128], [100, 0, 300, 7], [1], [513, 64, 255]])
+def test_group_gemm(dtype, sizes):
+    N, K = 264, 136
+    L, G = sum(sizes), len(sizes)
+    offs = torch.tensor(sizes).cumsum(0).to(torch.int32)
+    A, B = _rand((L, K), dtype, 18), _rand((G, N, K), dtype, 19, K ** -0.5)
+    _check(ob.group_gemm(A.cuda(), B.cuda(), offs.cuda()), O.group_gemm(A, B, offs.tolist()), dtype)
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("M,N,K", [(708, 5008, 256), (300, 5008, 512), (64, 1024, 1024), (5, 8, 64), (130, 264, 72)])
+def test_gemm_log_softmax(dtype, M, N, K):
+    A, B, C = _rand((M, K), dtype, 20), _rand((N, K), dtype, 21, K ** -0.5), _rand((N,), dtype, 22)
+    want = O.gemm_log_softmax(A, B, C)
+    got32, arg = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda(), out_dtype=torch.float32, return_argmax=True)
+    torch.testing.assert_close(got32.cpu(), want, rtol=1e-4, atol=2e-4)
+    # every row is a normalised distribution (reference tests/test_gemm_log_softmax.py: |logsumexp| < 5e-3)
+    assert got32.logsumexp(-1).abs().max().item() < 1e-4
+    got_arg = arg.cpu().long()
+    want_arg = want.argmax(-1)
+    same = got_arg == want_arg
+    # a differing argmax is only acceptable on a numerical tie
+    assert torch.all(same | ((want.gather(1, got_arg[:, None]) - want.gather(1, want_arg[:, None])).abs()[:, 0] < 1e-5))
+    got16 = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda())
+    assert got16.dtype == dtype
+    torch.testing.assert_close(got16.float().cpu(), want, rtol=2e-2, atol=5e-2)
+
+
+def test_gemm_log_softmax_padding_rows_are_inert():
+    """Vocabulary padded 5002 -> 5008 with zero weight rows and bias -1e4
+    (reference oasr/models/base.py:163-197): a padding class never wins and takes no mass."""
+    dtype = torch.bfloat16
+    M, N, K, raw = 200, 5008, 256, 5002
+    A, B, C = _rand((M, K), dtype, 23), _rand((N, K), dtype, 24, 0.02), torch.zeros(N, dtype=dtype)
+    B[raw:] = 0
+    C[raw:] = -1e4
+    got, arg = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda(), out_dtype=torch.float32, return_argmax=True)
+    assert int(arg.max()) < raw
+    want = O.gemm_log_softmax(A[:, :], B[:raw], C[:raw])
+    torch.testing.assert_close(got[:, :raw].cpu(), want, rtol=1e-4, atol=2e-4)

@@ -1,0 +1,170 @@
+"""GPU parity: norm / activation / depthwise-conv kernels vs the CPU oracle.
+
+Cases follow the reference's kernel unit tests (tests/test_norm.py,
+tests/test_activation.py, tests/test_conv.py): same shapes families, same
+tolerances or tighter, plus ragged / empty / non-vectorisable extents.
+"""
+import pytest
+import torch
+
+import oasr_b200 as ob
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.bfloat16, torch.float16, torch.float32]
+TOL = {torch.bfloat16: 2e-2, torch.float16: 3e-3, torch.float32: 2e-5}
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def _close(got, want, dtype, scale=1.0):
+    got = got.float().cpu()
+    want = want.float()
+    # the oracle's fp32 result rounded to the kernel's output type is the target
+    want_r = want.to(dtype).float()
+    tol = TOL[dtype] * scale
+    err = (got - want_r).abs().max().item() if got.numel() else 0.0
+    assert err <= tol * max(1.0, want.abs().max().item() if want.numel() else 1.0), f"max err {err}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 250, 512), (3, 7, 256), (2, 5, 1024), (1, 1, 8), (2, 3, 80), (5, 333),
+                                   (2, 4, 4096), (2, 4, 4104), (0, 16), (3, 5, 12)])
+def test_layer_norm(dtype, shape):
+    x = _rand(shape, dtype, 1, 2.0)
+    H = shape[-1]
+    w, b = _rand((H,), dtype, 2) + 1, _rand((H,), dtype, 3)
+    got = ob.layer_norm(x.cuda(), w.cuda(), b.cuda(), 1e-5)
+    _close(got, O.layer_norm(x, w, b, 1e-5), dtype)
+    got = ob.layer_norm(x.cuda(), w.cuda(), None, 1e-5)
+    _close(got, O.layer_norm(x, w, None, 1e-5), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", [0, 1, 2, 4])
+def test_layer_norm_activation(dtype, act):
+    x = _rand((3, 17, 512), dtype, 4)
+    w, b = _rand((512,), dtype, 5) + 1, _rand((512,), dtype, 6)
+    got = ob.layer_norm_activation(x.cuda(), w.cuda(), b.cuda(), 1e-5, act)
+    _close(got, O.layer_norm(x, w, b, 1e-5, act), dtype)
+    got = ob.rms_norm_activation(x.cuda(), w.cuda(), b.cuda(), 1e-5, act)
+    _close(got, O.rms_norm(x, w, b, 1e-5, act), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 250, 512), (2, 3, 1000), (7, 24)])
+def test_rms_norm(dtype, shape):
+    x = _rand(shape, dtype, 7, 3.0)
+    H = shape[-1]
+    w, b = _rand((H,), dtype, 8) + 1, _rand((H,), dtype, 9)
+    _close(ob.rms_norm(x.cuda(), w.cuda(), None, 1e-5), O.rms_norm(x, w, None, 1e-5), dtype)
+    _close(ob.rms_norm(x.cuda(), w.cuda(), b.cuda(), 1e-6), O.rms_norm(x, w, b, 1e-6), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 250, 512), (2, 9, 256), (3, 5, 12)])
+@pytest.mark.parametrize("alpha", [1.0, 0.5])
+def test_add_layer_norm_residual(dtype, shape, alpha):
+    x, r = _rand(shape, dtype, 10), _rand(shape, dtype, 11, 2.0)
+    H = shape[-1]
+    w, b = _rand((H,), dtype, 12) + 1, _rand((H,), dtype, 13)
+    out, res = ob.add_layer_norm_residual(x.cuda(), r.cuda(), w.cuda(), b.cuda(), 1e-5, alpha)
+    want_out, want_res = O.add_layer_norm_residual(x, r, w, b, 1e-5, alpha)
+    _close(out, want_out, dtype)
+    # the carried sum is the fp32 sum rounded ONCE: bit-exact (reference tests/test_norm.py:276-281)
+    want_fma = torch.addcmul(r.float(), torch.tensor(alpha), x.float()).to(dtype)
+    assert torch.equal(res.cpu(), want_res) or torch.equal(res.cpu(), want_fma)
+    out2 = ob.add_layer_norm(x.cuda(), r.cuda(), w.cuda(), b.cuda(), 1e-5, alpha=alpha)
+    assert torch.equal(out2, out)
+    o3, r3 = ob.add_rms_norm_residual(x.cuda(), r.cuda(), w.cuda(), b.cuda(), 1e-5, alpha)
+    w_o3, w_r3 = O.add_rms_norm_residual(x, r, w, b, 1e-5, alpha)
+    _close(o3, w_o3, dtype)
+    assert torch.equal(r3.cpu(), w_r3) or torch.equal(r3.cpu(), want_fma)
+    assert torch.equal(ob.add_rms_norm(x.cuda(), r.cuda(), w.cuda(), b.cuda(), 1e-5, alpha), o3)
+
+
+def test_norm_rejects_padded_rows_and_cpu():
+    x = torch.randn(4, 8, 64, device="cuda", dtype=torch.bfloat16)[:, :, :32]
+    w = torch.ones(32, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ob.layer_norm(x, w)
+    with pytest.raises(RuntimeError):
+        ob.layer_norm(torch.randn(2, 32), torch.ones(32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 250, 512), (2, 7, 256), (3, 5, 20), (1, 3, 1024)])
+@pytest.mark.parametrize("act", [-1, 2, 0])
+def test_batch_norm(dtype, shape, act):
+    x = _rand(shape, dtype, 14, 2.0)
+    C = shape[-1]
+    w, b = _rand((C,), dtype, 15) + 1, _rand((C,), dtype, 16)
+    mean, var = _rand((C,), dtype, 17), _rand((C,), dtype, 18).abs() + 0.5
+    want = O.batch_norm(x, w, b, mean, var, 1e-5, act)
+    args = [t.cuda() for t in (x, w, b, mean, var)]
+    if act == -1:
+        got = ob.batch_norm_1d(*args, 1e-5)
+    elif act == 2:
+        got = ob.batch_norm_swish(*args, 1e-5)
+    else:
+        got = ob.batch_norm_activation(*args, 1e-5, act)
+    _close(got, want, dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 250, 1024), (2, 3, 16), (3, 5, 24), (1, 1, 2), (0, 4, 64)])
+def test_glu_swish(dtype, shape):
+    x = _rand(shape, dtype, 19, 2.0)
+    _close(ob.glu(x.cuda()), O.glu(x), dtype)
+    _close(ob.swish(x.cuda()), O.swish(x), dtype)
+    out = torch.empty_like(x, device="cuda")
+    assert ob.swish(x.cuda(), out=out) is out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,T,C,K,pad", [(4, 250, 256, 15, 7), (2, 100, 512, 15, (14, 0)), (3, 33, 64, 9, (8, 0)),
+                                          (1, 30, 512, 15, 0), (2, 17, 24, 3, 1), (2, 40, 10, 4, (2, 1)),
+                                          (1, 5, 64, 15, 7), (2, 64, 128, 31, 15)])
+def test_depthwise_conv1d(dtype, B, T, C, K, pad):
+    x = _rand((B, T, C), dtype, 20)
+    w = _rand((K, 1, C), dtype, 21, 0.3)
+    b = _rand((C,), dtype, 22)
+    got = ob.depthwise_conv1d(x.cuda(), w.cuda(), b.cuda(), pad)
+    _close(got, O.depthwise_conv1d(x, w, b, pad), dtype, scale=2.0)
+    got = ob.depthwise_conv1d(x.cuda(), w.cuda().reshape(K, C), None, pad)
+    _close(got, O.depthwise_conv1d(x, w, None, pad), dtype, scale=2.0)
+    got = ob.depthwise_conv1d_silu(x.cuda(), w.cuda(), b.cuda(), pad)
+    _close(got, O.depthwise_conv1d(x, w, b, pad, act=2), dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bool_mask", [True, False])
+def test_depthwise_conv1d_fsmn_mask(dtype, bool_mask):
+    B, T, C, K = 3, 40, 64, 11
+    x = _rand((B, T, C), dtype, 23)
+    w = _rand((K, C), dtype, 24, 0.3)
+    lens = torch.tensor([40, 25, 1])
+    mask = (torch.arange(T)[None, :] < lens[:, None]).unsqueeze(-1)
+    m = mask if bool_mask else mask.to(dtype)
+    got = ob.depthwise_conv1d(x.cuda(), w.cuda(), None, (K - 1) // 2, mask=m.cuda(), add_input=True)
+    _close(got, O.depthwise_conv1d(x, w, None, (K - 1) // 2, mask=mask, add_input=True), dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("T", [16, 3, 1])
+def test_causal_conv1d_state(dtype, T):
+    B, C, K = 3, 64, 9
+    w = _rand((C, 1, K), dtype, 25, 0.3)
+    b = _rand((C,), dtype, 26)
+    state = _rand((B, K - 1, C), dtype, 27)
+    st_gpu = state.cuda().clone()
+    for step in range(3):
+        x = _rand((B, T, C), dtype, 28 + step)
+        want, state = O.causal_conv1d(x, state, w, b)
+        got = ob.causal_conv1d(x.cuda(), st_gpu, w.cuda(), b.cuda())
+        _close(got, want, dtype, scale=2.0)
+        assert torch.equal(st_gpu.cpu(), state)  # rolled state is a pure copy: bit-exact
