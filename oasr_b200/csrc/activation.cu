@@ -78,7 +78,7 @@ extern "C" {
 
 int oasr_b200_glu(void* out, const void* in, int64_t rows, int64_t channels, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(out && in, OASR_ERR_INVALID, "glu: null pointer argument");
+  OB_REQUIRE(rows == 0 || (out && in), OASR_ERR_INVALID, "glu: null pointer argument");
   OB_REQUIRE(rows >= 0 && channels > 0 && channels < (1 << 24), OASR_ERR_INVALID,
              "glu: bad shape rows=%lld channels=%lld", (long long)rows, (long long)channels);
   if (rows == 0) return OASR_OK;
@@ -98,7 +98,7 @@ int oasr_b200_glu(void* out, const void* in, int64_t rows, int64_t channels, int
 
 int oasr_b200_swish(void* out, const void* in, int64_t numel, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(out && in, OASR_ERR_INVALID, "swish: null pointer argument");
+  OB_REQUIRE(numel == 0 || (out && in), OASR_ERR_INVALID, "swish: null pointer argument");
   OB_REQUIRE(numel >= 0, OASR_ERR_INVALID, "swish: negative element count");
   if (numel == 0) return OASR_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

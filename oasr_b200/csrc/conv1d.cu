@@ -314,7 +314,7 @@ int oasr_b200_depthwise_conv1d(void* out, const void* in, const void* weight, co
                                int64_t pad_left, int64_t pad_right, const void* mask, int mask_is_bool,
                                int add_input, int activation, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "depthwise_conv1d: null pointer argument");
+  OB_REQUIRE(batch == 0 || (out && in && weight), OASR_ERR_INVALID, "depthwise_conv1d: null pointer argument");
   OB_REQUIRE(batch >= 0 && seq_len >= 0 && channels > 0 && kernel_size > 0 && pad_left >= 0 && pad_right >= 0,
              OASR_ERR_INVALID, "depthwise_conv1d: bad shape");
   OB_REQUIRE(channels < (1 << 24) && seq_len < (1 << 30) && kernel_size < (1 << 16), OASR_ERR_INVALID,

@@ -601,7 +601,7 @@ int run(Problem& pr, int dtype, cudaStream_t s) {
 
 int validate_common(const char* op, const void* D, const void* A, const void* B, const void* bias, int64_t M,
                     int64_t N, int64_t K) {
-  OB_REQUIRE(D && A && B, OASR_ERR_INVALID, "%s: null pointer argument", op);
+  OB_REQUIRE(M == 0 || (D && A && B), OASR_ERR_INVALID, "%s: null pointer argument", op);
   OB_REQUIRE(M >= 0 && N > 0 && K > 0, OASR_ERR_INVALID, "%s: bad shape M=%lld N=%lld K=%lld", op, (long long)M,
              (long long)N, (long long)K);
   OB_REQUIRE(N % 8 == 0 && K % 8 == 0, OASR_ERR_ALIGN,
@@ -667,7 +667,8 @@ int oasr_b200_gemm_residual_f32(float* R_out, const float* R_in, const void* A, 
   using namespace ob;
   using namespace ob::gemm;
   if (int rc = validate_common("gemm_residual_f32", R_out, A, B, bias, M, N, K)) return rc;
-  OB_REQUIRE(R_in && is_aligned(R_in, 16), OASR_ERR_INVALID, "gemm_residual_f32: residual pointer null or unaligned");
+  OB_REQUIRE(M == 0 || (R_in && is_aligned(R_in, 16)), OASR_ERR_INVALID,
+             "gemm_residual_f32: residual pointer null or unaligned");
   if (M == 0) return OASR_OK;
   Problem pr{};
   pr.sched = kSchedDense; pr.epi = kEpiResid;

@@ -224,7 +224,7 @@ int launch_norm(const NormArgs& a, cudaStream_t stream) {
 
 int validate_norm(const void* out, const void* in, const void* weight, int64_t rows, int64_t hidden,
                   int act) {
-  OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "norm: null pointer argument");
+  OB_REQUIRE(rows == 0 || (out && in && weight), OASR_ERR_INVALID, "norm: null pointer argument");
   OB_REQUIRE(rows >= 0 && hidden > 0, OASR_ERR_INVALID, "norm: bad shape rows=%lld hidden=%lld",
              (long long)rows, (long long)hidden);
   OB_REQUIRE(hidden <= (1 << 24), OASR_ERR_INVALID, "norm: hidden=%lld is too large", (long long)hidden);
@@ -238,7 +238,7 @@ int norm_entry(void* out, void* res_out, const void* in, const void* res, const 
                const void* bias, int64_t rows, int64_t hidden, double eps, double alpha, int act,
                int dtype, bool add, void* stream) {
   if (int rc = validate_norm(out, in, weight, rows, hidden, act)) return rc;
-  if (add) OB_REQUIRE(res != nullptr, OASR_ERR_INVALID, "add-norm: residual pointer is null");
+  if (add) OB_REQUIRE(rows == 0 || res != nullptr, OASR_ERR_INVALID, "add-norm: residual pointer is null");
   NormArgs a{out, res_out, in, res, weight, bias, rows, (int)hidden, (float)eps, (float)alpha, act};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int {
@@ -380,7 +380,7 @@ int oasr_b200_add_layer_norm(void* out, const void* in, const void* residual, co
 int oasr_b200_add_layer_norm_residual(void* out, void* residual_out, const void* in, const void* residual,
                                       const void* weight, const void* bias, int64_t rows, int64_t hidden,
                                       double eps, double alpha, int dtype, void* stream) {
-  if (!residual_out) return ob::set_error(OASR_ERR_INVALID, "add_layer_norm_residual: residual_out is null");
+  if (!residual_out && rows > 0) return ob::set_error(OASR_ERR_INVALID, "add_layer_norm_residual: residual_out is null");
   return ob::norm_entry<false>(out, residual_out, in, residual, weight, bias, rows, hidden, eps, alpha,
                                OASR_ACT_NONE, dtype, true, stream);
 }
@@ -404,7 +404,7 @@ int oasr_b200_add_rms_norm(void* out, const void* in, const void* residual, cons
 int oasr_b200_add_rms_norm_residual(void* out, void* residual_out, const void* in, const void* residual,
                                     const void* weight, const void* bias, int64_t rows, int64_t hidden,
                                     double eps, double alpha, int dtype, void* stream) {
-  if (!residual_out) return ob::set_error(OASR_ERR_INVALID, "add_rms_norm_residual: residual_out is null");
+  if (!residual_out && rows > 0) return ob::set_error(OASR_ERR_INVALID, "add_rms_norm_residual: residual_out is null");
   return ob::norm_entry<true>(out, residual_out, in, residual, weight, bias, rows, hidden, eps, alpha,
                               OASR_ACT_NONE, dtype, true, stream);
 }
@@ -413,7 +413,7 @@ int oasr_b200_batch_norm(void* out, const void* in, const void* weight, const vo
                          const void* running_mean, const void* running_var, int64_t rows, int64_t channels,
                          double eps, int activation, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(out && in && weight && bias && running_mean && running_var, OASR_ERR_INVALID,
+  OB_REQUIRE(rows == 0 || (out && in && weight && bias && running_mean && running_var), OASR_ERR_INVALID,
              "batch_norm: null pointer argument");
   OB_REQUIRE(rows >= 0 && channels > 0 && channels < (1 << 24), OASR_ERR_INVALID,
              "batch_norm: bad shape rows=%lld channels=%lld", (long long)rows, (long long)channels);

@@ -1,0 +1,174 @@
+"""Generate the golden fixtures in this directory from the REFERENCE implementation.
+
+Run where the reference checkout is available (it is not on the GPU box):
+
+    OASR_REFERENCE=/root/reference python tests/golden/make_golden.py
+
+The script imports the reference package with its torch backend
+(``OASR_LAYERS_BACKEND=torch OASR_FUSED_ADDNORM=0``), rebinds the two call
+sites that have no torch route at the operator boundary (``oasr.glu`` ->
+``F.glu``, ``oasr.gemm_log_softmax`` -> ``log_softmax(linear)``), loads the
+seeded synthetic weights of ``oracle.conformer.init_params`` into the
+reference model, runs the reference entry points on seeded inputs, checks the
+CPU oracle against them and writes small ``.npz`` fixtures.  Inputs are never
+stored: tests regenerate them from the same seeds.
+"""
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+sys.path.insert(0, str(ROOT))
+REF = os.environ.get("OASR_REFERENCE", "/root/reference")
+os.environ["OASR_LAYERS_BACKEND"] = "torch"
+os.environ["OASR_FUSED_ADDNORM"] = "0"
+sys.path.insert(0, REF)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+import oasr  # noqa: E402  (the reference)
+from oasr.models.conformer.config import ConformerEncoderConfig, ConformerModelConfig  # noqa: E402
+from oasr.models.conformer.model import ConformerModel  # noqa: E402
+
+from oracle import conformer as OC  # noqa: E402
+from oracle import ops as O  # noqa: E402
+from tests.golden import cases  # noqa: E402
+
+torch.set_grad_enabled(False)
+oasr.glu = lambda x, out=None: F.glu(x, dim=-1)
+oasr.gemm_log_softmax = lambda A, B, C=None, out=None: F.log_softmax(F.linear(A, B, C), dim=-1)
+
+
+def build_reference_model(cfg: OC.ConformerConfig, params):
+    enc = ConformerEncoderConfig(
+        input_size=cfg.input_size, output_size=cfg.d_model, attention_heads=cfg.heads, linear_units=cfg.ffn,
+        num_blocks=cfg.layers, cnn_module_kernel=cfg.kernel, cnn_module_norm=cfg.cnn_module_norm,
+        embed_layer_norm=cfg.embed_layer_norm)
+    model = ConformerModel(ConformerModelConfig(encoder=enc, vocab_size=cfg.vocab_padded)).eval()
+    sd = model.state_dict()
+    own = dict(model.named_parameters())
+    own.update(dict(model.named_buffers()))
+    missing = [k for k in sd if k not in params and not k.endswith("pos_enc.pe") and "num_batches_tracked" not in k]
+    assert not missing, f"oracle parameter spec misses reference tensors: {missing}"
+    for name, value in params.items():
+        assert name in own, f"reference model has no tensor {name}"
+        assert tuple(own[name].shape) == tuple(value.shape), (name, own[name].shape, value.shape)
+        own[name].data.copy_(value)
+    return model
+
+
+def model_case(name: str):
+    case = cases.MODEL_CASES[name]
+    cfg = case["cfg"]
+    params = OC.init_params(cfg, seed=case["weight_seed"], perturb=case["perturb"])
+    feats, lengths = cases.make_features(case)
+    model = build_reference_model(cfg, params)
+    out = {}
+    for path, ref_fn, ora_fn in (
+        ("padded", model.forward_offline, OC.forward_offline),
+        ("packed", model.forward_offline_packed, OC.forward_offline_packed),
+    ):
+        ref_lp, ref_len = ref_fn(feats, lengths)
+        ora_lp, ora_len = ora_fn(params, cfg, feats, lengths)
+        assert torch.equal(ref_len.long().cpu(), ora_len.long()), (ref_len, ora_len)
+        valid = torch.arange(ref_lp.shape[1])[None, :] < ora_len[:, None]
+        # padding classes sit at about -1e4, where one fp32 ulp is 1e-3: compare the raw vocabulary only
+        diff = (ref_lp - ora_lp)[valid][:, :cfg.vocab].abs().max().item()
+        print(f"{name}/{path}: reference vs oracle max-abs over valid frames = {diff:.3e}")
+        assert diff < 5e-5, "oracle does not restate the reference"
+        ref_tok = OC.greedy_tokens(ref_lp, ora_len, cfg.vocab)
+        assert ref_tok == OC.greedy_tokens(ora_lp, ora_len, cfg.vocab)
+        out[f"{path}_out_len"] = ref_len.long().numpy()
+        out[f"{path}_tokens"] = np.array([t for h in ref_tok for t in h + [-1]], dtype=np.int32)
+        if case["store"] == "full":
+            out[f"{path}_log_probs"] = ref_lp.numpy()
+        else:  # compact: first 64 classes of every frame + per-frame (max, argmax) over the raw vocabulary
+            out[f"{path}_log_probs_head"] = ref_lp[:, :, :64].numpy()
+            mx = ref_lp[:, :, :cfg.vocab].max(-1)
+            out[f"{path}_frame_max"] = mx.values.numpy()
+            out[f"{path}_frame_argmax"] = mx.indices.numpy().astype(np.int32)
+            top2 = ref_lp[:, :, :cfg.vocab].topk(2, -1).values
+            out[f"{path}_frame_margin"] = (top2[..., 0] - top2[..., 1]).numpy()
+    np.savez_compressed(HERE / f"model_{name}.npz", **out)
+
+
+def operator_cases():
+    """Operator-level outputs of the reference's own torch routes."""
+    from oasr.cache.paged_kv import flat_write_index
+    from oasr.functionals.attention import _sdpa_reference, _sdpa_varlen_reference, gather_paged_kv
+    from oasr.functionals.gemm_torch import torch_gemm_log_softmax
+    from oasr.layers.norm import _add_layer_norm_ref
+    from oasr.models.conformer.packing import build_packed_layout
+
+    out = {}
+    # --- dense attention with bias, lengths, starts, causal, GQA -------------------------------
+    for name, c in cases.FMHA_CASES.items():
+        t = cases.make_fmha(c)
+        ref = _sdpa_reference(t["q"], t["k"], t["v"], c["scale"], t.get("bias"), t.get("seqlens"), c["causal"],
+                              t.get("seqstarts"))
+        ora = O.fmha(t["q"], t["k"], t["v"], c["scale"], t.get("bias"), t.get("seqlens"), t.get("seqstarts"),
+                     None, c["causal"])
+        ref = torch.nan_to_num(ref, nan=0.0)  # SDPA gives NaN on a fully masked row; the kernel contract is 0
+        d = (ref - ora).abs().max().item()
+        print(f"fmha/{name}: reference vs oracle {d:.3e}")
+        assert d < 2e-5
+        out[f"fmha_{name}"] = ref.numpy()
+    # --- paged gather + attention ----------------------------------------------------------------
+    for name, c in cases.PAGED_CASES.items():
+        t = cases.make_paged(c)
+        kd, vd = gather_paged_kv(t["k_pool"], t["v_pool"], t["block_table"])
+        ok, ov = O.gather_paged_kv(t["k_pool"], t["v_pool"], t["block_table"])
+        assert torch.equal(kd, ok) and torch.equal(vd, ov)
+        idx = flat_write_index(t["block_table"], t["offsets"], c["t_new"], c["block_size"])
+        oidx = O.flat_write_index(t["block_table"].numpy(), t["offsets"].numpy(), c["t_new"], c["block_size"])
+        assert np.array_equal(idx.numpy(), oidx)
+        out[f"paged_{name}_write_index"] = idx.numpy()
+        ref = _sdpa_reference(t["q"], kd, vd, c["scale"], t["bias"], t["seqlens"])
+        ora = O.fmha(t["q"], t["k_pool"], t["v_pool"], c["scale"], t["bias"], t["seqlens"], None, t["block_table"])
+        d = (torch.nan_to_num(ref, nan=0.0) - ora).abs().max().item()
+        print(f"paged/{name}: reference vs oracle {d:.3e}")
+        assert d < 2e-5
+        out[f"paged_{name}_out"] = torch.nan_to_num(ref, nan=0.0).numpy()
+    # --- varlen -----------------------------------------------------------------------------------
+    for name, c in cases.VARLEN_CASES.items():
+        t = cases.make_varlen(c)
+        ref = torch.zeros_like(t["q"])
+        _sdpa_varlen_reference(t["q"], t["k"], t["v"], c["scale"], t["cu"], t["cu"], t["bias"], t["bias_offsets"], ref)
+        ora = O.fmha_varlen(t["q"], t["k"], t["v"], c["scale"], t["cu"], t["cu"], t["bias"], t["bias_offsets"])
+        d = (ref - ora).abs().max().item()
+        print(f"varlen/{name}: reference vs oracle {d:.3e}")
+        assert d < 2e-5
+        out[f"varlen_{name}"] = ref.numpy()
+        # the packed layout index tensors (integer work, bit-exact)
+        valid = torch.arange(max(c["lens"]))[None, :] < torch.tensor(c["lens"])[:, None]
+        lay = build_packed_layout(valid, 15, num_heads=c["H"])
+        mine = cases.packed_layout(c["lens"], 15, c["H"])
+        for key in ("cu_seqlens", "pack_src_idx", "conv_gather_idx", "bias_offsets"):
+            assert np.array_equal(getattr(lay, key).numpy(), mine[key]), key
+            out[f"layout_{name}_{key}"] = getattr(lay, key).numpy()
+    # --- add + LayerNorm and the CTC head ------------------------------------------------------------
+    g = torch.Generator().manual_seed(11)
+    x, r = torch.randn(5, 7, 64, generator=g), torch.randn(5, 7, 64, generator=g)
+    w, b = torch.randn(64, generator=g), torch.randn(64, generator=g)
+    ref_o, ref_s = _add_layer_norm_ref(x, r, w, b, 1e-5, 0.5)
+    ora_o, ora_s = O.add_layer_norm_residual(x, r, w, b, 1e-5, 0.5)
+    assert (ref_o - ora_o).abs().max() < 1e-6 and torch.equal(ref_s, ora_s)
+    out["add_layer_norm_out"], out["add_layer_norm_sum"] = ref_o.numpy(), ref_s.numpy()
+    A, B, C = torch.randn(9, 64, generator=g), torch.randn(40, 64, generator=g), torch.randn(40, generator=g)
+    ref = torch.empty(9, 40)
+    torch_gemm_log_softmax(ref, A, B, C, 1)
+    assert (ref - O.gemm_log_softmax(A, B, C)).abs().max() < 1e-6
+    out["gemm_log_softmax"] = ref.numpy()
+    np.savez_compressed(HERE / "operators.npz", **out)
+
+
+if __name__ == "__main__":
+    operator_cases()
+    for name in cases.MODEL_CASES:
+        model_case(name)
+    print("fixtures written to", HERE)

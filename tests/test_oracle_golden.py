@@ -1,0 +1,97 @@
+"""CPU: the oracle reproduces the fixtures written from the reference (tests/golden/make_golden.py)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import conformer as OC
+from oracle import ops as O
+from tests.golden import cases
+
+GOLD = Path(__file__).resolve().parent / "golden"
+OPS = np.load(GOLD / "operators.npz")
+
+
+@pytest.mark.parametrize("name", list(cases.FMHA_CASES))
+def test_fmha_oracle(name):
+    c = cases.FMHA_CASES[name]
+    t = cases.make_fmha(c)
+    got = O.fmha(t["q"], t["k"], t["v"], c["scale"], t.get("bias"), t.get("seqlens"), t.get("seqstarts"), None,
+                 c["causal"])
+    assert np.abs(got.numpy() - OPS[f"fmha_{name}"]).max() < 2e-5
+
+
+def test_fully_masked_rows_are_zero():
+    c = cases.FMHA_CASES["starts"]
+    t = cases.make_fmha(c)
+    got = O.fmha(t["q"], t["k"], t["v"], c["scale"], t["bias"], t["seqlens"], t["seqstarts"])
+    assert torch.count_nonzero(got[2]) == 0  # window [40, 40) is empty
+
+
+@pytest.mark.parametrize("name", list(cases.PAGED_CASES))
+def test_paged_oracle(name):
+    c = cases.PAGED_CASES[name]
+    t = cases.make_paged(c)
+    idx = O.flat_write_index(t["block_table"].numpy(), t["offsets"].numpy(), c["t_new"], c["block_size"])
+    assert np.array_equal(idx, OPS[f"paged_{name}_write_index"])
+    got = O.fmha(t["q"], t["k_pool"], t["v_pool"], c["scale"], t["bias"], t["seqlens"], None, t["block_table"])
+    assert np.abs(got.numpy() - OPS[f"paged_{name}_out"]).max() < 2e-5
+
+
+@pytest.mark.parametrize("name", list(cases.VARLEN_CASES))
+def test_varlen_oracle_and_layout(name):
+    c = cases.VARLEN_CASES[name]
+    t = cases.make_varlen(c)
+    got = O.fmha_varlen(t["q"], t["k"], t["v"], c["scale"], t["cu"], t["cu"], t["bias"], t["bias_offsets"])
+    assert np.abs(got.numpy() - OPS[f"varlen_{name}"]).max() < 2e-5
+    lay = cases.packed_layout(c["lens"], 15, c["H"])
+    for key in ("cu_seqlens", "pack_src_idx", "conv_gather_idx", "bias_offsets"):
+        assert np.array_equal(lay[key], OPS[f"layout_{name}_{key}"])
+
+
+def test_add_layer_norm_and_head_oracle():
+    g = torch.Generator().manual_seed(11)
+    x, r = torch.randn(5, 7, 64, generator=g), torch.randn(5, 7, 64, generator=g)
+    w, b = torch.randn(64, generator=g), torch.randn(64, generator=g)
+    o, s = O.add_layer_norm_residual(x, r, w, b, 1e-5, 0.5)
+    assert np.abs(o.numpy() - OPS["add_layer_norm_out"]).max() < 1e-6
+    assert np.array_equal(s.numpy(), OPS["add_layer_norm_sum"])
+    A, B, C = torch.randn(9, 64, generator=g), torch.randn(40, 64, generator=g), torch.randn(40, generator=g)
+    assert np.abs(O.gemm_log_softmax(A, B, C).numpy() - OPS["gemm_log_softmax"]).max() < 1e-6
+
+
+def test_paged_write_then_gather_roundtrip():
+    c = dict(cases.PAGED_CASES["bs16"])
+    t = cases.make_paged(c)
+    g = torch.Generator().manual_seed(5)
+    new_k = torch.randn(c["B"], c["Hkv"], c["t_new"], c["D"], generator=g)
+    new_v = torch.randn(c["B"], c["Hkv"], c["t_new"], c["D"], generator=g)
+    O.write_kv_chunk(t["k_pool"], t["v_pool"], new_k, new_v, t["block_table"], t["offsets"], c["block_size"])
+    kd, vd = O.gather_paged_kv(t["k_pool"], t["v_pool"], t["block_table"])
+    for b in range(c["B"]):
+        o = int(t["offsets"][b])
+        assert torch.equal(kd[b, :, o:o + c["t_new"]], new_k[b]) and torch.equal(vd[b, :, o:o + c["t_new"]], new_v[b])
+
+
+@pytest.mark.parametrize("name", ["tiny", "config1"])
+def test_model_oracle_matches_reference_fixture(name):
+    case = cases.MODEL_CASES[name]
+    cfg = case["cfg"]
+    gold = np.load(GOLD / f"model_{name}.npz")
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    for path, fn in (("padded", OC.forward_offline), ("packed", OC.forward_offline_packed)):
+        lp, out_len = fn(P, cfg, feats, lengths)
+        assert np.array_equal(out_len.numpy(), gold[f"{path}_out_len"])
+        valid = (torch.arange(lp.shape[1])[None, :] < out_len[:, None]).numpy()
+        if case["store"] == "full":
+            d = np.abs(lp.numpy() - gold[f"{path}_log_probs"])[valid][:, :cfg.vocab].max()
+        else:
+            d = np.abs(lp[:, :, :64].numpy() - gold[f"{path}_log_probs_head"])[valid].max()
+            mx = lp[:, :, :cfg.vocab].max(-1)
+            d = max(d, np.abs(mx.values.numpy() - gold[f"{path}_frame_max"])[valid].max())
+        assert d < 5e-5, d
+        toks = OC.greedy_tokens(lp, out_len, cfg.vocab)
+        flat = np.array([t for h in toks for t in h + [-1]], dtype=np.int32)
+        assert np.array_equal(flat, gold[f"{path}_tokens"])
