@@ -230,22 +230,28 @@ OASR_API int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B,
  * oasr/kernels/cute/attention/fmha_sm80.py:552, mask rules
  * oasr/kernels/cute/mask.py:102-117):
  *   out[b,h,i,:] = softmax_j(q[b,h,i,:].k[b,h/(H/Hkv),j,:]*scale + bias[b,h,i,j]) . v
- * q, out (B,H,Tq,D); dense k, v (B,Hkv,Tk,D).  bias (nullable) is in the
- * activation dtype with row stride bias_stride_q and head/batch strides
- * bias_stride_h / bias_stride_b (elements).  seqlens / seqstarts (nullable,
- * int32[B]) keep keys in [start, len); causal masks j > i.  Rows with no
- * visible key produce zeros.  Paged mode (block_table != NULL): k, v are
- * pools (num_blocks, block_size, Hkv, D), block_table is int32
- * (B, blocks_per_seq) and Tk = blocks_per_seq * block_size. */
+ * q (B,H,Tq,D) and dense k, v (B,Hkv,Tk,D) may be strided views: *_strides
+ * (nullable = canonical) are HOST arrays of 3 element strides {batch, head,
+ * row}, each a multiple of 8, with unit stride along D.  out is canonical
+ * (B,H,Tq,D).  bias (nullable) is in the activation dtype with element strides
+ * bias_stride_b / _h / _q and unit stride along keys.  seqlens / seqstarts
+ * (nullable, int32[B]) keep keys in [start, len); causal masks j > i.  Rows
+ * with no visible key produce zeros.  Paged mode (block_table != NULL): k, v
+ * are pools (num_blocks, block_size, Hkv, D), block_table is int32
+ * (B, blocks_per_seq), Tk is ignored (= blocks_per_seq * block_size).
+ * D is 64 or 128. */
 OASR_API int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v,
+                            const int64_t* q_strides /*host, nullable*/,
+                            const int64_t* k_strides /*host, nullable*/,
+                            const int64_t* v_strides /*host, nullable*/,
                             const void* bias /*nullable*/, int64_t bias_stride_b,
                             int64_t bias_stride_h, int64_t bias_stride_q,
                             const int32_t* seqlens /*nullable*/,
                             const int32_t* seqstarts /*nullable*/,
                             const int32_t* block_table /*nullable*/, int64_t blocks_per_seq,
-                            int64_t block_size, int64_t B, int64_t H, int64_t Hkv, int64_t Tq,
-                            int64_t Tk, int64_t D, double scale, int causal, int dtype,
-                            void* stream);
+                            int64_t block_size, int64_t num_blocks, int64_t B, int64_t H,
+                            int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale,
+                            int causal, int dtype, void* stream);
 /* Packed variable-length attention, the reference's fmha_varlen
  * (oasr/functionals/attention.py:592-693): q, out (total_q,H,D); k, v
  * (total_k,Hkv,D); cu_seqlens_* int32[S+1]; bias (nullable) flat, segment s is
@@ -255,8 +261,9 @@ OASR_API int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, cons
                                    const void* bias /*nullable*/,
                                    const void* bias_offsets /*nullable*/, int bias_offsets_is_i64,
                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                   int64_t num_segs, int64_t max_seqlen_q, int64_t H, int64_t Hkv,
-                                   int64_t D, double scale, int dtype, void* stream);
+                                   int64_t num_segs, int64_t total_q, int64_t total_k,
+                                   int64_t max_seqlen_q, int64_t H, int64_t Hkv, int64_t D,
+                                   double scale, int dtype, void* stream);
 
 /* ---- paged KV cache ---------------------------------------------------- */
 /* Scatter a chunk of new keys/values into the page pools.  k_new, v_new are

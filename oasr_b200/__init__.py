@@ -9,6 +9,8 @@ reference package so its layers, models and engine run on these kernels.
 from __future__ import annotations
 
 from . import _lib
+from .attention import fmha, fmha_varlen, gather_paged_kv  # noqa: F401
+from .cache import PagedKVCache, gather_rows, scatter_rows, write_kv_chunk  # noqa: F401
 from .functional import (  # noqa: F401
     add_layer_norm,
     add_layer_norm_residual,

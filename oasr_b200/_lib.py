@@ -55,8 +55,8 @@ _SIGNATURES = {
     "oasr_b200_bmm": [P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_group_gemm": [P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_gemm_log_softmax": [P, P, P, P, I, I, I, c_int, c_int, P, P],
-    "oasr_b200_fmha": [P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
-    "oasr_b200_fmha_varlen": [P, P, P, P, P, P, c_int, P, P, I, I, I, I, I, c_double, c_int, P],
+    "oasr_b200_fmha": [P, P, P, P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_fmha_varlen": [P, P, P, P, P, P, c_int, P, P, I, I, I, I, I, I, I, c_double, c_int, P],
     "oasr_b200_paged_kv_write": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, c_int, P],
     "oasr_b200_paged_kv_gather": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_gather_rows": [P, P, P, I, I, P],
