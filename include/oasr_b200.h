@@ -133,6 +133,23 @@ OASR_API int oasr_b200_add_rms_norm_residual(void* out, void* residual_out, cons
                                              const void* bias /*nullable*/, int64_t rows,
                                              int64_t hidden, double eps, double alpha, int dtype,
                                              void* stream);
+/* Residual-stream step of the fused encoder layer: the residual stream is
+ * fp32, sub-layer outputs y and normalised activations h are 16-bit.
+ *   s = res_in + alpha * y   (either operand nullable = absent)
+ *   mode 0: res_out = s (nullable), h = LN_a(s)
+ *   mode 1: res_out = s (nullable), h = s * w_a + b_a with fp32 w_a/b_a (a
+ *           folded inference BatchNorm used as pre-norm)
+ *   mode 2: res_out = LN_a(s), h = LN_b(res_out)
+ * It is the reference's `x = residual + alpha*sub(x); x = norm(x)` pairs
+ * (oasr/models/conformer/model.py:722-751; fused form :602-663) with the sum
+ * never rounded to 16 bits.  res_out may alias res_in.  hidden % 8 == 0,
+ * hidden <= 2048. */
+OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
+                                    const float* res_in /*nullable*/,
+                                    const void* y /*nullable*/, double alpha, int mode,
+                                    const void* w_a, const void* b_a, const void* w_b /*mode 2*/,
+                                    const void* b_b /*mode 2*/, int64_t rows, int64_t hidden,
+                                    double eps, int dtype, void* stream);
 /* Inference batch norm over channels-last rows, optional activation
  * (activation = OASR_ACT_NONE for plain BN).  Replaces batchnorm1d,
  * batchnorm_activation and batchnorm_swish (csrc/norm_jit_binding.cu:13,32,35;
@@ -168,6 +185,27 @@ OASR_API int oasr_b200_depthwise_conv1d(void* out, const void* in, const void* w
                                         int64_t pad_left, int64_t pad_right,
                                         const void* mask /*nullable*/, int mask_is_bool,
                                         int add_input, int activation, int dtype, void* stream);
+/* Depthwise conv over PACKED segments: in/out (total, channels) rows,
+ * segment s = rows [cu_seqlens[s], cu_seqlens[s+1]), each convolved alone with
+ * (kernel_size-1)/2 zero frames on both sides -- the gapped-buffer scatter /
+ * conv / gather of ConvolutionModule._forward_packed_noncausal
+ * (oasr/models/conformer/model.py:223-233) without the gapped buffer.
+ * post_scale/post_shift (nullable, fp32[channels]) apply y*scale+shift after
+ * the bias (a folded inference BatchNorm, oasr/layers/norm.py:64-74), then the
+ * activation.  right_fill (nullable, fp32[channels]) with fill_frames
+ * (int32[S]) makes the first fill_frames[s] frames past a segment's end read
+ * right_fill instead of zero: the value padded rows carry in the padded-batch
+ * path, where they are zeroed BEFORE pointwise_conv1 (model.py:176-197). */
+OASR_API int oasr_b200_depthwise_conv1d_packed(void* out, const void* in, const void* weight,
+                                               const void* bias /*nullable*/,
+                                               const float* post_scale /*nullable*/,
+                                               const float* post_shift /*nullable*/,
+                                               const float* right_fill /*nullable*/,
+                                               const int32_t* fill_frames /*nullable*/,
+                                               const int32_t* cu_seqlens, int64_t num_segs,
+                                               int64_t max_seg_len, int64_t channels,
+                                               int64_t kernel_size, int activation, int dtype,
+                                               void* stream);
 /* Streaming causal depthwise conv with a rolling state: in (batch, seq_len,
  * channels), state (batch, kernel_size-1, channels) updated in place to the
  * last kernel_size-1 frames of [state, in], weight (channels, kernel_size).
@@ -264,6 +302,22 @@ OASR_API int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, cons
                                    int64_t num_segs, int64_t total_q, int64_t total_k,
                                    int64_t max_seqlen_q, int64_t H, int64_t Hkv, int64_t D,
                                    double scale, int dtype, void* stream);
+
+/* Conformer relative-position attention over packed rows, the whole of
+ * RelPositionMultiHeadedAttention._forward_packed between linear_qkv and
+ * linear_out (oasr/layers/attention/attention.py:323-386) in one kernel:
+ *   score[i,j] = ((q_i+u).k_j + (q_i+v).p_j) * scale,  j within i's segment,
+ * where the position term is a second 64-wide K-atom of the same MMA instead
+ * of a materialised (S,H,Tm,Tm) bias.  qkv4 is (total, 4*H*64) rows
+ * [q+u | q+v | k | v] (the fused projection with the query block duplicated
+ * and pos_bias_u / pos_bias_v folded into its bias); pos is linear_pos(pe)
+ * (pos_rows >= max_seqlen rows of H*64, row stride pos_stride elements);
+ * out is (total, H*64).  Head dim is 64. */
+OASR_API int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const void* pos,
+                                          int64_t pos_rows, int64_t pos_stride,
+                                          const int32_t* cu_seqlens, int64_t num_segs,
+                                          int64_t max_seqlen, int64_t total, int64_t H,
+                                          double scale, int dtype, void* stream);
 
 /* ---- paged KV cache ---------------------------------------------------- */
 /* Scatter a chunk of new keys/values into the page pools.  k_new, v_new are

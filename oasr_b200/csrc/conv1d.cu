@@ -45,6 +45,8 @@ struct DwArgs {
   const float* post_scale;   // nullable (C) fp32: y = y*scale + shift applied after bias
   const float* post_shift;   // nullable (C) fp32
   const int32_t* cu_seqlens; // nullable: packed mode, (S+1)
+  const float* right_fill;   // nullable (C) fp32: value of the frames just past a segment's end
+  const int32_t* fill_frames;// with right_fill: how many such frames each segment has (S)
   int64_t batch;             // batch size or number of segments
   int seq_len;               // padded mode: frames per batch row
   int out_len;               // padded mode: output frames per batch row
@@ -83,6 +85,13 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
   }
   const int t0 = blockIdx.y * kTile;
   if (t0 >= OL) return;
+  float f0 = 0.f, f1 = 0.f;
+  int fill_end = TL;  // frames in [TL, fill_end) read the fill value instead of zero
+  if (a.right_fill) {
+    f0 = a.right_fill[c];
+    f1 = a.right_fill[c + 1];
+    fill_end = TL + a.fill_frames[b];
+  }
   const T* in = static_cast<const T*>(a.in) + in_row0 * C + c;
   T* out = static_cast<T*>(a.out) + out_row0 * C + c;
   const T* w = static_cast<const T*>(a.weight) + c;
@@ -116,6 +125,7 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
     const int ti = first + k;
     float2 v = make_float2(0.f, 0.f);
     if (ti >= 0 && ti < TL) v = Pair<T>::ld(in + static_cast<int64_t>(ti) * C);
+    else if (ti >= TL && ti < fill_end) v = make_float2(f0, f1);
     x0[k] = v.x;
     x1[k] = v.y;
   }
@@ -126,6 +136,7 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
       const int ti = first + j + K - 1;
       float2 v = make_float2(0.f, 0.f);
       if (ti >= 0 && ti < TL) v = Pair<T>::ld(in + static_cast<int64_t>(ti) * C);
+      else if (ti >= TL && ti < fill_end) v = make_float2(f0, f1);
       x0[K - 1] = v.x;
       x1[K - 1] = v.y;
       float acc0 = 0.f, acc1 = 0.f;
@@ -288,26 +299,35 @@ __global__ void __launch_bounds__(256) causal_state_update_kernel(T* __restrict_
 
 }  // namespace
 
-// Internal (C++) entry used by the fused encoder: packed segments, "same"
-// padding, optional folded-BatchNorm affine and activation.
-int depthwise_conv1d_packed(void* out, const void* in, const void* weight, const void* bias,
-                            const float* post_scale, const float* post_shift, const int32_t* cu_seqlens,
-                            int64_t num_segs, int max_seg_len, int channels, int kernel_size, int act,
-                            int dtype, cudaStream_t stream) {
-  OB_REQUIRE(out && in && weight && cu_seqlens, OASR_ERR_INVALID, "packed depthwise conv: null pointer");
-  OB_REQUIRE(kernel_size % 2 == 1, OASR_ERR_INVALID, "packed depthwise conv needs an odd kernel size");
-  if (num_segs == 0 || max_seg_len == 0) return OASR_OK;
-  DwArgs a{};
-  a.out = out; a.in = in; a.weight = weight; a.bias = bias;
-  a.post_scale = post_scale; a.post_shift = post_shift; a.cu_seqlens = cu_seqlens;
-  a.batch = num_segs; a.seq_len = 0; a.out_len = 0; a.channels = channels;
-  a.kernel_size = kernel_size; a.pad_left = (kernel_size - 1) / 2; a.act = act;
-  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, max_seg_len, stream); });
-}
-
 }  // namespace ob
 
 extern "C" {
+
+int oasr_b200_depthwise_conv1d_packed(void* out, const void* in, const void* weight, const void* bias,
+                                      const float* post_scale, const float* post_shift, const float* right_fill,
+                                      const int32_t* fill_frames, const int32_t* cu_seqlens, int64_t num_segs,
+                                      int64_t max_seg_len, int64_t channels, int64_t kernel_size, int activation,
+                                      int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(num_segs >= 0 && max_seg_len >= 0 && channels > 0 && kernel_size > 0, OASR_ERR_INVALID,
+             "depthwise_conv1d_packed: bad shape");
+  if (num_segs == 0 || max_seg_len == 0) return OASR_OK;
+  OB_REQUIRE(out && in && weight && cu_seqlens, OASR_ERR_INVALID, "depthwise_conv1d_packed: null pointer argument");
+  OB_REQUIRE(kernel_size % 2 == 1, OASR_ERR_INVALID, "depthwise_conv1d_packed needs an odd kernel size");
+  OB_REQUIRE((post_scale == nullptr) == (post_shift == nullptr), OASR_ERR_INVALID,
+             "depthwise_conv1d_packed: post_scale and post_shift go together");
+  OB_REQUIRE((right_fill == nullptr) == (fill_frames == nullptr), OASR_ERR_INVALID,
+             "depthwise_conv1d_packed: right_fill and fill_frames go together");
+  OB_REQUIRE(act_is_known(activation), OASR_ERR_INVALID, "depthwise_conv1d_packed: unknown activation id %d", activation);
+  DwArgs a{};
+  a.out = out; a.in = in; a.weight = weight; a.bias = bias;
+  a.post_scale = post_scale; a.post_shift = post_shift; a.cu_seqlens = cu_seqlens;
+  a.right_fill = right_fill; a.fill_frames = fill_frames;
+  a.batch = num_segs; a.channels = (int)channels;
+  a.kernel_size = (int)kernel_size; a.pad_left = ((int)kernel_size - 1) / 2; a.act = activation;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, (int)max_seg_len, s); });
+}
 
 int oasr_b200_depthwise_conv1d(void* out, const void* in, const void* weight, const void* bias,
                                int64_t batch, int64_t seq_len, int64_t channels, int64_t kernel_size,

@@ -482,14 +482,22 @@ bool stride_ok(int64_t s) { return s % 8 == 0; }
 
 }  // namespace fmha
 
-// Internal C++ entry: Conformer relative-position attention over packed rows.
-// qkv4 is (total, 4*H*64): [q+u | q+v | k | v] per row; pos is (pos_rows, H*64) with row stride pos_stride.
-int fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t pos_stride,
-                       const int32_t* cu_seqlens, int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H,
-                       double scale, int dtype, cudaStream_t stream) {
-  using namespace fmha;
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, int64_t pos_rows,
+                                 int64_t pos_stride, const int32_t* cu_seqlens, int64_t num_segs,
+                                 int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype,
+                                 void* stream_) {
+  using namespace ob;
+  using namespace ob::fmha;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int D = 64;
+  if (num_segs == 0 || max_seqlen == 0 || total == 0) return OASR_OK;
   OB_REQUIRE(out && qkv4 && pos && cu_seqlens, OASR_ERR_INVALID, "fmha_varlen_relpos: null pointer argument");
+  OB_REQUIRE(pos_rows >= max_seqlen, OASR_ERR_INVALID, "fmha_varlen_relpos: pos must cover max_seqlen rows");
+  OB_REQUIRE(num_segs <= 65535 && H <= 65535, OASR_ERR_INVALID, "fmha_varlen_relpos: segment / head count too large");
   OB_REQUIRE(is_aligned(out, 16) && is_aligned(qkv4, 16) && is_aligned(pos, 16) && pos_stride % 8 == 0,
              OASR_ERR_ALIGN, "fmha_varlen_relpos: operands must be 16-byte aligned");
   if (num_segs == 0 || max_seqlen == 0 || total == 0) return OASR_OK;
@@ -509,9 +517,6 @@ int fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, int64_t pos
   return dispatch(maps, p, D, dtype, grid, stream);
 }
 
-}  // namespace ob
-
-extern "C" {
 
 int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,
                    const int64_t* k_strides, const int64_t* v_strides, const void* bias, int64_t bias_stride_b,

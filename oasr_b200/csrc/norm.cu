@@ -344,21 +344,188 @@ int launch_bn(const BnArgs& a, cudaStream_t s) {
   return check_launch("batch_norm kernel launch");
 }
 
-}  // namespace
+// ---------------------------------------------------------------------------
+// Residual-stream step of the fused encoder layer.  The residual stream is
+// fp32; sub-layer outputs and normalised activations are 16-bit:
+//   s = res_in + alpha * y                                (fp32; y nullable)
+//   mode 0:  res_out = s,          h = LN_a(s)
+//   mode 1:  res_out = s,          h = s * scale_a + shift_a     (folded inference BatchNorm)
+//   mode 2:  res_out = LN_a(s),    h = LN_b(res_out)             (layer tail: norm_final, then the
+//                                                                 next layer's first pre-norm)
+// One warp per row, the row stays in registers (12*H bytes of traffic per row
+// for a 16-bit y: 4H + 2H read, 4H + 2H written).
+// ---------------------------------------------------------------------------
+struct AddNormArgs {
+  void* h_out;          // T
+  float* res_out;       // nullable (mode 0/1: sum is not kept)
+  const float* res_in;
+  const void* y;        // T, nullable
+  float alpha;
+  const void *w_a, *b_a;        // T (LN) ; mode 1: fp32 scale / shift
+  const void *w_b, *b_b;        // T (mode 2)
+  int64_t rows;
+  int hidden;
+  float eps;
+};
 
-// Internal (C++) entry used by the fused encoder: fp32 rows in, 16-bit rows out.
-int layer_norm_f32_in(void* out, const float* in, const void* weight, const void* bias, int64_t rows,
-                      int64_t hidden, double eps, int out_dtype, cudaStream_t stream) {
-  if (int rc = validate_norm(out, in, weight, rows, hidden, OASR_ACT_NONE)) return rc;
-  NormArgs a{out, nullptr, in, nullptr, weight, bias, rows, (int)hidden, (float)eps, 1.f, OASR_ACT_NONE};
-  return OB_DISPATCH_HALF(out_dtype, T, [&]() -> int {
-    return launch_norm<float, T, T, false, false, false>(a, stream);
-  });
+template <int kChunks>
+__device__ __forceinline__ void row_layer_norm(float (&x)[kChunks][kGran], int H, int lane, float eps) {
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    if ((c * 32 + lane) * kGran < H) {
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) sum += x[c][i];
+    }
+  }
+  const float mean = warp_sum(sum) / H;
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    if ((c * 32 + lane) * kGran < H) {
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) {
+        const float d = x[c][i] - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / H + eps);
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+    for (int i = 0; i < kGran; ++i) x[c][i] = (x[c][i] - mean) * rstd;
+  }
 }
+
+template <typename T, int kChunks, int kMode>
+__global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int H = a.hidden;
+  const float* res = a.res_in ? a.res_in + row * H : nullptr;
+  const T* y = a.y ? static_cast<const T*>(a.y) + row * H : nullptr;
+  float x[kChunks][kGran];
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int e = (c * 32 + lane) * kGran;
+    if (e < H) {
+      if (res) {
+        load8(res + e, x[c]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) x[c][i] = 0.f;
+      }
+      if (y) {
+        float yy[kGran];
+        load8(y + e, yy);
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) x[c][i] = fmaf(a.alpha, yy[i], x[c][i]);
+      }
+      if (kMode != 2 && a.res_out) store8(a.res_out + row * H + e, x[c]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) x[c][i] = 0.f;
+    }
+  }
+  T* h = static_cast<T*>(a.h_out) + row * H;
+  if constexpr (kMode == 1) {
+    const float* sc = static_cast<const float*>(a.w_a);
+    const float* sh = static_cast<const float*>(a.b_a);
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int e = (c * 32 + lane) * kGran;
+      if (e < H) {
+        float s8[kGran], t8[kGran], o8[kGran];
+        load8_param(sc + e, s8);
+        load8_param(sh + e, t8);
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) o8[i] = fmaf(x[c][i], s8[i], t8[i]);
+        store8(h + e, o8);
+      }
+    }
+    return;
+  } else {
+    row_layer_norm<kChunks>(x, H, lane, a.eps);
+    const T* w = static_cast<const T*>(a.w_a);
+    const T* b = static_cast<const T*>(a.b_a);
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const int e = (c * 32 + lane) * kGran;
+      if (e < H) {
+        float g[kGran], bb[kGran];
+        load8_param(w + e, g);
+        load8_param(b + e, bb);
+#pragma unroll
+        for (int i = 0; i < kGran; ++i) x[c][i] = fmaf(x[c][i], g[i], bb[i]);
+        if constexpr (kMode == 0) store8(h + e, x[c]);
+        else store8(a.res_out + row * H + e, x[c]);
+      }
+    }
+    if constexpr (kMode == 2) {
+      row_layer_norm<kChunks>(x, H, lane, a.eps);
+      const T* w2 = static_cast<const T*>(a.w_b);
+      const T* b2 = static_cast<const T*>(a.b_b);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        const int e = (c * 32 + lane) * kGran;
+        if (e < H) {
+          float g[kGran], bb[kGran], o8[kGran];
+          load8_param(w2 + e, g);
+          load8_param(b2 + e, bb);
+#pragma unroll
+          for (int i = 0; i < kGran; ++i) o8[i] = fmaf(x[c][i], g[i], bb[i]);
+          store8(h + e, o8);
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int kMode>
+int launch_add_norm(const AddNormArgs& a, cudaStream_t s) {
+  const int chunks = (a.hidden / kGran + 31) / 32;
+  const int warps = 4;
+  const unsigned grid = static_cast<unsigned>((a.rows + warps - 1) / warps);
+#define OB_AN_CASE(C) add_norm_f32_kernel<T, C, kMode><<<grid, warps * 32, 0, s>>>(a)
+  if (chunks <= 1) OB_AN_CASE(1);
+  else if (chunks <= 2) OB_AN_CASE(2);
+  else if (chunks <= 4) OB_AN_CASE(4);
+  else OB_AN_CASE(8);
+#undef OB_AN_CASE
+  return check_launch("add_norm_f32 launch");
+}
+
+}  // namespace
 
 }  // namespace ob
 
 extern "C" {
+
+int oasr_b200_add_norm_f32(void* h_out, float* res_out, const float* res_in, const void* y, double alpha, int mode,
+                           const void* w_a, const void* b_a, const void* w_b, const void* b_b, int64_t rows,
+                           int64_t hidden, double eps, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(rows >= 0 && hidden > 0, OASR_ERR_INVALID, "add_norm_f32: bad shape");
+  if (rows == 0) return OASR_OK;
+  OB_REQUIRE(h_out && (res_in || y) && w_a && b_a, OASR_ERR_INVALID, "add_norm_f32: null pointer argument");
+  OB_REQUIRE(mode >= 0 && mode <= 2, OASR_ERR_INVALID, "add_norm_f32: mode must be 0, 1 or 2");
+  OB_REQUIRE(mode != 2 || (res_out && w_b && b_b), OASR_ERR_INVALID, "add_norm_f32: mode 2 needs res_out and the second norm");
+  OB_REQUIRE(hidden % 8 == 0 && hidden <= 2048, OASR_ERR_UNSUPPORTED,
+             "add_norm_f32: hidden must be a multiple of 8 and at most 2048 (got %lld)", (long long)hidden);
+  OB_REQUIRE(is_aligned(h_out, 16) && (!res_in || is_aligned(res_in, 16)) && (!res_out || is_aligned(res_out, 16)) &&
+                 (!y || is_aligned(y, 16)) && is_aligned(w_a, 16) && is_aligned(b_a, 16) &&
+                 (!w_b || is_aligned(w_b, 16)) && (!b_b || is_aligned(b_b, 16)),
+             OASR_ERR_ALIGN, "add_norm_f32: pointers must be 16-byte aligned");
+  AddNormArgs a{h_out, res_out, res_in, y, (float)alpha, w_a, b_a, w_b, b_b, rows, (int)hidden, (float)eps};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+    if (mode == 0) return launch_add_norm<T, 0>(a, s);
+    if (mode == 1) return launch_add_norm<T, 1>(a, s);
+    return launch_add_norm<T, 2>(a, s);
+  });
+}
 
 int oasr_b200_layer_norm(void* out, const void* in, const void* weight, const void* bias, int64_t rows,
                          int64_t hidden, double eps, int dtype, void* stream) {

@@ -1,0 +1,62 @@
+"""Fused building blocks of the encoder layer that have no single counterpart in the
+reference's operator list: each one replaces a short chain of reference operators and torch
+glue (cited per function) so that intermediates never reach HBM or are never rounded."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .functional import _DTYPE_ID, _need_cuda, _p, _stream
+
+ADD_NORM_LN, ADD_NORM_AFFINE, ADD_NORM_LN_LN = 0, 1, 2
+
+
+def add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: Optional[torch.Tensor],
+                 y: Optional[torch.Tensor], alpha: float, mode: int, w_a, b_a, w_b=None, b_b=None,
+                 eps: float = 1e-5) -> None:
+    """``s = res_in + alpha*y`` in fp32, then (mode 0) ``h = LN_a(s)``, (mode 1) ``h = s*w_a + b_a``
+    with fp32 per-channel ``w_a/b_a``, or (mode 2) ``res_out = LN_a(s); h = LN_b(res_out)``.
+    The ``x = residual + alpha*sub(x)`` / ``norm(x)`` pairs of ConformerEncoderLayer.forward_packed
+    (oasr/models/conformer/model.py:722-751) with an fp32 residual stream."""
+    _need_cuda(h_out, res_out, res_in, y)
+    rows = h_out.numel() // h_out.size(-1)
+    _lib.call("oasr_b200_add_norm_f32", _p(h_out), _p(res_out), _p(res_in), _p(y), float(alpha), int(mode), _p(w_a),
+              _p(b_a), _p(w_b), _p(b_b), rows, h_out.size(-1), float(eps), _DTYPE_ID[h_out.dtype], _stream(h_out))
+
+
+def depthwise_conv1d_packed(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                            cu_seqlens: torch.Tensor, max_seg_len: int, *, post_scale=None, post_shift=None,
+                            right_fill=None, fill_frames=None, activation: int = -1, out=None) -> torch.Tensor:
+    """Depthwise conv over packed ``(total, C)`` rows, every ``cu_seqlens`` segment alone, optional
+    folded BatchNorm (``post_scale/post_shift`` fp32) and activation: the gapped scatter / conv /
+    gather / BatchNorm+swish of ConvolutionModule._forward_packed_noncausal
+    (oasr/models/conformer/model.py:223-233) in one kernel."""
+    _need_cuda(x, weight, bias, cu_seqlens)
+    if out is None:
+        out = torch.empty_like(x)
+    K = weight.size(0)
+    _lib.call("oasr_b200_depthwise_conv1d_packed", _p(out), _p(x), _p(weight), _p(bias), _p(post_scale),
+              _p(post_shift), _p(right_fill), _p(fill_frames), _p(cu_seqlens), cu_seqlens.numel() - 1,
+              int(max_seg_len), x.size(-1), K, int(activation), _DTYPE_ID[x.dtype], _stream(x))
+    return out
+
+
+def fmha_varlen_relpos(qkv4: torch.Tensor, pos: torch.Tensor, cu_seqlens: torch.Tensor, max_seg_len: int,
+                       heads: int, scale: float, out=None) -> torch.Tensor:
+    """Conformer relative-position attention over packed rows
+    (RelPositionMultiHeadedAttention._forward_packed, oasr/layers/attention/attention.py:323-386).
+    ``qkv4`` ``(total, 4*d)`` = ``[q+u | q+v | k | v]``; ``pos`` = ``linear_pos(pe)[:>=max_seg_len]``
+    as a ``(rows, d)`` view with unit inner stride; returns ``(total, d)``."""
+    _need_cuda(qkv4, pos, cu_seqlens)
+    total, d4 = qkv4.shape
+    d = d4 // 4
+    if out is None:
+        out = torch.empty(total, d, device=qkv4.device, dtype=qkv4.dtype)
+    if pos.stride(1) != 1:
+        raise ValueError("pos must have unit stride along the feature axis")
+    _lib.call("oasr_b200_fmha_varlen_relpos", _p(out), _p(qkv4), _p(pos), pos.size(0), pos.stride(0), _p(cu_seqlens),
+              cu_seqlens.numel() - 1, int(max_seg_len), total, heads, float(scale), _DTYPE_ID[qkv4.dtype],
+              _stream(qkv4))
+    return out

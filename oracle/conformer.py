@@ -51,7 +51,7 @@ class ConformerConfig:
 
 CONFIG1 = ConformerConfig()                                             # CPU-runnable reference case
 CONFIG2 = ConformerConfig(d_model=512, heads=8)                         # offline bf16 headline case
-TINY = ConformerConfig(d_model=64, heads=2, ffn=128, layers=2, vocab=90)
+TINY = ConformerConfig(d_model=128, heads=2, ffn=256, layers=2, vocab=90)
 
 
 # ---------------------------------------------------------------------------

