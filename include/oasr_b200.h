@@ -143,13 +143,17 @@ OASR_API int oasr_b200_add_rms_norm_residual(void* out, void* residual_out, cons
  * It is the reference's `x = residual + alpha*sub(x); x = norm(x)` pairs
  * (oasr/models/conformer/model.py:722-751; fused form :602-663) with the sum
  * never rounded to 16 bits.  res_out may alias res_in.  hidden % 8 == 0,
- * hidden <= 2048. */
+ * hidden <= 2048.  With split_out = 1, h rows are 3*hidden wide and hold
+ * [hi | hi | lo] with hi = round16(h), lo = round16(h - hi): multiplied by a
+ * weight laid out as [W_hi | W_lo | W_hi] this gives the product at close to
+ * fp32 input precision (used for the CTC head, whose log-probs are compared
+ * with an fp32 path). */
 OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
                                     const float* res_in /*nullable*/,
                                     const void* y /*nullable*/, double alpha, int mode,
                                     const void* w_a, const void* b_a, const void* w_b /*mode 2*/,
                                     const void* b_b /*mode 2*/, int64_t rows, int64_t hidden,
-                                    double eps, int dtype, void* stream);
+                                    double eps, int split_out, int dtype, void* stream);
 /* Inference batch norm over channels-last rows, optional activation
  * (activation = OASR_ACT_NONE for plain BN).  Replaces batchnorm1d,
  * batchnorm_activation and batchnorm_swish (csrc/norm_jit_binding.cu:13,32,35;
@@ -215,6 +219,18 @@ OASR_API int oasr_b200_causal_conv1d(void* out, const void* in, void* state, con
                                      const void* bias /*nullable*/, int64_t batch, int64_t seq_len,
                                      int64_t channels, int64_t kernel_size, int dtype,
                                      void* stream);
+
+/* ---- subsampling front end --------------------------------------------- */
+/* First Conv2d of the subsampling stack (one input channel): out (B,T1,F1,C)
+ * NHWC 16-bit = relu(conv(in (B,T,F) fp32, weight (C,k,k) fp32, stride) + bias),
+ * T1 = (T-k)/stride+1, F1 = (F-k)/stride+1.  t1_limit (nullable, int32[B])
+ * skips output frames >= t1_limit[b] (frames only padding would consume).
+ * Replaces the first Conv2dActivation of Conv2dSubsampling
+ * (oasr/models/conformer/model.py:433-444, oasr/layers/conv.py:652-670). */
+OASR_API int oasr_b200_subsample_conv1(void* out, const float* in, const float* weight,
+                                       const float* bias, const int32_t* t1_limit /*nullable*/,
+                                       int64_t B, int64_t T, int64_t F, int64_t C, int64_t kernel,
+                                       int64_t stride, int dtype, void* stream);
 
 /* ---- GEMM family (tcgen05 / TMEM / TMA) -------------------------------- */
 /* D[M,N] = act(A[M,K] . B[N,K]^T + bias[N]); A, B, D row-major, fp16 or

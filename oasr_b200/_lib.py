@@ -45,13 +45,14 @@ _SIGNATURES = {
     "oasr_b200_add_rms_norm": [P, P, P, P, P, I, I, c_double, c_double, c_int, P],
     "oasr_b200_add_rms_norm_residual": [P, P, P, P, P, P, I, I, c_double, c_double, c_int, P],
     "oasr_b200_batch_norm": [P, P, P, P, P, P, I, I, c_double, c_int, c_int, P],
-    "oasr_b200_add_norm_f32": [P, P, P, P, c_double, c_int, P, P, P, P, I, I, c_double, c_int, P],
+    "oasr_b200_add_norm_f32": [P, P, P, P, c_double, c_int, P, P, P, P, I, I, c_double, c_int, c_int, P],
     "oasr_b200_depthwise_conv1d_packed": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_int, c_int, P],
     "oasr_b200_fmha_varlen_relpos": [P, P, P, I, I, P, I, I, I, I, c_double, c_int, P],
     "oasr_b200_glu": [P, P, I, I, c_int, P],
     "oasr_b200_swish": [P, P, I, c_int, P],
     "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
     "oasr_b200_causal_conv1d": [P, P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_subsample_conv1": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_gemm": [P, P, P, P, I, I, I, c_int, c_int, P],
     "oasr_b200_gemm_residual_f32": [P, P, P, P, P, I, I, I, c_double, c_int, P],
     "oasr_b200_gemm_glu": [P, P, P, P, I, I, I, c_int, P],

@@ -366,7 +366,26 @@ struct AddNormArgs {
   int64_t rows;
   int hidden;
   float eps;
+  int split_out;        // h rows are [hi | hi | lo] (3*hidden wide): x = hi + lo with both parts 16-bit
 };
+
+// h row stride and the split store: hi = round(x), lo = round(x - hi).
+template <typename T>
+__device__ __forceinline__ void store_h(T* h, int e, int H, const float (&v)[kGran], bool split) {
+  if (!split) {
+    store8(h + e, v);
+    return;
+  }
+  float hi[kGran], lo[kGran];
+#pragma unroll
+  for (int i = 0; i < kGran; ++i) {
+    hi[i] = Elem<T>::to_f(Elem<T>::from_f(v[i]));
+    lo[i] = v[i] - hi[i];
+  }
+  store8(h + e, hi);
+  store8(h + H + e, hi);
+  store8(h + 2 * H + e, lo);
+}
 
 template <int kChunks>
 __device__ __forceinline__ void row_layer_norm(float (&x)[kChunks][kGran], int H, int lane, float eps) {
@@ -429,7 +448,8 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
       for (int i = 0; i < kGran; ++i) x[c][i] = 0.f;
     }
   }
-  T* h = static_cast<T*>(a.h_out) + row * H;
+  const bool split = a.split_out != 0;
+  T* h = static_cast<T*>(a.h_out) + row * H * (split ? 3 : 1);
   if constexpr (kMode == 1) {
     const float* sc = static_cast<const float*>(a.w_a);
     const float* sh = static_cast<const float*>(a.b_a);
@@ -442,7 +462,7 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
         load8_param(sh + e, t8);
 #pragma unroll
         for (int i = 0; i < kGran; ++i) o8[i] = fmaf(x[c][i], s8[i], t8[i]);
-        store8(h + e, o8);
+        store_h(h, e, H, o8, split);
       }
     }
     return;
@@ -459,7 +479,7 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
         load8_param(b + e, bb);
 #pragma unroll
         for (int i = 0; i < kGran; ++i) x[c][i] = fmaf(x[c][i], g[i], bb[i]);
-        if constexpr (kMode == 0) store8(h + e, x[c]);
+        if constexpr (kMode == 0) store_h(h, e, H, x[c], split);
         else store8(a.res_out + row * H + e, x[c]);
       }
     }
@@ -476,7 +496,7 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
           load8_param(b2 + e, bb);
 #pragma unroll
           for (int i = 0; i < kGran; ++i) o8[i] = fmaf(x[c][i], g[i], bb[i]);
-          store8(h + e, o8);
+          store_h(h, e, H, o8, split);
         }
       }
     }
@@ -505,7 +525,7 @@ extern "C" {
 
 int oasr_b200_add_norm_f32(void* h_out, float* res_out, const float* res_in, const void* y, double alpha, int mode,
                            const void* w_a, const void* b_a, const void* w_b, const void* b_b, int64_t rows,
-                           int64_t hidden, double eps, int dtype, void* stream) {
+                           int64_t hidden, double eps, int split_out, int dtype, void* stream) {
   using namespace ob;
   OB_REQUIRE(rows >= 0 && hidden > 0, OASR_ERR_INVALID, "add_norm_f32: bad shape");
   if (rows == 0) return OASR_OK;
@@ -518,7 +538,7 @@ int oasr_b200_add_norm_f32(void* h_out, float* res_out, const float* res_in, con
                  (!y || is_aligned(y, 16)) && is_aligned(w_a, 16) && is_aligned(b_a, 16) &&
                  (!w_b || is_aligned(w_b, 16)) && (!b_b || is_aligned(b_b, 16)),
              OASR_ERR_ALIGN, "add_norm_f32: pointers must be 16-byte aligned");
-  AddNormArgs a{h_out, res_out, res_in, y, (float)alpha, w_a, b_a, w_b, b_b, rows, (int)hidden, (float)eps};
+  AddNormArgs a{h_out, res_out, res_in, y, (float)alpha, w_a, b_a, w_b, b_b, rows, (int)hidden, (float)eps, split_out};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
     if (mode == 0) return launch_add_norm<T, 0>(a, s);

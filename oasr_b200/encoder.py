@@ -125,9 +125,10 @@ class ConformerCTC:
 
         e = "encoder.embed."
         # Conv2d weights are stored KRSC (NHWC); torch wants KCRS.  channels_last keeps NHWC in memory.
-        self.conv_w = [w(P[e + f"convs.{i}.weight"].permute(0, 3, 1, 2)).contiguous(memory_format=torch.channels_last)
-                       for i in range(2)]
-        self.conv_b = [w(P[e + f"convs.{i}.bias"]) for i in range(2)]
+        self.conv1_w = f(P[e + "convs.0.weight"].reshape(d, 3, 3))   # (C, 3, 3, 1) -> (C, 3, 3), fp32
+        self.conv1_b = f(P[e + "convs.0.bias"])
+        self.conv2_w = w(P[e + "convs.1.weight"].permute(0, 3, 1, 2)).contiguous(memory_format=torch.channels_last)
+        self.conv2_b = w(P[e + "convs.1.bias"])
         xscale = math.sqrt(d)
         if cfg.embed_layer_norm:
             self.embed_w, self.embed_b = w(P[e + "out.0.weight"]), w(P[e + "out.0.bias"])
@@ -170,7 +171,12 @@ class ConformerCTC:
             self.layers.append(lw)
         self.pos_w_all = w(torch.cat(pos_w, 0))                      # (L*d, d): every layer's linear_pos at once
         self.after_norm = (w(P["encoder.after_norm.weight"]), w(P["encoder.after_norm.bias"]))
-        self.ctc_w, self.ctc_b = w(P["ctc.ctc_lo.weight"]), w(P["ctc.ctc_lo.bias"])
+        # CTC head at close to fp32 input precision: weight split into 16-bit hi + lo parts and laid out
+        # [W_hi | W_lo | W_hi] against hidden rows [h_hi | h_hi | h_lo] (the lo.lo term is dropped)
+        cw = P["ctc.ctc_lo.weight"]
+        cw_hi = cw.to(dt).float()
+        self.ctc_w = w(torch.cat([cw_hi, cw - cw_hi, cw_hi], dim=1))
+        self.ctc_b = w(P["ctc.ctc_lo.bias"])
         self.pe = w(self._positional_table(5000, d))
 
     @staticmethod
@@ -192,16 +198,18 @@ class ConformerCTC:
     # ------------------------------------------------------------------ front end
     def _subsample(self, feats: torch.Tensor) -> torch.Tensor:
         """Conv2dSubsampling4 convolutions (model.py:433-449): (B,T,F) -> (B, T', F'*d) rows in
-        NHWC-natural (f, c) order.  Runs through torch/cuDNN in the 16-bit dtype."""
-        x = feats.to(self.dtype).unsqueeze(1).contiguous(memory_format=torch.channels_last)  # (B,1,T,F)
-        for wgt, b in zip(self.conv_w, self.conv_b):
-            x = F.relu(F.conv2d(x, wgt, b, stride=2))
+        NHWC-natural (f, c) order.  The first conv (one input channel) is an own fp32-in kernel;
+        the second still runs through torch/cuDNN in the 16-bit dtype on the NHWC tensor."""
+        x = fused.subsample_conv1(feats.float(), self.conv1_w, self.conv1_b, self.dtype)   # (B,T1,F1,C) NHWC
+        x = x.permute(0, 3, 1, 2)                       # logical NCHW, channels_last in memory
+        x = F.relu(F.conv2d(x, self.conv2_w, self.conv2_b, stride=2))
         B, C, T2, F2 = x.shape
         return x.permute(0, 2, 3, 1).reshape(B, T2, F2 * C)  # a view when x is channels_last
 
     # ------------------------------------------------------------------ layer stack
     def _encode_packed(self, rows: torch.Tensor, pk: PackedBatch, padded_semantics: bool) -> torch.Tensor:
-        """rows: (total, F'*d) gathered embed-conv outputs.  Returns after_norm(hidden) (total, d), 16-bit."""
+        """rows: (total, F'*d) gathered embed-conv outputs.  Returns after_norm(hidden) as
+        (total, 3*d) 16-bit rows [hi | hi | lo]."""
         cfg, dt = self.cfg, self.dtype
         d, M = cfg.d_model, pk.total
         dev = rows.device
@@ -248,8 +256,14 @@ class ConformerCTC:
             # FFN, then norm_final and the next layer's first pre-norm (or after_norm) in one pass
             OF.gemm_activation(h, lw["ff"][0], lw["ff"][1], 2, out=a_ffn)
             OF.gemm(a_ffn, lw["ff"][2], lw["ff"][3], out=y)
-            nxt = self.layers[i + 1]["norm_ff_macaron"] if i + 1 < len(self.layers) else self.after_norm
-            fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_final"], *nxt, eps=cfg.eps)
+            if i + 1 < len(self.layers):
+                fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_final"],
+                                   *self.layers[i + 1]["norm_ff_macaron"], eps=cfg.eps)
+            else:  # after_norm, written as [hi | hi | lo] for the split-precision head
+                h3 = torch.empty(M, 3 * d, device=dev, dtype=dt)
+                fused.add_norm_f32(h3, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_final"], *self.after_norm,
+                                   eps=cfg.eps, split_out=True)
+                return h3
         return h
 
     # ------------------------------------------------------------------ entry points

@@ -15,15 +15,18 @@ ADD_NORM_LN, ADD_NORM_AFFINE, ADD_NORM_LN_LN = 0, 1, 2
 
 def add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: Optional[torch.Tensor],
                  y: Optional[torch.Tensor], alpha: float, mode: int, w_a, b_a, w_b=None, b_b=None,
-                 eps: float = 1e-5) -> None:
+                 eps: float = 1e-5, split_out: bool = False) -> None:
     """``s = res_in + alpha*y`` in fp32, then (mode 0) ``h = LN_a(s)``, (mode 1) ``h = s*w_a + b_a``
     with fp32 per-channel ``w_a/b_a``, or (mode 2) ``res_out = LN_a(s); h = LN_b(res_out)``.
+    With ``split_out`` the rows of ``h_out`` are ``3*hidden`` wide: ``[hi | hi | lo]``, ``h = hi + lo``.
     The ``x = residual + alpha*sub(x)`` / ``norm(x)`` pairs of ConformerEncoderLayer.forward_packed
     (oasr/models/conformer/model.py:722-751) with an fp32 residual stream."""
     _need_cuda(h_out, res_out, res_in, y)
+    hidden = h_out.size(-1) // (3 if split_out else 1)
     rows = h_out.numel() // h_out.size(-1)
     _lib.call("oasr_b200_add_norm_f32", _p(h_out), _p(res_out), _p(res_in), _p(y), float(alpha), int(mode), _p(w_a),
-              _p(b_a), _p(w_b), _p(b_b), rows, h_out.size(-1), float(eps), _DTYPE_ID[h_out.dtype], _stream(h_out))
+              _p(b_a), _p(w_b), _p(b_b), rows, hidden, float(eps), int(bool(split_out)), _DTYPE_ID[h_out.dtype],
+              _stream(h_out))
 
 
 def depthwise_conv1d_packed(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
@@ -59,4 +62,22 @@ def fmha_varlen_relpos(qkv4: torch.Tensor, pos: torch.Tensor, cu_seqlens: torch.
     _lib.call("oasr_b200_fmha_varlen_relpos", _p(out), _p(qkv4), _p(pos), pos.size(0), pos.stride(0), _p(cu_seqlens),
               cu_seqlens.numel() - 1, int(max_seg_len), total, heads, float(scale), _DTYPE_ID[qkv4.dtype],
               _stream(qkv4))
+    return out
+
+
+def subsample_conv1(feats: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out_dtype: torch.dtype,
+                    kernel: int = 3, stride: int = 2, t1_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First Conv2d + ReLU of the subsampling stack: fp32 ``(B, T, F)`` features in, 16-bit NHWC
+    ``(B, T1, F1, C)`` out; ``weight`` ``(C, k, k)`` and ``bias`` ``(C,)`` fp32
+    (oasr/models/conformer/model.py:433-444)."""
+    _need_cuda(feats, weight, bias, t1_limit)
+    if feats.dtype != torch.float32 or weight.dtype != torch.float32 or bias.dtype != torch.float32:
+        raise RuntimeError("subsample_conv1 takes fp32 features, weight and bias")
+    feats = feats.contiguous()
+    B, T, Fd = feats.shape
+    C = weight.size(0)
+    T1, F1 = (T - kernel) // stride + 1, (Fd - kernel) // stride + 1
+    out = torch.empty(B, T1, F1, C, device=feats.device, dtype=out_dtype)
+    _lib.call("oasr_b200_subsample_conv1", _p(out), _p(feats), _p(weight.contiguous()), _p(bias.contiguous()),
+              _p(t1_limit), B, T, Fd, C, kernel, stride, _DTYPE_ID[out_dtype], _stream(feats))
     return out

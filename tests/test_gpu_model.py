@@ -3,6 +3,13 @@ fixtures written from the reference, on the same seeded weights and features.
 
 Gates (bf16 vs the fp32 path, valid frames, raw-vocabulary columns): max-abs <= 2e-2,
 mean-abs <= 1e-3, greedy-argmax agreement >= 99.9 % of frames.
+
+The argmax gate is asserted on the frames whose oracle top-1/top-2 margin exceeds 2e-2 (the
+max-abs tolerance); the agreement over ALL frames is printed and bounded from below.  With
+weights ~N(0, 0.02) a quarter of the frames have a margin below the tolerance itself, and
+rounding nothing but the weight matrices to bf16 (every activation kept in fp32, CPU) already
+changes the argmax on 0.6 % of the frames of config 1 -- no bf16 implementation can agree on
+99.9 % of all frames there.
 """
 from pathlib import Path
 
@@ -61,7 +68,8 @@ def test_encoder_ctc_matches_oracle(name, path):
     valid = _valid(lp, out_len)
     mx, mean, agree, agree_clear = _report(lp, want, valid, cfg.vocab, f"{name}/{path}")
     assert mx <= MAX_ABS and mean <= MEAN_ABS
-    assert agree >= ARGMAX_AGREE or agree_clear >= ARGMAX_AGREE
+    assert agree_clear >= ARGMAX_AGREE
+    assert agree >= 0.95
     # against the fixture written from the reference itself
     gold = np.load(GOLD / f"model_{name}.npz")
     assert np.array_equal(out_len.cpu().numpy(), gold[f"{path}_out_len"])
@@ -107,3 +115,22 @@ def test_greedy_search_matches_oracle_tokens():
     # token sequences agree with the reference's wherever its per-frame margin is not a numerical tie
     same = sum(a == b for a, b in zip(flat, ref)) / max(len(ref), 1)
     print(f"greedy tokens identical positions: {same:.4f} (len {len(flat)} vs {len(ref)})")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_subsample_conv1_matches_conv2d(dtype):
+    """First subsampling conv (own kernel) vs F.conv2d + ReLU in fp32."""
+    import torch.nn.functional as F
+    from oasr_b200 import fused
+
+    g = torch.Generator().manual_seed(3)
+    feats = torch.randn(3, 67, 80, generator=g)
+    w = torch.randn(256, 3, 3, generator=g) * 0.3
+    b = torch.randn(256, generator=g) * 0.1
+    got = fused.subsample_conv1(feats.cuda(), w.cuda(), b.cuda(), dtype)
+    want = F.relu(F.conv2d(feats.unsqueeze(1), w.unsqueeze(1), b, stride=2)).permute(0, 2, 3, 1)  # (B,T1,F1,C)
+    assert got.shape == want.shape
+    assert torch.equal(got.cpu(), want.to(dtype)) or (got.float().cpu() - want).abs().max() < 2e-2
+    lim = torch.tensor([33, 5, 0], dtype=torch.int32).cuda()
+    part = fused.subsample_conv1(feats.cuda(), w.cuda(), b.cuda(), dtype, t1_limit=lim)
+    assert torch.equal(part[0], got[0]) and torch.equal(part[1, :5], got[1, :5])
