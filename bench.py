@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Headline benchmark: offline Conformer encoder + CTC throughput in audio-seconds / second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE config 2): 12-layer Conformer, d_model 512, 8 heads, FFN 2048, conv
+kernel 15, 80-dim fbank, 4x Conv2d subsampling, CTC vocabulary 5002 (head padded to 5008),
+bf16 compute, random-init weights from a seed; one step = one batch of 64 utterances with
+lengths uniform in 200..2000 frames (10 ms hop), features iid N(0,1), sequence-packed.
+Synthetic features stand in for real audio (no dataset is available offline).
+
+One JSON line is printed by rank 0:
+  value      features already in HBM, features -> packed fp32 log-probs + per-frame argmax,
+             device-timed per step with CUDA events (L2 flushed between steps)
+  e2e        the public call a user makes (ConformerCTC.greedy_search): pinned host
+             features -> H2D -> encoder + head -> D2H of the per-frame argmax -> token lists
+  roofline   the dominant kernel (the tcgen05 GEMM): algorithmic flops / CUDA-event time of
+             its launches in an instrumented extra step, against the measured bf16 peak
+  cpu_baseline  the fp32 CPU oracle (a port of the reference's torch path) on a bounded sample
+Under torchrun every rank runs its own batch (utterance-sharded, no collective on the data
+path); time is the max over ranks, value the sum of audio over ranks divided by it.
+
+``--impl reference`` times the CPU port of the reference's fp32 path (the reference package
+itself does not travel to the GPU box) on a bounded sample per step and prints the same line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FRAME_S = 0.01
+WORKLOAD = "conformer12_d512_h8_ffn2048_k15_vocab5002_b64_len200-2000_packed"
+CPU_SAMPLE_UTTS = 8
+
+
+def make_batch(rank: int, batch: int = 64):
+    """Seeded lengths (numpy default_rng(2024 + rank)) and features (torch seed 7 + rank)."""
+    rng = np.random.default_rng(2024 + rank)
+    lengths = [int(x) for x in rng.integers(200, 2001, size=batch)]
+    g = torch.Generator().manual_seed(7 + rank)
+    feats = torch.randn(batch, max(lengths), 80, generator=g)
+    return feats, lengths
+
+
+def model_config():
+    from oasr_b200.encoder import ConformerConfig
+
+    return ConformerConfig(input_size=80, d_model=512, heads=8, ffn=2048, layers=12, kernel=15, vocab=5002)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def gemm_flops(name, args):
+    """Algorithmic flops (2*M*N*K) of one GEMM-family C-ABI call from its integer arguments."""
+    if name == "oasr_b200_gemm":
+        M, N, K = args[4], args[5], args[6]
+    elif name == "oasr_b200_gemm_glu":
+        M, N, K = args[4], 2 * args[5], args[6]
+    elif name == "oasr_b200_gemm_log_softmax":
+        M, N, K = args[4], args[5], args[6]
+    elif name == "oasr_b200_gemm_residual_f32":
+        M, N, K = args[5], args[6], args[7]
+    else:
+        return None
+    return 2.0 * M * N * K
+
+
+def instrumented_step(run_step):
+    """One extra step with a CUDA-event pair around every C-ABI call, on the launching stream."""
+    from oasr_b200 import _lib
+
+    records, open_ev = [], {}
+
+    def hook(name, phase, args):
+        if phase == "begin":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            open_ev[name] = ev
+        else:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            records.append((name, open_ev.pop(name), end, gemm_flops(name, args)))
+
+    _lib.set_call_hook(hook)
+    try:
+        run_step()
+        torch.cuda.synchronize()
+    finally:
+        _lib.set_call_hook(None)
+    per = {}
+    for name, a, b, fl in records:
+        d = per.setdefault(name.replace("oasr_b200_", ""), {"launches": 0, "ms": 0.0, "flops": 0.0})
+        d["launches"] += 1
+        d["ms"] += a.elapsed_time(b)
+        if fl:
+            d["flops"] += fl
+    return per
+
+
+def cpu_port_throughput(sample_utts: int, repeats: int = 1, threads=None):
+    """audio-s/s of the fp32 CPU port of the reference path on the first `sample_utts` utterances."""
+    from oracle import conformer as OC
+
+    if threads:
+        torch.set_num_threads(threads)
+    cfg = OC.CONFIG2
+    P = OC.init_params(cfg, 1234)
+    feats, lengths = make_batch(0)
+    lens = lengths[:sample_utts]
+    f = feats[:sample_utts, :max(lens)].contiguous()
+    lt = torch.tensor(lens, dtype=torch.int64)
+    audio_s = sum(lens) * FRAME_S
+    with torch.no_grad():
+        best = None
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            OC.forward_offline_packed(P, cfg, f, lt)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+    return audio_s / best, audio_s, best, torch.get_num_threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for _ in range(args.warmup):
+        cpu_port_throughput(2)
+    times, audio = [], 0.0
+    for _ in range(args.steps):
+        v, a, dt, thr = cpu_port_throughput(CPU_SAMPLE_UTTS)
+        times.append(dt)
+        audio += a
+    value = audio / sum(times)
+    sample = f"first {CPU_SAMPLE_UTTS} of the 64 utterances per step (packed path, fp32)"
+    line = {
+        "impl": "reference", "metric": "audio_seconds_per_second", "value": value, "unit": "audio-s/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "audio-s/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "audio-s/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    import oasr_b200
+    from oasr_b200 import _lib
+    from oasr_b200.encoder import ConformerCTC
+    from oasr_b200.weights import init_params
+
+    cfg = model_config()
+    model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16)
+    feats_host, lengths = make_batch(rank)
+    feats_host = feats_host.pin_memory()
+    feats_dev = feats_host.cuda(non_blocking=True)
+    audio_s = sum(lengths) * FRAME_S
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def device_step():
+        return model.forward_offline_packed(feats_dev, lengths, padded_output=False)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        device_step()
+    barrier()
+    assert oasr_b200.device_status() == 0
+    # ---------------- device-resident throughput ----------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = _lib.launch_count()
+    evs = []
+    barrier()
+    for _ in range(args.steps):
+        flush.fill_(1)                       # L2 flush, outside the per-step event pair
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        device_step()
+        b.record()
+        evs.append((a, b))
+    barrier()
+    launches = _lib.launch_count() - launches0
+    step_ms = [a.elapsed_time(b) for a, b in evs]
+    total_ms = float(sum(step_ms))
+    # ---------------- end to end through the public call ----------------
+    for _ in range(2):
+        model.greedy_search(feats_host.cuda(non_blocking=True), lengths)
+    barrier()
+    t0 = time.perf_counter()
+    d2h = 0
+    for _ in range(args.steps):
+        f = feats_host.cuda(non_blocking=True)
+        hyp = model.greedy_search(f, lengths)
+        d2h = 4 * sum(max((n - 3) // 4, 0) for n in lengths)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    assert oasr_b200.device_status() == 0
+
+    t = torch.tensor([total_ms, e2e_s * 1e3, audio_s * args.steps], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = t.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, audio_total = float(mx[0]), float(mx[1]), float(sm[2])
+    else:
+        total_ms, e2e_ms, audio_total = float(t[0]), float(t[1]), float(t[2])
+
+    if rank == 0:
+        per = instrumented_step(device_step)
+        peaks = measured_peaks()
+        gemm = {"launches": 0, "ms": 0.0, "flops": 0.0}
+        for k in ("gemm", "gemm_glu"):
+            if k in per:
+                for f in gemm:
+                    gemm[f] += per[k][f]
+        step_total = total_ms / args.steps if dist is None else float(np.mean(step_ms))
+        achieved = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
+        roofline = {
+            "kernel": "gemm_tcgen05_kernel (oasr_b200_gemm / gemm_glu launches of one step)",
+            "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["bf16_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
+            "traffic": None, "launches": gemm["launches"], "share_of_step": gemm["ms"] / step_total if step_total else None,
+        }
+        kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}
+        cpu = None
+        if not args.no_cpu_baseline:
+            v, a, dt, thr = cpu_port_throughput(CPU_SAMPLE_UTTS)
+            cpu = {"value": v, "unit": "audio-s/s", "cores": thr, "kind": "port",
+                   "sample": f"first {CPU_SAMPLE_UTTS} of the 64 utterances ({a:.1f} audio-s), fp32 packed path, one run of {dt:.1f} s"}
+        line = {
+            "metric": "audio_seconds_per_second", "value": audio_total / (total_ms * 1e-3), "unit": "audio-s/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": 64 * world, "parallelism": f"utterance-sharded x{world}, no collective",
+                       "l2": "256 MiB flush write between steps; per-step working set (weights 240 MB + activations) > 126 MB L2",
+                       "audio_seconds_per_step": audio_total / args.steps},
+            "e2e": {"value": audio_total / (e2e_ms * 1e-3), "unit": "audio-s/s",
+                    "h2d_bytes_per_step": int(feats_host.numel() * 4), "d2h_bytes_per_step": int(d2h),
+                    "api": "ConformerCTC.greedy_search(pinned host features -> token lists)"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+            "kernels_one_step": kernels,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -79,6 +79,9 @@ OASR_API const char* oasr_b200_last_error(void);
  * `stream`.  Returns 0 when no kernel reported a problem, else
  * OASR_ERR_DEVICE_WAIT with the raw word in *word (nullable). */
 OASR_API int oasr_b200_device_status(uint32_t* word /*host*/, void* stream);
+/* Number of kernels this library has launched in this process so far
+ * (host-side counter, one per launch; no reference counterpart). */
+OASR_API unsigned long long oasr_b200_launch_count(void);
 /* Process-wide integer tunables.  "gemm_bn": 0 = heuristic tile width, or 64 /
  * 128 / 256 to force it (no reference counterpart; the reference selects tiles
  * through its JIT variant names, oasr/jit/gemm.py:863-880). */

@@ -90,6 +90,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = c_char_p
         fn.argtypes = []
+    lib.oasr_b200_launch_count.restype = ctypes.c_ulonglong
+    lib.oasr_b200_launch_count.argtypes = []
     for name, argtypes in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -101,7 +103,22 @@ def load() -> ctypes.CDLL:
 
 
 def exported_names() -> list[str]:
-    return list(_STRING_FUNCS) + list(_SIGNATURES)
+    return list(_STRING_FUNCS) + ["oasr_b200_launch_count"] + list(_SIGNATURES)
+
+
+def launch_count() -> int:
+    """Kernels launched through the library by this process so far."""
+    return int(load().oasr_b200_launch_count())
+
+
+# Optional per-call observer used by bench.py to time kernels with CUDA events:
+# called as hook(name, phase) with phase "begin" / "end" around every C-ABI call.
+_call_hook = None
+
+
+def set_call_hook(hook) -> None:
+    global _call_hook
+    _call_hook = hook
 
 
 def last_error() -> str:
@@ -121,7 +138,14 @@ def check(code: int) -> None:
 
 
 def call(name: str, *args) -> None:
-    check(getattr(load(), name)(*args))
+    if _call_hook is None:
+        check(getattr(load(), name)(*args))
+        return
+    _call_hook(name, "begin", args)
+    try:
+        check(getattr(load(), name)(*args))
+    finally:
+        _call_hook(name, "end", args)
 
 
 def version() -> str:

@@ -17,7 +17,10 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+static unsigned long long g_launches = 0;  // kernels launched through this library (host-side count)
+
 int check_launch(const char* what) {
+  ++g_launches;
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     return set_error(OASR_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
@@ -68,6 +71,8 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   return ob::set_error(OASR_ERR_INVALID, "unknown tunable '%s'", name ? name : "(null)");
 }
+
+unsigned long long oasr_b200_launch_count(void) { return ob::g_launches; }
 
 const char* oasr_b200_version(void) { return "oasr_b200 0.1.0 sm_100a"; }
 

@@ -95,3 +95,16 @@ def test_model_oracle_matches_reference_fixture(name):
         toks = OC.greedy_tokens(lp, out_len, cfg.vocab)
         flat = np.array([t for h in toks for t in h + [-1]], dtype=np.int32)
         assert np.array_equal(flat, gold[f"{path}_tokens"])
+
+
+def test_package_weight_init_equals_oracle_init():
+    """The product's seeded init and the oracle's are the same tensors, so GPU runs and the
+    CPU baseline see identical weights."""
+    from oasr_b200.encoder import ConformerConfig
+    from oasr_b200.weights import init_params
+
+    cfg = OC.TINY
+    mine = init_params(ConformerConfig(**{f: getattr(cfg, f) for f in ConformerConfig.__dataclass_fields__}), 99)
+    theirs = OC.init_params(cfg, 99, 0.0)
+    assert list(mine) == list(theirs)
+    assert all(torch.equal(mine[k], theirs[k]) for k in mine)
