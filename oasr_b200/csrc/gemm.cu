@@ -129,7 +129,9 @@ template <int BN, int kStages>
 struct Smem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
-  static constexpr int kBarOffset = kStages * (kABytes + kBBytes);
+  static constexpr int kStageOut = kStages * (kABytes + kBBytes);  // 2 x 16 KB output staging (128 rows x 128 B)
+  static constexpr int kOutBytes = BM * 128;
+  static constexpr int kBarOffset = kStageOut + 2 * kOutBytes;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
@@ -158,11 +160,18 @@ __device__ __forceinline__ void load_bias8(const T* p, float (&f)[8]) {
   for (int i = 0; i < 8; ++i) f[i] = Elem<T>::to_f(v.v[i]);
 }
 
+// Output path: the epilogue warps write 128-byte row pieces into a swizzled staging tile and one
+// thread stores the tile with TMA (clipped at the tensor edge).  Grouped problems keep per-thread
+// stores because a tile may end inside the tensor (at a group boundary).
+template <int kSched, int kEpi>
+constexpr bool uses_tma_store() { return kSched != kSchedGroup && kEpi != kEpiResid; }
+
 template <typename T, int BN, int kStages, int kSched, int kEpi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const Params p) {
+                    const __grid_constant__ CUtensorMap tmap_d, const Params p) {
   using S = Smem<BN, kStages>;
+  constexpr bool kTmaStore = uses_tma_store<kSched, kEpi>();
   constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr uint32_t kIdesc = ptx::umma_idesc_f16(kBf16, BM, BN);
@@ -195,6 +204,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     ptx::fence_proxy_async_smem();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    if (kTmaStore) ptx::prefetch_tensormap(&tmap_d);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
@@ -274,6 +284,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // kEpiLsm running statistics of this thread's row
     float run_max = -INFINITY, run_sum = 0.f, lse = 0.f;
     int run_arg = 0;
+    // TMA-store staging: `w` is this thread's 128 bytes of row (q*32+lane) for output columns
+    // starting at `col`; the 128 x 128 B tile goes out as one box at (col, row0, batch).
+    uint8_t* stage_out = smem + S::kStageOut;
+    int out_buf = 0;
+    const bool issuer = threadIdx.x == 64;
+    const int tile_row = q * 32 + lane;
+    auto stage_and_store = [&](const uint32_t (&w)[32], int col, const Tile& tt) {
+      if (issuer) ptx::bulk_wait_group_read<1>();  // the store that last used this buffer has read it
+      ptx::named_barrier_sync(1, kEpiWarps * 32);
+      uint8_t* row = stage_out + out_buf * S::kOutBytes + tile_row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<uint4*>(row + ((c ^ (tile_row & 7)) * 16)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::named_barrier_sync(1, kEpiWarps * 32);
+      if (issuer) {
+        ptx::tma_store_3d(&tmap_d, stage_out + out_buf * S::kOutBytes, col, tt.a_row, tt.a_batch);
+        ptx::bulk_commit_group();
+      }
+      out_buf ^= 1;
+    };
     for (int iter = 0; ok && sched.get(iter, t); ++iter) {
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
@@ -283,7 +315,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < t.row_end;
       const uint32_t t_acc = tmem_base + lane_base + acc * BN;
 
-      if constexpr (kEpi == kEpiStore) {
+      if constexpr (kEpi == kEpiStore && kTmaStore) {
+        const T* bias = static_cast<const T*>(p.bias);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[64];
+          ptx::tmem_ld_32x32(t_acc + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          ptx::tmem_ld_32x32(t_acc + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          ptx::tmem_ld_wait();
+          uint32_t w[32];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int col = t.n0 + c0 + g * 8;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g * 8 + i]);
+            if (bias && col < p.N) {
+              float bb[8];
+              load_bias8(bias + col, bb);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += bb[i];
+            }
+            if (p.act != OASR_ACT_NONE) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = apply_act_rt(v[i], p.act);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) w[g * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
+          }
+          stage_and_store(w, t.n0 + c0, t);
+        }
+      } else if constexpr (kEpi == kEpiStore) {
         T* drow = static_cast<T*>(p.D) + row * p.N;
         const T* bias = static_cast<const T*>(p.bias);
 #pragma unroll 1
@@ -355,6 +418,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
         }
+      } else if constexpr (kEpi == kEpiGlu && kTmaStore) {
+        // accumulator columns [0, BN/2) hold the value half, [BN/2, BN) the gate half
+        constexpr int HN = BN / 2;
+        const int n0 = t.n0 / 2;
+        const T* bias = static_cast<const T*>(p.bias);
+#pragma unroll 1
+        for (int c0 = 0; c0 < HN; c0 += 64) {
+          if (n0 + c0 >= p.N) break;
+          uint32_t w[32];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t rv[32], rg[32];
+            ptx::tmem_ld_32x32(t_acc + c0 + half * 32, rv);
+            ptx::tmem_ld_32x32(t_acc + HN + c0 + half * 32, rg);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = n0 + c0 + half * 32 + g * 8;
+              float v[8], gt[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { v[i] = bits_f(rv[g * 8 + i]); gt[i] = bits_f(rg[g * 8 + i]); }
+              if (bias && col < p.N) {
+                float bb[8];
+                load_bias8(bias + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += bb[i];
+                load_bias8(bias + p.N + col, bb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) gt[i] += bb[i];
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] *= sigmoid_f(gt[i]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) w[half * 16 + g * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
+            }
+          }
+          stage_and_store(w, n0 + c0, t);
+        }
       } else if constexpr (kEpi == kEpiGlu) {
         // accumulator columns [0, BN/2) hold the value half, [BN/2, BN) the gate half
         constexpr int HN = BN / 2;
@@ -400,15 +501,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // column tiles.  Pass 1: the same products again, written as logit - lse.
         const T* bias = static_cast<const T*>(p.bias);
         if (t.pass == 0 && t.n_idx == 0) { run_max = -INFINITY; run_sum = 0.f; run_arg = 0; }
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (t.n0 + c0 >= p.N) break;
+        uint32_t wout[32];
+        // 32 accumulator columns starting at tile column cc; kHalf selects the half of `wout` a
+        // 16-bit output chunk fills (compile-time so that `wout` stays in registers)
+        auto process32 = [&](int cc, auto half_c) {
+          constexpr int kHalf = decltype(half_c)::value;
           uint32_t r[32];
-          ptx::tmem_ld_32x32(t_acc + c0, r);
+          ptx::tmem_ld_32x32(t_acc + cc, r);
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int col = t.n0 + c0 + g * 8;
+            const int col = t.n0 + cc + g * 8;
             if (col < p.N) {
               float v[8];
 #pragma unroll
@@ -433,6 +536,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) run_sum += __expf(v[i] - run_max);
+              } else if constexpr (kTmaStore) {
+                if (p.out_f32) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) wout[g * 8 + i] = __float_as_uint(v[i] - lse);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) wout[kHalf * 16 + g * 4 + i] = pack2<T>(v[2 * i] - lse, v[2 * i + 1] - lse);
+                }
               } else if (row_ok) {
                 if (p.out_f32) {
                   float* orow = static_cast<float*>(p.D) + row * p.N + col;
@@ -447,6 +558,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               }
             }
           }
+        };
+        const bool storing = kTmaStore && t.pass == 1;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          if (t.n0 + c0 >= p.N) break;
+          process32(c0, std::integral_constant<int, 0>{});
+          if (storing && p.out_f32) stage_and_store(wout, t.n0 + c0, t);         // 32 fp32 columns = 128 bytes
+          if (t.n0 + c0 + 32 < p.N) {
+            process32(c0 + 32, std::integral_constant<int, 1>{});
+            if (storing && p.out_f32) stage_and_store(wout, t.n0 + c0 + 32, t);
+          }
+          if (storing && !p.out_f32) stage_and_store(wout, t.n0 + c0, t);        // 64 16-bit columns = 128 bytes
         }
         if (t.pass == 0 && t.n_idx == p.num_n_tiles - 1) {
           lse = run_max + __logf(run_sum);
@@ -458,6 +581,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
     }
+    if (kTmaStore && issuer) ptx::bulk_wait_group<0>();  // all output tiles have left shared memory and landed
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusGemmEpilogue);
   }
 
@@ -506,7 +630,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(T* __restrict__ D, const
 int g_force_bn = 0;  // 0 = heuristic; otherwise 64 / 128 / 256 (set through oasr_b200_set_tunable)
 
 template <typename T, int BN, int kStages, int kSched, int kEpi>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_t work_items, cudaStream_t s) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p, int64_t work_items,
+           cudaStream_t s) {
   using S = Smem<BN, kStages>;
   auto kern = gemm_tcgen05_kernel<T, BN, kStages, kSched, kEpi>;
   static bool attr_done = false;
@@ -518,15 +643,15 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int64_
   }
   int64_t grid = work_items < sm_count() ? work_items : sm_count();
   if (grid < 1) grid = 1;
-  kern<<<static_cast<unsigned>(grid), kThreads, S::kDynamic, s>>>(ta, tb, p);
+  kern<<<static_cast<unsigned>(grid), kThreads, S::kDynamic, s>>>(ta, tb, td, p);
   return check_launch("tcgen05 gemm launch");
 }
 
 // stage counts: as deep as fits beside the barriers in ~200 KB
 template <int BN> struct StagesFor;
-template <> struct StagesFor<64> { static constexpr int v = 8; };   // 24 KB / stage
-template <> struct StagesFor<128> { static constexpr int v = 6; };  // 32 KB / stage
-template <> struct StagesFor<256> { static constexpr int v = 4; };  // 48 KB / stage
+template <> struct StagesFor<64> { static constexpr int v = 7; };   // 24 KB / stage
+template <> struct StagesFor<128> { static constexpr int v = 5; };  // 32 KB / stage
+template <> struct StagesFor<256> { static constexpr int v = 4; };  // 48 KB / stage (+32 KB staging = 224 KB)
 
 int pick_bn(int64_t m_tiles_total, int64_t N) {
   if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) return g_force_bn;
@@ -581,15 +706,27 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
   p.num_m_tiles = static_cast<int>((pr.M + BM - 1) / BM);
   p.num_n_tiles = static_cast<int>((n_eff + bn - 1) / bn);
   p.num_k_blocks = static_cast<int>((pr.K + BK - 1) / BK);
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, td;
   if (int rc = make_maps<T>(pr, bn, dtype, &ta, &tb)) return rc;
+  if (uses_tma_store<kSched, kEpi>()) {
+    // output (N, M, batch): one 128-row x 128-byte box per store
+    const bool f32 = kEpi == kEpiLsm && p.out_f32;
+    const uint64_t es = f32 ? 4 : 2;
+    uint64_t ddims[3] = {(uint64_t)pr.N, (uint64_t)pr.M, (uint64_t)(kSched == kSchedDense ? pr.batch : 1)};
+    uint64_t dstr[3] = {0, (uint64_t)pr.N * es, (uint64_t)pr.N * es * (uint64_t)pr.M};
+    uint32_t dbox[3] = {f32 ? 32u : 64u, BM, 1};
+    if (int rc = make_tensor_map(&td, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : tma_dtype(dtype), 3, p.D, ddims, dstr, dbox))
+      return rc;
+  } else {
+    td = ta;
+  }
   int64_t work;
   if (kSched == kSchedSweep) work = p.num_m_tiles;
   else work = m_tiles_total * p.num_n_tiles;
   switch (bn) {
-    case 256: return launch<T, 256, StagesFor<256>::v, kSched, kEpi>(ta, tb, p, work, s);
-    case 128: return launch<T, 128, StagesFor<128>::v, kSched, kEpi>(ta, tb, p, work, s);
-    default: return launch<T, 64, StagesFor<64>::v, kSched, kEpi>(ta, tb, p, work, s);
+    case 256: return launch<T, 256, StagesFor<256>::v, kSched, kEpi>(ta, tb, td, p, work, s);
+    case 128: return launch<T, 128, StagesFor<128>::v, kSched, kEpi>(ta, tb, td, p, work, s);
+    default: return launch<T, 64, StagesFor<64>::v, kSched, kEpi>(ta, tb, td, p, work, s);
   }
 }
 
