@@ -121,12 +121,15 @@ def gemm_flops(name, args):
 
 
 def instrumented_step(run_step):
-    """One extra step with a CUDA-event pair around every C-ABI call, on the launching stream."""
+    """One extra step with CUDA-event pairs on the launching stream: around every step of the
+    native executor (its own event records) and around every other C-ABI call (Python hook)."""
     from oasr_b200 import _lib
 
     records, open_ev = [], {}
 
     def hook(name, phase, args):
+        if name in ("oasr_b200_conformer_encode_packed", "oasr_b200_profile_enable", "oasr_b200_profile_get"):
+            return
         if phase == "begin":
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
@@ -134,21 +137,26 @@ def instrumented_step(run_step):
         else:
             end = torch.cuda.Event(enable_timing=True)
             end.record()
-            records.append((name, open_ev.pop(name), end, gemm_flops(name, args)))
+            records.append((name.replace("oasr_b200_", ""), open_ev.pop(name), end, gemm_flops(name, args)))
 
     _lib.set_call_hook(hook)
     try:
-        run_step()
+        native = _lib.profile_steps(run_step)
         torch.cuda.synchronize()
     finally:
         _lib.set_call_hook(None)
     per = {}
-    for name, a, b, fl in records:
-        d = per.setdefault(name.replace("oasr_b200_", ""), {"launches": 0, "ms": 0.0, "flops": 0.0})
+
+    def add(label, ms, fl):
+        d = per.setdefault(label, {"launches": 0, "ms": 0.0, "flops": 0.0})
         d["launches"] += 1
-        d["ms"] += a.elapsed_time(b)
-        if fl:
-            d["flops"] += fl
+        d["ms"] += ms
+        d["flops"] += fl or 0.0
+
+    for name, a, b, fl in records:
+        add(name, a.elapsed_time(b), fl)
+    for label, ms, fl in native:
+        add(label, ms, fl)
     return per
 
 
@@ -301,19 +309,21 @@ def main():
         per = instrumented_step(device_step)
         peaks = measured_peaks()
         gemm = {"launches": 0, "ms": 0.0, "flops": 0.0}
-        for k in ("gemm", "gemm_glu"):
-            if k in per:
+        for k, v in per.items():
+            if k.startswith("gemm ") or k.startswith("gemm_glu"):   # every launch of gemm_tcgen05_kernel but the head
                 for f in gemm:
-                    gemm[f] += per[k][f]
+                    gemm[f] += v[f]
         step_total = total_ms / args.steps if dist is None else float(np.mean(step_ms))
         achieved = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
         roofline = {
-            "kernel": "gemm_tcgen05_kernel (oasr_b200_gemm / gemm_glu launches of one step)",
+            "kernel": "gemm_tcgen05_kernel (all gemm / gemm_glu launches of one step of the layer stack)",
             "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
             "frac": achieved / peaks["bf16_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
             "traffic": None, "launches": gemm["launches"], "share_of_step": gemm["ms"] / step_total if step_total else None,
         }
-        kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4)} for k, v in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}
+        kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
+                       **({"tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 1)} if v["flops"] and v["ms"] else {})}
+                   for k, v in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}
         cpu = None
         if not args.no_cpu_baseline:
             v, a, dt, thr = cpu_port_throughput(CPU_SAMPLE_UTTS)

@@ -373,6 +373,74 @@ OASR_API int oasr_b200_gather_rows(void* out, const void* in, const int64_t* ind
 OASR_API int oasr_b200_scatter_rows(void* out, const void* in, const int64_t* index, int64_t n_in,
                                     int64_t row_bytes, void* stream);
 
+/* ---- encoder layer stack (native executor) ------------------------------ */
+/* Device pointers to the prepared weights of one Conformer encoder layer
+ * (ConformerEncoderLayer, oasr/models/conformer/model.py:499-752).  16-bit
+ * tensors are in the model dtype, `float` ones are fp32.  Weight matrices are
+ * [out_features, in_features] row-major as in the reference's Linear. */
+typedef struct oasr_b200_conformer_layer {
+  const void *norm_ff_macaron_w, *norm_ff_macaron_b;
+  const void *ffm_w1, *ffm_b1, *ffm_w2, *ffm_b2;   /* feed_forward_macaron */
+  const void *norm_mha_w, *norm_mha_b;
+  const void *qkv4_w, *qkv4_b;   /* [Wq;Wq;Wk;Wv] (4d,d) and [bq+u;bq+v;bk;bv] */
+  const void *out_w, *out_b;     /* self_attn.linear_out */
+  const float *norm_conv_scale, *norm_conv_shift;  /* norm_conv as folded inference BatchNorm */
+  const void *pw1_w, *pw1_b;     /* pointwise_conv1 (2d,d) */
+  const void *dw_w, *dw_b;       /* depthwise_conv (K,d) */
+  const float *conv_bn_scale, *conv_bn_shift;      /* conv_module.norm_activation folded */
+  const float *glu_of_bias;      /* value of a zeroed row after pointwise_conv1 + GLU */
+  const void *pw2_w, *pw2_b;
+  const void *norm_ff_w, *norm_ff_b;
+  const void *ff_w1, *ff_b1, *ff_w2, *ff_b2;       /* feed_forward */
+  const void *norm_final_w, *norm_final_b;
+} oasr_b200_conformer_layer;
+
+typedef struct oasr_b200_conformer_model {
+  int32_t d_model, heads, ffn, kernel, num_layers, vocab_padded, embed_in, dtype;
+  double eps;
+  const oasr_b200_conformer_layer* layers;   /* HOST array of num_layers entries */
+  const void *embed_w, *embed_b;             /* embed Linear (d, embed_in) */
+  const void *embed_ln_w, *embed_ln_b;       /* nullable: embed LayerNorm with sqrt(d) folded in */
+  const void *pos_w_all;                     /* (num_layers*d, d): every layer's linear_pos */
+  const void *pe;                            /* (pe_rows, d) positional table */
+  int64_t pe_rows;
+  const void *after_norm_w, *after_norm_b;
+  const void *ctc_w, *ctc_b;                 /* (vocab_padded, 3d) split head weight, (vocab_padded) bias */
+} oasr_b200_conformer_model;
+
+/* Bytes of device scratch oasr_b200_conformer_encode_packed needs for `total`
+ * packed frames with segments of at most `max_seg` frames. */
+OASR_API int64_t oasr_b200_conformer_workspace_bytes(const oasr_b200_conformer_model* model,
+                                                     int64_t total, int64_t max_seg);
+/* The whole packed encoder + CTC head in one host call: embed Linear, the
+ * layer stack of ConformerEncoder.forward_packed (oasr/models/conformer/model.py:830-868,
+ * layer :709-752), after_norm and the fused CTC head (oasr/layers/ctc.py:48-51),
+ * as a fixed sequence of this library's kernels on `stream`.  rows is
+ * (total, embed_in): the gathered outputs of the subsampling convolutions.
+ * fill_frames (nullable, int32[num_segs]) selects the padded-batch semantics
+ * of the depthwise conv (see oasr_b200_depthwise_conv1d_packed).  log_probs
+ * (nullable) is fp32 (total, vocab_padded); argmax (nullable) int32[total].
+ * workspace must hold oasr_b200_conformer_workspace_bytes() bytes, 256-byte
+ * aligned.  Nothing is allocated and the host never waits for the device. */
+OASR_API int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model,
+                                               const void* rows, const int32_t* cu_seqlens,
+                                               const int32_t* fill_frames /*nullable*/,
+                                               int64_t num_segs, int64_t total, int64_t max_seg,
+                                               void* workspace, int64_t workspace_bytes,
+                                               float* log_probs /*nullable*/,
+                                               int32_t* argmax /*nullable*/, void* stream);
+
+/* Per-step timing of oasr_b200_conformer_encode_packed for benchmarks (no
+ * reference counterpart).  profile_enable(1) clears the records and makes the
+ * executor bracket every step with a CUDA-event pair on its stream;
+ * profile_enable(0) stops recording and clears.  profile_get waits for record
+ * `index` and returns its label (a static string), device milliseconds and
+ * algorithmic flops (0 for steps that are not GEMMs). */
+OASR_API int oasr_b200_profile_enable(int on);
+OASR_API int oasr_b200_profile_count(void);
+OASR_API int oasr_b200_profile_get(int index, const char** label /*host*/, double* ms /*host*/,
+                                   double* flops /*host*/);
+
 #ifdef __cplusplus
 }
 #endif

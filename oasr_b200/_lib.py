@@ -67,6 +67,34 @@ _SIGNATURES = {
     "oasr_b200_scatter_rows": [P, P, P, I, I, P],
 }
 
+
+
+class ConformerLayer(ctypes.Structure):
+    """struct oasr_b200_conformer_layer (include/oasr_b200.h)."""
+
+    _fields_ = [(n, c_void_p) for n in (
+        "norm_ff_macaron_w", "norm_ff_macaron_b", "ffm_w1", "ffm_b1", "ffm_w2", "ffm_b2", "norm_mha_w", "norm_mha_b",
+        "qkv4_w", "qkv4_b", "out_w", "out_b", "norm_conv_scale", "norm_conv_shift", "pw1_w", "pw1_b", "dw_w", "dw_b",
+        "conv_bn_scale", "conv_bn_shift", "glu_of_bias", "pw2_w", "pw2_b", "norm_ff_w", "norm_ff_b", "ff_w1", "ff_b1",
+        "ff_w2", "ff_b2", "norm_final_w", "norm_final_b")]
+
+
+class ConformerModel(ctypes.Structure):
+    """struct oasr_b200_conformer_model (include/oasr_b200.h)."""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "d_model", "heads", "ffn", "kernel", "num_layers", "vocab_padded", "embed_in", "dtype")] + [
+        ("eps", c_double), ("layers", POINTER(ConformerLayer)),
+        ("embed_w", c_void_p), ("embed_b", c_void_p), ("embed_ln_w", c_void_p), ("embed_ln_b", c_void_p),
+        ("pos_w_all", c_void_p), ("pe", c_void_p), ("pe_rows", c_int64),
+        ("after_norm_w", c_void_p), ("after_norm_b", c_void_p), ("ctc_w", c_void_p), ("ctc_b", c_void_p)]
+
+
+_SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, I, P, P, P]
+
+_SIGNATURES["oasr_b200_profile_enable"] = [c_int]
+_SIGNATURES["oasr_b200_profile_get"] = [c_int, POINTER(c_char_p), POINTER(c_double), POINTER(c_double)]
+
 _STRING_FUNCS = ("oasr_b200_version", "oasr_b200_last_error")
 
 
@@ -92,6 +120,10 @@ def load() -> ctypes.CDLL:
         fn.argtypes = []
     lib.oasr_b200_launch_count.restype = ctypes.c_ulonglong
     lib.oasr_b200_launch_count.argtypes = []
+    lib.oasr_b200_profile_count.restype = c_int
+    lib.oasr_b200_profile_count.argtypes = []
+    lib.oasr_b200_conformer_workspace_bytes.restype = c_int64
+    lib.oasr_b200_conformer_workspace_bytes.argtypes = [POINTER(ConformerModel), I, I]
     for name, argtypes in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -103,7 +135,7 @@ def load() -> ctypes.CDLL:
 
 
 def exported_names() -> list[str]:
-    return list(_STRING_FUNCS) + ["oasr_b200_launch_count"] + list(_SIGNATURES)
+    return list(_STRING_FUNCS) + ["oasr_b200_launch_count", "oasr_b200_conformer_workspace_bytes", "oasr_b200_profile_count"] + list(_SIGNATURES)
 
 
 def launch_count() -> int:
@@ -146,6 +178,23 @@ def call(name: str, *args) -> None:
         check(getattr(load(), name)(*args))
     finally:
         _call_hook(name, "end", args)
+
+
+def profile_steps(run) -> list:
+    """Run ``run()`` once with the native executor's per-step CUDA-event timing on; returns
+    ``[(label, ms, flops), ...]`` in launch order."""
+    lib = load()
+    call("oasr_b200_profile_enable", 1)
+    try:
+        run()
+        out = []
+        for i in range(lib.oasr_b200_profile_count()):
+            label, ms, fl = c_char_p(), c_double(), c_double()
+            call("oasr_b200_profile_get", i, ctypes.byref(label), ctypes.byref(ms), ctypes.byref(fl))
+            out.append((label.value.decode(), ms.value, fl.value))
+        return out
+    finally:
+        call("oasr_b200_profile_enable", 0)
 
 
 def version() -> str:

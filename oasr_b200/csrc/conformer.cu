@@ -1,0 +1,195 @@
+// Native executor of the packed Conformer encoder + CTC head: one host call
+// enqueues the whole fixed kernel sequence (13 launches per layer) on the
+// caller's stream.  Host code only; every step is one of this library's own
+// C-ABI kernels.  No allocation, no host synchronisation, launch order and
+// kernel choice are pure functions of the shapes.
+#include <cmath>
+#include <vector>
+
+#include "common.cuh"
+
+namespace ob {
+namespace {
+
+struct Workspace {
+  float* res;      // (M, d) fp32 residual stream
+  uint8_t* h;      // (M, d)   16-bit normalised activation
+  uint8_t* y;      // (M, d)   16-bit sub-layer output
+  uint8_t* a_ffn;  // (M, ffn)
+  uint8_t* qkv4;   // (M, 4d)
+  uint8_t* att;    // (M, d)
+  uint8_t* g;      // (M, d)
+  uint8_t* cv;     // (M, d)
+  uint8_t* h3;     // (M, 3d)  after_norm as [hi | hi | lo]
+  uint8_t* pos;    // (max_seg, L*d)
+  int64_t bytes;
+};
+
+int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
+
+// Optional per-step timing of the executor: a CUDA-event pair around every step, on the launching
+// stream.  Off by default; switched on for one call by a benchmark.
+struct ProfRecord {
+  const char* label;
+  double flops;
+  cudaEvent_t a, b;
+};
+bool g_prof_on = false;
+std::vector<ProfRecord> g_prof;
+
+void prof_clear() {
+  for (auto& r : g_prof) {
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  g_prof.clear();
+}
+
+Workspace carve(const oasr_b200_conformer_model& m, int64_t M, int64_t max_seg, uint8_t* base) {
+  Workspace w{};
+  const int64_t d = m.d_model;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    uint8_t* p = base ? base + off : nullptr;
+    off += align256(bytes);
+    return p;
+  };
+  w.res = reinterpret_cast<float*>(take(M * d * 4));
+  w.h = take(M * d * 2);
+  w.y = take(M * d * 2);
+  w.a_ffn = take(M * m.ffn * 2);
+  w.qkv4 = take(M * 4 * d * 2);
+  w.att = take(M * d * 2);
+  w.g = take(M * d * 2);
+  w.cv = take(M * d * 2);
+  w.h3 = take(M * 3 * d * 2);
+  w.pos = take(max_seg * m.num_layers * d * 2);
+  w.bytes = off;
+  return w;
+}
+
+}  // namespace
+}  // namespace ob
+
+extern "C" {
+
+int64_t oasr_b200_conformer_workspace_bytes(const oasr_b200_conformer_model* model, int64_t total, int64_t max_seg) {
+  if (!model || total < 0 || max_seg < 0) return -1;
+  return ob::carve(*model, total, max_seg, nullptr).bytes;
+}
+
+#define OB_STEP(label, flops, call)                                        \
+  do {                                                                     \
+    ob::ProfRecord pr_{label, static_cast<double>(flops), nullptr, nullptr}; \
+    if (ob::g_prof_on) {                                                   \
+      cudaEventCreate(&pr_.a);                                             \
+      cudaEventCreate(&pr_.b);                                             \
+      cudaEventRecord(pr_.a, static_cast<cudaStream_t>(stream));           \
+    }                                                                      \
+    int rc_ = (call);                                                      \
+    if (ob::g_prof_on) {                                                   \
+      cudaEventRecord(pr_.b, static_cast<cudaStream_t>(stream));           \
+      ob::g_prof.push_back(pr_);                                           \
+    }                                                                      \
+    if (rc_ != OASR_OK) return rc_;                                        \
+  } while (0)
+
+int oasr_b200_profile_enable(int on) {
+  ob::prof_clear();
+  ob::g_prof_on = on != 0;
+  return OASR_OK;
+}
+
+int oasr_b200_profile_count(void) { return static_cast<int>(ob::g_prof.size()); }
+
+int oasr_b200_profile_get(int index, const char** label, double* ms, double* flops) {
+  if (index < 0 || index >= static_cast<int>(ob::g_prof.size()))
+    return ob::set_error(OASR_ERR_INVALID, "profile_get: index %d out of range", index);
+  const ob::ProfRecord& r = ob::g_prof[index];
+  cudaError_t e = cudaEventSynchronize(r.b);
+  float t = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.a, r.b);
+  if (e != cudaSuccess) return ob::set_error(OASR_ERR_CUDA, "profile_get: %s", cudaGetErrorString(e));
+  if (label) *label = r.label;
+  if (ms) *ms = t;
+  if (flops) *flops = r.flops;
+  return OASR_OK;
+}
+
+int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, const void* rows,
+                                      const int32_t* cu_seqlens, const int32_t* fill_frames, int64_t num_segs,
+                                      int64_t total, int64_t max_seg, void* workspace, int64_t workspace_bytes,
+                                      float* log_probs, int32_t* argmax, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(model && model->layers, OASR_ERR_INVALID, "conformer_encode_packed: null model");
+  const oasr_b200_conformer_model& m = *model;
+  OB_REQUIRE(m.num_layers > 0 && m.d_model > 0 && m.heads > 0 && m.d_model == m.heads * 64, OASR_ERR_UNSUPPORTED,
+             "conformer_encode_packed: needs head_dim 64 (d_model %d, heads %d)", m.d_model, m.heads);
+  OB_REQUIRE(num_segs >= 0 && total >= 0 && max_seg >= 0, OASR_ERR_INVALID, "conformer_encode_packed: bad shape");
+  if (total == 0 || num_segs == 0) return OASR_OK;
+  OB_REQUIRE(rows && cu_seqlens && workspace, OASR_ERR_INVALID, "conformer_encode_packed: null pointer argument");
+  OB_REQUIRE(is_aligned(workspace, 256), OASR_ERR_ALIGN, "conformer_encode_packed: workspace must be 256-byte aligned");
+  OB_REQUIRE(max_seg <= m.pe_rows, OASR_ERR_INVALID,
+             "conformer_encode_packed: segment of %lld frames exceeds the positional table (%lld rows)",
+             (long long)max_seg, (long long)m.pe_rows);
+  Workspace w = carve(m, total, max_seg, static_cast<uint8_t*>(workspace));
+  OB_REQUIRE(workspace_bytes >= w.bytes, OASR_ERR_INVALID, "conformer_encode_packed: workspace of %lld bytes, %lld needed",
+             (long long)workspace_bytes, (long long)w.bytes);
+  const int64_t M = total, d = m.d_model, L = m.num_layers;
+  const int dt = m.dtype;
+  const double scale = 1.0 / std::sqrt(64.0);
+  const oasr_b200_conformer_layer* ly = m.layers;
+
+  // embed Linear (+ LayerNorm with sqrt(d) folded) -> fp32 residual, and the first pre-norm
+  OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm(w.y, rows, m.embed_w, m.embed_b, M, d, m.embed_in, OASR_ACT_NONE, dt, stream));
+  if (m.embed_ln_w) {
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 2, m.embed_ln_w, m.embed_ln_b,
+                                   ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, M, d, 1e-5, 0, dt, stream));
+  } else {
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b,
+                                   nullptr, nullptr, M, d, m.eps, 0, dt, stream));
+  }
+  // linear_pos of every layer in one GEMM: (max_seg, d) x (L*d, d)^T
+  OB_STEP("gemm linear_pos", 2.0 * max_seg * L * d * d, oasr_b200_gemm(w.pos, m.pe, m.pos_w_all, nullptr, max_seg, L * d, d, OASR_ACT_NONE, dt, stream));
+
+  for (int64_t i = 0; i < L; ++i) {
+    const oasr_b200_conformer_layer& l = ly[i];
+    // macaron feed-forward
+    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
+    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
+                                   m.eps, 0, dt, stream));
+    // relative-position self-attention
+    OB_STEP("gemm qkv4", 2.0 * M * 4 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs, max_seg,
+                                         M, m.heads, scale, dt, stream));
+    OB_STEP("gemm attn_out", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.att, l.out_w, l.out_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
+                                   nullptr, M, d, m.eps, 0, dt, stream));
+    // convolution module
+    OB_STEP("gemm_glu pw1", 2.0 * M * 2 * d * d, oasr_b200_gemm_glu(w.g, w.h, l.pw1_w, l.pw1_b, M, d, d, dt, stream));
+    OB_STEP("depthwise_conv1d_packed", 0, oasr_b200_depthwise_conv1d_packed(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
+                                              fill_frames ? l.glu_of_bias : nullptr, fill_frames, cu_seqlens, num_segs,
+                                              max_seg, d, m.kernel, OASR_ACT_SWISH, dt, stream));
+    OB_STEP("gemm pw2", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.cv, l.pw2_w, l.pw2_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, M, d,
+                                   m.eps, 0, dt, stream));
+    // feed-forward, norm_final, then the next layer's first pre-norm (or after_norm, split for the head)
+    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ff_w1, l.ff_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
+    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ff_w2, l.ff_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    if (i + 1 < L) {
+      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b,
+                                     ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, M, d, m.eps, 0, dt, stream));
+    } else {
+      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h3, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b, m.after_norm_w,
+                                     m.after_norm_b, M, d, m.eps, 1, dt, stream));
+    }
+  }
+  if (log_probs) {
+    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * 3 * d, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
+                                       argmax, stream));
+  }
+  return OASR_OK;
+}
+
+}  // extern "C"

@@ -60,7 +60,7 @@ struct DwArgs {
   int add_input;
 };
 
-constexpr int kTile = 16;
+constexpr int kTile = 8;
 
 template <typename T, int K, bool kAffine, bool kAct>
 __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
@@ -92,9 +92,9 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
     f1 = a.right_fill[c + 1];
     fill_end = TL + a.fill_frames[b];
   }
-  const T* in = static_cast<const T*>(a.in) + in_row0 * C + c;
-  T* out = static_cast<T*>(a.out) + out_row0 * C + c;
-  const T* w = static_cast<const T*>(a.weight) + c;
+  const T* __restrict__ in = static_cast<const T*>(a.in) + in_row0 * C + c;
+  T* __restrict__ out = static_cast<T*>(a.out) + out_row0 * C + c;
+  const T* __restrict__ w = static_cast<const T*>(a.weight) + c;
 
   float w0[K], w1[K];
 #pragma unroll
@@ -117,11 +117,13 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
     sh1 = a.post_shift[c + 1];
   }
 
-  // window[k] holds input frame (t - pad_left + k) for the current output t.
-  float x0[K], x1[K];
+  // All kTile + K - 1 input frames of this thread's run are loaded up front (independent loads,
+  // full memory-level parallelism), then the outputs are computed from registers.
+  constexpr int kWin = kTile + K - 1;
+  float x0[kWin], x1[kWin];
   const int first = t0 - a.pad_left;
 #pragma unroll
-  for (int k = 0; k < K - 1; ++k) {
+  for (int k = 0; k < kWin; ++k) {
     const int ti = first + k;
     float2 v = make_float2(0.f, 0.f);
     if (ti >= 0 && ti < TL) v = Pair<T>::ld(in + static_cast<int64_t>(ti) * C);
@@ -133,17 +135,11 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
   for (int j = 0; j < kTile; ++j) {
     const int t = t0 + j;
     if (t < OL) {
-      const int ti = first + j + K - 1;
-      float2 v = make_float2(0.f, 0.f);
-      if (ti >= 0 && ti < TL) v = Pair<T>::ld(in + static_cast<int64_t>(ti) * C);
-      else if (ti >= TL && ti < fill_end) v = make_float2(f0, f1);
-      x0[K - 1] = v.x;
-      x1[K - 1] = v.y;
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
-        acc0 = fmaf(x0[k], w0[k], acc0);
-        acc1 = fmaf(x1[k], w1[k], acc1);
+        acc0 = fmaf(x0[j + k], w0[k], acc0);
+        acc1 = fmaf(x1[j + k], w1[k], acc1);
       }
       acc0 += b0;
       acc1 += b1;
@@ -156,13 +152,136 @@ __global__ void __launch_bounds__(128) dwconv_window_kernel(DwArgs a) {
         acc1 = apply_act_rt(acc1, a.act);
       }
       Pair<T>::st(out + static_cast<int64_t>(t) * C, acc0, acc1);
-#pragma unroll
-      for (int k = 0; k < K - 1; ++k) {
-        x0[k] = x0[k + 1];
-        x1[k] = x1[k + 1];
-      }
     }
   }
+}
+
+// Shared-memory tiled form (the fast path when channels*sizeof(T) is a multiple of 16): a block
+// of 256 threads stages kTT + K - 1 input frames x up to 512 channels with 16-byte coalesced
+// loads (all independent: the whole tile is in flight at once), then every thread slides a
+// K-frame register window down its channel pair and writes kTT outputs.
+constexpr int kTT = 32;
+constexpr int kCB = 512;  // channels per block
+
+template <typename T, int K, bool kAffine, bool kAct>
+__global__ void __launch_bounds__(256) dwconv_tile_kernel(DwArgs a) {
+  extern __shared__ __align__(16) uint8_t dw_smem[];
+  T* tile = reinterpret_cast<T*>(dw_smem);
+  const int C = a.channels;
+  const int cb0 = blockIdx.y * kCB;
+  const int cw = min(kCB, C - cb0);          // channels of this block (multiple of 16 bytes / sizeof(T))
+  const int64_t b = blockIdx.z;
+  int64_t in_row0, out_row0;
+  int TL, OL;
+  if (a.cu_seqlens) {
+    const int s0 = a.cu_seqlens[b], s1 = a.cu_seqlens[b + 1];
+    TL = s1 - s0; OL = TL; in_row0 = s0; out_row0 = s0;
+  } else {
+    TL = a.seq_len; OL = a.out_len; in_row0 = b * a.seq_len; out_row0 = b * a.out_len;
+  }
+  const int t0 = blockIdx.x * kTT;
+  if (t0 >= OL) return;
+  int fill_end = TL;
+  if (a.right_fill) fill_end = TL + a.fill_frames[b];
+  constexpr int kRows = kTT + K - 1;
+  constexpr int kPer16 = 16 / sizeof(T);
+  const int chunks_per_row = cw / kPer16;
+  const int first = t0 - a.pad_left;
+  const T* __restrict__ in = static_cast<const T*>(a.in) + in_row0 * C + cb0;
+  // ---- stage the input tile ----
+  for (int i = threadIdx.x; i < kRows * chunks_per_row; i += blockDim.x) {
+    const int r = i / chunks_per_row, ch = i - r * chunks_per_row;
+    const int ti = first + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (ti >= 0 && ti < TL) {
+      v = __ldg(reinterpret_cast<const uint4*>(in + static_cast<int64_t>(ti) * C) + ch);
+    } else if (ti >= TL && ti < fill_end) {
+      Pack<T> pk;
+#pragma unroll
+      for (int q = 0; q < kPer16; ++q) pk.v[q] = Elem<T>::from_f(a.right_fill[cb0 + ch * kPer16 + q]);
+      v = *reinterpret_cast<uint4*>(&pk);
+    }
+    *reinterpret_cast<uint4*>(tile + r * cw + ch * kPer16) = v;
+  }
+  // ---- per-thread constants (overlaps with the tile loads) ----
+  const int c = threadIdx.x * 2;
+  const bool active = c < cw;
+  float w0[K], w1[K], b0 = 0.f, b1 = 0.f, sc0 = 1.f, sc1 = 1.f, sh0 = 0.f, sh1 = 0.f;
+  if (active) {
+    const T* __restrict__ w = static_cast<const T*>(a.weight) + cb0 + c;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float2 ww = Pair<T>::ld(w + static_cast<int64_t>(k) * C);
+      w0[k] = ww.x; w1[k] = ww.y;
+    }
+    if (a.bias) {
+      const float2 bb = Pair<T>::ld(static_cast<const T*>(a.bias) + cb0 + c);
+      b0 = bb.x; b1 = bb.y;
+    }
+    if constexpr (kAffine) {
+      sc0 = a.post_scale[cb0 + c]; sc1 = a.post_scale[cb0 + c + 1];
+      sh0 = a.post_shift[cb0 + c]; sh1 = a.post_shift[cb0 + c + 1];
+    }
+  }
+  __syncthreads();
+  if (!active) return;
+  T* __restrict__ out = static_cast<T*>(a.out) + out_row0 * C + cb0 + c;
+  float x0[K], x1[K];
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) {
+    const float2 v = Pair<T>::ld(tile + k * cw + c);
+    x0[k] = v.x; x1[k] = v.y;
+  }
+#pragma unroll
+  for (int j = 0; j < kTT; ++j) {
+    const int t = t0 + j;
+    if (t < OL) {
+      const float2 v = Pair<T>::ld(tile + (j + K - 1) * cw + c);
+      x0[K - 1] = v.x; x1[K - 1] = v.y;
+      float acc0 = b0, acc1 = b1;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        acc0 = fmaf(x0[k], w0[k], acc0);
+        acc1 = fmaf(x1[k], w1[k], acc1);
+      }
+      if constexpr (kAffine) {
+        acc0 = fmaf(acc0, sc0, sh0);
+        acc1 = fmaf(acc1, sc1, sh1);
+      }
+      if constexpr (kAct) {
+        acc0 = apply_act_rt(acc0, a.act);
+        acc1 = apply_act_rt(acc1, a.act);
+      }
+      Pair<T>::st(out + static_cast<int64_t>(t) * C, acc0, acc1);
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k) { x0[k] = x0[k + 1]; x1[k] = x1[k + 1]; }
+    }
+  }
+}
+
+template <typename T, int K>
+int launch_tile(const DwArgs& a, int max_out_len, cudaStream_t s) {
+  const int cw = a.channels < kCB ? a.channels : kCB;
+  const size_t smem = static_cast<size_t>(kTT + K - 1) * cw * sizeof(T);
+  dim3 block(256);
+  dim3 grid((max_out_len + kTT - 1) / kTT, (a.channels + kCB - 1) / kCB, static_cast<unsigned>(a.batch));
+  const bool affine = a.post_scale != nullptr;
+  const bool act = a.act != OASR_ACT_NONE;
+#define OB_DW_TILE(AFF, ACT)                                                                         \
+  do {                                                                                               \
+    auto kern = dwconv_tile_kernel<T, K, AFF, ACT>;                                                  \
+    if (smem > 48 * 1024) {                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return set_error(OASR_ERR_CUDA, "depthwise_conv1d: %s", cudaGetErrorString(e)); \
+    }                                                                                                \
+    kern<<<grid, block, smem, s>>>(a);                                                               \
+  } while (0)
+  if (affine && act) OB_DW_TILE(true, true);
+  else if (affine) OB_DW_TILE(true, false);
+  else if (act) OB_DW_TILE(false, true);
+  else OB_DW_TILE(false, false);
+#undef OB_DW_TILE
+  return check_launch("depthwise_conv1d (tiled) kernel launch");
 }
 
 // Any kernel size / channel count, optional mask and add_input
@@ -222,6 +341,21 @@ int launch_dw(const DwArgs& a, int max_out_len, cudaStream_t s) {
                     is_aligned(a.out, 2 * sizeof(T)) && is_aligned(a.weight, 2 * sizeof(T)) &&
                     (!a.bias || is_aligned(a.bias, 2 * sizeof(T))) && a.batch <= 65535 &&
                     (max_out_len + kTile - 1) / kTile <= 65535;
+  const bool tiled = fast && (a.channels * sizeof(T)) % 16 == 0 && (a.channels % kCB == 0 || a.channels < kCB) &&
+                     is_aligned(a.in, 16) && (max_out_len + kTT - 1) / kTT <= 65535 &&
+                     (a.channels + kCB - 1) / kCB <= 65535;
+  if (tiled) {
+    switch (a.kernel_size) {
+      case 3: return launch_tile<T, 3>(a, max_out_len, s);
+      case 5: return launch_tile<T, 5>(a, max_out_len, s);
+      case 7: return launch_tile<T, 7>(a, max_out_len, s);
+      case 9: return launch_tile<T, 9>(a, max_out_len, s);
+      case 11: return launch_tile<T, 11>(a, max_out_len, s);
+      case 15: return launch_tile<T, 15>(a, max_out_len, s);
+      case 31: return launch_tile<T, 31>(a, max_out_len, s);
+      default: break;
+    }
+  }
   if (fast) {
     switch (a.kernel_size) {
       case 3: return launch_window<T, 3>(a, max_out_len, s);

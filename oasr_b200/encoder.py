@@ -178,6 +178,7 @@ class ConformerCTC:
         self.ctc_w = w(torch.cat([cw_hi, cw - cw_hi, cw_hi], dim=1))
         self.ctc_b = w(P["ctc.ctc_lo.bias"])
         self.pe = w(self._positional_table(5000, d))
+        self._build_native_model()
 
     @staticmethod
     def _fold_bn(P, prefix, f):
@@ -196,75 +197,81 @@ class ConformerCTC:
         return pe
 
     # ------------------------------------------------------------------ front end
-    def _subsample(self, feats: torch.Tensor) -> torch.Tensor:
+    def _subsample(self, feats: torch.Tensor, t1_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Conv2dSubsampling4 convolutions (model.py:433-449): (B,T,F) -> (B, T', F'*d) rows in
         NHWC-natural (f, c) order.  The first conv (one input channel) is an own fp32-in kernel;
         the second still runs through torch/cuDNN in the 16-bit dtype on the NHWC tensor."""
-        x = fused.subsample_conv1(feats.float(), self.conv1_w, self.conv1_b, self.dtype)   # (B,T1,F1,C) NHWC
+        # frames of the first conv that only padding would consume are skipped (left uninitialised:
+        # they feed only output frames that are never gathered)
+        x = fused.subsample_conv1(feats.float(), self.conv1_w, self.conv1_b, self.dtype, t1_limit=t1_limit)  # NHWC
         x = x.permute(0, 3, 1, 2)                       # logical NCHW, channels_last in memory
         x = F.relu(F.conv2d(x, self.conv2_w, self.conv2_b, stride=2))
         B, C, T2, F2 = x.shape
         return x.permute(0, 2, 3, 1).reshape(B, T2, F2 * C)  # a view when x is channels_last
 
     # ------------------------------------------------------------------ layer stack
-    def _encode_packed(self, rows: torch.Tensor, pk: PackedBatch, padded_semantics: bool) -> torch.Tensor:
-        """rows: (total, F'*d) gathered embed-conv outputs.  Returns after_norm(hidden) as
-        (total, 3*d) 16-bit rows [hi | hi | lo]."""
-        cfg, dt = self.cfg, self.dtype
-        d, M = cfg.d_model, pk.total
-        dev = rows.device
-        scale = 1.0 / math.sqrt(cfg.head_dim)
-        res = torch.empty(M, d, device=dev, dtype=torch.float32)
-        h = torch.empty(M, d, device=dev, dtype=dt)
-        y = torch.empty(M, d, device=dev, dtype=dt)
-        a_ffn = torch.empty(M, cfg.ffn, device=dev, dtype=dt)
-        qkv4 = torch.empty(M, 4 * d, device=dev, dtype=dt)
-        att = torch.empty(M, d, device=dev, dtype=dt)
-        g = torch.empty(M, d, device=dev, dtype=dt)
-        cv = torch.empty(M, d, device=dev, dtype=dt)
+    def _build_native_model(self) -> None:
+        """Fill the C structs of the native executor with the prepared device pointers."""
+        import ctypes
 
-        # embed Linear (+LayerNorm, x sqrt(d) folded) -> fp32 residual, and the first pre-norm
-        OF.gemm(rows, self.embed_w, self.embed_b, out=y)
-        first = self.layers[0]["norm_ff_macaron"]
-        if cfg.embed_layer_norm:
-            fused.add_norm_f32(h, res, None, y, 1.0, fused.ADD_NORM_LN_LN, self.embed_ln_w, self.embed_ln_b, *first,
-                               eps=1e-5)
-        else:
-            fused.add_norm_f32(h, res, None, y, 1.0, fused.ADD_NORM_LN, *first, eps=cfg.eps)
-        # linear_pos of every layer in one GEMM: (Tm, d) x (L*d, d)^T
-        pos_all = OF.gemm(self.pe[:pk.max_seg], self.pos_w_all)
+        from . import _lib
+        from .functional import _DTYPE_ID
 
+        def ptr(t):
+            return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+        L = len(self.layers)
+        arr = (_lib.ConformerLayer * L)()
         for i, lw in enumerate(self.layers):
-            # macaron FFN (model.py:709-721)
-            OF.gemm_activation(h, lw["ffm"][0], lw["ffm"][1], 2, out=a_ffn)
-            OF.gemm(a_ffn, lw["ffm"][2], lw["ffm"][3], out=y)
-            fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_mha"], eps=cfg.eps)
-            # relative-position self-attention (attention.py:323-386)
-            OF.gemm(h, lw["qkv4"][0], lw["qkv4"][1], out=qkv4)
-            fused.fmha_varlen_relpos(qkv4, pos_all[:, i * d:(i + 1) * d], pk.cu_seqlens, pk.max_seg, cfg.heads, scale,
-                                     out=att)
-            OF.gemm(att, lw["out"][0], lw["out"][1], out=y)
-            fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_AFFINE, *lw["norm_conv_affine"], eps=cfg.eps)
-            # convolution module (model.py:223-233)
-            OF.gemm_glu(h, lw["pw1"][0], lw["pw1"][1], out=g)
-            fused.depthwise_conv1d_packed(
-                g, lw["dw"][0], lw["dw"][1], pk.cu_seqlens, pk.max_seg, post_scale=lw["conv_bn"][0],
-                post_shift=lw["conv_bn"][1], right_fill=lw["glu_of_bias"] if padded_semantics else None,
-                fill_frames=pk.fill_frames if padded_semantics else None, activation=2, out=cv)
-            OF.gemm(cv, lw["pw2"][0], lw["pw2"][1], out=y)
-            fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_ff"], eps=cfg.eps)
-            # FFN, then norm_final and the next layer's first pre-norm (or after_norm) in one pass
-            OF.gemm_activation(h, lw["ff"][0], lw["ff"][1], 2, out=a_ffn)
-            OF.gemm(a_ffn, lw["ff"][2], lw["ff"][3], out=y)
-            if i + 1 < len(self.layers):
-                fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_final"],
-                                   *self.layers[i + 1]["norm_ff_macaron"], eps=cfg.eps)
-            else:  # after_norm, written as [hi | hi | lo] for the split-precision head
-                h3 = torch.empty(M, 3 * d, device=dev, dtype=dt)
-                fused.add_norm_f32(h3, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_final"], *self.after_norm,
-                                   eps=cfg.eps, split_out=True)
-                return h3
-        return h
+            c = arr[i]
+            c.norm_ff_macaron_w, c.norm_ff_macaron_b = map(ptr, lw["norm_ff_macaron"])
+            c.ffm_w1, c.ffm_b1, c.ffm_w2, c.ffm_b2 = map(ptr, lw["ffm"])
+            c.norm_mha_w, c.norm_mha_b = map(ptr, lw["norm_mha"])
+            c.qkv4_w, c.qkv4_b = map(ptr, lw["qkv4"])
+            c.out_w, c.out_b = map(ptr, lw["out"])
+            c.norm_conv_scale, c.norm_conv_shift = map(ptr, lw["norm_conv_affine"])
+            c.pw1_w, c.pw1_b = map(ptr, lw["pw1"])
+            c.dw_w, c.dw_b = map(ptr, lw["dw"])
+            c.conv_bn_scale, c.conv_bn_shift = map(ptr, lw["conv_bn"])
+            c.glu_of_bias = ptr(lw["glu_of_bias"])
+            c.pw2_w, c.pw2_b = map(ptr, lw["pw2"])
+            c.norm_ff_w, c.norm_ff_b = map(ptr, lw["norm_ff"])
+            c.ff_w1, c.ff_b1, c.ff_w2, c.ff_b2 = map(ptr, lw["ff"])
+            c.norm_final_w, c.norm_final_b = map(ptr, lw["norm_final"])
+        cfg = self.cfg
+        m = _lib.ConformerModel()
+        m.d_model, m.heads, m.ffn, m.kernel, m.num_layers = cfg.d_model, cfg.heads, cfg.ffn, cfg.kernel, L
+        m.vocab_padded, m.embed_in, m.dtype, m.eps = cfg.vocab_padded, self.embed_w.size(1), _DTYPE_ID[self.dtype], cfg.eps
+        m.layers = arr
+        m.embed_w, m.embed_b = ptr(self.embed_w), ptr(self.embed_b)
+        m.embed_ln_w, m.embed_ln_b = ptr(self.embed_ln_w), ptr(self.embed_ln_b)
+        m.pos_w_all, m.pe, m.pe_rows = ptr(self.pos_w_all), ptr(self.pe), self.pe.size(0)
+        m.after_norm_w, m.after_norm_b = map(ptr, self.after_norm)
+        m.ctc_w, m.ctc_b = ptr(self.ctc_w), ptr(self.ctc_b)
+        self._native_layers, self._native_model = arr, m   # keep both alive
+        self._workspace = None
+
+    def _encode_packed(self, rows: torch.Tensor, pk: PackedBatch, padded_semantics: bool):
+        """rows: (total, F'*d) gathered embed-conv outputs -> (log_probs (total, V) fp32, argmax (total,) int32).
+        One call into the native executor (oasr_b200_conformer_encode_packed)."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _p
+
+        lib = _lib.load()
+        need = lib.oasr_b200_conformer_workspace_bytes(ctypes.byref(self._native_model), pk.total, pk.max_seg)
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=rows.device)
+        ws = self._workspace
+        off = (-ws.data_ptr()) % 256
+        log_probs = torch.empty(pk.total, self.cfg.vocab_padded, device=rows.device, dtype=torch.float32)
+        argmax = torch.empty(pk.total, device=rows.device, dtype=torch.int32)
+        _lib.call("oasr_b200_conformer_encode_packed", ctypes.byref(self._native_model), _p(rows), _p(pk.cu_seqlens),
+                  _p(pk.fill_frames) if padded_semantics else None, pk.num_segs, pk.total, pk.max_seg,
+                  ctypes.c_void_p(ws.data_ptr() + off), ws.numel() - off, _p(log_probs), _p(argmax),
+                  ctypes.c_void_p(torch.cuda.current_stream(rows.device).cuda_stream))
+        return log_probs, argmax
 
     # ------------------------------------------------------------------ entry points
     def _forward(self, features: torch.Tensor, lengths, padded_semantics: bool, padded_output: bool,
@@ -273,18 +280,19 @@ class ConformerCTC:
             raise RuntimeError("features must be a CUDA tensor (oasr_b200 has no CPU path)")
         lens_host = lengths.tolist() if isinstance(lengths, torch.Tensor) else [int(x) for x in lengths]
         out_lens = [max((n - 3) // 4, 0) for n in lens_host]
-        conv_rows = self._subsample(features)                                  # (B, Tp, F'*d)
-        B, Tp, W = conv_rows.shape
+        T = features.size(1)
+        Tp = (((T - 3) // 2 + 1) - 3) // 2 + 1
         pk = build_packed_batch(out_lens, Tp, self.cfg.kernel, features.device)
+        t1_limit = torch.tensor([2 * n + 1 for n in out_lens], dtype=torch.int32).to(features.device, non_blocking=True)
+        conv_rows = self._subsample(features, t1_limit)                        # (B, Tp, F'*d)
+        B, Tp, W = conv_rows.shape
         out_lengths = torch.tensor(out_lens, dtype=torch.int64, device=features.device)
         V = self.cfg.vocab_padded
         if pk.total == 0:
             lp = torch.zeros(B, Tp, V, device=features.device) if padded_output else torch.zeros(0, V, device=features.device)
             return (lp, out_lengths, None, pk) if return_argmax else (lp, out_lengths, pk)
         rows = gather_rows(conv_rows.reshape(B * Tp, W), pk.pack_src_idx)      # pack_hidden, before the embed Linear
-        hidden = self._encode_packed(rows, pk, padded_semantics)
-        res = OF.gemm_log_softmax(hidden, self.ctc_w, self.ctc_b, out_dtype=torch.float32, return_argmax=True)
-        log_probs, argmax = res
+        log_probs, argmax = self._encode_packed(rows, pk, padded_semantics)
         if padded_output:
             # padded rows carry hidden = 0 in the reference (packing.py:228-232): log_softmax(bias)
             pad_row = torch.log_softmax(self.ctc_b.float(), dim=-1)
