@@ -188,20 +188,35 @@ __global__ void __launch_bounds__(256) dwconv_tile_kernel(DwArgs a) {
   const int chunks_per_row = cw / kPer16;
   const int first = t0 - a.pad_left;
   const T* __restrict__ in = static_cast<const T*>(a.in) + in_row0 * C + cb0;
-  // ---- stage the input tile ----
-  for (int i = threadIdx.x; i < kRows * chunks_per_row; i += blockDim.x) {
-    const int r = i / chunks_per_row, ch = i - r * chunks_per_row;
-    const int ti = first + r;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (ti >= 0 && ti < TL) {
-      v = __ldg(reinterpret_cast<const uint4*>(in + static_cast<int64_t>(ti) * C) + ch);
-    } else if (ti >= TL && ti < fill_end) {
-      Pack<T> pk;
+  // ---- stage the input tile: four independent 16-byte loads in flight per thread ----
+  const int n_chunks = kRows * chunks_per_row;
+  for (int i0 = threadIdx.x; i0 < n_chunks; i0 += 4 * blockDim.x) {
+    uint4 v[4];
 #pragma unroll
-      for (int q = 0; q < kPer16; ++q) pk.v[q] = Elem<T>::from_f(a.right_fill[cb0 + ch * kPer16 + q]);
-      v = *reinterpret_cast<uint4*>(&pk);
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * blockDim.x;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (i < n_chunks) {
+        const int r = i / chunks_per_row, ch = i - r * chunks_per_row;
+        const int ti = first + r;
+        if (ti >= 0 && ti < TL) {
+          v[u] = __ldg(reinterpret_cast<const uint4*>(in + static_cast<int64_t>(ti) * C) + ch);
+        } else if (ti >= TL && ti < fill_end) {
+          Pack<T> pk;
+#pragma unroll
+          for (int q = 0; q < kPer16; ++q) pk.v[q] = Elem<T>::from_f(a.right_fill[cb0 + ch * kPer16 + q]);
+          v[u] = *reinterpret_cast<uint4*>(&pk);
+        }
+      }
     }
-    *reinterpret_cast<uint4*>(tile + r * cw + ch * kPer16) = v;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < n_chunks) {
+        const int r = i / chunks_per_row, ch = i - r * chunks_per_row;
+        *reinterpret_cast<uint4*>(tile + r * cw + ch * kPer16) = v[u];
+      }
+    }
   }
   // ---- per-thread constants (overlaps with the tile loads) ----
   const int c = threadIdx.x * 2;
@@ -249,8 +264,13 @@ __global__ void __launch_bounds__(256) dwconv_tile_kernel(DwArgs a) {
         acc1 = fmaf(acc1, sc1, sh1);
       }
       if constexpr (kAct) {
-        acc0 = apply_act_rt(acc0, a.act);
-        acc1 = apply_act_rt(acc1, a.act);
+        if constexpr (sizeof(T) == 2) {
+          acc0 = apply_act_fast(acc0, a.act);
+          acc1 = apply_act_fast(acc1, a.act);
+        } else {
+          acc0 = apply_act_rt(acc0, a.act);
+          acc1 = apply_act_rt(acc1, a.act);
+        }
       }
       Pair<T>::st(out + static_cast<int64_t>(t) * C, acc0, acc1);
 #pragma unroll

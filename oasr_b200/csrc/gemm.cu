@@ -339,7 +339,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             if (p.act != OASR_ACT_NONE) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = apply_act_rt(v[i], p.act);
+              for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) w[g * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
@@ -370,7 +370,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               }
               if (p.act != OASR_ACT_NONE) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = apply_act_rt(v[i], p.act);
+                for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
               }
               if (row_ok) {
                 uint4 o;
@@ -449,7 +449,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (int i = 0; i < 8; ++i) gt[i] += bb[i];
               }
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] *= sigmoid_f(gt[i]);
+              for (int i = 0; i < 8; ++i) v[i] *= sigmoid_fast(gt[i]);
 #pragma unroll
               for (int i = 0; i < 4; ++i) w[half * 16 + g * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
             }
@@ -486,7 +486,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (int i = 0; i < 8; ++i) gt[i] += bb[i];
               }
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] *= sigmoid_f(gt[i]);
+              for (int i = 0; i < 8; ++i) v[i] *= sigmoid_fast(gt[i]);
               if (row_ok) {
                 uint4 o;
                 o.x = pack2<T>(v[0], v[1]); o.y = pack2<T>(v[2], v[3]);
