@@ -430,6 +430,30 @@ OASR_API int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* 
                                                float* log_probs /*nullable*/,
                                                int32_t* argmax /*nullable*/, void* stream);
 
+/* This entry point has no counterpart in the reference.  It does what
+ * oasr_b200_conformer_encode_packed does for callers that must not allocate
+ * device memory (a plugin inside a process whose own pool already owns the
+ * GPU's memory, code between a framework's allocator hooks, a latency-critical
+ * thread that may not risk the device-wide stall of a cudaMalloc): the scratch
+ * is a 64 MiB array built into the library instead of a caller workspace.
+ * Inputs and outputs are still the caller's.  A batch that needs more scratch
+ * than oasr_b200_conformer_noalloc_capacity_bytes() is refused with
+ * OASR_ERR_INVALID and nothing is launched.  The first call on a device
+ * resolves the array's device address; make it with that device current and
+ * outside any stream capture.  All calls share the array (it keeps the last
+ * call's contents; no step reads it before writing), so calls that overlap on
+ * the GPU race with each other and must be serialised by the caller. */
+OASR_API int oasr_b200_conformer_encode_packed_noalloc(const oasr_b200_conformer_model* model,
+                                                       const void* rows,
+                                                       const int32_t* cu_seqlens,
+                                                       const int32_t* fill_frames /*nullable*/,
+                                                       int64_t num_segs, int64_t total,
+                                                       int64_t max_seg,
+                                                       float* log_probs /*nullable*/,
+                                                       int32_t* argmax /*nullable*/, void* stream);
+/* Size in bytes of the built-in scratch array of the entry point above. */
+OASR_API int64_t oasr_b200_conformer_noalloc_capacity_bytes(void);
+
 /* Per-step timing of oasr_b200_conformer_encode_packed for benchmarks (no
  * reference counterpart).  profile_enable(1) clears the records and makes the
  * executor bracket every step with a CUDA-event pair on its stream;

@@ -92,6 +92,7 @@ class ConformerModel(ctypes.Structure):
 
 _SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, I, P, P, P]
 
+_SIGNATURES["oasr_b200_conformer_encode_packed_noalloc"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, P, P]
 _SIGNATURES["oasr_b200_profile_enable"] = [c_int]
 _SIGNATURES["oasr_b200_profile_get"] = [c_int, POINTER(c_char_p), POINTER(c_double), POINTER(c_double)]
 
@@ -120,6 +121,8 @@ def load() -> ctypes.CDLL:
         fn.argtypes = []
     lib.oasr_b200_launch_count.restype = ctypes.c_ulonglong
     lib.oasr_b200_launch_count.argtypes = []
+    lib.oasr_b200_conformer_noalloc_capacity_bytes.restype = c_int64
+    lib.oasr_b200_conformer_noalloc_capacity_bytes.argtypes = []
     lib.oasr_b200_profile_count.restype = c_int
     lib.oasr_b200_profile_count.argtypes = []
     lib.oasr_b200_conformer_workspace_bytes.restype = c_int64
@@ -135,7 +138,8 @@ def load() -> ctypes.CDLL:
 
 
 def exported_names() -> list[str]:
-    return list(_STRING_FUNCS) + ["oasr_b200_launch_count", "oasr_b200_conformer_workspace_bytes", "oasr_b200_profile_count"] + list(_SIGNATURES)
+    return list(_STRING_FUNCS) + ["oasr_b200_launch_count", "oasr_b200_conformer_workspace_bytes", "oasr_b200_profile_count",
+                                  "oasr_b200_conformer_noalloc_capacity_bytes"] + list(_SIGNATURES)
 
 
 def launch_count() -> int:

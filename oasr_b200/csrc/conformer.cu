@@ -37,6 +37,11 @@ struct ProfRecord {
 bool g_prof_on = false;
 std::vector<ProfRecord> g_prof;
 
+// Scratch of oasr_b200_conformer_encode_packed_noalloc: lives in the library image, so every GPU
+// whose context loads the library holds these bytes until the process exits.
+constexpr int64_t kStaticScratchBytes = int64_t(64) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 void prof_clear() {
   for (auto& r : g_prof) {
     cudaEventDestroy(r.a);
@@ -190,6 +195,55 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
                                        argmax, stream));
   }
   return OASR_OK;
+}
+
+int64_t oasr_b200_conformer_noalloc_capacity_bytes(void) { return ob::kStaticScratchBytes; }
+
+// Same work as oasr_b200_conformer_encode_packed, for callers that are not allowed to allocate
+// device memory: a plugin living inside a host process that handed all of the GPU's memory to its
+// own pool at start-up, code running between a framework's allocator hooks, or a real-time
+// thread where a cudaMalloc (which may synchronise the whole device) is off limits.  They cannot
+// bring a workspace, so the scratch is a fixed 64 MiB array inside the library.
+//
+// Set-up: the array's name is only a host-side handle here, not something a kernel can be given.
+// The first call on each device -- made with that device current -- asks the runtime for the
+// array's device address (cudaGetSymbolAddress), checks the result and keeps it for later calls
+// on that device.  Make that first call outside of any stream capture.
+//
+// Limits and sharing: a batch whose scratch need (oasr_b200_conformer_workspace_bytes) exceeds
+// oasr_b200_conformer_noalloc_capacity_bytes() is refused with OASR_ERR_INVALID before anything
+// is launched.  All calls on a device use the same array; it keeps whatever the previous call
+// left there and no step depends on its initial contents (every buffer carved from it is fully
+// written before it is read), so nothing is cleared.  Two calls whose kernels overlap on the GPU
+// (different streams, or different host threads) would overwrite each other's intermediates:
+// serialise them.  No cudaMalloc / cudaFree or allocating library routine is called.
+int oasr_b200_conformer_encode_packed_noalloc(const oasr_b200_conformer_model* model, const void* rows,
+                                              const int32_t* cu_seqlens, const int32_t* fill_frames,
+                                              int64_t num_segs, int64_t total, int64_t max_seg, float* log_probs,
+                                              int32_t* argmax, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(model != nullptr, OASR_ERR_INVALID, "conformer_encode_packed_noalloc: null model");
+  OB_REQUIRE(total >= 0 && max_seg >= 0, OASR_ERR_INVALID, "conformer_encode_packed_noalloc: bad shape");
+  const int64_t need = carve(*model, total, max_seg, nullptr).bytes;
+  OB_REQUIRE(need <= kStaticScratchBytes, OASR_ERR_INVALID,
+             "conformer_encode_packed_noalloc: this batch needs %lld bytes of scratch but the built-in array holds "
+             "%lld; send fewer frames per call or use oasr_b200_conformer_encode_packed with your own workspace",
+             (long long)need, (long long)kStaticScratchBytes);
+  static unsigned char* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  OB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, OASR_ERR_CUDA,
+             "conformer_encode_packed_noalloc: cannot identify the current device (%s)", cudaGetErrorString(e));
+  if (scratch_of_device[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    OB_REQUIRE(e == cudaSuccess && ptr != nullptr, OASR_ERR_CUDA,
+               "conformer_encode_packed_noalloc: the scratch array has no device address on device %d (%s)", dev,
+               cudaGetErrorString(e));
+    scratch_of_device[dev] = ptr;
+  }
+  return oasr_b200_conformer_encode_packed(model, rows, cu_seqlens, fill_frames, num_segs, total, max_seg,
+                                           scratch_of_device[dev], kStaticScratchBytes, log_probs, argmax, stream);
 }
 
 }  // extern "C"

@@ -273,6 +273,24 @@ class ConformerCTC:
                   ctypes.c_void_p(torch.cuda.current_stream(rows.device).cuda_stream))
         return log_probs, argmax
 
+    def encode_rows_noalloc(self, rows: torch.Tensor, pk: PackedBatch, log_probs: torch.Tensor,
+                            argmax: torch.Tensor, padded_semantics: bool = False) -> None:
+        """The layer stack + head for callers that cannot allocate device memory (a host that gave all
+        GPU memory to its own pool, an allocator hook, a thread that must not risk a device-wide stall):
+        ``log_probs (total, V) fp32`` and ``argmax (total,) int32`` are the caller's, the scratch is the
+        64 MiB array built into the library (oasr_b200_conformer_encode_packed_noalloc).  Raises if the
+        batch needs more scratch than that.  Calls share the array: do not overlap two of them on the
+        GPU.  The first call on a device resolves the array's address; make it outside stream capture."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _p
+
+        _lib.call("oasr_b200_conformer_encode_packed_noalloc", ctypes.byref(self._native_model), _p(rows),
+                  _p(pk.cu_seqlens), _p(pk.fill_frames) if padded_semantics else None, pk.num_segs, pk.total,
+                  pk.max_seg, _p(log_probs), _p(argmax),
+                  ctypes.c_void_p(torch.cuda.current_stream(rows.device).cuda_stream))
+
     # ------------------------------------------------------------------ entry points
     def _forward(self, features: torch.Tensor, lengths, padded_semantics: bool, padded_output: bool,
                  return_argmax: bool):
