@@ -53,10 +53,10 @@ def make_batch(rank: int, batch: int = 64):
     return feats, lengths
 
 
-def model_config():
+def model_config(layers: int = 12):
     from oasr_b200.encoder import ConformerConfig
 
-    return ConformerConfig(input_size=80, d_model=512, heads=8, ffn=2048, layers=12, kernel=15, vocab=5002)
+    return ConformerConfig(input_size=80, d_model=512, heads=8, ffn=2048, layers=layers, kernel=15, vocab=5002)
 
 
 def measured_peaks():
@@ -219,6 +219,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=64, help="utterances per step (64 = the headline workload)")
+    ap.add_argument("--layers", type=int, default=12, help="encoder layers (12 = the headline workload); "
+                    "smaller values with --batch give the reduced case used for ncu captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -242,9 +245,11 @@ def main():
     from oasr_b200.encoder import ConformerCTC
     from oasr_b200.weights import init_params
 
-    cfg = model_config()
+    cfg = model_config(args.layers)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16)
-    feats_host, lengths = make_batch(rank)
+    feats_host, lengths = make_batch(rank, args.batch)
+    workload = WORKLOAD if (args.batch, args.layers) == (64, 12) else \
+        f"REDUCED profiling case: conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002_b{args.batch}_len200-2000_packed"
     feats_host = feats_host.pin_memory()
     feats_dev = feats_host.cuda(non_blocking=True)
     audio_s = sum(lengths) * FRAME_S
@@ -333,7 +338,7 @@ def main():
             "metric": "audio_seconds_per_second", "value": audio_total / (total_ms * 1e-3), "unit": "audio-s/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": 64 * world, "parallelism": f"utterance-sharded x{world}, no collective",
+            "config": {"workload": workload, "global_batch": args.batch * world, "parallelism": f"utterance-sharded x{world}, no collective",
                        "l2": "256 MiB flush write between steps; per-step working set (weights 240 MB + activations) > 126 MB L2",
                        "audio_seconds_per_step": audio_total / args.steps},
             "e2e": {"value": audio_total / (e2e_ms * 1e-3), "unit": "audio-s/s",
