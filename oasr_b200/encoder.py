@@ -205,7 +205,8 @@ class ConformerCTC:
         # they feed only output frames that are never gathered)
         x = fused.subsample_conv1(feats.float(), self.conv1_w, self.conv1_b, self.dtype, t1_limit=t1_limit)  # NHWC
         x = x.permute(0, 3, 1, 2)                       # logical NCHW, channels_last in memory
-        x = F.relu(F.conv2d(x, self.conv2_w, self.conv2_b, stride=2))
+        # cuDNN's fused conv + bias + ReLU (one kernel instead of conv, bias add and clamp)
+        x = torch.cudnn_convolution_relu(x, self.conv2_w, self.conv2_b, (2, 2), (0, 0), (1, 1), 1)
         B, C, T2, F2 = x.shape
         return x.permute(0, 2, 3, 1).reshape(B, T2, F2 * C)  # a view when x is channels_last
 
