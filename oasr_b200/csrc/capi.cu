@@ -56,7 +56,7 @@ uint32_t* device_status_ptr() {
   return ptrs[dev];
 }
 
-namespace gemm { extern int g_force_bn; }
+namespace gemm { extern int g_force_bn; extern int g_use_pairs; }
 
 }  // namespace ob
 
@@ -67,6 +67,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
     if (value != 0 && value != 64 && value != 128 && value != 256)
       return ob::set_error(OASR_ERR_INVALID, "gemm_bn must be 0, 64, 128 or 256 (got %d)", value);
     ob::gemm::g_force_bn = value;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "gemm_pairs") == 0) {
+    ob::gemm::g_use_pairs = value != 0;
     return OASR_OK;
   }
   return ob::set_error(OASR_ERR_INVALID, "unknown tunable '%s'", name ? name : "(null)");

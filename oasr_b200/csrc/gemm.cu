@@ -1,7 +1,7 @@
 // GEMM family on the 5th-generation tensor cores:
 //   D[M,N] = epilogue(A[M,K] . B[N,K]^T + bias[N]),  A/B fp16 or bf16, fp32 accumulate.
 //
-// One persistent, warp-specialised kernel (192 threads, one CTA per SM):
+// One persistent, warp-specialised kernel (192 or 320 threads, one CTA per SM):
 //   warp 0   TMA producer: streams 128x64 A tiles and BNx64 B tiles (128-byte
 //            swizzle) into a kStages-deep shared-memory ring, one mbarrier pair
 //            (full/empty) per stage;
@@ -9,9 +9,10 @@
 //            K=16) four times per stage into a TMEM accumulator and commits the
 //            stage back to the producer; owns the TMEM allocation (2 x BN
 //            columns, so the epilogue of tile i overlaps the main loop of i+1);
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = row, 32 columns per
-//            load), apply bias / activation / residual / GLU / log-softmax in
-//            fp32 and store with one rounding.
+//   warps 2-5 (and 6-9 for the store / GLU epilogues) epilogue: tcgen05.ld the
+//            accumulator (lane = row, 32 columns per load), apply bias /
+//            activation / residual / GLU / log-softmax in fp32, round once, stage
+//            128-byte row pieces in swizzled shared memory and TMA-store them.
 // Tensor-pipe bound; algorithmic flops 2*M*N*K.  No cluster launch and no TMA
 // multicast: every CTA loads its own operands.
 //
@@ -36,8 +37,7 @@ namespace gemm {
 constexpr int BM = 128;   // rows per tile (= UMMA M, = TMEM lanes)
 constexpr int BK = 64;    // K elements per stage (= 128 bytes = one swizzle row)
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 4;  // per group; store / GLU epilogues run two groups (8 warps)
 
 enum Epi { kEpiStore = 0, kEpiResid = 1, kEpiGlu = 2, kEpiLsm = 3 };
 enum Sched { kSchedDense = 0, kSchedGroup = 1, kSchedSweep = 2 };
@@ -67,13 +67,30 @@ struct Tile {
   int pass, n_idx;      // sweep scheduler only
 };
 
-template <int kSched, int BN>
+template <int kSched, int BN, int kCtas = 1>
 struct Scheduler {
   const Params& p;
+  uint32_t rank = 0;  // CTA rank inside a pair (kCtas == 2)
   __device__ explicit Scheduler(const Params& p_) : p(p_) {}
   // iter-th work item of this CTA; false when the CTA has no more work.
   __device__ bool get(int iter, Tile& t) const {
-    if constexpr (kSched == kSchedDense) {
+    if constexpr (kSched == kSchedDense && kCtas == 2) {
+      // a pair of CTAs owns a 256-row x BN tile: CTA `rank` holds rows [m*256 + rank*128, +128) of A and
+      // rows [n*BN + rank*BN/2, +BN/2) of B (GLU: rank 0 the value rows, rank 1 the gate rows)
+      const int64_t per_batch = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
+      const int64_t w = (blockIdx.x >> 1) + static_cast<int64_t>(iter) * (gridDim.x >> 1);
+      if (w >= per_batch * p.batch) return false;
+      const int b = static_cast<int>(w / per_batch);
+      const int r = static_cast<int>(w - b * per_batch);
+      const int m = r / p.num_n_tiles, n = r - m * p.num_n_tiles;
+      t.a_row = m * 2 * BM + static_cast<int>(rank) * BM; t.a_batch = b;
+      t.b_row = n * BN + static_cast<int>(rank) * (BN / 2); t.b_batch = b;
+      t.out_row = static_cast<int64_t>(b) * p.M + t.a_row;
+      t.row_end = static_cast<int64_t>(b) * p.M + p.M;
+      t.n0 = n * BN;
+      t.pass = 0; t.n_idx = n;
+      return true;
+    } else if constexpr (kSched == kSchedDense) {
       const int64_t per_batch = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
       const int64_t w = blockIdx.x + static_cast<int64_t>(iter) * gridDim.x;
       if (w >= per_batch * p.batch) return false;
@@ -125,10 +142,10 @@ struct Scheduler {
   }
 };
 
-template <int BN, int kStages>
+template <int BN, int kStages, int kCtas = 1>
 struct Smem {
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBBytes = (BN / kCtas) * BK * 2;  // a CTA of a pair holds half of the B tile
   static constexpr int kStageOut = kStages * (kABytes + kBBytes);  // 2 x 16 KB output staging (128 rows x 128 B)
   static constexpr int kOutBytes = BM * 128;
   static constexpr int kBarOffset = kStageOut + 2 * kOutBytes;
@@ -165,16 +182,30 @@ __device__ __forceinline__ void load_bias8(const T* p, float (&f)[8]) {
 // stores because a tile may end inside the tensor (at a group boundary).
 template <int kSched, int kEpi>
 constexpr bool uses_tma_store() { return kSched != kSchedGroup && kEpi != kEpiResid; }
+// Epilogue warp groups (4 warps = all 128 TMEM lanes each).  With a single warp per scheduler the
+// epilogue's load / convert / store chain is latency-bound and slower than the main loop of a
+// K = 512 tile; two groups take alternate 64-column chunks of the accumulator.
+template <int kSched, int kEpi>
+constexpr int epi_groups() { return (uses_tma_store<kSched, kEpi>() && (kEpi == kEpiStore || kEpi == kEpiGlu)) ? 2 : 1; }
+template <int kSched, int kEpi>
+constexpr int threads_for() { return 64 + 32 * kEpiWarps * epi_groups<kSched, kEpi>(); }
 
-template <typename T, int BN, int kStages, int kSched, int kEpi>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_d, const Params p) {
-  using S = Smem<BN, kStages>;
+// kCtas == 2: the kernel is launched in clusters of two CTAs that share one 256-row MMA
+// (tcgen05 cta_group::2).  Each CTA loads its own 128 A rows and its own half of the B tile (no
+// multicast), the leader CTA (rank 0) issues the MMAs for both, every CTA drains its own 128
+// accumulator rows.  Per flop this halves the B bytes a CTA pulls from L2, which is what limits the
+// single-CTA 128 x 256 tile.
+template <typename T, int BN, int kStages, int kSched, int kEpi, int kCtas>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                          const CUtensorMap& tmap_d, const Params& p) {
+  using S = Smem<BN, kStages, kCtas>;
   constexpr bool kTmaStore = uses_tma_store<kSched, kEpi>();
+  constexpr int kGroups = epi_groups<kSched, kEpi>();
   constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-  constexpr uint32_t kIdesc = ptx::umma_idesc_f16(kBf16, BM, BN);
+  constexpr uint32_t kIdesc = ptx::umma_idesc_f16(kBf16, BM * kCtas, BN);
+  static_assert(kCtas == 1 || (kSched == kSchedDense && kTmaStore), "CTA pairs: dense problems with TMA stores");
+  const uint32_t cta_rank = kCtas == 2 ? ptx::cluster_ctarank() : 0u;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -197,7 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&tfull_bar[i], 1);
-      ptx::mbar_init(&tempty_bar[i], kEpiWarps);
+      ptx::mbar_init(&tempty_bar[i], kEpiWarps * kGroups * kCtas);  // the leader waits for both CTAs' epilogues
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -207,15 +238,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (kTmaStore) ptx::prefetch_tensormap(&tmap_d);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (kCtas == 2) {
+      ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kCtas == 2) ptx::cluster_sync();  // the peer's barriers are initialised before anything targets them
+  else __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  Scheduler<kSched, BN> sched(p);
+  Scheduler<kSched, BN, kCtas> sched(p);
+  sched.rank = cta_rank;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -227,6 +265,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int iter = 0; ok && sched.get(iter, t); ++iter) {
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          if constexpr (kCtas == 2) {
+            // both CTAs' bytes are credited to the leader's barrier; only the leader arrives on it
+            const uint32_t lead_full = ptx::map_to_cta(&full_bar[stage], 0);
+            if (cta_rank == 0) ptx::mbar_expect_tx(&full_bar[stage], 2 * (S::kABytes + S::kBBytes));
+            ptx::tma_load_3d_pair(sA + stage * S::kABytes, &tmap_a, kb * BK, t.a_row, t.a_batch, lead_full);
+            int b_row = t.b_row;
+            if constexpr (kEpi == kEpiGlu) b_row = (cta_rank == 0 ? 0 : p.N) + t.n0 / 2;  // value | gate rows
+            ptx::tma_load_3d_pair(sB + stage * S::kBBytes, &tmap_b, kb * BK, b_row, t.b_batch, lead_full);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           ptx::mbar_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
           ptx::tma_load_3d(sA + stage * S::kABytes, &tmap_a, kb * BK, t.a_row, t.a_batch, &full_bar[stage]);
           if constexpr (kEpi == kEpiGlu) {
@@ -245,7 +294,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       Tile t;
@@ -265,12 +314,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = ptx::smem_desc_kmajor_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t bdesc = ptx::smem_desc_kmajor_sw128(b_addr + k * UMMA_K * 2);
-            ptx::umma_f16(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (kCtas == 2) ptx::umma_f16_pair(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            else ptx::umma_f16(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
-          ptx::umma_commit(&empty_bar[stage]);
+          if constexpr (kCtas == 2) ptx::umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
+          else ptx::umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) ptx::umma_commit(&tfull_bar[acc]);
+        if (ok) {
+          if constexpr (kCtas == 2) ptx::umma_commit_pair(&tfull_bar[acc], 3);
+          else ptx::umma_commit(&tfull_bar[acc]);
+        }
       }
       if (!ok && p.status) atomicOr(p.status, kStatusGemmMma);
     }
@@ -285,26 +339,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     float run_max = -INFINITY, run_sum = 0.f, lse = 0.f;
     int run_arg = 0;
     // TMA-store staging: `w` is this thread's 128 bytes of row (q*32+lane) for output columns
-    // starting at `col`; the 128 x 128 B tile goes out as one box at (col, row0, batch).
+    // starting at `col`; the 128 x 128 B tile goes out as one box at (col, row0, batch).  With two
+    // warp groups each group owns one staging buffer and one named barrier; a single group
+    // alternates between the two buffers.
+    const int grp = (warp - 2) >> 2;
     uint8_t* stage_out = smem + S::kStageOut;
-    int out_buf = 0;
-    const bool issuer = threadIdx.x == 64;
+    int out_buf = kGroups == 2 ? grp : 0;
+    const bool issuer = ((warp - 2) & 3) == 0 && lane == 0;
     const int tile_row = q * 32 + lane;
     auto stage_and_store = [&](const uint32_t (&w)[32], int col, const Tile& tt) {
-      if (issuer) ptx::bulk_wait_group_read<1>();  // the store that last used this buffer has read it
-      ptx::named_barrier_sync(1, kEpiWarps * 32);
+      if (issuer) {  // the store that last used this buffer has finished reading it
+        if constexpr (kGroups == 2) ptx::bulk_wait_group_read<0>();
+        else ptx::bulk_wait_group_read<1>();
+      }
+      ptx::named_barrier_sync(1 + grp, kEpiWarps * 32);
       uint8_t* row = stage_out + out_buf * S::kOutBytes + tile_row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         *reinterpret_cast<uint4*>(row + ((c ^ (tile_row & 7)) * 16)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
       }
       ptx::fence_proxy_async_smem();
-      ptx::named_barrier_sync(1, kEpiWarps * 32);
+      ptx::named_barrier_sync(1 + grp, kEpiWarps * 32);
       if (issuer) {
         ptx::tma_store_3d(&tmap_d, stage_out + out_buf * S::kOutBytes, col, tt.a_row, tt.a_batch);
         ptx::bulk_commit_group();
       }
-      out_buf ^= 1;
+      if constexpr (kGroups == 1) out_buf ^= 1;
+    };
+    // 32 accumulator columns -> 16 packed words of `w` (kHalf = which half), bias and activation in fp32
+    auto finish32 = [&](const uint32_t (&r)[32], uint32_t (&w)[32], auto half_c, int col0, const T* bias) {
+      constexpr int kHalf = decltype(half_c)::value;
+#pragma unroll
+      for (int g8 = 0; g8 < 4; ++g8) {
+        const int col = col0 + g8 * 8;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g8 * 8 + i]);
+        if (bias && col < p.N) {
+          float bb[8];
+          load_bias8(bias + col, bb);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += bb[i];
+        }
+        if (p.act == OASR_ACT_SWISH) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = swish_fast(v[i]);
+        } else if (p.act != OASR_ACT_NONE) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[kHalf * 16 + g8 * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
+      }
     };
     for (int iter = 0; ok && sched.get(iter, t); ++iter) {
       const int acc = iter & 1;
@@ -316,36 +402,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const uint32_t t_acc = tmem_base + lane_base + acc * BN;
 
       if constexpr (kEpi == kEpiStore && kTmaStore) {
+        // group `grp` takes the 64-column chunks grp, grp + kGroups, ...; the TMEM load of the next 32
+        // columns is always in flight while the current 32 are converted
         const T* bias = static_cast<const T*>(p.bias);
+        const int nchunks = (min(BN, p.N - t.n0) + 63) / 64;
+        uint32_t ra[32], rb[32], w[32];
+        int ci = grp;
+        if (ci < nchunks) ptx::tmem_ld_32x32(t_acc + ci * 64, ra);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64) {
-          if (t.n0 + c0 >= p.N) break;
-          uint32_t r[64];
-          ptx::tmem_ld_32x32(t_acc + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-          ptx::tmem_ld_32x32(t_acc + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        for (; ci < nchunks; ci += kGroups) {
+          const int c0 = ci * 64;
           ptx::tmem_ld_wait();
-          uint32_t w[32];
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const int col = t.n0 + c0 + g * 8;
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g * 8 + i]);
-            if (bias && col < p.N) {
-              float bb[8];
-              load_bias8(bias + col, bb);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += bb[i];
-            }
-            if (p.act != OASR_ACT_NONE) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) w[g * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
-          }
+          ptx::tmem_ld_32x32(t_acc + c0 + 32, rb);
+          finish32(ra, w, std::integral_constant<int, 0>{}, t.n0 + c0, bias);
+          ptx::tmem_ld_wait();
+          if (ci + kGroups < nchunks) ptx::tmem_ld_32x32(t_acc + (ci + kGroups) * 64, ra);
+          finish32(rb, w, std::integral_constant<int, 1>{}, t.n0 + c0 + 32, bias);
           stage_and_store(w, t.n0 + c0, t);
         }
+        ptx::tmem_ld_wait();
       } else if constexpr (kEpi == kEpiStore) {
         T* drow = static_cast<T*>(p.D) + row * p.N;
         const T* bias = static_cast<const T*>(p.bias);
@@ -424,7 +499,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int n0 = t.n0 / 2;
         const T* bias = static_cast<const T*>(p.bias);
 #pragma unroll 1
-        for (int c0 = 0; c0 < HN; c0 += 64) {
+        for (int c0 = grp * 64; c0 < HN; c0 += 64 * kGroups) {
           if (n0 + c0 >= p.N) break;
           uint32_t w[32];
 #pragma unroll
@@ -579,7 +654,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        if constexpr (kCtas == 2) ptx::mbar_arrive_cluster(ptx::map_to_cta(&tempty_bar[acc], 0));
+        else ptx::mbar_arrive(&tempty_bar[acc]);
+      }
     }
     if (kTmaStore && issuer) ptx::bulk_wait_group<0>();  // all output tiles have left shared memory and landed
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusGemmEpilogue);
@@ -592,10 +670,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (kCtas == 2) {
+    // neither CTA may leave (or release TMEM) while the leader's MMAs can still read the peer's shared
+    // memory or the peer can still arrive on the leader's barriers
+    ptx::tc_fence_before_sync();
+    ptx::cluster_sync();
+  }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (kCtas == 2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+template <typename T, int BN, int kStages, int kSched, int kEpi>
+__global__ void __launch_bounds__(threads_for<kSched, kEpi>(), 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+  gemm_body<T, BN, kStages, kSched, kEpi, 1>(tmap_a, tmap_b, tmap_d, p);
+}
+
+template <typename T, int kStages, int kEpi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_for<kSchedDense, kEpi>(), 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+  gemm_body<T, 256, kStages, kSchedDense, kEpi, 2>(tmap_a, tmap_b, tmap_d, p);
 }
 
 // ---------------------------------------------------------------------------
@@ -628,6 +727,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(T* __restrict__ D, const
 // Host side
 // ---------------------------------------------------------------------------
 int g_force_bn = 0;  // 0 = heuristic; otherwise 64 / 128 / 256 (set through oasr_b200_set_tunable)
+int g_use_pairs = 0; // 1 = large dense problems run on CTA pairs (cta_group::2); 0 (default) = single-CTA tiles.
+                     // Measured on B200 (M 17.5k, K 512..2048): pairs are 5-20 % slower than single-CTA tiles here.
 
 template <typename T, int BN, int kStages, int kSched, int kEpi>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p, int64_t work_items,
@@ -643,8 +744,29 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, 
   }
   int64_t grid = work_items < sm_count() ? work_items : sm_count();
   if (grid < 1) grid = 1;
-  kern<<<static_cast<unsigned>(grid), kThreads, S::kDynamic, s>>>(ta, tb, td, p);
+  kern<<<static_cast<unsigned>(grid), threads_for<kSched, kEpi>(), S::kDynamic, s>>>(ta, tb, td, p);
   return check_launch("tcgen05 gemm launch");
+}
+
+constexpr int kPairStages = 6;  // 32 KB per stage and CTA (+32 KB staging = 224 KB)
+
+template <typename T, int kEpi>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p,
+                int64_t work_items, cudaStream_t s) {
+  using S = Smem<256, kPairStages, 2>;
+  auto kern = gemm_tcgen05_pair_kernel<T, kPairStages, kEpi>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+    if (e != cudaSuccess) return set_error(OASR_ERR_CUDA, "gemm: cannot reserve %d bytes of shared memory: %s",
+                                           S::kDynamic, cudaGetErrorString(e));
+    attr_done = true;
+  }
+  int64_t clusters = sm_count() / 2;
+  if (work_items < clusters) clusters = work_items;
+  if (clusters < 1) clusters = 1;
+  kern<<<static_cast<unsigned>(2 * clusters), threads_for<kSchedDense, kEpi>(), S::kDynamic, s>>>(ta, tb, td, p);
+  return check_launch("tcgen05 pair gemm launch");
 }
 
 // stage counts: as deep as fits beside the barriers in ~200 KB
@@ -678,7 +800,7 @@ struct Problem {
 };
 
 template <typename T>
-int make_maps(const Problem& pr, int bn, int dtype, CUtensorMap* ta, CUtensorMap* tb) {
+int make_maps(const Problem& pr, int bn, int dtype, CUtensorMap* ta, CUtensorMap* tb, bool pair) {
   // A: (K, rows, batch); B: (K, rows, batch)
   const int64_t a_rows = pr.sched == kSchedGroup ? pr.M : pr.M;
   const int64_t a_batch = pr.sched == kSchedDense ? pr.batch : 1;
@@ -690,7 +812,7 @@ int make_maps(const Problem& pr, int bn, int dtype, CUtensorMap* ta, CUtensorMap
   if (int rc = make_tensor_map(ta, tma_dtype(dtype), 3, pr.A, adims, astr, abox)) return rc;
   uint64_t bdims[3] = {(uint64_t)pr.K, (uint64_t)b_rows, (uint64_t)b_batch};
   uint64_t bstr[3] = {0, (uint64_t)pr.K * 2, (uint64_t)pr.K * 2 * (uint64_t)b_rows};
-  uint32_t bbox[3] = {BK, (uint32_t)(pr.epi == kEpiGlu ? bn / 2 : bn), 1};
+  uint32_t bbox[3] = {BK, (uint32_t)((pr.epi == kEpiGlu || pair) ? bn / 2 : bn), 1};
   return make_tensor_map(tb, tma_dtype(dtype), 3, pr.B, bdims, bstr, bbox);
 }
 
@@ -703,11 +825,15 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
   const int64_t n_eff = kEpi == kEpiGlu ? 2 * pr.N : pr.N;  // accumulator columns
   int bn = kEpi == kEpiLsm ? (g_force_bn ? g_force_bn : 256) : pick_bn(m_tiles_total, n_eff);
   if (kEpi == kEpiGlu && bn < 128) bn = 128;  // half tiles of >= 64 columns
+  constexpr bool kPairCapable = kSched == kSchedDense && (kEpi == kEpiStore || kEpi == kEpiGlu);
+  const bool pair = kPairCapable && g_use_pairs && g_force_bn == 0 && pr.M >= 1024 && n_eff >= 256 && pr.K >= 128;
+  if (pair) bn = 256;
   p.num_m_tiles = static_cast<int>((pr.M + BM - 1) / BM);
+  if (pair) p.num_m_tiles = static_cast<int>((pr.M + 2 * BM - 1) / (2 * BM));
   p.num_n_tiles = static_cast<int>((n_eff + bn - 1) / bn);
   p.num_k_blocks = static_cast<int>((pr.K + BK - 1) / BK);
   CUtensorMap ta, tb, td;
-  if (int rc = make_maps<T>(pr, bn, dtype, &ta, &tb)) return rc;
+  if (int rc = make_maps<T>(pr, bn, dtype, &ta, &tb, pair)) return rc;
   if (uses_tma_store<kSched, kEpi>()) {
     // output (N, M, batch): one 128-row x 128-byte box per store
     const bool f32 = kEpi == kEpiLsm && p.out_f32;
@@ -723,6 +849,9 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
   int64_t work;
   if (kSched == kSchedSweep) work = p.num_m_tiles;
   else work = m_tiles_total * p.num_n_tiles;
+  if constexpr (kPairCapable) {
+    if (pair) return launch_pair<T, kEpi>(ta, tb, td, p, static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles * pr.batch, s);
+  }
   switch (bn) {
     case 256: return launch<T, 256, StagesFor<256>::v, kSched, kEpi>(ta, tb, td, p, work, s);
     case 128: return launch<T, 128, StagesFor<128>::v, kSched, kEpi>(ta, tb, td, p, work, s);

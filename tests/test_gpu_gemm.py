@@ -153,3 +153,30 @@ def test_gemm_log_softmax_padding_rows_are_inert():
     assert int(arg.max()) < raw
     want = O.gemm_log_softmax(A[:, :], B[:raw], C[:raw])
     torch.testing.assert_close(got[:, :raw].cpu(), want, rtol=1e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", HALF)
+@pytest.mark.parametrize("M,N,K", [(1024, 256, 128), (1300, 520, 264), (4096, 2048, 512), (2049, 512, 2048),
+                                   (17536, 512, 512)])
+def test_gemm_cta_pairs_match_single_cta_tiles(dtype, M, N, K):
+    """Large dense problems run on CTA pairs (cta_group::2); same products, same rounding as the
+    single-CTA kernel and the oracle."""
+    from oasr_b200 import tunables
+
+    A, B, C = _rand((M, K), dtype, 31), _rand((N, K), dtype, 32, K ** -0.5), _rand((N,), dtype, 33)
+    want = O.gemm(A, B, C, 2)
+    got_single = ob.gemm_activation(A.cuda(), B.cuda(), C.cuda(), 2)
+    tunables.set("gemm_pairs", 1)
+    try:
+        got_pair = ob.gemm_activation(A.cuda(), B.cuda(), C.cuda(), 2)
+        if N % 2 == 0:
+            Bg, Cg = _rand((2 * N, K), dtype, 34, K ** -0.5), _rand((2 * N,), dtype, 35)
+            _check(ob.gemm_glu(A.cuda(), Bg.cuda(), Cg.cuda()), O.gemm_glu(A, Bg, Cg), dtype)
+    finally:
+        tunables.set("gemm_pairs", 0)
+    _check(got_pair, want, dtype)
+    _check(got_single, want, dtype)
+    assert torch.equal(got_pair, got_single)   # fp32 accumulation order along K is the same
+    if N % 2 == 0:
+        Bg, Cg = _rand((2 * N, K), dtype, 34, K ** -0.5), _rand((2 * N,), dtype, 35)
+        _check(ob.gemm_glu(A.cuda(), Bg.cuda(), Cg.cuda()), O.gemm_glu(A, Bg, Cg), dtype)
