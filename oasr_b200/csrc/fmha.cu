@@ -352,29 +352,45 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
       if (!ptx::mbar_wait(&s_full[b], ph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t t_s = tmem_base + lane_base + kColS + b * BKV;
-      // ---- pass 1: scale, bias, mask (log2 domain), write back, row max ----
+      // ---- pass 1: row max.  Interior tiles without a bias need no mask and no write-back: the max of
+      // the raw scores is taken and the (positive) scale applied in pass 2.  Edge tiles and biased tiles
+      // get scale, bias and masks applied here (log2 domain) and written back to TMEM. ----
+      const bool plain_tile = !bias_row && !p.causal && key0 + BKV <= kv_len && key0 >= kv_start;
       float tile_max = kNegInf;
+      if (plain_tile) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(t_s + c0, v);
-        ptx::tmem_ld_wait();
+        for (int c0 = 0; c0 < BKV; c0 += 32) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(t_s + c0, v);
+          ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c0 + i;
-          float x = __uint_as_float(v[i]) * p.scale_log2;
-          if (bias_row && row_ok && key < kv_len) x = fmaf(Elem<T>::to_f(__ldg(bias_row + key)), 1.4426950408889634f, x);
-          const bool visible = key < kv_len && key >= kv_start && !(p.causal && key > row_in_seq);
-          x = visible ? x : kNegInf;
-          tile_max = fmaxf(tile_max, x);
-          v[i] = __float_as_uint(x);
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
         }
-        ptx::tmem_st_32x32(t_s + c0, v);
+        tile_max *= p.scale_log2;
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BKV; c0 += 32) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(t_s + c0, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c0 + i;
+            float x = __uint_as_float(v[i]) * p.scale_log2;
+            if (bias_row && row_ok && key < kv_len) x = fmaf(Elem<T>::to_f(__ldg(bias_row + key)), 1.4426950408889634f, x);
+            const bool visible = key < kv_len && key >= kv_start && !(p.causal && key > row_in_seq);
+            x = visible ? x : kNegInf;
+            tile_max = fmaxf(tile_max, x);
+            v[i] = __float_as_uint(x);
+          }
+          ptx::tmem_st_32x32(t_s + c0, v);
+        }
+        ptx::tmem_st_wait();
       }
-      ptx::tmem_st_wait();
       const float m_new = fmaxf(m_run, tile_max);
       const float m_use = (m_new == kNegInf) ? 0.f : m_new;  // empty-row clamp
       const float alpha = (m_run == kNegInf) ? 0.f : exp2f(m_run - m_use);
+      const float pscale = plain_tile ? p.scale_log2 : 1.f;   // pass 2 computes exp2(x * pscale - m_use)
       // ---- pass 2: exponentiate, sum, round, write P (K-major, 128-byte swizzle) ----
       // P[b] is free: this thread folded O of tile j-2 (po_done[b]) in the previous iteration.
       float row_sum = 0.f;
@@ -387,8 +403,8 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2f(__uint_as_float(v[i]) - m_use);
-          const float p1 = exp2f(__uint_as_float(v[i + 1]) - m_use);
+          const float p0 = exp2f(fmaf(__uint_as_float(v[i]), pscale, -m_use));
+          const float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), pscale, -m_use));
           row_sum += p0 + p1;
           packed[i / 2] = pack2<T>(p0, p1);
         }
