@@ -215,7 +215,7 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -264,13 +264,15 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)   # started early: nvidia-smi needs ~1 s before its first sample
+    sampler.start()
     for _ in range(args.warmup):
         device_step()
     barrier()
     assert oasr_b200.device_status() == 0
+    time.sleep(1.0)
+    sampler.rows.clear()                 # keep only samples taken from here on (timed regions)
     # ---------------- device-resident throughput ----------------
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     launches0 = _lib.launch_count()
     evs = []
     barrier()
