@@ -39,6 +39,7 @@ class ConformerConfig:
     cnn_module_norm: str = "batch_norm"   # also the type of norm_conv (model.py:575-581)
     embed_layer_norm: bool = True         # oasr/models/conformer/config.py:56
     eps: float = 1e-5
+    causal: bool = False                  # causal depthwise conv (lorder = kernel - 1), used for streaming
 
     @property
     def vocab_padded(self) -> int:       # align_out_features, oasr/models/base.py:170-178
@@ -52,6 +53,8 @@ class ConformerConfig:
 CONFIG1 = ConformerConfig()                                             # CPU-runnable reference case
 CONFIG2 = ConformerConfig(d_model=512, heads=8)                         # offline bf16 headline case
 TINY = ConformerConfig(d_model=128, heads=2, ffn=256, layers=2, vocab=90)
+TINY_STREAM = ConformerConfig(d_model=128, heads=2, ffn=256, layers=2, vocab=90, causal=True)
+CONFIG3 = ConformerConfig(d_model=512, heads=8, causal=True)           # streaming chunked case
 
 
 # ---------------------------------------------------------------------------
@@ -324,3 +327,79 @@ def greedy_tokens(log_probs: torch.Tensor, out_len: torch.Tensor, vocab: int, bl
             prev = i
         res.append(hyp)
     return res
+
+
+# ---------------------------------------------------------------------------
+# Streaming: chunk-by-chunk forward with cached keys/values and conv left context
+# ---------------------------------------------------------------------------
+class StreamState:
+    """Per-stream state of ConformerEncoder.forward_chunk_paged (model.py:913-1023) kept densely:
+    per layer the cached keys / values (H, T_cached, dk) and the conv module's left context
+    (kernel-1 frames of its input), plus the number of encoder frames emitted so far."""
+
+    def __init__(self, cfg: ConformerConfig):
+        H, dk, d = cfg.heads, cfg.head_dim, cfg.d_model
+        self.k = [torch.zeros(H, 0, dk) for _ in range(cfg.layers)]
+        self.v = [torch.zeros(H, 0, dk) for _ in range(cfg.layers)]
+        self.cnn = [torch.zeros(cfg.kernel - 1, d) for _ in range(cfg.layers)]   # zero-initialised slot buffer
+        self.offset = 0
+
+
+def forward_chunk(P, cfg: ConformerConfig, state: StreamState, xs: torch.Tensor, max_past_frames: int,
+                  block: int = 16) -> torch.Tensor:
+    """One streaming chunk of one stream: xs (T_in, F) feature window -> log-probs (chunk, Vpad).
+
+    Restates forward_chunk_paged with att/cnn caches (model.py:913-1023), the paged attention of
+    RelPositionMultiHeadedAttention._forward_paged (oasr/layers/attention/attention.py:229-280) and the
+    cached causal ConvolutionModule.forward (model.py:168-198).  The cache manager keeps whole blocks
+    of ``block`` frames and drops the oldest ones so that at most ``max_past_frames`` cached frames are
+    visible when a chunk starts (oasr/cache/attention_cache.py:387-398,427-465); key j of the cache has
+    absolute position offset - cached + j (model.py:993-1001)."""
+    assert cfg.causal
+    d, H, dk, K = cfg.d_model, cfg.heads, cfg.head_dim, cfg.kernel
+    x, _ = embed(P, cfg, xs.unsqueeze(0))                 # (1, chunk, d); positions are handled below
+    x = x[0]
+    chunk = x.shape[0]
+    while state.k[0].shape[1] > max_past_frames:          # evict whole blocks, oldest first
+        for i in range(cfg.layers):
+            state.k[i] = state.k[i][:, block:]
+            state.v[i] = state.v[i][:, block:]
+    cached = state.k[0].shape[1]
+    pe = positional_table(5000, d)
+    pos_start = state.offset - cached
+    pos_emb = pe[pos_start:pos_start + cached + chunk]    # (cached + chunk, d)
+    scale = 1.0 / math.sqrt(dk)
+    for i in range(cfg.layers):
+        p = f"encoder.encoders.{i}"
+        x = x + 0.5 * _ffn(P, p + ".feed_forward_macaron", _norm(P, p + ".norm_ff_macaron", x, "layer_norm", cfg.eps))
+        # --- attention over [cache ; chunk] ---
+        h = _norm(P, p + ".norm_mha", x, "layer_norm", cfg.eps)
+        a = p + ".self_attn"
+        qkv = F.linear(h, P[a + ".linear_qkv.weight"], P[a + ".linear_qkv.bias"])
+        q, k, v = (t.view(chunk, H, dk).transpose(0, 1) for t in qkv.split(d, dim=-1))     # (H, chunk, dk)
+        state.k[i] = torch.cat([state.k[i], k], dim=1)
+        state.v[i] = torch.cat([state.v[i], v], dim=1)
+        pp = F.linear(pos_emb, P[a + ".linear_pos.weight"]).view(-1, H, dk).permute(1, 2, 0)  # (H, dk, T_kv)
+        q_u = q + P[a + ".pos_bias_u"].unsqueeze(1)
+        q_v = q + P[a + ".pos_bias_v"].unsqueeze(1)
+        s = torch.matmul(q_u, state.k[i].transpose(-1, -2)) * scale + torch.matmul(q_v, pp) * scale
+        o = torch.matmul(torch.softmax(s, dim=-1), state.v[i])                                # (H, chunk, dk)
+        o = o.transpose(0, 1).reshape(chunk, d)
+        x = x + F.linear(o, P[a + ".linear_out.weight"], P[a + ".linear_out.bias"])
+        # --- conv module with left context (causal, lorder = K-1) ---
+        c = p + ".conv_module"
+        h = _norm(P, p + ".norm_conv", x, cfg.cnn_module_norm, cfg.eps)
+        cat = torch.cat([state.cnn[i], h], dim=0)                      # (K-1 + chunk, d)
+        state.cnn[i] = cat[-(K - 1):].clone()
+        y = F.linear(cat, P[c + ".pointwise_conv1.weight"].squeeze(-1), P[c + ".pointwise_conv1.bias"])
+        y = F.glu(y, dim=-1)
+        w = P[c + ".depthwise_conv.weight"].reshape(K, d).t().unsqueeze(1)
+        y = F.conv1d(y.t().unsqueeze(0), w, P[c + ".depthwise_conv.bias"], groups=d)[0].t()   # (chunk, d)
+        y = F.silu(_norm(P, c + ".norm_activation", y, cfg.cnn_module_norm, cfg.eps))
+        y = F.linear(y, P[c + ".pointwise_conv2.weight"].squeeze(-1), P[c + ".pointwise_conv2.bias"])
+        x = x + y
+        x = x + 0.5 * _ffn(P, p + ".feed_forward", _norm(P, p + ".norm_ff", x, "layer_norm", cfg.eps))
+        x = _norm(P, p + ".norm_final", x, "layer_norm", cfg.eps)
+    x = _norm(P, "encoder.after_norm", x, "layer_norm", cfg.eps)
+    state.offset += chunk
+    return ctc_head(P, x)

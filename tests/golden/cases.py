@@ -133,3 +133,16 @@ def packed_layout(lens, conv_kernel: int, num_heads: int):
         conv_gather_idx=np.arange(int(lens.sum()), dtype=np.int64) + half * seg_id,
         bias_offsets=np.concatenate([[0], np.cumsum(num_heads * lens * lens)]).astype(np.int32),
     )
+
+
+# Streaming: chunk = 16 encoder frames = windows of 67 feature frames stepped by 64
+# (oasr/engine/streaming_backend/paged.py:83-104), two streams, seven chunks, a history cap
+# of 2 chunks so that eviction (and the shifted position window) is exercised.
+STREAM_CASE = dict(cfg=OC.TINY_STREAM, weight_seed=1234, perturb=0.1, feat_seed=17, streams=2, chunks=7,
+                   window=67, step=64, num_left_chunks=2, chunk_size=16)
+
+
+def make_stream_features(case):
+    g = torch.Generator().manual_seed(case["feat_seed"])
+    total = case["step"] * (case["chunks"] - 1) + case["window"]
+    return torch.randn(case["streams"], total, case["cfg"].input_size, generator=g)

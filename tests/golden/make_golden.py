@@ -48,7 +48,7 @@ def build_reference_model(cfg: OC.ConformerConfig, params):
     enc = ConformerEncoderConfig(
         input_size=cfg.input_size, output_size=cfg.d_model, attention_heads=cfg.heads, linear_units=cfg.ffn,
         num_blocks=cfg.layers, cnn_module_kernel=cfg.kernel, cnn_module_norm=cfg.cnn_module_norm,
-        embed_layer_norm=cfg.embed_layer_norm)
+        embed_layer_norm=cfg.embed_layer_norm, causal=cfg.causal)
     model = ConformerModel(ConformerModelConfig(encoder=enc, vocab_size=cfg.vocab_padded)).eval()
     sd = model.state_dict()
     own = dict(model.named_parameters())
@@ -167,7 +167,48 @@ def operator_cases():
     np.savez_compressed(HERE / "operators.npz", **out)
 
 
+def stream_case():
+    """Chunk-by-chunk streaming through the reference's own cache managers on the CPU
+    (the per-stream driver of tests/test_pipeline.py:166-239)."""
+    from oasr.cache import AttentionCacheManager, BlockPool, CacheConfig, CnnCacheManager, StreamContext
+
+    case = cases.STREAM_CASE
+    cfg = case["cfg"]
+    params = OC.init_params(cfg, seed=case["weight_seed"], perturb=case["perturb"])
+    model = build_reference_model(cfg, params)
+    feats = cases.make_stream_features(case)
+    ccfg = CacheConfig(num_layers=cfg.layers, n_kv_head=cfg.heads, head_dim=cfg.head_dim, hidden_dim=cfg.d_model,
+                       kernel_size=cfg.kernel, chunk_size=case["chunk_size"], num_left_chunks=case["num_left_chunks"],
+                       block_size_frames=case["chunk_size"], max_num_blocks=64, max_blocks_per_seq=16,
+                       device=torch.device("cpu"), dtype=torch.float32)
+    max_past = case["num_left_chunks"] * case["chunk_size"]   # commit-time eviction of the per-stream driver
+    out = {}
+    for sidx in range(case["streams"]):
+        pool = BlockPool(ccfg)
+        att_mgr, cnn_mgr = AttentionCacheManager(pool, ccfg), CnnCacheManager(ccfg)
+        att_mgr.allocate_stream(sidx, slot_id=0)
+        cnn_mgr.allocate_stream(sidx, slot_id=0)
+        ctx = StreamContext(sidx, att_mgr, cnn_mgr)
+        state = OC.StreamState(cfg)
+        offset, ref_chunks, worst = 0, [], 0.0
+        for c in range(case["chunks"]):
+            xs = feats[sidx, c * case["step"]: c * case["step"] + case["window"]]
+            ctx.prepare_chunk()
+            probs = model.forward_chunk_paged(xs.unsqueeze(0), offset, ctx.get_att_caches(), ctx.get_cnn_cache(),
+                                              cache_t1=int(att_mgr._cache_seqlens[0]))
+            ctx.commit_chunk_paged(probs.size(1))
+            offset += probs.size(1)
+            mine = OC.forward_chunk(params, cfg, state, xs, max_past)
+            worst = max(worst, (probs[0] - mine)[:, :cfg.vocab].abs().max().item())
+            ref_chunks.append(probs[0])
+        print(f"stream {sidx}: reference vs oracle max-abs over {case['chunks']} chunks = {worst:.3e}")
+        assert worst < 5e-5, "streaming oracle does not restate the reference"
+        out[f"stream{sidx}_log_probs"] = torch.stack(ref_chunks).numpy()
+    np.savez_compressed(HERE / "stream_tiny.npz", **out)
+
+
 if __name__ == "__main__":
+    stream_case()
     operator_cases()
     for name in cases.MODEL_CASES:
         model_case(name)

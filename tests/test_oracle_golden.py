@@ -108,3 +108,23 @@ def test_package_weight_init_equals_oracle_init():
     theirs = OC.init_params(cfg, 99, 0.0)
     assert list(mine) == list(theirs)
     assert all(torch.equal(mine[k], theirs[k]) for k in mine)
+
+
+def test_streaming_oracle_matches_reference_fixture():
+    """Chunk-by-chunk oracle (cached K/V, conv left context, block eviction) vs the fixture written
+    from the reference's forward_chunk_paged driven by its own cache managers."""
+    case = cases.STREAM_CASE
+    cfg = case["cfg"]
+    gold = np.load(GOLD / "stream_tiny.npz")
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats = cases.make_stream_features(case)
+    max_past = case["num_left_chunks"] * case["chunk_size"]
+    for s in range(case["streams"]):
+        state = OC.StreamState(cfg)
+        for c in range(case["chunks"]):
+            xs = feats[s, c * case["step"]: c * case["step"] + case["window"]]
+            lp = OC.forward_chunk(P, cfg, state, xs, max_past)
+            assert lp.shape[0] == case["chunk_size"]
+            d = np.abs(lp.numpy() - gold[f"stream{s}_log_probs"][c])[:, :cfg.vocab].max()
+            assert d < 5e-5, (s, c, d)
+        assert state.k[0].shape[1] <= max_past + case["chunk_size"]
