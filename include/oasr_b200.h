@@ -214,6 +214,27 @@ OASR_API int oasr_b200_depthwise_conv1d_packed(void* out, const void* in, const 
                                                int64_t max_seg_len, int64_t channels,
                                                int64_t kernel_size, int activation, int dtype,
                                                void* stream);
+/* oasr_b200_depthwise_conv1d with a per-channel affine (fp32 post_scale /
+ * post_shift, a folded inference BatchNorm) applied after the bias and before
+ * the activation: depthwise_conv followed by BatchNormActivation of the conv
+ * module (oasr/models/conformer/model.py:193-194) in one kernel. */
+OASR_API int oasr_b200_depthwise_conv1d_affine(void* out, const void* in, const void* weight,
+                                               const void* bias /*nullable*/,
+                                               const float* post_scale /*nullable*/,
+                                               const float* post_shift /*nullable*/, int64_t batch,
+                                               int64_t seq_len, int64_t channels,
+                                               int64_t kernel_size, int64_t pad_left,
+                                               int64_t pad_right, int activation, int dtype,
+                                               void* stream);
+/* Conv-module left context of streaming chunks (ConvolutionModule.forward with
+ * a cache, oasr/models/conformer/model.py:176-190, plus SlotTensor.gather /
+ * scatter, oasr/cache/state.py:88-94): xcat[b] = [state[slot_ids[b]] ; x[b]]
+ * with state (num_slots, state_len, channels), x (B, T, channels), xcat
+ * (B, state_len + T, channels); afterwards state[slot_ids[b]] is set to the
+ * last state_len rows of xcat[b]. */
+OASR_API int oasr_b200_conv_state_concat(void* xcat, void* state, const int64_t* slot_ids,
+                                         const void* x, int64_t B, int64_t state_len, int64_t T,
+                                         int64_t channels, int dtype, void* stream);
 /* Streaming causal depthwise conv with a rolling state: in (batch, seq_len,
  * channels), state (batch, kernel_size-1, channels) updated in place to the
  * last kernel_size-1 frames of [state, in], weight (channels, kernel_size).
@@ -339,6 +360,23 @@ OASR_API int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const voi
                                           int64_t max_seqlen, int64_t total, int64_t H,
                                           double scale, int dtype, void* stream);
 
+/* Streaming form of the above: the attention of
+ * RelPositionMultiHeadedAttention._forward_paged (oasr/layers/attention/attention.py:229-280)
+ * after the chunk's keys/values were written to the page pools.  qkv4 is
+ * (B*Tq, 4*H*64) rows [q+u | q+v | k | v] of the chunk, k_pool / v_pool are
+ * (num_blocks, block_size, H, 64), block_table int32 (B, blocks_per_seq),
+ * seqlens int32[B] the visible keys per stream INCLUDING the chunk.  Key j of
+ * stream b takes its position term from row pos_start[b] + j of pos (the
+ * projected positional table linear_pos(pe), pos_rows x H*64, row stride
+ * pos_stride), i.e. pos_start = offset - cached frames
+ * (oasr/models/conformer/model.py:993-1001).  out is (B*Tq, H*64).  Tq <= 128. */
+OASR_API int oasr_b200_fmha_paged_relpos(void* out, const void* qkv4, void* k_pool, void* v_pool,
+                                         const void* pos, int64_t pos_rows, int64_t pos_stride,
+                                         const int32_t* pos_start, const int32_t* block_table,
+                                         const int32_t* seqlens, int64_t B, int64_t Tq, int64_t H,
+                                         int64_t blocks_per_seq, int64_t block_size,
+                                         int64_t num_blocks, double scale, int dtype, void* stream);
+
 /* ---- paged KV cache ---------------------------------------------------- */
 /* Scatter a chunk of new keys/values into the page pools.  k_new, v_new are
  * (B, Hkv, T, D) with element strides (sb, sh, st) and unit stride along D;
@@ -407,6 +445,8 @@ typedef struct oasr_b200_conformer_model {
   int64_t pe_rows;
   const void *after_norm_w, *after_norm_b;
   const void *ctc_w, *ctc_b;                 /* (vocab_padded, 3d) split head weight, (vocab_padded) bias */
+  const void *pos_proj;                      /* nullable: (pos_proj_rows, num_layers*d) = pe . pos_w_all^T, streaming */
+  int64_t pos_proj_rows;
 } oasr_b200_conformer_model;
 
 /* Bytes of device scratch oasr_b200_conformer_encode_packed needs for `total`
@@ -430,6 +470,33 @@ OASR_API int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* 
                                                void* workspace, int64_t workspace_bytes,
                                                float* log_probs /*nullable*/,
                                                int32_t* argmax /*nullable*/, void* stream);
+
+/* One streaming chunk for B streams: ConformerEncoder.forward_chunk_paged
+ * (oasr/models/conformer/model.py:913-1023) + CTC head in one host call.
+ * rows (B*T, embed_in) are the subsampled chunk frames; layer l appends its
+ * keys/values at logical positions cache_seqlens[b].. to k_pools[l] / v_pools[l]
+ * (HOST arrays of num_layers device pointers, pools (num_blocks, block_size, H,
+ * 64)) through block_table (B, blocks_per_seq), attends over total_seqlens[b] =
+ * cache_seqlens[b] + T keys with positions starting at pos_start[b] = offset[b] -
+ * cache_seqlens[b], and runs the causal conv module on [cnn_state[l, slot_ids[b]] ;
+ * chunk], updating cnn_state (num_layers, num_slots, kernel-1, d) in place.  The
+ * caller allocated the chunk's pages before the call and advances cache_seqlens
+ * after it, as with the reference's AttentionCacheManager.  T <= 128. */
+OASR_API int64_t oasr_b200_conformer_chunk_workspace_bytes(const oasr_b200_conformer_model* model,
+                                                           int64_t B, int64_t T);
+OASR_API int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model,
+                                             const void* rows, int64_t B, int64_t T,
+                                             void* const* k_pools /*host*/,
+                                             void* const* v_pools /*host*/,
+                                             const int32_t* block_table,
+                                             const int32_t* cache_seqlens,
+                                             const int32_t* total_seqlens,
+                                             const int32_t* pos_start, int64_t blocks_per_seq,
+                                             int64_t block_size, int64_t num_blocks,
+                                             void* cnn_state, int64_t num_slots,
+                                             const int64_t* slot_ids, void* workspace,
+                                             int64_t workspace_bytes, float* log_probs /*nullable*/,
+                                             int32_t* argmax /*nullable*/, void* stream);
 
 /* This entry point has no counterpart in the reference.  It does what
  * oasr_b200_conformer_encode_packed does for callers that must not allocate

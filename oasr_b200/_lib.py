@@ -48,6 +48,9 @@ _SIGNATURES = {
     "oasr_b200_add_norm_f32": [P, P, P, P, c_double, c_int, P, P, P, P, I, I, c_double, c_int, c_int, P],
     "oasr_b200_depthwise_conv1d_packed": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_int, c_int, P],
     "oasr_b200_fmha_varlen_relpos": [P, P, P, I, I, P, I, I, I, I, c_double, c_int, P],
+    "oasr_b200_fmha_paged_relpos": [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, c_double, c_int, P],
+    "oasr_b200_depthwise_conv1d_affine": [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P],
+    "oasr_b200_conv_state_concat": [P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_glu": [P, P, I, I, c_int, P],
     "oasr_b200_swish": [P, P, I, c_int, P],
     "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
@@ -87,12 +90,15 @@ class ConformerModel(ctypes.Structure):
         ("eps", c_double), ("layers", POINTER(ConformerLayer)),
         ("embed_w", c_void_p), ("embed_b", c_void_p), ("embed_ln_w", c_void_p), ("embed_ln_b", c_void_p),
         ("pos_w_all", c_void_p), ("pe", c_void_p), ("pe_rows", c_int64),
-        ("after_norm_w", c_void_p), ("after_norm_b", c_void_p), ("ctc_w", c_void_p), ("ctc_b", c_void_p)]
+        ("after_norm_w", c_void_p), ("after_norm_b", c_void_p), ("ctc_w", c_void_p), ("ctc_b", c_void_p),
+        ("pos_proj", c_void_p), ("pos_proj_rows", c_int64)]
 
 
 _SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, I, P, P, P]
 
 _SIGNATURES["oasr_b200_conformer_encode_packed_noalloc"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, P, P]
+_SIGNATURES["oasr_b200_conformer_chunk_paged"] = [POINTER(ConformerModel), P, I, I, POINTER(c_void_p), POINTER(c_void_p),
+                                                 P, P, P, P, I, I, I, P, I, P, P, I, P, P, P]
 _SIGNATURES["oasr_b200_profile_enable"] = [c_int]
 _SIGNATURES["oasr_b200_profile_get"] = [c_int, POINTER(c_char_p), POINTER(c_double), POINTER(c_double)]
 
@@ -123,6 +129,8 @@ def load() -> ctypes.CDLL:
     lib.oasr_b200_launch_count.argtypes = []
     lib.oasr_b200_conformer_noalloc_capacity_bytes.restype = c_int64
     lib.oasr_b200_conformer_noalloc_capacity_bytes.argtypes = []
+    lib.oasr_b200_conformer_chunk_workspace_bytes.restype = c_int64
+    lib.oasr_b200_conformer_chunk_workspace_bytes.argtypes = [POINTER(ConformerModel), I, I]
     lib.oasr_b200_profile_count.restype = c_int
     lib.oasr_b200_profile_count.argtypes = []
     lib.oasr_b200_conformer_workspace_bytes.restype = c_int64
@@ -139,7 +147,7 @@ def load() -> ctypes.CDLL:
 
 def exported_names() -> list[str]:
     return list(_STRING_FUNCS) + ["oasr_b200_launch_count", "oasr_b200_conformer_workspace_bytes", "oasr_b200_profile_count",
-                                  "oasr_b200_conformer_noalloc_capacity_bytes"] + list(_SIGNATURES)
+                                  "oasr_b200_conformer_noalloc_capacity_bytes", "oasr_b200_conformer_chunk_workspace_bytes"] + list(_SIGNATURES)
 
 
 def launch_count() -> int:

@@ -27,6 +27,35 @@ struct Workspace {
 
 int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
+struct ChunkWorkspace {
+  float* res;
+  uint8_t *h, *y, *a_ffn, *qkv4, *att, *xcat, *g, *cv, *h3;
+  int64_t bytes;
+};
+
+ChunkWorkspace carve_chunk(const oasr_b200_conformer_model& m, int64_t B, int64_t T, uint8_t* base) {
+  ChunkWorkspace w{};
+  const int64_t d = m.d_model, M = B * T, MC = B * (T + m.kernel - 1);
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    uint8_t* p = base ? base + off : nullptr;
+    off += align256(bytes);
+    return p;
+  };
+  w.res = reinterpret_cast<float*>(take(M * d * 4));
+  w.h = take(M * d * 2);
+  w.y = take(M * d * 2);
+  w.a_ffn = take(M * m.ffn * 2);
+  w.qkv4 = take(M * 4 * d * 2);
+  w.att = take(M * d * 2);
+  w.xcat = take(MC * d * 2);
+  w.g = take(MC * d * 2);
+  w.cv = take(M * d * 2);
+  w.h3 = take(M * 3 * d * 2);
+  w.bytes = off;
+  return w;
+}
+
 // Optional per-step timing of the executor: a CUDA-event pair around every step, on the launching
 // stream.  Off by default; switched on for one call by a benchmark.
 struct ProfRecord {
@@ -244,6 +273,91 @@ int oasr_b200_conformer_encode_packed_noalloc(const oasr_b200_conformer_model* m
   }
   return oasr_b200_conformer_encode_packed(model, rows, cu_seqlens, fill_frames, num_segs, total, max_seg,
                                            scratch_of_device[dev], kStaticScratchBytes, log_probs, argmax, stream);
+}
+
+int64_t oasr_b200_conformer_chunk_workspace_bytes(const oasr_b200_conformer_model* model, int64_t B, int64_t T) {
+  if (!model || B < 0 || T < 0) return -1;
+  return ob::carve_chunk(*model, B, T, nullptr).bytes;
+}
+
+int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, const void* rows, int64_t B, int64_t T,
+                                    void* const* k_pools, void* const* v_pools, const int32_t* block_table,
+                                    const int32_t* cache_seqlens, const int32_t* total_seqlens,
+                                    const int32_t* pos_start, int64_t blocks_per_seq, int64_t block_size,
+                                    int64_t num_blocks, void* cnn_state, int64_t num_slots, const int64_t* slot_ids,
+                                    void* workspace, int64_t workspace_bytes, float* log_probs, int32_t* argmax,
+                                    void* stream) {
+  using namespace ob;
+  OB_REQUIRE(model && model->layers, OASR_ERR_INVALID, "conformer_chunk_paged: null model");
+  const oasr_b200_conformer_model& m = *model;
+  OB_REQUIRE(m.d_model == m.heads * 64, OASR_ERR_UNSUPPORTED, "conformer_chunk_paged: needs head_dim 64");
+  OB_REQUIRE(B >= 0 && T > 0 && T <= 128, OASR_ERR_INVALID, "conformer_chunk_paged: bad shape (B %lld, T %lld)",
+             (long long)B, (long long)T);
+  if (B == 0) return OASR_OK;
+  OB_REQUIRE(rows && k_pools && v_pools && block_table && cache_seqlens && total_seqlens && pos_start && cnn_state &&
+                 slot_ids && workspace,
+             OASR_ERR_INVALID, "conformer_chunk_paged: null pointer argument");
+  OB_REQUIRE(m.pos_proj && m.pos_proj_rows > 0, OASR_ERR_INVALID,
+             "conformer_chunk_paged: the model has no projected positional table (pos_proj)");
+  OB_REQUIRE(is_aligned(workspace, 256), OASR_ERR_ALIGN, "conformer_chunk_paged: workspace must be 256-byte aligned");
+  ChunkWorkspace w = carve_chunk(m, B, T, static_cast<uint8_t*>(workspace));
+  OB_REQUIRE(workspace_bytes >= w.bytes, OASR_ERR_INVALID, "conformer_chunk_paged: workspace of %lld bytes, %lld needed",
+             (long long)workspace_bytes, (long long)w.bytes);
+  const int64_t d = m.d_model, L = m.num_layers, M = B * T, SL = m.kernel - 1, MC = B * (T + SL);
+  const int dt = m.dtype;
+  const double scale = 1.0 / std::sqrt(64.0);
+  const oasr_b200_conformer_layer* ly = m.layers;
+
+  OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm(w.y, rows, m.embed_w, m.embed_b, M, d, m.embed_in, OASR_ACT_NONE, dt, stream));
+  if (m.embed_ln_w) {
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 2, m.embed_ln_w, m.embed_ln_b,
+                                   ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, M, d, 1e-5, 0, dt, stream));
+  } else {
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 0, ly[0].norm_ff_macaron_w,
+                                   ly[0].norm_ff_macaron_b, nullptr, nullptr, M, d, m.eps, 0, dt, stream));
+  }
+  for (int64_t i = 0; i < L; ++i) {
+    const oasr_b200_conformer_layer& l = ly[i];
+    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
+    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
+                                   m.eps, 0, dt, stream));
+    // attention: project, append the chunk's keys/values to the pages, attend over cache + chunk
+    OB_STEP("gemm qkv4", 2.0 * M * 4 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("paged_kv_write", 0, oasr_b200_paged_kv_write(k_pools[i], v_pools[i], w.qkv4 + 2 * d * 2, w.qkv4 + 3 * d * 2,
+                                     block_table, cache_seqlens, B, m.heads, T, 64, T * 4 * d, 64, 4 * d, blocks_per_seq,
+                                     block_size, num_blocks, 2, stream));
+    OB_STEP("fmha_paged_relpos", 0, oasr_b200_fmha_paged_relpos(w.att, w.qkv4, k_pools[i], v_pools[i],
+                                     static_cast<const uint8_t*>(m.pos_proj) + i * d * 2, m.pos_proj_rows, L * d,
+                                     pos_start, block_table, total_seqlens, B, T, m.heads, blocks_per_seq, block_size,
+                                     num_blocks, scale, dt, stream));
+    OB_STEP("gemm attn_out", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.att, l.out_w, l.out_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
+                                   nullptr, M, d, m.eps, 0, dt, stream));
+    // convolution module with the cached left context
+    OB_STEP("conv_state_concat", 0, oasr_b200_conv_state_concat(w.xcat, static_cast<uint8_t*>(cnn_state) + i * num_slots * SL * d * 2,
+                                     slot_ids, w.h, B, SL, T, d, dt, stream));
+    OB_STEP("gemm_glu pw1", 2.0 * MC * 2 * d * d, oasr_b200_gemm_glu(w.g, w.xcat, l.pw1_w, l.pw1_b, MC, d, d, dt, stream));
+    OB_STEP("depthwise_conv1d", 0, oasr_b200_depthwise_conv1d_affine(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
+                                     B, T + SL, d, m.kernel, 0, 0, OASR_ACT_SWISH, dt, stream));
+    OB_STEP("gemm pw2", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.cv, l.pw2_w, l.pw2_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, M, d,
+                                   m.eps, 0, dt, stream));
+    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ff_w1, l.ff_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
+    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ff_w2, l.ff_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    if (i + 1 < L) {
+      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b,
+                                     ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, M, d, m.eps, 0, dt, stream));
+    } else {
+      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h3, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b, m.after_norm_w,
+                                     m.after_norm_b, M, d, m.eps, 1, dt, stream));
+    }
+  }
+  if (log_probs) {
+    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * 3 * d, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
+                                       argmax, stream));
+  }
+  return OASR_OK;
 }
 
 }  // extern "C"

@@ -451,11 +451,98 @@ __global__ void __launch_bounds__(256) causal_state_update_kernel(T* __restrict_
   }
 }
 
+// xcat[b] = [state[slot[b]] (SL rows) ; x[b] (T rows)], 16-byte pieces.
+__global__ void __launch_bounds__(256) conv_state_concat_kernel(uint8_t* __restrict__ xcat,
+                                                                const uint8_t* __restrict__ state,
+                                                                const int64_t* __restrict__ slots,
+                                                                const uint8_t* __restrict__ x, int64_t B, int SL, int T,
+                                                                int64_t row_bytes) {
+  const int64_t pieces = row_bytes / 16;
+  const int64_t total = B * (SL + T) * pieces;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t piece = i % pieces;
+    const int64_t row = i / pieces;
+    const int r = static_cast<int>(row % (SL + T));
+    const int64_t b = row / (SL + T);
+    const uint8_t* src = r < SL ? state + ((slots[b] * SL + r) * row_bytes) : x + ((b * T + (r - SL)) * row_bytes);
+    *reinterpret_cast<uint4*>(xcat + row * row_bytes + piece * 16) = *reinterpret_cast<const uint4*>(src + piece * 16);
+  }
+}
+// state[slot[b]] = last SL rows of xcat[b] (read from xcat, so the update cannot race with itself).
+__global__ void __launch_bounds__(256) conv_state_update_kernel(uint8_t* __restrict__ state,
+                                                                const int64_t* __restrict__ slots,
+                                                                const uint8_t* __restrict__ xcat, int64_t B, int SL,
+                                                                int T, int64_t row_bytes) {
+  const int64_t pieces = row_bytes / 16;
+  const int64_t total = B * SL * pieces;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t piece = i % pieces;
+    const int64_t row = i / pieces;
+    const int r = static_cast<int>(row % SL);
+    const int64_t b = row / SL;
+    *reinterpret_cast<uint4*>(state + (slots[b] * SL + r) * row_bytes + piece * 16) =
+        *reinterpret_cast<const uint4*>(xcat + (b * (SL + T) + T + r) * row_bytes + piece * 16);
+  }
+}
+
 }  // namespace
 
 }  // namespace ob
 
 extern "C" {
+
+int oasr_b200_conv_state_concat(void* xcat, void* state, const int64_t* slot_ids, const void* x, int64_t B,
+                                int64_t state_len, int64_t T, int64_t channels, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(B >= 0 && state_len >= 0 && T > 0 && channels > 0, OASR_ERR_INVALID, "conv_state_concat: bad shape");
+  if (B == 0) return OASR_OK;
+  OB_REQUIRE(xcat && state && slot_ids && x, OASR_ERR_INVALID, "conv_state_concat: null pointer argument");
+  const int64_t es = dtype == OASR_DT_F32 ? 4 : 2;
+  OB_REQUIRE(dtype == OASR_DT_F32 || dtype == OASR_DT_F16 || dtype == OASR_DT_BF16, OASR_ERR_DTYPE,
+             "conv_state_concat: unsupported dtype id %d", dtype);
+  const int64_t row_bytes = channels * es;
+  OB_REQUIRE(row_bytes % 16 == 0 && is_aligned(xcat, 16) && is_aligned(state, 16) && is_aligned(x, 16), OASR_ERR_ALIGN,
+             "conv_state_concat: rows must be multiples of 16 bytes and 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  int64_t g = (B * (state_len + T) * (row_bytes / 16) + 255) / 256;
+  if (g > cap) g = cap;
+  conv_state_concat_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(
+      static_cast<uint8_t*>(xcat), static_cast<const uint8_t*>(state), slot_ids, static_cast<const uint8_t*>(x), B,
+      (int)state_len, (int)T, row_bytes);
+  if (int rc = check_launch("conv_state_concat launch")) return rc;
+  if (state_len == 0) return OASR_OK;
+  g = (B * state_len * (row_bytes / 16) + 255) / 256;
+  if (g > cap) g = cap;
+  conv_state_update_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(static_cast<uint8_t*>(state), slot_ids,
+                                                                   static_cast<const uint8_t*>(xcat), B, (int)state_len,
+                                                                   (int)T, row_bytes);
+  return check_launch("conv_state_update launch");
+}
+
+int oasr_b200_depthwise_conv1d_affine(void* out, const void* in, const void* weight, const void* bias,
+                                      const float* post_scale, const float* post_shift, int64_t batch,
+                                      int64_t seq_len, int64_t channels, int64_t kernel_size, int64_t pad_left,
+                                      int64_t pad_right, int activation, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(batch >= 0 && seq_len >= 0 && channels > 0 && kernel_size > 0 && pad_left >= 0 && pad_right >= 0,
+             OASR_ERR_INVALID, "depthwise_conv1d_affine: bad shape");
+  const int64_t out_len = seq_len + pad_left + pad_right - kernel_size + 1;
+  OB_REQUIRE(out_len > 0, OASR_ERR_INVALID, "depthwise_conv1d_affine has invalid output length %lld", (long long)out_len);
+  if (batch == 0) return OASR_OK;
+  OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "depthwise_conv1d_affine: null pointer argument");
+  OB_REQUIRE((post_scale == nullptr) == (post_shift == nullptr), OASR_ERR_INVALID,
+             "depthwise_conv1d_affine: post_scale and post_shift go together");
+  OB_REQUIRE(act_is_known(activation), OASR_ERR_INVALID, "depthwise_conv1d_affine: unknown activation id %d", activation);
+  DwArgs a{};
+  a.out = out; a.in = in; a.weight = weight; a.bias = bias; a.post_scale = post_scale; a.post_shift = post_shift;
+  a.batch = batch; a.seq_len = (int)seq_len; a.out_len = (int)out_len; a.channels = (int)channels;
+  a.kernel_size = (int)kernel_size; a.pad_left = (int)pad_left; a.act = activation;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, (int)out_len, s); });
+}
 
 int oasr_b200_depthwise_conv1d_packed(void* out, const void* in, const void* weight, const void* bias,
                                       const float* post_scale, const float* post_shift, const float* right_fill,

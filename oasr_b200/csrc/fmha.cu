@@ -65,6 +65,8 @@ struct Params {
   int64_t bias_sb, bias_sh, bias_sq;  // dense / paged bias strides (elements)
   const void* bias_offsets;           // varlen: per-segment start (elements)
   int bias_off_i64;
+  const int32_t* pos_start;           // relpos + paged: first position row of each stream's key 0
+  int out_token_major;                // dense/paged: out is (B*Tq, H*D) rows instead of (B,H,Tq,D)
   void* out;
   uint32_t* status;
 };
@@ -130,8 +132,13 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
     if (p.seqstarts) kv_start = max(p.seqstarts[bz], 0);
     q_row_c1 = q0; q_c3 = bz;
     kv_row_c1 = 0; kv_c3 = bz;
-    out_row_stride = D;
-    out_row0 = ((static_cast<int64_t>(bz) * p.H + h) * p.Tq + q0) * D;
+    if (p.out_token_major) {
+      out_row_stride = static_cast<int64_t>(p.H) * D;
+      out_row0 = ((static_cast<int64_t>(bz) * p.Tq + q0) * p.H + h) * D;
+    } else {
+      out_row_stride = D;
+      out_row0 = ((static_cast<int64_t>(bz) * p.H + h) * p.Tq + q0) * D;
+    }
   }
   if (q0 >= tq_seg) return;  // CTA-uniform
   int kv_end = kv_len;
@@ -214,13 +221,19 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
             if (col >= p.blocks_per_seq) col = p.blocks_per_seq - 1;  // masked keys: any valid page
             int page = p.block_table[static_cast<int64_t>(bz) * p.blocks_per_seq + col];
             page = min(max(page, 0), p.num_blocks - 1);
+            if (p.relpos) {
+              ptx::tma_load_4d(dk + pg * bs * 128, &maps.k, 0, 0, hkv, page, &kv_full[b]);
+            } else {
 #pragma unroll
-            for (int a = 0; a < kAtoms; ++a)
-              ptx::tma_load_4d(dk + a * kAtomBytes + pg * bs * 128, &maps.k, a * 64, 0, hkv, page, &kv_full[b]);
+              for (int a = 0; a < kAtoms; ++a)
+                ptx::tma_load_4d(dk + a * kAtomBytes + pg * bs * 128, &maps.k, a * 64, 0, hkv, page, &kv_full[b]);
+            }
 #pragma unroll
             for (int a = 0; a < S::kVAtoms; ++a)
               ptx::tma_load_4d(dv + a * kAtomBytes + pg * bs * 128, &maps.v, a * 64, 0, hkv, page, &kv_full[b]);
           }
+          // position term of the keys of this tile: rows pos_start[b] + key0 ... of the projected table
+          if (p.relpos) ptx::tma_load_4d(dk + kAtomBytes, &maps.k2, 0, p.pos_start[bz] + key0, h, 0, &kv_full[b]);
         } else {
           if (p.relpos) {
             ptx::tma_load_4d(dk, &maps.k, 0, kv_row_c1 + key0, hkv, kv_c3, &kv_full[b]);
@@ -533,6 +546,50 @@ int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, i
   return dispatch(maps, p, D, dtype, grid, stream);
 }
 
+
+int oasr_b200_fmha_paged_relpos(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos,
+                                int64_t pos_rows, int64_t pos_stride, const int32_t* pos_start,
+                                const int32_t* block_table, const int32_t* seqlens, int64_t B, int64_t Tq, int64_t H,
+                                int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, double scale,
+                                int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::fmha;
+  const int D = 64;
+  OB_REQUIRE(B >= 0 && Tq >= 0 && H > 0, OASR_ERR_INVALID, "fmha_paged_relpos: bad shape");
+  if (B == 0 || Tq == 0) return OASR_OK;
+  OB_REQUIRE(out && qkv4 && k_pool && v_pool && pos && pos_start && block_table && seqlens, OASR_ERR_INVALID,
+             "fmha_paged_relpos: null pointer argument");
+  OB_REQUIRE(Tq <= BQ, OASR_ERR_UNSUPPORTED, "fmha_paged_relpos: at most %d query frames per stream", BQ);
+  OB_REQUIRE(block_size > 0 && blocks_per_seq > 0 && num_blocks > 0 && BKV % block_size == 0 && block_size % 8 == 0,
+             OASR_ERR_UNSUPPORTED,
+             "fmha_paged_relpos: block size must divide 128 and be a multiple of 8 (got %lld)", (long long)block_size);
+  OB_REQUIRE(is_aligned(out, 16) && is_aligned(qkv4, 16) && is_aligned(k_pool, 16) && is_aligned(v_pool, 16) &&
+                 is_aligned(pos, 16) && pos_stride % 8 == 0,
+             OASR_ERR_ALIGN, "fmha_paged_relpos: operands must be 16-byte aligned");
+  OB_REQUIRE(B <= 65535 && H <= 65535, OASR_ERR_INVALID, "fmha_paged_relpos: batch / head count too large");
+  const int64_t d = H * D, ld = 4 * d;
+  const uint8_t* base = static_cast<const uint8_t*>(qkv4);
+  Maps maps;
+  if (int rc = make_map(&maps.q, dtype, base, D, Tq, H, B, ld, D, Tq * ld, BQ)) return rc;
+  if (int rc = make_map(&maps.q2, dtype, base + d * 2, D, Tq, H, B, ld, D, Tq * ld, BQ)) return rc;
+  if (int rc = make_map(&maps.k, dtype, k_pool, D, block_size, H, num_blocks, H * D, D, block_size * H * D,
+                        (int)block_size))
+    return rc;
+  if (int rc = make_map(&maps.v, dtype, v_pool, D, block_size, H, num_blocks, H * D, D, block_size * H * D,
+                        (int)block_size))
+    return rc;
+  if (int rc = make_map(&maps.k2, dtype, pos, D, pos_rows, H, 1, pos_stride, D, pos_stride * pos_rows, BKV)) return rc;
+  Params p{};
+  p.mode = kPaged; p.B = (int)B; p.H = (int)H; p.Hkv = (int)H; p.Tq = (int)Tq;
+  p.Tk = (int)(blocks_per_seq * block_size);
+  p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  p.relpos = 1; p.seqlens = seqlens; p.pos_start = pos_start; p.out_token_major = 1;
+  p.block_table = block_table; p.blocks_per_seq = (int)blocks_per_seq; p.block_size = (int)block_size;
+  p.num_blocks = (int)num_blocks;
+  p.out = out; p.status = device_status_ptr();
+  dim3 grid(1, (unsigned)H, (unsigned)B);
+  return dispatch(maps, p, D, dtype, grid, static_cast<cudaStream_t>(stream));
+}
 
 int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,
                    const int64_t* k_strides, const int64_t* v_strides, const void* bias, int64_t bias_stride_b,

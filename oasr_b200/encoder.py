@@ -48,6 +48,7 @@ class ConformerConfig:
     cnn_module_norm: str = "batch_norm"
     embed_layer_norm: bool = True
     eps: float = 1e-5
+    causal: bool = False   # causal depthwise conv (left context kernel-1): the streaming configuration
 
     @property
     def vocab_padded(self) -> int:
@@ -249,8 +250,10 @@ class ConformerCTC:
         m.pos_w_all, m.pe, m.pe_rows = ptr(self.pos_w_all), ptr(self.pe), self.pe.size(0)
         m.after_norm_w, m.after_norm_b = map(ptr, self.after_norm)
         m.ctc_w, m.ctc_b = ptr(self.ctc_w), ptr(self.ctc_b)
+        m.pos_proj, m.pos_proj_rows = None, 0
         self._native_layers, self._native_model = arr, m   # keep both alive
         self._workspace = None
+        self._pos_proj = None
 
     def _encode_packed(self, rows: torch.Tensor, pk: PackedBatch, padded_semantics: bool):
         """rows: (total, F'*d) gathered embed-conv outputs -> (log_probs (total, V) fp32, argmax (total,) int32).
@@ -293,8 +296,66 @@ class ConformerCTC:
                   ctypes.c_void_p(torch.cuda.current_stream(rows.device).cuda_stream))
 
     # ------------------------------------------------------------------ entry points
+    # ------------------------------------------------------------------ streaming
+    def new_streaming_cache(self, max_streams: int, max_past_frames: int, chunk_frames: int = 16, block_size: int = 16,
+                            seed: Optional[int] = 0):
+        """Page pools, block table and conv left-context buffers for ``max_streams`` concurrent streams."""
+        from .streaming import StreamingCache
+
+        c = self.cfg
+        return StreamingCache(c.layers, c.heads, c.head_dim, c.d_model, c.kernel, max_streams, max_past_frames,
+                              chunk_frames, block_size, self.device, self.dtype, seed)
+
+    def forward_chunk_paged(self, xs: torch.Tensor, slots, cache, return_argmax: bool = False):
+        """One streaming chunk for the streams in ``slots``: ``xs (B, window, F)`` feature windows ->
+        ``log_probs (B, chunk, V)`` fp32 (ConformerEncoder.forward_chunk_paged + head,
+        oasr/models/conformer/model.py:913-1023, oasr/models/base.py:763-777).  K/V pages and the conv
+        left context in ``cache`` are updated in place; page allocation, eviction and the commit of
+        ``cache_seqlens`` happen around the single native call."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _p
+
+        if not self.cfg.causal:
+            raise RuntimeError("streaming needs a causal conv module (cfg.causal=True)")
+        if not xs.is_cuda:
+            raise RuntimeError("xs must be a CUDA tensor (oasr_b200 has no CPU path)")
+        if self._pos_proj is None:   # linear_pos of the whole positional table, every layer at once
+            self._pos_proj = OF.gemm(self.pe, self.pos_w_all)
+            self._native_model.pos_proj = ctypes.c_void_p(self._pos_proj.data_ptr())
+            self._native_model.pos_proj_rows = self._pos_proj.size(0)
+        slots = list(slots)
+        B = xs.size(0)
+        table, cached, total, pos_start, slot_ids = cache.prepare(slots)
+        conv_rows = self._subsample(xs)                                        # (B, chunk, F'*d)
+        T = conv_rows.size(1)
+        if T != cache.chunk:
+            raise RuntimeError(f"the feature window gives {T} encoder frames, the cache was built for {cache.chunk}")
+        rows = conv_rows.reshape(B * T, -1).contiguous()
+        lib = _lib.load()
+        need = lib.oasr_b200_conformer_chunk_workspace_bytes(ctypes.byref(self._native_model), B, T)
+        if self._workspace is None or self._workspace.numel() < need + 256:
+            self._workspace = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=xs.device)
+        ws = self._workspace
+        off = (-ws.data_ptr()) % 256
+        L = self.cfg.layers
+        kp = (ctypes.c_void_p * L)(*[cache.k_pool[i].data_ptr() for i in range(L)])
+        vp = (ctypes.c_void_p * L)(*[cache.v_pool[i].data_ptr() for i in range(L)])
+        log_probs = torch.empty(B, T, self.cfg.vocab_padded, device=xs.device, dtype=torch.float32)
+        argmax = torch.empty(B, T, device=xs.device, dtype=torch.int32)
+        _lib.call("oasr_b200_conformer_chunk_paged", ctypes.byref(self._native_model), _p(rows), B, T, kp, vp, _p(table),
+                  _p(cached), _p(total), _p(pos_start), table.size(1), cache.block_size, cache.num_blocks,
+                  _p(cache.cnn_state), cache.max_streams, _p(slot_ids), ctypes.c_void_p(ws.data_ptr() + off),
+                  ws.numel() - off, _p(log_probs), _p(argmax),
+                  ctypes.c_void_p(torch.cuda.current_stream(xs.device).cuda_stream))
+        cache.commit(slots)
+        return (log_probs, argmax) if return_argmax else log_probs
+
     def _forward(self, features: torch.Tensor, lengths, padded_semantics: bool, padded_output: bool,
                  return_argmax: bool):
+        if self.cfg.causal:
+            raise NotImplementedError("offline forward with a causal conv module is not wired; use forward_chunk_paged")
         if not features.is_cuda:
             raise RuntimeError("features must be a CUDA tensor (oasr_b200 has no CPU path)")
         lens_host = lengths.tolist() if isinstance(lengths, torch.Tensor) else [int(x) for x in lengths]
