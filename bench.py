@@ -128,7 +128,8 @@ def instrumented_step(run_step):
     records, open_ev = [], {}
 
     def hook(name, phase, args):
-        if name in ("oasr_b200_conformer_encode_packed", "oasr_b200_profile_enable", "oasr_b200_profile_get"):
+        if name in ("oasr_b200_conformer_encode_packed", "oasr_b200_conformer_chunk_paged", "oasr_b200_profile_enable",
+                    "oasr_b200_profile_get"):
             return
         if phase == "begin":
             ev = torch.cuda.Event(enable_timing=True)
@@ -212,8 +213,81 @@ def run_reference_arm(args):
     return 0
 
 
+def run_streaming(args):
+    """Config-3 style measurement (``--workload streaming``): 256 concurrent streams, one step = one
+    chunk (67-frame window, 16 encoder frames, 0.64 audio-s) for every stream through the paged chunk
+    executor; history cap 256 frames in 16-frame pages handed out in a random order.  The cache is
+    brought to its steady state (17 pages per stream) by the warm-up chunks."""
+    import dataclasses
+
+    import oasr_b200
+    from oasr_b200 import _lib
+    from oasr_b200.encoder import ConformerCTC
+    from oasr_b200.weights import init_params
+
+    torch.cuda.set_device(0)
+    streams, window, chunk, max_past = args.batch if args.batch != 64 else 256, 67, 16, 256
+    cfg = dataclasses.replace(model_config(args.layers), causal=True)
+    model = ConformerCTC(cfg, init_params(cfg, 1234), device="cuda:0", dtype=torch.bfloat16)
+    cache = model.new_streaming_cache(streams, max_past, chunk_frames=chunk, seed=5)
+    slots = list(range(streams))
+    g = torch.Generator().manual_seed(7)
+    host = [torch.randn(streams, window, 80, generator=g).pin_memory() for _ in range(8)]
+    dev = [h.cuda() for h in host]
+    warm = max(args.warmup, max_past // chunk + 1)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+    for i in range(warm):
+        model.forward_chunk_paged(dev[i % 8], slots, cache)
+    torch.cuda.synchronize()
+    assert oasr_b200.device_status() == 0
+    time.sleep(1.0)
+    sampler.rows.clear()
+    launches0 = _lib.launch_count()
+    evs = []
+    for i in range(args.steps):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        model.forward_chunk_paged(dev[i % 8], slots, cache, return_argmax=True)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    launches = _lib.launch_count() - launches0
+    total_ms = float(sum(a.elapsed_time(b) for a, b in evs))
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        _, am = model.forward_chunk_paged(host[i % 8].cuda(non_blocking=True), slots, cache, return_argmax=True)
+        toks = am.cpu()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    assert oasr_b200.device_status() == 0
+    per = instrumented_step(lambda: model.forward_chunk_paged(dev[0], slots, cache))
+    audio = streams * chunk * 4 * FRAME_S * args.steps
+    kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
+                   **({"tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 1)} if v["flops"] and v["ms"] else {})}
+               for k, v in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}
+    print(json.dumps({
+        "metric": "audio_seconds_per_second", "value": audio / (total_ms * 1e-3), "unit": "audio-s/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warm, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"streaming conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002: {streams} streams x 1 chunk "
+                               f"(window {window} frames -> {chunk} encoder frames), history {max_past} frames in 16-frame pages, "
+                               "random page order, bf16 K/V", "l2": "256 MiB flush write between steps",
+                   "audio_seconds_per_step": audio / args.steps},
+        "e2e": {"value": audio / e2e_s, "unit": "audio-s/s", "h2d_bytes_per_step": int(host[0].numel() * 4),
+                "d2h_bytes_per_step": int(toks.numel() * 4),
+                "api": "ConformerCTC.forward_chunk_paged(pinned host windows) -> per-frame argmax on the host"},
+        "gpu_launches": int(launches), "clocks": clocks, "kernels_one_step": kernels}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="offline", choices=["offline", "streaming"],
+                    help="offline = the headline packed batch; streaming = 256 streams x one paged chunk per step")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -226,6 +300,10 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload == "streaming":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
+        return run_streaming(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

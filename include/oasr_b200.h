@@ -84,7 +84,11 @@ OASR_API int oasr_b200_device_status(uint32_t* word /*host*/, void* stream);
 OASR_API unsigned long long oasr_b200_launch_count(void);
 /* Process-wide integer tunables.  "gemm_bn": 0 = heuristic tile width, or 64 /
  * 128 / 256 to force it; "gemm_pairs": 1 lets large dense GEMMs run
- * on CTA pairs (tcgen05 cta_group::2), 0 (default) keeps single-CTA tiles (no reference counterpart; the reference selects tiles
+ * on CTA pairs (tcgen05 cta_group::2), 0 (default) keeps single-CTA tiles;
+ * "dwconv_path": 0 (default) = register-streaming depthwise conv where it
+ * applies, 1 = the shared-memory tiled kernel; "fmha_chunk_path": 1 (default)
+ * = paged rel-pos attention with <= 16 query frames runs the warp-per-(stream,
+ * head) kernel, 0 = always the 128-row tcgen05 kernel (no reference counterpart; the reference selects tiles
  * through its JIT variant names, oasr/jit/gemm.py:863-880). */
 OASR_API int oasr_b200_set_tunable(const char* name, int value);
 

@@ -57,6 +57,8 @@ uint32_t* device_status_ptr() {
 }
 
 namespace gemm { extern int g_force_bn; extern int g_use_pairs; }
+extern int g_dw_path;
+extern int g_fmha_chunk_path;
 
 }  // namespace ob
 
@@ -71,6 +73,14 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   if (name && std::strcmp(name, "gemm_pairs") == 0) {
     ob::gemm::g_use_pairs = value != 0;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "fmha_chunk_path") == 0) {
+    ob::g_fmha_chunk_path = value != 0;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "dwconv_path") == 0) {
+    ob::g_dw_path = value != 0;
     return OASR_OK;
   }
   return ob::set_error(OASR_ERR_INVALID, "unknown tunable '%s'", name ? name : "(null)");

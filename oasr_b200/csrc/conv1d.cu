@@ -13,6 +13,7 @@
 #include "common.cuh"
 
 namespace ob {
+int g_dw_path = 0;  // 0 = heuristic (register-streaming kernel where it applies); 1 = shared-memory tiled kernel; set through oasr_b200_set_tunable("dwconv_path")
 namespace {
 
 template <typename T>
@@ -304,6 +305,123 @@ int launch_tile(const DwArgs& a, int max_out_len, cudaStream_t s) {
   return check_launch("depthwise_conv1d (tiled) kernel launch");
 }
 
+// Register-streaming form for 16-bit element types (the default fast path): no shared memory and
+// no block-wide barrier.  A thread owns one channel pair; a warp's 32-bit loads of one frame are
+// one coalesced 128-byte request.  All kST + K - 1 frames of a thread's run are requested up front
+// (independent loads), then the K-deep window rotates through statically indexed registers and the
+// taps are packed two-channel fp32 FMAs (fma.rn.f32x2).  Neighbouring tiles re-read the K-1 halo
+// frames from L2.
+constexpr int kST = 32;
+
+template <typename T>
+__device__ __forceinline__ float2 unpack_pair(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack_pair<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <typename T, int K, bool kAffine, bool kAct>
+__global__ void __launch_bounds__(256) dwconv_stream_kernel(DwArgs a) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  const int C = a.channels;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  if (c >= C) return;
+  const int64_t b = blockIdx.z;
+  int64_t in_row0, out_row0;
+  int TL, OL;
+  if (a.cu_seqlens) {
+    const int s0 = a.cu_seqlens[b], s1 = a.cu_seqlens[b + 1];
+    TL = s1 - s0; OL = TL; in_row0 = s0; out_row0 = s0;
+  } else {
+    TL = a.seq_len; OL = a.out_len; in_row0 = b * a.seq_len; out_row0 = b * a.out_len;
+  }
+  const int t0 = blockIdx.x * kST;
+  if (t0 >= OL) return;
+  int fill_end = TL;
+  uint32_t fill = 0;
+  if (a.right_fill) {
+    fill_end = TL + a.fill_frames[b];
+    fill = pack_pair<T>(a.right_fill[c], a.right_fill[c + 1]);
+  }
+  const uint32_t* __restrict__ in = reinterpret_cast<const uint32_t*>(static_cast<const T*>(a.in) + in_row0 * C + c);
+  const int64_t row_u32 = C / 2;
+  const int first = t0 - a.pad_left;
+  constexpr int kRows = kST + K - 1;
+  uint32_t raw[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int ti = first + r;
+    uint32_t v = 0;
+    if (ti >= 0 && ti < TL) v = __ldg(in + ti * row_u32);
+    else if (ti >= TL && ti < fill_end) v = fill;
+    raw[r] = v;
+  }
+  float2 w[K];
+  {
+    const uint32_t* __restrict__ wp = reinterpret_cast<const uint32_t*>(static_cast<const T*>(a.weight) + c);
+#pragma unroll
+    for (int k = 0; k < K; ++k) w[k] = unpack_pair<T>(__ldg(wp + k * row_u32));
+  }
+  float2 bias = make_float2(0.f, 0.f), sc = make_float2(1.f, 1.f), sh = make_float2(0.f, 0.f);
+  if (a.bias) bias = unpack_pair<T>(__ldg(reinterpret_cast<const uint32_t*>(static_cast<const T*>(a.bias) + c)));
+  if constexpr (kAffine) {
+    sc = *reinterpret_cast<const float2*>(a.post_scale + c);
+    sh = *reinterpret_cast<const float2*>(a.post_shift + c);
+  }
+  uint32_t* __restrict__ out = reinterpret_cast<uint32_t*>(static_cast<T*>(a.out) + out_row0 * C + c);
+  float2 x[K];
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) x[k] = unpack_pair<T>(raw[k]);
+#pragma unroll
+  for (int j = 0; j < kST; ++j) {
+    x[(j + K - 1) % K] = unpack_pair<T>(raw[j + K - 1]);
+    float2 acc = bias;
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc = __ffma2_rn(x[(j + k) % K], w[k], acc);
+    if constexpr (kAffine) acc = __ffma2_rn(acc, sc, sh);
+    if constexpr (kAct) {
+      acc.x = apply_act_fast(acc.x, a.act);
+      acc.y = apply_act_fast(acc.y, a.act);
+    }
+    if (t0 + j < OL) out[(t0 + j) * row_u32] = pack_pair<T>(acc.x, acc.y);
+  }
+}
+
+template <typename T, int K>
+int launch_stream(const DwArgs& a, int max_out_len, cudaStream_t s) {
+  if constexpr (sizeof(T) != 2) {
+    return set_error(OASR_ERR_DTYPE, "depthwise_conv1d: streaming kernel is 16-bit only");
+  } else {
+    const int pairs = a.channels / 2;
+    const int threads = pairs >= 256 ? 256 : ((pairs + 31) / 32) * 32;
+    dim3 block(threads);
+    dim3 grid((max_out_len + kST - 1) / kST, (pairs + threads - 1) / threads, static_cast<unsigned>(a.batch));
+    const bool affine = a.post_scale != nullptr;
+    const bool act = a.act != OASR_ACT_NONE;
+    if (affine && act) dwconv_stream_kernel<T, K, true, true><<<grid, block, 0, s>>>(a);
+    else if (affine) dwconv_stream_kernel<T, K, true, false><<<grid, block, 0, s>>>(a);
+    else if (act) dwconv_stream_kernel<T, K, false, true><<<grid, block, 0, s>>>(a);
+    else dwconv_stream_kernel<T, K, false, false><<<grid, block, 0, s>>>(a);
+    return check_launch("depthwise_conv1d (streaming) kernel launch");
+  }
+}
+
 // Any kernel size / channel count, optional mask and add_input
 // (include/oasr/conv/conv1d.cuh:23-113 semantics).  One thread per output element.
 template <typename T>
@@ -364,6 +482,20 @@ int launch_dw(const DwArgs& a, int max_out_len, cudaStream_t s) {
   const bool tiled = fast && (a.channels * sizeof(T)) % 16 == 0 && (a.channels % kCB == 0 || a.channels < kCB) &&
                      is_aligned(a.in, 16) && (max_out_len + kTT - 1) / kTT <= 65535 &&
                      (a.channels + kCB - 1) / kCB <= 65535;
+  const bool stream = fast && sizeof(T) == 2 && is_aligned(a.in, 4) && is_aligned(a.out, 4) && is_aligned(a.weight, 4) &&
+                      (!a.bias || is_aligned(a.bias, 4)) && (!a.post_scale || (is_aligned(a.post_scale, 8) && is_aligned(a.post_shift, 8))) &&
+                      (max_out_len + kST - 1) / kST <= 65535 && a.kernel_size <= 15 && g_dw_path == 0;
+  if (stream) {
+    switch (a.kernel_size) {
+      case 3: return launch_stream<T, 3>(a, max_out_len, s);
+      case 5: return launch_stream<T, 5>(a, max_out_len, s);
+      case 7: return launch_stream<T, 7>(a, max_out_len, s);
+      case 9: return launch_stream<T, 9>(a, max_out_len, s);
+      case 11: return launch_stream<T, 11>(a, max_out_len, s);
+      case 15: return launch_stream<T, 15>(a, max_out_len, s);
+      default: break;
+    }
+  }
   if (tiled) {
     switch (a.kernel_size) {
       case 3: return launch_tile<T, 3>(a, max_out_len, s);

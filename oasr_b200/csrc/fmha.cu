@@ -511,6 +511,13 @@ bool stride_ok(int64_t s) { return s % 8 == 0; }
 
 }  // namespace fmha
 
+namespace fmha_chunk {   // fmha_chunk.cu: warp-per-(stream, head) kernel for <= 16 query frames
+bool applies(int64_t Tq, int64_t block_size, int64_t blocks_per_seq);
+int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos, int64_t pos_rows, int64_t pos_stride,
+        const int32_t* pos_start, const int32_t* block_table, const int32_t* seqlens, int64_t B, int64_t Tq, int64_t H,
+        int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, double scale, int dtype, cudaStream_t stream);
+}  // namespace fmha_chunk
+
 }  // namespace ob
 
 extern "C" {
@@ -567,6 +574,9 @@ int oasr_b200_fmha_paged_relpos(void* out, const void* qkv4, void* k_pool, void*
                  is_aligned(pos, 16) && pos_stride % 8 == 0,
              OASR_ERR_ALIGN, "fmha_paged_relpos: operands must be 16-byte aligned");
   OB_REQUIRE(B <= 65535 && H <= 65535, OASR_ERR_INVALID, "fmha_paged_relpos: batch / head count too large");
+  if (fmha_chunk::applies(Tq, block_size, blocks_per_seq))
+    return fmha_chunk::run(out, qkv4, k_pool, v_pool, pos, pos_rows, pos_stride, pos_start, block_table, seqlens, B, Tq,
+                           H, blocks_per_seq, block_size, num_blocks, scale, dtype, static_cast<cudaStream_t>(stream));
   const int64_t d = H * D, ld = 4 * d;
   const uint8_t* base = static_cast<const uint8_t*>(qkv4);
   Maps maps;

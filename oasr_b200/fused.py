@@ -81,3 +81,25 @@ def subsample_conv1(feats: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
     _lib.call("oasr_b200_subsample_conv1", _p(out), _p(feats), _p(weight.contiguous()), _p(bias.contiguous()),
               _p(t1_limit), B, T, Fd, C, kernel, stride, _DTYPE_ID[out_dtype], _stream(feats))
     return out
+
+
+def fmha_paged_relpos(qkv4: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, pos: torch.Tensor,
+                      pos_start: torch.Tensor, block_table: torch.Tensor, seqlens: torch.Tensor, heads: int,
+                      scale: float, out=None) -> torch.Tensor:
+    """Relative-position attention of the new frames of ``B`` streams over their paged history
+    (RelPositionMultiHeadedAttention.forward_paged, oasr/layers/attention/attention.py:388-470).
+    ``qkv4 (B, Tq, 4*d)`` = ``[q+u | q+v | k | v]`` of the new frames (their k/v already written to the
+    pages); pools ``(num_blocks, block_size, H, 64)``; ``pos (rows, d)`` = ``linear_pos(pe)``;
+    ``pos_start (B,)`` = table row of each stream's key 0; ``seqlens (B,)`` = visible keys including the
+    new frames.  Returns ``(B, Tq, d)``."""
+    _need_cuda(qkv4, k_pool, v_pool, pos, block_table, seqlens, pos_start)
+    B, Tq, d4 = qkv4.shape
+    d = d4 // 4
+    if out is None:
+        out = torch.empty(B, Tq, d, device=qkv4.device, dtype=qkv4.dtype)
+    if not qkv4.is_contiguous() or pos.stride(1) != 1:
+        raise ValueError("qkv4 must be contiguous and pos must have unit stride along the feature axis")
+    _lib.call("oasr_b200_fmha_paged_relpos", _p(out), _p(qkv4), _p(k_pool), _p(v_pool), _p(pos), pos.size(0),
+              pos.stride(0), _p(pos_start), _p(block_table), _p(seqlens), B, Tq, heads, block_table.size(1),
+              k_pool.size(1), k_pool.size(0), float(scale), _DTYPE_ID[qkv4.dtype], _stream(qkv4))
+    return out

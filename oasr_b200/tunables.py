@@ -2,6 +2,9 @@
 
 ``gemm_bn``: 0 lets the heuristic choose the GEMM tile width, 64 / 128 / 256 force it.
 ``gemm_pairs``: 1 runs large dense GEMMs on CTA pairs (tcgen05 cta_group::2), 0 (default) on single-CTA tiles.
+``dwconv_path``: 0 (default) uses the register-streaming depthwise conv kernel where it applies, 1 the shared-memory tiled one.
+``fmha_chunk_path``: 1 (default) runs paged rel-pos attention with <= 16 query frames on the warp-per-(stream, head)
+kernel, 0 always on the 128-row tcgen05 kernel.
 """
 from __future__ import annotations
 

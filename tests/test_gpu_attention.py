@@ -192,3 +192,44 @@ def test_gather_scatter_rows_roundtrip():
     neg = torch.tensor([3, -1, 7], device="cuda")
     g2 = ob.gather_rows(src, neg)
     assert torch.count_nonzero(g2[1]) == 0 and torch.equal(g2[0], src[3])
+
+
+@pytest.mark.parametrize("block_size,Tq,path", [(16, 16, 1), (16, 16, 0), (16, 5, 1), (32, 16, 1), (64, 9, 1)])
+def test_fmha_paged_relpos_matches_fp32_reference(block_size, Tq, path):
+    """Both kernels behind fmha_paged_relpos (warp-per-(stream, head) for <= 16 frames, 128-row tcgen05)
+    against an fp32 torch restatement: random page permutation, ragged history lengths."""
+    from oasr_b200 import fused, tunables
+
+    torch.manual_seed(11)
+    B, H, D, hist = 37, 8, 64, 272
+    d = H * D
+    bps = hist // block_size + 1
+    num_blocks = B * bps + 3
+    dt = torch.bfloat16
+    dev = "cuda"
+    k_pool = torch.randn(num_blocks, block_size, H, D, device=dev, dtype=dt)
+    v_pool = torch.randn(num_blocks, block_size, H, D, device=dev, dtype=dt)
+    table = torch.randperm(num_blocks, device=dev)[: B * bps].view(B, bps).int()
+    seqlens = torch.randint(Tq, hist + 1, (B,), device=dev, dtype=torch.int32)
+    seqlens[0], seqlens[1] = Tq, hist
+    pos_start = torch.randint(0, 3000, (B,), device=dev, dtype=torch.int32)
+    pos = torch.randn(5000, d, device=dev, dtype=dt)
+    qkv4 = (torch.randn(B, Tq, 4 * d, device=dev) * 0.5).to(dt)
+    scale = D ** -0.5
+    tunables.set("fmha_chunk_path", path)
+    try:
+        got = fused.fmha_paged_relpos(qkv4, k_pool, v_pool, pos, pos_start, table, seqlens, H, scale).float()
+    finally:
+        tunables.set("fmha_chunk_path", 1)
+    assert ob.device_status() == 0
+    for b in range(B):
+        n = int(seqlens[b])
+        idx = (table[b].long()[:, None] * block_size + torch.arange(block_size, device=dev)[None]).reshape(-1)[:n]
+        k = k_pool.view(-1, H, D)[idx].float()            # (n, H, D)
+        v = v_pool.view(-1, H, D)[idx].float()
+        pp = pos[int(pos_start[b]): int(pos_start[b]) + n].float().view(n, H, D)
+        qu = qkv4[b, :, :d].float().view(Tq, H, D)
+        qv = qkv4[b, :, d:2 * d].float().view(Tq, H, D)
+        s = (torch.einsum("qhd,khd->hqk", qu, k) + torch.einsum("qhd,khd->hqk", qv, pp)) * scale
+        want = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(Tq, d)
+        assert (got[b] - want).abs().max().item() < 3e-2, (b, n, (got[b] - want).abs().max().item())
