@@ -260,6 +260,30 @@ OASR_API int oasr_b200_subsample_conv1(void* out, const float* in, const float* 
                                        const float* bias, const int32_t* t1_limit /*nullable*/,
                                        int64_t B, int64_t T, int64_t F, int64_t C, int64_t kernel,
                                        int64_t stride, int dtype, void* stream);
+/* The same convolution written in the parity-split layout the second
+ * convolution reads: out (B, ceil(T1/2), 4, ceil(F1/2), C) with plane
+ * (t1 & 1) * 2 + (f1 & 1) and rows (t1 / 2, f1 / 2); 3x3 taps, stride 2 only.
+ * Positions no output frame < t1_limit[b] needs are left unwritten (no
+ * reference counterpart: the reference keeps NHWC between the convolutions,
+ * oasr/models/conformer/model.py:433-449). */
+OASR_API int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const float* weight,
+                                           const float* bias, const int32_t* t1_limit /*nullable*/,
+                                           int64_t B, int64_t T, int64_t F, int64_t C, int dtype,
+                                           void* stream);
+/* Second Conv2d of the subsampling stack (3x3, stride 2, C -> N channels, +
+ * bias + ReLU) as an implicit GEMM on the tensor cores, writing only valid
+ * output frames, already packed: out (total_frames, F2, N) with utterance b's
+ * frames at rows [cu_frames[b], cu_frames[b+1]) (cu_frames: int32[B+1] on the
+ * device), F2 = (F1-3)/2+1.  x1 is the parity-split output of
+ * oasr_b200_subsample_conv1_s2d; w2 is (N, 3, 3, C) = (N, 9*C) row-major (taps
+ * outermost, input channels innermost).  Replaces the second Conv2dActivation
+ * of Conv2dSubsampling (oasr/models/conformer/model.py:445-449, CUTLASS implicit
+ * GEMM include/oasr/conv/conv2d.cuh:78-86) and the pack_hidden gather after it
+ * (oasr/models/conformer/packing.py:204-216). */
+OASR_API int oasr_b200_subsample_conv2(void* out, const void* x1, const void* w2,
+                                       const void* bias /*nullable*/, const int32_t* cu_frames,
+                                       int64_t B, int64_t T1, int64_t F1, int64_t C, int64_t N,
+                                       int64_t total_frames, int dtype, void* stream);
 
 /* ---- GEMM family (tcgen05 / TMEM / TMA) -------------------------------- */
 /* D[M,N] = act(A[M,K] . B[N,K]^T + bias[N]); A, B, D row-major, fp16 or

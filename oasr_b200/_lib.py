@@ -56,6 +56,8 @@ _SIGNATURES = {
     "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
     "oasr_b200_causal_conv1d": [P, P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv1": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
+    "oasr_b200_subsample_conv1_s2d": [P, P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_subsample_conv2": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_gemm": [P, P, P, P, I, I, I, c_int, c_int, P],
     "oasr_b200_gemm_residual_f32": [P, P, P, P, P, I, I, I, c_double, c_int, P],
     "oasr_b200_gemm_glu": [P, P, P, P, I, I, I, c_int, P],

@@ -69,6 +69,101 @@ __global__ void __launch_bounds__(256) subsample_conv1_kernel(Conv1Args a) {
   }
 }
 
+// Fast form for the common 3x3 / stride-2 case.  A block stages the 2R+1 feature frames that R
+// output frames need in shared memory (one coalesced pass), then thread (row r, channel group g)
+// walks the F1 positions of output frame t1_0 + r: the taps come from shared memory as warp
+// broadcasts (two new columns per input row and position, the third is carried over), the 72
+// multiply-adds of its 8 channels are 36 packed fp32x2 FMAs, and the C/8 threads of a position
+// write C*2 contiguous bytes.
+// kS2d selects the output layout: 0 = NHWC (B, T1, F1, C); 1 = parity-split
+// (B, ceil(T1/2), 4, ceil(F1/2)+pad, C) with plane index (t1 & 1) * 2 + (f1 & 1) and rows (t1 / 2,
+// f1 / 2), so that every tap of a following 3x3 / stride-2 convolution reads a dense box.
+template <typename T, bool kS2d>
+__global__ void __launch_bounds__(256) subsample_conv1_k3s2_kernel(Conv1Args a, int rows_per_block, int TH, int FH) {
+  extern __shared__ float xs[];   // (2R+1) x F
+  const int groups = a.C / 8;
+  const int cg = threadIdx.x % groups;
+  const int r = threadIdx.x / groups;
+  const int b = blockIdx.y;
+  const int t1_0 = blockIdx.x * rows_per_block;
+  int t1_end = a.T1;
+  if (a.t1_limit) t1_end = min(t1_end, a.t1_limit[b]);
+  if (t1_0 >= t1_end) return;
+  const int in_rows = min(2 * rows_per_block + 1, a.T - 2 * t1_0);
+  const float* __restrict__ xin = a.in + (static_cast<int64_t>(b) * a.T + 2 * t1_0) * a.F;
+  for (int i = threadIdx.x; i < in_rows * a.F; i += blockDim.x) xs[i] = __ldg(xin + i);
+  const int c0 = cg * 8;
+  float2 w[9][4], bias[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    bias[q] = make_float2(a.bias[c0 + 2 * q], a.bias[c0 + 2 * q + 1]);
+#pragma unroll
+    for (int tap = 0; tap < 9; ++tap)
+      w[tap][q] = make_float2(a.weight[(c0 + 2 * q) * 9 + tap], a.weight[(c0 + 2 * q + 1) * 9 + tap]);
+  }
+  __syncthreads();
+  const int t1 = t1_0 + r;
+  if (r >= rows_per_block || t1 >= t1_end) return;
+  const float* x0 = xs + (2 * r) * a.F;
+  const float* x1 = x0 + a.F;
+  const float* x2 = x1 + a.F;
+  T* out;
+  int64_t pos_stride_even, odd_offset;
+  if constexpr (kS2d) {
+    // plane (t1&1)*2 + fpar of frame pair t1/2; consecutive f1 of equal parity are C apart
+    out = static_cast<T*>(a.out) + ((static_cast<int64_t>(b) * TH + (t1 >> 1)) * 4 + (t1 & 1) * 2) * FH * a.C + c0;
+    pos_stride_even = a.C;
+    odd_offset = static_cast<int64_t>(FH) * a.C;
+  } else {
+    out = static_cast<T*>(a.out) + (static_cast<int64_t>(b) * a.T1 + t1) * a.F1 * a.C + c0;
+    pos_stride_even = 0;
+    odd_offset = 0;
+  }
+  float c00 = x0[0], c10 = x1[0], c20 = x2[0];
+  for (int f1 = 0; f1 < a.F1; ++f1) {
+    const float c01 = x0[2 * f1 + 1], c02 = x0[2 * f1 + 2];
+    const float c11 = x1[2 * f1 + 1], c12 = x1[2 * f1 + 2];
+    const float c21 = x2[2 * f1 + 1], c22 = x2[2 * f1 + 2];
+    const float xv[9] = {c00, c01, c02, c10, c11, c12, c20, c21, c22};
+    float2 acc[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[q] = bias[q];
+#pragma unroll
+    for (int tap = 0; tap < 9; ++tap) {
+      const float2 xx = make_float2(xv[tap], xv[tap]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[q] = __ffma2_rn(xx, w[tap][q], acc[q]);
+    }
+    Pack<T> o;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      o.v[2 * q] = Elem<T>::from_f(fmaxf(acc[q].x, 0.f));
+      o.v[2 * q + 1] = Elem<T>::from_f(fmaxf(acc[q].y, 0.f));
+    }
+    if constexpr (kS2d) st128(out + (f1 & 1) * odd_offset + (f1 >> 1) * pos_stride_even, o);
+    else st128(out + static_cast<int64_t>(f1) * a.C, o);
+    c00 = c02; c10 = c12; c20 = c22;
+  }
+}
+
+template <typename T>
+int launch_k3s2(const Conv1Args& a, bool s2d, cudaStream_t s) {
+  const int groups = a.C / 8;
+  const int R = 256 / groups;
+  const size_t smem = static_cast<size_t>(2 * R + 1) * a.F * sizeof(float);
+  dim3 grid(static_cast<unsigned>((a.T1 + R - 1) / R), static_cast<unsigned>(a.B));
+  const int TH = (a.T1 + 1) / 2, FH = (a.F1 + 1) / 2;
+  if (s2d) subsample_conv1_k3s2_kernel<T, true><<<grid, 256, smem, s>>>(a, R, TH, FH);
+  else subsample_conv1_k3s2_kernel<T, false><<<grid, 256, smem, s>>>(a, R, TH, FH);
+  return check_launch("subsample_conv1 launch");
+}
+
+bool k3s2_applies(const Conv1Args& a) {
+  const int groups = a.C / 8;
+  return a.k == 3 && a.s == 2 && groups >= 1 && groups <= 256 && 256 % groups == 0 &&
+         static_cast<size_t>(2 * (256 / groups) + 1) * a.F * sizeof(float) <= 48 * 1024;
+}
+
 }  // namespace
 }  // namespace ob
 
@@ -90,6 +185,10 @@ int oasr_b200_subsample_conv1(void* out, const float* in, const float* weight, c
   OB_REQUIRE(is_aligned(out, 16), OASR_ERR_ALIGN, "subsample_conv1: out must be 16-byte aligned");
   Conv1Args a{out, in, weight, bias, t1_limit, (int)B, (int)T, (int)F, (int)C,
               (int)((T - kernel) / stride + 1), (int)((F - kernel) / stride + 1), (int)kernel, (int)stride};
+  OB_REQUIRE(B <= 65535, OASR_ERR_INVALID, "subsample_conv1: batch too large");
+  if (k3s2_applies(a)) {
+    return OB_DISPATCH_HALF(dtype, T_, [&]() -> int { return launch_k3s2<T_>(a, false, static_cast<cudaStream_t>(stream)); });
+  }
   const int groups = (int)(C / 8);
   const int block = (256 / groups) * groups;      // whole positions per block
   const int lanes = block / groups;
@@ -107,6 +206,23 @@ int oasr_b200_subsample_conv1(void* out, const float* in, const float* weight, c
     else subsample_conv1_kernel<T_, 5><<<grid, block, 0, s>>>(a);
     return check_launch("subsample_conv1 launch");
   });
+}
+
+int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const float* weight, const float* bias,
+                                  const int32_t* t1_limit, int64_t B, int64_t T, int64_t F, int64_t C, int dtype,
+                                  void* stream) {
+  using namespace ob;
+  OB_REQUIRE(B >= 0 && T >= 3 && F >= 3 && C > 0, OASR_ERR_INVALID, "subsample_conv1_s2d: bad shape");
+  if (B == 0) return OASR_OK;
+  OB_REQUIRE(out && in && weight && bias, OASR_ERR_INVALID, "subsample_conv1_s2d: null pointer argument");
+  OB_REQUIRE(C % 8 == 0 && is_aligned(out, 16), OASR_ERR_ALIGN,
+             "subsample_conv1_s2d: channels must be a multiple of 8 and out 16-byte aligned");
+  OB_REQUIRE(B <= 65535, OASR_ERR_INVALID, "subsample_conv1_s2d: batch too large");
+  Conv1Args a{out, in, weight, bias, t1_limit, (int)B, (int)T, (int)F, (int)C, (int)((T - 3) / 2 + 1),
+              (int)((F - 3) / 2 + 1), 3, 2};
+  OB_REQUIRE(k3s2_applies(a), OASR_ERR_UNSUPPORTED,
+             "subsample_conv1_s2d: channels / 8 must be a power of two <= 256 (got C = %lld)", (long long)C);
+  return OB_DISPATCH_HALF(dtype, T_, [&]() -> int { return launch_k3s2<T_>(a, true, static_cast<cudaStream_t>(stream)); });
 }
 
 }  // extern "C"

@@ -40,7 +40,7 @@ constexpr int UMMA_K = 16;
 constexpr int kEpiWarps = 4;  // per group; store / GLU epilogues run two groups (8 warps)
 
 enum Epi { kEpiStore = 0, kEpiResid = 1, kEpiGlu = 2, kEpiLsm = 3 };
-enum Sched { kSchedDense = 0, kSchedGroup = 1, kSchedSweep = 2 };
+enum Sched { kSchedDense = 0, kSchedGroup = 1, kSchedSweep = 2, kSchedConv = 3 };
 
 struct Params {
   int M, N, K;            // per-problem extents (N = output columns)
@@ -56,6 +56,10 @@ struct Params {
   int out_f32;            // kEpiLsm: 1 = fp32 output, 0 = T output
   int32_t* argmax;        // kEpiLsm: nullable
   uint32_t* status;       // device status word (nullable)
+  // kSchedConv (3x3 / stride-2 convolution as an implicit GEMM over a parity-split NHWC input):
+  int conv_f2;            // output positions per output frame (rows of one frame in a tile)
+  int conv_tpt;           // output frames per 128-row tile = 128 / conv_f2
+  int conv_cblocks;       // input channels / 64
 };
 
 struct Tile {
@@ -125,6 +129,29 @@ struct Scheduler {
         start = end;
       }
       return false;
+    } else if constexpr (kSched == kSchedConv) {
+      // work item = (utterance b, block of conv_tpt output frames, column tile); `offsets` holds the
+      // packed output frame offsets cu[0..groups] (cu[b+1] - cu[b] valid output frames of utterance b)
+      int64_t w = blockIdx.x + static_cast<int64_t>(iter) * gridDim.x;
+      const int n = static_cast<int>(w % p.num_n_tiles);
+      int64_t mt = w / p.num_n_tiles;
+      for (int b = 0; b < p.groups; ++b) {
+        const int lo = p.offsets[b], hi = p.offsets[b + 1];
+        const int frames = hi - lo;
+        const int tiles = (frames + p.conv_tpt - 1) / p.conv_tpt;
+        if (mt < tiles) {
+          const int t0 = static_cast<int>(mt) * p.conv_tpt;
+          t.a_row = t0; t.a_batch = b;
+          t.b_row = n * BN; t.b_batch = 0;
+          t.out_row = static_cast<int64_t>(lo + t0) * p.conv_f2;
+          t.row_end = static_cast<int64_t>(lo + min(t0 + p.conv_tpt, frames)) * p.conv_f2;
+          t.n0 = n * BN;
+          t.pass = 0; t.n_idx = n;
+          return true;
+        }
+        mt -= tiles;
+      }
+      return false;
     } else {
       const int per_row_tile = 2 * p.num_n_tiles;
       const int64_t m = blockIdx.x + static_cast<int64_t>(iter / per_row_tile) * gridDim.x;
@@ -181,7 +208,7 @@ __device__ __forceinline__ void load_bias8(const T* p, float (&f)[8]) {
 // thread stores the tile with TMA (clipped at the tensor edge).  Grouped problems keep per-thread
 // stores because a tile may end inside the tensor (at a group boundary).
 template <int kSched, int kEpi>
-constexpr bool uses_tma_store() { return kSched != kSchedGroup && kEpi != kEpiResid; }
+constexpr bool uses_tma_store() { return kSched != kSchedGroup && kSched != kSchedConv && kEpi != kEpiResid; }
 // Epilogue warp groups (4 warps = all 128 TMEM lanes each).  With a single warp per scheduler the
 // epilogue's load / convert / store chain is latency-bound and slower than the main loop of a
 // K = 512 tile; two groups take alternate 64-column chunks of the accumulator.
@@ -273,6 +300,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
             int b_row = t.b_row;
             if constexpr (kEpi == kEpiGlu) b_row = (cta_rank == 0 ? 0 : p.N) + t.n0 / 2;  // value | gate rows
             ptx::tma_load_3d_pair(sB + stage * S::kBBytes, &tmap_b, kb * BK, b_row, t.b_batch, lead_full);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          if constexpr (kSched == kSchedConv) {
+            // K block kb = (tap, 64-channel block).  Tap (kh, kw) of output (t2, f2) reads input frame
+            // 2*t2 + kh, feature 2*f2 + kw: parity plane (kh&1)*2 + (kw&1), rows (t2 + kh/2, f2 + kw/2) --
+            // one dense box of conv_tpt x conv_f2 rows x 64 channels.  Rows past the box stay stale in
+            // shared memory: they only feed accumulator rows that are never stored.
+            const int tap = kb / p.conv_cblocks, cb = kb - tap * p.conv_cblocks;
+            const int kh = tap / 3, kw = tap - 3 * kh;
+            ptx::mbar_expect_tx(&full_bar[stage], static_cast<uint32_t>(p.conv_tpt * p.conv_f2 * 128) + S::kBBytes);
+            ptx::tma_load_5d(sA + stage * S::kABytes, &tmap_a, cb * BK, kw >> 1, (kh & 1) * 2 + (kw & 1),
+                             t.a_row + (kh >> 1), t.a_batch, &full_bar[stage]);
+            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * BK, t.b_row, t.b_batch, &full_bar[stage]);
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
             continue;
           }
@@ -993,6 +1034,58 @@ int oasr_b200_group_gemm(void* D, const void* A, const void* B, const int32_t* o
   pr.p.offsets = offsets;
   pr.p.D = D; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
   return run<kSchedGroup, kEpiStore>(pr, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_subsample_conv2(void* out, const void* x1, const void* w2, const void* bias, const int32_t* cu_frames,
+                              int64_t B, int64_t T1, int64_t F1, int64_t C, int64_t N, int64_t total_frames, int dtype,
+                              void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  OB_REQUIRE(B >= 0 && T1 >= 3 && F1 >= 3 && C > 0 && N > 0 && total_frames >= 0, OASR_ERR_INVALID,
+             "subsample_conv2: bad shape");
+  if (B == 0 || total_frames == 0) return OASR_OK;
+  OB_REQUIRE(out && x1 && w2 && cu_frames, OASR_ERR_INVALID, "subsample_conv2: null pointer argument");
+  OB_REQUIRE(C % 64 == 0 && N % 8 == 0, OASR_ERR_ALIGN,
+             "subsample_conv2: input channels must be a multiple of 64 and output channels of 8 (got %lld, %lld)",
+             (long long)C, (long long)N);
+  OB_REQUIRE(is_aligned(out, 16) && is_aligned(x1, 16) && is_aligned(w2, 16) && (!bias || is_aligned(bias, 16)),
+             OASR_ERR_ALIGN, "subsample_conv2: operand pointers must be 16-byte aligned");
+  const int64_t F2 = (F1 - 3) / 2 + 1, TH = (T1 + 1) / 2, FH = (F1 + 1) / 2;
+  OB_REQUIRE(F2 >= 1 && F2 <= BM, OASR_ERR_UNSUPPORTED, "subsample_conv2: at most %d output positions per frame", BM);
+  OB_REQUIRE(B < 65536 && total_frames * F2 < (int64_t(1) << 31), OASR_ERR_INVALID, "subsample_conv2: extent too large");
+  const int tpt = static_cast<int>(BM / F2);
+  const int64_t K = 9 * C;
+  Params p{};
+  p.M = static_cast<int>(total_frames * F2); p.N = static_cast<int>(N); p.K = static_cast<int>(K); p.batch = 1;
+  p.groups = static_cast<int>(B); p.offsets = cu_frames;
+  p.D = out; p.bias = bias; p.act = OASR_ACT_RELU; p.alpha = 1.f;
+  p.conv_f2 = static_cast<int>(F2); p.conv_tpt = tpt; p.conv_cblocks = static_cast<int>(C / 64);
+  p.status = device_status_ptr();
+  int bn = N >= 256 ? 256 : (N >= 128 ? 128 : 64);
+  if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) bn = g_force_bn;
+  p.num_m_tiles = 0;
+  p.num_n_tiles = static_cast<int>((N + bn - 1) / bn);
+  p.num_k_blocks = static_cast<int>(K / BK);
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[5] = {(uint64_t)C, (uint64_t)FH, 4, (uint64_t)TH, (uint64_t)B};
+    uint64_t str[5] = {0, (uint64_t)C * 2, (uint64_t)FH * C * 2, (uint64_t)4 * FH * C * 2, (uint64_t)TH * 4 * FH * C * 2};
+    uint32_t box[5] = {BK, (uint32_t)F2, 1, (uint32_t)tpt, 1};
+    if (int rc = make_tensor_map(&ta, tma_dtype(dtype), 5, x1, dims, str, box)) return rc;
+    uint64_t bdims[3] = {(uint64_t)K, (uint64_t)N, 1};
+    uint64_t bstr[3] = {0, (uint64_t)K * 2, (uint64_t)K * 2 * (uint64_t)N};
+    uint32_t bbox[3] = {BK, (uint32_t)bn, 1};
+    if (int rc = make_tensor_map(&tb, tma_dtype(dtype), 3, w2, bdims, bstr, bbox)) return rc;
+  }
+  const int64_t work = (total_frames / tpt + B) * p.num_n_tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+    switch (bn) {
+      case 256: return launch<T, 256, StagesFor<256>::v, kSchedConv, kEpiStore>(ta, tb, ta, p, work, s);
+      case 128: return launch<T, 128, StagesFor<128>::v, kSchedConv, kEpiStore>(ta, tb, ta, p, work, s);
+      default: return launch<T, 64, StagesFor<64>::v, kSchedConv, kEpiStore>(ta, tb, ta, p, work, s);
+    }
+  });
 }
 
 int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B, const void* bias, int64_t M, int64_t N,

@@ -125,11 +125,11 @@ class ConformerCTC:
             return t.to(torch.float32).to(dev).contiguous()
 
         e = "encoder.embed."
-        # Conv2d weights are stored KRSC (NHWC); torch wants KCRS.  channels_last keeps NHWC in memory.
+        # Conv2d weights are stored KRSC (NHWC): exactly the (N, 9*C) K-major operand of the implicit GEMM.
         self.conv1_w = f(P[e + "convs.0.weight"].reshape(d, 3, 3))   # (C, 3, 3, 1) -> (C, 3, 3), fp32
         self.conv1_b = f(P[e + "convs.0.bias"])
-        self.conv2_w = w(P[e + "convs.1.weight"].permute(0, 3, 1, 2)).contiguous(memory_format=torch.channels_last)
         self.conv2_b = w(P[e + "convs.1.bias"])
+        self.conv2_krsc = w(P[e + "convs.1.weight"])                  # (C_out, 3, 3, C_in): taps outermost, channels innermost
         xscale = math.sqrt(d)
         if cfg.embed_layer_norm:
             self.embed_w, self.embed_b = w(P[e + "out.0.weight"]), w(P[e + "out.0.bias"])
@@ -198,18 +198,15 @@ class ConformerCTC:
         return pe
 
     # ------------------------------------------------------------------ front end
-    def _subsample(self, feats: torch.Tensor, t1_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Conv2dSubsampling4 convolutions (model.py:433-449): (B,T,F) -> (B, T', F'*d) rows in
-        NHWC-natural (f, c) order.  The first conv (one input channel) is an own fp32-in kernel;
-        the second still runs through torch/cuDNN in the 16-bit dtype on the NHWC tensor."""
-        # frames of the first conv that only padding would consume are skipped (left uninitialised:
-        # they feed only output frames that are never gathered)
-        x = fused.subsample_conv1(feats.float(), self.conv1_w, self.conv1_b, self.dtype, t1_limit=t1_limit)  # NHWC
-        x = x.permute(0, 3, 1, 2)                       # logical NCHW, channels_last in memory
-        # cuDNN's fused conv + bias + ReLU (one kernel instead of conv, bias add and clamp)
-        x = torch.cudnn_convolution_relu(x, self.conv2_w, self.conv2_b, (2, 2), (0, 0), (1, 1), 1)
-        B, C, T2, F2 = x.shape
-        return x.permute(0, 2, 3, 1).reshape(B, T2, F2 * C)  # a view when x is channels_last
+    def _subsample_packed(self, feats: torch.Tensor, out_lens: List[int], cu_frames: torch.Tensor, total: int,
+                          t1_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Conv2dSubsampling4 convolutions (model.py:433-449) + pack_hidden (packing.py:204-216):
+        ``(B, T, F)`` fp32 features -> ``(total, F' * d)`` packed rows in ``(f, c)`` order, valid frames only.
+        First conv: fp32-in stencil kernel writing the parity-split layout; second conv: tcgen05 implicit GEMM."""
+        B, T, Fd = feats.shape
+        T1, F1 = (T - 3) // 2 + 1, (Fd - 3) // 2 + 1
+        x1 = fused.subsample_conv1_s2d(feats.float(), self.conv1_w, self.conv1_b, self.dtype, t1_limit=t1_limit)
+        return fused.subsample_conv2(x1, T1, F1, self.conv2_krsc, self.conv2_b, cu_frames, total)
 
     # ------------------------------------------------------------------ layer stack
     def _build_native_model(self) -> None:
@@ -328,11 +325,11 @@ class ConformerCTC:
         slots = list(slots)
         B = xs.size(0)
         table, cached, total, pos_start, slot_ids = cache.prepare(slots)
-        conv_rows = self._subsample(xs)                                        # (B, chunk, F'*d)
-        T = conv_rows.size(1)
+        T = (((xs.size(1) - 3) // 2 + 1) - 3) // 2 + 1
         if T != cache.chunk:
             raise RuntimeError(f"the feature window gives {T} encoder frames, the cache was built for {cache.chunk}")
-        rows = conv_rows.reshape(B * T, -1).contiguous()
+        cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=xs.device)
+        rows = self._subsample_packed(xs, [T] * B, cu, B * T)                  # (B * chunk, F'*d)
         lib = _lib.load()
         need = lib.oasr_b200_conformer_chunk_workspace_bytes(ctypes.byref(self._native_model), B, T)
         if self._workspace is None or self._workspace.numel() < need + 256:
@@ -364,14 +361,13 @@ class ConformerCTC:
         Tp = (((T - 3) // 2 + 1) - 3) // 2 + 1
         pk = build_packed_batch(out_lens, Tp, self.cfg.kernel, features.device)
         t1_limit = torch.tensor([2 * n + 1 for n in out_lens], dtype=torch.int32).to(features.device, non_blocking=True)
-        conv_rows = self._subsample(features, t1_limit)                        # (B, Tp, F'*d)
-        B, Tp, W = conv_rows.shape
+        B = features.size(0)
         out_lengths = torch.tensor(out_lens, dtype=torch.int64, device=features.device)
         V = self.cfg.vocab_padded
         if pk.total == 0:
             lp = torch.zeros(B, Tp, V, device=features.device) if padded_output else torch.zeros(0, V, device=features.device)
             return (lp, out_lengths, None, pk) if return_argmax else (lp, out_lengths, pk)
-        rows = gather_rows(conv_rows.reshape(B * Tp, W), pk.pack_src_idx)      # pack_hidden, before the embed Linear
+        rows = self._subsample_packed(features, out_lens, pk.cu_seqlens, pk.total, t1_limit)   # packed before the embed Linear
         log_probs, argmax = self._encode_packed(rows, pk, padded_semantics)
         if padded_output:
             # padded rows carry hidden = 0 in the reference (packing.py:228-232): log_softmax(bias)
@@ -394,20 +390,85 @@ class ConformerCTC:
         lp, ol, pk = self._forward(features, lengths, False, padded_output, False)
         return (lp, ol) if padded_output else (lp, ol, pk)
 
+    @staticmethod
+    def _collapse(ids, seg_lengths) -> List[List[int]]:
+        """Per-frame argmax ids of packed segments -> token lists: drop repeats, then blanks (id 0), never
+        across a segment boundary (rule of csrc/decoder/ctc/cpu/ctc_greedy_search.cc:26-55)."""
+        import numpy as np
+
+        a = np.asarray(ids, dtype=np.int64)
+        if a.size == 0:
+            return [[] for _ in seg_lengths]
+        lens = np.asarray(seg_lengths, dtype=np.int64)
+        ends = np.cumsum(lens)
+        starts = ends - lens
+        prev = np.empty_like(a)
+        prev[1:] = a[:-1]
+        prev[starts[lens > 0]] = -1
+        keep = (a != prev) & (a != 0)
+        csum = np.concatenate([[0], np.cumsum(keep)])
+        counts = csum[ends] - csum[starts]
+        kept = a[keep]
+        out, pos = [], 0
+        for c in counts.tolist():
+            out.append(kept[pos:pos + c].tolist())
+            pos += c
+        return out
+
     def greedy_search(self, features: torch.Tensor, lengths, packed: bool = True) -> List[List[int]]:
-        """Features -> greedy CTC token lists (argmax per frame in the head's epilogue, then drop
-        repeats and blanks; rule of csrc/decoder/ctc/cpu/ctc_greedy_search.cc:26-55)."""
+        """Features -> greedy CTC token lists (argmax per frame in the head's epilogue, collapsed on the host)."""
         _, _, argmax, pk = self._forward(features, lengths, not packed, False, True)
         if argmax is None:
             return [[] for _ in pk.seg_lengths]
-        ids = argmax.cpu().tolist()
-        out, pos = [], 0
-        for n in pk.seg_lengths:
-            hyp, prev = [], None
-            for t in ids[pos:pos + n]:
-                if t != prev and t != 0:
-                    hyp.append(t)
-                prev = t
-            out.append(hyp)
-            pos += n
-        return out
+        return self._collapse(argmax.cpu().numpy(), pk.seg_lengths)
+
+    def greedy_search_batches(self, batches, packed: bool = True):
+        """Pipelined greedy search over an iterable of ``(host_features, lengths)`` batches (pinned host
+        memory for the copies to overlap): the host-to-device copy of batch i+1 runs on a copy stream
+        under the encoder of batch i, and the device-to-host read and token collapse of batch i run
+        under the encoder of batch i+1.  Yields one list of token lists per batch, in order."""
+        dev = self.device
+        main = torch.cuda.current_stream(dev)
+        copy_stream = torch.cuda.Stream(dev)
+        pending = None
+        staged = None
+
+        def stage(item):
+            feats_host, lengths = item
+            with torch.cuda.stream(copy_stream):
+                f = feats_host.to(dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+            return f, lengths, ev
+
+        it = iter(batches)
+        nxt = next(it, None)
+        if nxt is not None:
+            staged = stage(nxt)
+        while staged is not None:
+            f, lengths, ev = staged
+            nxt = next(it, None)
+            staged = stage(nxt) if nxt is not None else None      # next copy goes out before this batch's launches
+            main.wait_event(ev)
+            f.record_stream(main)
+            _, _, argmax, pk = self._forward(f, lengths, not packed, False, True)
+            if argmax is None:
+                cur = (None, pk, None)
+            else:
+                host = torch.empty(argmax.shape, dtype=argmax.dtype, pin_memory=True)
+                host.copy_(argmax, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(main)
+                cur = (host, pk, done)
+            if pending is not None:
+                yield self._finish(pending)
+            pending = cur
+        if pending is not None:
+            yield self._finish(pending)
+
+    def _finish(self, item) -> List[List[int]]:
+        host, pk, done = item
+        if host is None:
+            return [[] for _ in pk.seg_lengths]
+        done.synchronize()
+        return self._collapse(host.numpy(), pk.seg_lengths)

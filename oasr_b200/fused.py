@@ -83,6 +83,41 @@ def subsample_conv1(feats: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
     return out
 
 
+def subsample_conv1_s2d(feats: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out_dtype: torch.dtype,
+                        t1_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First Conv2d (3x3, stride 2) + ReLU written in the parity-split layout ``subsample_conv2`` reads:
+    ``(B, ceil(T1/2), 4, ceil(F1/2), C)``, plane ``(t1 & 1) * 2 + (f1 & 1)``, rows ``(t1 // 2, f1 // 2)``.
+    Positions that no frame below ``t1_limit[b]`` needs stay unwritten."""
+    _need_cuda(feats, weight, bias, t1_limit)
+    if feats.dtype != torch.float32 or weight.dtype != torch.float32 or bias.dtype != torch.float32:
+        raise RuntimeError("subsample_conv1_s2d takes fp32 features, weight and bias")
+    feats = feats.contiguous()
+    B, T, Fd = feats.shape
+    C = weight.size(0)
+    T1, F1 = (T - 3) // 2 + 1, (Fd - 3) // 2 + 1
+    out = torch.empty(B, (T1 + 1) // 2, 4, (F1 + 1) // 2, C, device=feats.device, dtype=out_dtype)
+    _lib.call("oasr_b200_subsample_conv1_s2d", _p(out), _p(feats), _p(weight.contiguous()), _p(bias.contiguous()),
+              _p(t1_limit), B, T, Fd, C, _DTYPE_ID[out_dtype], _stream(feats))
+    return out
+
+
+def subsample_conv2(x1: torch.Tensor, T1: int, F1: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                    cu_frames: torch.Tensor, total_frames: int) -> torch.Tensor:
+    """Second Conv2d (3x3, stride 2) + bias + ReLU of the subsampling stack on the tensor cores, valid
+    output frames only and already packed: ``x1`` from ``subsample_conv1_s2d``; ``weight (N, 3, 3, C)``
+    (taps outermost, input channels innermost); ``cu_frames (B+1,) int32`` packed frame offsets.
+    Returns ``(total_frames, F2 * N)`` rows in ``(f, c)`` order (oasr/models/conformer/model.py:445-449
+    followed by pack_hidden, packing.py:204-216)."""
+    _need_cuda(x1, weight, bias, cu_frames)
+    B, C = x1.size(0), x1.size(-1)
+    N = weight.size(0)
+    F2 = (F1 - 3) // 2 + 1
+    out = torch.empty(total_frames, F2 * N, device=x1.device, dtype=x1.dtype)
+    _lib.call("oasr_b200_subsample_conv2", _p(out), _p(x1), _p(weight), _p(bias), _p(cu_frames), B, T1, F1, C, N,
+              total_frames, _DTYPE_ID[x1.dtype], _stream(x1))
+    return out
+
+
 def fmha_paged_relpos(qkv4: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, pos: torch.Tensor,
                       pos_start: torch.Tensor, block_table: torch.Tensor, seqlens: torch.Tensor, heads: int,
                       scale: float, out=None) -> torch.Tensor:

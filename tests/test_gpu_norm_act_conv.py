@@ -4,6 +4,7 @@ Cases follow the reference's kernel unit tests (tests/test_norm.py,
 tests/test_activation.py, tests/test_conv.py): same shapes families, same
 tolerances or tighter, plus ragged / empty / non-vectorisable extents.
 """
+import numpy as np
 import pytest
 import torch
 
@@ -168,3 +169,42 @@ def test_causal_conv1d_state(dtype, T):
         got = ob.causal_conv1d(x.cuda(), st_gpu, w.cuda(), b.cuda())
         _close(got, want, dtype, scale=2.0)
         assert torch.equal(st_gpu.cpu(), state)  # rolled state is a pure copy: bit-exact
+
+
+@pytest.mark.parametrize("C,lens", [(128, [96, 151, 40]), (512, [403, 67, 1000, 250]), (256, [67] * 5)])
+def test_subsampling_front_end_matches_torch_conv2d(C, lens):
+    """conv1 (fp32 stencil, parity-split layout) + conv2 (tcgen05 implicit GEMM, packed valid frames)
+    against torch conv2d + ReLU in fp32 on the same 16-bit-rounded weights and intermediate."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(5)
+    B, T, F = len(lens), max(lens), 80
+    feats = torch.randn(B, T, F, device="cuda")
+    w1 = torch.randn(C, 3, 3, device="cuda") * 0.3
+    b1 = torch.randn(C, device="cuda") * 0.1
+    w2 = (torch.randn(C, 3, 3, C, device="cuda") * (9 * C) ** -0.5).bfloat16()
+    b2 = (torch.randn(C, device="cuda") * 0.1).bfloat16()
+    out_lens = [(n - 3) // 4 for n in lens]
+    cu = torch.tensor([0] + list(np.cumsum(out_lens)), dtype=torch.int32, device="cuda")
+    total = int(cu[-1])
+    t1_limit = torch.tensor([2 * n + 1 for n in out_lens], dtype=torch.int32, device="cuda")
+    T1, F1 = (T - 3) // 2 + 1, (F - 3) // 2 + 1
+    x1 = fused.subsample_conv1_s2d(feats, w1, b1, torch.bfloat16, t1_limit=t1_limit)
+    got = fused.subsample_conv2(x1, T1, F1, w2, b2, cu, total).float()
+    assert ob.device_status() == 0
+    # reference
+    y1 = torch.relu(torch.nn.functional.conv2d(feats[:, None], w1[:, None], b1, stride=2)).bfloat16().float()  # (B,C,T1,F1)
+    # conv1 against the NHWC kernel and the parity-split layout
+    nhwc = fused.subsample_conv1(feats, w1, b1, torch.bfloat16).float()
+    assert (nhwc - y1.permute(0, 2, 3, 1)).abs().max().item() < 2e-2
+    for b, n in enumerate(out_lens):
+        lim = 2 * n + 1
+        t1 = torch.arange(lim, device="cuda")
+        f1 = torch.arange(F1, device="cuda")
+        plane = (t1[:, None] & 1) * 2 + (f1[None] & 1)
+        s2d = x1[b][t1[:, None] // 2, plane, f1[None] // 2].float()             # (lim, F1, C)
+        assert torch.equal(s2d, nhwc[b, :lim])
+    y2 = torch.relu(torch.nn.functional.conv2d(y1, w2.float().permute(0, 3, 1, 2), b2.float(), stride=2))      # (B,C,T2,F2)
+    want = torch.cat([y2[b, :, :n].permute(1, 2, 0).reshape(n, -1) for b, n in enumerate(out_lens)])
+    err = (got - want).abs().max().item()
+    assert err < 3e-2, err

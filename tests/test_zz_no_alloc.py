@@ -12,7 +12,6 @@ import pytest
 import torch
 
 from oasr_b200 import _lib
-from oasr_b200.cache import gather_rows
 from oasr_b200.encoder import ConformerCTC, ConformerConfig, build_packed_batch
 from oasr_b200.weights import init_params
 
@@ -28,9 +27,7 @@ def _setup():
     T = feats.size(1)
     Tp = (((T - 3) // 2 + 1) - 3) // 2 + 1
     pk = build_packed_batch(out_lens, Tp, cfg.kernel, feats.device)
-    conv_rows = model._subsample(feats)
-    B, Tp2, W = conv_rows.shape
-    rows = gather_rows(conv_rows.reshape(B * Tp2, W), pk.pack_src_idx)
+    rows = model._subsample_packed(feats, out_lens, pk.cu_seqlens, pk.total)
     return cfg, model, pk, rows
 
 
