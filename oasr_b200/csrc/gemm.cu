@@ -76,6 +76,21 @@ struct Scheduler {
   const Params& p;
   uint32_t rank = 0;  // CTA rank inside a pair (kCtas == 2)
   __device__ explicit Scheduler(const Params& p_) : p(p_) {}
+  // Does this CTA have an iter-th work item?  The MMA issuer needs nothing else from the scheduler,
+  // and a tile boundary is where a stalled issuer starves the tensor pipe.
+  __device__ bool has(int iter) const {
+    if constexpr (kSched == kSchedDense) {
+      const uint32_t ctas = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
+      const uint32_t first = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+      const uint32_t total = static_cast<uint32_t>(p.num_m_tiles) * p.num_n_tiles * p.batch;
+      return first + static_cast<uint32_t>(iter) * ctas < total;
+    } else if constexpr (kSched == kSchedSweep) {
+      return blockIdx.x + static_cast<uint32_t>(iter / (2 * p.num_n_tiles)) * gridDim.x < static_cast<uint32_t>(p.num_m_tiles);
+    } else {
+      Tile t;
+      return get(iter, t);
+    }
+  }
   // iter-th work item of this CTA; false when the CTA has no more work.
   __device__ bool get(int iter, Tile& t) const {
     if constexpr (kSched == kSchedDense && kCtas == 2) {
@@ -95,10 +110,11 @@ struct Scheduler {
       t.pass = 0; t.n_idx = n;
       return true;
     } else if constexpr (kSched == kSchedDense) {
-      const int64_t per_batch = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
-      const int64_t w = blockIdx.x + static_cast<int64_t>(iter) * gridDim.x;
+      // tile counts fit 32 bits (the host checks); 64-bit divisions here would sit on every role's tile boundary
+      const uint32_t per_batch = static_cast<uint32_t>(p.num_m_tiles) * p.num_n_tiles;
+      const uint32_t w = blockIdx.x + static_cast<uint32_t>(iter) * gridDim.x;
       if (w >= per_batch * p.batch) return false;
-      const int b = static_cast<int>(w / per_batch);
+      const int b = p.batch == 1 ? 0 : static_cast<int>(w / per_batch);
       const int r = static_cast<int>(w - b * per_batch);
       const int m = r / p.num_n_tiles, n = r - m * p.num_n_tiles;
       t.a_row = m * BM; t.a_batch = b;
@@ -338,9 +354,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
     if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      Tile t;
       bool ok = true;
-      for (int iter = 0; ok && sched.get(iter, t); ++iter) {
+      for (int iter = 0; ok && sched.has(iter); ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1u;
         if (!ptx::mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -385,14 +400,33 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
     // alternates between the two buffers.
     const int grp = (warp - 2) >> 2;
     uint8_t* stage_out = smem + S::kStageOut;
-    int out_buf = kGroups == 2 ? grp : 0;
+    int out_buf = 0;
     const bool issuer = ((warp - 2) & 3) == 0 && lane == 0;
     const int tile_row = q * 32 + lane;
-    auto stage_and_store = [&](const uint32_t (&w)[32], int col, const Tile& tt) {
-      if (issuer) {  // the store that last used this buffer has finished reading it
-        if constexpr (kGroups == 2) ptx::bulk_wait_group_read<0>();
-        else ptx::bulk_wait_group_read<1>();
+    // Two-group form: every warp stages and stores its own 32 rows, so no barrier couples the warps and their
+    // load / convert / store chains overlap.  A warp owns two 32-row x 64-byte buffers (64-byte swizzle); a unit
+    // of 32 output columns goes out per store, and a buffer is rewritten only after the store before the most
+    // recent one has finished reading it.
+    auto stage32_and_store = [&](const uint32_t* w16, int col, const Tile& tt) {
+      if (lane == 0) ptx::bulk_wait_group_read<1>();
+      __syncwarp();
+      uint8_t* buf = stage_out + ((warp - 2) * 2 + out_buf) * 2048;
+      uint8_t* row = buf + lane * 64;
+      const int swz = (lane >> 1) & 3;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(row + ((c ^ swz) << 4)) = make_uint4(w16[4 * c], w16[4 * c + 1], w16[4 * c + 2], w16[4 * c + 3]);
       }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && tt.a_row + q * 32 < p.M) {
+        ptx::tma_store_3d(&tmap_d, buf, col, tt.a_row + q * 32, tt.a_batch);
+        ptx::bulk_commit_group();
+      }
+      out_buf ^= 1;
+    };
+    auto stage_and_store = [&](const uint32_t (&w)[32], int col, const Tile& tt) {
+      if (issuer) ptx::bulk_wait_group_read<1>();  // the store that last used this buffer has finished reading it
       ptx::named_barrier_sync(1 + grp, kEpiWarps * 32);
       uint8_t* row = stage_out + out_buf * S::kOutBytes + tile_row * 128;
 #pragma unroll
@@ -405,11 +439,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         ptx::tma_store_3d(&tmap_d, stage_out + out_buf * S::kOutBytes, col, tt.a_row, tt.a_batch);
         ptx::bulk_commit_group();
       }
-      if constexpr (kGroups == 1) out_buf ^= 1;
+      out_buf ^= 1;
     };
     // 32 accumulator columns -> 16 packed words of `w` (kHalf = which half), bias and activation in fp32
-    auto finish32 = [&](const uint32_t (&r)[32], uint32_t (&w)[32], auto half_c, int col0, const T* bias) {
+    // act_c: 0 = none, 1 = swish, 2 = any other id (run-time switch).  Compile-time so that the instructions a
+    // tile executes are contiguous: with the switch inlined per element, the never-taken activations sit between
+    // the executed instructions and the loop runs at the speed of instruction fetch.
+    auto finish32 = [&](const uint32_t (&r)[32], uint32_t (&w)[32], auto half_c, auto act_c, int col0, const T* bias) {
       constexpr int kHalf = decltype(half_c)::value;
+      constexpr int kAct = decltype(act_c)::value;
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) {
         const int col = col0 + g8 * 8;
@@ -422,10 +460,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] += bb[i];
         }
-        if (p.act == OASR_ACT_SWISH) {
+        if constexpr (kAct == 1) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = swish_fast(v[i]);
-        } else if (p.act != OASR_ACT_NONE) {
+        } else if constexpr (kAct == 2) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
         }
@@ -447,21 +485,31 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         // columns is always in flight while the current 32 are converted
         const T* bias = static_cast<const T*>(p.bias);
         const int nchunks = (min(BN, p.N - t.n0) + 63) / 64;
-        uint32_t ra[32], rb[32], w[32];
-        int ci = grp;
-        if (ci < nchunks) ptx::tmem_ld_32x32(t_acc + ci * 64, ra);
+        // one 64-column TMEM load per chunk; the next chunk's load is issued as soon as this chunk has been
+        // converted, under the staging and the stores
+        auto store_tile = [&](auto act_c) {
+          uint32_t r[64], w[32];
+          int ci = grp;
+          if (ci < nchunks) ptx::tmem_ld_32x64(t_acc + ci * 64, r);
 #pragma unroll 1
-        for (; ci < nchunks; ci += kGroups) {
-          const int c0 = ci * 64;
+          for (; ci < nchunks; ci += kGroups) {
+            const int c0 = ci * 64;
+            ptx::tmem_ld_wait();
+            finish32(reinterpret_cast<const uint32_t(&)[32]>(r[0]), w, std::integral_constant<int, 0>{}, act_c, t.n0 + c0, bias);
+            finish32(reinterpret_cast<const uint32_t(&)[32]>(r[32]), w, std::integral_constant<int, 1>{}, act_c, t.n0 + c0 + 32, bias);
+            if (ci + kGroups < nchunks) ptx::tmem_ld_32x64(t_acc + (ci + kGroups) * 64, r);
+            if constexpr (kGroups == 2) {
+              stage32_and_store(w, t.n0 + c0, t);
+              if (t.n0 + c0 + 32 < p.N) stage32_and_store(w + 16, t.n0 + c0 + 32, t);
+            } else {
+              stage_and_store(w, t.n0 + c0, t);
+            }
+          }
           ptx::tmem_ld_wait();
-          ptx::tmem_ld_32x32(t_acc + c0 + 32, rb);
-          finish32(ra, w, std::integral_constant<int, 0>{}, t.n0 + c0, bias);
-          ptx::tmem_ld_wait();
-          if (ci + kGroups < nchunks) ptx::tmem_ld_32x32(t_acc + (ci + kGroups) * 64, ra);
-          finish32(rb, w, std::integral_constant<int, 1>{}, t.n0 + c0 + 32, bias);
-          stage_and_store(w, t.n0 + c0, t);
-        }
-        ptx::tmem_ld_wait();
+        };
+        if (p.act == OASR_ACT_NONE) store_tile(std::integral_constant<int, 0>{});
+        else if (p.act == OASR_ACT_SWISH) store_tile(std::integral_constant<int, 1>{});
+        else store_tile(std::integral_constant<int, 2>{});
       } else if constexpr (kEpi == kEpiStore) {
         T* drow = static_cast<T*>(p.D) + row * p.N;
         const T* bias = static_cast<const T*>(p.bias);
@@ -485,8 +533,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
                 for (int i = 0; i < 8; ++i) v[i] += bb[i];
               }
               if (p.act != OASR_ACT_NONE) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
+      #pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = apply_act_fast(v[i], p.act);
               }
               if (row_ok) {
                 uint4 o;
@@ -569,8 +617,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
 #pragma unroll
               for (int i = 0; i < 4; ++i) w[half * 16 + g * 4 + i] = pack2<T>(v[2 * i], v[2 * i + 1]);
             }
+            if constexpr (kGroups == 2) {
+              if (n0 + c0 + half * 32 < p.N) stage32_and_store(w + half * 16, n0 + c0 + half * 32, t);
+            }
           }
-          stage_and_store(w, n0 + c0, t);
+          if constexpr (kGroups == 1) stage_and_store(w, n0 + c0, t);
         }
       } else if constexpr (kEpi == kEpiGlu) {
         // accumulator columns [0, BN/2) hold the value half, [BN/2, BN) the gate half
@@ -700,7 +751,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         else ptx::mbar_arrive(&tempty_bar[acc]);
       }
     }
-    if (kTmaStore && issuer) ptx::bulk_wait_group<0>();  // all output tiles have left shared memory and landed
+    if (kTmaStore && (kGroups == 2 ? lane == 0 : issuer)) ptx::bulk_wait_group<0>();  // all output tiles have left shared memory and landed
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusGemmEpilogue);
   }
 
@@ -881,8 +932,10 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
     const uint64_t es = f32 ? 4 : 2;
     uint64_t ddims[3] = {(uint64_t)pr.N, (uint64_t)pr.M, (uint64_t)(kSched == kSchedDense ? pr.batch : 1)};
     uint64_t dstr[3] = {0, (uint64_t)pr.N * es, (uint64_t)pr.N * es * (uint64_t)pr.M};
-    uint32_t dbox[3] = {f32 ? 32u : 64u, BM, 1};
-    if (int rc = make_tensor_map(&td, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : tma_dtype(dtype), 3, p.D, ddims, dstr, dbox))
+    constexpr bool kHalfUnits = epi_groups<kSched, kEpi>() == 2;   // 32-column stores from 64-byte-swizzled staging
+    uint32_t dbox[3] = {(f32 || kHalfUnits) ? 32u : 64u, kHalfUnits ? 32u : (uint32_t)BM, 1};  // two-group epilogues store per warp
+    if (int rc = make_tensor_map(&td, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : tma_dtype(dtype), 3, p.D, ddims, dstr, dbox,
+                                 kHalfUnits ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   } else {
     td = ta;
@@ -890,6 +943,7 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
   int64_t work;
   if (kSched == kSchedSweep) work = p.num_m_tiles;
   else work = m_tiles_total * p.num_n_tiles;
+  OB_REQUIRE(work < (int64_t(1) << 31), OASR_ERR_INVALID, "gemm: too many output tiles (%lld)", (long long)work);
   if constexpr (kPairCapable) {
     if (pair) return launch_pair<T, kEpi>(ta, tb, td, p, static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles * pr.batch, s);
   }
