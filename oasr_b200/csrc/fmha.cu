@@ -99,7 +99,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-template <typename T, int D, int kAtoms>
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// kGeneral = false: no bias, no causal mask, no key start -- the only mask is key < kv_len (the packed
+// relative-position path and plain attention).  The softmax then never writes scores back to TMEM and the
+// code a tile executes stays small.
+template <typename T, int D, int kAtoms, bool kGeneral>
 __global__ void __launch_bounds__(kThreads, 1)
 fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
   using S = Smem<D, kAtoms>;
@@ -365,11 +374,69 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
       if (!ptx::mbar_wait(&s_full[b], ph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t t_s = tmem_base + lane_base + kColS + b * BKV;
+      float tile_max = kNegInf, m_new, m_use, alpha, row_sum = 0.f;
+      uint8_t* p_tile = sP + b * 2 * kAtomBytes;
+      // keys c0..c0+31 of row r: atom c0/64, 16-byte chunks (c0%64)/8 .. +3, XOR-swizzled by r%8
+      auto write_p = [&](const uint32_t (&packed)[16], int c0) {
+        uint8_t* row_base = p_tile + (c0 / 64) * kAtomBytes + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((c0 % 64) / 8 + q4) ^ (r & 7);
+          *reinterpret_cast<uint4*>(row_base + chunk * 16) =
+              make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+        }
+      };
+      if constexpr (!kGeneral) {
+        // ---- pass 1: row max of the raw scores; 32-key blocks that end inside the valid keys need no mask ----
+#pragma unroll 1
+        for (int c0 = 0; c0 < BKV; c0 += 32) {
+          if (key0 + c0 >= kv_len) break;
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(t_s + c0, v);
+          ptx::tmem_ld_wait();
+          if (key0 + c0 + 32 <= kv_len) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, key0 + c0 + i < kv_len ? __uint_as_float(v[i]) : kNegInf);
+          }
+        }
+        tile_max *= p.scale_log2;   // the scale is positive
+        m_new = fmaxf(m_run, tile_max);
+        m_use = (m_new == kNegInf) ? 0.f : m_new;  // empty-row clamp
+        alpha = (m_run == kNegInf) ? 0.f : ex2_fast(m_run - m_use);
+        // ---- pass 2: exponentiate, sum, round, write P (K-major, 128-byte swizzle) ----
+#pragma unroll 1
+        for (int c0 = 0; c0 < BKV; c0 += 32) {
+          uint32_t packed[16];
+          if (key0 + c0 >= kv_len) {   // P of keys past the end is zero (V rows there may hold anything finite)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) packed[i] = 0u;
+          } else {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(t_s + c0, v);
+            ptx::tmem_ld_wait();
+            const bool full = key0 + c0 + 32 <= kv_len;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float p0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+              float p1 = ex2_fast(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+              if (!full) {
+                p0 = key0 + c0 + i < kv_len ? p0 : 0.f;
+                p1 = key0 + c0 + i + 1 < kv_len ? p1 : 0.f;
+              }
+              row_sum += p0 + p1;
+              packed[i / 2] = pack2<T>(p0, p1);
+            }
+          }
+          write_p(packed, c0);
+        }
+      } else {
       // ---- pass 1: row max.  Interior tiles without a bias need no mask and no write-back: the max of
       // the raw scores is taken and the (positive) scale applied in pass 2.  Edge tiles and biased tiles
       // get scale, bias and masks applied here (log2 domain) and written back to TMEM. ----
       const bool plain_tile = !bias_row && !p.causal && key0 + BKV <= kv_len && key0 >= kv_start;
-      float tile_max = kNegInf;
       if (plain_tile) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BKV; c0 += 32) {
@@ -400,14 +467,12 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
         }
         ptx::tmem_st_wait();
       }
-      const float m_new = fmaxf(m_run, tile_max);
-      const float m_use = (m_new == kNegInf) ? 0.f : m_new;  // empty-row clamp
-      const float alpha = (m_run == kNegInf) ? 0.f : exp2f(m_run - m_use);
+      m_new = fmaxf(m_run, tile_max);
+      m_use = (m_new == kNegInf) ? 0.f : m_new;  // empty-row clamp
+      alpha = (m_run == kNegInf) ? 0.f : exp2f(m_run - m_use);
       const float pscale = plain_tile ? p.scale_log2 : 1.f;   // pass 2 computes exp2(x * pscale - m_use)
       // ---- pass 2: exponentiate, sum, round, write P (K-major, 128-byte swizzle) ----
       // P[b] is free: this thread folded O of tile j-2 (po_done[b]) in the previous iteration.
-      float row_sum = 0.f;
-      uint8_t* p_tile = sP + b * 2 * kAtomBytes;
 #pragma unroll 1
       for (int c0 = 0; c0 < BKV; c0 += 32) {
         uint32_t v[32];
@@ -421,14 +486,8 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
           row_sum += p0 + p1;
           packed[i / 2] = pack2<T>(p0, p1);
         }
-        // keys c0..c0+31 of row r: atom c0/64, 16-byte chunks (c0%64)/8 .. +3, XOR-swizzled by r%8
-        uint8_t* row_base = p_tile + (c0 / 64) * kAtomBytes + r * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c0 % 64) / 8 + q4) ^ (r & 7);
-          *reinterpret_cast<uint4*>(row_base + chunk * 16) =
-              make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-        }
+        write_p(packed, c0);
+      }
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s_free[b]);
@@ -482,10 +541,10 @@ int make_map(CUtensorMap* m, int dtype, const void* base, int D, int64_t rows, i
   return make_tensor_map(m, tma_dtype(dtype), 4, base, dims, str, box);
 }
 
-template <typename T, int D, int kAtoms>
-int launch(const Maps& maps, const Params& p, dim3 grid, cudaStream_t s) {
+template <typename T, int D, int kAtoms, bool kGeneral>
+int launch_k(const Maps& maps, const Params& p, dim3 grid, cudaStream_t s) {
   using S = Smem<D, kAtoms>;
-  auto kern = fmha_tcgen05_kernel<T, D, kAtoms>;
+  auto kern = fmha_tcgen05_kernel<T, D, kAtoms, kGeneral>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
@@ -496,6 +555,12 @@ int launch(const Maps& maps, const Params& p, dim3 grid, cudaStream_t s) {
   }
   kern<<<grid, kThreads, S::kDynamic, s>>>(maps, p);
   return check_launch("fmha launch");
+}
+
+template <typename T, int D, int kAtoms>
+int launch(const Maps& maps, const Params& p, dim3 grid, cudaStream_t s) {
+  const bool general = p.bias != nullptr || p.causal || p.seqstarts != nullptr;
+  return general ? launch_k<T, D, kAtoms, true>(maps, p, grid, s) : launch_k<T, D, kAtoms, false>(maps, p, grid, s);
 }
 
 int dispatch(const Maps& maps, const Params& p, int D, int dtype, dim3 grid, cudaStream_t s) {
