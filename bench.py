@@ -395,6 +395,7 @@ def main():
 
     if rank == 0:
         per = instrumented_step(device_step)
+        pk_rows = sum(max((n - 3) // 4, 0) for n in lengths)
         peaks = measured_peaks()
         gemm = {"launches": 0, "ms": 0.0, "flops": 0.0}
         for k, v in per.items():
@@ -407,7 +408,12 @@ def main():
             "kernel": "gemm_tcgen05_kernel (all gemm / gemm_glu launches of one step of the layer stack)",
             "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
             "frac": achieved / peaks["bf16_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
-            "traffic": None, "launches": gemm["launches"], "share_of_step": gemm["ms"] / step_total if step_total else None,
+            # DRAM bytes of ONE FFN w_1 launch (M x 2048 x 512, the launch type with the largest share): operand reads
+            # scaled from the reduced-case ncu capture under profiles/ (A grows with M, B is constant: every operand
+            # byte is read once), plus the output bytes, which the reduced case cannot show (its output stays in L2)
+            "traffic": int(2 * (pk_rows * 512 + 2048 * 512 + pk_rows * 2048)) if args.layers else None,
+            "traffic_of": "one FFN w_1 launch; reads scaled from the ncu reduced case, writes = output size",
+            "launches": gemm["launches"], "share_of_step": gemm["ms"] / step_total if step_total else None,
         }
         kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
                        **({"tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 1)} if v["flops"] and v["ms"] else {})}
