@@ -294,6 +294,25 @@ OASR_API int oasr_b200_subsample_conv2(void* out, const void* x1, const void* w2
 OASR_API int oasr_b200_gemm(void* D, const void* A, const void* B, const void* bias /*nullable*/,
                             int64_t M, int64_t N, int64_t K, int activation, int dtype,
                             void* stream);
+/* 8-bit operand kinds of the GEMM (no reference counterpart: the reference has no quantised path,
+ * oasr/layers/linear.py:7 only names a future one).  D (M,N) 16-bit =
+ * act( (A_q . B_q^T) * a_scale[m] * b_scale[n] + bias[n] ), A_q (M,K) and B_q (N,K) one byte per
+ * element: kind OASR_Q8_FP8_E4M3 = fp8 e4m3 operands with fp32 accumulation (tcgen05 kind::f8f6f4),
+ * OASR_Q8_INT8 = signed int8 operands with int32 accumulation (kind::i8).  a_scale fp32[M] per
+ * token, b_scale fp32[N] per output channel.  glu != 0: B_q has 2N rows (value | gate), b_scale
+ * and bias 2N entries, D = value * sigmoid(gate).  K % 16 == 0, N % 8 == 0. */
+#define OASR_Q8_FP8_E4M3 1
+#define OASR_Q8_INT8 2
+OASR_API int oasr_b200_gemm_q8(void* D, const void* A_q, const float* a_scale, const void* B_q,
+                               const float* b_scale, const void* bias /*nullable, 16-bit*/,
+                               int64_t M, int64_t N, int64_t K, int activation, int glu, int kind,
+                               int out_dtype, void* stream);
+/* Row-wise dynamic quantisation: q (rows, cols) one byte per element and scale fp32[rows] with
+ * x ~ q * scale; scale = amax(row) / 448 (fp8 e4m3, round to nearest, saturating) or amax / 127
+ * (int8, round to nearest).  x 16-bit, cols % 16 == 0.  Used per token on activations and per
+ * output channel on weights (no reference counterpart). */
+OASR_API int oasr_b200_quantize_rows(void* q, float* scale, const void* x, int64_t rows, int64_t cols,
+                                     int kind, int dtype, void* stream);
 /* Residual form used by the fused encoder layer (no reference counterpart as
  * an operator; it is the reference's `residual + alpha * Linear(x)` pair,
  * oasr/models/conformer/model.py:722-751, with the sum kept in fp32):
@@ -460,6 +479,11 @@ typedef struct oasr_b200_conformer_layer {
   const void *norm_ff_w, *norm_ff_b;
   const void *ff_w1, *ff_b1, *ff_w2, *ff_b2;       /* feed_forward */
   const void *norm_final_w, *norm_final_b;
+  /* 8-bit copies of the eight Linear weights (one byte per element, same shapes) and their fp32
+   * per-output-channel scales, in the order ffm_w1, ffm_w2, qkv4, out, pw1, pw2, ff_w1, ff_w2;
+   * read only when the model's quant_kind is not 0 (no reference counterpart). */
+  const void* q_w[8];
+  const float* q_s[8];
 } oasr_b200_conformer_layer;
 
 typedef struct oasr_b200_conformer_model {
@@ -475,6 +499,9 @@ typedef struct oasr_b200_conformer_model {
   const void *ctc_w, *ctc_b;                 /* (vocab_padded, 3d) split head weight, (vocab_padded) bias */
   const void *pos_proj;                      /* nullable: (pos_proj_rows, num_layers*d) = pe . pos_w_all^T, streaming */
   int64_t pos_proj_rows;
+  int32_t quant_kind;                        /* 0 = 16-bit GEMMs; OASR_Q8_FP8_E4M3 / OASR_Q8_INT8: the eight Linear GEMMs of every
+                                                layer run on 8-bit operands, activations quantised per token on the fly
+                                                (offline entry point only) */
 } oasr_b200_conformer_model;
 
 /* Bytes of device scratch oasr_b200_conformer_encode_packed needs for `total`

@@ -55,6 +55,8 @@ _SIGNATURES = {
     "oasr_b200_swish": [P, P, I, c_int, P],
     "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
     "oasr_b200_causal_conv1d": [P, P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_gemm_q8": [P, P, P, P, P, P, I, I, I, c_int, c_int, c_int, c_int, P],
+    "oasr_b200_quantize_rows": [P, P, P, I, I, c_int, c_int, P],
     "oasr_b200_subsample_conv1": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv1_s2d": [P, P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv2": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
@@ -81,7 +83,7 @@ class ConformerLayer(ctypes.Structure):
         "norm_ff_macaron_w", "norm_ff_macaron_b", "ffm_w1", "ffm_b1", "ffm_w2", "ffm_b2", "norm_mha_w", "norm_mha_b",
         "qkv4_w", "qkv4_b", "out_w", "out_b", "norm_conv_scale", "norm_conv_shift", "pw1_w", "pw1_b", "dw_w", "dw_b",
         "conv_bn_scale", "conv_bn_shift", "glu_of_bias", "pw2_w", "pw2_b", "norm_ff_w", "norm_ff_b", "ff_w1", "ff_b1",
-        "ff_w2", "ff_b2", "norm_final_w", "norm_final_b")]
+        "ff_w2", "ff_b2", "norm_final_w", "norm_final_b")] + [("q_w", c_void_p * 8), ("q_s", c_void_p * 8)]
 
 
 class ConformerModel(ctypes.Structure):
@@ -93,7 +95,7 @@ class ConformerModel(ctypes.Structure):
         ("embed_w", c_void_p), ("embed_b", c_void_p), ("embed_ln_w", c_void_p), ("embed_ln_b", c_void_p),
         ("pos_w_all", c_void_p), ("pe", c_void_p), ("pe_rows", c_int64),
         ("after_norm_w", c_void_p), ("after_norm_b", c_void_p), ("ctc_w", c_void_p), ("ctc_b", c_void_p),
-        ("pos_proj", c_void_p), ("pos_proj_rows", c_int64)]
+        ("pos_proj", c_void_p), ("pos_proj_rows", c_int64), ("quant_kind", ctypes.c_int32)]
 
 
 _SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, I, P, P, P]

@@ -22,6 +22,8 @@ struct Workspace {
   uint8_t* cv;     // (M, d)
   uint8_t* h3;     // (M, 3d)  after_norm as [hi | hi | lo]
   uint8_t* pos;    // (max_seg, L*d)
+  uint8_t* q8;     // (M, max(ffn, d)) one byte per element: per-token quantised GEMM input (quant_kind != 0)
+  float* qs;       // (M) its scales
   int64_t bytes;
 };
 
@@ -98,6 +100,10 @@ Workspace carve(const oasr_b200_conformer_model& m, int64_t M, int64_t max_seg, 
   w.cv = take(M * d * 2);
   w.h3 = take(M * 3 * d * 2);
   w.pos = take(max_seg * m.num_layers * d * 2);
+  if (m.quant_kind != 0) {
+    w.q8 = take(M * (m.ffn > d ? m.ffn : d));
+    w.qs = reinterpret_cast<float*>(take(M * 4));
+  }
   w.bytes = off;
   return w;
 }
@@ -175,6 +181,20 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   const oasr_b200_conformer_layer* ly = m.layers;
 
   // embed Linear (+ LayerNorm with sqrt(d) folded) -> fp32 residual, and the first pre-norm
+  // One Linear of the layer stack: 16-bit GEMM, or per-token quantisation of the input followed by the 8-bit GEMM
+  // on the pre-quantised weight `qi` of the layer (order of oasr_b200_conformer_layer::q_w).
+  const int qk = m.quant_kind;
+  OB_REQUIRE(qk == 0 || qk == OASR_Q8_FP8_E4M3 || qk == OASR_Q8_INT8, OASR_ERR_INVALID, "conformer_encode_packed: bad quant_kind %d", qk);
+#define OB_LINEAR(label, fl, out, in, wt, bs, lay, qi, N, K, act, glu)                                              \
+  do {                                                                                                              \
+    if (qk == 0) {                                                                                                  \
+      if (glu) OB_STEP("gemm_glu " label, fl, oasr_b200_gemm_glu(out, in, wt, bs, M, N, K, dt, stream));              \
+      else OB_STEP("gemm " label, fl, oasr_b200_gemm(out, in, wt, bs, M, N, K, act, dt, stream));                    \
+    } else {                                                                                                        \
+      OB_STEP("quantize_rows", 0, oasr_b200_quantize_rows(w.q8, w.qs, in, M, K, qk, dt, stream));                     \
+      OB_STEP("gemm_q8 " label, fl, oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, M, N, K, act, glu, qk, dt, stream)); \
+    }                                                                                                               \
+  } while (0)
   OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm(w.y, rows, m.embed_w, m.embed_b, M, d, m.embed_in, OASR_ACT_NONE, dt, stream));
   if (m.embed_ln_w) {
     OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 2, m.embed_ln_w, m.embed_ln_b,
@@ -189,28 +209,28 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_conformer_layer& l = ly[i];
     // macaron feed-forward
-    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
-    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    OB_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, l, 0, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, d, m.ffn, OASR_ACT_NONE, 0);
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
                                    m.eps, 0, dt, stream));
     // relative-position self-attention
-    OB_STEP("gemm qkv4", 2.0 * M * 4 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
+    OB_LINEAR("qkv4", 2.0 * M * 4 * d * d, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, d, OASR_ACT_NONE, 0);
     OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs, max_seg,
                                          M, m.heads, scale, dt, stream));
-    OB_STEP("gemm attn_out", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.att, l.out_w, l.out_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_LINEAR("attn_out", 2.0 * M * d * d, w.y, w.att, l.out_w, l.out_b, l, 3, d, d, OASR_ACT_NONE, 0);
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
                                    nullptr, M, d, m.eps, 0, dt, stream));
     // convolution module
-    OB_STEP("gemm_glu pw1", 2.0 * M * 2 * d * d, oasr_b200_gemm_glu(w.g, w.h, l.pw1_w, l.pw1_b, M, d, d, dt, stream));
+    OB_LINEAR("pw1", 2.0 * M * 2 * d * d, w.g, w.h, l.pw1_w, l.pw1_b, l, 4, d, d, OASR_ACT_NONE, 1);
     OB_STEP("depthwise_conv1d_packed", 0, oasr_b200_depthwise_conv1d_packed(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
                                               fill_frames ? l.glu_of_bias : nullptr, fill_frames, cu_seqlens, num_segs,
                                               max_seg, d, m.kernel, OASR_ACT_SWISH, dt, stream));
-    OB_STEP("gemm pw2", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.cv, l.pw2_w, l.pw2_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_LINEAR("pw2", 2.0 * M * d * d, w.y, w.cv, l.pw2_w, l.pw2_b, l, 5, d, d, OASR_ACT_NONE, 0);
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, M, d,
                                    m.eps, 0, dt, stream));
     // feed-forward, norm_final, then the next layer's first pre-norm (or after_norm, split for the head)
-    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ff_w1, l.ff_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
-    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ff_w2, l.ff_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    OB_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ff_w1, l.ff_b1, l, 6, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, d, m.ffn, OASR_ACT_NONE, 0);
     if (i + 1 < L) {
       OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b,
                                      ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, M, d, m.eps, 0, dt, stream));
@@ -300,6 +320,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
   OB_REQUIRE(m.pos_proj && m.pos_proj_rows > 0, OASR_ERR_INVALID,
              "conformer_chunk_paged: the model has no projected positional table (pos_proj)");
   OB_REQUIRE(is_aligned(workspace, 256), OASR_ERR_ALIGN, "conformer_chunk_paged: workspace must be 256-byte aligned");
+  OB_REQUIRE(m.quant_kind == 0, OASR_ERR_UNSUPPORTED, "conformer_chunk_paged: 8-bit GEMM kinds are wired into the offline entry point only");
   ChunkWorkspace w = carve_chunk(m, B, T, static_cast<uint8_t*>(workspace));
   OB_REQUIRE(workspace_bytes >= w.bytes, OASR_ERR_INVALID, "conformer_chunk_paged: workspace of %lld bytes, %lld needed",
              (long long)workspace_bytes, (long long)w.bytes);

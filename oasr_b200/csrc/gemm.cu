@@ -57,6 +57,9 @@ struct Params {
   int32_t* argmax;        // kEpiLsm: nullable
   uint32_t* status;       // device status word (nullable)
   // kSchedConv (3x3 / stride-2 convolution as an implicit GEMM over a parity-split NHWC input):
+  // 8-bit operand kinds: D = (A_q . B_q^T) * a_scale[row] * b_scale[col] (+ bias)
+  const float* a_scale;   // [M] per-row (per-token) scales of A
+  const float* b_scale;   // [N] (GLU: [2N]) per-row (per-output-channel) scales of B
   int conv_f2;            // output positions per output frame (rows of one frame in a tile)
   int conv_tpt;           // output frames per 128-row tile = 128 / conv_f2
   int conv_cblocks;       // input channels / 64
@@ -238,7 +241,10 @@ constexpr int threads_for() { return 64 + 32 * kEpiWarps * epi_groups<kSched, kE
 // multicast), the leader CTA (rank 0) issues the MMAs for both, every CTA drains its own 128
 // accumulator rows.  Per flop this halves the B bytes a CTA pulls from L2, which is what limits the
 // single-CTA 128 x 256 tile.
-template <typename T, int BN, int kStages, int kSched, int kEpi, int kCtas>
+// kKind: 0 = 16-bit operands of type T; 1 = fp8 e4m3 operands (kind::f8f6f4, fp32 accumulators); 2 = signed
+// int8 operands (kind::i8, int32 accumulators).  For the 8-bit kinds T is the OUTPUT type, a K block is 128
+// elements (the same 128 bytes per shared-memory row) and the epilogue multiplies by the row and column scales.
+template <typename T, int BN, int kStages, int kSched, int kEpi, int kCtas, int kKind = 0>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                           const CUtensorMap& tmap_d, const Params& p) {
   using S = Smem<BN, kStages, kCtas>;
@@ -246,7 +252,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
   constexpr int kGroups = epi_groups<kSched, kEpi>();
   constexpr uint32_t kTmemCols = 2 * BN;  // 128, 256 or 512: a power of two >= 32
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
-  constexpr uint32_t kIdesc = ptx::umma_idesc_f16(kBf16, BM * kCtas, BN);
+  constexpr uint32_t kIdesc = kKind == 0 ? ptx::umma_idesc_f16(kBf16, BM * kCtas, BN)
+                            : kKind == 1 ? ptx::umma_idesc_8bit(1, 0, 0, BM, BN)
+                                         : ptx::umma_idesc_8bit(2, 1, 1, BM, BN);
+  constexpr int kBKe = kKind == 0 ? BK : 2 * BK;  // K elements per stage
+  static_assert(kKind == 0 || (kCtas == 1 && kSched == kSchedDense && (kEpi == kEpiStore || kEpi == kEpiGlu)),
+                "8-bit kinds: dense problems, store / GLU epilogues, single-CTA tiles");
   static_assert(kCtas == 1 || (kSched == kSchedDense && kTmaStore), "CTA pairs: dense problems with TMA stores");
   const uint32_t cta_rank = kCtas == 2 ? ptx::cluster_ctarank() : 0u;
 
@@ -334,14 +345,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
             continue;
           }
           ptx::mbar_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
-          ptx::tma_load_3d(sA + stage * S::kABytes, &tmap_a, kb * BK, t.a_row, t.a_batch, &full_bar[stage]);
+          ptx::tma_load_3d(sA + stage * S::kABytes, &tmap_a, kb * kBKe, t.a_row, t.a_batch, &full_bar[stage]);
           if constexpr (kEpi == kEpiGlu) {
             // value rows [n0/2, +BN/2) and gate rows [N + n0/2, +BN/2) of the 2N-row weight
-            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * BK, t.b_row / 2, t.b_batch, &full_bar[stage]);
-            ptx::tma_load_3d(sB + stage * S::kBBytes + S::kBBytes / 2, &tmap_b, kb * BK, p.N + t.b_row / 2,
+            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * kBKe, t.b_row / 2, t.b_batch, &full_bar[stage]);
+            ptx::tma_load_3d(sB + stage * S::kBBytes + S::kBBytes / 2, &tmap_b, kb * kBKe, p.N + t.b_row / 2,
                              t.b_batch, &full_bar[stage]);
           } else {
-            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * BK, t.b_row, t.b_batch, &full_bar[stage]);
+            ptx::tma_load_3d(sB + stage * S::kBBytes, &tmap_b, kb * kBKe, t.b_row, t.b_batch, &full_bar[stage]);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -371,6 +382,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
             const uint64_t adesc = ptx::smem_desc_kmajor_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t bdesc = ptx::smem_desc_kmajor_sw128(b_addr + k * UMMA_K * 2);
             if constexpr (kCtas == 2) ptx::umma_f16_pair(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            else if constexpr (kKind == 1) ptx::umma_f8(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            else if constexpr (kKind == 2) ptx::umma_i8(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
             else ptx::umma_f16(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
           if constexpr (kCtas == 2) ptx::umma_commit_pair(&empty_bar[stage], 3);  // frees the stage in both CTAs
@@ -442,6 +455,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       out_buf ^= 1;
     };
     // 32 accumulator columns -> 16 packed words of `w` (kHalf = which half), bias and activation in fp32
+    // accumulator word -> float (int32 accumulators of kind::i8 are converted), and this thread's row scale
+    auto acc_f = [](uint32_t u) -> float {
+      if constexpr (kKind == 2) return __int2float_rn(static_cast<int>(u));
+      else return __uint_as_float(u);
+    };
+    float row_scale = 1.f;
     // act_c: 0 = none, 1 = swish, 2 = any other id (run-time switch).  Compile-time so that the instructions a
     // tile executes are contiguous: with the switch inlined per element, the never-taken activations sit between
     // the executed instructions and the loop runs at the speed of instruction fetch.
@@ -453,7 +472,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         const int col = col0 + g8 * 8;
         float v[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = bits_f(r[g8 * 8 + i]);
+        for (int i = 0; i < 8; ++i) v[i] = acc_f(r[g8 * 8 + i]);
+        if constexpr (kKind != 0) {
+          if (col < p.N) {
+            const float4 s0 = *reinterpret_cast<const float4*>(p.b_scale + col);
+            const float4 s1 = *reinterpret_cast<const float4*>(p.b_scale + col + 4);
+            v[0] *= row_scale * s0.x; v[1] *= row_scale * s0.y; v[2] *= row_scale * s0.z; v[3] *= row_scale * s0.w;
+            v[4] *= row_scale * s1.x; v[5] *= row_scale * s1.y; v[6] *= row_scale * s1.z; v[7] *= row_scale * s1.w;
+          }
+        }
         if (bias && col < p.N) {
           float bb[8];
           load_bias8(bias + col, bb);
@@ -479,6 +506,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
       const int64_t row = t.out_row + q * 32 + lane;
       const bool row_ok = row < t.row_end;
       const uint32_t t_acc = tmem_base + lane_base + acc * BN;
+      if constexpr (kKind != 0) row_scale = row_ok ? p.a_scale[row] : 0.f;
 
       if constexpr (kEpi == kEpiStore && kTmaStore) {
         // group `grp` takes the 64-column chunks grp, grp + kGroups, ...; the TMEM load of the next 32
@@ -602,7 +630,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
               const int col = n0 + c0 + half * 32 + g * 8;
               float v[8], gt[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) { v[i] = bits_f(rv[g * 8 + i]); gt[i] = bits_f(rg[g * 8 + i]); }
+              for (int i = 0; i < 8; ++i) { v[i] = acc_f(rv[g * 8 + i]); gt[i] = acc_f(rg[g * 8 + i]); }
+              if constexpr (kKind != 0) {
+                if (col < p.N) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    v[i] *= row_scale * p.b_scale[col + i];
+                    gt[i] *= row_scale * p.b_scale[p.N + col + i];
+                  }
+                }
+              }
               if (bias && col < p.N) {
                 float bb[8];
                 load_bias8(bias + col, bb);
@@ -782,6 +819,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   gemm_body<T, BN, kStages, kSched, kEpi, 1>(tmap_a, tmap_b, tmap_d, p);
 }
 
+template <typename T, int BN, int kStages, int kEpi, int kKind>
+__global__ void __launch_bounds__(threads_for<kSchedDense, kEpi>(), 1)
+gemm_tcgen05_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+  gemm_body<T, BN, kStages, kSchedDense, kEpi, 1, kKind>(tmap_a, tmap_b, tmap_d, p);
+}
+
 template <typename T, int kStages, int kEpi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_for<kSchedDense, kEpi>(), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -838,6 +882,24 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, 
   if (grid < 1) grid = 1;
   kern<<<static_cast<unsigned>(grid), threads_for<kSched, kEpi>(), S::kDynamic, s>>>(ta, tb, td, p);
   return check_launch("tcgen05 gemm launch");
+}
+
+template <typename T, int BN, int kStages, int kEpi, int kKind>
+int launch_q8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p, int64_t work_items,
+              cudaStream_t s) {
+  using S = Smem<BN, kStages>;
+  auto kern = gemm_tcgen05_q8_kernel<T, BN, kStages, kEpi, kKind>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+    if (e != cudaSuccess) return set_error(OASR_ERR_CUDA, "gemm_q8: cannot reserve %d bytes of shared memory: %s",
+                                           S::kDynamic, cudaGetErrorString(e));
+    attr_done = true;
+  }
+  int64_t grid = work_items < sm_count() ? work_items : sm_count();
+  if (grid < 1) grid = 1;
+  kern<<<static_cast<unsigned>(grid), threads_for<kSchedDense, kEpi>(), S::kDynamic, s>>>(ta, tb, td, p);
+  return check_launch("tcgen05 8-bit gemm launch");
 }
 
 constexpr int kPairStages = 6;  // 32 KB per stage and CTA (+32 KB staging = 224 KB)
@@ -991,6 +1053,38 @@ int launch_simt(void* D, const void* A, const void* B, const void* bias, int64_t
   return check_launch("simt gemm launch");
 }
 
+// 8-bit operand GEMM: A_q (M, K) and B_q (N or 2N, K) hold one byte per element.
+template <typename T, int kEpi, int kKind>
+int run_q8_typed(Params& p, const void* A, const void* B, int64_t M, int64_t N, int64_t K, int out_dtype, cudaStream_t s) {
+  const int64_t n_eff = kEpi == kEpiGlu ? 2 * N : N;
+  const int64_t m_tiles = (M + BM - 1) / BM;
+  int bn = pick_bn(m_tiles, n_eff);
+  if (kEpi == kEpiGlu && bn < 128) bn = 128;
+  p.num_m_tiles = static_cast<int>(m_tiles);
+  p.num_n_tiles = static_cast<int>((n_eff + bn - 1) / bn);
+  p.num_k_blocks = static_cast<int>((K + 2 * BK - 1) / (2 * BK));
+  CUtensorMap ta, tb, td;
+  uint64_t adims[3] = {(uint64_t)K, (uint64_t)M, 1};
+  uint64_t astr[3] = {0, (uint64_t)K, (uint64_t)K * (uint64_t)M};
+  uint32_t abox[3] = {2 * BK, BM, 1};
+  if (int rc = make_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, A, adims, astr, abox)) return rc;
+  uint64_t bdims[3] = {(uint64_t)K, (uint64_t)n_eff, 1};
+  uint64_t bstr[3] = {0, (uint64_t)K, (uint64_t)K * (uint64_t)n_eff};
+  uint32_t bbox[3] = {2 * BK, (uint32_t)(kEpi == kEpiGlu ? bn / 2 : bn), 1};
+  if (int rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, bdims, bstr, bbox)) return rc;
+  uint64_t ddims[3] = {(uint64_t)N, (uint64_t)M, 1};
+  uint64_t dstr[3] = {0, (uint64_t)N * 2, (uint64_t)N * 2 * (uint64_t)M};
+  uint32_t dbox[3] = {32u, 32u, 1};  // two-group epilogues store 32 x 32 pieces per warp
+  if (int rc = make_tensor_map(&td, tma_dtype(out_dtype), 3, p.D, ddims, dstr, dbox, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
+  const int64_t work = m_tiles * p.num_n_tiles;
+  OB_REQUIRE(work < (int64_t(1) << 31), OASR_ERR_INVALID, "gemm_q8: too many output tiles");
+  switch (bn) {
+    case 256: return launch_q8<T, 256, StagesFor<256>::v, kEpi, kKind>(ta, tb, td, p, work, s);
+    case 128: return launch_q8<T, 128, StagesFor<128>::v, kEpi, kKind>(ta, tb, td, p, work, s);
+    default: return launch_q8<T, 64, StagesFor<64>::v, kEpi, kKind>(ta, tb, td, p, work, s);
+  }
+}
+
 }  // namespace gemm
 
 // Internal C++ entry: reference GEMM on CUDA cores (tests compare the
@@ -1021,6 +1115,38 @@ int oasr_b200_gemm(void* D, const void* A, const void* B, const void* bias, int6
   pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
   pr.p.D = D; pr.p.bias = bias; pr.p.act = activation; pr.p.alpha = 1.f;
   return run<kSchedDense, kEpiStore>(pr, dtype, s);
+}
+
+int oasr_b200_gemm_q8(void* D, const void* A_q, const float* a_scale, const void* B_q, const float* b_scale,
+                      const void* bias, int64_t M, int64_t N, int64_t K, int activation, int glu, int kind,
+                      int out_dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  OB_REQUIRE(M == 0 || (D && A_q && B_q && a_scale && b_scale), OASR_ERR_INVALID, "gemm_q8: null pointer argument");
+  OB_REQUIRE(M >= 0 && N > 0 && K > 0, OASR_ERR_INVALID, "gemm_q8: bad shape M=%lld N=%lld K=%lld", (long long)M,
+             (long long)N, (long long)K);
+  OB_REQUIRE(kind == OASR_Q8_FP8_E4M3 || kind == OASR_Q8_INT8, OASR_ERR_INVALID, "gemm_q8: kind must be 1 (fp8 e4m3) or 2 (int8)");
+  OB_REQUIRE(N % 8 == 0 && K % 16 == 0, OASR_ERR_ALIGN, "gemm_q8 needs N a multiple of 8 and K a multiple of 16 (got N=%lld K=%lld)",
+             (long long)N, (long long)K);
+  OB_REQUIRE(is_aligned(A_q, 16) && is_aligned(B_q, 16) && is_aligned(D, 16) && is_aligned(b_scale, 16) &&
+                 (!bias || is_aligned(bias, 16)),
+             OASR_ERR_ALIGN, "gemm_q8: operand pointers must be 16-byte aligned");
+  OB_REQUIRE(act_is_known(activation) && (!glu || activation == OASR_ACT_NONE), OASR_ERR_INVALID,
+             "gemm_q8: unknown activation id %d (none with glu)", activation);
+  OB_REQUIRE(M < (int64_t(1) << 31) && N < (1 << 30) && K < (1 << 30), OASR_ERR_INVALID, "gemm_q8: extent too large");
+  if (M == 0) return OASR_OK;
+  Params p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
+  p.D = D; p.bias = bias; p.act = activation; p.alpha = 1.f;
+  p.a_scale = a_scale; p.b_scale = b_scale; p.status = device_status_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(out_dtype, T, [&]() -> int {
+    if (kind == OASR_Q8_FP8_E4M3)
+      return glu ? run_q8_typed<T, kEpiGlu, 1>(p, A_q, B_q, M, N, K, out_dtype, s)
+                 : run_q8_typed<T, kEpiStore, 1>(p, A_q, B_q, M, N, K, out_dtype, s);
+    return glu ? run_q8_typed<T, kEpiGlu, 2>(p, A_q, B_q, M, N, K, out_dtype, s)
+               : run_q8_typed<T, kEpiStore, 2>(p, A_q, B_q, M, N, K, out_dtype, s);
+  });
 }
 
 int oasr_b200_gemm_residual_f32(float* R_out, const float* R_in, const void* A, const void* B, const void* bias,

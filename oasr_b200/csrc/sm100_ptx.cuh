@@ -166,6 +166,30 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// 8-bit operand kinds (same shared-memory geometry: 128-byte rows, 32 bytes of K per instruction = 32 elements).
+// kind::f8f6f4 with e4m3 operands accumulates in fp32, kind::i8 with signed operands in int32.
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Makes `bar` complete one arrival once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -306,6 +330,14 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(bool bf16, int M, int N, b
                                                       bool b_mn_major = false) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
          ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Instruction descriptor of the 8-bit kinds, K-major operands: c_format 1 = fp32 / 2 = int32 accumulators;
+// operand formats of kind::f8f6f4: 0 = e4m3, 1 = e5m2; of kind::i8: 0 = unsigned, 1 = signed.
+__host__ __device__ constexpr uint32_t umma_idesc_8bit(uint32_t c_format, uint32_t a_format, uint32_t b_format, int M,
+                                                       int N) {
+  return (c_format << 4) | (a_format << 7) | (b_format << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 

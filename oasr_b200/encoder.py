@@ -103,7 +103,13 @@ class ConformerCTC:
     """WeNet-style Conformer encoder + CTC head running on the sm_100a kernels."""
 
     def __init__(self, cfg: ConformerConfig, params: Dict[str, torch.Tensor], device="cuda",
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, quant: Optional[str] = None):
+        """``quant``: None = 16-bit GEMMs; "fp8" / "int8" = the eight Linear GEMMs of every layer run on
+        fp8-e4m3 / int8 operands (weights quantised per output channel here, activations per token on the
+        fly); offline entry points only."""
+        if quant not in (None, "fp8", "int8"):
+            raise ValueError("quant must be None, 'fp8' or 'int8'")
+        self.quant_kind = {None: 0, "fp8": 1, "int8": 2}[quant]
         if cfg.head_dim != 64:
             raise ValueError("the fused relative-position attention kernel needs head_dim 64")
         if cfg.d_model % 8 or cfg.ffn % 8:
@@ -209,8 +215,19 @@ class ConformerCTC:
         return fused.subsample_conv2(x1, T1, F1, self.conv2_krsc, self.conv2_b, cu_frames, total)
 
     # ------------------------------------------------------------------ layer stack
+    def _quantize_weights(self) -> None:
+        """Per-output-channel 8-bit copies of the eight Linear weights of every layer, in the order of
+        oasr_b200_conformer_layer::q_w (ffm_w1, ffm_w2, qkv4, out, pw1, pw2, ff_w1, ff_w2)."""
+        from . import quant
+
+        for lw in self.layers:
+            ws = [lw["ffm"][0], lw["ffm"][2], lw["qkv4"][0], lw["out"][0], lw["pw1"][0], lw["pw2"][0], lw["ff"][0], lw["ff"][2]]
+            lw["q8"] = [quant.quantize_rows(w, self.quant_kind) for w in ws]
+
     def _build_native_model(self) -> None:
         """Fill the C structs of the native executor with the prepared device pointers."""
+        if self.quant_kind and "q8" not in self.layers[0]:
+            self._quantize_weights()
         import ctypes
 
         from . import _lib
@@ -237,6 +254,9 @@ class ConformerCTC:
             c.norm_ff_w, c.norm_ff_b = map(ptr, lw["norm_ff"])
             c.ff_w1, c.ff_b1, c.ff_w2, c.ff_b2 = map(ptr, lw["ff"])
             c.norm_final_w, c.norm_final_b = map(ptr, lw["norm_final"])
+            if self.quant_kind:
+                for qi, (wq, ws) in enumerate(lw["q8"]):
+                    c.q_w[qi], c.q_s[qi] = wq.data_ptr(), ws.data_ptr()
         cfg = self.cfg
         m = _lib.ConformerModel()
         m.d_model, m.heads, m.ffn, m.kernel, m.num_layers = cfg.d_model, cfg.heads, cfg.ffn, cfg.kernel, L
@@ -248,6 +268,7 @@ class ConformerCTC:
         m.after_norm_w, m.after_norm_b = map(ptr, self.after_norm)
         m.ctc_w, m.ctc_b = ptr(self.ctc_w), ptr(self.ctc_b)
         m.pos_proj, m.pos_proj_rows = None, 0
+        m.quant_kind = self.quant_kind
         self._native_layers, self._native_model = arr, m   # keep both alive
         self._workspace = None
         self._pos_proj = None
@@ -316,6 +337,8 @@ class ConformerCTC:
 
         if not self.cfg.causal:
             raise RuntimeError("streaming needs a causal conv module (cfg.causal=True)")
+        if self.quant_kind:
+            raise NotImplementedError("the streaming chunk executor runs 16-bit GEMMs only")
         if not xs.is_cuda:
             raise RuntimeError("xs must be a CUDA tensor (oasr_b200 has no CPU path)")
         if self._pos_proj is None:   # linear_pos of the whole positional table, every layer at once

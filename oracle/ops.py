@@ -264,3 +264,38 @@ def ctc_greedy(log_probs: torch.Tensor, length: int, blank: int = 0):
             out.append(i)
         prev = i
     return out
+
+
+# ---------------------------------------------------------------------------
+# 8-bit operand GEMMs (no reference counterpart: oasr/layers/linear.py:7 only
+# names a future quantised path).  Restated here so that the CUDA kernels have
+# a CPU statement of their arithmetic to be checked against.
+# ---------------------------------------------------------------------------
+def quantize_rows(x: torch.Tensor, kind: int):
+    """Row-wise dynamic quantisation, the arithmetic of the CUDA kernel step by step in fp32:
+    ``scale = amax / qmax``; ``inv = 1 / scale``; ``q = round(x * inv)`` (fp8 e4m3 round-to-nearest-even,
+    or int8 round-half-even clipped to +-127).  kind 1 = fp8 e4m3 (qmax 448), 2 = int8 (qmax 127).
+    Returns ``(codes uint8, scale fp32, dequantised fp32 values of the codes)``."""
+    x = x.float()
+    amax = x.abs().amax(dim=1)
+    qmax = 448.0 if kind == 1 else 127.0
+    scale = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
+    inv = 1.0 / scale
+    y = x * inv[:, None]
+    if kind == 1:
+        q8 = y.to(torch.float8_e4m3fn)
+        return q8.view(torch.uint8), scale, q8.float()
+    qi = torch.clamp(torch.round(y), -127, 127).to(torch.int8)
+    return qi.view(torch.uint8), scale, qi.float()
+
+
+def gemm_q8(a_vals: torch.Tensor, a_scale: torch.Tensor, b_vals: torch.Tensor, b_scale: torch.Tensor, bias=None,
+            activation: int = -1, glu: bool = False) -> torch.Tensor:
+    """fp32 statement of the 8-bit GEMM on the dequantised code values: ``(A . B^T) * sa * sb + bias``."""
+    y = (a_vals.double() @ b_vals.double().t()).float() * a_scale[:, None] * b_scale[None, :]
+    if bias is not None:
+        y = y + bias.float()
+    if glu:
+        n = y.size(1) // 2
+        return y[:, :n] * torch.sigmoid(y[:, n:])
+    return globals()["activation"](y, activation) if activation >= 0 else y
