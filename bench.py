@@ -227,6 +227,9 @@ def run_streaming(args):
     from oasr_b200.weights import init_params
 
     torch.cuda.set_device(0)
+    if args.no_pdl:
+        from oasr_b200 import tunables
+        tunables.set("pdl", 0)
     streams, window, chunk, max_past = args.batch if args.batch != 64 else 256, 67, 16, 256
     cfg = dataclasses.replace(model_config(args.layers), causal=True)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device="cuda:0", dtype=torch.bfloat16)
@@ -294,6 +297,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="launch in plain stream order (comparison run)")
+    ap.add_argument("--quant", default="none", choices=["none", "fp8", "int8"],
+                    help="run the eight Linear GEMMs of every layer on 8-bit operands (not the headline dtype)")
     ap.add_argument("--batch", type=int, default=64, help="utterances per step (64 = the headline workload)")
     ap.add_argument("--layers", type=int, default=12, help="encoder layers (12 = the headline workload); "
                     "smaller values with --batch give the reduced case used for ncu captures")
@@ -324,8 +330,12 @@ def main():
     from oasr_b200.encoder import ConformerCTC
     from oasr_b200.weights import init_params
 
+    if args.no_pdl:
+        from oasr_b200 import tunables
+        tunables.set("pdl", 0)
     cfg = model_config(args.layers)
-    model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16)
+    model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16,
+                         quant=None if args.quant == "none" else args.quant)
     feats_host, lengths = make_batch(rank, args.batch)
     workload = WORKLOAD if (args.batch, args.layers) == (64, 12) else \
         f"REDUCED profiling case: conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002_b{args.batch}_len200-2000_packed"
@@ -399,7 +409,7 @@ def main():
         peaks = measured_peaks()
         gemm = {"launches": 0, "ms": 0.0, "flops": 0.0}
         for k, v in per.items():
-            if k.startswith("gemm ") or k.startswith("gemm_glu"):   # every launch of gemm_tcgen05_kernel but the head
+            if k.startswith("gemm ") or k.startswith("gemm_glu") or k.startswith("gemm_q8"):   # every launch of gemm_tcgen05_kernel but the head
                 for f in gemm:
                     gemm[f] += v[f]
         step_total = total_ms / args.steps if dist is None else float(np.mean(step_ms))
@@ -426,7 +436,9 @@ def main():
         line = {
             "metric": "audio_seconds_per_second", "value": audio_total / (total_ms * 1e-3), "unit": "audio-s/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
+            "data": "synthetic",
             "config": {"workload": workload, "global_batch": args.batch * world, "parallelism": f"utterance-sharded x{world}, no collective",
                        "l2": "256 MiB flush write between steps; per-step working set (weights 240 MB + activations) > 126 MB L2",
                        "audio_seconds_per_step": audio_total / args.steps},

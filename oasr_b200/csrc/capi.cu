@@ -58,6 +58,7 @@ uint32_t* device_status_ptr() {
 
 namespace gemm { extern int g_force_bn; extern int g_use_pairs; }
 extern int g_dw_path;
+int g_pdl = 1;
 extern int g_fmha_chunk_path;
 
 }  // namespace ob
@@ -77,6 +78,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   if (name && std::strcmp(name, "fmha_chunk_path") == 0) {
     ob::g_fmha_chunk_path = value != 0;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "pdl") == 0) {
+    ob::g_pdl = value != 0;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "dwconv_path") == 0) {

@@ -205,4 +205,23 @@ inline bool act_is_known(int act) {
 
 int sm_count();  // cached multiprocessor count of the current device (capi.cu)
 
+// Launch with programmatic stream serialisation (the kernel must call grid_dep_wait() before it touches
+// global memory): its blocks may be scheduled while the previous kernel of the stream drains.  The "pdl"
+// tunable (default 1) switches the attribute off.
+extern int g_pdl;
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = g_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 }  // namespace ob

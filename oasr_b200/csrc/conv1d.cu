@@ -11,6 +11,7 @@
 // The reference kernel launches one CTA of C/8 threads per output frame and
 // re-reads all K taps and weights per frame (include/oasr/conv/conv1d.cuh:23-113).
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ob {
 int g_dw_path = 0;  // 0 = heuristic (register-streaming kernel where it applies); 1 = shared-memory tiled kernel; set through oasr_b200_set_tunable("dwconv_path")
@@ -339,6 +340,8 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
 template <typename T, int K, bool kAffine, bool kAct>
 __global__ void __launch_bounds__(256) dwconv_stream_kernel(DwArgs a) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
+  ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
+  ptx::grid_dep_wait();
   const int C = a.channels;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
   if (c >= C) return;
@@ -414,10 +417,10 @@ int launch_stream(const DwArgs& a, int max_out_len, cudaStream_t s) {
     dim3 grid((max_out_len + kST - 1) / kST, (pairs + threads - 1) / threads, static_cast<unsigned>(a.batch));
     const bool affine = a.post_scale != nullptr;
     const bool act = a.act != OASR_ACT_NONE;
-    if (affine && act) dwconv_stream_kernel<T, K, true, true><<<grid, block, 0, s>>>(a);
-    else if (affine) dwconv_stream_kernel<T, K, true, false><<<grid, block, 0, s>>>(a);
-    else if (act) dwconv_stream_kernel<T, K, false, true><<<grid, block, 0, s>>>(a);
-    else dwconv_stream_kernel<T, K, false, false><<<grid, block, 0, s>>>(a);
+    if (affine && act) launch_pdl(dwconv_stream_kernel<T, K, true, true>, grid, block, 0, s, a);
+    else if (affine) launch_pdl(dwconv_stream_kernel<T, K, true, false>, grid, block, 0, s, a);
+    else if (act) launch_pdl(dwconv_stream_kernel<T, K, false, true>, grid, block, 0, s, a);
+    else launch_pdl(dwconv_stream_kernel<T, K, false, false>, grid, block, 0, s, a);
     return check_launch("depthwise_conv1d (streaming) kernel launch");
   }
 }

@@ -119,6 +119,10 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
   constexpr uint32_t kColS = 0, kColO = 256;
   constexpr float kNegInf = -INFINITY;
 
+  // no-ops unless launched with programmatic stream serialisation; cu_seqlens / seqlens below are already
+  // global reads, so the wait comes first
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
   // ---- which rows / keys does this CTA own ---------------------------------
   const int q0 = blockIdx.x * BQ;
   const int h = blockIdx.y;
@@ -553,7 +557,7 @@ int launch_k(const Maps& maps, const Params& p, dim3 grid, cudaStream_t s) {
                        cudaGetErrorString(e));
     attr_done = true;
   }
-  kern<<<grid, kThreads, S::kDynamic, s>>>(maps, p);
+  launch_pdl(kern, grid, dim3(kThreads), S::kDynamic, s, maps, p);
   return check_launch("fmha launch");
 }
 

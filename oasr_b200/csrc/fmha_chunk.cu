@@ -100,6 +100,8 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     ptx::fence_proxy_async_smem();
   }
   __syncthreads();
+  ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
+  ptx::grid_dep_wait();
   bool ok = true;
   const int item = blockIdx.x * kWarps + warp;
   const bool live = item < p.B * p.H;   // warp-uniform; dead warps skip to the common exit
@@ -323,7 +325,7 @@ int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos
                          cudaGetErrorString(e));
       attr_done = true;
     }
-    kern<<<grid, kWarps * 32, kSmemDynamic, stream>>>(mk, mv, mp, p);
+    launch_pdl(kern, dim3(grid), dim3(kWarps * 32), kSmemDynamic, stream, mk, mv, mp, p);
     return check_launch("fmha_paged_relpos (chunk kernel) launch");
   });
 }

@@ -305,6 +305,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
   else __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up done: let the next kernel of the stream start its own set-up, then wait for the previous kernel's
+  // results (no-ops unless launched with programmatic stream serialisation)
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
 
   Scheduler<kSched, BN, kCtas> sched(p);
   sched.rank = cta_rank;
@@ -880,7 +884,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, 
   }
   int64_t grid = work_items < sm_count() ? work_items : sm_count();
   if (grid < 1) grid = 1;
-  kern<<<static_cast<unsigned>(grid), threads_for<kSched, kEpi>(), S::kDynamic, s>>>(ta, tb, td, p);
+  launch_pdl(kern, dim3(static_cast<unsigned>(grid)), dim3(threads_for<kSched, kEpi>()), S::kDynamic, s, ta, tb, td, p);
   return check_launch("tcgen05 gemm launch");
 }
 
@@ -898,7 +902,7 @@ int launch_q8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& t
   }
   int64_t grid = work_items < sm_count() ? work_items : sm_count();
   if (grid < 1) grid = 1;
-  kern<<<static_cast<unsigned>(grid), threads_for<kSchedDense, kEpi>(), S::kDynamic, s>>>(ta, tb, td, p);
+  launch_pdl(kern, dim3(static_cast<unsigned>(grid)), dim3(threads_for<kSchedDense, kEpi>()), S::kDynamic, s, ta, tb, td, p);
   return check_launch("tcgen05 8-bit gemm launch");
 }
 

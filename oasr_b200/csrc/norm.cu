@@ -8,6 +8,7 @@
 // LN 4H, add+LN+residual 8H (include/oasr/norm.cuh:28-93,396-484 in the
 // reference make 3-4 passes over the row from global memory instead).
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ob {
 namespace {
@@ -419,6 +420,8 @@ __device__ __forceinline__ void row_layer_norm(float (&x)[kChunks][kGran], int H
 
 template <typename T, int kChunks, int kMode>
 __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
+  ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
+  ptx::grid_dep_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= a.rows) return;
@@ -508,7 +511,7 @@ int launch_add_norm(const AddNormArgs& a, cudaStream_t s) {
   const int chunks = (a.hidden / kGran + 31) / 32;
   const int warps = 4;
   const unsigned grid = static_cast<unsigned>((a.rows + warps - 1) / warps);
-#define OB_AN_CASE(C) add_norm_f32_kernel<T, C, kMode><<<grid, warps * 32, 0, s>>>(a)
+#define OB_AN_CASE(C) launch_pdl(add_norm_f32_kernel<T, C, kMode>, dim3(grid), dim3(warps * 32), 0, s, a)
   if (chunks <= 1) OB_AN_CASE(1);
   else if (chunks <= 2) OB_AN_CASE(2);
   else if (chunks <= 4) OB_AN_CASE(4);

@@ -8,6 +8,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ob {
 namespace {
@@ -15,6 +16,8 @@ namespace {
 template <typename T, int kKind>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(uint8_t* __restrict__ q, float* __restrict__ scale,
                                                             const T* __restrict__ x, int64_t rows, int cols) {
+  ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
+  ptx::grid_dep_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -74,9 +77,9 @@ int oasr_b200_quantize_rows(void* q, float* scale, const void* x, int64_t rows, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
     if (kind == OASR_Q8_FP8_E4M3)
-      quantize_rows_kernel<T, OASR_Q8_FP8_E4M3><<<grid, 256, 0, s>>>(static_cast<uint8_t*>(q), scale, static_cast<const T*>(x), rows, (int)cols);
+      launch_pdl(quantize_rows_kernel<T, OASR_Q8_FP8_E4M3>, dim3(grid), dim3(256), 0, s, static_cast<uint8_t*>(q), scale, static_cast<const T*>(x), rows, (int)cols);
     else
-      quantize_rows_kernel<T, OASR_Q8_INT8><<<grid, 256, 0, s>>>(static_cast<uint8_t*>(q), scale, static_cast<const T*>(x), rows, (int)cols);
+      launch_pdl(quantize_rows_kernel<T, OASR_Q8_INT8>, dim3(grid), dim3(256), 0, s, static_cast<uint8_t*>(q), scale, static_cast<const T*>(x), rows, (int)cols);
     return check_launch("quantize_rows launch");
   });
 }

@@ -73,6 +73,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched with programmatic stream serialisation may start while the previous kernel of the stream
+// is still draining: everything before grid_dep_wait() (barrier set-up, TMEM allocation, descriptor
+// prefetch) overlaps that tail; after it the previous grid has completed and its writes are visible.  Without
+// the launch attribute both are no-ops.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -29,7 +29,6 @@ import torch.nn.functional as F
 
 from . import functional as OF
 from . import fused
-from .cache import gather_rows
 
 PAD_LOGIT = -1e4
 
