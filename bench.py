@@ -227,9 +227,9 @@ def run_streaming(args):
     from oasr_b200.weights import init_params
 
     torch.cuda.set_device(0)
-    if args.no_pdl:
+    if args.pdl:
         from oasr_b200 import tunables
-        tunables.set("pdl", 0)
+        tunables.set("pdl", 1)
     streams, window, chunk, max_past = args.batch if args.batch != 64 else 256, 67, 16, 256
     cfg = dataclasses.replace(model_config(args.layers), causal=True)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device="cuda:0", dtype=torch.bfloat16)
@@ -297,7 +297,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-pdl", action="store_true", help="launch in plain stream order (comparison run)")
+    ap.add_argument("--pdl", action="store_true", help="launch the hot kernels with programmatic stream serialisation (comparison run)")
     ap.add_argument("--quant", default="none", choices=["none", "fp8", "int8"],
                     help="run the eight Linear GEMMs of every layer on 8-bit operands (not the headline dtype)")
     ap.add_argument("--batch", type=int, default=64, help="utterances per step (64 = the headline workload)")
@@ -330,9 +330,9 @@ def main():
     from oasr_b200.encoder import ConformerCTC
     from oasr_b200.weights import init_params
 
-    if args.no_pdl:
+    if args.pdl:
         from oasr_b200 import tunables
-        tunables.set("pdl", 0)
+        tunables.set("pdl", 1)
     cfg = model_config(args.layers)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16,
                          quant=None if args.quant == "none" else args.quant)

@@ -88,10 +88,12 @@ OASR_API unsigned long long oasr_b200_launch_count(void);
  * "dwconv_path": 0 (default) = register-streaming depthwise conv where it
  * applies, 1 = the shared-memory tiled kernel; "fmha_chunk_path": 1 (default)
  * = paged rel-pos attention with <= 16 query frames runs the warp-per-(stream,
- * head) kernel, 0 = always the 128-row tcgen05 kernel; "pdl": 1 (default) launches
+ * head) kernel, 0 = always the 128-row tcgen05 kernel; "fmha_relpos_path": 1 (default) =
+ * packed relative-position attention on the two-CTAs-per-SM kernel (64-key tiles),
+ * 0 = on the general kernel; "pdl": 1 launches
  * the GEMM, attention, add+norm, depthwise-conv and quantise kernels with
  * programmatic stream serialisation (their set-up overlaps the previous
- * kernel's tail), 0 = plain stream order (no reference counterpart; the reference selects tiles
+ * kernel's tail), 0 (default) = plain stream order (no reference counterpart; the reference selects tiles
  * through its JIT variant names, oasr/jit/gemm.py:863-880). */
 OASR_API int oasr_b200_set_tunable(const char* name, int value);
 

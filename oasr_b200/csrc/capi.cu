@@ -58,7 +58,8 @@ uint32_t* device_status_ptr() {
 
 namespace gemm { extern int g_force_bn; extern int g_use_pairs; }
 extern int g_dw_path;
-int g_pdl = 1;
+extern int g_fmha_relpos_path;
+int g_pdl = 0;  // measured neutral on both workloads (offline 7.32 vs 7.36 ms, streaming 3.79 vs 3.71 ms per step): off by default
 extern int g_fmha_chunk_path;
 
 }  // namespace ob
@@ -78,6 +79,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   if (name && std::strcmp(name, "fmha_chunk_path") == 0) {
     ob::g_fmha_chunk_path = value != 0;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "fmha_relpos_path") == 0) {
+    ob::g_fmha_relpos_path = value != 0;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "pdl") == 0) {

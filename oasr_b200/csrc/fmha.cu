@@ -580,6 +580,12 @@ bool stride_ok(int64_t s) { return s % 8 == 0; }
 
 }  // namespace fmha
 
+namespace fmha_relpos {  // fmha_relpos.cu: packed relative-position form, two CTAs per SM
+int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t pos_stride, const int32_t* cu_seqlens,
+        int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype, cudaStream_t stream);
+}  // namespace fmha_relpos
+extern int g_fmha_relpos_path;
+
 namespace fmha_chunk {   // fmha_chunk.cu: warp-per-(stream, head) kernel for <= 16 query frames
 bool applies(int64_t Tq, int64_t block_size, int64_t blocks_per_seq);
 int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos, int64_t pos_rows, int64_t pos_stride,
@@ -606,6 +612,8 @@ int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, i
   OB_REQUIRE(is_aligned(out, 16) && is_aligned(qkv4, 16) && is_aligned(pos, 16) && pos_stride % 8 == 0,
              OASR_ERR_ALIGN, "fmha_varlen_relpos: operands must be 16-byte aligned");
   if (num_segs == 0 || max_seqlen == 0 || total == 0) return OASR_OK;
+  if (g_fmha_relpos_path)
+    return fmha_relpos::run(out, qkv4, pos, pos_rows, pos_stride, cu_seqlens, num_segs, max_seqlen, total, H, scale, dtype, stream);
   const int64_t d = H * D, ld = 4 * d;
   const uint8_t* base = static_cast<const uint8_t*>(qkv4);
   Maps maps;

@@ -5,7 +5,8 @@
 ``dwconv_path``: 0 (default) uses the register-streaming depthwise conv kernel where it applies, 1 the shared-memory tiled one.
 ``fmha_chunk_path``: 1 (default) runs paged rel-pos attention with <= 16 query frames on the warp-per-(stream, head)
 kernel, 0 always on the 128-row tcgen05 kernel.
-``pdl``: 1 (default) launches the hot kernels with programmatic stream serialisation, 0 in plain stream order.
+``fmha_relpos_path``: 1 (default) runs packed relative-position attention on the two-CTAs-per-SM kernel, 0 on the general one.
+``pdl``: 1 launches the hot kernels with programmatic stream serialisation, 0 (default) in plain stream order.
 """
 from __future__ import annotations
 

@@ -233,3 +233,43 @@ def test_fmha_paged_relpos_matches_fp32_reference(block_size, Tq, path):
         s = (torch.einsum("qhd,khd->hqk", qu, k) + torch.einsum("qhd,khd->hqk", qv, pp)) * scale
         want = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(Tq, d)
         assert (got[b] - want).abs().max().item() < 3e-2, (b, n, (got[b] - want).abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("path", [1, 0])
+def test_fmha_varlen_relpos_matches_fp32_reference(dtype, path):
+    """Packed relative-position attention, both kernels behind the entry point (two CTAs per SM with 64-key
+    tiles; general 128-key kernel) against an fp32 torch restatement on ragged segments, incl. lengths that
+    are not multiples of any tile size and a single-frame segment."""
+    from oasr_b200 import fused, tunables
+
+    torch.manual_seed(21)
+    lens = [1, 49, 64, 65, 127, 128, 129, 300, 499, 31]
+    H, D = 4, 64
+    d = H * D
+    total = sum(lens)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32).cuda()
+    qkv4 = (torch.randn(total, 4 * d) * 0.7).to(dtype).cuda()
+    pos = torch.randn(600, d).to(dtype).cuda()
+    scale = D ** -0.5
+    tunables.set("fmha_relpos_path", path)
+    try:
+        got = fused.fmha_varlen_relpos(qkv4, pos, cu, max(lens), H, scale).float().cpu()
+        again = fused.fmha_varlen_relpos(qkv4, pos, cu, max(lens), H, scale).float().cpu()
+    finally:
+        tunables.set("fmha_relpos_path", 1)
+    assert ob.device_status() == 0
+    assert torch.equal(got, again)
+    x = qkv4.float().cpu()
+    pp = pos.float().cpu()
+    for s, n in enumerate(lens):
+        a = int(cu[s])
+        qu = x[a:a + n, :d].view(n, H, D)
+        qv = x[a:a + n, d:2 * d].view(n, H, D)
+        k = x[a:a + n, 2 * d:3 * d].view(n, H, D)
+        v = x[a:a + n, 3 * d:].view(n, H, D)
+        p = pp[:n].view(n, H, D)
+        sc = (torch.einsum("qhd,khd->hqk", qu, k) + torch.einsum("qhd,khd->hqk", qv, p)) * scale
+        want = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v).reshape(n, d)
+        err = (got[a:a + n] - want).abs().max().item()
+        assert err < TOL, (s, n, err)
