@@ -429,7 +429,29 @@ OASR_API int oasr_b200_fmha_paged_relpos(void* out, const void* qkv4, void* k_po
                                          int64_t blocks_per_seq, int64_t block_size,
                                          int64_t num_blocks, double scale, int dtype, void* stream);
 
+/* The same attention over fp8 pages: k_pool / v_pool hold e4m3 codes (one byte per element, same
+ * (num_blocks, block_size, H, 64) layout) and k_scale / v_scale fp32[H] the per-head scales
+ * (value ~ code * scale).  The codes are converted to fp16 in shared memory; Tq <= 16, pages of 16 or
+ * a multiple of 32 frames, at most 64 pages per stream (no reference counterpart: the reference keeps
+ * 16-bit pages, oasr/cache/block_pool.py:33-41). */
+OASR_API int oasr_b200_fmha_paged_relpos_fp8(void* out, const void* qkv4, void* k_pool, void* v_pool,
+                                             const float* k_scale, const float* v_scale, const void* pos,
+                                             int64_t pos_rows, int64_t pos_stride, const int32_t* pos_start,
+                                             const int32_t* block_table, const int32_t* seqlens,
+                                             int64_t B, int64_t Tq, int64_t H, int64_t blocks_per_seq,
+                                             int64_t block_size, int64_t num_blocks, double scale,
+                                             int dtype, void* stream);
+
 /* ---- paged KV cache ---------------------------------------------------- */
+/* paged_kv_write with quantisation: 16-bit k_new / v_new (element strides as below, unit stride along
+ * D) are divided by their head's scale and stored as fp8 e4m3 codes (round to nearest even,
+ * saturating) in one-byte pools of the same layout; same index rule (no reference counterpart). */
+OASR_API int oasr_b200_paged_kv_write_fp8(void* k_pool, void* v_pool, const void* k_new, const void* v_new,
+                                          const float* k_scale, const float* v_scale,
+                                          const int32_t* block_table, const int32_t* offsets, int64_t B,
+                                          int64_t Hkv, int64_t T, int64_t D, int64_t stride_b,
+                                          int64_t stride_h, int64_t stride_t, int64_t blocks_per_seq,
+                                          int64_t block_size, int64_t num_blocks, int dtype, void* stream);
 /* Scatter a chunk of new keys/values into the page pools.  k_new, v_new are
  * (B, Hkv, T, D) with element strides (sb, sh, st) and unit stride along D;
  * logical position offsets[b] + t of stream b lands in physical row
@@ -553,6 +575,7 @@ OASR_API int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* mo
                                              const int32_t* total_seqlens,
                                              const int32_t* pos_start, int64_t blocks_per_seq,
                                              int64_t block_size, int64_t num_blocks,
+                                             const float* kv_scales /*nullable: fp8 pages, fp32 (num_layers, 2, heads) K then V scales*/,
                                              void* cnn_state, int64_t num_slots,
                                              const int64_t* slot_ids, void* workspace,
                                              int64_t workspace_bytes, float* log_probs /*nullable*/,

@@ -55,6 +55,8 @@ _SIGNATURES = {
     "oasr_b200_swish": [P, P, I, c_int, P],
     "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
     "oasr_b200_causal_conv1d": [P, P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_fmha_paged_relpos_fp8": [P, P, P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, c_double, c_int, P],
+    "oasr_b200_paged_kv_write_fp8": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, c_int, P],
     "oasr_b200_gemm_q8": [P, P, P, P, P, P, I, I, I, c_int, c_int, c_int, c_int, P],
     "oasr_b200_quantize_rows": [P, P, P, I, I, c_int, c_int, P],
     "oasr_b200_subsample_conv1": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
@@ -102,7 +104,7 @@ _SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, 
 
 _SIGNATURES["oasr_b200_conformer_encode_packed_noalloc"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, P, P]
 _SIGNATURES["oasr_b200_conformer_chunk_paged"] = [POINTER(ConformerModel), P, I, I, POINTER(c_void_p), POINTER(c_void_p),
-                                                 P, P, P, P, I, I, I, P, I, P, P, I, P, P, P]
+                                                 P, P, P, P, I, I, I, P, P, I, P, P, I, P, P, P]
 _SIGNATURES["oasr_b200_profile_enable"] = [c_int]
 _SIGNATURES["oasr_b200_profile_get"] = [c_int, POINTER(c_char_p), POINTER(c_double), POINTER(c_double)]
 

@@ -304,7 +304,8 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
                                     void* const* k_pools, void* const* v_pools, const int32_t* block_table,
                                     const int32_t* cache_seqlens, const int32_t* total_seqlens,
                                     const int32_t* pos_start, int64_t blocks_per_seq, int64_t block_size,
-                                    int64_t num_blocks, void* cnn_state, int64_t num_slots, const int64_t* slot_ids,
+                                    int64_t num_blocks, const float* kv_scales, void* cnn_state, int64_t num_slots,
+                                    const int64_t* slot_ids,
                                     void* workspace, int64_t workspace_bytes, float* log_probs, int32_t* argmax,
                                     void* stream) {
   using namespace ob;
@@ -345,13 +346,25 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
                                    m.eps, 0, dt, stream));
     // attention: project, append the chunk's keys/values to the pages, attend over cache + chunk
     OB_STEP("gemm qkv4", 2.0 * M * 4 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
-    OB_STEP("paged_kv_write", 0, oasr_b200_paged_kv_write(k_pools[i], v_pools[i], w.qkv4 + 2 * d * 2, w.qkv4 + 3 * d * 2,
-                                     block_table, cache_seqlens, B, m.heads, T, 64, T * 4 * d, 64, 4 * d, blocks_per_seq,
-                                     block_size, num_blocks, 2, stream));
-    OB_STEP("fmha_paged_relpos", 0, oasr_b200_fmha_paged_relpos(w.att, w.qkv4, k_pools[i], v_pools[i],
-                                     static_cast<const uint8_t*>(m.pos_proj) + i * d * 2, m.pos_proj_rows, L * d,
-                                     pos_start, block_table, total_seqlens, B, T, m.heads, blocks_per_seq, block_size,
-                                     num_blocks, scale, dt, stream));
+    if (kv_scales) {   // fp8 pages: per-head scales of this layer, K then V
+      const float* ks = kv_scales + static_cast<int64_t>(i) * 2 * m.heads;
+      const float* vs = ks + m.heads;
+      OB_STEP("paged_kv_write", 0, oasr_b200_paged_kv_write_fp8(k_pools[i], v_pools[i], w.qkv4 + 2 * d * 2, w.qkv4 + 3 * d * 2,
+                                       ks, vs, block_table, cache_seqlens, B, m.heads, T, 64, T * 4 * d, 64, 4 * d,
+                                       blocks_per_seq, block_size, num_blocks, dt, stream));
+      OB_STEP("fmha_paged_relpos", 0, oasr_b200_fmha_paged_relpos_fp8(w.att, w.qkv4, k_pools[i], v_pools[i], ks, vs,
+                                       static_cast<const uint8_t*>(m.pos_proj) + i * d * 2, m.pos_proj_rows, L * d,
+                                       pos_start, block_table, total_seqlens, B, T, m.heads, blocks_per_seq, block_size,
+                                       num_blocks, scale, dt, stream));
+    } else {
+      OB_STEP("paged_kv_write", 0, oasr_b200_paged_kv_write(k_pools[i], v_pools[i], w.qkv4 + 2 * d * 2, w.qkv4 + 3 * d * 2,
+                                       block_table, cache_seqlens, B, m.heads, T, 64, T * 4 * d, 64, 4 * d, blocks_per_seq,
+                                       block_size, num_blocks, 2, stream));
+      OB_STEP("fmha_paged_relpos", 0, oasr_b200_fmha_paged_relpos(w.att, w.qkv4, k_pools[i], v_pools[i],
+                                       static_cast<const uint8_t*>(m.pos_proj) + i * d * 2, m.pos_proj_rows, L * d,
+                                       pos_start, block_table, total_seqlens, B, T, m.heads, blocks_per_seq, block_size,
+                                       num_blocks, scale, dt, stream));
+    }
     OB_STEP("gemm attn_out", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.att, l.out_w, l.out_b, M, d, d, OASR_ACT_NONE, dt, stream));
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
                                    nullptr, M, d, m.eps, 0, dt, stream));

@@ -588,9 +588,11 @@ extern int g_fmha_relpos_path;
 
 namespace fmha_chunk {   // fmha_chunk.cu: warp-per-(stream, head) kernel for <= 16 query frames
 bool applies(int64_t Tq, int64_t block_size, int64_t blocks_per_seq);
-int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos, int64_t pos_rows, int64_t pos_stride,
-        const int32_t* pos_start, const int32_t* block_table, const int32_t* seqlens, int64_t B, int64_t Tq, int64_t H,
-        int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, double scale, int dtype, cudaStream_t stream);
+bool applies_fp8(int64_t Tq, int64_t block_size, int64_t blocks_per_seq);
+int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const float* k_scale, const float* v_scale, const void* pos,
+        int64_t pos_rows, int64_t pos_stride, const int32_t* pos_start, const int32_t* block_table, const int32_t* seqlens,
+        int64_t B, int64_t Tq, int64_t H, int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, double scale,
+        int dtype, cudaStream_t stream);
 }  // namespace fmha_chunk
 
 }  // namespace ob
@@ -652,8 +654,9 @@ int oasr_b200_fmha_paged_relpos(void* out, const void* qkv4, void* k_pool, void*
              OASR_ERR_ALIGN, "fmha_paged_relpos: operands must be 16-byte aligned");
   OB_REQUIRE(B <= 65535 && H <= 65535, OASR_ERR_INVALID, "fmha_paged_relpos: batch / head count too large");
   if (fmha_chunk::applies(Tq, block_size, blocks_per_seq))
-    return fmha_chunk::run(out, qkv4, k_pool, v_pool, pos, pos_rows, pos_stride, pos_start, block_table, seqlens, B, Tq,
-                           H, blocks_per_seq, block_size, num_blocks, scale, dtype, static_cast<cudaStream_t>(stream));
+    return fmha_chunk::run(out, qkv4, k_pool, v_pool, nullptr, nullptr, pos, pos_rows, pos_stride, pos_start, block_table,
+                           seqlens, B, Tq, H, blocks_per_seq, block_size, num_blocks, scale, dtype,
+                           static_cast<cudaStream_t>(stream));
   const int64_t d = H * D, ld = 4 * d;
   const uint8_t* base = static_cast<const uint8_t*>(qkv4);
   Maps maps;
@@ -676,6 +679,27 @@ int oasr_b200_fmha_paged_relpos(void* out, const void* qkv4, void* k_pool, void*
   p.out = out; p.status = device_status_ptr();
   dim3 grid(1, (unsigned)H, (unsigned)B);
   return dispatch(maps, p, D, dtype, grid, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_fmha_paged_relpos_fp8(void* out, const void* qkv4, void* k_pool, void* v_pool, const float* k_scale,
+                                    const float* v_scale, const void* pos, int64_t pos_rows, int64_t pos_stride,
+                                    const int32_t* pos_start, const int32_t* block_table, const int32_t* seqlens, int64_t B,
+                                    int64_t Tq, int64_t H, int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks,
+                                    double scale, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(B >= 0 && Tq >= 0 && H > 0, OASR_ERR_INVALID, "fmha_paged_relpos_fp8: bad shape");
+  if (B == 0 || Tq == 0) return OASR_OK;
+  OB_REQUIRE(out && qkv4 && k_pool && v_pool && k_scale && v_scale && pos && pos_start && block_table && seqlens,
+             OASR_ERR_INVALID, "fmha_paged_relpos_fp8: null pointer argument");
+  OB_REQUIRE(block_size > 0 && blocks_per_seq > 0 && num_blocks > 0, OASR_ERR_INVALID, "fmha_paged_relpos_fp8: bad page geometry");
+  OB_REQUIRE(fmha_chunk::applies_fp8(Tq, block_size, blocks_per_seq), OASR_ERR_UNSUPPORTED,
+             "fmha_paged_relpos_fp8: at most 16 query frames, pages of 16 or a multiple of 32 frames, at most 64 pages per stream");
+  OB_REQUIRE(is_aligned(out, 16) && is_aligned(qkv4, 16) && is_aligned(k_pool, 16) && is_aligned(v_pool, 16) &&
+                 is_aligned(pos, 16) && pos_stride % 8 == 0,
+             OASR_ERR_ALIGN, "fmha_paged_relpos_fp8: operands must be 16-byte aligned");
+  return fmha_chunk::run(out, qkv4, k_pool, v_pool, k_scale, v_scale, pos, pos_rows, pos_stride, pos_start, block_table,
+                         seqlens, B, Tq, H, blocks_per_seq, block_size, num_blocks, scale, dtype,
+                         static_cast<cudaStream_t>(stream));
 }
 
 int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,

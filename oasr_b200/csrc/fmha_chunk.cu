@@ -16,6 +16,7 @@
 // (oasr/layers/attention/attention.py:388-470) + paged fmha (oasr/functionals/attention.py:369-551):
 // every new frame sees the whole cached window and the whole chunk; keys >= seqlens[b] are masked.
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include <type_traits>
 
@@ -50,6 +51,8 @@ struct Params {
   int blocks_per_seq, block_size, num_blocks;
   void* out;             // (B*Tq, H*D)
   uint32_t* status;
+  const float* k_scale;  // fp8 pages: [H] per-head scales of the K / V codes (x ~ code * scale)
+  const float* v_scale;
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -83,14 +86,24 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-template <typename T>
+// fp8 pages (kFp8): K and V arrive as e4m3 codes (64 bytes per key, plain layout) in the first 4 KB of a stage, the
+// position rows behind them; the warp converts the codes to fp16 into two working tiles in the swizzled layout the
+// ldmatrix path reads ("shared-memory-staged" dequantisation: one cvt per value pair, exact), multiplies q+u by the
+// K scale once when it loads it (as fp16) and the output by the V scale once at the end.  The content product and
+// P.V then run as fp16 MMAs, the position product stays in T; all accumulate in the same fp32 registers.
+// Per warp: 2 stages x 8 KB + 2 x 4 KB working tiles = the same 24 KB as the 16-bit ring.
+template <typename T, bool kFp8>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_pos, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kStageB = kFp8 ? 2 * (kTileBytes / 2) + kTileBytes : kStageBytes;   // fp8: K8 2 KB | V8 2 KB | pos 4 KB
+  constexpr int kPosOff = kFp8 ? kTileBytes : kTileBytes;                           // position rows sit 4 KB into a stage either way
+  using TC = typename std::conditional<kFp8, __half, T>::type;                      // operand type of the content / P.V MMAs
   uint8_t* ring = smem + warp * kStages * kStageBytes;
+  uint8_t* work = ring + kStages * kStageB;                                         // fp8 only: K and V working tiles (fp16)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBars) + warp * kStages;
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(smem + kSmemBars + kWarps * kStages * 8);
   if (threadIdx.x == 0) *abort_flag = 0;
@@ -132,10 +145,21 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         const int c0 = __shfl_sync(0xffffffffu, pg_lo, col1 & 31), c1 = __shfl_sync(0xffffffffu, pg_hi, col1 & 31);
         const int page0 = col0 < 32 ? a0 : a1, page1 = col1 < 32 ? c0 : c1;
         if (lane == 0) {
-          uint8_t* dst = ring + s * kStageBytes;
+          uint8_t* dst = ring + s * kStageB;
           ptx::fence_proxy_async_smem();
-          ptx::mbar_expect_tx(&bars[s], kStageBytes);
-          if (small_pages) {
+          ptx::mbar_expect_tx(&bars[s], kStageB);
+          if constexpr (kFp8) {
+            if (small_pages) {
+              ptx::tma_load_4d(dst, &map_k, 0, 0, h, page0, &bars[s]);
+              ptx::tma_load_4d(dst + 16 * 64, &map_k, 0, 0, h, page1, &bars[s]);
+              ptx::tma_load_4d(dst + kTileBytes / 2, &map_v, 0, 0, h, page0, &bars[s]);
+              ptx::tma_load_4d(dst + kTileBytes / 2 + 16 * 64, &map_v, 0, 0, h, page1, &bars[s]);
+            } else {
+              const int r0 = key0 % p.block_size;
+              ptx::tma_load_4d(dst, &map_k, 0, r0, h, page0, &bars[s]);
+              ptx::tma_load_4d(dst + kTileBytes / 2, &map_v, 0, r0, h, page0, &bars[s]);
+            }
+          } else if (small_pages) {
             ptx::tma_load_4d(dst, &map_k, 0, 0, h, page0, &bars[s]);
             ptx::tma_load_4d(dst + 16 * 128, &map_k, 0, 0, h, page1, &bars[s]);
             ptx::tma_load_4d(dst + 2 * kTileBytes, &map_v, 0, 0, h, page0, &bars[s]);
@@ -145,7 +169,7 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             ptx::tma_load_4d(dst, &map_k, 0, r0, h, page0, &bars[s]);
             ptx::tma_load_4d(dst + 2 * kTileBytes, &map_v, 0, r0, h, page0, &bars[s]);
           }
-          ptx::tma_load_4d(dst + kTileBytes, &map_pos, 0, pos0 + key0, h, 0, &bars[s]);
+          ptx::tma_load_4d(dst + kPosOff, &map_pos, 0, pos0 + key0, h, 0, &bars[s]);
         }
       };
       issue(0, 0);
@@ -166,6 +190,14 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
               a = __ldg(reinterpret_cast<const uint32_t*>(q + r * p.ld + c));
               bb = __ldg(reinterpret_cast<const uint32_t*>(q + r * p.ld + d + c));
             }
+            if constexpr (kFp8) {   // q+u as fp16, times the K scale of this head
+              const float ks = p.k_scale[h];
+              float2 f;
+              if constexpr (std::is_same<T, __nv_bfloat16>::value) f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&a));
+              else f = __half22float2(*reinterpret_cast<__half2*>(&a));
+              const __half2 hq = __floats2half2_rn(f.x * ks, f.y * ks);
+              a = *reinterpret_cast<const uint32_t*>(&hq);
+            }
             qu[kk][e] = a;
             qv[kk][e] = bb;
           }
@@ -180,7 +212,36 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         const int s = it % kStages;
         const bool arrived = ptx::mbar_wait(&bars[s], (it / kStages) & 1u, abort_flag);
         if (!__all_sync(0xffffffffu, arrived)) { ok = false; break; }
-        const uint32_t tile = ptx::smem_u32(ring + s * kStageBytes);
+        const uint32_t stage = ptx::smem_u32(ring + s * kStageB);
+        if constexpr (kFp8) {
+          // 2 x 2 KB of codes -> 2 x 4 KB of fp16 in the swizzled 128-byte-row layout; lane handles 16-byte pieces
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const uint8_t* src = ring + s * kStageB + which * (kTileBytes / 2);
+            uint8_t* dstw = work + which * kTileBytes;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int piece = lane + 32 * u, key = piece >> 2, part = piece & 3;   // 16 codes = d 16*part .. +15 of one key
+              const uint4 c = *reinterpret_cast<const uint4*>(src + piece * 16);
+              const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+              uint32_t hw[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(cw[i] & 0xffffu), __NV_E4M3);
+                const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(cw[i] >> 16), __NV_E4M3);
+                hw[2 * i] = static_cast<uint32_t>(lo.x) | (static_cast<uint32_t>(lo.y) << 16);
+                hw[2 * i + 1] = static_cast<uint32_t>(hi.x) | (static_cast<uint32_t>(hi.y) << 16);
+              }
+              uint8_t* rowp = dstw + key * 128;
+              *reinterpret_cast<uint4*>(rowp + (((2 * part) ^ (key & 7)) << 4)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+              *reinterpret_cast<uint4*>(rowp + (((2 * part + 1) ^ (key & 7)) << 4)) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+            }
+          }
+          __syncwarp();
+        }
+        const uint32_t k_tile = kFp8 ? ptx::smem_u32(work) : stage;
+        const uint32_t v_tile = kFp8 ? ptx::smem_u32(work + kTileBytes) : stage + 2 * kTileBytes;
+        const uint32_t p_tile = stage + kPosOff;
         // ---- S = (q+u).K^T + (q+v).P^T : 16 x 32 in four 8-key accumulators ----
         float sc[4][4];
 #pragma unroll
@@ -191,10 +252,10 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
           for (int kp = 0; kp < 2; ++kp) {
             const uint32_t off = r * 128 + (((kp * 4 + (lane >> 3)) ^ (r & 7)) << 4);
             uint32_t kb[4], pb[4];
-            ldmatrix_x4(kb, tile + off);
-            ldmatrix_x4(pb, tile + kTileBytes + off);
-            mma16816<T>(sc[n], qu[2 * kp], kb[0], kb[1]);
-            mma16816<T>(sc[n], qu[2 * kp + 1], kb[2], kb[3]);
+            ldmatrix_x4(kb, k_tile + off);
+            ldmatrix_x4(pb, p_tile + off);
+            mma16816<TC>(sc[n], qu[2 * kp], kb[0], kb[1]);
+            mma16816<TC>(sc[n], qu[2 * kp + 1], kb[2], kb[3]);
             mma16816<T>(sc[n], qv[2 * kp], pb[0], pb[1]);
             mma16816<T>(sc[n], qv[2 * kp + 1], pb[2], pb[3]);
           }
@@ -230,8 +291,8 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
           const float p2 = exp2f(sc[n][2] - m_use[1]), p3 = exp2f(sc[n][3] - m_use[1]);
           rs[0] += p0 + p1;
           rs[1] += p2 + p3;
-          pa[n >> 1][(n & 1) * 2] = pack2<T>(p0, p1);
-          pa[n >> 1][(n & 1) * 2 + 1] = pack2<T>(p2, p3);
+          pa[n >> 1][(n & 1) * 2] = pack2<TC>(p0, p1);
+          pa[n >> 1][(n & 1) * 2 + 1] = pack2<TC>(p2, p3);
         }
         l_run[0] = l_run[0] * alpha[0] + rs[0];
         l_run[1] = l_run[1] * alpha[1] + rs[1];
@@ -248,9 +309,9 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
           for (int np = 0; np < 4; ++np) {
             const uint32_t off = r * 128 + (((2 * np + (lane >> 4)) ^ (r & 7)) << 4);
             uint32_t vb[4];
-            ldmatrix_x4_trans(vb, tile + 2 * kTileBytes + off);
-            mma16816<T>(o[2 * np], pa[kk], vb[0], vb[1]);
-            mma16816<T>(o[2 * np + 1], pa[kk], vb[2], vb[3]);
+            ldmatrix_x4_trans(vb, v_tile + off);
+            mma16816<TC>(o[2 * np], pa[kk], vb[0], vb[1]);
+            mma16816<TC>(o[2 * np + 1], pa[kk], vb[2], vb[3]);
           }
         }
         __syncwarp();
@@ -262,8 +323,12 @@ fmha_chunk_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
           l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
           l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
         }
-        const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
-        const float inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+        float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
+        float inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+        if constexpr (kFp8) {
+          inv0 *= p.v_scale[h];
+          inv1 *= p.v_scale[h];
+        }
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
           const int c = n * 8 + 2 * t;
@@ -293,18 +358,52 @@ int make_map(CUtensorMap* m, int dtype, const void* base, int64_t rows, int64_t 
   return make_tensor_map(m, tma_dtype(dtype), 4, base, dims, str, box);
 }
 
+// fp8 pool (num_blocks, block_size, H, 64) of one-byte codes: 64-byte rows, plain (unswizzled) boxes
+int make_map_u8(CUtensorMap* m, const void* base, int64_t block_size, int64_t heads, int64_t num_blocks, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)block_size, (uint64_t)heads, (uint64_t)num_blocks};
+  uint64_t str[4] = {0, (uint64_t)heads * D, (uint64_t)D, (uint64_t)block_size * heads * D};
+  uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
+  return make_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 bool applies(int64_t Tq, int64_t block_size, int64_t blocks_per_seq) {
   return g_fmha_chunk_path && Tq <= 16 && (block_size == 16 || block_size % 32 == 0) && blocks_per_seq <= 64;
 }
+bool applies_fp8(int64_t Tq, int64_t block_size, int64_t blocks_per_seq) {
+  return Tq <= 16 && (block_size == 16 || block_size % 32 == 0) && blocks_per_seq <= 64;
+}
 
-int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos, int64_t pos_rows, int64_t pos_stride,
-        const int32_t* pos_start, const int32_t* block_table, const int32_t* seqlens, int64_t B, int64_t Tq, int64_t H,
-        int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, double scale, int dtype, cudaStream_t stream) {
+template <typename T, bool kFp8>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mp, const Params& p, unsigned grid, cudaStream_t stream) {
+  auto kern = fmha_chunk_kernel<T, kFp8>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDynamic);
+    if (e != cudaSuccess)
+      return set_error(OASR_ERR_CUDA, "fmha_paged_relpos: cannot reserve %d bytes of shared memory: %s", kSmemDynamic,
+                       cudaGetErrorString(e));
+    attr_done = true;
+  }
+  launch_pdl(kern, dim3(grid), dim3(kWarps * 32), kSmemDynamic, stream, mk, mv, mp, p);
+  return check_launch("fmha_paged_relpos (chunk kernel) launch");
+}
+
+// k_scale / v_scale null: 16-bit pools; otherwise the pools hold fp8 e4m3 codes with per-head scales.
+int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const float* k_scale, const float* v_scale, const void* pos,
+        int64_t pos_rows, int64_t pos_stride, const int32_t* pos_start, const int32_t* block_table, const int32_t* seqlens,
+        int64_t B, int64_t Tq, int64_t H, int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, double scale,
+        int dtype, cudaStream_t stream) {
   const int64_t d = H * D;
   const int box_rows = block_size == 16 ? 16 : 32;
+  const bool fp8 = k_scale != nullptr;
   CUtensorMap mk, mv, mp;
-  if (int rc = make_map(&mk, dtype, k_pool, block_size, H, num_blocks, H * D, D, block_size * H * D, box_rows)) return rc;
-  if (int rc = make_map(&mv, dtype, v_pool, block_size, H, num_blocks, H * D, D, block_size * H * D, box_rows)) return rc;
+  if (fp8) {
+    if (int rc = make_map_u8(&mk, k_pool, block_size, H, num_blocks, box_rows)) return rc;
+    if (int rc = make_map_u8(&mv, v_pool, block_size, H, num_blocks, box_rows)) return rc;
+  } else {
+    if (int rc = make_map(&mk, dtype, k_pool, block_size, H, num_blocks, H * D, D, block_size * H * D, box_rows)) return rc;
+    if (int rc = make_map(&mv, dtype, v_pool, block_size, H, num_blocks, H * D, D, block_size * H * D, box_rows)) return rc;
+  }
   if (int rc = make_map(&mp, dtype, pos, pos_rows, H, 1, pos_stride, D, pos_stride * pos_rows, kKeys)) return rc;
   Params p{};
   p.qkv4 = static_cast<const uint8_t*>(qkv4);
@@ -314,19 +413,10 @@ int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const void* pos
   p.seqlens = seqlens; p.pos_start = pos_start; p.block_table = block_table;
   p.blocks_per_seq = (int)blocks_per_seq; p.block_size = (int)block_size; p.num_blocks = (int)num_blocks;
   p.out = out; p.status = device_status_ptr();
+  p.k_scale = k_scale; p.v_scale = v_scale;
   const unsigned grid = (unsigned)((B * H + kWarps - 1) / kWarps);
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
-    auto kern = fmha_chunk_kernel<T>;
-    static bool attr_done = false;
-    if (!attr_done) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDynamic);
-      if (e != cudaSuccess)
-        return set_error(OASR_ERR_CUDA, "fmha_paged_relpos: cannot reserve %d bytes of shared memory: %s", kSmemDynamic,
-                         cudaGetErrorString(e));
-      attr_done = true;
-    }
-    launch_pdl(kern, dim3(grid), dim3(kWarps * 32), kSmemDynamic, stream, mk, mv, mp, p);
-    return check_launch("fmha_paged_relpos (chunk kernel) launch");
+    return fp8 ? launch<T, true>(mk, mv, mp, p, grid, stream) : launch<T, false>(mk, mv, mp, p, grid, stream);
   });
 }
 

@@ -5,6 +5,8 @@
 // Index rule (oasr/cache/paged_kv.py:23-40 in the reference): logical frame
 // pos = offsets[b] + t of stream b lives at physical pool row
 //   block_table[b, pos / block_size] * block_size + pos % block_size.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace ob {
@@ -119,6 +121,60 @@ __global__ void __launch_bounds__(256) move_rows_kernel(uint8_t* __restrict__ ou
   }
 }
 
+// fp8 page write: the same index rule, every 16-bit value divided by its head's scale and rounded to e4m3
+// (round to nearest even, saturating at +-448).  One thread converts 8 consecutive values of K and of V.
+struct PagedWriteFp8Args {
+  uint8_t *k_pool, *v_pool;
+  const void *k_new, *v_new;
+  const float *k_scale, *v_scale;   // [Hkv]
+  const int32_t* block_table;
+  const int32_t* offsets;
+  int64_t B, Hkv, T, D;
+  int64_t stride_b, stride_h, stride_t;  // elements
+  int64_t blocks_per_seq, block_size, num_blocks;
+};
+
+template <typename T>
+__device__ __forceinline__ uint2 to_e4m3x8(const Pack<T>& v, float inv) {
+  uint32_t w[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(Elem<T>::to_f(v.v[hh * 4]) * inv, Elem<T>::to_f(v.v[hh * 4 + 1]) * inv),
+                                                 __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(Elem<T>::to_f(v.v[hh * 4 + 2]) * inv, Elem<T>::to_f(v.v[hh * 4 + 3]) * inv),
+                                                 __NV_SATFINITE, __NV_E4M3);
+    w[hh] = lo | (hi << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) paged_kv_write_fp8_kernel(PagedWriteFp8Args a) {
+  const int64_t pieces = a.D / 8;
+  const int64_t total = a.B * a.T * a.Hkv * pieces;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t piece = i % pieces;
+    int64_t r = i / pieces;
+    const int64_t h = r % a.Hkv;
+    r /= a.Hkv;
+    const int64_t t = r % a.T;
+    const int64_t b = r / a.T;
+    const int64_t pos = static_cast<int64_t>(a.offsets[b]) + t;
+    const int64_t logical = pos / a.block_size;
+    if (pos < 0 || logical >= a.blocks_per_seq) continue;  // outside the table: dropped, never written
+    const int64_t page = a.block_table[b * a.blocks_per_seq + logical];
+    if (page < 0 || page >= a.num_blocks) continue;
+    const int64_t dst_row = page * a.block_size + pos % a.block_size;
+    const int64_t dst = (dst_row * a.Hkv + h) * a.D + piece * 8;
+    const int64_t src = b * a.stride_b + h * a.stride_h + t * a.stride_t + piece * 8;
+    const Pack<T> kv = ld128(static_cast<const T*>(a.k_new) + src);
+    const Pack<T> vv = ld128(static_cast<const T*>(a.v_new) + src);
+    *reinterpret_cast<uint2*>(a.k_pool + dst) = to_e4m3x8<T>(kv, 1.f / a.k_scale[h]);
+    *reinterpret_cast<uint2*>(a.v_pool + dst) = to_e4m3x8<T>(vv, 1.f / a.v_scale[h]);
+  }
+}
+
 unsigned grid_for(int64_t items) {
   int64_t g = (items + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
@@ -162,6 +218,29 @@ int oasr_b200_paged_kv_write(void* k_pool, void* v_pool, const void* k_new, cons
     else paged_kv_write_kernel<4><<<grid_for(B * T * Hkv * D), 256, 0, s>>>(a);
   }
   return check_launch("paged_kv_write launch");
+}
+
+int oasr_b200_paged_kv_write_fp8(void* k_pool, void* v_pool, const void* k_new, const void* v_new, const float* k_scale,
+                                 const float* v_scale, const int32_t* block_table, const int32_t* offsets, int64_t B,
+                                 int64_t Hkv, int64_t T, int64_t D, int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                                 int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(k_pool && v_pool && k_new && v_new && k_scale && v_scale && block_table && offsets, OASR_ERR_INVALID,
+             "paged_kv_write_fp8: null pointer argument");
+  OB_REQUIRE(B >= 0 && Hkv > 0 && T >= 0 && D > 0 && blocks_per_seq > 0 && block_size > 0 && num_blocks > 0,
+             OASR_ERR_INVALID, "paged_kv_write_fp8: bad shape");
+  OB_REQUIRE(D % 8 == 0 && stride_b % 8 == 0 && stride_h % 8 == 0 && stride_t % 8 == 0 && is_aligned(k_new, 16) &&
+                 is_aligned(v_new, 16) && is_aligned(k_pool, 8) && is_aligned(v_pool, 8),
+             OASR_ERR_ALIGN, "paged_kv_write_fp8: head_dim and strides must be multiples of 8 elements, sources 16-byte aligned");
+  if (B == 0 || T == 0) return OASR_OK;
+  PagedWriteFp8Args a{static_cast<uint8_t*>(k_pool), static_cast<uint8_t*>(v_pool), k_new, v_new, k_scale, v_scale,
+                      block_table, offsets, B, Hkv, T, D, stride_b, stride_h, stride_t, blocks_per_seq, block_size, num_blocks};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = grid_for(B * T * Hkv * (D / 8));
+  return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
+    paged_kv_write_fp8_kernel<T_><<<grid, 256, 0, s>>>(a);
+    return check_launch("paged_kv_write_fp8 launch");
+  });
 }
 
 int oasr_b200_paged_kv_gather(void* k_out, void* v_out, const void* k_pool, const void* v_pool,

@@ -315,13 +315,30 @@ class ConformerCTC:
     # ------------------------------------------------------------------ entry points
     # ------------------------------------------------------------------ streaming
     def new_streaming_cache(self, max_streams: int, max_past_frames: int, chunk_frames: int = 16, block_size: int = 16,
-                            seed: Optional[int] = 0):
-        """Page pools, block table and conv left-context buffers for ``max_streams`` concurrent streams."""
+                            seed: Optional[int] = 0, kv_scales: Optional[torch.Tensor] = None):
+        """Page pools, block table and conv left-context buffers for ``max_streams`` concurrent streams.
+        ``kv_scales`` ``(layers, 2, heads)`` fp32 (K then V, e.g. from ``calibrate_kv_scales``) switches the
+        pools to fp8 e4m3 codes with those per-head scales."""
         from .streaming import StreamingCache
 
         c = self.cfg
         return StreamingCache(c.layers, c.heads, c.head_dim, c.d_model, c.kernel, max_streams, max_past_frames,
-                              chunk_frames, block_size, self.device, self.dtype, seed)
+                              chunk_frames, block_size, self.device, self.dtype, seed, kv_scales)
+
+    def calibrate_kv_scales(self, windows, chunk_frames: int = 16, margin: float = 1.0) -> torch.Tensor:
+        """Per (layer, head) fp8 scales ``amax / 448`` of the keys and values seen while the feature windows
+        ``windows`` (an iterable of ``(B, window, F)`` tensors, consecutive chunks of the same B streams) run through
+        a 16-bit cache.  Returns ``(layers, 2, heads)`` fp32."""
+        c = self.cfg
+        windows = list(windows)
+        B = windows[0].size(0)
+        cache = self.new_streaming_cache(B, max_past_frames=chunk_frames * len(windows), chunk_frames=chunk_frames, seed=None)
+        for xs in windows:
+            self.forward_chunk_paged(xs.to(self.device), list(range(B)), cache)
+        k = cache.k_pool.float().abs().amax(dim=(1, 2, 4))     # (L, H)
+        v = cache.v_pool.float().abs().amax(dim=(1, 2, 4))
+        scales = torch.stack([k, v], dim=1) * (margin / 448.0)
+        return torch.clamp(scales, min=1e-8).contiguous()
 
     def forward_chunk_paged(self, xs: torch.Tensor, slots, cache, return_argmax: bool = False):
         """One streaming chunk for the streams in ``slots``: ``xs (B, window, F)`` feature windows ->
@@ -365,7 +382,7 @@ class ConformerCTC:
         argmax = torch.empty(B, T, device=xs.device, dtype=torch.int32)
         _lib.call("oasr_b200_conformer_chunk_paged", ctypes.byref(self._native_model), _p(rows), B, T, kp, vp, _p(table),
                   _p(cached), _p(total), _p(pos_start), table.size(1), cache.block_size, cache.num_blocks,
-                  _p(cache.cnn_state), cache.max_streams, _p(slot_ids), ctypes.c_void_p(ws.data_ptr() + off),
+                  _p(cache.kv_scales), _p(cache.cnn_state), cache.max_streams, _p(slot_ids), ctypes.c_void_p(ws.data_ptr() + off),
                   ws.numel() - off, _p(log_probs), _p(argmax),
                   ctypes.c_void_p(torch.cuda.current_stream(xs.device).cuda_stream))
         cache.commit(slots)

@@ -138,3 +138,33 @@ def fmha_paged_relpos(qkv4: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
               pos.stride(0), _p(pos_start), _p(block_table), _p(seqlens), B, Tq, heads, block_table.size(1),
               k_pool.size(1), k_pool.size(0), float(scale), _DTYPE_ID[qkv4.dtype], _stream(qkv4))
     return out
+
+
+def fmha_paged_relpos_fp8(qkv4: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, k_scale: torch.Tensor,
+                          v_scale: torch.Tensor, pos: torch.Tensor, pos_start: torch.Tensor, block_table: torch.Tensor,
+                          seqlens: torch.Tensor, heads: int, scale: float, out=None) -> torch.Tensor:
+    """``fmha_paged_relpos`` over fp8 pages: uint8 pools of e4m3 codes and per-head fp32 scales ``(H,)``."""
+    _need_cuda(qkv4, k_pool, v_pool, k_scale, v_scale, pos, block_table, seqlens, pos_start)
+    B, Tq, d4 = qkv4.shape
+    d = d4 // 4
+    if out is None:
+        out = torch.empty(B, Tq, d, device=qkv4.device, dtype=qkv4.dtype)
+    _lib.call("oasr_b200_fmha_paged_relpos_fp8", _p(out), _p(qkv4), _p(k_pool), _p(v_pool), _p(k_scale), _p(v_scale),
+              _p(pos), pos.size(0), pos.stride(0), _p(pos_start), _p(block_table), _p(seqlens), B, Tq, heads,
+              block_table.size(1), k_pool.size(1), k_pool.size(0), float(scale), _DTYPE_ID[qkv4.dtype], _stream(qkv4))
+    return out
+
+
+def paged_kv_write_fp8(k_pool: torch.Tensor, v_pool: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                       k_scale: torch.Tensor, v_scale: torch.Tensor, block_table: torch.Tensor,
+                       offsets: torch.Tensor) -> None:
+    """Quantising page write: ``k_new / v_new (B, H, T, D)`` 16-bit views (unit stride along D) -> e4m3 codes
+    ``x / scale[h]`` in uint8 pools ``(num_blocks, block_size, H, D)`` at logical positions ``offsets[b] + t``."""
+    _need_cuda(k_pool, v_pool, k_new, v_new, k_scale, v_scale, block_table, offsets)
+    B, H, T, D = k_new.shape
+    if k_new.stride() != v_new.stride() or k_new.stride(3) != 1:
+        raise ValueError("k_new and v_new must share strides and have unit stride along D")
+    sb, sh, st, _ = k_new.stride()
+    _lib.call("oasr_b200_paged_kv_write_fp8", _p(k_pool), _p(v_pool), _p(k_new), _p(v_new), _p(k_scale), _p(v_scale),
+              _p(block_table), _p(offsets), B, H, T, D, sb, sh, st, block_table.size(1), k_pool.size(1), k_pool.size(0),
+              _DTYPE_ID[k_new.dtype], _stream(k_new))

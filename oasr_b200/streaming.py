@@ -18,7 +18,7 @@ import torch
 class StreamingCache:
     def __init__(self, num_layers: int, heads: int, head_dim: int, d_model: int, conv_kernel: int, max_streams: int,
                  max_past_frames: int, chunk_frames: int = 16, block_size: int = 16, device="cuda",
-                 dtype=torch.bfloat16, seed: Optional[int] = 0):
+                 dtype=torch.bfloat16, seed: Optional[int] = 0, kv_scales: Optional[torch.Tensor] = None):
         if chunk_frames % block_size:
             raise ValueError("a chunk must be a whole number of pages")
         self.L, self.H, self.D, self.d, self.K = num_layers, heads, head_dim, d_model, conv_kernel
@@ -29,7 +29,16 @@ class StreamingCache:
         self.num_blocks = max_streams * self.max_blocks
         self.device = torch.device(device)
         # pools are zero-initialised: stale page contents must be finite (they are masked, not skipped)
-        self.k_pool = torch.zeros(num_layers, self.num_blocks, block_size, heads, head_dim, device=self.device, dtype=dtype)
+        # kv_scales (layers, 2, heads) fp32: the pools hold fp8 e4m3 codes (one byte per element, code 0 = 0.0)
+        self.kv_scales = None
+        if kv_scales is not None:
+            if tuple(kv_scales.shape) != (num_layers, 2, heads):
+                raise ValueError("kv_scales must be (layers, 2, heads)")
+            self.kv_scales = kv_scales.to(self.device, torch.float32).contiguous()
+            dtype_pool = torch.uint8
+        else:
+            dtype_pool = dtype
+        self.k_pool = torch.zeros(num_layers, self.num_blocks, block_size, heads, head_dim, device=self.device, dtype=dtype_pool)
         self.v_pool = torch.zeros_like(self.k_pool)
         self.cnn_state = torch.zeros(num_layers, max_streams, conv_kernel - 1, d_model, device=self.device, dtype=dtype)
         # physical pages are handed out in a random order (a seeded permutation)

@@ -299,3 +299,13 @@ def gemm_q8(a_vals: torch.Tensor, a_scale: torch.Tensor, b_vals: torch.Tensor, b
         n = y.size(1) // 2
         return y[:, :n] * torch.sigmoid(y[:, n:])
     return globals()["activation"](y, activation) if activation >= 0 else y
+
+
+def quantize_kv_fp8(x: torch.Tensor, scale: torch.Tensor):
+    """fp8 page codes of keys / values ``x (..., H, D)`` with per-head scales ``scale (H,)``, the arithmetic of
+    the CUDA page write in fp32: ``code = e4m3(x * (1 / scale[h]))`` (round to nearest even; inputs are expected
+    within +-448 * scale).  Returns ``(codes uint8, dequantised fp32 = value(code) * scale[h])``."""
+    inv = (1.0 / scale.float())[:, None]
+    y = (x.float() * inv).clamp(-448.0, 448.0)
+    q = y.to(torch.float8_e4m3fn)
+    return q.view(torch.uint8), q.float() * scale.float()[:, None]

@@ -61,3 +61,73 @@ def test_streaming_is_independent_of_batch_composition():
         a = model.forward_chunk_paged(xs, [3, 1], both)
         b = model.forward_chunk_paged(xs[1:2], [0], alone)
         assert torch.equal(a[1], b[0])
+
+
+def test_fp8_page_write_is_bit_exact_and_fp8_attention_matches_the_dequantised_reference():
+    from oasr_b200 import fused
+    from oracle import ops as O
+
+    torch.manual_seed(31)
+    B, H, D, Tq, bs, hist = 19, 8, 64, 16, 16, 272
+    d = H * D
+    bps = hist // bs + 1
+    num_blocks = B * bps + 2
+    dev = "cuda"
+    k_scale = (torch.rand(H) * 0.01 + 0.005).to(dev)
+    v_scale = (torch.rand(H) * 0.01 + 0.005).to(dev)
+    table = torch.randperm(num_blocks, device=dev)[: B * bps].view(B, bps).int()
+    seqlens = torch.randint(Tq, hist + 1, (B,), device=dev, dtype=torch.int32)
+    k_pool = torch.zeros(num_blocks, bs, H, D, dtype=torch.uint8, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    # fill every stream's history through the quantising page write, 16 frames at a time
+    hist_k = (torch.randn(B, hist + Tq, H, D) * 1.5).bfloat16().to(dev)
+    hist_v = (torch.randn(B, hist + Tq, H, D) * 1.5).bfloat16().to(dev)
+    for c in range(0, hist + Tq, Tq):
+        off = torch.full((B,), c, dtype=torch.int32, device=dev)
+        fused.paged_kv_write_fp8(k_pool, v_pool, hist_k[:, c:c + Tq].permute(0, 2, 1, 3), hist_v[:, c:c + Tq].permute(0, 2, 1, 3),
+                                 k_scale, v_scale, table, off)
+    want_k, deq_k = O.quantize_kv_fp8(hist_k.cpu(), k_scale.cpu())
+    want_v, deq_v = O.quantize_kv_fp8(hist_v.cpu(), v_scale.cpu())
+    for b in (0, B - 1):
+        idx = (table[b].long()[:, None] * bs + torch.arange(bs, device=dev)[None]).reshape(-1)[: hist + Tq]
+        assert torch.equal(k_pool.view(-1, H, D)[idx].cpu(), want_k[b])
+        assert torch.equal(v_pool.view(-1, H, D)[idx].cpu(), want_v[b])
+    pos_start = torch.randint(0, 3000, (B,), device=dev, dtype=torch.int32)
+    pos = torch.randn(5000, d, device=dev).bfloat16()
+    qkv4 = (torch.randn(B, Tq, 4 * d, device=dev) * 0.5).bfloat16()
+    scale = D ** -0.5
+    got = fused.fmha_paged_relpos_fp8(qkv4, k_pool, v_pool, k_scale, v_scale, pos, pos_start, table, seqlens, H, scale).float().cpu()
+    assert ob.device_status() == 0
+    for b in range(B):
+        n = int(seqlens[b])
+        pp = pos[int(pos_start[b]): int(pos_start[b]) + n].float().cpu().view(n, H, D)
+        qu = qkv4[b, :, :d].float().cpu().view(Tq, H, D)
+        qv = qkv4[b, :, d:2 * d].float().cpu().view(Tq, H, D)
+        s = (torch.einsum("qhd,khd->hqk", qu, deq_k[b, :n]) + torch.einsum("qhd,khd->hqk", qv, pp)) * scale
+        want = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), deq_v[b, :n]).reshape(Tq, d)
+        err = (got[b] - want).abs().max().item()
+        assert err < 3e-2 * max(1.0, want.abs().max().item()), (b, n, err)
+
+
+def test_streaming_with_fp8_pages_reaches_the_cosine_gate_against_16_bit_pages():
+    case = cases.STREAM_CASE
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats = cases.make_stream_features(case).cuda()
+    model = ConformerCTC(_cfg(cfg), P)
+    max_past = case["num_left_chunks"] * case["chunk_size"]
+    windows = [feats[:, c * case["step"]: c * case["step"] + case["window"]] for c in range(case["chunks"])]
+    scales = model.calibrate_kv_scales(windows[:4], case["chunk_size"], margin=1.5)   # first four chunks, 50 % headroom
+    assert scales.shape == (cfg.layers, 2, cfg.heads) and (scales > 0).all()
+    ref_cache = model.new_streaming_cache(2, max_past, seed=1)
+    q_cache = model.new_streaming_cache(2, max_past, seed=2, kv_scales=scales)
+    assert q_cache.k_pool.dtype == torch.uint8
+    a, b = [], []
+    for xs in windows:
+        a.append(model.forward_chunk_paged(xs, [0, 1], ref_cache)[..., :cfg.vocab].float())
+        b.append(model.forward_chunk_paged(xs, [1, 0], q_cache)[..., :cfg.vocab].float())
+    assert ob.device_status() == 0
+    a, b = torch.stack(a).flatten().double(), torch.stack(b).flatten().double()
+    cos = torch.nn.functional.cosine_similarity(a, b, dim=0).item()
+    print(f"fp8 pages vs 16-bit pages: cosine {cos:.6f}, max-abs {(a - b).abs().max().item():.3e}")
+    assert cos >= 0.999, cos
