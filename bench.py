@@ -233,11 +233,12 @@ def run_streaming(args):
     streams, window, chunk, max_past = args.batch if args.batch != 64 else 256, 67, 16, 256
     cfg = dataclasses.replace(model_config(args.layers), causal=True)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device="cuda:0", dtype=torch.bfloat16)
-    cache = model.new_streaming_cache(streams, max_past, chunk_frames=chunk, seed=5)
     slots = list(range(streams))
     g = torch.Generator().manual_seed(7)
     host = [torch.randn(streams, window, 80, generator=g).pin_memory() for _ in range(8)]
     dev = [h.cuda() for h in host]
+    kv_scales = model.calibrate_kv_scales([d[:16] for d in dev[:4]], chunk, margin=1.5) if args.kv == "fp8" else None
+    cache = model.new_streaming_cache(streams, max_past, chunk_frames=chunk, seed=5, kv_scales=kv_scales)
     warm = max(args.warmup, max_past // chunk + 1)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     sampler = ClockSampler(0)
@@ -279,7 +280,7 @@ def run_streaming(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"streaming conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002: {streams} streams x 1 chunk "
                                f"(window {window} frames -> {chunk} encoder frames), history {max_past} frames in 16-frame pages, "
-                               "random page order, bf16 K/V", "l2": "256 MiB flush write between steps",
+                               f"random page order, {'fp8 e4m3 K/V pages with per-head scales' if args.kv == 'fp8' else 'bf16 K/V'}", "l2": "256 MiB flush write between steps",
                    "audio_seconds_per_step": audio / args.steps},
         "e2e": {"value": audio / e2e_s, "unit": "audio-s/s", "h2d_bytes_per_step": int(host[0].numel() * 4),
                 "d2h_bytes_per_step": int(toks.numel() * 4),
@@ -298,6 +299,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--pdl", action="store_true", help="launch the hot kernels with programmatic stream serialisation (comparison run)")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"],
+                    help="streaming workload: K/V page format (fp8 = e4m3 codes with per-head scales calibrated on four chunks)")
     ap.add_argument("--quant", default="none", choices=["none", "fp8", "int8"],
                     help="run the eight Linear GEMMs of every layer on 8-bit operands (not the headline dtype)")
     ap.add_argument("--batch", type=int, default=64, help="utterances per step (64 = the headline workload)")
