@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (it is not on the GPU box):
 
-    OASR_REFERENCE=/root/reference python tests/golden/make_golden.py
+    OASR_REFERENCE=<path of the reference checkout> python tests/golden/make_golden.py
 
 The script imports the reference package with its torch backend
 (``OASR_LAYERS_BACKEND=torch OASR_FUSED_ADDNORM=0``), rebinds the two call
@@ -22,7 +22,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
 sys.path.insert(0, str(ROOT))
-REF = os.environ.get("OASR_REFERENCE", "/root/reference")
+REF = os.environ.get("OASR_REFERENCE")
+if not REF:
+    raise SystemExit("set OASR_REFERENCE to the path of the reference checkout")
 os.environ["OASR_LAYERS_BACKEND"] = "torch"
 os.environ["OASR_FUSED_ADDNORM"] = "0"
 sys.path.insert(0, REF)
