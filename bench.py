@@ -294,7 +294,7 @@ def main():
     ap.add_argument("--workload", default="offline", choices=["offline", "streaming"],
                     help="offline = the headline packed batch; streaming = 256 streams x one paged chunk per step")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -134,3 +134,33 @@ def test_subsample_conv1_matches_conv2d(dtype):
     lim = torch.tensor([33, 5, 0], dtype=torch.int32).cuda()
     part = fused.subsample_conv1(feats.cuda(), w.cuda(), b.cuda(), dtype, t1_limit=lim)
     assert torch.equal(part[0], got[0]) and torch.equal(part[1, :5], got[1, :5])
+
+
+def test_ragged_batch_with_too_short_and_minimal_utterances():
+    """Edge cases of the packed pipeline: an utterance shorter than the subsampling window (no output frame), one
+    that gives exactly one frame, and the pipelined greedy search over several batches.  The other utterances must
+    come out exactly as without the degenerate ones, and an all-empty batch must return empty results."""
+    case = cases.MODEL_CASES["tiny"]
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    lengths = [int(x) for x in lengths]
+    model = ConformerCTC(_cfg(cfg), P)
+    base, base_len = model.forward_offline_packed(feats.cuda(), lengths)
+    T = feats.size(1)
+    extra = torch.randn(2, T, feats.size(2), generator=torch.Generator().manual_seed(1))
+    mixed = torch.cat([extra[:1], feats, extra[1:]], 0)                     # [too short] + batch + [one frame]
+    mixed_len = [5] + lengths + [7]
+    lp, out_len = model.forward_offline_packed(mixed.cuda(), mixed_len)
+    assert out_len.tolist() == [0] + base_len.tolist() + [1]
+    for b in range(len(lengths)):
+        k = int(base_len[b])
+        assert torch.equal(lp[b + 1, :k], base[b, :k])
+    assert torch.isfinite(lp[-1, :1]).all()
+    hyps = list(model.greedy_search_batches([(mixed.pin_memory(), mixed_len), (feats.pin_memory(), lengths)]))
+    assert len(hyps) == 2 and len(hyps[0]) == len(mixed_len) and hyps[0][0] == []
+    assert hyps[0][1:-1] == hyps[1] == model.greedy_search(feats.cuda(), lengths)
+    empty_lp, empty_len = model.forward_offline_packed(extra.cuda(), [3, 6])
+    assert empty_len.tolist() == [0, 0] and empty_lp.shape[0] == 2
+    assert model.greedy_search(extra.cuda(), [3, 6]) == [[], []]
+    assert ob.device_status() == 0
