@@ -337,7 +337,9 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <typename T, int K, bool kAffine, bool kAct>
+// kAct: 0 = none, 1 = swish, 2 = any other id (run-time switch).  Swish is separate so that the unrolled tap
+// loop does not carry the never-taken activations between the instructions it executes (instruction fetch).
+template <typename T, int K, bool kAffine, int kAct>
 __global__ void __launch_bounds__(256) dwconv_stream_kernel(DwArgs a) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
   ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
@@ -398,7 +400,10 @@ __global__ void __launch_bounds__(256) dwconv_stream_kernel(DwArgs a) {
 #pragma unroll
     for (int k = 0; k < K; ++k) acc = __ffma2_rn(x[(j + k) % K], w[k], acc);
     if constexpr (kAffine) acc = __ffma2_rn(acc, sc, sh);
-    if constexpr (kAct) {
+    if constexpr (kAct == 1) {
+      acc.x = swish_fast(acc.x);
+      acc.y = swish_fast(acc.y);
+    } else if constexpr (kAct == 2) {
       acc.x = apply_act_fast(acc.x, a.act);
       acc.y = apply_act_fast(acc.y, a.act);
     }
@@ -416,11 +421,16 @@ int launch_stream(const DwArgs& a, int max_out_len, cudaStream_t s) {
     dim3 block(threads);
     dim3 grid((max_out_len + kST - 1) / kST, (pairs + threads - 1) / threads, static_cast<unsigned>(a.batch));
     const bool affine = a.post_scale != nullptr;
-    const bool act = a.act != OASR_ACT_NONE;
-    if (affine && act) launch_pdl(dwconv_stream_kernel<T, K, true, true>, grid, block, 0, s, a);
-    else if (affine) launch_pdl(dwconv_stream_kernel<T, K, true, false>, grid, block, 0, s, a);
-    else if (act) launch_pdl(dwconv_stream_kernel<T, K, false, true>, grid, block, 0, s, a);
-    else launch_pdl(dwconv_stream_kernel<T, K, false, false>, grid, block, 0, s, a);
+    const int act = a.act == OASR_ACT_NONE ? 0 : (a.act == OASR_ACT_SWISH ? 1 : 2);
+    if (affine) {
+      if (act == 1) launch_pdl(dwconv_stream_kernel<T, K, true, 1>, grid, block, 0, s, a);
+      else if (act == 0) launch_pdl(dwconv_stream_kernel<T, K, true, 0>, grid, block, 0, s, a);
+      else launch_pdl(dwconv_stream_kernel<T, K, true, 2>, grid, block, 0, s, a);
+    } else {
+      if (act == 1) launch_pdl(dwconv_stream_kernel<T, K, false, 1>, grid, block, 0, s, a);
+      else if (act == 0) launch_pdl(dwconv_stream_kernel<T, K, false, 0>, grid, block, 0, s, a);
+      else launch_pdl(dwconv_stream_kernel<T, K, false, 2>, grid, block, 0, s, a);
+    }
     return check_launch("depthwise_conv1d (streaming) kernel launch");
   }
 }
