@@ -1,0 +1,148 @@
+"""FastConformer / Nemotron encoder LAYER STACK on the sm_100a operators (offline, padded batch).
+
+The composition the reference's ``NemotronEncoderLayer.forward`` serves
+(oasr/models/nemotron/encoder.py:217-267): macaron FFNs with SiLU, Transformer-XL relative-position
+attention with a ``rel_shift``-ed position bias and the chunked-limited window
+(encoder.py:82-149, 300-359), conv module with a causal depthwise conv and LayerNorm+SiLU
+(encoder.py:150-214), fused add+LayerNorm between the sub-layers, fp32 residual stream.
+Every contraction, normalisation, activation, convolution and the attention run on this package's
+kernels (head_dim 128 attention with an additive bias, ``layer_norm_activation``, causal
+``depthwise_conv1d``); the position bias is built by one batched GEMM against the projected
+relative table and shifted with the same pad/view identity as the reference, in torch.
+The 8x depthwise-separable subsampling front end and the RNN-T head are outside this module: the
+input is the post-subsampling hidden state ``(B, T, C)``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List
+
+import torch
+
+from . import functional as OF
+from . import fused
+from .attention import fmha
+
+MASK_FLOOR = -1.0e4   # finite additive floor of a masked key (encoder.py:80)
+_SWISH = 2
+
+
+class FastConformerLayers:
+    def __init__(self, hidden: int, heads: int, ffn: int, layers: int, kernel: int, sliding_window: int, lookahead: int,
+                 params: Dict[str, torch.Tensor], device="cuda", dtype: torch.dtype = torch.bfloat16, eps: float = 1e-5):
+        if hidden % heads or hidden // heads not in (64, 128):
+            raise ValueError("head_dim must be 64 or 128")
+        self.C, self.H, self.D, self.F, self.L, self.K = hidden, heads, hidden // heads, ffn, layers, kernel
+        self.left, self.right, self.eps = sliding_window - 1, lookahead, eps
+        self.device, self.dtype = torch.device(device), dtype
+        w = lambda t: t.detach().to(torch.float32).to(dtype).to(self.device).contiguous()
+        f = lambda t: t.detach().to(torch.float32).to(self.device).contiguous()
+        opt = lambda k: w(params[k]) if k in params else None
+        self.layers: List[dict] = []
+        for i in range(layers):
+            p = f"layers.{i}."
+            a, c = p + "self_attn.", p + "conv."
+            lw = {}
+            for ff in ("feed_forward1", "feed_forward2"):
+                lw[ff] = (w(params[p + ff + ".linear1.weight"]), opt(p + ff + ".linear1.bias"),
+                          w(params[p + ff + ".linear2.weight"]), opt(p + ff + ".linear2.bias"))
+            # q projected twice, once per global bias: [Wq; Wq; Wk; Wv] with [bq+u; bq+v; bk; bv] (the biases are
+            # added in fp32 here, as the packed Conformer path does)
+            wq, wk, wv = (params[a + n + ".weight"].float() for n in ("q_proj", "k_proj", "v_proj"))
+            zero = torch.zeros(hidden)
+            bq, bk, bv = (params.get(a + n + ".bias", zero).float() for n in ("q_proj", "k_proj", "v_proj"))
+            u, v = params[a + "bias_u"].float().reshape(-1), params[a + "bias_v"].float().reshape(-1)
+            lw["qkv4"] = (w(torch.cat([wq, wq, wk, wv], 0)), w(torch.cat([bq + u, bq + v, bk, bv], 0)))
+            lw["o"] = (w(params[a + "o_proj.weight"]), opt(a + "o_proj.bias"))
+            lw["rel"] = w(params[a + "relative_k_proj.weight"])
+            lw["pw1"] = (w(params[c + "pointwise_conv1.weight"].squeeze(-1)), opt(c + "pointwise_conv1.bias"))
+            lw["dw"] = (w(params[c + "depthwise_conv.weight"].reshape(kernel, hidden)), opt(c + "depthwise_conv.bias"))
+            lw["conv_norm"] = (w(params[c + "norm.weight"]), w(params[c + "norm.bias"]))
+            lw["pw2"] = (w(params[c + "pointwise_conv2.weight"].squeeze(-1)), opt(c + "pointwise_conv2.bias"))
+            for n in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
+                lw[n] = (w(params[p + n + ".weight"]), w(params[p + n + ".bias"]))
+            self.layers.append(lw)
+
+    # ---- host-side tables (lengths are host values: no device synchronisation) ----
+    def _position_table(self, T: int) -> torch.Tensor:
+        inv_freq = 1.0 / (10000.0 ** (torch.arange(0, self.C, 2, dtype=torch.float32) / self.C))
+        positions = torch.arange(T - 1, -T, -1, dtype=torch.float32)
+        freqs = torch.outer(positions, inv_freq)
+        table = torch.stack([freqs.sin(), freqs.cos()], dim=-1).reshape(freqs.size(0), self.C)
+        return table.to(self.dtype).to(self.device)            # (2T-1, C)
+
+    def _masks(self, T: int, lengths: List[int]):
+        chunk = self.right + 1
+        left_chunks = self.left // chunk if self.left >= 0 else T
+        qc = torch.arange(T).div(chunk, rounding_mode="trunc")
+        diff = qc.unsqueeze(1) - qc.unsqueeze(0)
+        window = (diff >= 0) & (diff <= left_chunks)
+        keep = torch.arange(T).unsqueeze(0) < torch.tensor(lengths).unsqueeze(1)
+        attn_mask = window.view(1, 1, T, T) & keep.view(-1, 1, 1, T)     # (B, 1, T, T)
+        silent = attn_mask.logical_not().all(dim=-1).transpose(1, 2)     # (B, T, 1)
+        return attn_mask.to(self.device), (silent.to(self.device) if bool(silent.any()) else None)
+
+    # ---- one layer ----
+    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, attn_mask, silent, B: int, T: int) -> torch.Tensor:
+        C, H, D = self.C, self.H, self.D
+        qkv4 = OF.gemm(h, *lw["qkv4"]).view(B, T, 4, H, D)
+        qu, qv, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(4))          # (B, H, T, D) views
+        rel_k = OF.gemm(rel_table, lw["rel"]).view(-1, H, D)                          # (2T-1, H, D)
+        # (q + v) against the projected table, one batched GEMM over (b, h): (B*H, T, D) x (B*H, 2T-1, D)^T
+        a = qv.reshape(B * H, T, D)
+        b = rel_k.permute(1, 0, 2).unsqueeze(0).expand(B, H, 2 * T - 1, D).reshape(B * H, 2 * T - 1, D)
+        P = 2 * T - 1
+        Pp = (P + 7) // 8 * 8                                                         # GEMM needs N % 8 == 0
+        if Pp != P:
+            b = torch.nn.functional.pad(b, (0, 0, 0, Pp - P))
+        bd = OF.bmm(a.contiguous(), b.contiguous())[..., :P].reshape(B, H, T, P)
+        # Transformer-XL shift (pad one column, reinterpret (T, P+1) as (P+1, T), drop the first row)
+        shifted = torch.nn.functional.pad(bd, (1, 0)).view(B, H, -1, T)[:, :, 1:].reshape(B, H, T, P)
+        bias = (shifted[..., :T].float() * (D ** -0.5)).masked_fill(attn_mask.logical_not(), MASK_FLOOR).to(self.dtype)
+        out = fmha(qu.contiguous(), k.contiguous(), v.contiguous(), softmax_scale=D ** -0.5, attn_bias=bias.contiguous())
+        if silent is not None:
+            out = out.masked_fill(silent.transpose(1, 2).unsqueeze(-1), 0.0)
+        merged = out.permute(0, 2, 1, 3).reshape(B * T, C).contiguous()
+        return OF.gemm(merged, *lw["o"])
+
+    def _conv(self, lw, h: torch.Tensor, silent, B: int, T: int) -> torch.Tensor:
+        x = OF.gemm_glu(h, *lw["pw1"])                                                # pointwise_conv1 + GLU
+        x = x.view(B, T, self.C)
+        if silent is not None:
+            x = x.masked_fill(silent, 0.0)
+        x = OF.depthwise_conv1d(x.contiguous(), lw["dw"][0], lw["dw"][1], padding=(self.K - 1, 0))   # causal
+        x = OF.layer_norm_activation(x.view(B * T, self.C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
+        return OF.gemm(x, *lw["pw2"])
+
+    def forward(self, hidden: torch.Tensor, lengths: List[int]) -> torch.Tensor:
+        """``hidden (B, T, C)`` post-subsampling states, host ``lengths`` -> ``(B, T, C)`` fp32: the output of the
+        layer stack of NemotronEncoder.forward (encoder.py:542-583)."""
+        if not hidden.is_cuda:
+            raise RuntimeError("hidden must be a CUDA tensor (oasr_b200 has no CPU path)")
+        B, T, C = hidden.shape
+        M = B * T
+        attn_mask, silent = self._masks(T, [int(n) for n in lengths])
+        rel_table = self._position_table(T)
+        res = hidden.reshape(M, C).to(torch.float32).contiguous()     # fp32 residual stream
+        h = torch.empty(M, C, device=hidden.device, dtype=self.dtype)
+        first = self.layers[0]["norm_feed_forward1"]
+        fused.add_norm_f32(h, None, res, None, 0.0, fused.ADD_NORM_LN, *first, eps=self.eps)          # LN(x)
+        out = None
+        for i, lw in enumerate(self.layers):
+            w1, b1, w2, b2 = lw["feed_forward1"]
+            y = OF.gemm(OF.gemm_activation(h, w1, b1, _SWISH), w2, b2)
+            fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_self_att"], eps=self.eps)
+            y = self._attention(lw, h, rel_table, attn_mask, silent, B, T)
+            fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_conv"], eps=self.eps)
+            y = self._conv(lw, h, silent, B, T)
+            fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_feed_forward2"], eps=self.eps)
+            w1, b1, w2, b2 = lw["feed_forward2"]
+            y = OF.gemm(OF.gemm_activation(h, w1, b1, _SWISH), w2, b2)
+            if i + 1 < self.L:
+                # norm_out of this layer is the next layer's input; its norm_feed_forward1 follows at once
+                nxt = self.layers[i + 1]["norm_feed_forward1"]
+                fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *nxt, eps=self.eps)
+            else:
+                out = torch.empty(M, C, device=hidden.device, dtype=torch.float32)
+                fused.add_norm_f32(h, out, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *lw["norm_out"], eps=self.eps)
+        return out.view(B, T, C)

@@ -1,0 +1,180 @@
+"""CPU oracle (test infrastructure, never imported by the product path) for the FastConformer / Nemotron
+encoder LAYER STACK: fp32 torch restatement of the reference's layer composition after the subsampling
+front end.  Pinned against the reference itself by ``tests/golden/make_golden.py`` (fixture
+``tests/golden/fastconformer_tiny.npz``).
+
+Restated from the reference (paths inside its project):
+  * ``rel_shift``                          oasr/models/nemotron/encoder.py:82-96
+  * ``relative_position_embedding``        oasr/models/nemotron/encoder.py:99-121
+  * ``chunked_limited_mask``               oasr/models/nemotron/encoder.py:124-149
+  * conv module (pw1, GLU, causal depthwise, LayerNorm+SiLU, pw2)   encoder.py:150-214
+  * layer (macaron FFNs, fused add+LayerNorm chain)                 encoder.py:217-267
+  * attention with the Transformer-XL position bias, MASK_FLOOR     encoder.py:300-359
+  * encoder loop: window mask & key padding, silent rows            encoder.py:542-583
+The 8x depthwise-separable subsampling stack and the RNN-T head are not restated here.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn.functional as F
+
+MASK_FLOOR = -1.0e4
+
+
+@dataclass
+class FastConformerConfig:
+    hidden: int = 256
+    heads: int = 2
+    ffn: int = 512
+    layers: int = 2
+    kernel: int = 9
+    sliding_window: int = 9      # left context = sliding_window - 1 frames
+    lookahead: int = 3           # right context in frames (chunk = lookahead + 1)
+    bias: bool = True            # attention_bias and convolution_bias of the reference config
+    eps: float = 1e-5
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+
+TINY = FastConformerConfig()
+
+
+def param_spec(cfg: FastConformerConfig):
+    """(name, shape, kind) in the reference's state-dict naming; kind: 'w' matrix, 'g' norm gain, 'b' bias."""
+    C, Fd, K, H, D = cfg.hidden, cfg.ffn, cfg.kernel, cfg.heads, cfg.head_dim
+    out = []
+    for i in range(cfg.layers):
+        p = f"layers.{i}."
+        for ff in ("feed_forward1", "feed_forward2"):
+            out += [(p + ff + ".linear1.weight", (Fd, C), "w"), (p + ff + ".linear2.weight", (C, Fd), "w")]
+            if cfg.bias:
+                out += [(p + ff + ".linear1.bias", (Fd,), "b"), (p + ff + ".linear2.bias", (C,), "b")]
+        a = p + "self_attn."
+        out += [(a + "bias_u", (H, D), "w"), (a + "bias_v", (H, D), "w")]
+        for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            out.append((a + n + ".weight", (C, C), "w"))
+            if cfg.bias:
+                out.append((a + n + ".bias", (C,), "b"))
+        out.append((a + "relative_k_proj.weight", (C, C), "w"))
+        c = p + "conv."
+        out += [(c + "pointwise_conv1.weight", (2 * C, C, 1), "w"), (c + "depthwise_conv.weight", (K, 1, C), "w"),
+                (c + "norm.weight", (C,), "g"), (c + "norm.bias", (C,), "b"), (c + "pointwise_conv2.weight", (C, C, 1), "w")]
+        if cfg.bias:
+            out += [(c + "pointwise_conv1.bias", (2 * C,), "b"), (c + "depthwise_conv.bias", (C,), "b"),
+                    (c + "pointwise_conv2.bias", (C,), "b")]
+        for n in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
+            out += [(p + n + ".weight", (C,), "g"), (p + n + ".bias", (C,), "b")]
+    return out
+
+
+def init_params(cfg: FastConformerConfig, seed: int) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic weights: matrices ~ N(0, 0.06), gains 1 + N(0, 0.1), biases N(0, 0.1)."""
+    g = torch.Generator().manual_seed(seed)
+    P = {}
+    for name, shape, kind in param_spec(cfg):
+        if kind == "w":
+            P[name] = torch.randn(shape, generator=g) * 0.06
+        elif kind == "g":
+            P[name] = 1.0 + torch.randn(shape, generator=g) * 0.1
+        else:
+            P[name] = torch.randn(shape, generator=g) * 0.1
+    return P
+
+
+def rel_shift(scores: torch.Tensor) -> torch.Tensor:
+    b, h, t_q, p = scores.shape
+    padded = F.pad(scores, (1, 0))
+    return padded.view(b, h, -1, t_q)[:, :, 1:].view(b, h, t_q, p)
+
+
+def relative_position_embedding(length: int, dim: int) -> torch.Tensor:
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    positions = torch.arange(length - 1, -length, -1, dtype=torch.float32)
+    freqs = torch.outer(positions, inv_freq)
+    return torch.stack([freqs.sin(), freqs.cos()], dim=-1).reshape(freqs.size(0), dim)   # (2L-1, dim)
+
+
+def chunked_limited_mask(query_len: int, key_len: int, left_context: int, right_context: int) -> torch.Tensor:
+    chunk = right_context + 1
+    left_chunks = left_context // chunk if left_context >= 0 else key_len
+    q_chunk = torch.arange(query_len).div(chunk, rounding_mode="trunc")
+    k_chunk = torch.arange(key_len).div(chunk, rounding_mode="trunc")
+    diff = q_chunk.unsqueeze(1) - k_chunk.unsqueeze(0)
+    return (diff >= 0) & (diff <= left_chunks)   # (T_q, T_k) bool
+
+
+def _lin(P, name, x):
+    return F.linear(x, P[name + ".weight"], P.get(name + ".bias"))
+
+
+def _ln(P, name, x, eps):
+    return F.layer_norm(x, (x.size(-1),), P[name + ".weight"], P[name + ".bias"], eps)
+
+
+def _ffn(P, p, x):
+    return _lin(P, p + ".linear2", F.silu(_lin(P, p + ".linear1", x)))
+
+
+def attention(P, a, cfg, x, pos_emb, attn_mask, silent):
+    B, T, C = x.shape
+    H, D = cfg.heads, cfg.head_dim
+    split = lambda t: t.view(B, T, H, D).transpose(1, 2)      # (B, H, T, D)
+    q, k, v = split(_lin(P, a + "q_proj", x)), split(_lin(P, a + "k_proj", x)), split(_lin(P, a + "v_proj", x))
+    rel_k = F.linear(pos_emb, P[a + "relative_k_proj.weight"]).view(1, -1, H, D)
+    scaling = D ** -0.5
+    matrix_bd = (q + P[a + "bias_v"].unsqueeze(1)) @ rel_k.permute(0, 2, 3, 1)
+    matrix_bd = rel_shift(matrix_bd)[..., :T] * scaling
+    bias = matrix_bd.masked_fill(attn_mask.logical_not(), MASK_FLOOR)
+    scores = ((q + P[a + "bias_u"].unsqueeze(1)) @ k.transpose(-1, -2)) * scaling + bias
+    out = torch.softmax(scores, dim=-1) @ v
+    if silent is not None:
+        out = out.masked_fill(silent.transpose(1, 2).unsqueeze(-1), 0.0)
+    return _lin(P, a + "o_proj", out.transpose(1, 2).reshape(B, T, C))
+
+
+def conv_module(P, c, cfg, x, silent):
+    x = F.glu(F.linear(x, P[c + "pointwise_conv1.weight"].squeeze(-1), P.get(c + "pointwise_conv1.bias")), dim=-1)
+    if silent is not None:
+        x = x.masked_fill(silent, 0.0)
+    x = F.pad(x, (0, 0, cfg.kernel - 1, 0))
+    w = P[c + "depthwise_conv.weight"].permute(2, 1, 0)       # (K,1,C) -> (C,1,K)
+    x = F.conv1d(x.transpose(1, 2), w, P.get(c + "depthwise_conv.bias"), groups=cfg.hidden).transpose(1, 2)
+    x = F.silu(_ln(P, c + "norm", x, 1e-5))
+    return F.linear(x, P[c + "pointwise_conv2.weight"].squeeze(-1), P.get(c + "pointwise_conv2.bias"))
+
+
+def layer_forward(P, i: int, cfg, x, pos_emb, attn_mask, silent):
+    p = f"layers.{i}."
+    residual = x
+    h = _ln(P, p + "norm_feed_forward1", x, cfg.eps)
+    residual = residual + 0.5 * _ffn(P, p + "feed_forward1", h)
+    h = _ln(P, p + "norm_self_att", residual, cfg.eps)
+    residual = residual + attention(P, p + "self_attn.", cfg, h, pos_emb, attn_mask, silent)
+    h = _ln(P, p + "norm_conv", residual, cfg.eps)
+    residual = residual + conv_module(P, p + "conv.", cfg, h, silent)
+    h = _ln(P, p + "norm_feed_forward2", residual, cfg.eps)
+    residual = residual + 0.5 * _ffn(P, p + "feed_forward2", h)
+    return _ln(P, p + "norm_out", residual, cfg.eps)
+
+
+def layers_forward(P: Dict[str, torch.Tensor], cfg: FastConformerConfig, hidden: torch.Tensor, lengths: List[int]):
+    """Layer stack of NemotronEncoder.forward on post-subsampling ``hidden (B, T, C)`` with valid ``lengths``:
+    returns ``(B, T, C)`` (rows past a length are whatever the masked computation yields, as in the reference)."""
+    B, T, C = hidden.shape
+    keep = torch.arange(T).unsqueeze(0) < torch.tensor(lengths).unsqueeze(1)
+    window = chunked_limited_mask(T, T, cfg.sliding_window - 1, cfg.lookahead).view(1, 1, T, T)
+    attn_mask = window & keep.view(B, 1, 1, T)
+    silent: Optional[torch.Tensor] = attn_mask.logical_not().all(dim=-1).transpose(1, 2)   # (B, T, 1)
+    if not bool(silent.any()):
+        silent = None
+    pos_emb = relative_position_embedding(T, C)
+    x = hidden.float()
+    for i in range(cfg.layers):
+        x = layer_forward(P, i, cfg, x, pos_emb, attn_mask, silent)
+    return x

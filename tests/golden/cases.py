@@ -146,3 +146,13 @@ def make_stream_features(case):
     g = torch.Generator().manual_seed(case["feat_seed"])
     total = case["step"] * (case["chunks"] - 1) + case["window"]
     return torch.randn(case["streams"], total, case["cfg"].input_size, generator=g)
+
+
+# FastConformer / Nemotron layer stack (after the subsampling front end): two layers, hidden 256 = 2 heads x 128,
+# kernel 9, chunked-limited attention (left 8 frames, lookahead 3), ragged lengths so that key padding is exercised.
+FASTCONFORMER_CASE = dict(weight_seed=99, hidden_seed=5, lengths=[37, 21, 30])
+
+
+def make_fastconformer_hidden(case, cfg):
+    g = torch.Generator().manual_seed(case["hidden_seed"])
+    return torch.randn(len(case["lengths"]), max(case["lengths"]), cfg.hidden, generator=g)

@@ -209,7 +209,49 @@ def stream_case():
     np.savez_compressed(HERE / "stream_tiny.npz", **out)
 
 
+def fastconformer_case():
+    """Layer stack of the reference's NemotronEncoder (its own layers, masks and position table, random weights
+    from the oracle's seeded initialiser) on a ragged batch of post-subsampling hidden states."""
+    from oasr.models.nemotron.config import NemotronEncoderConfig
+    from oasr.models.nemotron.encoder import (NemotronEncoderLayer, chunked_limited_mask,
+                                              relative_position_embedding)
+    from oracle import fastconformer as OF
+
+    cfg = OF.TINY
+    case = cases.FASTCONFORMER_CASE
+    rc = NemotronEncoderConfig(hidden_size=cfg.hidden, num_hidden_layers=cfg.layers, num_attention_heads=cfg.heads,
+                               num_key_value_heads=cfg.heads, intermediate_size=cfg.ffn, conv_kernel_size=cfg.kernel,
+                               sliding_window=cfg.sliding_window, default_num_lookahead_tokens=cfg.lookahead,
+                               attention_bias=cfg.bias, convolution_bias=cfg.bias)
+    P = OF.init_params(cfg, case["weight_seed"])
+    layers = torch.nn.ModuleList(NemotronEncoderLayer(rc) for _ in range(cfg.layers)).eval()
+    missing, unexpected = layers.load_state_dict({k[len("layers."):]: v for k, v in P.items()}, strict=True)
+    hidden = cases.make_fastconformer_hidden(case, cfg)
+    lengths = torch.tensor(case["lengths"])
+    t_out = hidden.size(1)
+    with torch.no_grad():
+        keep = torch.arange(t_out).unsqueeze(0) < lengths.unsqueeze(1)
+        window = chunked_limited_mask(t_out, t_out, cfg.sliding_window - 1, cfg.lookahead, hidden.device)
+        attn_mask = window & keep.view(-1, 1, 1, t_out)
+        silent = attn_mask.logical_not().all(dim=-1).transpose(1, 2)
+        if not bool(silent.any()):
+            silent = None
+        pos_emb = relative_position_embedding(t_out, cfg.hidden, hidden.device, hidden.dtype)
+        x = hidden
+        for layer in layers:
+            x = layer(x, pos_emb, attn_mask, silent)
+        mine = OF.layers_forward(P, cfg, hidden, case["lengths"])
+    d = (x - mine).abs().max().item()
+    print(f"fastconformer layer stack: reference vs oracle max-abs = {d:.3e} (silent rows: {silent is not None})")
+    assert d < 5e-5, "FastConformer oracle does not restate the reference"
+    np.savez_compressed(HERE / "fastconformer_tiny.npz", hidden_out=x.numpy())
+
+
 if __name__ == "__main__":
+    if "--only-fastconformer" in sys.argv:
+        fastconformer_case()
+        sys.exit(0)
+    fastconformer_case()
     stream_case()
     operator_cases()
     for name in cases.MODEL_CASES:

@@ -1,0 +1,50 @@
+"""GPU parity of the FastConformer / Nemotron layer stack composed from this package's operators against the fp32
+oracle and the fixture written from the reference's own layers."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oasr_b200 as ob
+from oasr_b200.fastconformer import FastConformerLayers
+from oracle import fastconformer as OFC
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def test_layer_stack_matches_oracle_and_reference_fixture():
+    cfg, case = OFC.TINY, cases.FASTCONFORMER_CASE
+    P = OFC.init_params(cfg, case["weight_seed"])
+    hidden = cases.make_fastconformer_hidden(case, cfg)
+    model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    got = model.forward(hidden.cuda(), case["lengths"]).cpu()
+    assert ob.device_status() == 0
+    want = OFC.layers_forward(P, cfg, hidden, case["lengths"])
+    gold = torch.from_numpy(np.load(GOLD / "fastconformer_tiny.npz")["hidden_out"])
+    valid = torch.arange(hidden.size(1))[None, :] < torch.tensor(case["lengths"])[:, None]
+    for ref in (want, gold):
+        d = (got - ref).abs()[valid]
+        # layer-normalised outputs of O(1): bf16 GEMM inputs / weights against the fp32 path
+        assert d.max().item() < 6e-2 and d.mean().item() < 6e-3, (d.max().item(), d.mean().item())
+    cos = torch.nn.functional.cosine_similarity(got[valid].flatten(), want[valid].flatten(), dim=0).item()
+    print(f"fastconformer layer stack: max-abs {(got - want).abs()[valid].max().item():.3e}, cosine {cos:.6f}")
+    assert cos > 0.9995
+
+
+def test_config4_sized_layer_runs_and_is_isolated_per_utterance():
+    """One layer at the FastConformer width (hidden 1024, 8 heads of 128, FFN 4096, kernel 9): an utterance inside a
+    padded batch equals the same utterance alone on its valid frames (key padding and silent rows do their job)."""
+    torch.manual_seed(3)
+    cfg = OFC.FastConformerConfig(hidden=1024, heads=8, ffn=4096, layers=1, kernel=9, sliding_window=57, lookahead=3, bias=False)
+    P = OFC.init_params(cfg, 11)
+    lengths = [96, 41]
+    hidden = torch.randn(2, 96, 1024)
+    model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    both = model.forward(hidden.cuda(), lengths)
+    alone = model.forward(hidden[1:2, :41].contiguous().cuda(), [41])
+    assert ob.device_status() == 0
+    assert torch.isfinite(both).all()
+    assert (both[1, :41] - alone[0]).abs().max().item() < 2e-2

@@ -128,3 +128,22 @@ def test_streaming_oracle_matches_reference_fixture():
             d = np.abs(lp.numpy() - gold[f"stream{s}_log_probs"][c])[:, :cfg.vocab].max()
             assert d < 5e-5, (s, c, d)
         assert state.k[0].shape[1] <= max_past + case["chunk_size"]
+
+
+def test_fastconformer_oracle_matches_reference_fixture():
+    """The FastConformer / Nemotron layer-stack oracle against the output of the reference's own layers
+    (fixture written by tests/golden/make_golden.py from NemotronEncoderLayer on the CPU)."""
+    from oracle import fastconformer as OFC
+
+    gold = np.load(GOLD / "fastconformer_tiny.npz")
+    cfg, case = OFC.TINY, cases.FASTCONFORMER_CASE
+    P = OFC.init_params(cfg, case["weight_seed"])
+    hidden = cases.make_fastconformer_hidden(case, cfg)
+    out = OFC.layers_forward(P, cfg, hidden, case["lengths"]).numpy()
+    assert np.abs(out - gold["hidden_out"]).max() < 5e-5
+    # the relative shift identity the reference pins in its own tests: row i, column j holds source column (L-1)+j-i
+    L = 5
+    src = torch.arange(2 * L - 1, dtype=torch.float32).expand(1, 1, L, 2 * L - 1).contiguous()
+    sh = OFC.rel_shift(src)[0, 0, :, :L]
+    want = torch.tensor([[(L - 1) + j - i for j in range(L)] for i in range(L)], dtype=torch.float32)
+    assert torch.equal(sh, want)
