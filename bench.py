@@ -114,6 +114,9 @@ def gemm_flops(name, args):
         M, N, K = args[4], 2 * args[5], args[6]
     elif name == "oasr_b200_gemm_log_softmax":
         M, N, K = args[4], args[5], args[6]
+    elif name == "oasr_b200_subsample_conv2":   # implicit GEMM: rows = frames x F2 positions, K = 9 taps x C
+        F2 = (args[7] - 3) // 2 + 1
+        M, N, K = args[10] * F2, args[9], 9 * args[8]
     elif name == "oasr_b200_gemm_residual_f32":
         M, N, K = args[5], args[6], args[7]
     else:
