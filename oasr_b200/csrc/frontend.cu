@@ -164,6 +164,65 @@ bool k3s2_applies(const Conv1Args& a) {
          static_cast<size_t>(2 * (256 / groups) + 1) * a.F * sizeof(float) <= 48 * 1024;
 }
 
+// Depthwise 3x3 / stride-2 Conv2d on NHWC 16-bit data with causal-style zero padding (pad_lo rows/columns before,
+// pad_hi after, on both the time and the frequency axis): the depthwise half of a stage of the FastConformer 8x
+// subsampling stack (oasr/models/nemotron/subsampling.py:204-224, padding geometry :39-53).  HBM-bound: a thread
+// owns 8 channels of one output position (9 x 16-byte loads, 72 FMAs, one 16-byte store); output frames at or past
+// out_len[b] (nullable) are written as zeros, which is the reference's per-stage time mask.
+struct Dw2dArgs {
+  void* out;
+  const void* in;
+  const void* weight;   // (C, 3, 3) 16-bit
+  const void* bias;     // nullable (C)
+  const int32_t* out_len;
+  int B, T, F, C, To, Fo, pad_lo;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) depthwise_conv2d_k3s2_kernel(Dw2dArgs a) {
+  const int groups = a.C / 8;
+  const int64_t total = static_cast<int64_t>(a.B) * a.To * a.Fo * groups;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int cg = static_cast<int>(i % groups);
+    int64_t r = i / groups;
+    const int fo = static_cast<int>(r % a.Fo);
+    r /= a.Fo;
+    const int to = static_cast<int>(r % a.To);
+    const int b = static_cast<int>(r / a.To);
+    const int c0 = cg * 8;
+    float acc[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    const bool live = !a.out_len || to < a.out_len[b];
+    if (live) {
+      if (a.bias) {
+        const Pack<T> bb = ld128(static_cast<const T*>(a.bias) + c0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] = Elem<T>::to_f(bb.v[q]);
+      }
+#pragma unroll
+      for (int di = 0; di < 3; ++di) {
+        const int t = 2 * to + di - a.pad_lo;
+        if (t < 0 || t >= a.T) continue;
+#pragma unroll
+        for (int dj = 0; dj < 3; ++dj) {
+          const int f = 2 * fo + dj - a.pad_lo;
+          if (f < 0 || f >= a.F) continue;
+          const Pack<T> x = ld128(static_cast<const T*>(a.in) + ((static_cast<int64_t>(b) * a.T + t) * a.F + f) * a.C + c0);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            acc[q] = fmaf(Elem<T>::to_f(x.v[q]), Elem<T>::to_f(static_cast<const T*>(a.weight)[(c0 + q) * 9 + di * 3 + dj]), acc[q]);
+        }
+      }
+    }
+    Pack<T> o;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) o.v[q] = Elem<T>::from_f(acc[q]);
+    st128(static_cast<T*>(a.out) + ((static_cast<int64_t>(b) * a.To + to) * a.Fo + fo) * a.C + c0, o);
+  }
+}
+
 }  // namespace
 }  // namespace ob
 
@@ -223,6 +282,31 @@ int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const float* weigh
   OB_REQUIRE(k3s2_applies(a), OASR_ERR_UNSUPPORTED,
              "subsample_conv1_s2d: channels / 8 must be a power of two <= 256 (got C = %lld)", (long long)C);
   return OB_DISPATCH_HALF(dtype, T_, [&]() -> int { return launch_k3s2<T_>(a, true, static_cast<cudaStream_t>(stream)); });
+}
+
+int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weight, const void* bias,
+                                    const int32_t* out_len, int64_t B, int64_t T, int64_t F, int64_t C, int64_t pad_lo,
+                                    int64_t pad_hi, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(B >= 0 && T > 0 && F > 0 && C > 0 && pad_lo >= 0 && pad_hi >= 0, OASR_ERR_INVALID,
+             "depthwise_conv2d_k3s2: bad shape");
+  OB_REQUIRE(T + pad_lo + pad_hi >= 3 && F + pad_lo + pad_hi >= 3, OASR_ERR_INVALID,
+             "depthwise_conv2d_k3s2: padded input smaller than the kernel");
+  if (B == 0) return OASR_OK;
+  OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "depthwise_conv2d_k3s2: null pointer argument");
+  OB_REQUIRE(C % 8 == 0 && is_aligned(out, 16) && is_aligned(in, 16) && (!bias || is_aligned(bias, 16)), OASR_ERR_ALIGN,
+             "depthwise_conv2d_k3s2: channels must be a multiple of 8 and the tensors 16-byte aligned");
+  Dw2dArgs a{out, in, weight, bias, out_len, (int)B, (int)T, (int)F, (int)C,
+             (int)((T + pad_lo + pad_hi - 3) / 2 + 1), (int)((F + pad_lo + pad_hi - 3) / 2 + 1), (int)pad_lo};
+  const int64_t total = B * a.To * a.Fo * (C / 8);
+  int64_t g = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (g > cap) g = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
+    depthwise_conv2d_k3s2_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(a);
+    return check_launch("depthwise_conv2d_k3s2 launch");
+  });
 }
 
 }  // extern "C"

@@ -1,4 +1,5 @@
-"""FastConformer / Nemotron encoder LAYER STACK on the sm_100a operators (offline, padded batch).
+"""FastConformer / Nemotron encoder (8x subsampling front end + layer stack) on the sm_100a operators (offline,
+padded batch).
 
 The composition the reference's ``NemotronEncoderLayer.forward`` serves
 (oasr/models/nemotron/encoder.py:217-267): macaron FFNs with SiLU, Transformer-XL relative-position
@@ -9,8 +10,10 @@ Every contraction, normalisation, activation, convolution and the attention run 
 kernels (head_dim 128 attention with an additive bias, ``layer_norm_activation``, causal
 ``depthwise_conv1d``); the position bias is built by one batched GEMM against the projected
 relative table and shifted with the same pad/view identity as the reference, in torch.
-The 8x depthwise-separable subsampling front end and the RNN-T head are outside this module: the
-input is the post-subsampling hidden state ``(B, T, C)``.
+``FastConformerEncoder`` puts the 8x causal depthwise-separable subsampling front end in front of the stack
+(oasr/models/nemotron/subsampling.py:26-131, 204-224): stem conv on the fp32 stencil kernel, two stages of
+depthwise 3x3 / stride-2 conv (own NHWC kernel) + pointwise GEMM with a fused ReLU, projection GEMM.  The RNN-T
+head is outside this module.
 """
 from __future__ import annotations
 
@@ -29,9 +32,16 @@ _SWISH = 2
 
 class FastConformerLayers:
     def __init__(self, hidden: int, heads: int, ffn: int, layers: int, kernel: int, sliding_window: int, lookahead: int,
-                 params: Dict[str, torch.Tensor], device="cuda", dtype: torch.dtype = torch.bfloat16, eps: float = 1e-5):
+                 params: Dict[str, torch.Tensor], device="cuda", dtype: torch.dtype = torch.bfloat16, eps: float = 1e-5,
+                 quant: str = None):
+        """``quant`` "fp8" / "int8": the Linear GEMMs of every layer (FFNs, q/k/v, output, pointwise convs) run on
+        8-bit operands with per-output-channel weight scales and per-token dynamic activation scales."""
         if hidden % heads or hidden // heads not in (64, 128):
             raise ValueError("head_dim must be 64 or 128")
+        if quant not in (None, "fp8", "int8"):
+            raise ValueError("quant must be None, 'fp8' or 'int8'")
+        self.qkind = {None: 0, "fp8": 1, "int8": 2}[quant]
+        self._q8 = {}
         self.C, self.H, self.D, self.F, self.L, self.K = hidden, heads, hidden // heads, ffn, layers, kernel
         self.left, self.right, self.eps = sliding_window - 1, lookahead, eps
         self.device, self.dtype = torch.device(device), dtype
@@ -63,6 +73,20 @@ class FastConformerLayers:
                 lw[n] = (w(params[p + n + ".weight"]), w(params[p + n + ".bias"]))
             self.layers.append(lw)
 
+    def _linear(self, x: torch.Tensor, w: torch.Tensor, b, act: int = -1, glu: bool = False) -> torch.Tensor:
+        """One Linear: 16-bit GEMM, or per-token quantisation + 8-bit GEMM against the cached 8-bit weight."""
+        if not self.qkind:
+            if glu:
+                return OF.gemm_glu(x, w, b)
+            return OF.gemm_activation(x, w, b, act) if act >= 0 else OF.gemm(x, w, b)
+        from . import quant
+        key = w.data_ptr()
+        if key not in self._q8:
+            self._q8[key] = quant.quantize_rows(w, self.qkind)
+        wq, ws = self._q8[key]
+        xq, xs = quant.quantize_rows(x, self.qkind)
+        return quant.gemm_q8(xq, xs, wq, ws, b, kind=self.qkind, activation=act, glu=glu, out_dtype=self.dtype)
+
     # ---- host-side tables (lengths are host values: no device synchronisation) ----
     def _position_table(self, T: int) -> torch.Tensor:
         inv_freq = 1.0 / (10000.0 ** (torch.arange(0, self.C, 2, dtype=torch.float32) / self.C))
@@ -85,7 +109,7 @@ class FastConformerLayers:
     # ---- one layer ----
     def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, attn_mask, silent, B: int, T: int) -> torch.Tensor:
         C, H, D = self.C, self.H, self.D
-        qkv4 = OF.gemm(h, *lw["qkv4"]).view(B, T, 4, H, D)
+        qkv4 = self._linear(h, *lw["qkv4"]).view(B, T, 4, H, D)
         qu, qv, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(4))          # (B, H, T, D) views
         rel_k = OF.gemm(rel_table, lw["rel"]).view(-1, H, D)                          # (2T-1, H, D)
         # (q + v) against the projected table, one batched GEMM over (b, h): (B*H, T, D) x (B*H, 2T-1, D)^T
@@ -103,16 +127,16 @@ class FastConformerLayers:
         if silent is not None:
             out = out.masked_fill(silent.transpose(1, 2).unsqueeze(-1), 0.0)
         merged = out.permute(0, 2, 1, 3).reshape(B * T, C).contiguous()
-        return OF.gemm(merged, *lw["o"])
+        return self._linear(merged, *lw["o"])
 
     def _conv(self, lw, h: torch.Tensor, silent, B: int, T: int) -> torch.Tensor:
-        x = OF.gemm_glu(h, *lw["pw1"])                                                # pointwise_conv1 + GLU
+        x = self._linear(h, *lw["pw1"], glu=True)                                     # pointwise_conv1 + GLU
         x = x.view(B, T, self.C)
         if silent is not None:
             x = x.masked_fill(silent, 0.0)
         x = OF.depthwise_conv1d(x.contiguous(), lw["dw"][0], lw["dw"][1], padding=(self.K - 1, 0))   # causal
         x = OF.layer_norm_activation(x.view(B * T, self.C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
-        return OF.gemm(x, *lw["pw2"])
+        return self._linear(x, *lw["pw2"])
 
     def forward(self, hidden: torch.Tensor, lengths: List[int]) -> torch.Tensor:
         """``hidden (B, T, C)`` post-subsampling states, host ``lengths`` -> ``(B, T, C)`` fp32: the output of the
@@ -130,14 +154,14 @@ class FastConformerLayers:
         out = None
         for i, lw in enumerate(self.layers):
             w1, b1, w2, b2 = lw["feed_forward1"]
-            y = OF.gemm(OF.gemm_activation(h, w1, b1, _SWISH), w2, b2)
+            y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
             fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_self_att"], eps=self.eps)
             y = self._attention(lw, h, rel_table, attn_mask, silent, B, T)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_conv"], eps=self.eps)
             y = self._conv(lw, h, silent, B, T)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_feed_forward2"], eps=self.eps)
             w1, b1, w2, b2 = lw["feed_forward2"]
-            y = OF.gemm(OF.gemm_activation(h, w1, b1, _SWISH), w2, b2)
+            y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
             if i + 1 < self.L:
                 # norm_out of this layer is the next layer's input; its norm_feed_forward1 follows at once
                 nxt = self.layers[i + 1]["norm_feed_forward1"]
@@ -146,3 +170,52 @@ class FastConformerLayers:
                 out = torch.empty(M, C, device=hidden.device, dtype=torch.float32)
                 fused.add_norm_f32(h, out, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *lw["norm_out"], eps=self.eps)
         return out.view(B, T, C)
+
+
+class FastConformerEncoder:
+    """``NemotronEncoder.forward`` (oasr/models/nemotron/encoder.py:542-583, ``scale_input`` False): mel features
+    ``(B, T, mels)`` with host lengths -> ``(hidden (B, T', C) fp32, out_lengths)``.  Takes the reference's state-dict
+    names (``subsampling.conv_in.weight``, ``subsampling.layers.N.depthwise_conv.weight``, ``layers.N...``)."""
+
+    def __init__(self, hidden: int, heads: int, ffn: int, layers: int, kernel: int, sliding_window: int, lookahead: int,
+                 mels: int, sub_channels: int, params: Dict[str, torch.Tensor], device="cuda",
+                 dtype: torch.dtype = torch.bfloat16, stages: int = 3):
+        self.stack = FastConformerLayers(hidden, heads, ffn, layers, kernel, sliding_window, lookahead, params, device, dtype)
+        self.device, self.dtype, self.stages, self.Cs = torch.device(device), dtype, stages, sub_channels
+        w = lambda t: t.detach().to(torch.float32).to(dtype).to(self.device).contiguous()
+        f = lambda t: t.detach().to(torch.float32).to(self.device).contiguous()
+        s = "subsampling."
+        self.conv_in = (f(params[s + "conv_in.weight"].reshape(sub_channels, 3, 3)), f(params[s + "conv_in.bias"]))
+        self.sub_stages = []
+        for i in range(stages - 1):
+            p = f"{s}layers.{i}."
+            self.sub_stages.append((w(params[p + "depthwise_conv.weight"].reshape(sub_channels, 3, 3)),
+                                    w(params[p + "depthwise_conv.bias"]),
+                                    w(params[p + "pointwise_conv.weight"].reshape(sub_channels, sub_channels)),
+                                    w(params[p + "pointwise_conv.bias"])))
+        self.proj = (w(params[s + "linear.weight"]), w(params[s + "linear.bias"]))
+
+    def subsample(self, feats: torch.Tensor, lengths: List[int]):
+        B = feats.size(0)
+        nxt = lambda ls: [(n + 2 + 1 - 3) // 2 + 1 for n in ls]
+        # stem: one input channel, pad (2, 1) on time and frequency, 3x3 / stride 2, + bias + ReLU (fp32 in, 16-bit NHWC out)
+        x = fused.subsample_conv1(torch.nn.functional.pad(feats.float(), (2, 1, 2, 1)), *self.conv_in, self.dtype)
+        lengths = nxt(lengths)
+        keep = (torch.arange(x.size(1))[None, :] < torch.tensor(lengths)[:, None]).to(self.device)
+        x = x * keep[:, :, None, None].to(x.dtype)                       # frames past the valid length back to zero
+        for dw_w, dw_b, pw_w, pw_b in self.sub_stages:
+            lengths = nxt(lengths)
+            lens_dev = torch.tensor(lengths, dtype=torch.int32).to(self.device, non_blocking=True)
+            x = fused.depthwise_conv2d_k3s2(x, dw_w, dw_b, 2, 1, out_len=lens_dev)       # masked frames come out zero
+            _, T, Fd, C = x.shape
+            x = OF.gemm_activation(x.view(B * T * Fd, C), pw_w, pw_b, 0).view(B, T, Fd, C)   # pointwise conv + ReLU
+            keep = (torch.arange(T)[None, :] < torch.tensor(lengths)[:, None]).to(self.device)
+            x = x * keep[:, :, None, None].to(x.dtype)
+        B, T, Fd, C = x.shape
+        return OF.gemm(x.reshape(B * T, Fd * C), *self.proj).view(B, T, -1), lengths
+
+    def forward(self, feats: torch.Tensor, lengths: List[int]):
+        if not feats.is_cuda:
+            raise RuntimeError("feats must be a CUDA tensor (oasr_b200 has no CPU path)")
+        hidden, out_len = self.subsample(feats, [int(n) for n in lengths])
+        return self.stack.forward(hidden, out_len), out_len

@@ -1,6 +1,6 @@
 """CPU oracle (test infrastructure, never imported by the product path) for the FastConformer / Nemotron
-encoder LAYER STACK: fp32 torch restatement of the reference's layer composition after the subsampling
-front end.  Pinned against the reference itself by ``tests/golden/make_golden.py`` (fixture
+encoder: fp32 torch restatement of the reference's 8x subsampling front end and layer composition.
+Pinned against the reference itself by ``tests/golden/make_golden.py`` (fixture
 ``tests/golden/fastconformer_tiny.npz``).
 
 Restated from the reference (paths inside its project):
@@ -11,7 +11,8 @@ Restated from the reference (paths inside its project):
   * layer (macaron FFNs, fused add+LayerNorm chain)                 encoder.py:217-267
   * attention with the Transformer-XL position bias, MASK_FLOOR     encoder.py:300-359
   * encoder loop: window mask & key padding, silent rows            encoder.py:542-583
-The 8x depthwise-separable subsampling stack and the RNN-T head are not restated here.
+  * 8x causal depthwise-separable subsampling                       oasr/models/nemotron/subsampling.py:26-131, 204-224
+The RNN-T head is not restated here.
 """
 from __future__ import annotations
 
@@ -73,13 +74,13 @@ def param_spec(cfg: FastConformerConfig):
     return out
 
 
-def init_params(cfg: FastConformerConfig, seed: int) -> Dict[str, torch.Tensor]:
-    """Seeded synthetic weights: matrices ~ N(0, 0.06), gains 1 + N(0, 0.1), biases N(0, 0.1)."""
+def init_params(cfg: FastConformerConfig, seed: int, w_std: float = 0.06) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic weights: matrices ~ N(0, w_std), gains 1 + N(0, 0.1), biases N(0, 0.1)."""
     g = torch.Generator().manual_seed(seed)
     P = {}
     for name, shape, kind in param_spec(cfg):
         if kind == "w":
-            P[name] = torch.randn(shape, generator=g) * 0.06
+            P[name] = torch.randn(shape, generator=g) * w_std
         elif kind == "g":
             P[name] = 1.0 + torch.randn(shape, generator=g) * 0.1
         else:
@@ -178,3 +179,76 @@ def layers_forward(P: Dict[str, torch.Tensor], cfg: FastConformerConfig, hidden:
     for i in range(cfg.layers):
         x = layer_forward(P, i, cfg, x, pos_emb, attn_mask, silent)
     return x
+
+
+# ---------------------------------------------------------------------------
+# 8x causal depthwise-separable subsampling (oasr/models/nemotron/subsampling.py:26-131, 204-224) and the whole
+# encoder forward (oasr/models/nemotron/encoder.py:542-583)
+# ---------------------------------------------------------------------------
+@dataclass
+class SubsamplingConfig:
+    mels: int = 32
+    channels: int = 64
+    stages: int = 3          # log2(subsampling factor 8)
+
+    def bins(self) -> int:
+        b = self.mels
+        for _ in range(self.stages):
+            b = (b + 3 - 3) // 2 + 1
+        return b
+
+
+TINY_SUB = SubsamplingConfig()
+
+
+def subsampling_param_spec(sub: SubsamplingConfig, hidden: int):
+    Cs = sub.channels
+    out = [("subsampling.conv_in.weight", (Cs, 3, 3, 1), "w"), ("subsampling.conv_in.bias", (Cs,), "b")]
+    for i in range(sub.stages - 1):
+        p = f"subsampling.layers.{i}."
+        out += [(p + "depthwise_conv.weight", (Cs, 3, 3, 1), "w"), (p + "depthwise_conv.bias", (Cs,), "b"),
+                (p + "pointwise_conv.weight", (Cs, 1, 1, Cs), "w"), (p + "pointwise_conv.bias", (Cs,), "b")]
+    out += [("subsampling.linear.weight", (hidden, Cs * sub.bins()), "w"), ("subsampling.linear.bias", (hidden,), "b")]
+    return out
+
+
+def init_subsampling_params(sub: SubsamplingConfig, hidden: int, seed: int) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    P = {}
+    for name, shape, kind in subsampling_param_spec(sub, hidden):
+        P[name] = torch.randn(shape, generator=g) * (0.25 if kind == "w" else 0.1)
+    return P
+
+
+def _mask_time(x, lengths):        # x NCHW (B, C, T, F)
+    keep = torch.arange(x.size(2)).unsqueeze(0) < lengths.unsqueeze(1)
+    return x * keep[:, None, :, None]
+
+
+def subsampling_forward(P, sub: SubsamplingConfig, feats: torch.Tensor, lengths: torch.Tensor):
+    """``feats (B, T, mels)`` -> ``(embeddings (B, T', hidden), lengths')``; pad (2, 1) on time and frequency before
+    every 3x3 / stride-2 convolution, frames at or past the valid length re-zeroed after every stage."""
+    pad = lambda x: F.pad(x, (2, 1, 2, 1))       # NCHW: last dim = frequency, then time
+    out_len = lambda l: (l + 2 + 1 - 3) // 2 + 1
+    x = feats.float().unsqueeze(1)               # (B, 1, T, F)
+    w = P["subsampling.conv_in.weight"].permute(0, 3, 1, 2)
+    x = torch.relu(F.conv2d(pad(x), w, P["subsampling.conv_in.bias"], stride=2))
+    lengths = out_len(lengths)
+    x = _mask_time(x, lengths)
+    for i in range(sub.stages - 1):
+        p = f"subsampling.layers.{i}."
+        x = F.conv2d(pad(x), P[p + "depthwise_conv.weight"].permute(0, 3, 1, 2), P[p + "depthwise_conv.bias"], stride=2,
+                     groups=sub.channels)
+        pw = P[p + "pointwise_conv.weight"][:, 0, 0, :]                      # (C_out, C_in)
+        x = torch.relu(torch.einsum("bctf,oc->botf", x, pw) + P[p + "pointwise_conv.bias"][None, :, None, None])
+        lengths = out_len(lengths)
+        x = _mask_time(x, lengths)
+    b, c, t, f = x.shape
+    flat = x.permute(0, 2, 3, 1).reshape(b, t, f * c)                        # NHWC flatten: (frequency, channel)
+    return F.linear(flat, P["subsampling.linear.weight"], P["subsampling.linear.bias"]), lengths
+
+
+def encoder_forward(P, cfg: FastConformerConfig, sub: SubsamplingConfig, feats: torch.Tensor, lengths: List[int]):
+    """NemotronEncoder.forward with scale_input False: ``(hidden (B, T', C), out_lengths)``."""
+    hidden, out_len = subsampling_forward(P, sub, feats, torch.tensor(lengths))
+    return layers_forward(P, cfg, hidden, out_len.tolist()), out_len

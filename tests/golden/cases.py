@@ -156,3 +156,12 @@ FASTCONFORMER_CASE = dict(weight_seed=99, hidden_seed=5, lengths=[37, 21, 30])
 def make_fastconformer_hidden(case, cfg):
     g = torch.Generator().manual_seed(case["hidden_seed"])
     return torch.randn(len(case["lengths"]), max(case["lengths"]), cfg.hidden, generator=g)
+
+
+# whole FastConformer encoder (8x subsampling + layer stack): 32 mel bins, 64 subsampling channels, ragged lengths
+FASTCONFORMER_ENCODER_CASE = dict(weight_seed=99, sub_seed=100, feat_seed=6, lengths=[203, 120, 77])
+
+
+def make_fastconformer_features(case, sub):
+    g = torch.Generator().manual_seed(case["feat_seed"])
+    return torch.randn(len(case["lengths"]), max(case["lengths"]), sub.mels, generator=g)

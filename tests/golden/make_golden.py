@@ -244,7 +244,26 @@ def fastconformer_case():
     d = (x - mine).abs().max().item()
     print(f"fastconformer layer stack: reference vs oracle max-abs = {d:.3e} (silent rows: {silent is not None})")
     assert d < 5e-5, "FastConformer oracle does not restate the reference"
-    np.savez_compressed(HERE / "fastconformer_tiny.npz", hidden_out=x.numpy())
+    # whole encoder: the reference's NemotronEncoder (subsampling + layers) on ragged mel features
+    from oasr.models.nemotron.encoder import NemotronEncoder
+
+    sub, ecase = OF.TINY_SUB, cases.FASTCONFORMER_ENCODER_CASE
+    rc.num_mel_bins, rc.subsampling_conv_channels = sub.mels, sub.channels
+    enc = NemotronEncoder(rc).eval()
+    PE = dict(OF.init_params(cfg, ecase["weight_seed"]))
+    PE.update(OF.init_subsampling_params(sub, cfg.hidden, ecase["sub_seed"]))
+    enc.load_state_dict(PE, strict=True)
+    feats = cases.make_fastconformer_features(ecase, sub)
+    with torch.no_grad():
+        ref_hidden, ref_mask = enc(feats, torch.tensor(ecase["lengths"]))
+        mine_hidden, mine_len = OF.encoder_forward(PE, cfg, sub, feats, ecase["lengths"])
+    ref_len = ref_mask.squeeze(1).sum(-1)
+    assert torch.equal(ref_len, mine_len), (ref_len, mine_len)
+    de = (ref_hidden - mine_hidden).abs().max().item()
+    print(f"fastconformer encoder: reference vs oracle max-abs = {de:.3e}, out lengths {mine_len.tolist()}")
+    assert de < 1e-4, "FastConformer encoder oracle does not restate the reference"
+    np.savez_compressed(HERE / "fastconformer_tiny.npz", hidden_out=x.numpy(), encoder_out=ref_hidden.numpy(),
+                        encoder_len=ref_len.numpy())
 
 
 if __name__ == "__main__":

@@ -48,3 +48,31 @@ def test_config4_sized_layer_runs_and_is_isolated_per_utterance():
     assert ob.device_status() == 0
     assert torch.isfinite(both).all()
     assert (both[1, :41] - alone[0]).abs().max().item() < 2e-2
+
+
+def test_whole_encoder_matches_oracle_and_reference_fixture():
+    """8x subsampling front end + layer stack against the oracle and the reference's NemotronEncoder output."""
+    from oasr_b200.fastconformer import FastConformerEncoder
+
+    cfg, sub, case = OFC.TINY, OFC.TINY_SUB, cases.FASTCONFORMER_ENCODER_CASE
+    P = dict(OFC.init_params(cfg, case["weight_seed"]))
+    P.update(OFC.init_subsampling_params(sub, cfg.hidden, case["sub_seed"]))
+    feats = cases.make_fastconformer_features(case, sub)
+    enc = FastConformerEncoder(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead,
+                               sub.mels, sub.channels, P)
+    got, out_len = enc.forward(feats.cuda(), case["lengths"])
+    assert ob.device_status() == 0
+    gold = np.load(GOLD / "fastconformer_tiny.npz")
+    assert out_len == gold["encoder_len"].tolist()
+    want, _ = OFC.encoder_forward(P, cfg, sub, feats, case["lengths"])
+    valid = torch.arange(got.size(1))[None, :] < torch.tensor(out_len)[:, None]
+    got = got.cpu()
+    for ref in (want, torch.from_numpy(gold["encoder_out"])):
+        d = (got - ref).abs()[valid]
+        assert d.max().item() < 8e-2 and d.mean().item() < 8e-3, (d.max().item(), d.mean().item())
+    # the subsampling front end alone, tighter
+    hid, _ = enc.subsample(feats.cuda(), case["lengths"])
+    ref_hid, ref_len = OFC.subsampling_forward(P, sub, feats, torch.tensor(case["lengths"]))
+    dh = (hid.float().cpu() - ref_hid).abs()[valid]
+    assert dh.max().item() < 3e-2 * max(1.0, ref_hid.abs().max().item()), dh.max().item()
+    print(f"fastconformer encoder: max-abs {(got - want).abs()[valid].max().item():.3e}; front end {dh.max().item():.3e} of {ref_hid.abs().max().item():.2f}")

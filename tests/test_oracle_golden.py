@@ -147,3 +147,17 @@ def test_fastconformer_oracle_matches_reference_fixture():
     sh = OFC.rel_shift(src)[0, 0, :, :L]
     want = torch.tensor([[(L - 1) + j - i for j in range(L)] for i in range(L)], dtype=torch.float32)
     assert torch.equal(sh, want)
+
+
+def test_fastconformer_encoder_oracle_matches_reference_fixture():
+    """Whole FastConformer encoder oracle (8x subsampling + layer stack) against the reference's NemotronEncoder output."""
+    from oracle import fastconformer as OFC
+
+    gold = np.load(GOLD / "fastconformer_tiny.npz")
+    cfg, sub, case = OFC.TINY, OFC.TINY_SUB, cases.FASTCONFORMER_ENCODER_CASE
+    P = dict(OFC.init_params(cfg, case["weight_seed"]))
+    P.update(OFC.init_subsampling_params(sub, cfg.hidden, case["sub_seed"]))
+    feats = cases.make_fastconformer_features(case, sub)
+    out, out_len = OFC.encoder_forward(P, cfg, sub, feats, case["lengths"])
+    assert out_len.tolist() == gold["encoder_len"].tolist()
+    assert np.abs(out.numpy() - gold["encoder_out"]).max() < 1e-4
