@@ -147,7 +147,7 @@ class FastConformerLayers:
         M = B * T
         attn_mask, silent = self._masks(T, [int(n) for n in lengths])
         rel_table = self._position_table(T)
-        res = hidden.reshape(M, C).to(torch.float32).contiguous()     # fp32 residual stream
+        res = hidden.reshape(M, C).to(torch.float32, copy=True).contiguous()   # fp32 residual stream (updated in place: own copy)
         h = torch.empty(M, C, device=hidden.device, dtype=self.dtype)
         first = self.layers[0]["norm_feed_forward1"]
         fused.add_norm_f32(h, None, res, None, 0.0, fused.ADD_NORM_LN, *first, eps=self.eps)          # LN(x)

@@ -43,7 +43,9 @@ def test_config4_sized_layer_runs_and_is_isolated_per_utterance():
     lengths = [96, 41]
     hidden = torch.randn(2, 96, 1024)
     model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
-    both = model.forward(hidden.cuda(), lengths)
+    hidden_dev = hidden.cuda()
+    both = model.forward(hidden_dev, lengths)
+    assert torch.equal(hidden_dev.cpu(), hidden)                       # the fp32 input is not the residual buffer
     alone = model.forward(hidden[1:2, :41].contiguous().cuda(), [41])
     assert ob.device_status() == 0
     assert torch.isfinite(both).all()
@@ -76,3 +78,22 @@ def test_whole_encoder_matches_oracle_and_reference_fixture():
     dh = (hid.float().cpu() - ref_hid).abs()[valid]
     assert dh.max().item() < 3e-2 * max(1.0, ref_hid.abs().max().item()), dh.max().item()
     print(f"fastconformer encoder: max-abs {(got - want).abs()[valid].max().item():.3e}; front end {dh.max().item():.3e} of {ref_hid.abs().max().item():.2f}")
+
+
+@pytest.mark.parametrize("mode", ["fp8", "int8"])
+def test_quantised_layer_stack_reaches_the_cosine_gate_against_the_16_bit_run(mode):
+    """FastConformer width (hidden 1024, 8 heads of 128, FFN 4096), two layers: Linear GEMMs on 8-bit operands
+    (per-output-channel weight scales, per-token dynamic activation scales) against the bf16 run: cosine >= 0.999."""
+    cfg = OFC.FastConformerConfig(hidden=1024, heads=8, ffn=4096, layers=2, kernel=9, sliding_window=57, lookahead=3, bias=False)
+    P = OFC.init_params(cfg, 13, w_std=0.02)     # BASELINE's N(0, 0.02) init: at 0.06 and width 1024 the attention is
+    lengths = [120, 77]                          # near one-hot and any rounding flips it
+    hidden = torch.randn(2, 120, 1024, generator=torch.Generator().manual_seed(2)).cuda()
+    args = (cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    ref = FastConformerLayers(*args).forward(hidden, lengths)
+    got = FastConformerLayers(*args, quant=mode).forward(hidden, lengths)
+    assert ob.device_status() == 0
+    valid = (torch.arange(120)[None, :] < torch.tensor(lengths)[:, None]).cuda()
+    cos = torch.nn.functional.cosine_similarity(got[valid].flatten().double(), ref[valid].flatten().double(), dim=0).item()
+    rel = ((got[valid] - ref[valid]).norm() / ref[valid].norm()).item()
+    print(f"{mode} FastConformer layers vs bf16: cosine {cos:.6f}, relative error {rel:.4f}")
+    assert cos >= 0.999, cos
