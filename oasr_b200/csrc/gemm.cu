@@ -933,13 +933,17 @@ template <> struct StagesFor<64> { static constexpr int v = 7; };   // 24 KB / s
 template <> struct StagesFor<128> { static constexpr int v = 5; };  // 32 KB / stage
 template <> struct StagesFor<256> { static constexpr int v = 4; };  // 48 KB / stage (+32 KB staging = 224 KB)
 
-int pick_bn(int64_t m_tiles_total, int64_t N) {
+int pick_bn(int64_t m_tiles_total, int64_t N, int64_t K = 512) {
   if (g_force_bn == 64 || g_force_bn == 128 || g_force_bn == 256) return g_force_bn;
   const int sms = sm_count();
   double best = 1e30;
   int best_bn = 128;
   const int cand[3] = {256, 128, 64};
-  const double unit_cost[3] = {1.0, 1.08, 1.25};  // relative cost per output column of the narrower tiles
+  // relative cost per output column of the narrower tiles: small at K = 512, where a tile is bound by its epilogue,
+  // growing with K as the main loop takes over (a 128-wide tile moves 1.4x the operand bytes per flop; measured
+  // 1.08 / 1.25 at K = 512, 1.45 / 2.0 at K >= 2048)
+  const double kf = K <= 512 ? 0.0 : (K >= 2048 ? 1.0 : static_cast<double>(K - 512) / 1536.0);
+  const double unit_cost[3] = {1.0, 1.08 + 0.37 * kf, 1.25 + 0.75 * kf};
   for (int i = 0; i < 3; ++i) {
     const int bn = cand[i];
     const int64_t tiles = m_tiles_total * ((N + bn - 1) / bn);
@@ -981,7 +985,7 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
   if (kSched == kSchedGroup) m_tiles_total = (pr.M + BM - 1) / BM + pr.groups;
   else m_tiles_total = ((pr.M + BM - 1) / BM) * (kSched == kSchedDense ? pr.batch : 1);
   const int64_t n_eff = kEpi == kEpiGlu ? 2 * pr.N : pr.N;  // accumulator columns
-  int bn = kEpi == kEpiLsm ? (g_force_bn ? g_force_bn : 256) : pick_bn(m_tiles_total, n_eff);
+  int bn = kEpi == kEpiLsm ? (g_force_bn ? g_force_bn : 256) : pick_bn(m_tiles_total, n_eff, pr.K);
   if (kEpi == kEpiGlu && bn < 128) bn = 128;  // half tiles of >= 64 columns
   constexpr bool kPairCapable = kSched == kSchedDense && (kEpi == kEpiStore || kEpi == kEpiGlu);
   const bool pair = kPairCapable && g_use_pairs && g_force_bn == 0 && pr.M >= 1024 && n_eff >= 256 && pr.K >= 128;
@@ -1062,7 +1066,7 @@ template <typename T, int kEpi, int kKind>
 int run_q8_typed(Params& p, const void* A, const void* B, int64_t M, int64_t N, int64_t K, int out_dtype, cudaStream_t s) {
   const int64_t n_eff = kEpi == kEpiGlu ? 2 * N : N;
   const int64_t m_tiles = (M + BM - 1) / BM;
-  int bn = pick_bn(m_tiles, n_eff);
+  int bn = pick_bn(m_tiles, n_eff, K / 2);   // 8-bit operands: half the bytes per K element
   if (kEpi == kEpiGlu && bn < 128) bn = 128;
   p.num_m_tiles = static_cast<int>(m_tiles);
   p.num_n_tiles = static_cast<int>((n_eff + bn - 1) / bn);
