@@ -74,7 +74,59 @@ unsigned grid_for(int64_t work_items, int block) {
 }  // namespace
 }  // namespace ob
 
+namespace ob {
+namespace {
+
+// Transformer-XL relative shift + scale + attention mask in one pass: bd (B, H, T, ld) holds the scores of query i
+// against the 2T-1 relative positions (column p = distance T-1-p); key j of query i sits at column (T-1) + j - i.
+// out (B, H, T, T) = visible(b, i, j) ? bd[b, h, i, T-1+j-i] * scale : floor, with the chunked-limited window
+// (query chunk - key chunk in [0, left_chunks], chunks of `chunk` frames) and key padding j < lengths[b]
+// (oasr/models/nemotron/encoder.py:82-96 rel_shift, :124-149 chunked_limited_mask, :343-348 mask floor).
+template <typename T>
+__global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out, const T* __restrict__ bd,
+                                                            const int32_t* __restrict__ lengths, int B, int H, int Tn, int ld,
+                                                            float scale, int chunk, int left_chunks, float floor_v) {
+  const int64_t total = static_cast<int64_t>(B) * H * Tn * Tn;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const int j = static_cast<int>(e % Tn);
+    int64_t r = e / Tn;
+    const int i = static_cast<int>(r % Tn);
+    r /= Tn;                                  // r = b * H + h
+    const int b = static_cast<int>(r / H);
+    const int dc = i / chunk - j / chunk;
+    const bool visible = dc >= 0 && dc <= left_chunks && j < lengths[b];
+    float v = floor_v;
+    if (visible) v = Elem<T>::to_f(bd[(r * Tn + i) * ld + (Tn - 1) + j - i]) * scale;
+    out[e] = Elem<T>::from_f(v);
+  }
+}
+
+}  // namespace
+}  // namespace ob
+
 extern "C" {
+
+int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, int64_t B, int64_t H, int64_t T, int64_t ld,
+                            double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(B >= 0 && H > 0 && T > 0 && ld >= 2 * T - 1 && chunk > 0 && left_chunks >= 0, OASR_ERR_INVALID,
+             "relshift_bias: bad shape");
+  if (B == 0) return OASR_OK;
+  OB_REQUIRE(out && bd && lengths, OASR_ERR_INVALID, "relshift_bias: null pointer argument");
+  const int64_t total = B * H * T * T;
+  int64_t g = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (g > cap) g = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
+    relshift_bias_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(static_cast<T_*>(out), static_cast<const T_*>(bd), lengths,
+                                                                      (int)B, (int)H, (int)T, (int)ld, (float)scale, (int)chunk,
+                                                                      (int)left_chunks, (float)floor_value);
+    return check_launch("relshift_bias launch");
+  });
+}
+
 
 int oasr_b200_glu(void* out, const void* in, int64_t rows, int64_t channels, int dtype, void* stream) {
   using namespace ob;

@@ -8,8 +8,8 @@ attention with a ``rel_shift``-ed position bias and the chunked-limited window
 (encoder.py:150-214), fused add+LayerNorm between the sub-layers, fp32 residual stream.
 Every contraction, normalisation, activation, convolution and the attention run on this package's
 kernels (head_dim 128 attention with an additive bias, ``layer_norm_activation``, causal
-``depthwise_conv1d``); the position bias is built by one batched GEMM against the projected
-relative table and shifted with the same pad/view identity as the reference, in torch.
+``depthwise_conv1d``); the position bias is one batched GEMM against the projected relative table
+followed by one kernel that applies the Transformer-XL shift, the scale and the window / padding mask.
 ``FastConformerEncoder`` puts the 8x causal depthwise-separable subsampling front end in front of the stack
 (oasr/models/nemotron/subsampling.py:26-131, 204-224): stem conv on the fp32 stencil kernel, two stages of
 depthwise 3x3 / stride-2 conv (own NHWC kernel) + pointwise GEMM with a fused ReLU, projection GEMM.  The RNN-T
@@ -107,7 +107,7 @@ class FastConformerLayers:
         return attn_mask.to(self.device), (silent.to(self.device) if bool(silent.any()) else None)
 
     # ---- one layer ----
-    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, attn_mask, silent, B: int, T: int) -> torch.Tensor:
+    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, lens_dev, silent, B: int, T: int) -> torch.Tensor:
         C, H, D = self.C, self.H, self.D
         qkv4 = self._linear(h, *lw["qkv4"]).view(B, T, 4, H, D)
         qu, qv, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(4))          # (B, H, T, D) views
@@ -119,11 +119,11 @@ class FastConformerLayers:
         Pp = (P + 7) // 8 * 8                                                         # GEMM needs N % 8 == 0
         if Pp != P:
             b = torch.nn.functional.pad(b, (0, 0, 0, Pp - P))
-        bd = OF.bmm(a.contiguous(), b.contiguous())[..., :P].reshape(B, H, T, P)
-        # Transformer-XL shift (pad one column, reinterpret (T, P+1) as (P+1, T), drop the first row)
-        shifted = torch.nn.functional.pad(bd, (1, 0)).view(B, H, -1, T)[:, :, 1:].reshape(B, H, T, P)
-        bias = (shifted[..., :T].float() * (D ** -0.5)).masked_fill(attn_mask.logical_not(), MASK_FLOOR).to(self.dtype)
-        out = fmha(qu.contiguous(), k.contiguous(), v.contiguous(), softmax_scale=D ** -0.5, attn_bias=bias.contiguous())
+        bd = OF.bmm(a.contiguous(), b.contiguous()).view(B, H, T, Pp)
+        # Transformer-XL shift, scale, chunked-limited window and key padding (finite floor) in one kernel
+        chunk = self.right + 1
+        bias = fused.relshift_bias(bd, lens_dev, T, D ** -0.5, chunk, self.left // chunk if self.left >= 0 else T, MASK_FLOOR)
+        out = fmha(qu.contiguous(), k.contiguous(), v.contiguous(), softmax_scale=D ** -0.5, attn_bias=bias)
         if silent is not None:
             out = out.masked_fill(silent.transpose(1, 2).unsqueeze(-1), 0.0)
         merged = out.permute(0, 2, 1, 3).reshape(B * T, C).contiguous()
@@ -145,7 +145,9 @@ class FastConformerLayers:
             raise RuntimeError("hidden must be a CUDA tensor (oasr_b200 has no CPU path)")
         B, T, C = hidden.shape
         M = B * T
-        attn_mask, silent = self._masks(T, [int(n) for n in lengths])
+        lengths = [int(n) for n in lengths]
+        _, silent = self._masks(T, lengths)
+        lens_dev = torch.tensor(lengths, dtype=torch.int32).to(self.device, non_blocking=True)
         rel_table = self._position_table(T)
         res = hidden.reshape(M, C).to(torch.float32, copy=True).contiguous()   # fp32 residual stream (updated in place: own copy)
         h = torch.empty(M, C, device=hidden.device, dtype=self.dtype)
@@ -156,7 +158,7 @@ class FastConformerLayers:
             w1, b1, w2, b2 = lw["feed_forward1"]
             y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
             fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_self_att"], eps=self.eps)
-            y = self._attention(lw, h, rel_table, attn_mask, silent, B, T)
+            y = self._attention(lw, h, rel_table, lens_dev, silent, B, T)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_conv"], eps=self.eps)
             y = self._conv(lw, h, silent, B, T)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_feed_forward2"], eps=self.eps)

@@ -97,3 +97,23 @@ def test_quantised_layer_stack_reaches_the_cosine_gate_against_the_16_bit_run(mo
     rel = ((got[valid] - ref[valid]).norm() / ref[valid].norm()).item()
     print(f"{mode} FastConformer layers vs bf16: cosine {cos:.6f}, relative error {rel:.4f}")
     assert cos >= 0.999, cos
+
+
+def test_relshift_bias_equals_the_pad_view_identity():
+    """One-kernel rel_shift + scale + window / padding mask against the reference's pad-and-reinterpret identity and
+    its mask (oasr/models/nemotron/encoder.py:82-96, 124-149, 343-348), bit for bit."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(4)
+    B, H, T, chunk, left = 3, 4, 37, 4, 8
+    P = 2 * T - 1
+    ld = (P + 7) // 8 * 8
+    bd = torch.randn(B, H, T, ld).bfloat16()
+    lengths = [37, 21, 30]
+    scale = 128 ** -0.5
+    got = fused.relshift_bias(bd.cuda(), torch.tensor(lengths, dtype=torch.int32).cuda(), T, scale, chunk, left // chunk).cpu()
+    shifted = OFC.rel_shift(bd[..., :P].float())[..., :T] * scale
+    window = OFC.chunked_limited_mask(T, T, left, chunk - 1).view(1, 1, T, T)
+    keep = (torch.arange(T)[None, :] < torch.tensor(lengths)[:, None]).view(B, 1, 1, T)
+    want = shifted.masked_fill((window & keep).logical_not(), -1.0e4).bfloat16()
+    assert torch.equal(got, want)
