@@ -292,10 +292,69 @@ def run_streaming(args):
     return 0
 
 
+def run_fastconformer(args):
+    """Config-4 style measurement (``--workload fastconformer``): FastConformer encoder (8x subsampling, 24 layers,
+    hidden 1024, 8 heads of 128, FFN 4096, kernel 9, 128 mel bins), random-init weights, one step = one padded batch
+    of 128 utterances with lengths uniform in 500..3000 frames.  ``--quant fp8|int8`` runs the layers' Linear GEMMs on
+    8-bit operands.  The encoder is a Python composition of this package's operators (not a one-call executor)."""
+    import oasr_b200
+    from oasr_b200 import _lib
+    from oasr_b200.fastconformer import FastConformerEncoder
+    from oracle import fastconformer as OFC   # seeded synthetic weights only (no oracle computation is timed)
+
+    torch.cuda.set_device(0)
+    layers = 24 if args.layers == 12 else args.layers
+    batch = 128 if args.batch == 64 else args.batch
+    cfg = OFC.FastConformerConfig(hidden=1024, heads=8, ffn=4096, layers=layers, kernel=9, sliding_window=57, lookahead=3, bias=False)
+    sub = OFC.SubsamplingConfig(mels=128, channels=256)
+    P = dict(OFC.init_params(cfg, 1234, w_std=0.02))
+    P.update(OFC.init_subsampling_params(sub, cfg.hidden, 1235))
+    enc = FastConformerEncoder(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead,
+                               sub.mels, sub.channels, P)
+    if args.quant != "none":
+        enc.stack.qkind = {"fp8": 1, "int8": 2}[args.quant]
+    rng = np.random.default_rng(2024)
+    lengths = [int(x) for x in rng.integers(500, 3001, size=batch)]
+    feats = torch.randn(batch, max(lengths), sub.mels, generator=torch.Generator().manual_seed(7)).cuda()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        enc.forward(feats, lengths)
+    torch.cuda.synchronize()
+    assert oasr_b200.device_status() == 0
+    sampler.rows.clear()
+    steps = min(args.steps, 10)
+    launches0 = _lib.launch_count()
+    evs = []
+    for _ in range(steps):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        enc.forward(feats, lengths)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    total_ms = float(sum(a.elapsed_time(b) for a, b in evs))
+    clocks = sampler.stop()
+    audio = sum(lengths) * FRAME_S * steps
+    print(json.dumps({
+        "metric": "audio_seconds_per_second", "value": audio / (total_ms * 1e-3), "unit": "audio-s/s", "n_gpus": 1,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
+        "data": "synthetic",
+        "config": {"workload": f"fastconformer{layers}_d1024_h8_ffn4096_k9_mel128_sub8x_b{batch}_len500-3000_padded",
+                   "audio_seconds_per_step": audio / steps, "l2": "256 MiB flush write between steps"},
+        "gpu_launches": int(_lib.launch_count() - launches0), "clocks": clocks}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="offline", choices=["offline", "streaming"],
-                    help="offline = the headline packed batch; streaming = 256 streams x one paged chunk per step")
+    ap.add_argument("--workload", default="offline", choices=["offline", "streaming", "fastconformer"],
+                    help="offline = the headline packed batch; streaming = 256 streams x one paged chunk per step; "
+                         "fastconformer = a padded batch through the FastConformer encoder (operator composition)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
@@ -317,6 +376,10 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
         return run_streaming(args)
+    if args.workload == "fastconformer":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
+        return run_fastconformer(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
