@@ -292,6 +292,98 @@ def run_streaming(args):
     return 0
 
 
+def run_sweep(args):
+    """Config-5 style measurement (``--workload sweep``): 4096 utterances with log-normal lengths (median 6 s, clipped
+    1-30 s) through the headline Conformer, sorted by length, packed to <= 8192 frames per pack
+    (oasr_b200.sharding.plan_packs, the reference's packing rule) and dealt to the ranks by cost
+    (assign_packs); no collective on the data path, token lists gathered on the host at the end.  One "step" = the
+    whole sweep.  ``--quant int8|fp8`` runs the Linear GEMMs on 8-bit operands (bf16 is the control)."""
+    import oasr_b200
+    from oasr_b200 import _lib, sharding
+    from oasr_b200.encoder import ConformerCTC
+    from oasr_b200.weights import init_params
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    cfg = model_config(args.layers)
+    model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16,
+                         quant=None if args.quant == "none" else args.quant)
+    n_utts = 4096 if args.batch == 64 else args.batch
+    rng = np.random.default_rng(2024)
+    lengths = [int(round(100 * min(max(x, 1.0), 30.0))) for x in rng.lognormal(np.log(6.0), 0.6, size=n_utts)]
+    packs = sharding.plan_packs(lengths, 8192, 4)
+    mine = sharding.assign_packs(lengths, packs, world)[rank]
+    g = torch.Generator(device=f"cuda:{local_rank}").manual_seed(7 + rank)
+    batches = []
+    for j in mine:
+        ls = [lengths[i] for i in packs[j]]
+        batches.append((packs[j], torch.randn(len(ls), max(ls), 80, generator=g, device=f"cuda:{local_rank}"), ls))
+
+    def sweep():
+        out = {}
+        for idx, feats, ls in batches:
+            _, _, argmax, pk = model._forward(feats, ls, False, False, True)
+            hyps = model._collapse(argmax.cpu().numpy(), pk.seg_lengths) if argmax is not None else [[] for _ in ls]
+            out.update(zip(idx, hyps))
+        return out
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for idx, feats, ls in batches[:3] + batches[-3:]:      # warm-up: smallest and largest shapes
+        model._forward(feats, ls, False, False, True)
+    barrier()
+    sampler.rows.clear()
+    launches0 = _lib.launch_count()
+    barrier()
+    t0 = time.perf_counter()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    local = sweep()
+    b.record()
+    torch.cuda.synchronize()
+    wall_s = time.perf_counter() - t0
+    dev_ms = a.elapsed_time(b)
+    clocks = sampler.stop()
+    assert oasr_b200.device_status() == 0
+    merged = sharding.gather_results(local, n_utts) if dist is not None else [local[i] for i in range(n_utts)]
+    t = torch.tensor([dev_ms, wall_s * 1e3], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        assert merged is not None and len(merged) == n_utts
+        audio = sum(lengths) * FRAME_S
+        print(json.dumps({
+            "metric": "audio_seconds_per_second", "value": audio / (float(t[0]) * 1e-3), "unit": "audio-s/s", "n_gpus": world,
+            "steps": 1, "warmup": 6, "ms_per_step": float(t[0]), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
+            "data": "synthetic",
+            "config": {"workload": f"sweep of {n_utts} utterances, log-normal lengths (median 6 s, 1-30 s), conformer{args.layers}_d512, "
+                                   f"{len(packs)} packs of <= 8192 frames, cost-balanced over {world} rank(s), no collective",
+                       "audio_seconds": audio},
+            "e2e": {"value": audio / (float(t[1]) * 1e-3), "unit": "audio-s/s",
+                    "api": "per pack: forward + D2H of the per-frame argmax + token collapse; features resident on the device"},
+            "gpu_launches": int(_lib.launch_count() - launches0), "clocks": clocks}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def run_fastconformer(args):
     """Config-4 style measurement (``--workload fastconformer``): FastConformer encoder (8x subsampling, 24 layers,
     hidden 1024, 8 heads of 128, FFN 4096, kernel 9, 128 mel bins), random-init weights, one step = one padded batch
@@ -352,7 +444,7 @@ def run_fastconformer(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="offline", choices=["offline", "streaming", "fastconformer"],
+    ap.add_argument("--workload", default="offline", choices=["offline", "streaming", "fastconformer", "sweep"],
                     help="offline = the headline packed batch; streaming = 256 streams x one paged chunk per step; "
                          "fastconformer = a padded batch through the FastConformer encoder (operator composition)")
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,6 +468,10 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
         return run_streaming(args)
+    if args.workload == "sweep":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
+        return run_sweep(args)
     if args.workload == "fastconformer":
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
