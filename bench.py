@@ -328,10 +328,8 @@ def run_sweep(args):
         batches.append((packs[j], torch.randn(len(ls), max(ls), 80, generator=g, device=f"cuda:{local_rank}"), ls))
 
     def sweep():
-        out = {}
-        for idx, feats, ls in batches:
-            _, _, argmax, pk = model._forward(feats, ls, False, False, True)
-            hyps = model._collapse(argmax.cpu().numpy(), pk.seg_lengths) if argmax is not None else [[] for _ in ls]
+        out = {}   # pipelined: the D2H read and token collapse of pack i run under the encoder of pack i+1
+        for (idx, _, _), hyps in zip(batches, model.greedy_search_batches((f, ls) for _, f, ls in batches)):
             out.update(zip(idx, hyps))
         return out
 
@@ -376,7 +374,7 @@ def run_sweep(args):
                                    f"{len(packs)} packs of <= 8192 frames, cost-balanced over {world} rank(s), no collective",
                        "audio_seconds": audio},
             "e2e": {"value": audio / (float(t[1]) * 1e-3), "unit": "audio-s/s",
-                    "api": "per pack: forward + D2H of the per-frame argmax + token collapse; features resident on the device"},
+                    "api": "ConformerCTC.greedy_search_batches over the packs (features resident on the device)"},
             "gpu_launches": int(_lib.launch_count() - launches0), "clocks": clocks}), flush=True)
     if dist is not None:
         dist.barrier()
