@@ -175,6 +175,7 @@ struct Dw2dArgs {
   const void* weight;   // (C, 3, 3) 16-bit
   const void* bias;     // nullable (C)
   const int32_t* out_len;
+  const int32_t* in_len;   // nullable: input frames >= in_len[b] count as zeros (whatever the buffer holds there)
   int B, T, F, C, To, Fo, pad_lo;
 };
 
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(256) depthwise_conv2d_k3s2_kernel(Dw2dArgs a) 
 #pragma unroll
     for (int q = 0; q < 8; ++q) acc[q] = 0.f;
     const bool live = !a.out_len || to < a.out_len[b];
+    const int t_end = a.in_len ? min(a.T, a.in_len[b]) : a.T;
     if (live) {
       if (a.bias) {
         const Pack<T> bb = ld128(static_cast<const T*>(a.bias) + c0);
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(256) depthwise_conv2d_k3s2_kernel(Dw2dArgs a) 
 #pragma unroll
       for (int di = 0; di < 3; ++di) {
         const int t = 2 * to + di - a.pad_lo;
-        if (t < 0 || t >= a.T) continue;
+        if (t < 0 || t >= t_end) continue;
 #pragma unroll
         for (int dj = 0; dj < 3; ++dj) {
           const int f = 2 * fo + dj - a.pad_lo;
@@ -285,7 +287,7 @@ int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const float* weigh
 }
 
 int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weight, const void* bias,
-                                    const int32_t* out_len, int64_t B, int64_t T, int64_t F, int64_t C, int64_t pad_lo,
+                                    const int32_t* out_len, const int32_t* in_len, int64_t B, int64_t T, int64_t F, int64_t C, int64_t pad_lo,
                                     int64_t pad_hi, int dtype, void* stream) {
   using namespace ob;
   OB_REQUIRE(B >= 0 && T > 0 && F > 0 && C > 0 && pad_lo >= 0 && pad_hi >= 0, OASR_ERR_INVALID,
@@ -296,7 +298,7 @@ int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weigh
   OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "depthwise_conv2d_k3s2: null pointer argument");
   OB_REQUIRE(C % 8 == 0 && is_aligned(out, 16) && is_aligned(in, 16) && (!bias || is_aligned(bias, 16)), OASR_ERR_ALIGN,
              "depthwise_conv2d_k3s2: channels must be a multiple of 8 and the tensors 16-byte aligned");
-  Dw2dArgs a{out, in, weight, bias, out_len, (int)B, (int)T, (int)F, (int)C,
+  Dw2dArgs a{out, in, weight, bias, out_len, in_len, (int)B, (int)T, (int)F, (int)C,
              (int)((T + pad_lo + pad_hi - 3) / 2 + 1), (int)((F + pad_lo + pad_hi - 3) / 2 + 1), (int)pad_lo};
   const int64_t total = B * a.To * a.Fo * (C / 8);
   int64_t g = (total + 255) / 256;

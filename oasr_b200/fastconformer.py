@@ -123,7 +123,7 @@ class FastConformerLayers:
         # Transformer-XL shift, scale, chunked-limited window and key padding (finite floor) in one kernel
         chunk = self.right + 1
         bias = fused.relshift_bias(bd, lens_dev, T, D ** -0.5, chunk, self.left // chunk if self.left >= 0 else T, MASK_FLOOR)
-        out = fmha(qu.contiguous(), k.contiguous(), v.contiguous(), softmax_scale=D ** -0.5, attn_bias=bias)
+        out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias)     # strided (B, H, T, D) views of the projection
         if silent is not None:
             out = out.masked_fill(silent.transpose(1, 2).unsqueeze(-1), 0.0)
         merged = out.permute(0, 2, 1, 3).reshape(B * T, C).contiguous()
@@ -198,21 +198,19 @@ class FastConformerEncoder:
         self.proj = (w(params[s + "linear.weight"]), w(params[s + "linear.bias"]))
 
     def subsample(self, feats: torch.Tensor, lengths: List[int]):
+        """Frames at or past a row's valid length are never zeroed in memory: every consumer reads them as zeros
+        (``in_len`` of the depthwise conv) or ignores them, so valid frames equal the reference's, padded frames differ."""
         B = feats.size(0)
         nxt = lambda ls: [(n + 2 + 1 - 3) // 2 + 1 for n in ls]
+        dev_i32 = lambda ls: torch.tensor(ls, dtype=torch.int32).to(self.device, non_blocking=True)
         # stem: one input channel, pad (2, 1) on time and frequency, 3x3 / stride 2, + bias + ReLU (fp32 in, 16-bit NHWC out)
         x = fused.subsample_conv1(torch.nn.functional.pad(feats.float(), (2, 1, 2, 1)), *self.conv_in, self.dtype)
         lengths = nxt(lengths)
-        keep = (torch.arange(x.size(1))[None, :] < torch.tensor(lengths)[:, None]).to(self.device)
-        x = x * keep[:, :, None, None].to(x.dtype)                       # frames past the valid length back to zero
         for dw_w, dw_b, pw_w, pw_b in self.sub_stages:
-            lengths = nxt(lengths)
-            lens_dev = torch.tensor(lengths, dtype=torch.int32).to(self.device, non_blocking=True)
-            x = fused.depthwise_conv2d_k3s2(x, dw_w, dw_b, 2, 1, out_len=lens_dev)       # masked frames come out zero
+            in_len, lengths = lengths, nxt(lengths)
+            x = fused.depthwise_conv2d_k3s2(x, dw_w, dw_b, 2, 1, out_len=dev_i32(lengths), in_len=dev_i32(in_len))
             _, T, Fd, C = x.shape
             x = OF.gemm_activation(x.view(B * T * Fd, C), pw_w, pw_b, 0).view(B, T, Fd, C)   # pointwise conv + ReLU
-            keep = (torch.arange(T)[None, :] < torch.tensor(lengths)[:, None]).to(self.device)
-            x = x * keep[:, :, None, None].to(x.dtype)
         B, T, Fd, C = x.shape
         return OF.gemm(x.reshape(B * T, Fd * C), *self.proj).view(B, T, -1), lengths
 
