@@ -452,14 +452,15 @@ OASR_API int oasr_b200_fmha_paged_relpos_fp8(void* out, const void* qkv4, void* 
                                              int64_t block_size, int64_t num_blocks, double scale,
                                              int dtype, void* stream);
 
-/* Attention bias of the FastConformer layer in one pass: out (B, H, T, T) 16-bit =
+/* Attention bias of the FastConformer layer in one pass: out (B, H, T, T) 16-bit with row stride ld_out >= T
+ * elements (a multiple of 8 lets the attention kernel fetch it in 16-byte pieces; columns T..ld_out-1 are not written) =
  * visible(b,i,j) ? bd[b,h,i,(T-1)+j-i] * scale : floor_value, where bd (B, H, T, ld >= 2T-1) are the scores of the
  * position-biased queries against the 2T-1 projected relative positions, and visible = key j in the query's chunked-
  * limited window (i/chunk - j/chunk in [0, left_chunks]) and j < lengths[b].  Replaces rel_shift, the scale, the
  * window & padding mask and the masked_fill of oasr/models/nemotron/encoder.py:82-96, 124-149, 343-348. */
 OASR_API int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, int64_t B, int64_t H,
-                                     int64_t T, int64_t ld, double scale, int64_t chunk, int64_t left_chunks,
-                                     double floor_value, int dtype, void* stream);
+                                     int64_t T, int64_t ld, int64_t ld_out, double scale, int64_t chunk,
+                                     int64_t left_chunks, double floor_value, int dtype, void* stream);
 
 /* ---- paged KV cache ---------------------------------------------------- */
 /* paged_kv_write with quantisation: 16-bit k_new / v_new (element strides as below, unit stride along

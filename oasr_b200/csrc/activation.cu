@@ -84,21 +84,29 @@ namespace {
 // (oasr/models/nemotron/encoder.py:82-96 rel_shift, :124-149 chunked_limited_mask, :343-348 mask floor).
 template <typename T>
 __global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out, const T* __restrict__ bd,
-                                                            const int32_t* __restrict__ lengths, int B, int H, int Tn, int ld,
+                                                            const int32_t* __restrict__ lengths, int B, int H, int Tn, int ld, int ld_out,
                                                             float scale, int chunk, int left_chunks, float floor_v) {
-  const int64_t total = static_cast<int64_t>(B) * H * Tn * Tn;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
-    const int j = static_cast<int>(e % Tn);
-    int64_t r = e / Tn;
-    const int i = static_cast<int>(r % Tn);
-    r /= Tn;                                  // r = b * H + h
+  // One warp per output row (b, h, i): the visible keys of a row are one interval [lo, hi), so the per-element work is a
+  // compare, a 2-byte load at a row-constant offset and a store; the row decomposition is done once per warp.
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = static_cast<int64_t>(B) * H * Tn;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const T floor_t = Elem<T>::from_f(floor_v);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += wstride) {
+    const int64_t r = row / Tn;               // b * H + h
+    const int i = static_cast<int>(row - r * Tn);
     const int b = static_cast<int>(r / H);
-    const int dc = i / chunk - j / chunk;
-    const bool visible = dc >= 0 && dc <= left_chunks && j < lengths[b];
-    float v = floor_v;
-    if (visible) v = Elem<T>::to_f(bd[(r * Tn + i) * ld + (Tn - 1) + j - i]) * scale;
-    out[e] = Elem<T>::from_f(v);
+    const int qc = i / chunk;
+    const int lo = max(0, (qc - left_chunks) * chunk);
+    const int hi = min(min((qc + 1) * chunk, Tn), lengths[b]);
+    const T* src = bd + row * ld + (Tn - 1 - i);
+    T* dst = out + row * ld_out;
+#pragma unroll 4
+    for (int j = lane; j < Tn; j += 32) {
+      T v = floor_t;
+      if (j >= lo && j < hi) v = Elem<T>::from_f(Elem<T>::to_f(src[j]) * scale);
+      dst[j] = v;
+    }
   }
 }
 
@@ -108,20 +116,22 @@ __global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out,
 extern "C" {
 
 int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, int64_t B, int64_t H, int64_t T, int64_t ld,
-                            double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {
+                            int64_t ld_out, double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(B >= 0 && H > 0 && T > 0 && ld >= 2 * T - 1 && chunk > 0 && left_chunks >= 0, OASR_ERR_INVALID,
+  OB_REQUIRE(B >= 0 && H > 0 && T > 0 && ld >= 2 * T - 1 && ld_out >= T && chunk > 0 && left_chunks >= 0, OASR_ERR_INVALID,
              "relshift_bias: bad shape");
   if (B == 0) return OASR_OK;
   OB_REQUIRE(out && bd && lengths, OASR_ERR_INVALID, "relshift_bias: null pointer argument");
-  const int64_t total = B * H * T * T;
-  int64_t g = (total + 255) / 256;
+  const int64_t rows = B * H * T;
+  if (chunk > T) chunk = T;              // every frame is in chunk 0 either way; keeps the interval arithmetic in int range
+  if (left_chunks > T) left_chunks = T;
+  int64_t g = (rows + 7) / 8;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   if (g > cap) g = cap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
     relshift_bias_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(static_cast<T_*>(out), static_cast<const T_*>(bd), lengths,
-                                                                      (int)B, (int)H, (int)T, (int)ld, (float)scale, (int)chunk,
+                                                                      (int)B, (int)H, (int)T, (int)ld, (int)ld_out, (float)scale, (int)chunk,
                                                                       (int)left_chunks, (float)floor_value);
     return check_launch("relshift_bias launch");
   });

@@ -99,6 +99,17 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
+template <typename T>
+__device__ __forceinline__ float unpack_lo(uint32_t w) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) return __uint_as_float(w << 16);
+  else return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu)));
+}
+template <typename T>
+__device__ __forceinline__ float unpack_hi(uint32_t w) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) return __uint_as_float(w & 0xffff0000u);
+  else return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+}
+
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -349,6 +360,7 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
       }
     }
     const bool row_ok = r < rows_valid;
+    const bool bias_vec = bias_row && p.mode == kDense && (reinterpret_cast<uintptr_t>(bias_row) & 15u) == 0;
     float m_run = kNegInf, l_run = 0.f, alpha_prev = 1.f;
     float o[D];
 #pragma unroll
@@ -456,12 +468,36 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
         for (int c0 = 0; c0 < BKV; c0 += 32) {
           uint32_t v[32];
           ptx::tmem_ld_32x32(t_s + c0, v);
+          // bias of keys c0..c0+31 of this row, packed two per word: 16-byte loads where the row is aligned and the
+          // group of 8 lies inside the bias width, element loads (predicated on the key range) otherwise
+          uint32_t bw[16];
+          if (bias_row && row_ok) {
+            const T* bp = bias_row + key0 + c0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int kg = key0 + c0 + g * 8;
+              if (bias_vec && kg + 8 <= p.Tk) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(bp + g * 8));
+                bw[g * 4] = w.x; bw[g * 4 + 1] = w.y; bw[g * 4 + 2] = w.z; bw[g * 4 + 3] = w.w;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                  const float b0 = kg + e < kv_len ? Elem<T>::to_f(__ldg(bp + g * 8 + e)) : 0.f;
+                  const float b1 = kg + e + 1 < kv_len ? Elem<T>::to_f(__ldg(bp + g * 8 + e + 1)) : 0.f;
+                  bw[g * 4 + e / 2] = pack2<T>(b0, b1);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) bw[i] = 0u;
+          }
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c0 + i;
-            float x = __uint_as_float(v[i]) * p.scale_log2;
-            if (bias_row && row_ok && key < kv_len) x = fmaf(Elem<T>::to_f(__ldg(bias_row + key)), 1.4426950408889634f, x);
+            const float bf = (i & 1) ? unpack_hi<T>(bw[i / 2]) : unpack_lo<T>(bw[i / 2]);
+            float x = fmaf(bf, 1.4426950408889634f, __uint_as_float(v[i]) * p.scale_log2);
             const bool visible = key < kv_len && key >= kv_start && !(p.causal && key > row_in_seq);
             x = visible ? x : kNegInf;
             tile_max = fmaxf(tile_max, x);

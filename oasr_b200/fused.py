@@ -187,14 +187,15 @@ def depthwise_conv2d_k3s2(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
 
 def relshift_bias(bd: torch.Tensor, lengths: torch.Tensor, T: int, scale: float, chunk: int, left_chunks: int,
                   floor_value: float = -1.0e4) -> torch.Tensor:
-    """``bd (B, H, T, ld >= 2T-1)`` position scores -> attention bias ``(B, H, T, T)``: Transformer-XL relative shift,
+    """``bd (B, H, T, ld >= 2T-1)`` position scores -> attention bias ``(B, H, T, T)`` (a view whose rows are padded to a multiple of 8 elements): Transformer-XL relative shift,
     scale, chunked-limited window and key-padding mask with a finite floor, in one kernel
     (oasr/models/nemotron/encoder.py:82-96, 124-149, 343-348)."""
     _need_cuda(bd, lengths)
     B, H, Tq, ld = bd.shape
     if Tq != T or not bd.is_contiguous():
         raise ValueError("bd must be contiguous (B, H, T, ld)")
-    out = torch.empty(B, H, T, T, device=bd.device, dtype=bd.dtype)
-    _lib.call("oasr_b200_relshift_bias", _p(out), _p(bd), _p(lengths), B, H, T, ld, float(scale), int(chunk), int(left_chunks),
+    ld_out = (T + 7) // 8 * 8          # rows start on 16-byte boundaries so the attention kernel reads them in 16-byte pieces
+    out = torch.empty(B, H, T, ld_out, device=bd.device, dtype=bd.dtype)
+    _lib.call("oasr_b200_relshift_bias", _p(out), _p(bd), _p(lengths), B, H, T, ld, ld_out, float(scale), int(chunk), int(left_chunks),
               float(floor_value), _DTYPE_ID[bd.dtype], _stream(bd))
-    return out
+    return out[..., :T]
