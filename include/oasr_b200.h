@@ -347,6 +347,13 @@ OASR_API int oasr_b200_gemm_glu(void* D, const void* A, const void* B,
  * bmm (csrc/bmm.cu, oasr/functionals/gemm.py:262-299). */
 OASR_API int oasr_b200_bmm(void* D, const void* A, const void* B, int64_t batch, int64_t M,
                            int64_t N, int64_t K, int dtype, void* stream);
+/* bmm over strided views: row m of A[b] starts at A + b*stride_a + m*lda elements (likewise B with stride_b, ldb),
+ * unit stride along K; all four strides are multiples of 8 elements.  D is packed (batch, M, N).  Lets the per-head
+ * operands of an attention layer be read in place from a (tokens, heads, head_dim) projection (batch = head:
+ * stride = head_dim, ld = heads*head_dim) instead of being copied head-major first. */
+OASR_API int oasr_b200_bmm_strided(void* D, const void* A, const void* B, int64_t batch, int64_t M,
+                                   int64_t N, int64_t K, int64_t lda, int64_t stride_a, int64_t ldb,
+                                   int64_t stride_b, int dtype, void* stream);
 /* Grouped GEMM: rows [offsets[g-1], offsets[g]) of A (L,K) times B[g] (N,K)^T.
  * `offsets` is a DEVICE int32 array of `groups` cumulative END rows; it is
  * read on the device (no host synchronisation, unlike the reference launcher
@@ -393,6 +400,20 @@ OASR_API int oasr_b200_fmha(void* out, const void* q, const void* k, const void*
                             int64_t block_size, int64_t num_blocks, int64_t B, int64_t H,
                             int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale,
                             int causal, int dtype, void* stream);
+/* Same attention, but out is written token-major, (B, Tq, H, D): the layout the output projection reads, which the
+ * reference reaches with transpose(1, 2).contiguous() after its fmha call (oasr/layers/attention/attention.py). */
+OASR_API int oasr_b200_fmha_bthd(void* out, const void* q, const void* k, const void* v,
+                                 const int64_t* q_strides /*host, nullable*/,
+                                 const int64_t* k_strides /*host, nullable*/,
+                                 const int64_t* v_strides /*host, nullable*/,
+                                 const void* bias /*nullable*/, int64_t bias_stride_b,
+                                 int64_t bias_stride_h, int64_t bias_stride_q,
+                                 const int32_t* seqlens /*nullable*/,
+                                 const int32_t* seqstarts /*nullable*/,
+                                 const int32_t* block_table /*nullable*/, int64_t blocks_per_seq,
+                                 int64_t block_size, int64_t num_blocks, int64_t B, int64_t H,
+                                 int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale,
+                                 int causal, int dtype, void* stream);
 /* Packed variable-length attention, the reference's fmha_varlen
  * (oasr/functionals/attention.py:592-693): q, out (total_q,H,D); k, v
  * (total_k,Hkv,D); cu_seqlens_* int32[S+1]; bias (nullable) flat, segment s is
@@ -454,12 +475,13 @@ OASR_API int oasr_b200_fmha_paged_relpos_fp8(void* out, const void* qkv4, void* 
 
 /* Attention bias of the FastConformer layer in one pass: out (B, H, T, T) 16-bit with row stride ld_out >= T
  * elements (a multiple of 8 lets the attention kernel fetch it in 16-byte pieces; columns T..ld_out-1 are not written) =
- * visible(b,i,j) ? bd[b,h,i,(T-1)+j-i] * scale : floor_value, where bd (B, H, T, ld >= 2T-1) are the scores of the
+ * visible(b,i,j) ? bd[b,h,i,(T-1)+j-i] * scale : floor_value, where bd (B, H, T, ld >= 2T-1; batch / head strides bd_stride_b / _h elements) are the scores of the
  * position-biased queries against the 2T-1 projected relative positions, and visible = key j in the query's chunked-
  * limited window (i/chunk - j/chunk in [0, left_chunks]) and j < lengths[b].  Replaces rel_shift, the scale, the
  * window & padding mask and the masked_fill of oasr/models/nemotron/encoder.py:82-96, 124-149, 343-348. */
 OASR_API int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, int64_t B, int64_t H,
-                                     int64_t T, int64_t ld, int64_t ld_out, double scale, int64_t chunk,
+                                     int64_t T, int64_t ld, int64_t ld_out, int64_t bd_stride_b /*0 = H*T*ld*/,
+                                     int64_t bd_stride_h /*0 = T*ld*/, double scale, int64_t chunk,
                                      int64_t left_chunks, double floor_value, int dtype, void* stream);
 
 /* ---- paged KV cache ---------------------------------------------------- */

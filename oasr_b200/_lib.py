@@ -60,7 +60,7 @@ _SIGNATURES = {
     "oasr_b200_gemm_q8": [P, P, P, P, P, P, I, I, I, c_int, c_int, c_int, c_int, P],
     "oasr_b200_quantize_rows": [P, P, P, I, I, c_int, c_int, P],
     "oasr_b200_subsample_conv1": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
-    "oasr_b200_relshift_bias": [P, P, P, I, I, I, I, I, c_double, I, I, c_double, c_int, P],
+    "oasr_b200_relshift_bias": [P, P, P, I, I, I, I, I, I, I, c_double, I, I, c_double, c_int, P],
     "oasr_b200_depthwise_conv2d_k3s2": [P, P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv1_s2d": [P, P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv2": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
@@ -71,6 +71,8 @@ _SIGNATURES = {
     "oasr_b200_group_gemm": [P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_gemm_log_softmax": [P, P, P, P, I, I, I, c_int, c_int, P, P],
     "oasr_b200_fmha": [P, P, P, P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_bmm_strided": [P, P, P, I, I, I, I, I, I, I, I, c_int, P],
+    "oasr_b200_fmha_bthd": [P, P, P, P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
     "oasr_b200_fmha_varlen": [P, P, P, P, P, P, c_int, P, P, I, I, I, I, I, I, I, c_double, c_int, P],
     "oasr_b200_paged_kv_write": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, c_int, P],
     "oasr_b200_paged_kv_gather": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],

@@ -55,7 +55,7 @@ def gather_paged_kv(k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: tor
 def fmha(q, k, v, *, softmax_scale: float, attn_bias: Optional[torch.Tensor] = None,
          cache_seqlens: Optional[torch.Tensor] = None, cache_seqstarts: Optional[torch.Tensor] = None,
          block_table: Optional[torch.Tensor] = None, causal: bool = False, out: Optional[torch.Tensor] = None,
-         validate: bool = True) -> torch.Tensor:
+         validate: bool = True, token_major: bool = False) -> torch.Tensor:
     """Fused multi-head attention (reference: functionals/attention.py:369-551).
 
     ``q`` ``(B, H, T_q, D)``; dense ``k``/``v`` ``(B, H_kv, T_k, D)`` or, with
@@ -65,6 +65,8 @@ def fmha(q, k, v, *, softmax_scale: float, attn_bias: Optional[torch.Tensor] = N
     ``[start, len)``; ``causal`` masks ``k_col > q_row``.  A fully masked row gives zeros.
     Unlike the reference wrapper no padding of the bias or widening of the block table
     is needed: the kernel predicates its bias reads and clamps page lookups.
+    ``token_major=True`` (an extension) returns ``(B, T_q, H, D)``, the layout the output
+    projection reads, instead of ``(B, H, T_q, D)``.
     """
     _need_cuda(q, k, v, attn_bias, cache_seqlens, cache_seqstarts, block_table, out)
     if q.dim() != 4:
@@ -114,10 +116,11 @@ def fmha(q, k, v, *, softmax_scale: float, attn_bias: Optional[torch.Tensor] = N
                 raise ValueError("block_table must be (B, max_blocks_per_seq)")
             if block_table.dtype != torch.int32:
                 block_table = block_table.to(torch.int32)
-        if out is not None and (out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous()):
-            raise ValueError("out must be contiguous and match q in shape/dtype")
+        want = (B, T_q, H, D) if token_major else (B, H, T_q, D)
+        if out is not None and (tuple(out.shape) != want or out.dtype != q.dtype or not out.is_contiguous()):
+            raise ValueError(f"out must be contiguous {want} in q's dtype")
     if out is None:
-        out = torch.empty(q.shape, dtype=q.dtype, device=q.device, memory_format=torch.contiguous_format)
+        out = torch.empty((B, T_q, H, D) if token_major else (B, H, T_q, D), dtype=q.dtype, device=q.device)
     q, qs = _canon(q)
     if paged:
         k, v = k.contiguous(), v.contiguous()
@@ -135,7 +138,8 @@ def fmha(q, k, v, *, softmax_scale: float, attn_bias: Optional[torch.Tensor] = N
         if attn_bias.stride(3) != 1 and attn_bias.size(3) > 1:
             attn_bias = attn_bias.contiguous()
         bsb, bsh, bsq = attn_bias.stride(0), attn_bias.stride(1), attn_bias.stride(2)
-    _lib.call("oasr_b200_fmha", _p(out), _p(q), _p(k), _p(v), qs, ks, vs, _p(attn_bias), bsb, bsh, bsq,
+    _lib.call("oasr_b200_fmha_bthd" if token_major else "oasr_b200_fmha", _p(out), _p(q), _p(k), _p(v), qs, ks, vs,
+              _p(attn_bias), bsb, bsh, bsq,
               _p(cache_seqlens), _p(cache_seqstarts), _p(block_table),
               block_table.size(1) if paged else 0, block_size, num_blocks, B, H, H_kv, T_q, T_k, D,
               float(softmax_scale), int(bool(causal)), _DTYPE_ID[q.dtype], _stream(q))

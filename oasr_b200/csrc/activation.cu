@@ -85,6 +85,7 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out, const T* __restrict__ bd,
                                                             const int32_t* __restrict__ lengths, int B, int H, int Tn, int ld, int ld_out,
+                                                            int64_t bd_sb, int64_t bd_sh,
                                                             float scale, int chunk, int left_chunks, float floor_v) {
   // One warp per output row (b, h, i): the visible keys of a row are one interval [lo, hi), so the per-element work is a
   // compare, a 2-byte load at a row-constant offset and a store; the row decomposition is done once per warp.
@@ -96,10 +97,11 @@ __global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out,
     const int64_t r = row / Tn;               // b * H + h
     const int i = static_cast<int>(row - r * Tn);
     const int b = static_cast<int>(r / H);
+    const int h = static_cast<int>(r - static_cast<int64_t>(b) * H);
     const int qc = i / chunk;
     const int lo = max(0, (qc - left_chunks) * chunk);
     const int hi = min(min((qc + 1) * chunk, Tn), lengths[b]);
-    const T* src = bd + row * ld + (Tn - 1 - i);
+    const T* src = bd + b * bd_sb + h * bd_sh + static_cast<int64_t>(i) * ld + (Tn - 1 - i);
     T* dst = out + row * ld_out;
 #pragma unroll 4
     for (int j = lane; j < Tn; j += 32) {
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out,
 extern "C" {
 
 int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, int64_t B, int64_t H, int64_t T, int64_t ld,
-                            int64_t ld_out, double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {
+                            int64_t ld_out, int64_t bd_stride_b, int64_t bd_stride_h, double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {
   using namespace ob;
   OB_REQUIRE(B >= 0 && H > 0 && T > 0 && ld >= 2 * T - 1 && ld_out >= T && chunk > 0 && left_chunks >= 0, OASR_ERR_INVALID,
              "relshift_bias: bad shape");
@@ -131,7 +133,8 @@ int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, i
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
     relshift_bias_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(static_cast<T_*>(out), static_cast<const T_*>(bd), lengths,
-                                                                      (int)B, (int)H, (int)T, (int)ld, (int)ld_out, (float)scale, (int)chunk,
+                                                                      (int)B, (int)H, (int)T, (int)ld, (int)ld_out, bd_stride_b ? bd_stride_b : H * T * ld,
+                                                                      bd_stride_h ? bd_stride_h : T * ld, (float)scale, (int)chunk,
                                                                       (int)left_chunks, (float)floor_value);
     return check_launch("relshift_bias launch");
   });

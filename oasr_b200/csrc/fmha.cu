@@ -738,12 +738,12 @@ int oasr_b200_fmha_paged_relpos_fp8(void* out, const void* qkv4, void* k_pool, v
                          static_cast<cudaStream_t>(stream));
 }
 
-int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,
+static int fmha_dense_or_paged(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,
                    const int64_t* k_strides, const int64_t* v_strides, const void* bias, int64_t bias_stride_b,
                    int64_t bias_stride_h, int64_t bias_stride_q, const int32_t* seqlens, const int32_t* seqstarts,
                    const int32_t* block_table, int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks,
                    int64_t B, int64_t H, int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale, int causal,
-                   int dtype, void* stream) {
+                   int dtype, void* stream, int out_token_major) {
   using namespace ob;
   using namespace ob::fmha;
   OB_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && Tq >= 0 && Tk >= 0 && D > 0, OASR_ERR_INVALID, "fmha: bad shape");
@@ -805,9 +805,31 @@ int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v, const
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.causal = causal; p.seqlens = seqlens; p.seqstarts = seqstarts;
   p.bias = bias; p.bias_sb = bias_stride_b; p.bias_sh = bias_stride_h; p.bias_sq = bias_stride_q;
-  p.out = out; p.status = device_status_ptr();
+  p.out = out; p.out_token_major = out_token_major; p.status = device_status_ptr();
   dim3 grid((unsigned)((Tq + BQ - 1) / BQ), (unsigned)H, (unsigned)B);
   return dispatch(maps, p, (int)D, dtype, grid, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_fmha(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,
+                   const int64_t* k_strides, const int64_t* v_strides, const void* bias, int64_t bias_stride_b,
+                   int64_t bias_stride_h, int64_t bias_stride_q, const int32_t* seqlens, const int32_t* seqstarts,
+                   const int32_t* block_table, int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks,
+                   int64_t B, int64_t H, int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale, int causal,
+                   int dtype, void* stream) {
+  return fmha_dense_or_paged(out, q, k, v, q_strides, k_strides, v_strides, bias, bias_stride_b, bias_stride_h,
+                             bias_stride_q, seqlens, seqstarts, block_table, blocks_per_seq, block_size, num_blocks, B, H,
+                             Hkv, Tq, Tk, D, scale, causal, dtype, stream, 0);
+}
+
+int oasr_b200_fmha_bthd(void* out, const void* q, const void* k, const void* v, const int64_t* q_strides,
+                        const int64_t* k_strides, const int64_t* v_strides, const void* bias, int64_t bias_stride_b,
+                        int64_t bias_stride_h, int64_t bias_stride_q, const int32_t* seqlens, const int32_t* seqstarts,
+                        const int32_t* block_table, int64_t blocks_per_seq, int64_t block_size, int64_t num_blocks,
+                        int64_t B, int64_t H, int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale, int causal,
+                        int dtype, void* stream) {
+  return fmha_dense_or_paged(out, q, k, v, q_strides, k_strides, v_strides, bias, bias_stride_b, bias_stride_h,
+                             bias_stride_q, seqlens, seqstarts, block_table, blocks_per_seq, block_size, num_blocks, B, H,
+                             Hkv, Tq, Tk, D, scale, causal, dtype, stream, 1);
 }
 
 int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, const void* v, const void* bias,

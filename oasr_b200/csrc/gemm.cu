@@ -959,6 +959,7 @@ struct Problem {
   int64_t M, N, K, batch, groups;
   const void *A, *B;
   Params p;
+  int64_t lda = 0, a_bs = 0, ldb = 0, b_bs = 0;   // element strides of A / B rows and batches; 0 = packed
 };
 
 template <typename T>
@@ -969,11 +970,13 @@ int make_maps(const Problem& pr, int bn, int dtype, CUtensorMap* ta, CUtensorMap
   const int64_t b_rows = pr.epi == kEpiGlu ? 2 * pr.N : pr.N;
   const int64_t b_batch = pr.sched == kSchedDense ? pr.batch : (pr.sched == kSchedGroup ? pr.groups : 1);
   uint64_t adims[3] = {(uint64_t)pr.K, (uint64_t)a_rows, (uint64_t)a_batch};
-  uint64_t astr[3] = {0, (uint64_t)pr.K * 2, (uint64_t)pr.K * 2 * (uint64_t)a_rows};
+  uint64_t astr[3] = {0, (uint64_t)(pr.lda ? pr.lda : pr.K) * 2,
+                      pr.a_bs ? (uint64_t)pr.a_bs * 2 : (uint64_t)pr.K * 2 * (uint64_t)a_rows};
   uint32_t abox[3] = {BK, BM, 1};
   if (int rc = make_tensor_map(ta, tma_dtype(dtype), 3, pr.A, adims, astr, abox)) return rc;
   uint64_t bdims[3] = {(uint64_t)pr.K, (uint64_t)b_rows, (uint64_t)b_batch};
-  uint64_t bstr[3] = {0, (uint64_t)pr.K * 2, (uint64_t)pr.K * 2 * (uint64_t)b_rows};
+  uint64_t bstr[3] = {0, (uint64_t)(pr.ldb ? pr.ldb : pr.K) * 2,
+                      pr.b_bs ? (uint64_t)pr.b_bs * 2 : (uint64_t)pr.K * 2 * (uint64_t)b_rows};
   uint32_t bbox[3] = {BK, (uint32_t)((pr.epi == kEpiGlu || pair) ? bn / 2 : bn), 1};
   return make_tensor_map(tb, tma_dtype(dtype), 3, pr.B, bdims, bstr, bbox);
 }
@@ -1206,6 +1209,28 @@ int oasr_b200_bmm(void* D, const void* A, const void* B, int64_t batch, int64_t 
   pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = (int)batch;
   pr.p.D = D; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
   return run<kSchedDense, kEpiStore>(pr, dtype, s);
+}
+
+int oasr_b200_bmm_strided(void* D, const void* A, const void* B, int64_t batch, int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t stride_a, int64_t ldb, int64_t stride_b, int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("bmm_strided", D, A, B, nullptr, M, N, K)) return rc;
+  OB_REQUIRE(batch >= 0 && batch < 65536, OASR_ERR_INVALID, "bmm_strided: bad batch %lld", (long long)batch);
+  OB_REQUIRE(lda >= K && ldb >= K && stride_a > 0 && stride_b > 0 && lda % 8 == 0 && ldb % 8 == 0 && stride_a % 8 == 0 &&
+                 stride_b % 8 == 0,
+             OASR_ERR_ALIGN, "bmm_strided: row and batch strides must be positive multiples of 8 elements, rows >= K");
+  if (M == 0 || batch == 0) return OASR_OK;
+  OB_REQUIRE(!use_simt(M, N, K), OASR_ERR_UNSUPPORTED,
+             "bmm_strided: shape (%lld, %lld, %lld) is below the tensor-core kernel's range; use bmm on packed operands",
+             (long long)M, (long long)N, (long long)K);
+  Problem pr{};
+  pr.sched = kSchedDense; pr.epi = kEpiStore;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = batch; pr.A = A; pr.B = B;
+  pr.lda = lda; pr.a_bs = stride_a; pr.ldb = ldb; pr.b_bs = stride_b;
+  pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = (int)batch;
+  pr.p.D = D; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
+  return run<kSchedDense, kEpiStore>(pr, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int oasr_b200_group_gemm(void* D, const void* A, const void* B, const int32_t* offsets, int64_t L, int64_t groups,

@@ -42,6 +42,7 @@ class FastConformerLayers:
             raise ValueError("quant must be None, 'fp8' or 'int8'")
         self.qkind = {None: 0, "fp8": 1, "int8": 2}[quant]
         self._q8 = {}
+        self._tables = {}
         self.C, self.H, self.D, self.F, self.L, self.K = hidden, heads, hidden // heads, ffn, layers, kernel
         self.left, self.right, self.eps = sliding_window - 1, lookahead, eps
         self.device, self.dtype = torch.device(device), dtype
@@ -89,44 +90,53 @@ class FastConformerLayers:
 
     # ---- host-side tables (lengths are host values: no device synchronisation) ----
     def _position_table(self, T: int) -> torch.Tensor:
+        """Sinusoid rows for relative positions T-1 .. -(T-1), then zero rows up to a multiple of 8 (the column granule
+        of the GEMM that multiplies them); built once per T and kept on the device."""
+        hit = self._tables.get(T)
+        if hit is not None:
+            return hit
         inv_freq = 1.0 / (10000.0 ** (torch.arange(0, self.C, 2, dtype=torch.float32) / self.C))
         positions = torch.arange(T - 1, -T, -1, dtype=torch.float32)
         freqs = torch.outer(positions, inv_freq)
         table = torch.stack([freqs.sin(), freqs.cos()], dim=-1).reshape(freqs.size(0), self.C)
-        return table.to(self.dtype).to(self.device)            # (2T-1, C)
+        P = table.size(0)
+        table = torch.nn.functional.pad(table, (0, 0, 0, (P + 7) // 8 * 8 - P))
+        out = table.to(self.dtype).to(self.device)             # (roundup8(2T-1), C)
+        if len(self._tables) >= 16:
+            self._tables.clear()
+        self._tables[T] = out
+        return out
 
-    def _masks(self, T: int, lengths: List[int]):
+    def _silent_rows(self, T: int, lengths: List[int]):
+        """``(B, T, 1)`` bool on the device, True where a query sees no key at all, or None when there is no such row.
+        A query in chunk c sees keys [max(0, (c - left_chunks) * chunk), min((c + 1) * chunk, len)): the range is
+        empty exactly when ``len <= max(0, (c - left_chunks) * chunk)`` (encoder.py:124-149, 343-348)."""
         chunk = self.right + 1
         left_chunks = self.left // chunk if self.left >= 0 else T
-        qc = torch.arange(T).div(chunk, rounding_mode="trunc")
-        diff = qc.unsqueeze(1) - qc.unsqueeze(0)
-        window = (diff >= 0) & (diff <= left_chunks)
-        keep = torch.arange(T).unsqueeze(0) < torch.tensor(lengths).unsqueeze(1)
-        attn_mask = window.view(1, 1, T, T) & keep.view(-1, 1, 1, T)     # (B, 1, T, T)
-        silent = attn_mask.logical_not().all(dim=-1).transpose(1, 2)     # (B, T, 1)
-        return attn_mask.to(self.device), (silent.to(self.device) if bool(silent.any()) else None)
+        lo = ((torch.arange(T).div(chunk, rounding_mode="trunc") - left_chunks) * chunk).clamp_(min=0)     # (T,)
+        silent = torch.tensor(lengths).unsqueeze(1) <= lo.unsqueeze(0)                                    # (B, T)
+        return silent.unsqueeze(-1).to(self.device) if bool(silent.any()) else None
 
     # ---- one layer ----
     def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, lens_dev, silent, B: int, T: int) -> torch.Tensor:
         C, H, D = self.C, self.H, self.D
         qkv4 = self._linear(h, *lw["qkv4"]).view(B, T, 4, H, D)
         qu, qv, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(4))          # (B, H, T, D) views
-        rel_k = OF.gemm(rel_table, lw["rel"]).view(-1, H, D)                          # (2T-1, H, D)
-        # (q + v) against the projected table, one batched GEMM over (b, h): (B*H, T, D) x (B*H, 2T-1, D)^T
-        a = qv.reshape(B * H, T, D)
-        b = rel_k.permute(1, 0, 2).unsqueeze(0).expand(B, H, 2 * T - 1, D).reshape(B * H, 2 * T - 1, D)
-        P = 2 * T - 1
-        Pp = (P + 7) // 8 * 8                                                         # GEMM needs N % 8 == 0
-        if Pp != P:
-            b = torch.nn.functional.pad(b, (0, 0, 0, Pp - P))
-        bd = OF.bmm(a.contiguous(), b.contiguous()).view(B, H, T, Pp)
+        # projected positions; the table carries zero rows up to a multiple of 8 (the GEMM's column granule)
+        Pp = rel_table.size(0)
+        rel_k = OF.gemm(rel_table, lw["rel"])                                         # (Pp, H*D)
+        # (q + v) against the projected table, one batched GEMM over heads with every (b, t) as a row; both operands
+        # are read in place: head h of the projection is the column block h*D of its rows
+        a = qkv4[:, :, 1].reshape(B * T, H, D).permute(1, 0, 2)
+        b = rel_k.view(Pp, H, D).permute(1, 0, 2)
+        bd = fused.bmm_strided(a, b).view(H, B, T, Pp).permute(1, 0, 2, 3)            # (B, H, T, Pp) view, head-major storage
         # Transformer-XL shift, scale, chunked-limited window and key padding (finite floor) in one kernel
         chunk = self.right + 1
         bias = fused.relshift_bias(bd, lens_dev, T, D ** -0.5, chunk, self.left // chunk if self.left >= 0 else T, MASK_FLOOR)
-        out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias)     # strided (B, H, T, D) views of the projection
+        out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias, token_major=True)   # strided views in, (B, T, H, D) out
         if silent is not None:
-            out = out.masked_fill(silent.transpose(1, 2).unsqueeze(-1), 0.0)
-        merged = out.permute(0, 2, 1, 3).reshape(B * T, C).contiguous()
+            out = out.masked_fill(silent.unsqueeze(-1), 0.0)
+        merged = out.view(B * T, C)
         return self._linear(merged, *lw["o"])
 
     def _conv(self, lw, h: torch.Tensor, silent, B: int, T: int) -> torch.Tensor:
@@ -146,7 +156,7 @@ class FastConformerLayers:
         B, T, C = hidden.shape
         M = B * T
         lengths = [int(n) for n in lengths]
-        _, silent = self._masks(T, lengths)
+        silent = self._silent_rows(T, lengths)
         lens_dev = torch.tensor(lengths, dtype=torch.int32).to(self.device, non_blocking=True)
         rel_table = self._position_table(T)
         res = hidden.reshape(M, C).to(torch.float32, copy=True).contiguous()   # fp32 residual stream (updated in place: own copy)

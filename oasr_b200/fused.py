@@ -185,6 +185,23 @@ def depthwise_conv2d_k3s2(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
     return out
 
 
+def bmm_strided(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``out[i] = a[i] @ b[i]^T`` for views ``a (batch, M, K)``, ``b (batch, N, K)`` with unit stride along ``K`` and row /
+    batch strides that are multiples of 8 elements: the operands are read in place (``oasr.bmm``,
+    oasr/functionals/gemm.py:262-299, takes packed operands only)."""
+    _need_cuda(a, b)
+    if a.dim() != 3 or b.dim() != 3 or a.size(0) != b.size(0) or a.size(2) != b.size(2) or a.dtype != b.dtype:
+        raise ValueError(f"bmm_strided: need (batch, M, K) and (batch, N, K); got {tuple(a.shape)}, {tuple(b.shape)}")
+    if a.stride(2) != 1 or b.stride(2) != 1:
+        raise ValueError("bmm_strided: unit stride along K required")
+    batch, M, K = a.shape
+    N = b.size(1)
+    out = torch.empty(batch, M, N, device=a.device, dtype=a.dtype)
+    _lib.call("oasr_b200_bmm_strided", _p(out), _p(a), _p(b), batch, M, N, K, a.stride(1), a.stride(0), b.stride(1), b.stride(0),
+              _DTYPE_ID[a.dtype], _stream(a))
+    return out
+
+
 def relshift_bias(bd: torch.Tensor, lengths: torch.Tensor, T: int, scale: float, chunk: int, left_chunks: int,
                   floor_value: float = -1.0e4) -> torch.Tensor:
     """``bd (B, H, T, ld >= 2T-1)`` position scores -> attention bias ``(B, H, T, T)`` (a view whose rows are padded to a multiple of 8 elements): Transformer-XL relative shift,
@@ -192,10 +209,11 @@ def relshift_bias(bd: torch.Tensor, lengths: torch.Tensor, T: int, scale: float,
     (oasr/models/nemotron/encoder.py:82-96, 124-149, 343-348)."""
     _need_cuda(bd, lengths)
     B, H, Tq, ld = bd.shape
-    if Tq != T or not bd.is_contiguous():
-        raise ValueError("bd must be contiguous (B, H, T, ld)")
+    if Tq != T or bd.stride(3) != 1 or bd.stride(2) != ld:
+        raise ValueError("bd must be (B, H, T, ld) with packed rows (batch and head strides are free)")
     ld_out = (T + 7) // 8 * 8          # rows start on 16-byte boundaries so the attention kernel reads them in 16-byte pieces
     out = torch.empty(B, H, T, ld_out, device=bd.device, dtype=bd.dtype)
-    _lib.call("oasr_b200_relshift_bias", _p(out), _p(bd), _p(lengths), B, H, T, ld, ld_out, float(scale), int(chunk), int(left_chunks),
+    _lib.call("oasr_b200_relshift_bias", _p(out), _p(bd), _p(lengths), B, H, T, ld, ld_out, bd.stride(0), bd.stride(1),
+              float(scale), int(chunk), int(left_chunks),
               float(floor_value), _DTYPE_ID[bd.dtype], _stream(bd))
     return out[..., :T]

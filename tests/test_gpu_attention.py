@@ -71,6 +71,27 @@ def test_fmha_strided_views_and_out():
     assert (got.float().cpu() - want).abs().max().item() < TOL
 
 
+def test_fmha_token_major_output_and_aligned_bias():
+    """token_major=True writes (B, T, H, D) with the same bits as the head-major result; the bias rows are padded to a
+    multiple of 8 elements, the form the kernel reads in 16-byte pieces, with ragged lengths and a tail group."""
+    dtype = torch.bfloat16
+    B, T, H, D = 2, 203, 2, 128
+    g = torch.Generator().manual_seed(9)
+    q, k, v = (torch.randn(B, H, T, D, generator=g).to(dtype).cuda() for _ in range(3))
+    ldb = (T + 7) // 8 * 8
+    bias = torch.randn(B, H, T, ldb, generator=g).to(dtype).cuda()[..., :T]
+    lens = torch.tensor([203, 77], dtype=torch.int32).cuda()
+    head_major = ob.fmha(q, k, v, softmax_scale=0.1, attn_bias=bias, cache_seqlens=lens)
+    packed_bias = ob.fmha(q, k, v, softmax_scale=0.1, attn_bias=bias.contiguous(), cache_seqlens=lens)
+    token_major = ob.fmha(q, k, v, softmax_scale=0.1, attn_bias=bias, cache_seqlens=lens, token_major=True)
+    assert ob.device_status() == 0
+    assert token_major.shape == (B, T, H, D)
+    assert torch.equal(token_major.transpose(1, 2), head_major)
+    assert torch.equal(packed_bias, head_major)          # 16-byte and element-wise bias fetches agree bit for bit
+    want = O.fmha(q.cpu(), k.cpu(), v.cpu(), 0.1, bias=bias.cpu(), seqlens=lens.cpu())
+    assert (head_major.float().cpu() - want).abs().max().item() < TOL
+
+
 def test_fmha_stale_keys_are_inert():
     """Finite stale data beyond cache_seqlens must not change the result at all (atol=0)."""
     dtype = torch.bfloat16

@@ -117,3 +117,36 @@ def test_relshift_bias_equals_the_pad_view_identity():
     keep = (torch.arange(T)[None, :] < torch.tensor(lengths)[:, None]).view(B, 1, 1, T)
     want = shifted.masked_fill((window & keep).logical_not(), -1.0e4).bfloat16()
     assert torch.equal(got, want)
+
+
+def test_relshift_bias_reads_head_major_scores():
+    """The same bias from scores stored (H, B, T, ld) and passed as a permuted view: batch / head strides are honoured."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(5)
+    B, H, T, chunk = 2, 3, 19, 3
+    ld = (2 * T - 1 + 7) // 8 * 8
+    bd = torch.randn(B, H, T, ld).bfloat16().cuda()
+    lens = torch.tensor([19, 11], dtype=torch.int32).cuda()
+    want = fused.relshift_bias(bd, lens, T, 0.25, chunk, 2)
+    head_major = bd.permute(1, 0, 2, 3).contiguous().permute(1, 0, 2, 3)
+    assert not head_major.is_contiguous()
+    assert torch.equal(fused.relshift_bias(head_major, lens, T, 0.25, chunk, 2), want)
+
+
+def test_bmm_strided_reads_heads_in_place():
+    """Per-head products straight from a (tokens, heads, head_dim) projection equal bmm on head-major copies, bit for bit."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(6)
+    M, H, D, N = 300, 4, 64, 136
+    proj = torch.randn(M, 3, H, D).bfloat16().cuda()          # a head's rows sit 3*H*D apart
+    table = torch.randn(N, H, D).bfloat16().cuda()
+    a = proj[:, 1].permute(1, 0, 2)                            # (H, M, D) view
+    b = table.permute(1, 0, 2)                                 # (H, N, D) view
+    got = fused.bmm_strided(a, b)
+    want = ob.bmm(a.contiguous(), b.contiguous())
+    assert ob.device_status() == 0
+    assert torch.equal(got, want)
+    ref = torch.einsum("hmd,hnd->hmn", a.float(), b.float())
+    assert (got.float() - ref).abs().max() < 0.08 * ref.abs().max().clamp(min=1.0)
