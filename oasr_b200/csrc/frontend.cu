@@ -179,49 +179,107 @@ struct Dw2dArgs {
   int B, T, F, C, To, Fo, pad_lo;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256) depthwise_conv2d_k3s2_kernel(Dw2dArgs a) {
+// kHoist: 256 % (C/8) == 0, so a thread keeps one channel group for its whole grid-stride walk; the weights sit in
+// shared memory as fp32 and the nine 16-byte input loads of a position are issued together.
+template <typename T, bool kHoist>
+__global__ void __launch_bounds__(256, 2) depthwise_conv2d_k3s2_kernel(Dw2dArgs a) {
   const int groups = a.C / 8;
-  const int64_t total = static_cast<int64_t>(a.B) * a.To * a.Fo * groups;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int cg = static_cast<int>(i % groups);
-    int64_t r = i / groups;
-    const int fo = static_cast<int>(r % a.Fo);
-    r /= a.Fo;
-    const int to = static_cast<int>(r % a.To);
-    const int b = static_cast<int>(r / a.To);
+  const int64_t positions = static_cast<int64_t>(a.B) * a.To * a.Fo;
+  const T* wt = static_cast<const T*>(a.weight);
+  const T* in = static_cast<const T*>(a.in);
+  if constexpr (kHoist) {
+    const int cg = threadIdx.x % groups;
     const int c0 = cg * 8;
-    float acc[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
-    const bool live = !a.out_len || to < a.out_len[b];
-    const int t_end = a.in_len ? min(a.T, a.in_len[b]) : a.T;
-    if (live) {
-      if (a.bias) {
-        const Pack<T> bb = ld128(static_cast<const T*>(a.bias) + c0);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] = Elem<T>::to_f(bb.v[q]);
-      }
+    const int lanes = 256 / groups;                 // positions per block and step
+    // weights as fp32 [tap][channel] (+ the bias row) in shared memory: a thread reads its 8 channels of a tap as two
+    // 16-byte words, consecutive threads consecutive words
+    extern __shared__ float dw2d_smem[];
+    float* sw = dw2d_smem;
+    for (int e = threadIdx.x; e < 10 * a.C; e += 256) {
+      const int k = e / a.C, c = e - k * a.C;
+      sw[e] = k < 9 ? Elem<T>::to_f(wt[c * 9 + k]) : (a.bias ? Elem<T>::to_f(static_cast<const T*>(a.bias)[c]) : 0.f);
+    }
+    __syncthreads();
+    const int64_t pstride = static_cast<int64_t>(gridDim.x) * lanes;
+    for (int64_t pos = static_cast<int64_t>(blockIdx.x) * lanes + threadIdx.x / groups; pos < positions; pos += pstride) {
+      const int fo = static_cast<int>(pos % a.Fo);
+      const int64_t r = pos / a.Fo;
+      const int to = static_cast<int>(r % a.To);
+      const int b = static_cast<int>(r / a.To);
+      const bool live = !a.out_len || to < a.out_len[b];
+      const int t_end = a.in_len ? min(a.T, a.in_len[b]) : a.T;
+      Pack<T> x[9];
+      bool ok[9];
 #pragma unroll
       for (int di = 0; di < 3; ++di) {
         const int t = 2 * to + di - a.pad_lo;
-        if (t < 0 || t >= t_end) continue;
 #pragma unroll
         for (int dj = 0; dj < 3; ++dj) {
           const int f = 2 * fo + dj - a.pad_lo;
-          if (f < 0 || f >= a.F) continue;
-          const Pack<T> x = ld128(static_cast<const T*>(a.in) + ((static_cast<int64_t>(b) * a.T + t) * a.F + f) * a.C + c0);
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            acc[q] = fmaf(Elem<T>::to_f(x.v[q]), Elem<T>::to_f(static_cast<const T*>(a.weight)[(c0 + q) * 9 + di * 3 + dj]), acc[q]);
+          ok[di * 3 + dj] = live && t >= 0 && t < t_end && f >= 0 && f < a.F;
+          if (ok[di * 3 + dj]) x[di * 3 + dj] = ld128(in + ((static_cast<int64_t>(b) * a.T + t) * a.F + f) * a.C + c0);
         }
       }
-    }
-    Pack<T> o;
+      float acc[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) o.v[q] = Elem<T>::from_f(acc[q]);
-    st128(static_cast<T*>(a.out) + ((static_cast<int64_t>(b) * a.To + to) * a.Fo + fo) * a.C + c0, o);
+      for (int q = 0; q < 8; ++q) acc[q] = live ? sw[9 * a.C + c0 + q] : 0.f;
+#pragma unroll
+      for (int k = 0; k < 9; ++k) {
+        if (ok[k]) {
+          const float4 w0 = *reinterpret_cast<const float4*>(sw + k * a.C + c0);
+          const float4 w1 = *reinterpret_cast<const float4*>(sw + k * a.C + c0 + 4);
+          const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] = fmaf(Elem<T>::to_f(x[k].v[q]), w[q], acc[q]);
+        }
+      }
+      Pack<T> o;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) o.v[q] = Elem<T>::from_f(acc[q]);
+      st128(static_cast<T*>(a.out) + pos * a.C + c0, o);
+    }
+  } else {
+    const int64_t total = positions * groups;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int cg = static_cast<int>(i % groups);
+      int64_t r = i / groups;
+      const int fo = static_cast<int>(r % a.Fo);
+      r /= a.Fo;
+      const int to = static_cast<int>(r % a.To);
+      const int b = static_cast<int>(r / a.To);
+      const int c0 = cg * 8;
+      float acc[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+      const bool live = !a.out_len || to < a.out_len[b];
+      const int t_end = a.in_len ? min(a.T, a.in_len[b]) : a.T;
+      if (live) {
+        if (a.bias) {
+          const Pack<T> bb = ld128(static_cast<const T*>(a.bias) + c0);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] = Elem<T>::to_f(bb.v[q]);
+        }
+#pragma unroll
+        for (int di = 0; di < 3; ++di) {
+          const int t = 2 * to + di - a.pad_lo;
+          if (t < 0 || t >= t_end) continue;
+#pragma unroll
+          for (int dj = 0; dj < 3; ++dj) {
+            const int f = 2 * fo + dj - a.pad_lo;
+            if (f < 0 || f >= a.F) continue;
+            const Pack<T> x = ld128(in + ((static_cast<int64_t>(b) * a.T + t) * a.F + f) * a.C + c0);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              acc[q] = fmaf(Elem<T>::to_f(x.v[q]), Elem<T>::to_f(wt[(c0 + q) * 9 + di * 3 + dj]), acc[q]);
+          }
+        }
+      }
+      Pack<T> o;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) o.v[q] = Elem<T>::from_f(acc[q]);
+      st128(static_cast<T*>(a.out) + ((static_cast<int64_t>(b) * a.To + to) * a.Fo + fo) * a.C + c0, o);
+    }
   }
 }
 
@@ -300,13 +358,16 @@ int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weigh
              "depthwise_conv2d_k3s2: channels must be a multiple of 8 and the tensors 16-byte aligned");
   Dw2dArgs a{out, in, weight, bias, out_len, in_len, (int)B, (int)T, (int)F, (int)C,
              (int)((T + pad_lo + pad_hi - 3) / 2 + 1), (int)((F + pad_lo + pad_hi - 3) / 2 + 1), (int)pad_lo};
-  const int64_t total = B * a.To * a.Fo * (C / 8);
+  const int groups = (int)(C / 8);
+  const bool hoist = 256 % groups == 0 && C <= 1024;     // 40 bytes of shared memory per channel
+  const int64_t total = B * a.To * a.Fo * groups;
   int64_t g = (total + 255) / 256;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * (hoist ? 2 : 16);   // hoisted: one resident wave, weights staged once
   if (g > cap) g = cap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
-    depthwise_conv2d_k3s2_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(a);
+    if (hoist) depthwise_conv2d_k3s2_kernel<T_, true><<<static_cast<unsigned>(g), 256, 10 * C * sizeof(float), s>>>(a);
+    else depthwise_conv2d_k3s2_kernel<T_, false><<<static_cast<unsigned>(g), 256, 0, s>>>(a);
     return check_launch("depthwise_conv2d_k3s2 launch");
   });
 }

@@ -107,18 +107,8 @@ class FastConformerLayers:
         self._tables[T] = out
         return out
 
-    def _silent_rows(self, T: int, lengths: List[int]):
-        """``(B, T, 1)`` bool on the device, True where a query sees no key at all, or None when there is no such row.
-        A query in chunk c sees keys [max(0, (c - left_chunks) * chunk), min((c + 1) * chunk, len)): the range is
-        empty exactly when ``len <= max(0, (c - left_chunks) * chunk)`` (encoder.py:124-149, 343-348)."""
-        chunk = self.right + 1
-        left_chunks = self.left // chunk if self.left >= 0 else T
-        lo = ((torch.arange(T).div(chunk, rounding_mode="trunc") - left_chunks) * chunk).clamp_(min=0)     # (T,)
-        silent = torch.tensor(lengths).unsqueeze(1) <= lo.unsqueeze(0)                                    # (B, T)
-        return silent.unsqueeze(-1).to(self.device) if bool(silent.any()) else None
-
     # ---- one layer ----
-    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, lens_dev, silent, B: int, T: int) -> torch.Tensor:
+    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, lens_dev, B: int, T: int) -> torch.Tensor:
         C, H, D = self.C, self.H, self.D
         qkv4 = self._linear(h, *lw["qkv4"]).view(B, T, 4, H, D)
         qu, qv, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(4))          # (B, H, T, D) views
@@ -133,30 +123,30 @@ class FastConformerLayers:
         # Transformer-XL shift, scale, chunked-limited window and key padding (finite floor) in one kernel
         chunk = self.right + 1
         bias = fused.relshift_bias(bd, lens_dev, T, D ** -0.5, chunk, self.left // chunk if self.left >= 0 else T, MASK_FLOOR)
-        out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias, token_major=True)   # strided views in, (B, T, H, D) out
-        if silent is not None:
-            out = out.masked_fill(silent.unsqueeze(-1), 0.0)
+        # strided views in, (B, T, H, D) out.  Keys at or past a stream's length carry the floor in the bias, whose
+        # softmax weight is exactly zero beside any visible key, so bounding the key range by the length only skips work
+        out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias, cache_seqlens=lens_dev, token_major=True)
         merged = out.view(B * T, C)
         return self._linear(merged, *lw["o"])
 
-    def _conv(self, lw, h: torch.Tensor, silent, B: int, T: int) -> torch.Tensor:
+    def _conv(self, lw, h: torch.Tensor, B: int, T: int) -> torch.Tensor:
         x = self._linear(h, *lw["pw1"], glu=True)                                     # pointwise_conv1 + GLU
         x = x.view(B, T, self.C)
-        if silent is not None:
-            x = x.masked_fill(silent, 0.0)
         x = OF.depthwise_conv1d(x.contiguous(), lw["dw"][0], lw["dw"][1], padding=(self.K - 1, 0))   # causal
         x = OF.layer_norm_activation(x.view(B * T, self.C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
         return self._linear(x, *lw["pw2"])
 
     def forward(self, hidden: torch.Tensor, lengths: List[int]) -> torch.Tensor:
         """``hidden (B, T, C)`` post-subsampling states, host ``lengths`` -> ``(B, T, C)`` fp32: the output of the
-        layer stack of NemotronEncoder.forward (encoder.py:542-583)."""
+        layer stack of NemotronEncoder.forward (encoder.py:542-583) on frames ``t < lengths[b]``.  Frames past a stream's
+        length are unspecified: the reference zero-fills attention rows that see no key (encoder.py:343-348), which are
+        always such padding frames (a valid frame sees at least itself), and no valid frame reads a padding frame -
+        attention masks them as keys, the convolution is causal, everything else is per frame."""
         if not hidden.is_cuda:
             raise RuntimeError("hidden must be a CUDA tensor (oasr_b200 has no CPU path)")
         B, T, C = hidden.shape
         M = B * T
         lengths = [int(n) for n in lengths]
-        silent = self._silent_rows(T, lengths)
         lens_dev = torch.tensor(lengths, dtype=torch.int32).to(self.device, non_blocking=True)
         rel_table = self._position_table(T)
         res = hidden.reshape(M, C).to(torch.float32, copy=True).contiguous()   # fp32 residual stream (updated in place: own copy)
@@ -168,9 +158,9 @@ class FastConformerLayers:
             w1, b1, w2, b2 = lw["feed_forward1"]
             y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
             fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_self_att"], eps=self.eps)
-            y = self._attention(lw, h, rel_table, lens_dev, silent, B, T)
+            y = self._attention(lw, h, rel_table, lens_dev, B, T)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_conv"], eps=self.eps)
-            y = self._conv(lw, h, silent, B, T)
+            y = self._conv(lw, h, B, T)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_feed_forward2"], eps=self.eps)
             w1, b1, w2, b2 = lw["feed_forward2"]
             y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
