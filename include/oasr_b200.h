@@ -223,6 +223,13 @@ OASR_API int oasr_b200_depthwise_conv1d_packed(void* out, const void* in, const 
                                                int64_t max_seg_len, int64_t channels,
                                                int64_t kernel_size, int activation, int dtype,
                                                void* stream);
+/* The same over packed segments with all kernel_size-1 zero frames on the LEFT (a causal conv: frame t
+ * of a segment reads frames t-kernel_size+1 .. t of that segment), the packed form of the FastConformer conv module's
+ * depthwise conv (oasr/models/nemotron/encoder.py CausalConv1d, padding (kernel_size-1, 0)). */
+OASR_API int oasr_b200_depthwise_conv1d_packed_causal(void* out, const void* in, const void* weight,
+                                                      const void* bias /*nullable*/, const int32_t* cu_seqlens,
+                                                      int64_t num_segs, int64_t max_seg_len, int64_t channels,
+                                                      int64_t kernel_size, int activation, int dtype, void* stream);
 /* oasr_b200_depthwise_conv1d with a per-channel affine (fp32 post_scale /
  * post_shift, a folded inference BatchNorm) applied after the bias and before
  * the activation: depthwise_conv followed by BatchNormActivation of the conv
@@ -414,6 +421,18 @@ OASR_API int oasr_b200_fmha_bthd(void* out, const void* q, const void* k, const 
                                  int64_t block_size, int64_t num_blocks, int64_t B, int64_t H,
                                  int64_t Hkv, int64_t Tq, int64_t Tk, int64_t D, double scale,
                                  int causal, int dtype, void* stream);
+/* fmha_varlen (next declaration) over strided views: rows of q / k / v are *_row_stride elements apart (0 = packed;
+ * multiples of 8), heads D apart, so the slices of one fused projection are read in place; with bias_rows_padded8 the
+ * rows of bias segment s are roundup8(Tk_s) elements apart and the offsets multiples of 8, which lets the kernel fetch
+ * the bias in 16-byte pieces. */
+OASR_API int oasr_b200_fmha_varlen_strided(void* out, const void* q, const void* k, const void* v,
+                                           int64_t q_row_stride, int64_t k_row_stride, int64_t v_row_stride,
+                                           const void* bias /*nullable*/, const void* bias_offsets /*nullable*/,
+                                           int bias_offsets_is_i64, int bias_rows_padded8,
+                                           const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                           int64_t num_segs, int64_t total_q, int64_t total_k,
+                                           int64_t max_seqlen_q, int64_t H, int64_t Hkv, int64_t D,
+                                           double scale, int dtype, void* stream);
 /* Packed variable-length attention, the reference's fmha_varlen
  * (oasr/functionals/attention.py:592-693): q, out (total_q,H,D); k, v
  * (total_k,Hkv,D); cu_seqlens_* int32[S+1]; bias (nullable) flat, segment s is
@@ -483,6 +502,15 @@ OASR_API int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* l
                                      int64_t T, int64_t ld, int64_t ld_out, int64_t bd_stride_b /*0 = H*T*ld*/,
                                      int64_t bd_stride_h /*0 = T*ld*/, double scale, int64_t chunk,
                                      int64_t left_chunks, double floor_value, int dtype, void* stream);
+
+/* Packed form of the same bias: bd (H, total, ld >= 2T-1) holds the position scores of every packed row (rows
+ * [cu_seqlens[s], cu_seqlens[s+1]) are stream s, at most T frames), and segment s of out is (H, len_s, roundup8(len_s))
+ * at bias_offsets[s] elements: the block-diagonal bias oasr_b200_fmha_varlen_strided reads with bias_rows_padded8 = 1.
+ * Only the chunked-limited window is masked; a segment holds no padding keys. */
+OASR_API int oasr_b200_relshift_bias_packed(void* out, const void* bd, const int32_t* cu_seqlens,
+                                            const int64_t* bias_offsets, int64_t num_segs, int64_t H,
+                                            int64_t total, int64_t T, int64_t ld, double scale, int64_t chunk,
+                                            int64_t left_chunks, double floor_value, int dtype, void* stream);
 
 /* ---- paged KV cache ---------------------------------------------------- */
 /* paged_kv_write with quantisation: 16-bit k_new / v_new (element strides as below, unit stride along

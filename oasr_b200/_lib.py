@@ -71,6 +71,9 @@ _SIGNATURES = {
     "oasr_b200_group_gemm": [P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_gemm_log_softmax": [P, P, P, P, I, I, I, c_int, c_int, P, P],
     "oasr_b200_fmha": [P, P, P, P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_depthwise_conv1d_packed_causal": [P, P, P, P, P, I, I, I, I, c_int, c_int, P],
+    "oasr_b200_relshift_bias_packed": [P, P, P, P, I, I, I, I, I, c_double, I, I, c_double, c_int, P],
+    "oasr_b200_fmha_varlen_strided": [P, P, P, P, I, I, I, P, P, c_int, c_int, P, P, I, I, I, I, I, I, I, c_double, c_int, P],
     "oasr_b200_bmm_strided": [P, P, P, I, I, I, I, I, I, I, I, c_int, P],
     "oasr_b200_fmha_bthd": [P, P, P, P, P, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, c_double, c_int, c_int, P],
     "oasr_b200_fmha_varlen": [P, P, P, P, P, P, c_int, P, P, I, I, I, I, I, I, I, c_double, c_int, P],

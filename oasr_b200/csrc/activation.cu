@@ -112,10 +112,72 @@ __global__ void __launch_bounds__(256) relshift_bias_kernel(T* __restrict__ out,
   }
 }
 
+// Packed form: scores bd (H, total, ld) over packed rows, one block-diagonal bias segment per stream.  Segment s is
+// (H, len_s, roundup8(len_s)) at offsets[s]; a warp finds its row's segment by bisection of cu_seqlens.
+template <typename T>
+__global__ void __launch_bounds__(256) relshift_bias_packed_kernel(T* __restrict__ out, const T* __restrict__ bd,
+                                                                   const int32_t* __restrict__ cu, const int64_t* __restrict__ offsets,
+                                                                   int S, int H, int total, int Tn, int ld, float scale,
+                                                                   int chunk, int left_chunks, float floor_v) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = static_cast<int64_t>(H) * total;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const T floor_t = Elem<T>::from_f(floor_v);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += wstride) {
+    const int h = static_cast<int>(row / total);
+    const int r = static_cast<int>(row - static_cast<int64_t>(h) * total);
+    int lo_s = 0, hi_s = S;                    // largest s with cu[s] <= r
+    while (hi_s - lo_s > 1) {
+      const int mid = (lo_s + hi_s) >> 1;
+      if (cu[mid] <= r) lo_s = mid; else hi_s = mid;
+    }
+    const int s0 = cu[lo_s];
+    const int len = cu[lo_s + 1] - s0;
+    const int i = r - s0;
+    if (i >= len) continue;                    // rows past the last segment
+    const int ld_s = (len + 7) & ~7;
+    const int qc = i / chunk;
+    const int lo = max(0, (qc - left_chunks) * chunk);
+    const int hi = min((qc + 1) * chunk, len);
+    const T* src = bd + row * ld + (Tn - 1 - i);
+    T* dst = out + offsets[lo_s] + (static_cast<int64_t>(h) * len + i) * ld_s;
+#pragma unroll 4
+    for (int j = lane; j < ld_s; j += 32) {
+      T v = floor_t;
+      if (j >= lo && j < hi) v = Elem<T>::from_f(Elem<T>::to_f(src[j]) * scale);
+      dst[j] = v;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace ob
 
 extern "C" {
+
+int oasr_b200_relshift_bias_packed(void* out, const void* bd, const int32_t* cu_seqlens, const int64_t* bias_offsets,
+                                   int64_t num_segs, int64_t H, int64_t total, int64_t T, int64_t ld, double scale,
+                                   int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(num_segs >= 0 && H > 0 && total >= 0 && T > 0 && ld >= 2 * T - 1 && chunk > 0 && left_chunks >= 0 &&
+                 H * total < (int64_t(1) << 40) && total < (int64_t(1) << 31),
+             OASR_ERR_INVALID, "relshift_bias_packed: bad shape");
+  if (num_segs == 0 || total == 0) return OASR_OK;
+  OB_REQUIRE(out && bd && cu_seqlens && bias_offsets, OASR_ERR_INVALID, "relshift_bias_packed: null pointer argument");
+  if (chunk > T) chunk = T;
+  if (left_chunks > T) left_chunks = T;
+  const int64_t rows = H * total;
+  int64_t g = (rows + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (g > cap) g = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
+    relshift_bias_packed_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(
+        static_cast<T_*>(out), static_cast<const T_*>(bd), cu_seqlens, bias_offsets, (int)num_segs, (int)H, (int)total, (int)T,
+        (int)ld, (float)scale, (int)chunk, (int)left_chunks, (float)floor_value);
+    return check_launch("relshift_bias_packed launch");
+  });
+}
 
 int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* lengths, int64_t B, int64_t H, int64_t T, int64_t ld,
                             int64_t ld_out, int64_t bd_stride_b, int64_t bd_stride_h, double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype, void* stream) {

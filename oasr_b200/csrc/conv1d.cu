@@ -715,6 +715,26 @@ int oasr_b200_depthwise_conv1d_packed(void* out, const void* in, const void* wei
   return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, (int)max_seg_len, s); });
 }
 
+int oasr_b200_depthwise_conv1d_packed_causal(void* out, const void* in, const void* weight, const void* bias,
+                                             const int32_t* cu_seqlens, int64_t num_segs, int64_t max_seg_len,
+                                             int64_t channels, int64_t kernel_size, int activation, int dtype,
+                                             void* stream) {
+  using namespace ob;
+  OB_REQUIRE(num_segs >= 0 && max_seg_len >= 0 && channels > 0 && kernel_size > 0, OASR_ERR_INVALID,
+             "depthwise_conv1d_packed_causal: bad shape");
+  if (num_segs == 0 || max_seg_len == 0) return OASR_OK;
+  OB_REQUIRE(out && in && weight && cu_seqlens, OASR_ERR_INVALID,
+             "depthwise_conv1d_packed_causal: null pointer argument");
+  OB_REQUIRE(act_is_known(activation), OASR_ERR_INVALID, "depthwise_conv1d_packed_causal: unknown activation id %d",
+             activation);
+  DwArgs a{};
+  a.out = out; a.in = in; a.weight = weight; a.bias = bias; a.cu_seqlens = cu_seqlens;
+  a.batch = num_segs; a.channels = (int)channels;
+  a.kernel_size = (int)kernel_size; a.pad_left = (int)kernel_size - 1; a.act = activation;   // all padding on the left
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_FLOAT(dtype, T, [&]() -> int { return launch_dw<T>(a, (int)max_seg_len, s); });
+}
+
 int oasr_b200_depthwise_conv1d(void* out, const void* in, const void* weight, const void* bias,
                                int64_t batch, int64_t seq_len, int64_t channels, int64_t kernel_size,
                                int64_t pad_left, int64_t pad_right, const void* mask, int mask_is_bool,

@@ -65,6 +65,7 @@ struct Params {
   int64_t bias_sb, bias_sh, bias_sq;  // dense / paged bias strides (elements)
   const void* bias_offsets;           // varlen: per-segment start (elements)
   int bias_off_i64;
+  int bias_ld8;                       // varlen: bias rows of a segment are roundup8(Tk_s) elements apart (16-byte aligned rows)
   const int32_t* pos_start;           // relpos + paged: first position row of each stream's key 0
   int out_token_major;                // dense/paged: out is (B*Tq, H*D) rows instead of (B,H,Tq,D)
   void* out;
@@ -354,13 +355,15 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
       if (p.mode == kVarlen) {
         const int64_t off = p.bias_off_i64 ? static_cast<const int64_t*>(p.bias_offsets)[bz]
                                            : static_cast<int64_t>(static_cast<const int32_t*>(p.bias_offsets)[bz]);
-        bias_row = bias + off + (static_cast<int64_t>(h) * tq_seg + row_in_seq) * kv_len;
+        bias_row = bias + off + (static_cast<int64_t>(h) * tq_seg + row_in_seq) * (p.bias_ld8 ? ((kv_len + 7) & ~7) : kv_len);
       } else {
         bias_row = bias + bz * p.bias_sb + h * p.bias_sh + static_cast<int64_t>(row_in_seq) * p.bias_sq;
       }
     }
     const bool row_ok = r < rows_valid;
-    const bool bias_vec = bias_row && p.mode == kDense && (reinterpret_cast<uintptr_t>(bias_row) & 15u) == 0;
+    const bool bias_vec = bias_row && (p.mode == kDense || (p.mode == kVarlen && p.bias_ld8)) &&
+                          (reinterpret_cast<uintptr_t>(bias_row) & 15u) == 0;
+    const int bias_cols = p.mode == kDense ? p.Tk : ((kv_len + 7) & ~7);   // columns of a bias row that exist in memory
     float m_run = kNegInf, l_run = 0.f, alpha_prev = 1.f;
     float o[D];
 #pragma unroll
@@ -476,7 +479,7 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               const int kg = key0 + c0 + g * 8;
-              if (bias_vec && kg + 8 <= p.Tk) {
+              if (bias_vec && kg + 8 <= bias_cols) {
                 const uint4 w = __ldg(reinterpret_cast<const uint4*>(bp + g * 8));
                 bw[g * 4] = w.x; bw[g * 4 + 1] = w.y; bw[g * 4 + 2] = w.z; bw[g * 4 + 3] = w.w;
               } else {
@@ -832,8 +835,9 @@ int oasr_b200_fmha_bthd(void* out, const void* q, const void* k, const void* v, 
                              Hkv, Tq, Tk, D, scale, causal, dtype, stream, 1);
 }
 
-int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, const void* v, const void* bias,
-                          const void* bias_offsets, int bias_offsets_is_i64, const int32_t* cu_seqlens_q,
+static int fmha_varlen_impl(void* out, const void* q, const void* k, const void* v, int64_t q_ld, int64_t k_ld,
+                           int64_t v_ld, const void* bias, const void* bias_offsets, int bias_offsets_is_i64,
+                           int bias_rows_padded8, const int32_t* cu_seqlens_q,
                           const int32_t* cu_seqlens_k, int64_t num_segs, int64_t total_q, int64_t total_k,
                           int64_t max_seqlen_q, int64_t H, int64_t Hkv, int64_t D, double scale, int dtype,
                           void* stream) {
@@ -852,11 +856,16 @@ int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, const void* v
   OB_REQUIRE(D == 64 || D == 128, OASR_ERR_UNSUPPORTED,
              "fmha_varlen: head_dim %lld is not supported (64 and 128 are)", (long long)D);
   OB_REQUIRE(num_segs <= 65535 && H <= 65535, OASR_ERR_INVALID, "fmha_varlen: segment / head count too large");
+  if (q_ld == 0) q_ld = H * D;
+  if (k_ld == 0) k_ld = Hkv * D;
+  if (v_ld == 0) v_ld = Hkv * D;
+  OB_REQUIRE(q_ld >= H * D && k_ld >= Hkv * D && v_ld >= Hkv * D && stride_ok(q_ld) && stride_ok(k_ld) && stride_ok(v_ld),
+             OASR_ERR_ALIGN, "fmha_varlen: row strides must cover a row and be multiples of 8 elements");
   Maps maps;
-  if (int rc = make_map(&maps.q, dtype, q, (int)D, total_q, H, 1, H * D, D, H * D * total_q, BQ)) return rc;
+  if (int rc = make_map(&maps.q, dtype, q, (int)D, total_q, H, 1, q_ld, D, q_ld * total_q, BQ)) return rc;
   const int64_t tk = total_k > 0 ? total_k : 1;
-  if (int rc = make_map(&maps.k, dtype, k, (int)D, tk, Hkv, 1, Hkv * D, D, Hkv * D * tk, BKV)) return rc;
-  if (int rc = make_map(&maps.v, dtype, v, (int)D, tk, Hkv, 1, Hkv * D, D, Hkv * D * tk, BKV)) return rc;
+  if (int rc = make_map(&maps.k, dtype, k, (int)D, tk, Hkv, 1, k_ld, D, k_ld * tk, BKV)) return rc;
+  if (int rc = make_map(&maps.v, dtype, v, (int)D, tk, Hkv, 1, v_ld, D, v_ld * tk, BKV)) return rc;
   maps.q2 = maps.q;
   maps.k2 = maps.k;
   Params p{};
@@ -864,9 +873,30 @@ int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, const void* v
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.cu_q = cu_seqlens_q; p.cu_k = cu_seqlens_k;
   p.bias = bias; p.bias_offsets = bias_offsets; p.bias_off_i64 = bias_offsets_is_i64;
+  p.bias_ld8 = bias_rows_padded8;
   p.out = out; p.status = device_status_ptr();
   dim3 grid((unsigned)((max_seqlen_q + BQ - 1) / BQ), (unsigned)H, (unsigned)num_segs);
   return dispatch(maps, p, (int)D, dtype, grid, static_cast<cudaStream_t>(stream));
+}
+
+int oasr_b200_fmha_varlen(void* out, const void* q, const void* k, const void* v, const void* bias,
+                          const void* bias_offsets, int bias_offsets_is_i64, const int32_t* cu_seqlens_q,
+                          const int32_t* cu_seqlens_k, int64_t num_segs, int64_t total_q, int64_t total_k,
+                          int64_t max_seqlen_q, int64_t H, int64_t Hkv, int64_t D, double scale, int dtype,
+                          void* stream) {
+  return fmha_varlen_impl(out, q, k, v, 0, 0, 0, bias, bias_offsets, bias_offsets_is_i64, 0, cu_seqlens_q, cu_seqlens_k,
+                          num_segs, total_q, total_k, max_seqlen_q, H, Hkv, D, scale, dtype, stream);
+}
+
+int oasr_b200_fmha_varlen_strided(void* out, const void* q, const void* k, const void* v, int64_t q_row_stride,
+                                  int64_t k_row_stride, int64_t v_row_stride, const void* bias,
+                                  const void* bias_offsets, int bias_offsets_is_i64, int bias_rows_padded8,
+                                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int64_t num_segs,
+                                  int64_t total_q, int64_t total_k, int64_t max_seqlen_q, int64_t H, int64_t Hkv,
+                                  int64_t D, double scale, int dtype, void* stream) {
+  return fmha_varlen_impl(out, q, k, v, q_row_stride, k_row_stride, v_row_stride, bias, bias_offsets,
+                          bias_offsets_is_i64, bias_rows_padded8, cu_seqlens_q, cu_seqlens_k, num_segs, total_q, total_k,
+                          max_seqlen_q, H, Hkv, D, scale, dtype, stream);
 }
 
 }  // extern "C"

@@ -20,6 +20,7 @@ from __future__ import annotations
 import math
 from typing import Dict, List
 
+import numpy as np
 import torch
 
 from . import functional as OF
@@ -107,50 +108,49 @@ class FastConformerLayers:
         self._tables[T] = out
         return out
 
-    # ---- one layer ----
-    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, lens_dev, B: int, T: int) -> torch.Tensor:
+    # ---- one layer; ``g`` is the geometry of the rows: padded (B, T, lens) or packed (cu, offsets) ----
+    def _attention(self, lw, h: torch.Tensor, rel_table: torch.Tensor, g) -> torch.Tensor:
         C, H, D = self.C, self.H, self.D
-        qkv4 = self._linear(h, *lw["qkv4"]).view(B, T, 4, H, D)
-        qu, qv, k, v = (qkv4[:, :, i].permute(0, 2, 1, 3) for i in range(4))          # (B, H, T, D) views
+        M = h.size(0)
+        qkv4 = self._linear(h, *lw["qkv4"]).view(M, 4, H, D)                          # q+u | q+v | k | v of every row
         # projected positions; the table carries zero rows up to a multiple of 8 (the GEMM's column granule)
         Pp = rel_table.size(0)
         rel_k = OF.gemm(rel_table, lw["rel"])                                         # (Pp, H*D)
-        # (q + v) against the projected table, one batched GEMM over heads with every (b, t) as a row; both operands
-        # are read in place: head h of the projection is the column block h*D of its rows
-        a = qkv4[:, :, 1].reshape(B * T, H, D).permute(1, 0, 2)
-        b = rel_k.view(Pp, H, D).permute(1, 0, 2)
-        bd = fused.bmm_strided(a, b).view(H, B, T, Pp).permute(1, 0, 2, 3)            # (B, H, T, Pp) view, head-major storage
-        # Transformer-XL shift, scale, chunked-limited window and key padding (finite floor) in one kernel
+        # (q + v) against the projected table, one batched GEMM over heads with every row of the batch as a row; both
+        # operands are read in place: head h of the projection is the column block h*D of its rows
+        bd = fused.bmm_strided(qkv4[:, 1].permute(1, 0, 2), rel_k.view(Pp, H, D).permute(1, 0, 2))      # (H, M, Pp)
         chunk = self.right + 1
-        bias = fused.relshift_bias(bd, lens_dev, T, D ** -0.5, chunk, self.left // chunk if self.left >= 0 else T, MASK_FLOOR)
-        # strided views in, (B, T, H, D) out.  Keys at or past a stream's length carry the floor in the bias, whose
-        # softmax weight is exactly zero beside any visible key, so bounding the key range by the length only skips work
-        out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias, cache_seqlens=lens_dev, token_major=True)
-        merged = out.view(B * T, C)
-        return self._linear(merged, *lw["o"])
+        left_chunks = self.left // chunk if self.left >= 0 else g["T"]
+        # Transformer-XL shift, scale, chunked-limited window (and key padding) with a finite floor in one kernel
+        if g["packed"]:
+            bias = fused.relshift_bias_packed(bd, g["cu"], g["offsets"], g["bias_numel"], g["T"], D ** -0.5, chunk, left_chunks,
+                                              MASK_FLOOR)
+            out = fused.fmha_varlen_strided(qkv4[:, 0], qkv4[:, 2], qkv4[:, 3], g["cu"], g["T"], D ** -0.5, bias, g["offsets"])
+        else:
+            B, T = g["B"], g["T"]
+            bias = fused.relshift_bias(bd.view(H, B, T, Pp).permute(1, 0, 2, 3), g["lens"], T, D ** -0.5, chunk, left_chunks,
+                                       MASK_FLOOR)
+            q5 = qkv4.view(B, T, 4, H, D)
+            qu, k, v = (q5[:, :, i].permute(0, 2, 1, 3) for i in (0, 2, 3))           # (B, H, T, D) views
+            # Keys at or past a stream's length carry the floor in the bias, whose softmax weight is exactly zero beside
+            # any visible key, so bounding the key range by the length only skips work
+            out = fmha(qu, k, v, softmax_scale=D ** -0.5, attn_bias=bias, cache_seqlens=g["lens"], token_major=True)
+        return self._linear(out.view(M, C), *lw["o"])
 
-    def _conv(self, lw, h: torch.Tensor, B: int, T: int) -> torch.Tensor:
+    def _conv(self, lw, h: torch.Tensor, g) -> torch.Tensor:
         x = self._linear(h, *lw["pw1"], glu=True)                                     # pointwise_conv1 + GLU
-        x = x.view(B, T, self.C)
-        x = OF.depthwise_conv1d(x.contiguous(), lw["dw"][0], lw["dw"][1], padding=(self.K - 1, 0))   # causal
-        x = OF.layer_norm_activation(x.view(B * T, self.C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
+        if g["packed"]:
+            x = fused.depthwise_conv1d_packed_causal(x, lw["dw"][0], lw["dw"][1], g["cu"], g["T"])
+        else:
+            x = OF.depthwise_conv1d(x.view(g["B"], g["T"], self.C), lw["dw"][0], lw["dw"][1], padding=(self.K - 1, 0))
+        x = OF.layer_norm_activation(x.view(-1, self.C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
         return self._linear(x, *lw["pw2"])
 
-    def forward(self, hidden: torch.Tensor, lengths: List[int]) -> torch.Tensor:
-        """``hidden (B, T, C)`` post-subsampling states, host ``lengths`` -> ``(B, T, C)`` fp32: the output of the
-        layer stack of NemotronEncoder.forward (encoder.py:542-583) on frames ``t < lengths[b]``.  Frames past a stream's
-        length are unspecified: the reference zero-fills attention rows that see no key (encoder.py:343-348), which are
-        always such padding frames (a valid frame sees at least itself), and no valid frame reads a padding frame -
-        attention masks them as keys, the convolution is causal, everything else is per frame."""
-        if not hidden.is_cuda:
-            raise RuntimeError("hidden must be a CUDA tensor (oasr_b200 has no CPU path)")
-        B, T, C = hidden.shape
-        M = B * T
-        lengths = [int(n) for n in lengths]
-        lens_dev = torch.tensor(lengths, dtype=torch.int32).to(self.device, non_blocking=True)
-        rel_table = self._position_table(T)
-        res = hidden.reshape(M, C).to(torch.float32, copy=True).contiguous()   # fp32 residual stream (updated in place: own copy)
-        h = torch.empty(M, C, device=hidden.device, dtype=self.dtype)
+    def _layers(self, res: torch.Tensor, g) -> torch.Tensor:
+        """``res (M, C)`` fp32 rows (overwritten: the residual stream) -> ``(M, C)`` fp32 output of the stack."""
+        M, C = res.shape
+        rel_table = self._position_table(g["T"])
+        h = torch.empty(M, C, device=res.device, dtype=self.dtype)
         first = self.layers[0]["norm_feed_forward1"]
         fused.add_norm_f32(h, None, res, None, 0.0, fused.ADD_NORM_LN, *first, eps=self.eps)          # LN(x)
         out = None
@@ -158,9 +158,9 @@ class FastConformerLayers:
             w1, b1, w2, b2 = lw["feed_forward1"]
             y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
             fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_self_att"], eps=self.eps)
-            y = self._attention(lw, h, rel_table, lens_dev, B, T)
+            y = self._attention(lw, h, rel_table, g)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_conv"], eps=self.eps)
-            y = self._conv(lw, h, B, T)
+            y = self._conv(lw, h, g)
             fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_feed_forward2"], eps=self.eps)
             w1, b1, w2, b2 = lw["feed_forward2"]
             y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
@@ -169,8 +169,50 @@ class FastConformerLayers:
                 nxt = self.layers[i + 1]["norm_feed_forward1"]
                 fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *nxt, eps=self.eps)
             else:
-                out = torch.empty(M, C, device=hidden.device, dtype=torch.float32)
+                out = torch.empty(M, C, device=res.device, dtype=torch.float32)
                 fused.add_norm_f32(h, out, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *lw["norm_out"], eps=self.eps)
+        return out
+
+    def forward(self, hidden: torch.Tensor, lengths: List[int], packed: bool = True) -> torch.Tensor:
+        """``hidden (B, T, C)`` post-subsampling states, host ``lengths`` -> ``(B, T, C)`` fp32: the output of the
+        layer stack of NemotronEncoder.forward (encoder.py:542-583) on frames ``t < lengths[b]``.
+
+        ``packed`` (default) runs the stack on the valid frames only - the rows of all streams back to back, attention
+        and the causal conv per segment - and returns zeros in the padding frames; ``packed=False`` runs the padded
+        batch as the reference does.  Either way frames past a stream's length are unspecified relative to the
+        reference: it zero-fills attention rows that see no key (encoder.py:343-348), which are always padding frames (a
+        valid frame sees at least itself), and no valid frame reads a padding frame - attention masks them as keys,
+        the convolution is causal, everything else is per frame."""
+        if not hidden.is_cuda:
+            raise RuntimeError("hidden must be a CUDA tensor (oasr_b200 has no CPU path)")
+        B, T, C = hidden.shape
+        lengths = [min(max(int(n), 0), T) for n in lengths]
+        if len(lengths) != B:
+            raise ValueError("one length per stream")
+        dev = hidden.device
+        if not packed:
+            g = {"packed": False, "B": B, "T": T,
+                 "lens": torch.tensor(lengths, dtype=torch.int32).to(dev, non_blocking=True)}
+            res = hidden.reshape(B * T, C).to(torch.float32, copy=True).contiguous()   # own copy: updated in place
+            return self._layers(res, g).view(B, T, C)
+        total = sum(lengths)
+        out = torch.zeros(B * T, C, device=dev, dtype=torch.float32)
+        if total == 0:
+            return out.view(B, T, C)
+        lens = np.asarray(lengths, dtype=np.int64)
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(lens, out=cu[1:])
+        # packed row r of stream b sits at padded row b*T + (r - cu[b])
+        rows = np.arange(total, dtype=np.int64) + np.repeat(np.arange(B, dtype=np.int64) * T - cu[:-1], lens)
+        # bias segment b: (H, len, roundup8(len)) elements, back to back
+        offsets = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(self.H * lens * ((lens + 7) // 8 * 8), out=offsets[1:])
+        g = {"packed": True, "T": int(lens.max()), "bias_numel": int(offsets[-1]),
+             "cu": torch.from_numpy(cu.astype(np.int32)).to(dev, non_blocking=True),
+             "offsets": torch.from_numpy(offsets).to(dev, non_blocking=True)}
+        rows_dev = torch.from_numpy(rows).to(dev, non_blocking=True)
+        res = hidden.reshape(B * T, C).index_select(0, rows_dev).float()               # (total, C) fp32, own storage
+        out.index_copy_(0, rows_dev, self._layers(res, g))
         return out.view(B, T, C)
 
 
@@ -214,8 +256,8 @@ class FastConformerEncoder:
         B, T, Fd, C = x.shape
         return OF.gemm(x.reshape(B * T, Fd * C), *self.proj).view(B, T, -1), lengths
 
-    def forward(self, feats: torch.Tensor, lengths: List[int]):
+    def forward(self, feats: torch.Tensor, lengths: List[int], packed: bool = True):
         if not feats.is_cuda:
             raise RuntimeError("feats must be a CUDA tensor (oasr_b200 has no CPU path)")
         hidden, out_len = self.subsample(feats, [int(n) for n in lengths])
-        return self.stack.forward(hidden, out_len), out_len
+        return self.stack.forward(hidden, out_len, packed=packed), out_len

@@ -46,6 +46,18 @@ def depthwise_conv1d_packed(x: torch.Tensor, weight: torch.Tensor, bias: Optiona
     return out
 
 
+def depthwise_conv1d_packed_causal(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                                   cu_seqlens: torch.Tensor, max_seg_len: int, activation: int = -1) -> torch.Tensor:
+    """Causal depthwise conv over packed ``(total, C)`` rows, ``weight (K, C)``: frame t of a segment reads frames
+    ``t-K+1 .. t`` of the same segment (zeros before its start)."""
+    _need_cuda(x, weight, bias, cu_seqlens)
+    out = torch.empty_like(x)
+    _lib.call("oasr_b200_depthwise_conv1d_packed_causal", _p(out), _p(x), _p(weight), _p(bias), _p(cu_seqlens),
+              cu_seqlens.numel() - 1, int(max_seg_len), x.size(-1), weight.size(0), int(activation), _DTYPE_ID[x.dtype],
+              _stream(x))
+    return out
+
+
 def fmha_varlen_relpos(qkv4: torch.Tensor, pos: torch.Tensor, cu_seqlens: torch.Tensor, max_seg_len: int,
                        heads: int, scale: float, out=None) -> torch.Tensor:
     """Conformer relative-position attention over packed rows
@@ -182,6 +194,38 @@ def depthwise_conv2d_k3s2(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
     out = torch.empty(B, To, Fo, C, device=x.device, dtype=x.dtype)
     _lib.call("oasr_b200_depthwise_conv2d_k3s2", _p(out), _p(x), _p(weight.contiguous()), _p(bias), _p(out_len), _p(in_len), B, T, Fd,
               C, int(pad_lo), int(pad_hi), _DTYPE_ID[x.dtype], _stream(x))
+    return out
+
+
+def relshift_bias_packed(bd: torch.Tensor, cu_seqlens: torch.Tensor, bias_offsets: torch.Tensor, bias_numel: int, T: int,
+                         scale: float, chunk: int, left_chunks: int, floor_value: float = -1.0e4) -> torch.Tensor:
+    """Packed ``relshift_bias``: ``bd (H, total, ld >= 2T-1)`` scores of packed rows -> flat block-diagonal bias, segment
+    ``s`` = ``(H, len_s, roundup8(len_s))`` at ``bias_offsets[s]`` (int64, multiples of 8), ``bias_numel`` elements in all."""
+    _need_cuda(bd, cu_seqlens, bias_offsets)
+    H, total, ld = bd.shape
+    if not bd.is_contiguous() or bias_offsets.dtype != torch.int64 or cu_seqlens.dtype != torch.int32:
+        raise ValueError("bd must be contiguous (H, total, ld); cu_seqlens int32, bias_offsets int64")
+    out = torch.empty(int(bias_numel), device=bd.device, dtype=bd.dtype)
+    _lib.call("oasr_b200_relshift_bias_packed", _p(out), _p(bd), _p(cu_seqlens), _p(bias_offsets), cu_seqlens.numel() - 1, H,
+              total, T, ld, float(scale), int(chunk), int(left_chunks), float(floor_value), _DTYPE_ID[bd.dtype], _stream(bd))
+    return out
+
+
+def fmha_varlen_strided(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seg_len: int,
+                        softmax_scale: float, bias: Optional[torch.Tensor] = None,
+                        bias_offsets: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Self-attention over packed segments with ``q/k/v (total, H, D)`` views whose rows may be strided (slices of one
+    fused projection) and an optional block-diagonal bias whose segment rows are ``roundup8(len_s)`` apart.  Returns
+    ``(total, H, D)`` contiguous."""
+    _need_cuda(q, k, v, cu_seqlens, bias, bias_offsets)
+    total, H, D = q.shape
+    for t in (q, k, v):
+        if t.shape != q.shape or t.stride(2) != 1 or t.stride(1) != D:
+            raise ValueError("q/k/v must be (total, H, D) views with unit stride along D and heads D apart")
+    out = torch.empty(total, H, D, device=q.device, dtype=q.dtype)
+    _lib.call("oasr_b200_fmha_varlen_strided", _p(out), _p(q), _p(k), _p(v), q.stride(0), k.stride(0), v.stride(0), _p(bias),
+              _p(bias_offsets), 1, 1, _p(cu_seqlens), _p(cu_seqlens), cu_seqlens.numel() - 1, total, total, int(max_seg_len),
+              H, H, D, float(softmax_scale), _DTYPE_ID[q.dtype], _stream(q))
     return out
 
 

@@ -15,12 +15,13 @@ pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 
 
-def test_layer_stack_matches_oracle_and_reference_fixture():
+@pytest.mark.parametrize("packed", [True, False])
+def test_layer_stack_matches_oracle_and_reference_fixture(packed):
     cfg, case = OFC.TINY, cases.FASTCONFORMER_CASE
     P = OFC.init_params(cfg, case["weight_seed"])
     hidden = cases.make_fastconformer_hidden(case, cfg)
     model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
-    got = model.forward(hidden.cuda(), case["lengths"]).cpu()
+    got = model.forward(hidden.cuda(), case["lengths"], packed=packed).cpu()
     assert ob.device_status() == 0
     want = OFC.layers_forward(P, cfg, hidden, case["lengths"])
     gold = torch.from_numpy(np.load(GOLD / "fastconformer_tiny.npz")["hidden_out"])
@@ -34,7 +35,8 @@ def test_layer_stack_matches_oracle_and_reference_fixture():
     assert cos > 0.9995
 
 
-def test_config4_sized_layer_runs_and_is_isolated_per_utterance():
+@pytest.mark.parametrize("packed", [True, False])
+def test_config4_sized_layer_runs_and_is_isolated_per_utterance(packed):
     """One layer at the FastConformer width (hidden 1024, 8 heads of 128, FFN 4096, kernel 9): an utterance inside a
     padded batch equals the same utterance alone on its valid frames (key padding and silent rows do their job)."""
     torch.manual_seed(3)
@@ -44,12 +46,32 @@ def test_config4_sized_layer_runs_and_is_isolated_per_utterance():
     hidden = torch.randn(2, 96, 1024)
     model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
     hidden_dev = hidden.cuda()
-    both = model.forward(hidden_dev, lengths)
+    both = model.forward(hidden_dev, lengths, packed=packed)
     assert torch.equal(hidden_dev.cpu(), hidden)                       # the fp32 input is not the residual buffer
-    alone = model.forward(hidden[1:2, :41].contiguous().cuda(), [41])
+    alone = model.forward(hidden[1:2, :41].contiguous().cuda(), [41], packed=packed)
     assert ob.device_status() == 0
     assert torch.isfinite(both).all()
     assert (both[1, :41] - alone[0]).abs().max().item() < 2e-2
+
+
+def test_packed_and_padded_execution_agree_on_ragged_batch():
+    """Valid frames only (packed rows, per-segment attention and causal conv) against the padded batch: same frames out,
+    zeros in the padding, with an empty stream and lengths that are not multiples of 8 in the batch."""
+    torch.manual_seed(8)
+    cfg = OFC.FastConformerConfig(hidden=256, heads=2, ffn=512, layers=2, kernel=9, sliding_window=25, lookahead=2, bias=True)
+    P = OFC.init_params(cfg, 5)
+    lengths = [150, 0, 67, 133, 1]
+    hidden = torch.randn(5, 150, 256).cuda()
+    model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    padded = model.forward(hidden, lengths, packed=False)
+    packed = model.forward(hidden, lengths, packed=True)
+    assert ob.device_status() == 0
+    valid = (torch.arange(150)[None, :] < torch.tensor(lengths)[:, None]).cuda()
+    assert (packed[valid] - padded[valid]).abs().max().item() < 2e-2
+    assert torch.count_nonzero(packed[~valid]) == 0
+    want = OFC.layers_forward(P, cfg, hidden.cpu(), lengths)
+    d = (packed.cpu() - want).abs()[valid.cpu()]
+    assert d.max().item() < 6e-2 and d.mean().item() < 6e-3, (d.max().item(), d.mean().item())
 
 
 def test_whole_encoder_matches_oracle_and_reference_fixture():
@@ -150,3 +172,28 @@ def test_bmm_strided_reads_heads_in_place():
     assert torch.equal(got, want)
     ref = torch.einsum("hmd,hnd->hmn", a.float(), b.float())
     assert (got.float() - ref).abs().max() < 0.08 * ref.abs().max().clamp(min=1.0)
+
+
+def test_relshift_bias_packed_equals_padded_per_segment():
+    """Block-diagonal bias of packed rows against the padded kernel, stream by stream, bit for bit; rows of a segment are
+    roundup8(len) apart and the padding columns carry the floor."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(12)
+    H, T, chunk, left_chunks = 3, 29, 3, 4
+    lens = [29, 5, 0, 18]
+    ld = (2 * T - 1 + 7) // 8 * 8
+    bd_pad = torch.randn(len(lens), H, T, ld).bfloat16().cuda()
+    padded = fused.relshift_bias(bd_pad, torch.tensor(lens, dtype=torch.int32).cuda(), T, 0.3, chunk, left_chunks)
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    total = int(cu[-1])
+    bd = torch.cat([bd_pad[b, :, :n] for b, n in enumerate(lens)], dim=1).contiguous()          # (H, total, ld)
+    ld8 = [(n + 7) // 8 * 8 for n in lens]
+    offs = np.concatenate([[0], np.cumsum([H * n * l for n, l in zip(lens, ld8)])]).astype(np.int64)
+    flat = fused.relshift_bias_packed(bd, torch.from_numpy(cu.astype(np.int32)).cuda(), torch.from_numpy(offs).cuda(),
+                                      int(offs[-1]), T, 0.3, chunk, left_chunks)
+    assert bd.size(1) == total
+    for b, n in enumerate(lens):
+        seg = flat[offs[b]:offs[b + 1]].view(H, n, ld8[b])
+        assert torch.equal(seg[..., :n], padded[b, :, :n, :n])
+        assert (seg[..., n:] == -1.0e4).all()
