@@ -385,7 +385,7 @@ def run_sweep(args):
 def run_fastconformer(args):
     """Config-4 style measurement (``--workload fastconformer``): FastConformer encoder (8x subsampling, 24 layers,
     hidden 1024, 8 heads of 128, FFN 4096, kernel 9, 128 mel bins), random-init weights, one step = one padded batch
-    of 128 utterances with lengths uniform in 500..3000 frames.  ``--quant fp8|int8`` runs the layers' Linear GEMMs on
+    of 128 utterances with lengths uniform in 500..3000 frames (the layer stack runs on the valid frames, packed).  ``--quant fp8|int8`` runs the layers' Linear GEMMs on
     8-bit operands.  The encoder is a Python composition of this package's operators (not a one-call executor)."""
     import oasr_b200
     from oasr_b200 import _lib
@@ -434,7 +434,7 @@ def run_fastconformer(args):
         "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
         "data": "synthetic",
-        "config": {"workload": f"fastconformer{layers}_d1024_h8_ffn4096_k9_mel128_sub8x_b{batch}_len500-3000_padded",
+        "config": {"workload": f"fastconformer{layers}_d1024_h8_ffn4096_k9_mel128_sub8x_b{batch}_len500-3000_padded_in_packed_layers",
                    "audio_seconds_per_step": audio / steps, "l2": "256 MiB flush write between steps"},
         "gpu_launches": int(_lib.launch_count() - launches0), "clocks": clocks}), flush=True)
     return 0
