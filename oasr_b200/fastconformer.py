@@ -246,8 +246,10 @@ class FastConformerEncoder:
         nxt = lambda ls: [(n + 2 + 1 - 3) // 2 + 1 for n in ls]
         dev_i32 = lambda ls: torch.tensor(ls, dtype=torch.int32).to(self.device, non_blocking=True)
         # stem: one input channel, pad (2, 1) on time and frequency, 3x3 / stride 2, + bias + ReLU (fp32 in, 16-bit NHWC out)
-        x = fused.subsample_conv1(torch.nn.functional.pad(feats.float(), (2, 1, 2, 1)), *self.conv_in, self.dtype)
+        # (frames past a stream's length are not computed: the next stage reads them as zeros through its ``in_len``)
         lengths = nxt(lengths)
+        x = fused.subsample_conv1(torch.nn.functional.pad(feats.float(), (2, 1, 2, 1)), *self.conv_in, self.dtype,
+                                  t1_limit=dev_i32(lengths))
         for dw_w, dw_b, pw_w, pw_b in self.sub_stages:
             in_len, lengths = lengths, nxt(lengths)
             x = fused.depthwise_conv2d_k3s2(x, dw_w, dw_b, 2, 1, out_len=dev_i32(lengths), in_len=dev_i32(in_len))
