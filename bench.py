@@ -45,10 +45,27 @@ WORKLOAD = "conformer12_d512_h8_ffn2048_k15_vocab5002_b64_len200-2000_packed"
 CPU_SAMPLE_UTTS = 8
 
 
-def make_batch(rank: int, batch: int = 64):
-    """Seeded lengths (numpy default_rng(2024 + rank)) and features (torch seed 7 + rank)."""
-    rng = np.random.default_rng(2024 + rank)
-    lengths = [int(x) for x in rng.integers(200, 2001, size=batch)]
+def deal_lengths(rank: int, world: int, batch: int = 64):
+    """The job's utterances are the ``world`` seeded draws of ``batch`` lengths (numpy default_rng(2024 + r)); one rank
+    keeps its own draw, several ranks deal the pool so that every rank gets ``batch`` utterances of about equal total
+    length (longest first, each to the lightest rank that still has room), as a length-aware loader shards a job: the
+    step time is the slowest rank's."""
+    draws = [[int(x) for x in np.random.default_rng(2024 + r).integers(200, 2001, size=batch)] for r in range(world)]
+    if world == 1:
+        return draws[0]
+    pool = sorted((n for d in draws for n in d), reverse=True)
+    load, mine = [0] * world, [[] for _ in range(world)]
+    for n in pool:
+        r = min((i for i in range(world) if len(mine[i]) < batch), key=lambda i: load[i])
+        mine[r].append(n)
+        load[r] += n
+    order = np.random.default_rng(99 + rank).permutation(batch)          # no length order inside a rank's batch
+    return [mine[rank][i] for i in order]
+
+
+def make_batch(rank: int, batch: int = 64, world: int = 1):
+    """Seeded lengths (``deal_lengths``) and features (torch seed 7 + rank)."""
+    lengths = deal_lengths(rank, world, batch)
     g = torch.Generator().manual_seed(7 + rank)
     feats = torch.randn(batch, max(lengths), 80, generator=g)
     return feats, lengths
@@ -499,7 +516,7 @@ def main():
     cfg = model_config(args.layers)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16,
                          quant=None if args.quant == "none" else args.quant)
-    feats_host, lengths = make_batch(rank, args.batch)
+    feats_host, lengths = make_batch(rank, args.batch, world)
     workload = WORKLOAD if (args.batch, args.layers) == (64, 12) else \
         f"REDUCED profiling case: conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002_b{args.batch}_len200-2000_packed"
     feats_host = feats_host.pin_memory()
@@ -603,7 +620,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
             "data": "synthetic",
-            "config": {"workload": workload, "global_batch": args.batch * world, "parallelism": f"utterance-sharded x{world}, no collective",
+            "config": {"workload": workload, "global_batch": args.batch * world, "parallelism": f"utterance-sharded x{world} (utterances dealt by length, {args.batch} per rank), no collective",
                        "l2": "256 MiB flush write between steps; per-step working set (weights 240 MB + activations) > 126 MB L2",
                        "audio_seconds_per_step": audio_total / args.steps},
             "e2e": {"value": audio_total / (e2e_ms * 1e-3), "unit": "audio-s/s",
