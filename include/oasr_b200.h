@@ -90,7 +90,8 @@ OASR_API unsigned long long oasr_b200_launch_count(void);
  * = paged rel-pos attention with <= 16 query frames runs the warp-per-(stream,
  * head) kernel, 0 = always the 128-row tcgen05 kernel; "fmha_relpos_path": 1 (default) =
  * packed relative-position attention on the two-CTAs-per-SM kernel (64-key tiles),
- * 0 = on the general kernel; "pdl": 1 launches
+ * 0 = on the general kernel; "lsm_path": the CTC head, 0 (default) = by size, 1 = the fused two-sweep
+ * kernel, 2 = fp32 logits GEMM + in-place row log-softmax kernel (fp32 output only); "pdl": 1 launches
  * the GEMM, attention, add+norm, depthwise-conv and quantise kernels with
  * programmatic stream serialisation (their set-up overlaps the previous
  * kernel's tail), 0 (default) = plain stream order (no reference counterpart; the reference selects tiles

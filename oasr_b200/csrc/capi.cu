@@ -56,7 +56,7 @@ uint32_t* device_status_ptr() {
   return ptrs[dev];
 }
 
-namespace gemm { extern int g_force_bn; extern int g_use_pairs; }
+namespace gemm { extern int g_force_bn; extern int g_use_pairs; extern int g_lsm_path; }
 extern int g_dw_path;
 extern int g_fmha_relpos_path;
 int g_pdl = 0;  // measured neutral on both workloads (offline 7.32 vs 7.36 ms, streaming 3.79 vs 3.71 ms per step): off by default
@@ -71,6 +71,11 @@ int oasr_b200_set_tunable(const char* name, int value) {
     if (value != 0 && value != 64 && value != 128 && value != 256)
       return ob::set_error(OASR_ERR_INVALID, "gemm_bn must be 0, 64, 128 or 256 (got %d)", value);
     ob::gemm::g_force_bn = value;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "lsm_path") == 0) {
+    if (value < 0 || value > 2) return ob::set_error(OASR_ERR_INVALID, "lsm_path must be 0, 1 or 2 (got %d)", value);
+    ob::gemm::g_lsm_path = value;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "gemm_pairs") == 0) {

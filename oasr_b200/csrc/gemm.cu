@@ -579,7 +579,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         }
       } else if constexpr (kEpi == kEpiResid) {
         float* orow = static_cast<float*>(p.D) + row * p.N;
-        const float* rrow = p.R_in + row * p.N;
+        const float* rrow = p.R_in ? p.R_in + row * p.N : nullptr;   // null: D = alpha * (A.B^T + bias)
         const T* bias = static_cast<const T*>(p.bias);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -601,8 +601,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
                 for (int i = 0; i < 8; ++i) v[i] += bb[i];
               }
               if (row_ok) {
-                const float4 r0 = *reinterpret_cast<const float4*>(rrow + col);
-                const float4 r1 = *reinterpret_cast<const float4*>(rrow + col + 4);
+                float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0;
+                if (rrow) {
+                  r0 = *reinterpret_cast<const float4*>(rrow + col);
+                  r1 = *reinterpret_cast<const float4*>(rrow + col + 4);
+                }
                 float4 o0, o1;
                 o0.x = fmaf(p.alpha, v[0], r0.x); o0.y = fmaf(p.alpha, v[1], r0.y);
                 o0.z = fmaf(p.alpha, v[2], r0.z); o0.w = fmaf(p.alpha, v[3], r0.w);
@@ -867,6 +870,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(T* __restrict__ D, const
 // Host side
 // ---------------------------------------------------------------------------
 int g_force_bn = 0;  // 0 = heuristic; otherwise 64 / 128 / 256 (set through oasr_b200_set_tunable)
+int g_lsm_path = 0;   // CTC head: 0 = by size, 1 = one fused two-sweep kernel, 2 = fp32 logits GEMM + in-place row kernel
 int g_use_pairs = 0; // 1 = large dense problems run on CTA pairs (cta_group::2); 0 (default) = single-CTA tiles.
                      // Measured on B200 (M 17.5k, K 512..2048): pairs are 5-20 % slower than single-CTA tiles here.
 
@@ -952,6 +956,101 @@ int pick_bn(int64_t m_tiles_total, int64_t N, int64_t K = 512) {
     if (cost < best) { best = cost; best_bn = bn; }
   }
   return best_bn;
+}
+
+// In-place log-softmax (+ first-maximum index) of fp32 rows, N % 8 == 0: a block per row, the row held in registers
+// (up to 8192 columns; longer rows are re-read), max and sum reduced across the block.
+__global__ void __launch_bounds__(256) log_softmax_rows_f32_kernel(float* __restrict__ x, int32_t* __restrict__ argmax,
+                                                                   int M, int N) {
+  constexpr int kCache = 8;
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  __shared__ float s_bcast[2];
+  const int n4 = N >> 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    float4* xr = reinterpret_cast<float4*>(x + static_cast<int64_t>(row) * N);
+    float4 c[kCache];
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    auto see = [&](const float4& v, int col) {
+      if (v.x > best) { best = v.x; arg = col; }
+      if (v.y > best) { best = v.y; arg = col + 1; }
+      if (v.z > best) { best = v.z; arg = col + 2; }
+      if (v.w > best) { best = v.w; arg = col + 3; }
+    };
+#pragma unroll
+    for (int k = 0; k < kCache; ++k) {
+      const int ch = threadIdx.x + k * 256;
+      if (ch < n4) { c[k] = xr[ch]; see(c[k], ch * 4); }
+    }
+    for (int ch = threadIdx.x + kCache * 256; ch < n4; ch += 256) see(xr[ch], ch * 4);
+    // block maximum, ties to the smaller column
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+    }
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = arg; }
+    __syncthreads();
+    if (warp == 0) {
+      float bv = lane < 8 ? s_val[lane] : -INFINITY;
+      int bi = lane < 8 ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == 0) {
+        s_bcast[0] = bv;
+        if (argmax) argmax[row] = bi;
+      }
+    }
+    __syncthreads();
+    const float mx = s_bcast[0];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < kCache; ++k) {
+      if (threadIdx.x + k * 256 < n4)
+        sum += __expf(c[k].x - mx) + __expf(c[k].y - mx) + __expf(c[k].z - mx) + __expf(c[k].w - mx);
+    }
+    for (int ch = threadIdx.x + kCache * 256; ch < n4; ch += 256) {
+      const float4 v = xr[ch];
+      sum += __expf(v.x - mx) + __expf(v.y - mx) + __expf(v.z - mx) + __expf(v.w - mx);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) s_val[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += s_val[w];
+      s_bcast[1] = mx + __logf(t);
+    }
+    __syncthreads();
+    const float lse = s_bcast[1];
+#pragma unroll
+    for (int k = 0; k < kCache; ++k) {
+      const int ch = threadIdx.x + k * 256;
+      if (ch < n4) xr[ch] = make_float4(c[k].x - lse, c[k].y - lse, c[k].z - lse, c[k].w - lse);
+    }
+    for (int ch = threadIdx.x + kCache * 256; ch < n4; ch += 256) {
+      const float4 v = xr[ch];
+      xr[ch] = make_float4(v.x - lse, v.y - lse, v.z - lse, v.w - lse);
+    }
+    __syncthreads();   // s_val / s_bcast are reused by the next row
+  }
+}
+
+// The split CTC head wins where the fused kernel cannot fill the GPU (one CTA per 128-row tile).  Measured on B200 at
+// N = 5008, K = 512: split 25 us per 1024 rows (103 us at M = 4096), fused flat at 310-320 us up to one tile per SM;
+// they cross at 96 row tiles.
+bool lsm_split_wins(int64_t M, int64_t N, int64_t K) {
+  (void)N; (void)K;
+  return (M + BM - 1) / BM <= (5 * sm_count()) / 8;
 }
 
 struct Problem {
@@ -1309,6 +1408,24 @@ int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B, const vo
   OB_REQUIRE(out_dtype == OASR_DT_F32 || out_dtype == dtype, OASR_ERR_DTYPE,
              "gemm_log_softmax: out dtype must be fp32 or the activation dtype");
   if (M == 0) return OASR_OK;
+  // Two forms.  The fused kernel sweeps the vocabulary twice per 128-row tile (statistics, then the same products
+  // written normalised) and never writes logits; it keeps one CTA per row tile, so it needs about as many row tiles
+  // as SMs.  The split form writes fp32 logits into `out` with the dense scheduler (every SM busy at any M) and
+  // normalises the rows in place: one GEMM instead of two for a second pass over the output.
+  const bool split_ok = out_dtype == OASR_DT_F32 && !use_simt(M, N, K);
+  const bool split = split_ok && (g_lsm_path == 2 || (g_lsm_path == 0 && lsm_split_wins(M, N, K)));
+  if (split) {
+    Problem pg{};
+    pg.sched = kSchedDense; pg.epi = kEpiResid;
+    pg.M = M; pg.N = N; pg.K = K; pg.batch = 1; pg.A = A; pg.B = B;
+    pg.p.M = (int)M; pg.p.N = (int)N; pg.p.K = (int)K; pg.p.batch = 1;
+    pg.p.D = out; pg.p.R_in = nullptr; pg.p.bias = bias; pg.p.act = OASR_ACT_NONE; pg.p.alpha = 1.f;
+    if (int rc = run<kSchedDense, kEpiResid>(pg, dtype, static_cast<cudaStream_t>(stream))) return rc;
+    int64_t g = M < static_cast<int64_t>(sm_count()) * 8 ? M : static_cast<int64_t>(sm_count()) * 8;
+    log_softmax_rows_f32_kernel<<<static_cast<unsigned>(g), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<float*>(out), argmax, (int)M, (int)N);
+    return check_launch("log_softmax_rows launch");
+  }
   Problem pr{};
   pr.sched = kSchedSweep; pr.epi = kEpiLsm;
   pr.M = M; pr.N = N; pr.K = K; pr.batch = 1; pr.A = A; pr.B = B;

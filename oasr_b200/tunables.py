@@ -1,6 +1,8 @@
 """Process-wide integer tunables of the native library (tile shapes etc.).
 
 ``gemm_bn``: 0 lets the heuristic choose the GEMM tile width, 64 / 128 / 256 force it.
+``lsm_path``: the CTC head - 0 (default) chooses by size, 1 the fused two-sweep kernel, 2 an fp32 logits GEMM followed by
+an in-place row log-softmax kernel (fp32 output only).
 ``gemm_pairs``: 1 runs large dense GEMMs on CTA pairs (tcgen05 cta_group::2), 0 (default) on single-CTA tiles.
 ``dwconv_path``: 0 (default) uses the register-streaming depthwise conv kernel where it applies, 1 the shared-memory tiled one.
 ``fmha_chunk_path``: 1 (default) runs paged rel-pos attention with <= 16 query frames on the warp-per-(stream, head)

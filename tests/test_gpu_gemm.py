@@ -123,11 +123,21 @@ def test_group_gemm(dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", HALF)
-@pytest.mark.parametrize("M,N,K", [(708, 5008, 256), (300, 5008, 512), (64, 1024, 1024), (5, 8, 64), (130, 264, 72)])
-def test_gemm_log_softmax(dtype, M, N, K):
+@pytest.mark.parametrize("M,N,K", [(708, 5008, 256), (300, 5008, 512), (64, 1024, 1024), (5, 8, 64), (130, 264, 72),
+                                   (40, 9008, 64)])
+@pytest.mark.parametrize("path", [1, 2])
+def test_gemm_log_softmax(dtype, M, N, K, path):
+    """path 1 = the fused two-sweep kernel, 2 = fp32 logits GEMM + in-place row log-softmax (fp32 output)."""
+    from oasr_b200 import tunables
+
     A, B, C = _rand((M, K), dtype, 20), _rand((N, K), dtype, 21, K ** -0.5), _rand((N,), dtype, 22)
     want = O.gemm_log_softmax(A, B, C)
-    got32, arg = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda(), out_dtype=torch.float32, return_argmax=True)
+    tunables.set("lsm_path", path)
+    try:
+        got32, arg = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda(), out_dtype=torch.float32, return_argmax=True)
+    finally:
+        tunables.set("lsm_path", 0)
+    assert ob.device_status() == 0
     torch.testing.assert_close(got32.cpu(), want, rtol=1e-4, atol=2e-4)
     # every row is a normalised distribution (reference tests/test_gemm_log_softmax.py: |logsumexp| < 5e-3)
     assert got32.logsumexp(-1).abs().max().item() < 1e-4
