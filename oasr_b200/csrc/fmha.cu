@@ -467,6 +467,10 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
         }
         tile_max *= p.scale_log2;
       } else {
+        // kInterior: every key of the tile is inside [kv_start, kv_len) and there is no causal edge, so the
+        // per-element visibility test drops out (the usual tile when the masks arrive through the bias)
+        auto biased_pass = [&](auto interior_c) {
+        constexpr bool kInterior = decltype(interior_c)::value;
 #pragma unroll 1
         for (int c0 = 0; c0 < BKV; c0 += 32) {
           uint32_t v[32];
@@ -501,13 +505,18 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
             const int key = key0 + c0 + i;
             const float bf = (i & 1) ? unpack_hi<T>(bw[i / 2]) : unpack_lo<T>(bw[i / 2]);
             float x = fmaf(bf, 1.4426950408889634f, __uint_as_float(v[i]) * p.scale_log2);
-            const bool visible = key < kv_len && key >= kv_start && !(p.causal && key > row_in_seq);
-            x = visible ? x : kNegInf;
+            if constexpr (!kInterior) {
+              const bool visible = key < kv_len && key >= kv_start && !(p.causal && key > row_in_seq);
+              x = visible ? x : kNegInf;
+            }
             tile_max = fmaxf(tile_max, x);
             v[i] = __float_as_uint(x);
           }
           ptx::tmem_st_32x32(t_s + c0, v);
         }
+        };
+        if (!p.causal && key0 + BKV <= kv_len && key0 >= kv_start) biased_pass(std::true_type{});
+        else biased_pass(std::false_type{});
         ptx::tmem_st_wait();
       }
       m_new = fmaxf(m_run, tile_max);
@@ -524,8 +533,8 @@ fmha_tcgen05_kernel(const __grid_constant__ Maps maps, const Params p) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2f(fmaf(__uint_as_float(v[i]), pscale, -m_use));
-          const float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), pscale, -m_use));
+          const float p0 = ex2_fast(fmaf(__uint_as_float(v[i]), pscale, -m_use));   // ex2(-inf) = +0: masked keys
+          const float p1 = ex2_fast(fmaf(__uint_as_float(v[i + 1]), pscale, -m_use));
           row_sum += p0 + p1;
           packed[i / 2] = pack2<T>(p0, p1);
         }
