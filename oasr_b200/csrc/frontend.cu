@@ -200,14 +200,23 @@ __global__ void __launch_bounds__(256, 2) depthwise_conv2d_k3s2_kernel(Dw2dArgs 
       sw[e] = k < 9 ? Elem<T>::to_f(wt[c * 9 + k]) : (a.bias ? Elem<T>::to_f(static_cast<const T*>(a.bias)[c]) : 0.f);
     }
     __syncthreads();
-    const int64_t pstride = static_cast<int64_t>(gridDim.x) * lanes;
-    for (int64_t pos = static_cast<int64_t>(blockIdx.x) * lanes + threadIdx.x / groups; pos < positions; pos += pstride) {
-      const int fo = static_cast<int>(pos % a.Fo);
-      const int64_t r = pos / a.Fo;
-      const int to = static_cast<int>(r % a.To);
-      const int b = static_cast<int>(r / a.To);
-      const bool live = !a.out_len || to < a.out_len[b];
-      const int t_end = a.in_len ? min(a.T, a.in_len[b]) : a.T;
+    // positions fit 32 bits (the host checks); the per-stream limits are re-read only when the stream changes, so the
+    // input loads of a position do not wait on them
+    const uint32_t pstride = gridDim.x * static_cast<uint32_t>(lanes);
+    const uint32_t npos = static_cast<uint32_t>(positions);
+    const uint32_t per_b = static_cast<uint32_t>(a.To) * a.Fo;
+    int cur_b = -1, lim_out = 0, t_end = 0;
+    for (uint32_t pos = blockIdx.x * static_cast<uint32_t>(lanes) + threadIdx.x / groups; pos < npos; pos += pstride) {
+      const int b = static_cast<int>(pos / per_b);
+      const uint32_t rem = pos - static_cast<uint32_t>(b) * per_b;
+      const int to = static_cast<int>(rem / a.Fo);
+      const int fo = static_cast<int>(rem - static_cast<uint32_t>(to) * a.Fo);
+      if (b != cur_b) {
+        cur_b = b;
+        lim_out = a.out_len ? a.out_len[b] : a.To;
+        t_end = a.in_len ? min(a.T, a.in_len[b]) : a.T;
+      }
+      const bool live = to < lim_out;
       Pack<T> x[9];
       bool ok[9];
 #pragma unroll
@@ -236,7 +245,7 @@ __global__ void __launch_bounds__(256, 2) depthwise_conv2d_k3s2_kernel(Dw2dArgs 
       Pack<T> o;
 #pragma unroll
       for (int q = 0; q < 8; ++q) o.v[q] = Elem<T>::from_f(acc[q]);
-      st128(static_cast<T*>(a.out) + pos * a.C + c0, o);
+      st128(static_cast<T*>(a.out) + static_cast<int64_t>(pos) * a.C + c0, o);
     }
   } else {
     const int64_t total = positions * groups;
@@ -359,7 +368,7 @@ int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weigh
   Dw2dArgs a{out, in, weight, bias, out_len, in_len, (int)B, (int)T, (int)F, (int)C,
              (int)((T + pad_lo + pad_hi - 3) / 2 + 1), (int)((F + pad_lo + pad_hi - 3) / 2 + 1), (int)pad_lo};
   const int groups = (int)(C / 8);
-  const bool hoist = 256 % groups == 0 && C <= 1024;     // 40 bytes of shared memory per channel
+  const bool hoist = 256 % groups == 0 && C <= 1024 && B * a.To * a.Fo < (int64_t(1) << 31);     // 40 bytes of shared memory per channel
   const int64_t total = B * a.To * a.Fo * groups;
   int64_t g = (total + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * (hoist ? 2 : 16);   // hoisted: one resident wave, weights staged once
