@@ -340,7 +340,7 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
 // kAct: 0 = none, 1 = swish, 2 = any other id (run-time switch).  Swish is separate so that the unrolled tap
 // loop does not carry the never-taken activations between the instructions it executes (instruction fetch).
 template <typename T, int K, bool kAffine, int kAct>
-__global__ void __launch_bounds__(256) dwconv_stream_kernel(DwArgs a) {
+__global__ void __launch_bounds__(256, 2) dwconv_stream_kernel(DwArgs a) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
   ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
   ptx::grid_dep_wait();
