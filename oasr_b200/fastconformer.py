@@ -195,10 +195,21 @@ class FastConformerLayers:
                  "lens": torch.tensor(lengths, dtype=torch.int32).to(dev, non_blocking=True)}
             res = hidden.reshape(B * T, C).to(torch.float32, copy=True).contiguous()   # own copy: updated in place
             return self._layers(res, g).view(B, T, C)
-        total = sum(lengths)
         out = torch.zeros(B * T, C, device=dev, dtype=torch.float32)
+        rows, rows_dev = self.forward_rows(hidden, lengths)
+        if rows is not None:
+            out.index_copy_(0, rows_dev, rows)
+        return out.view(B, T, C)
+
+    def forward_rows(self, hidden: torch.Tensor, lengths: List[int]):
+        """The stack on the valid frames only: ``(rows (total, C) fp32, row_index (total,) int64)`` with
+        ``row_index[r] = b * T + t`` of packed row r; ``(None, None)`` for a batch without a valid frame."""
+        B, T, C = hidden.shape
+        dev = hidden.device
+        lengths = [min(max(int(n), 0), T) for n in lengths]
+        total = sum(lengths)
         if total == 0:
-            return out.view(B, T, C)
+            return None, None
         lens = np.asarray(lengths, dtype=np.int64)
         cu = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(lens, out=cu[1:])
@@ -212,8 +223,7 @@ class FastConformerLayers:
              "offsets": torch.from_numpy(offsets).to(dev, non_blocking=True)}
         rows_dev = torch.from_numpy(rows).to(dev, non_blocking=True)
         res = hidden.reshape(B * T, C).index_select(0, rows_dev).float()               # (total, C) fp32, own storage
-        out.index_copy_(0, rows_dev, self._layers(res, g))
-        return out.view(B, T, C)
+        return self._layers(res, g), rows_dev
 
 
 class FastConformerEncoder:
@@ -238,6 +248,14 @@ class FastConformerEncoder:
                                     w(params[p + "pointwise_conv.weight"].reshape(sub_channels, sub_channels)),
                                     w(params[p + "pointwise_conv.bias"])))
         self.proj = (w(params[s + "linear.weight"]), w(params[s + "linear.bias"]))
+        # optional CTC projection (CtcProjection, oasr/layers/ctc.py:48-51) at close to fp32 input precision: the
+        # weight split into 16-bit hi + lo parts laid out [W_hi | W_lo | W_hi] against rows [h_hi | h_hi | h_lo]
+        self.ctc = None
+        if "ctc.ctc_lo.weight" in params:
+            cw = params["ctc.ctc_lo.weight"].detach().float()
+            cw_hi = cw.to(dtype).float()
+            self.ctc = (w(torch.cat([cw_hi, cw - cw_hi, cw_hi], dim=1)), w(params["ctc.ctc_lo.bias"]))
+            self._one, self._zero = f(torch.ones(hidden)), f(torch.zeros(hidden))
 
     def subsample(self, feats: torch.Tensor, lengths: List[int]):
         """Frames at or past a row's valid length are never zeroed in memory: every consumer reads them as zeros
@@ -263,3 +281,28 @@ class FastConformerEncoder:
             raise RuntimeError("feats must be a CUDA tensor (oasr_b200 has no CPU path)")
         hidden, out_len = self.subsample(feats, [int(n) for n in lengths])
         return self.stack.forward(hidden, out_len, packed=packed), out_len
+
+    def forward_ctc(self, feats: torch.Tensor, lengths: List[int], padded_output: bool = True, return_argmax: bool = False):
+        """Encoder + CTC head: ``(log_probs fp32, out_lengths[, argmax])``.  The head (fused GEMM + log-softmax with the
+        per-frame argmax in its epilogue) runs on the valid frames only; with ``padded_output`` the log-probs come
+        back ``(B, T', V)`` with padding frames holding ``log_softmax(bias)`` (a zero hidden row, as the reference's
+        padded batch gives), else packed ``(total, V)``."""
+        if self.ctc is None:
+            raise RuntimeError("this encoder was built without a CTC projection (no 'ctc.ctc_lo.weight' in the parameters)")
+        if not feats.is_cuda:
+            raise RuntimeError("feats must be a CUDA tensor (oasr_b200 has no CPU path)")
+        hidden, out_len = self.subsample(feats, [int(n) for n in lengths])
+        B, T, C = hidden.shape
+        V = self.ctc[0].size(0)
+        rows, rows_dev = self.stack.forward_rows(hidden, out_len)
+        if rows is None:
+            lp = torch.zeros((B, T, V) if padded_output else (0, V), device=feats.device)
+            return (lp, out_len, None) if return_argmax else (lp, out_len)
+        h3 = torch.empty(rows.size(0), 3 * C, device=rows.device, dtype=self.dtype)
+        fused.add_norm_f32(h3, None, rows, None, 0.0, fused.ADD_NORM_AFFINE, self._one, self._zero, eps=1e-5, split_out=True)
+        lp, arg = OF.gemm_log_softmax(h3, self.ctc[0], self.ctc[1], out_dtype=torch.float32, return_argmax=True)
+        if padded_output:
+            full = torch.log_softmax(self.ctc[1].float(), dim=-1).expand(B * T, V).contiguous()
+            full.index_copy_(0, rows_dev, lp)
+            lp = full.view(B, T, V)
+        return (lp, out_len, arg) if return_argmax else (lp, out_len)

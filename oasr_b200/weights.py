@@ -85,3 +85,77 @@ def init_params(cfg: ConformerConfig, seed: int = 1234) -> Dict[str, torch.Tenso
     out["ctc.ctc_lo.weight"][cfg.vocab:] = 0.0
     out["ctc.ctc_lo.bias"][cfg.vocab:] = PAD_LOGIT
     return out
+
+
+def fastconformer_param_spec(hidden: int, heads: int, ffn: int, layers: int, kernel: int, bias: bool
+                             ) -> List[Tuple[str, Tuple[int, ...], str]]:
+    """Ordered (name, shape, kind) of the FastConformer / Nemotron layer stack in the reference's state-dict
+    naming (oasr/models/nemotron/encoder.py:150-359); kind 'w' matrix, 'g' norm gain, 'b' bias."""
+    C, D = hidden, hidden // heads
+    spec: List[Tuple[str, Tuple[int, ...], str]] = []
+    for i in range(layers):
+        p = f"layers.{i}."
+        for ff in ("feed_forward1", "feed_forward2"):
+            spec += [(p + ff + ".linear1.weight", (ffn, C), "w"), (p + ff + ".linear2.weight", (C, ffn), "w")]
+            if bias:
+                spec += [(p + ff + ".linear1.bias", (ffn,), "b"), (p + ff + ".linear2.bias", (C,), "b")]
+        a = p + "self_attn."
+        spec += [(a + "bias_u", (heads, D), "w"), (a + "bias_v", (heads, D), "w")]
+        for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            spec.append((a + n + ".weight", (C, C), "w"))
+            if bias:
+                spec.append((a + n + ".bias", (C,), "b"))
+        spec.append((a + "relative_k_proj.weight", (C, C), "w"))
+        c = p + "conv."
+        spec += [(c + "pointwise_conv1.weight", (2 * C, C, 1), "w"), (c + "depthwise_conv.weight", (kernel, 1, C), "w"),
+                 (c + "norm.weight", (C,), "g"), (c + "norm.bias", (C,), "b"), (c + "pointwise_conv2.weight", (C, C, 1), "w")]
+        if bias:
+            spec += [(c + "pointwise_conv1.bias", (2 * C,), "b"), (c + "depthwise_conv.bias", (C,), "b"),
+                     (c + "pointwise_conv2.bias", (C,), "b")]
+        for n in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
+            spec += [(p + n + ".weight", (C,), "g"), (p + n + ".bias", (C,), "b")]
+    return spec
+
+
+def subsampled_bins(mels: int, stages: int = 3) -> int:
+    """Frequency bins left after ``stages`` 3x3 / stride-2 convolutions padded (2, 1)
+    (oasr/models/nemotron/subsampling.py:26-131)."""
+    for _ in range(stages):
+        mels = mels // 2 + 1
+    return mels
+
+
+def init_fastconformer_params(hidden: int, heads: int, ffn: int, layers: int, kernel: int, mels: int, channels: int,
+                              seed: int = 1234, w_std: float = 0.02, bias: bool = False, stages: int = 3,
+                              vocab: int = 0) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic FastConformer encoder weights (layer stack from ``seed``, 8x subsampling front end from
+    ``seed + 1``, optional CTC projection of ``vocab`` rows from ``seed + 2``): matrices ~ N(0, w_std), norm gains
+    1 + N(0, 0.1), biases N(0, 0.1); front-end matrices ~ N(0, 0.25) so that activations keep unit scale through
+    the three ReLU stages."""
+    g = torch.Generator().manual_seed(seed)
+    P: Dict[str, torch.Tensor] = {}
+    for name, shape, kind in fastconformer_param_spec(hidden, heads, ffn, layers, kernel, bias):
+        if kind == "w":
+            P[name] = torch.randn(shape, generator=g) * w_std
+        elif kind == "g":
+            P[name] = 1.0 + torch.randn(shape, generator=g) * 0.1
+        else:
+            P[name] = torch.randn(shape, generator=g) * 0.1
+    g = torch.Generator().manual_seed(seed + 1)
+    s = "subsampling."
+    front = [(s + "conv_in.weight", (channels, 3, 3, 1), "w"), (s + "conv_in.bias", (channels,), "b")]
+    for i in range(stages - 1):
+        p = f"{s}layers.{i}."
+        front += [(p + "depthwise_conv.weight", (channels, 3, 3, 1), "w"), (p + "depthwise_conv.bias", (channels,), "b"),
+                  (p + "pointwise_conv.weight", (channels, 1, 1, channels), "w"), (p + "pointwise_conv.bias", (channels,), "b")]
+    front += [(s + "linear.weight", (hidden, channels * subsampled_bins(mels, stages)), "w"), (s + "linear.bias", (hidden,), "b")]
+    for name, shape, kind in front:
+        P[name] = torch.randn(shape, generator=g) * (0.25 if kind == "w" else 0.1)
+    if vocab:
+        g = torch.Generator().manual_seed(seed + 2)
+        vp = (vocab + 7) // 8 * 8
+        P["ctc.ctc_lo.weight"] = torch.randn(vp, hidden, generator=g) * w_std
+        P["ctc.ctc_lo.bias"] = torch.zeros(vp)
+        P["ctc.ctc_lo.weight"][vocab:] = 0.0
+        P["ctc.ctc_lo.bias"][vocab:] = PAD_LOGIT
+    return P

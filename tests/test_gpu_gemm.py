@@ -190,3 +190,59 @@ def test_gemm_cta_pairs_match_single_cta_tiles(dtype, M, N, K):
     if N % 2 == 0:
         Bg, Cg = _rand((2 * N, K), dtype, 34, K ** -0.5), _rand((2 * N,), dtype, 35)
         _check(ob.gemm_glu(A.cuda(), Bg.cuda(), Cg.cuda()), O.gemm_glu(A, Bg, Cg), dtype)
+
+
+# ---- the regime the benchmark runs: M ~ 17k packed frames, ~1100 output tiles, ~7 tiles per persistent CTA, so the
+# ---- accumulator double buffer and the operand ring wrap their phases many times inside one launch
+BENCH_M = 16722          # packed frames of the headline batch (64 utterances, lengths seed 2024)
+
+
+def _sample_rows(M, n=1536, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    rows = torch.randperm(M, generator=g)[:n]
+    edge = torch.arange(max(M - 200, 0), M)                   # the ragged last tile, entirely
+    return torch.unique(torch.cat([rows, edge, torch.arange(0, min(M, 130))]))
+
+
+@pytest.mark.parametrize("M,N,K,act", [(BENCH_M, 2048, 512, 2), (BENCH_M, 512, 2048, -1), (BENCH_M, 512, 512, -1),
+                                       (BENCH_M, 1536, 512, -1), (BENCH_M, 2048, 512, -1), (17500, 512, 1520, -1)])
+def test_gemm_at_benchmark_size_on_sampled_rows(M, N, K, act):
+    dtype = torch.bfloat16
+    A, B, C = _rand((M, K), dtype, 11), _rand((N, K), dtype, 12, K ** -0.5), _rand((N,), dtype, 13)
+    got = (ob.gemm_activation(A.cuda(), B.cuda(), C.cuda(), act) if act >= 0 else ob.gemm(A.cuda(), B.cuda(), C.cuda()))
+    rows = _sample_rows(M)
+    want = O.gemm(A[rows], B, C, act) if act >= 0 else O.gemm(A[rows], B, C)
+    _check(got[rows.cuda()], want, dtype)
+    # every row, against the same product in fp32 on the device (cuBLAS used as a checker only)
+    ref = torch.nn.functional.linear(A.cuda().float(), B.cuda().float(), C.cuda().float())
+    if act >= 0:
+        ref = O.activation(ref.cpu(), act).cuda()
+    torch.testing.assert_close(got.float(), ref.to(dtype).float(), rtol=2e-2, atol=2e-2)
+    assert ob.device_status() == 0
+
+
+def test_gemm_glu_at_benchmark_size():
+    dtype = torch.bfloat16
+    M, N, K = BENCH_M, 512, 512
+    A, B, C = _rand((M, K), dtype, 14), _rand((2 * N, K), dtype, 15, K ** -0.5), _rand((2 * N,), dtype, 16)
+    got = ob.gemm_glu(A.cuda(), B.cuda(), C.cuda())
+    rows = _sample_rows(M)
+    _check(got[rows.cuda()], O.gemm_glu(A[rows], B, C), dtype)
+    y = torch.nn.functional.linear(A.cuda().float(), B.cuda().float(), C.cuda().float())
+    ref = y[:, :N] * torch.sigmoid(y[:, N:])
+    torch.testing.assert_close(got.float(), ref.to(dtype).float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M", [BENCH_M, 12032])     # above and just above the row-tile count where the fused sweep form takes over
+def test_gemm_log_softmax_default_path_at_benchmark_size(M):
+    dtype = torch.bfloat16
+    N, K = 5008, 512
+    A, B, C = _rand((M, K), dtype, 17), _rand((N, K), dtype, 18, K ** -0.5), _rand((N,), dtype, 19, 0.1)
+    out, arg = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda(), out_dtype=torch.float32, return_argmax=True)
+    rows = _sample_rows(M, 1024)
+    want = O.gemm_log_softmax(A[rows], B, C)
+    got = out[rows.cuda()].cpu()
+    assert (got - want).abs().max().item() < 2e-2
+    assert out.logsumexp(-1).abs().max().item() < 1e-3
+    assert torch.equal(arg.long(), out.argmax(-1))
+    assert ob.device_status() == 0
