@@ -21,8 +21,10 @@ One JSON line is printed by rank 0:
 Under torchrun every rank runs its own batch (utterance-sharded, no collective on the data
 path); time is the max over ranks, value the sum of audio over ranks divided by it.
 
-``--impl reference`` times the CPU port of the reference's fp32 path (the reference package
-itself does not travel to the GPU box) on a bounded sample per step and prints the same line.
+``--impl reference`` times the reference's own fp32 torch path on the host cores, the whole batch per
+step: the reference's ``ConformerModel.forward_offline_packed`` from the copy under ``oracle/_ref``
+(made by ``oracle/make_ref.py``; ``kind: "reference"``) when that copy is present, else the CPU port
+``oracle.conformer`` (``kind: "port"``, pinned to the reference at 2e-6), and prints the same line.
 """
 from __future__ import annotations
 
@@ -182,14 +184,39 @@ def instrumented_step(run_step):
     return per
 
 
-def cpu_port_throughput(sample_utts: int, repeats: int = 1, threads=None):
-    """audio-s/s of the fp32 CPU port of the reference path on the first `sample_utts` utterances."""
-    from oracle import conformer as OC
+_CPU_MODEL = {}
 
-    if threads:
-        torch.set_num_threads(threads)
+
+def _cpu_forward():
+    """(kind, callable(feats, lengths) -> log_probs) of the CPU arm: the reference's own model from oracle/_ref when
+    present, else the oracle port.  Built once per process."""
+    if "fn" in _CPU_MODEL:
+        return _CPU_MODEL["kind"], _CPU_MODEL["fn"]
+    from oracle import conformer as OC
+    from oracle import make_ref
+
     cfg = OC.CONFIG2
     P = OC.init_params(cfg, 1234)
+    kind, fn = "port", (lambda f, lt: OC.forward_offline_packed(P, cfg, f, lt)[0])
+    if make_ref.available():
+        try:
+            from oracle import ref_model
+
+            ref_model.load_torch_route()
+            model = ref_model.build_conformer(cfg, P)
+            kind, fn = "reference", (lambda f, lt: model.forward_offline_packed(f, lt)[0])
+        except Exception as e:   # an import problem of the copy must not take the bench down: fall back to the port
+            print(f"[bench] oracle/_ref could not be used ({type(e).__name__}: {e}); timing the CPU port", file=sys.stderr)
+    _CPU_MODEL.update(kind=kind, fn=fn)
+    return kind, fn
+
+
+def cpu_throughput(sample_utts: int, repeats: int = 1, threads=None):
+    """audio-s/s of the fp32 CPU arm on the first `sample_utts` utterances of rank 0's batch:
+    (value, audio_s, best_seconds, threads, kind)."""
+    if threads:
+        torch.set_num_threads(threads)
+    kind, fn = _cpu_forward()
     feats, lengths = make_batch(0)
     lens = lengths[:sample_utts]
     f = feats[:sample_utts, :max(lens)].contiguous()
@@ -199,33 +226,60 @@ def cpu_port_throughput(sample_utts: int, repeats: int = 1, threads=None):
         best = None
         for _ in range(repeats):
             t0 = time.perf_counter()
-            OC.forward_offline_packed(P, cfg, f, lt)
+            fn(f, lt)
             dt = time.perf_counter() - t0
             best = dt if best is None else min(best, dt)
-    return audio_s / best, audio_s, best, torch.get_num_threads()
+    return audio_s / best, audio_s, best, torch.get_num_threads(), kind
+
+
+def offline_config(batch: int, layers: int, world: int, audio_per_step: float):
+    """The ``config`` object of the headline workload, shared by both arms."""
+    workload = WORKLOAD if (batch, layers) == (64, 12) else \
+        f"REDUCED profiling case: conformer{layers}_d512_h8_ffn2048_k15_vocab5002_b{batch}_len200-2000_packed"
+    return {"workload": workload, "global_batch": batch * world,
+            "parallelism": f"utterance-sharded x{world} (utterances dealt by length, {batch} per rank), no collective",
+            "l2": "256 MiB flush write between steps; per-step working set (weights 240 MB + activations) > 126 MB L2",
+            "output": "packed (total_frames, 5008) fp32 log-probs + per-frame argmax (padded_output=False: the (B, T', V) "
+                      "re-padding of forward_offline_packed is not in the timed step)",
+            "audio_seconds_per_step": audio_per_step}
+
+
+REFERENCE_ARM_BUDGET_S = 150.0
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    for _ in range(args.warmup):
-        cpu_port_throughput(2)
+    for _ in range(max(args.warmup, 1)):
+        v8, _, dt8, _, kind = cpu_throughput(4)
+    # the whole 64-utterance batch per step when K steps of it fit the time budget, else the largest prefix that does
+    feats, lengths = make_batch(0, args.batch, 1)
+    full_audio = sum(lengths) * FRAME_S
+    est_full = full_audio / v8
+    n = args.batch
+    if est_full * args.steps > REFERENCE_ARM_BUDGET_S:
+        n = max(4, min(args.batch, int(args.batch * REFERENCE_ARM_BUDGET_S / (est_full * args.steps))))
     times, audio = [], 0.0
     for _ in range(args.steps):
-        v, a, dt, thr = cpu_port_throughput(CPU_SAMPLE_UTTS)
+        v, a, dt, thr, kind = cpu_throughput(n)
         times.append(dt)
         audio += a
     value = audio / sum(times)
-    sample = f"first {CPU_SAMPLE_UTTS} of the 64 utterances per step (packed path, fp32)"
+    sample = (f"all {args.batch} utterances of the batch per step" if n == args.batch else
+              f"first {n} of the {args.batch} utterances per step (the whole batch for {args.steps} steps would exceed "
+              f"{REFERENCE_ARM_BUDGET_S:.0f} s)") + \
+             (", the reference's ConformerModel.forward_offline_packed (torch backend, fp32) from oracle/_ref" if kind == "reference"
+              else ", CPU port of the reference's fp32 packed path (oracle.conformer)")
     line = {
         "impl": "reference", "metric": "audio_seconds_per_second", "value": value, "unit": "audio-s/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "audio-s/s", "cores": torch.get_num_threads(), "kind": "port",
+        "config": offline_config(args.batch, args.layers, world, full_audio * world),
+        "cpu_baseline": {"value": value, "unit": "audio-s/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": sample},
         "e2e": {"value": value, "unit": "audio-s/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -407,27 +461,24 @@ def run_fastconformer(args):
     import oasr_b200
     from oasr_b200 import _lib
     from oasr_b200.fastconformer import FastConformerEncoder
-    from oracle import fastconformer as OFC   # seeded synthetic weights only (no oracle computation is timed)
+    from oasr_b200.weights import init_fastconformer_params
 
     torch.cuda.set_device(0)
     layers = 24 if args.layers == 12 else args.layers
     batch = 128 if args.batch == 64 else args.batch
-    cfg = OFC.FastConformerConfig(hidden=1024, heads=8, ffn=4096, layers=layers, kernel=9, sliding_window=57, lookahead=3, bias=False)
-    sub = OFC.SubsamplingConfig(mels=128, channels=256)
-    P = dict(OFC.init_params(cfg, 1234, w_std=0.02))
-    P.update(OFC.init_subsampling_params(sub, cfg.hidden, 1235))
-    enc = FastConformerEncoder(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead,
-                               sub.mels, sub.channels, P)
+    hidden, heads, ffn, kernel, mels, channels, vocab = 1024, 8, 4096, 9, 128, 256, 1024
+    P = init_fastconformer_params(hidden, heads, ffn, layers, kernel, mels, channels, seed=1234, w_std=0.02, bias=False, vocab=vocab)
+    enc = FastConformerEncoder(hidden, heads, ffn, layers, kernel, 57, 3, mels, channels, P)
     if args.quant != "none":
         enc.stack.qkind = {"fp8": 1, "int8": 2}[args.quant]
     rng = np.random.default_rng(2024)
     lengths = [int(x) for x in rng.integers(500, 3001, size=batch)]
-    feats = torch.randn(batch, max(lengths), sub.mels, generator=torch.Generator().manual_seed(7)).cuda()
+    feats = torch.randn(batch, max(lengths), mels, generator=torch.Generator().manual_seed(7)).cuda()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     sampler = ClockSampler(0)
     sampler.start()
     for _ in range(max(args.warmup, 3)):
-        enc.forward(feats, lengths)
+        enc.forward_ctc(feats, lengths, padded_output=False, return_argmax=True)
     torch.cuda.synchronize()
     assert oasr_b200.device_status() == 0
     sampler.rows.clear()
@@ -438,7 +489,7 @@ def run_fastconformer(args):
         flush.fill_(1)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        enc.forward(feats, lengths)
+        enc.forward_ctc(feats, lengths, padded_output=False, return_argmax=True)   # encoder + vocabulary-1024 CTC head
         b.record()
         evs.append((a, b))
     torch.cuda.synchronize()
@@ -451,7 +502,7 @@ def run_fastconformer(args):
         "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
         "data": "synthetic",
-        "config": {"workload": f"fastconformer{layers}_d1024_h8_ffn4096_k9_mel128_sub8x_b{batch}_len500-3000_padded_in_packed_layers",
+        "config": {"workload": f"fastconformer{layers}_d1024_h8_ffn4096_k9_mel128_sub8x_ctc1024_b{batch}_len500-3000_padded_in_packed_layers",
                    "audio_seconds_per_step": audio / steps, "l2": "256 MiB flush write between steps"},
         "gpu_launches": int(_lib.launch_count() - launches0), "clocks": clocks}), flush=True)
     return 0
@@ -467,6 +518,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the one-off check of this step's log-probs against the CPU oracle")
     ap.add_argument("--pdl", action="store_true", help="launch the hot kernels with programmatic stream serialisation (comparison run)")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"],
                     help="streaming workload: K/V page format (fp8 = e4m3 codes with per-head scales calibrated on four chunks)")
@@ -498,11 +550,23 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback")
     torch.cuda.set_device(local_rank)
+    # The CPU baseline runs FIRST, on rank 0, on every host core, before any process group exists: the other ranks
+    # wait for it inside the rendezvous (a host wait), so no GPU spins in a collective while a CPU loop runs, and the
+    # thread count is the same at every N (torchrun exports OMP_NUM_THREADS=1, which set_num_threads overrides).
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        v, a, dt, thr, kind = cpu_throughput(args.batch, repeats=2, threads=os.cpu_count() or 1)
+        cpu = {"value": v, "unit": "audio-s/s", "cores": thr, "kind": kind,
+               "sample": f"all {args.batch} utterances of rank 0's batch ({a:.1f} audio-s), fp32 packed path, best of two runs ({dt:.1f} s)"}
     dist = None
+    host_pg = None
     if world > 1:
+        import datetime
+
         import torch.distributed as dist_mod
 
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(minutes=20))
+        host_pg = dist_mod.new_group(backend="gloo")     # end-of-run wait on the host: no NCCL kernel spins on idle GPUs
         dist = dist_mod
 
     import oasr_b200
@@ -517,8 +581,6 @@ def main():
     model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16,
                          quant=None if args.quant == "none" else args.quant)
     feats_host, lengths = make_batch(rank, args.batch, world)
-    workload = WORKLOAD if (args.batch, args.layers) == (64, 12) else \
-        f"REDUCED profiling case: conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002_b{args.batch}_len200-2000_packed"
     feats_host = feats_host.pin_memory()
     feats_dev = feats_host.cuda(non_blocking=True)
     audio_s = sum(lengths) * FRAME_S
@@ -589,40 +651,68 @@ def main():
         peaks = measured_peaks()
         gemm = {"launches": 0, "ms": 0.0, "flops": 0.0}
         for k, v in per.items():
-            if k.startswith("gemm ") or k.startswith("gemm_glu") or k.startswith("gemm_q8"):   # every launch of gemm_tcgen05_kernel but the head
-                for f in gemm:
+            if k.startswith("gemm ") or k.startswith("gemm_glu") or k.startswith("gemm_q8") or k.startswith("gemm_addnorm"):
+                for f in gemm:                      # every launch of the tcgen05 GEMM kernel in the layer stack (not the head)
                     gemm[f] += v[f]
         step_total = total_ms / args.steps if dist is None else float(np.mean(step_ms))
         achieved = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
+        # flops the kernels issue beyond the algorithmic 2*M*N*K: the query block of the fused projection is computed
+        # twice ([Wq; Wq; Wk; Wv], once per positional bias): 2*M*d*d per layer
+        d_model, ffn = cfg.d_model, cfg.ffn
+        issued = gemm["flops"] + 2.0 * pk_rows * d_model * d_model * cfg.layers
+        # peak: the burst figure when the SM clock sampled during the timed region is in the burst regime (>= 0.9 of the
+        # maximum), the sustained figure otherwise; both fractions are printed
+        burst = bool(clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.9 * clocks["sm_max_mhz"])
+        peak = peaks["bf16_burst"] if burst else peaks["bf16_sustained"]
         roofline = {
-            "kernel": "gemm_tcgen05_kernel (all gemm / gemm_glu launches of one step of the layer stack)",
-            "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
-            "frac": achieved / peaks["bf16_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
-            # DRAM bytes of ONE FFN w_1 launch (M x 2048 x 512, the launch type with the largest share): operand reads
-            # scaled from the reduced-case ncu capture under profiles/ (A grows with M, B is constant: every operand
-            # byte is read once), plus the output bytes, which the reduced case cannot show (its output stays in L2)
-            "traffic": int(2 * (pk_rows * 512 + 2048 * 512 + pk_rows * 2048)) if args.layers else None,
-            "traffic_of": "one FFN w_1 launch; reads scaled from the ncu reduced case, writes = output size",
+            "kernel": "gemm_tcgen05_kernel (all GEMM launches of one step of the layer stack, incl. the embed Linear)",
+            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak,
+            "peak_source": f"{peaks['source']} ({'burst' if burst else 'sustained'} bf16: median SM clock {clocks.get('sm_mhz')} MHz "
+                           f"of {clocks.get('sm_max_mhz')})",
+            "frac_of_burst": achieved / peaks["bf16_burst"], "frac_of_sustained": achieved / peaks["bf16_sustained"],
+            "flops": gemm["flops"], "flops_issued": issued, "achieved_issued": issued / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0,
+            # algorithmic DRAM bytes of ONE FFN w_1 launch (M x ffn x d_model, the launch type with the largest share): every
+            # operand byte once plus the output; the reduced-case ncu capture under profiles/ shows dram__bytes_read equal
+            # to the operand bytes (its output stays in L2, so the write side cannot be captured at a size ncu may run)
+            "traffic": int(2 * (pk_rows * d_model + ffn * d_model + pk_rows * ffn)),
+            "traffic_of": "one FFN w_1 launch: operand + output bytes (formula; dram__bytes_read of the reduced ncu case matches the operand part)",
             "launches": gemm["launches"], "share_of_step": gemm["ms"] / step_total if step_total else None,
         }
         kernels = {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
                        **({"tflops": round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 1)} if v["flops"] and v["ms"] else {})}
                    for k, v in sorted(per.items(), key=lambda kv: -kv[1]["ms"])}
-        cpu = None
-        if not args.no_cpu_baseline:
-            # the whole 64-utterance batch, twice (about 10-15 s of CPU work); the better run counts
-            v, a, dt, thr = cpu_port_throughput(64, repeats=2)
-            cpu = {"value": v, "unit": "audio-s/s", "cores": thr, "kind": "port",
-                   "sample": f"all 64 utterances of the batch ({a:.1f} audio-s), fp32 packed path, best of two runs ({dt:.1f} s)"}
+        # parity of what was timed: the first utterances of this step's own log-probs against the fp32 CPU oracle
+        parity = None
+        if not args.no_parity and args.quant == "none":
+            from oracle import conformer as OC
+
+            n_chk = min(4, len(lengths))
+            lp, out_len, pk = device_step()
+            rows = sum(pk.seg_lengths[:n_chk])
+            got = lp[:rows].float().cpu()
+            ocfg = OC.ConformerConfig(d_model=cfg.d_model, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, kernel=cfg.kernel,
+                                      vocab=cfg.vocab)
+            torch.set_num_threads(os.cpu_count() or 1)
+            with torch.no_grad():
+                lens = lengths[:n_chk]
+                want, wl = OC.forward_offline_packed(OC.init_params(ocfg, 1234), ocfg, feats_host[:n_chk, :max(lens)].contiguous(),
+                                                     torch.tensor(lens))
+            want = want[torch.arange(want.shape[1])[None, :] < wl[:, None]]
+            dlt = (got - want)[:, :cfg.vocab].abs()
+            same = got[:, :cfg.vocab].argmax(-1) == want[:, :cfg.vocab].argmax(-1)
+            top2 = want[:, :cfg.vocab].topk(2, -1).values
+            clear = (top2[:, 0] - top2[:, 1]) > 2e-2
+            parity = {"against": "fp32 CPU oracle (oracle.conformer.forward_offline_packed)", "utterances": n_chk, "frames": int(rows),
+                      "max_abs": dlt.max().item(), "mean_abs": dlt.mean().item(), "argmax": same.float().mean().item(),
+                      "argmax_margin_gt_2e-2": same[clear].float().mean().item() if clear.any() else None}
         line = {
             "metric": "audio_seconds_per_second", "value": audio_total / (total_ms * 1e-3), "unit": "audio-s/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
             "data": "synthetic",
-            "config": {"workload": workload, "global_batch": args.batch * world, "parallelism": f"utterance-sharded x{world} (utterances dealt by length, {args.batch} per rank), no collective",
-                       "l2": "256 MiB flush write between steps; per-step working set (weights 240 MB + activations) > 126 MB L2",
-                       "audio_seconds_per_step": audio_total / args.steps},
+            "config": offline_config(args.batch, args.layers, world, audio_total / args.steps),
             "e2e": {"value": audio_total / (e2e_ms * 1e-3), "unit": "audio-s/s",
                     "h2d_bytes_per_step": int(feats_host.numel() * 4), "d2h_bytes_per_step": int(d2h),
                     "api": "ConformerCTC.greedy_search_batches(pinned host features -> token lists), copies pipelined with compute"},
@@ -630,11 +720,13 @@ def main():
             "clocks": clocks,
             "roofline": roofline,
             "cpu_baseline": cpu,
+            "parity": parity,
             "kernels_one_step": kernels,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.barrier()
+        torch.cuda.synchronize()
+        dist.barrier(group=host_pg)          # ranks > 0 wait here on the host while rank 0 finishes its report
         dist.destroy_process_group()
     return 0
 

@@ -248,10 +248,12 @@ OASR_API int oasr_b200_depthwise_conv1d_affine(void* out, const void* in, const 
  * scatter, oasr/cache/state.py:88-94): xcat[b] = [state[slot_ids[b]] ; x[b]]
  * with state (num_slots, state_len, channels), x (B, T, channels), xcat
  * (B, state_len + T, channels); afterwards state[slot_ids[b]] is set to the
- * last state_len rows of xcat[b]. */
-OASR_API int oasr_b200_conv_state_concat(void* xcat, void* state, const int64_t* slot_ids,
-                                         const void* x, int64_t B, int64_t state_len, int64_t T,
-                                         int64_t channels, int dtype, void* stream);
+ * last state_len rows of xcat[b].  A slot id outside [0, num_slots) reads as
+ * a zero left context and is not written back. */
+OASR_API int oasr_b200_conv_state_concat(void* xcat, void* state, int64_t num_slots,
+                                         const int64_t* slot_ids, const void* x, int64_t B,
+                                         int64_t state_len, int64_t T, int64_t channels, int dtype,
+                                         void* stream);
 /* Streaming causal depthwise conv with a rolling state: in (batch, seq_len,
  * channels), state (batch, kernel_size-1, channels) updated in place to the
  * last kernel_size-1 frames of [state, in], weight (channels, kernel_size).
@@ -547,15 +549,17 @@ OASR_API int oasr_b200_paged_kv_gather(void* k_out, void* v_out, const void* k_p
 
 /* ---- packed-layout glue ------------------------------------------------ */
 /* out[i, :] = in[index[i], :] for i < n_out (rows of `row_bytes` bytes,
- * multiple of 16; index int64; a negative index writes zeros).  Covers
+ * multiple of 16; index int64; `in` has `in_rows` rows and an index outside
+ * [0, in_rows) writes a zero row instead of reading).  Covers
  * pack_hidden / the gapped-conv gather (oasr/models/conformer/packing.py:222-232,
  * oasr/models/conformer/model.py:223-233) and SlotTensor.gather
  * (oasr/cache/state.py:88-94). */
 OASR_API int oasr_b200_gather_rows(void* out, const void* in, const int64_t* index, int64_t n_out,
-                                   int64_t row_bytes, void* stream);
-/* out[index[i], :] = in[i, :] for i < n_in (index_copy_ along rows). */
+                                   int64_t row_bytes, int64_t in_rows, void* stream);
+/* out[index[i], :] = in[i, :] for i < n_in (index_copy_ along rows); `out` has
+ * `out_rows` rows and an index outside [0, out_rows) is skipped. */
 OASR_API int oasr_b200_scatter_rows(void* out, const void* in, const int64_t* index, int64_t n_in,
-                                    int64_t row_bytes, void* stream);
+                                    int64_t row_bytes, int64_t out_rows, void* stream);
 
 /* ---- encoder layer stack (native executor) ------------------------------ */
 /* Device pointers to the prepared weights of one Conformer encoder layer
@@ -662,7 +666,11 @@ OASR_API int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* mo
  * than oasr_b200_conformer_noalloc_capacity_bytes() is refused with
  * OASR_ERR_INVALID and nothing is launched.  The first call on a device
  * resolves the array's device address; make it with that device current and
- * outside any stream capture.  All calls share the array (it keeps the last
+ * outside any stream capture.  That first call is also when the CUDA runtime
+ * places the array on the device, so make one warm-up call per device (total
+ * = 0 is enough) at start-up, BEFORE the host's pool takes the GPU's memory;
+ * made later it fails with an out-of-memory status.  Serialise calls on a
+ * device, the first one included.  All calls share the array (it keeps the last
  * call's contents; no step reads it before writing), so calls that overlap on
  * the GPU race with each other and must be serialised by the caller. */
 OASR_API int oasr_b200_conformer_encode_packed_noalloc(const oasr_b200_conformer_model* model,

@@ -52,14 +52,20 @@ OPERATOR_NAMES = (
 )
 
 
-def install(oasr_module) -> dict:
+def install(oasr_module, lift_row_floor: bool = False) -> dict:
     """Rebind the hot-path operators on an imported reference ``oasr`` package.
 
     Layers and models of the reference look operators up as module attributes
     at call time (``oasr.gemm(...)``; ``from oasr.functionals.attention import
     fmha`` inside the call), so rebinding the attributes swaps the backend with
     no model or engine edit.  Returns the replaced attributes so a caller can
-    restore them.
+    restore them (``uninstall``).
+
+    ``lift_row_floor``: the reference's layers send projections of fewer than
+    ``GEMM_MIN_ROWS`` (128) rows to ``F.linear`` because its tiled kernel loses
+    to cuBLAS there (oasr/layers/_backend.py:293-320); the kernels here take any
+    row count, so the floor can be set to 0 (streaming chunks of a few streams
+    then stay on this library too).
     """
     import sys
 
@@ -78,4 +84,26 @@ def install(oasr_module) -> dict:
                 setattr(attn, name, getattr(this, name))
             saved[name] = getattr(oasr_module, name, None)
             setattr(oasr_module, name, getattr(this, name))
+    if lift_row_floor:
+        backend = getattr(getattr(oasr_module, "layers", None), "_backend", None)
+        if backend is not None and hasattr(backend, "GEMM_MIN_ROWS"):
+            saved["layers._backend.GEMM_MIN_ROWS"] = backend.GEMM_MIN_ROWS
+            backend.GEMM_MIN_ROWS = 0
     return saved
+
+
+def uninstall(oasr_module, saved: dict) -> None:
+    """Put back what ``install`` replaced (``saved`` is its return value)."""
+    attn = getattr(getattr(oasr_module, "functionals", None), "attention", None)
+    for key, value in saved.items():
+        if key == "layers._backend.GEMM_MIN_ROWS":
+            oasr_module.layers._backend.GEMM_MIN_ROWS = value
+            continue
+        target, name = (attn, key.rsplit(".", 1)[1]) if key.startswith("functionals.attention.") else (oasr_module, key)
+        if target is None:
+            continue
+        if value is None:
+            if hasattr(target, name):
+                delattr(target, name)
+        else:
+            setattr(target, name, value)

@@ -50,7 +50,7 @@ _SIGNATURES = {
     "oasr_b200_fmha_varlen_relpos": [P, P, P, I, I, P, I, I, I, I, c_double, c_int, P],
     "oasr_b200_fmha_paged_relpos": [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, c_double, c_int, P],
     "oasr_b200_depthwise_conv1d_affine": [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P],
-    "oasr_b200_conv_state_concat": [P, P, P, P, I, I, I, I, c_int, P],
+    "oasr_b200_conv_state_concat": [P, P, I, P, P, I, I, I, I, c_int, P],
     "oasr_b200_glu": [P, P, I, I, c_int, P],
     "oasr_b200_swish": [P, P, I, c_int, P],
     "oasr_b200_depthwise_conv1d": [P, P, P, P, I, I, I, I, I, I, P, c_int, c_int, c_int, c_int, P],
@@ -79,8 +79,8 @@ _SIGNATURES = {
     "oasr_b200_fmha_varlen": [P, P, P, P, P, P, c_int, P, P, I, I, I, I, I, I, I, c_double, c_int, P],
     "oasr_b200_paged_kv_write": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, c_int, P],
     "oasr_b200_paged_kv_gather": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
-    "oasr_b200_gather_rows": [P, P, P, I, I, P],
-    "oasr_b200_scatter_rows": [P, P, P, I, I, P],
+    "oasr_b200_gather_rows": [P, P, P, I, I, I, P],
+    "oasr_b200_scatter_rows": [P, P, P, I, I, I, P],
 }
 
 

@@ -74,33 +74,40 @@ class PagedKVCache:
 
 
 def gather_rows(src: torch.Tensor, index: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
-    """``out[i] = src[index[i]]`` over the leading dimension (a negative index gives a zero row):
+    """``out[i] = src[index[i]]`` over the leading dimension (an index outside ``[0, len(src))`` gives a zero row):
     ``pack_hidden`` / gapped-conv gather / ``SlotTensor.gather``
     (oasr/models/conformer/packing.py:222-225, oasr/cache/state.py:88-94)."""
     _need_cuda(src, index, out)
     src = src.contiguous()
     row_bytes = (src.numel() // src.size(0)) * src.element_size() if src.size(0) else 0
+    want_shape = (index.numel(),) + tuple(src.shape[1:])
     if out is None:
-        out = torch.empty((index.numel(),) + tuple(src.shape[1:]), device=src.device, dtype=src.dtype)
+        out = torch.empty(want_shape, device=src.device, dtype=src.dtype)
+    elif tuple(out.shape) != want_shape or out.dtype != src.dtype or not out.is_contiguous() or out.device != src.device:
+        raise ValueError(f"out must be a contiguous {src.dtype} tensor of shape {want_shape} on {src.device}")
     if index.dtype != torch.int64:
         index = index.to(torch.int64)
     if index.numel() and row_bytes:
-        _lib.call("oasr_b200_gather_rows", _p(out), _p(src), _p(index.contiguous()), index.numel(), row_bytes,
-                  _stream(src))
+        with torch.cuda.device(src.device):
+            _lib.call("oasr_b200_gather_rows", _p(out), _p(src), _p(index.contiguous()), index.numel(), row_bytes,
+                      src.size(0), _stream(src))
     return out
 
 
 def scatter_rows(dst: torch.Tensor, index: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     """``dst[index[i]] = src[i]`` (``index_copy_`` along dim 0: unpack_hidden / gapped-conv scatter /
-    ``SlotTensor.scatter``)."""
+    ``SlotTensor.scatter``); an index outside ``[0, len(dst))`` is skipped."""
     _need_cuda(dst, index, src)
     if not dst.is_contiguous():
         raise ValueError("dst must be contiguous")
     src = src.contiguous()
+    if src.dtype != dst.dtype or tuple(src.shape[1:]) != tuple(dst.shape[1:]) or src.size(0) != index.numel():
+        raise ValueError("src must hold one row of dst's row shape and dtype per index")
     row_bytes = (src.numel() // src.size(0)) * src.element_size() if src.size(0) else 0
     if index.dtype != torch.int64:
         index = index.to(torch.int64)
     if index.numel() and row_bytes:
-        _lib.call("oasr_b200_scatter_rows", _p(dst), _p(src), _p(index.contiguous()), index.numel(), row_bytes,
-                  _stream(src))
+        with torch.cuda.device(src.device):
+            _lib.call("oasr_b200_scatter_rows", _p(dst), _p(src), _p(index.contiguous()), index.numel(), row_bytes,
+                      dst.size(0), _stream(src))
     return dst

@@ -3,6 +3,7 @@
 // caller's stream.  Host code only; every step is one of this library's own
 // C-ABI kernels.  No allocation, no host synchronisation, launch order and
 // kernel choice are pure functions of the shapes.
+#include <atomic>
 #include <cmath>
 #include <vector>
 
@@ -214,7 +215,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
                                    m.eps, 0, dt, stream));
     // relative-position self-attention
-    OB_LINEAR("qkv4", 2.0 * M * 4 * d * d, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, d, OASR_ACT_NONE, 0);
+    OB_LINEAR("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, d, OASR_ACT_NONE, 0);
     OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs, max_seg,
                                          M, m.heads, scale, dt, stream));
     OB_LINEAR("attn_out", 2.0 * M * d * d, w.y, w.att, l.out_w, l.out_b, l, 3, d, d, OASR_ACT_NONE, 0);
@@ -240,7 +241,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
     }
   }
   if (log_probs) {
-    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * 3 * d, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
+    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued at split precision (K = 3d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
                                        argmax, stream));
   }
   return OASR_OK;
@@ -257,7 +258,12 @@ int64_t oasr_b200_conformer_noalloc_capacity_bytes(void) { return ob::kStaticScr
 // Set-up: the array's name is only a host-side handle here, not something a kernel can be given.
 // The first call on each device -- made with that device current -- asks the runtime for the
 // array's device address (cudaGetSymbolAddress), checks the result and keeps it for later calls
-// on that device.  Make that first call outside of any stream capture.
+// on that device.  Make that first call outside of any stream capture.  It is also the moment the
+// CUDA runtime loads this part of the library onto the device, which is when the 64 MiB are
+// really reserved: a host whose pool takes all GPU memory should make one warm-up call per device
+// (total = 0 is enough: the address is resolved before the empty batch returns) BEFORE the pool
+// grabs the memory; later the call would fail with an out-of-memory status instead.  The per-device
+// address is published atomically, so concurrent first calls are safe; they only repeat the lookup.
 //
 // Limits and sharing: a batch whose scratch need (oasr_b200_conformer_workspace_bytes) exceeds
 // oasr_b200_conformer_noalloc_capacity_bytes() is refused with OASR_ERR_INVALID before anything
@@ -278,21 +284,25 @@ int oasr_b200_conformer_encode_packed_noalloc(const oasr_b200_conformer_model* m
              "conformer_encode_packed_noalloc: this batch needs %lld bytes of scratch but the built-in array holds "
              "%lld; send fewer frames per call or use oasr_b200_conformer_encode_packed with your own workspace",
              (long long)need, (long long)kStaticScratchBytes);
-  static unsigned char* scratch_of_device[64] = {nullptr};
+  static std::atomic<unsigned char*> scratch_of_device[64];
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   OB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, OASR_ERR_CUDA,
              "conformer_encode_packed_noalloc: cannot identify the current device (%s)", cudaGetErrorString(e));
-  if (scratch_of_device[dev] == nullptr) {
-    unsigned char* ptr = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
-    OB_REQUIRE(e == cudaSuccess && ptr != nullptr, OASR_ERR_CUDA,
+  unsigned char* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_static_scratch);
+    OB_REQUIRE(e != cudaErrorMemoryAllocation, OASR_ERR_CUDA,
+               "conformer_encode_packed_noalloc: device %d has no room left for the library's %lld-byte scratch array; make "
+               "one warm-up call per device at start-up, before the host's pool takes the memory",
+               dev, (long long)kStaticScratchBytes);
+    OB_REQUIRE(e == cudaSuccess && scratch != nullptr, OASR_ERR_CUDA,
                "conformer_encode_packed_noalloc: the scratch array has no device address on device %d (%s)", dev,
                cudaGetErrorString(e));
-    scratch_of_device[dev] = ptr;
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
   }
-  return oasr_b200_conformer_encode_packed(model, rows, cu_seqlens, fill_frames, num_segs, total, max_seg,
-                                           scratch_of_device[dev], kStaticScratchBytes, log_probs, argmax, stream);
+  return oasr_b200_conformer_encode_packed(model, rows, cu_seqlens, fill_frames, num_segs, total, max_seg, scratch,
+                                           kStaticScratchBytes, log_probs, argmax, stream);
 }
 
 int64_t oasr_b200_conformer_chunk_workspace_bytes(const oasr_b200_conformer_model* model, int64_t B, int64_t T) {
@@ -345,7 +355,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
                                    m.eps, 0, dt, stream));
     // attention: project, append the chunk's keys/values to the pages, attend over cache + chunk
-    OB_STEP("gemm qkv4", 2.0 * M * 4 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
+    OB_STEP("gemm qkv4", 2.0 * M * 3 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
     if (kv_scales) {   // fp8 pages: per-head scales of this layer, K then V
       const float* ks = kv_scales + static_cast<int64_t>(i) * 2 * m.heads;
       const float* vs = ks + m.heads;
@@ -370,7 +380,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
                                    nullptr, M, d, m.eps, 0, dt, stream));
     // convolution module with the cached left context
     OB_STEP("conv_state_concat", 0, oasr_b200_conv_state_concat(w.xcat, static_cast<uint8_t*>(cnn_state) + i * num_slots * SL * d * 2,
-                                     slot_ids, w.h, B, SL, T, d, dt, stream));
+                                     num_slots, slot_ids, w.h, B, SL, T, d, dt, stream));
     OB_STEP("gemm_glu pw1", 2.0 * MC * 2 * d * d, oasr_b200_gemm_glu(w.g, w.xcat, l.pw1_w, l.pw1_b, MC, d, d, dt, stream));
     OB_STEP("depthwise_conv1d", 0, oasr_b200_depthwise_conv1d_affine(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
                                      B, T + SL, d, m.kernel, 0, 0, OASR_ACT_SWISH, dt, stream));
@@ -388,7 +398,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
     }
   }
   if (log_probs) {
-    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * 3 * d, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
+    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued at split precision (K = 3d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
                                        argmax, stream));
   }
   return OASR_OK;

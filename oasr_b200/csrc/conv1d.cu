@@ -601,7 +601,7 @@ __global__ void __launch_bounds__(256) conv_state_concat_kernel(uint8_t* __restr
                                                                 const uint8_t* __restrict__ state,
                                                                 const int64_t* __restrict__ slots,
                                                                 const uint8_t* __restrict__ x, int64_t B, int SL, int T,
-                                                                int64_t row_bytes) {
+                                                                int64_t row_bytes, int64_t num_slots) {
   const int64_t pieces = row_bytes / 16;
   const int64_t total = B * (SL + T) * pieces;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -610,15 +610,21 @@ __global__ void __launch_bounds__(256) conv_state_concat_kernel(uint8_t* __restr
     const int64_t row = i / pieces;
     const int r = static_cast<int>(row % (SL + T));
     const int64_t b = row / (SL + T);
-    const uint8_t* src = r < SL ? state + ((slots[b] * SL + r) * row_bytes) : x + ((b * T + (r - SL)) * row_bytes);
-    *reinterpret_cast<uint4*>(xcat + row * row_bytes + piece * 16) = *reinterpret_cast<const uint4*>(src + piece * 16);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < SL) {
+      const int64_t slot = slots[b];   // a slot id outside the buffer reads as an empty (zero) left context
+      if (slot >= 0 && slot < num_slots) v = *reinterpret_cast<const uint4*>(state + (slot * SL + r) * row_bytes + piece * 16);
+    } else {
+      v = *reinterpret_cast<const uint4*>(x + (b * T + (r - SL)) * row_bytes + piece * 16);
+    }
+    *reinterpret_cast<uint4*>(xcat + row * row_bytes + piece * 16) = v;
   }
 }
 // state[slot[b]] = last SL rows of xcat[b] (read from xcat, so the update cannot race with itself).
 __global__ void __launch_bounds__(256) conv_state_update_kernel(uint8_t* __restrict__ state,
                                                                 const int64_t* __restrict__ slots,
                                                                 const uint8_t* __restrict__ xcat, int64_t B, int SL,
-                                                                int T, int64_t row_bytes) {
+                                                                int T, int64_t row_bytes, int64_t num_slots) {
   const int64_t pieces = row_bytes / 16;
   const int64_t total = B * SL * pieces;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -627,7 +633,9 @@ __global__ void __launch_bounds__(256) conv_state_update_kernel(uint8_t* __restr
     const int64_t row = i / pieces;
     const int r = static_cast<int>(row % SL);
     const int64_t b = row / SL;
-    *reinterpret_cast<uint4*>(state + (slots[b] * SL + r) * row_bytes + piece * 16) =
+    const int64_t slot = slots[b];
+    if (slot < 0 || slot >= num_slots) continue;   // never a write outside the state buffer
+    *reinterpret_cast<uint4*>(state + (slot * SL + r) * row_bytes + piece * 16) =
         *reinterpret_cast<const uint4*>(xcat + (b * (SL + T) + T + r) * row_bytes + piece * 16);
   }
 }
@@ -638,10 +646,11 @@ __global__ void __launch_bounds__(256) conv_state_update_kernel(uint8_t* __restr
 
 extern "C" {
 
-int oasr_b200_conv_state_concat(void* xcat, void* state, const int64_t* slot_ids, const void* x, int64_t B,
-                                int64_t state_len, int64_t T, int64_t channels, int dtype, void* stream) {
+int oasr_b200_conv_state_concat(void* xcat, void* state, int64_t num_slots, const int64_t* slot_ids, const void* x,
+                                int64_t B, int64_t state_len, int64_t T, int64_t channels, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(B >= 0 && state_len >= 0 && T > 0 && channels > 0, OASR_ERR_INVALID, "conv_state_concat: bad shape");
+  OB_REQUIRE(B >= 0 && state_len >= 0 && T > 0 && channels > 0 && num_slots >= 0, OASR_ERR_INVALID,
+             "conv_state_concat: bad shape");
   if (B == 0) return OASR_OK;
   OB_REQUIRE(xcat && state && slot_ids && x, OASR_ERR_INVALID, "conv_state_concat: null pointer argument");
   const int64_t es = dtype == OASR_DT_F32 ? 4 : 2;
@@ -656,14 +665,14 @@ int oasr_b200_conv_state_concat(void* xcat, void* state, const int64_t* slot_ids
   if (g > cap) g = cap;
   conv_state_concat_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(
       static_cast<uint8_t*>(xcat), static_cast<const uint8_t*>(state), slot_ids, static_cast<const uint8_t*>(x), B,
-      (int)state_len, (int)T, row_bytes);
+      (int)state_len, (int)T, row_bytes, num_slots);
   if (int rc = check_launch("conv_state_concat launch")) return rc;
   if (state_len == 0) return OASR_OK;
   g = (B * state_len * (row_bytes / 16) + 255) / 256;
   if (g > cap) g = cap;
   conv_state_update_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(static_cast<uint8_t*>(state), slot_ids,
                                                                    static_cast<const uint8_t*>(xcat), B, (int)state_len,
-                                                                   (int)T, row_bytes);
+                                                                   (int)T, row_bytes, num_slots);
   return check_launch("conv_state_update launch");
 }
 

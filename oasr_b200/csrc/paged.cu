@@ -98,11 +98,13 @@ __global__ void __launch_bounds__(256) paged_kv_gather_kernel(PagedGatherArgs a)
   }
 }
 
-// Row gather / scatter with int64 indices; rows are multiples of 16 bytes.
+// Row gather / scatter with int64 indices; rows are multiples of 16 bytes.  `table_rows` is the row count of the
+// indexed side (source of a gather, destination of a scatter): an index outside [0, table_rows) never becomes an
+// address -- a gather writes a zero row for it, a scatter skips it.
 template <bool kScatter>
 __global__ void __launch_bounds__(256) move_rows_kernel(uint8_t* __restrict__ out, const uint8_t* __restrict__ in,
                                                         const int64_t* __restrict__ index, int64_t n,
-                                                        int64_t row_bytes) {
+                                                        int64_t row_bytes, int64_t table_rows) {
   const int64_t pieces = row_bytes / 16;
   const int64_t total = n * pieces;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -110,12 +112,12 @@ __global__ void __launch_bounds__(256) move_rows_kernel(uint8_t* __restrict__ ou
     const int64_t r = i / pieces, piece = i - r * pieces;
     const int64_t j = index[r];
     if constexpr (kScatter) {
-      if (j < 0) continue;
+      if (j < 0 || j >= table_rows) continue;
       *reinterpret_cast<uint4*>(out + j * row_bytes + piece * 16) =
           *reinterpret_cast<const uint4*>(in + r * row_bytes + piece * 16);
     } else {
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (j >= 0) v = *reinterpret_cast<const uint4*>(in + j * row_bytes + piece * 16);
+      if (j >= 0 && j < table_rows) v = *reinterpret_cast<const uint4*>(in + j * row_bytes + piece * 16);
       *reinterpret_cast<uint4*>(out + r * row_bytes + piece * 16) = v;
     }
   }
@@ -270,28 +272,30 @@ int oasr_b200_paged_kv_gather(void* k_out, void* v_out, const void* k_pool, cons
 }
 
 int oasr_b200_gather_rows(void* out, const void* in, const int64_t* index, int64_t n_out, int64_t row_bytes,
-                          void* stream) {
+                          int64_t in_rows, void* stream) {
   using namespace ob;
   OB_REQUIRE(out && in && index, OASR_ERR_INVALID, "gather_rows: null pointer argument");
+  OB_REQUIRE(in_rows >= 0, OASR_ERR_INVALID, "gather_rows: negative source row count");
   OB_REQUIRE(n_out >= 0 && row_bytes > 0 && row_bytes % 16 == 0, OASR_ERR_ALIGN,
              "gather_rows: row size must be a positive multiple of 16 bytes (got %lld)", (long long)row_bytes);
   OB_REQUIRE(is_aligned(out, 16) && is_aligned(in, 16), OASR_ERR_ALIGN, "gather_rows: pointers must be 16-byte aligned");
   if (n_out == 0) return OASR_OK;
   move_rows_kernel<false><<<grid_for(n_out * (row_bytes / 16)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint8_t*>(out), static_cast<const uint8_t*>(in), index, n_out, row_bytes);
+      static_cast<uint8_t*>(out), static_cast<const uint8_t*>(in), index, n_out, row_bytes, in_rows);
   return check_launch("gather_rows launch");
 }
 
 int oasr_b200_scatter_rows(void* out, const void* in, const int64_t* index, int64_t n_in, int64_t row_bytes,
-                           void* stream) {
+                           int64_t out_rows, void* stream) {
   using namespace ob;
   OB_REQUIRE(out && in && index, OASR_ERR_INVALID, "scatter_rows: null pointer argument");
+  OB_REQUIRE(out_rows >= 0, OASR_ERR_INVALID, "scatter_rows: negative destination row count");
   OB_REQUIRE(n_in >= 0 && row_bytes > 0 && row_bytes % 16 == 0, OASR_ERR_ALIGN,
              "scatter_rows: row size must be a positive multiple of 16 bytes (got %lld)", (long long)row_bytes);
   OB_REQUIRE(is_aligned(out, 16) && is_aligned(in, 16), OASR_ERR_ALIGN, "scatter_rows: pointers must be 16-byte aligned");
   if (n_in == 0) return OASR_OK;
   move_rows_kernel<true><<<grid_for(n_in * (row_bytes / 16)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint8_t*>(out), static_cast<const uint8_t*>(in), index, n_in, row_bytes);
+      static_cast<uint8_t*>(out), static_cast<const uint8_t*>(in), index, n_in, row_bytes, out_rows);
   return check_launch("scatter_rows launch");
 }
 
