@@ -79,6 +79,17 @@ OASR_API const char* oasr_b200_last_error(void);
  * `stream`.  Returns 0 when no kernel reported a problem, else
  * OASR_ERR_DEVICE_WAIT with the raw word in *word (nullable). */
 OASR_API int oasr_b200_device_status(uint32_t* word /*host*/, void* stream);
+/* Self-test of the bounded-wait path (no reference counterpart): launches one
+ * small CTA in which one role waits, for at most `poll_limit` polls (64 ..
+ * 2^20), on an mbarrier that nothing arrives on, and a second role waits on a
+ * barrier the first would have signalled.  Both must give up, set bit 8
+ * (0x100) of the device status word, release their tensor memory and return;
+ * `report` (device, nullable, zero it first) receives 1 | 2 for the two
+ * roles.  The next oasr_b200_device_status call then returns
+ * OASR_ERR_DEVICE_WAIT and clears the word; kernels launched afterwards run
+ * normally.  Nothing faults or hangs. */
+OASR_API int oasr_b200_selftest_bounded_wait(int64_t poll_limit, uint32_t* report /*device, nullable*/,
+                                             void* stream);
 /* Number of kernels this library has launched in this process so far
  * (host-side counter, one per launch; no reference counterpart). */
 OASR_API unsigned long long oasr_b200_launch_count(void);

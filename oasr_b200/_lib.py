@@ -36,6 +36,7 @@ I = c_int64
 _SIGNATURES = {
     "oasr_b200_device_status": [POINTER(c_uint32), P],
     "oasr_b200_set_tunable": [c_char_p, c_int],
+    "oasr_b200_selftest_bounded_wait": [I, P, P],
     "oasr_b200_layer_norm": [P, P, P, P, I, I, c_double, c_int, P],
     "oasr_b200_layer_norm_activation": [P, P, P, P, I, I, c_double, c_int, c_int, P],
     "oasr_b200_add_layer_norm": [P, P, P, P, P, I, I, c_double, c_double, c_int, P],

@@ -15,6 +15,7 @@ enum : uint32_t {
   kStatusFmhaLoad = 1u << 4,
   kStatusFmhaMma = 1u << 5,
   kStatusFmhaSoftmax = 1u << 6,
+  kStatusSelfTest = 1u << 8,
 };
 
 }  // namespace ob

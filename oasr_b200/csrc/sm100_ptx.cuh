@@ -64,13 +64,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the wait was abandoned (abort flag raised).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1u;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kSpinLimit);
 }
 
 // ---- programmatic dependent launch ---------------------------------------------

@@ -363,10 +363,12 @@ class ConformerCTC:
             self._native_model.pos_proj_rows = self._pos_proj.size(0)
         slots = list(slots)
         B = xs.size(0)
-        table, cached, total, pos_start, slot_ids = cache.prepare(slots)
         T = (((xs.size(1) - 3) // 2 + 1) - 3) // 2 + 1
-        if T != cache.chunk:
+        if T != cache.chunk:      # checked before any page is handed out: a refused call leaves the cache untouched
             raise RuntimeError(f"the feature window gives {T} encoder frames, the cache was built for {cache.chunk}")
+        if len(slots) != B:
+            raise RuntimeError(f"{B} feature windows for {len(slots)} slots")
+        table, cached, total, pos_start, slot_ids = cache.prepare(slots)
         cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=xs.device)
         rows = self._subsample_packed(xs, [T] * B, cu, B * T)                  # (B * chunk, F'*d)
         lib = _lib.load()

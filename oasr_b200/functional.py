@@ -34,6 +34,12 @@ def _p(t: Optional[torch.Tensor]):
 
 
 def _stream(t: torch.Tensor):
+    """The caller's current stream on the tensor's device.  The library launches on the CURRENT device (its SM count,
+    status word and tensor maps are per current device), so a tensor that lives on another GPU is refused here rather
+    than launched against the wrong context."""
+    if t.device.index is not None and t.device.index != torch.cuda.current_device():
+        raise RuntimeError(f"tensor on {t.device} but the current CUDA device is cuda:{torch.cuda.current_device()}: "
+                           f"wrap the call in `with torch.cuda.device({t.device.index}):`")
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 

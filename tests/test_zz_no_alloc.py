@@ -57,3 +57,39 @@ def test_noalloc_entry_point_refuses_oversized_batches():
         # sizes only: the refusal happens before any pointer is used or any kernel is launched
         _lib.call("oasr_b200_conformer_encode_packed_noalloc", ctypes.byref(model._native_model), None, None, None,
                   3, 10 ** 6, 500, None, None, None)
+
+
+def test_noalloc_padded_semantics_and_a_batch_just_under_the_capacity():
+    """The padded-batch form (``fill_frames``) and the largest batch the built-in array can hold: both equal the
+    workspace entry point, and one more row tile is refused."""
+    cfg, model, pk, rows = _setup()
+    want_lp, want_arg = model._encode_packed(rows, pk, True)                # padded semantics
+    lp = torch.full((pk.total, cfg.vocab_padded), float("nan"), device="cuda")
+    arg = torch.full((pk.total,), -1, device="cuda", dtype=torch.int32)
+    model.encode_rows_noalloc(rows, pk, lp, arg, padded_semantics=True)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(lp, want_lp, rtol=0, atol=2e-2)
+    assert (lp - want_lp).abs().max().item() <= 1e-6 and torch.equal(arg, want_arg)
+    # the largest number of 400-frame segments whose scratch still fits
+    lib = _lib.load()
+    cap = lib.oasr_b200_conformer_noalloc_capacity_bytes()
+    seg = 400
+    n = 1
+    while lib.oasr_b200_conformer_workspace_bytes(ctypes.byref(model._native_model), (n + 1) * seg, seg) <= cap:
+        n += 1
+    total = n * seg
+    assert lib.oasr_b200_conformer_workspace_bytes(ctypes.byref(model._native_model), total, seg) > 0.95 * cap
+    big = build_packed_batch([seg] * n, seg, cfg.kernel, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    big_rows = (torch.randn(total, rows.size(1), device="cuda", generator=g) * 0.5).to(rows.dtype)
+    want_lp, want_arg = model._encode_packed(big_rows, big, False)
+    lp = torch.full((total, cfg.vocab_padded), float("nan"), device="cuda")
+    arg = torch.full((total,), -1, device="cuda", dtype=torch.int32)
+    model.encode_rows_noalloc(big_rows, big, lp, arg)
+    torch.cuda.synchronize()
+    assert torch.isfinite(lp).all()
+    torch.testing.assert_close(lp, want_lp, rtol=0, atol=2e-2)
+    assert (lp - want_lp).abs().max().item() <= 1e-6 and torch.equal(arg, want_arg)
+    over = build_packed_batch([seg] * (n + 1), seg, cfg.kernel, "cuda")
+    with pytest.raises(_lib.OasrB200Error, match="bytes of scratch"):
+        model.encode_rows_noalloc(big_rows, over, lp, arg)
