@@ -179,6 +179,26 @@ OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
                                     const void* w_a, const void* b_a, const void* w_b /*mode 2*/,
                                     const void* b_b /*mode 2*/, int64_t rows, int64_t hidden,
                                     double eps, int split_out, int dtype, void* stream);
+/* Linear + residual step + norm in one kernel (no single reference
+ * counterpart: it replaces gemm (csrc/gemm_jit_binding.cu:9-12) followed by
+ * addlayernorm_residual (csrc/norm_jit_binding.cu:18-20, kernel
+ * include/oasr/norm.cuh:396-484) as the layer composes them,
+ * oasr/models/conformer/model.py:722-751):
+ *   y = A[M,K] . B[N,K]^T + bias (fp32, never rounded), s = res_in + alpha*y,
+ * then `mode` / w_a, b_a, w_b, b_b / split_out exactly as oasr_b200_add_norm_f32
+ * (h_out 16-bit [M,N] or [M,3N], res_out fp32 [M,N], may alias res_in).
+ * The output row must fill tensor memory: N = 128, 256 or 512
+ * (oasr_b200_gemm_add_norm_supported); other widths return
+ * OASR_ERR_UNSUPPORTED and the caller composes gemm + add_norm_f32. */
+OASR_API int oasr_b200_gemm_add_norm_f32(void* h_out, float* res_out /*nullable unless mode 2*/,
+                                         const float* res_in /*nullable*/, const void* A,
+                                         const void* B, const void* bias /*nullable*/, int64_t M,
+                                         int64_t N, int64_t K, double alpha, int mode,
+                                         const void* w_a, const void* b_a,
+                                         const void* w_b /*mode 2*/, const void* b_b /*mode 2*/,
+                                         double eps, int split_out, int dtype, void* stream);
+OASR_API int oasr_b200_gemm_add_norm_supported(int64_t N, int64_t K);
+
 /* Inference batch norm over channels-last rows, optional activation
  * (activation = OASR_ACT_NONE for plain BN).  Replaces batchnorm1d,
  * batchnorm_activation and batchnorm_swish (csrc/norm_jit_binding.cu:13,32,35;
@@ -387,7 +407,10 @@ OASR_API int oasr_b200_group_gemm(void* D, const void* A, const void* B, const i
  * the chip.  out_dtype is OASR_DT_F32 or the activation dtype.  Replaces
  * gemm_log_softmax (csrc/gemm_log_softmax_jit_binding.cu:8-11, kernel pair
  * include/oasr/gemm/gemm_log_softmax.cuh:124-166).  `argmax` (nullable,
- * int32[M]) receives the index of the first maximum of each row. */
+ * int32[M]) receives the index of the first maximum of each row.  With
+ * out == NULL and argmax != NULL only that index is produced (the input of a
+ * greedy CTC search, oasr/functionals/ctc_decode.py:359): one sweep over the
+ * vocabulary and 4 bytes written per row instead of the N log-probs. */
 OASR_API int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B,
                                         const void* bias /*nullable*/, int64_t M, int64_t N,
                                         int64_t K, int dtype, int out_dtype,

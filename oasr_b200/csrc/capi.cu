@@ -61,6 +61,7 @@ extern int g_dw_path;
 extern int g_fmha_relpos_path;
 int g_pdl = 0;  // measured neutral on both workloads (offline 7.32 vs 7.36 ms, streaming 3.79 vs 3.71 ms per step): off by default
 extern int g_fmha_chunk_path;
+extern int g_fused_addnorm;
 
 }  // namespace ob
 
@@ -92,6 +93,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   if (name && std::strcmp(name, "pdl") == 0) {
     ob::g_pdl = value != 0;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "fused_addnorm") == 0) {
+    ob::g_fused_addnorm = value != 0;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "dwconv_path") == 0) {

@@ -67,6 +67,11 @@ struct ProfRecord {
   cudaEvent_t a, b;
 };
 bool g_prof_on = false;
+}  // namespace
+// 1 (default): the last Linear of every sub-layer runs fused with the residual add and the following norm
+// (oasr_b200_gemm_add_norm_f32) where the model width allows it; 0: gemm + add_norm_f32 as two kernels.
+int g_fused_addnorm = 1;
+namespace {
 std::vector<ProfRecord> g_prof;
 
 // Scratch of oasr_b200_conformer_encode_packed_noalloc: lives in the library image, so every GPU
@@ -196,6 +201,28 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
       OB_STEP("gemm_q8 " label, fl, oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, M, N, K, act, glu, qk, dt, stream)); \
     }                                                                                                               \
   } while (0)
+  // Last Linear of a sub-layer + residual step + norm: one fused kernel where the width allows it (16-bit GEMMs),
+  // else the Linear into w.y followed by add_norm_f32.  `rin` is the residual input (null for the embed).
+  const bool fuse = qk == 0 && g_fused_addnorm != 0 && oasr_b200_gemm_add_norm_supported(d, d) != 0;
+#define OB_LINEAR_ADDNORM(label, fl, hout, rin, in, wt, bs, lay, qi, K, alpha, mode, wa, ba, wb, bb, eps_, split)       \
+  do {                                                                                                              \
+    if (fuse && oasr_b200_gemm_add_norm_supported(d, K)) {                                                          \
+      OB_STEP("gemm_addnorm " label, fl, oasr_b200_gemm_add_norm_f32(hout, w.res, rin, in, wt, bs, M, d, K, alpha, mode, wa, ba, \
+                                                                    wb, bb, eps_, split, dt, stream));              \
+    } else {                                                                                                        \
+      OB_LINEAR(label, fl, w.y, in, wt, bs, lay, qi, d, K, OASR_ACT_NONE, 0);                                        \
+      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(hout, w.res, rin, w.y, alpha, mode, wa, ba, wb, bb, M, d, eps_, split, dt, stream)); \
+    }                                                                                                               \
+  } while (0)
+  if (fuse && oasr_b200_gemm_add_norm_supported(d, m.embed_in)) {
+    if (m.embed_ln_w) {
+      OB_STEP("gemm_addnorm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_add_norm_f32(w.h, w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, 2,
+                                     m.embed_ln_w, m.embed_ln_b, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, 1e-5, 0, dt, stream));
+    } else {
+      OB_STEP("gemm_addnorm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_add_norm_f32(w.h, w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, 0,
+                                     ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, nullptr, nullptr, m.eps, 0, dt, stream));
+    }
+  } else {
   OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm(w.y, rows, m.embed_w, m.embed_b, M, d, m.embed_in, OASR_ACT_NONE, dt, stream));
   if (m.embed_ln_w) {
     OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 2, m.embed_ln_w, m.embed_ln_b,
@@ -204,6 +231,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
     OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b,
                                    nullptr, nullptr, M, d, m.eps, 0, dt, stream));
   }
+  }
   // linear_pos of every layer in one GEMM: (max_seg, d) x (L*d, d)^T
   OB_STEP("gemm linear_pos", 2.0 * max_seg * L * d * d, oasr_b200_gemm(w.pos, m.pe, m.pos_w_all, nullptr, max_seg, L * d, d, OASR_ACT_NONE, dt, stream));
 
@@ -211,36 +239,32 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
     const oasr_b200_conformer_layer& l = ly[i];
     // macaron feed-forward
     OB_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, l, 0, m.ffn, d, OASR_ACT_SWISH, 0);
-    OB_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, d, m.ffn, OASR_ACT_NONE, 0);
-    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
-                                   m.eps, 0, dt, stream));
+    OB_LINEAR_ADDNORM("ffn_w2", 2.0 * M * m.ffn * d, w.h, w.res, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, m.ffn, 0.5, 0, l.norm_mha_w,
+                      l.norm_mha_b, nullptr, nullptr, m.eps, 0);
     // relative-position self-attention
     OB_LINEAR("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, d, OASR_ACT_NONE, 0);
     OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs, max_seg,
                                          M, m.heads, scale, dt, stream));
-    OB_LINEAR("attn_out", 2.0 * M * d * d, w.y, w.att, l.out_w, l.out_b, l, 3, d, d, OASR_ACT_NONE, 0);
-    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
-                                   nullptr, M, d, m.eps, 0, dt, stream));
+    OB_LINEAR_ADDNORM("attn_out", 2.0 * M * d * d, w.h, w.res, w.att, l.out_w, l.out_b, l, 3, d, 1.0, 1, l.norm_conv_scale,
+                      l.norm_conv_shift, nullptr, nullptr, m.eps, 0);
     // convolution module
     OB_LINEAR("pw1", 2.0 * M * 2 * d * d, w.g, w.h, l.pw1_w, l.pw1_b, l, 4, d, d, OASR_ACT_NONE, 1);
     OB_STEP("depthwise_conv1d_packed", 0, oasr_b200_depthwise_conv1d_packed(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
                                               fill_frames ? l.glu_of_bias : nullptr, fill_frames, cu_seqlens, num_segs,
                                               max_seg, d, m.kernel, OASR_ACT_SWISH, dt, stream));
-    OB_LINEAR("pw2", 2.0 * M * d * d, w.y, w.cv, l.pw2_w, l.pw2_b, l, 5, d, d, OASR_ACT_NONE, 0);
-    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, M, d,
-                                   m.eps, 0, dt, stream));
+    OB_LINEAR_ADDNORM("pw2", 2.0 * M * d * d, w.h, w.res, w.cv, l.pw2_w, l.pw2_b, l, 5, d, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr,
+                      nullptr, m.eps, 0);
     // feed-forward, norm_final, then the next layer's first pre-norm (or after_norm, split for the head)
     OB_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ff_w1, l.ff_b1, l, 6, m.ffn, d, OASR_ACT_SWISH, 0);
-    OB_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, d, m.ffn, OASR_ACT_NONE, 0);
     if (i + 1 < L) {
-      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b,
-                                     ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, M, d, m.eps, 0, dt, stream));
+      OB_LINEAR_ADDNORM("ffn_w2", 2.0 * M * m.ffn * d, w.h, w.res, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, m.ffn, 0.5, 2, l.norm_final_w,
+                        l.norm_final_b, ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, m.eps, 0);
     } else {
-      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h3, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b, m.after_norm_w,
-                                     m.after_norm_b, M, d, m.eps, 1, dt, stream));
+      OB_LINEAR_ADDNORM("ffn_w2", 2.0 * M * m.ffn * d, w.h3, w.res, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, m.ffn, 0.5, 2, l.norm_final_w,
+                        l.norm_final_b, m.after_norm_w, m.after_norm_b, m.eps, 1);
     }
   }
-  if (log_probs) {
+  if (log_probs || argmax) {   // log_probs == NULL: token-only head, one vocabulary sweep, no log-prob write
     OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued at split precision (K = 3d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
                                        argmax, stream));
   }
@@ -397,7 +421,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
                                      m.after_norm_b, M, d, m.eps, 1, dt, stream));
     }
   }
-  if (log_probs) {
+  if (log_probs || argmax) {   // log_probs == NULL: token-only head, one vocabulary sweep, no log-prob write
     OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued at split precision (K = 3d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
                                        argmax, stream));
   }

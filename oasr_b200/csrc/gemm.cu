@@ -54,6 +54,7 @@ struct Params {
   float alpha;
   int act;
   int out_f32;            // kEpiLsm: 1 = fp32 output, 0 = T output
+  int lsm_passes;         // kEpiLsm: 2 = statistics sweep + normalised-output sweep; 1 = statistics only (argmax, no output)
   int32_t* argmax;        // kEpiLsm: nullable
   uint32_t* status;       // device status word (nullable)
   // kSchedConv (3x3 / stride-2 convolution as an implicit GEMM over a parity-split NHWC input):
@@ -88,7 +89,7 @@ struct Scheduler {
       const uint32_t total = static_cast<uint32_t>(p.num_m_tiles) * p.num_n_tiles * p.batch;
       return first + static_cast<uint32_t>(iter) * ctas < total;
     } else if constexpr (kSched == kSchedSweep) {
-      return blockIdx.x + static_cast<uint32_t>(iter / (2 * p.num_n_tiles)) * gridDim.x < static_cast<uint32_t>(p.num_m_tiles);
+      return blockIdx.x + static_cast<uint32_t>(iter / (p.lsm_passes * p.num_n_tiles)) * gridDim.x < static_cast<uint32_t>(p.num_m_tiles);
     } else {
       Tile t;
       return get(iter, t);
@@ -172,7 +173,7 @@ struct Scheduler {
       }
       return false;
     } else {
-      const int per_row_tile = 2 * p.num_n_tiles;
+      const int per_row_tile = p.lsm_passes * p.num_n_tiles;
       const int64_t m = blockIdx.x + static_cast<int64_t>(iter / per_row_tile) * gridDim.x;
       if (m >= p.num_m_tiles) return false;
       const int sub = iter % per_row_tile;
@@ -1098,7 +1099,7 @@ int run_typed(Problem& pr, int dtype, cudaStream_t s) {
   p.num_k_blocks = static_cast<int>((pr.K + BK - 1) / BK);
   CUtensorMap ta, tb, td;
   if (int rc = make_maps<T>(pr, bn, dtype, &ta, &tb, pair)) return rc;
-  if (uses_tma_store<kSched, kEpi>()) {
+  if (uses_tma_store<kSched, kEpi>() && p.D != nullptr) {
     // output (N, M, batch): one 128-row x 128-byte box per store
     const bool f32 = kEpi == kEpiLsm && p.out_f32;
     const uint64_t es = f32 ? 4 : 2;
@@ -1404,7 +1405,10 @@ int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B, const vo
                                int64_t K, int dtype, int out_dtype, int32_t* argmax, void* stream) {
   using namespace ob;
   using namespace ob::gemm;
-  if (int rc = validate_common("gemm_log_softmax", out, A, B, bias, M, N, K)) return rc;
+  // out == NULL with argmax != NULL: only the per-row index of the first maximum is wanted (greedy CTC search);
+  // one sweep over the vocabulary, nothing but 4 bytes per row is written
+  const bool tokens_only = out == nullptr && argmax != nullptr;
+  if (int rc = validate_common("gemm_log_softmax", tokens_only ? static_cast<const void*>(A) : out, A, B, bias, M, N, K)) return rc;
   OB_REQUIRE(out_dtype == OASR_DT_F32 || out_dtype == dtype, OASR_ERR_DTYPE,
              "gemm_log_softmax: out dtype must be fp32 or the activation dtype");
   if (M == 0) return OASR_OK;
@@ -1412,7 +1416,7 @@ int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B, const vo
   // written normalised) and never writes logits; it keeps one CTA per row tile, so it needs about as many row tiles
   // as SMs.  The split form writes fp32 logits into `out` with the dense scheduler (every SM busy at any M) and
   // normalises the rows in place: one GEMM instead of two for a second pass over the output.
-  const bool split_ok = out_dtype == OASR_DT_F32 && !use_simt(M, N, K);
+  const bool split_ok = out_dtype == OASR_DT_F32 && !use_simt(M, N, K) && !tokens_only;
   const bool split = split_ok && (g_lsm_path == 2 || (g_lsm_path == 0 && lsm_split_wins(M, N, K)));
   if (split) {
     Problem pg{};
@@ -1432,6 +1436,7 @@ int oasr_b200_gemm_log_softmax(void* out, const void* A, const void* B, const vo
   pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
   pr.p.D = out; pr.p.bias = bias; pr.p.act = OASR_ACT_NONE; pr.p.alpha = 1.f;
   pr.p.out_f32 = out_dtype == OASR_DT_F32 ? 1 : 0;
+  pr.p.lsm_passes = tokens_only ? 1 : 2;
   pr.p.argmax = argmax;
   return run<kSchedSweep, kEpiLsm>(pr, dtype, static_cast<cudaStream_t>(stream));
 }

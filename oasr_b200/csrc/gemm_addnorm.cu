@@ -1,0 +1,611 @@
+// Linear + residual add + LayerNorm in ONE kernel for the residual-stream steps of the encoder layer:
+//
+//   y = A[M,K] . B[N,K]^T + bias            (16-bit operands, fp32 accumulate, never rounded)
+//   s = res_in + alpha * y                  (fp32 residual stream; res_in nullable)
+//   mode 0:  res_out = s,        h = LN_a(s)
+//   mode 1:  res_out = s,        h = s * w_a + b_a          (fp32 per-channel scale/shift: a folded BatchNorm)
+//   mode 2:  res_out = LN_a(s),  h = LN_b(res_out)          (optionally h as [hi | hi | lo], 3N wide)
+//
+// It replaces a GEMM launch, the 16-bit round trip of y through HBM and an add+norm launch
+// (ConformerEncoderLayer.forward_packed: `x = residual + alpha * sub(x); x = norm(x)`,
+// oasr/models/conformer/model.py:722-751; fused reference form include/oasr/norm.cuh:396-484).
+//
+// Shape of the kernel.  The whole output row must sit in one CTA for the row statistics, so a CTA
+// owns 128 rows x N columns (N = 128, 256 or 512 = the fp32 columns of tensor memory).  Two CTAs of
+// a cluster form a pair that computes 256 rows with tcgen05 cta_group::2: each CTA stages its own
+// 128 rows of A and HALF of the B rows of every instruction, so per flop a CTA writes and reads
+// half the B bytes in shared memory -- at K = 512 shared-memory bandwidth, not the tensor pipe, is
+// what limits a single-CTA 128 x 256 tile.  No multicast: every CTA loads its own bytes.
+//   warp 0   TMA producer (A tile + its B rows per 64-wide K block, kStages-deep ring)
+//   warp 1   MMA issuer (leader CTA only; N/256 instructions of N<=256 per K16 step) + TMEM owner
+//   warps 2-5  epilogue, thread = output row (tcgen05.ld 32x32b: lane = row):
+//     pass 1  s = res + alpha*(acc + bias) per 32-column chunk; the residual chunk arrives by TMA into a
+//             swizzled per-warp buffer (prefetched two chunks ahead, the first two under the main loop),
+//             s goes back to the same buffer and out by TMA store, and back into the accumulator's own
+//             TMEM columns; running sums for mean / variance about the row's first value
+//     pass 2  re-reads s from TMEM, normalises, rounds once, stages 32 x 32 pieces (64-byte swizzle) and
+//             TMA-stores them (mode 2: writes LN_a(s) as fp32 instead, keeps it in TMEM, pass 3 stores h)
+// Every wait is bounded (mbar_wait); on give-up the CTA drains and raises the device status word.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "device_status.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.cuh"
+
+namespace ob {
+namespace gan {
+
+constexpr int BM = 128;      // rows per CTA (= TMEM lanes)
+constexpr int BK = 64;       // K elements per stage (128-byte rows)
+constexpr int UMMA_K = 16;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kChunk = 32;   // columns per epilogue step
+constexpr int kF32Bufs = 4;  // per warp: 32 rows x 32 fp32 (4 KB each), residual in / out staging
+constexpr int kHBufs = 2;    // per warp: 32 rows x 32 16-bit (2 KB each), h staging
+
+struct Params {
+  int M, N, K;
+  int num_k_blocks;
+  int num_pairs;           // 256-row tiles
+  const void* bias;        // T[N], nullable
+  float alpha;
+  int mode;                // 0, 1, 2 as above
+  int split_out;           // mode 2: h rows are [hi | hi | lo]
+  int has_res_in;
+  int has_res_out;
+  const void *w_a, *b_a;   // T[N] (mode 1: float[N])
+  const void *w_b, *b_b;   // T[N], mode 2
+  float eps;
+  uint32_t* status;
+};
+
+template <int N, int kStages>
+struct Smem {
+  static constexpr int kHalves = N > 256 ? N / 256 : 1;     // MMA instructions per K16 step
+  static constexpr int kNI = N / kHalves;                   // N of one instruction (pair-wide)
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBHalfBytes = (kNI / 2) * BK * 2;    // this CTA's B rows of one instruction
+  static constexpr int kBBytes = kHalves * kBHalfBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kRing = kStages * kStageBytes;
+  static constexpr int kWarpEpi = kF32Bufs * 4096 + kHBufs * 2048;
+  static constexpr int kEpiOffset = kRing;
+  static constexpr int kBarOffset = kEpiOffset + kEpiWarps * kWarpEpi;
+  static constexpr int kNumBars = 2 * kStages + 2 + kEpiWarps * kF32Bufs;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+__device__ __forceinline__ float u2f(uint32_t u) { return __uint_as_float(u); }
+__device__ __forceinline__ uint32_t f2u(float f) { return __float_as_uint(f); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 32 consecutive parameters (16-bit or fp32) starting at p as floats; warp-uniform addresses (broadcast loads).
+template <typename P>
+__device__ __forceinline__ void load_params32(const P* p, float (&f)[32]) {
+  if constexpr (std::is_same<P, float>::value) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
+      f[4 * i] = v.x; f[4 * i + 1] = v.y; f[4 * i + 2] = v.z; f[4 * i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      Pack<P> v = ld128_nc(p + 8 * i);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[8 * i + j] = Elem<P>::to_f(v.v[j]);
+    }
+  }
+}
+
+// TMA load of a 2-D fp32 box into this CTA's shared memory (used for the residual chunks).
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  ptx::tma_load_3d(dst, map, c0, c1, 0, bar);
+}
+
+template <typename T, int N, int kStages>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_rin, const __grid_constant__ CUtensorMap tmap_rout,
+                    const __grid_constant__ CUtensorMap tmap_h, const Params p) {
+  using S = Smem<N, kStages>;
+  constexpr int kHalves = S::kHalves;
+  constexpr int kNI = S::kNI;
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr uint32_t kIdesc = ptx::umma_idesc_f16(kBf16, 2 * BM, kNI);
+  constexpr uint32_t kTmemCols = N;              // 128, 256 or 512: a power of two >= 32
+  constexpr int kChunks = N / kChunk;
+  const uint32_t cta_rank = ptx::cluster_ctarank();
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kStages * S::kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 1;
+  uint64_t* rin_bar = tempty_bar + 1;            // [kEpiWarps][kF32Bufs]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rin_bar + kEpiWarps * kF32Bufs);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&full_bar[i], 1);
+      ptx::mbar_init(&empty_bar[i], 1);
+    }
+    ptx::mbar_init(tfull_bar, 1);
+    ptx::mbar_init(tempty_bar, kEpiWarps * 2);   // the leader waits for both CTAs' epilogue warps
+    for (int i = 0; i < kEpiWarps * kF32Bufs; ++i) ptx::mbar_init(&rin_bar[i], 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_rin);
+    ptx::prefetch_tensormap(&tmap_rout);
+    ptx::prefetch_tensormap(&tmap_h);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before_sync();
+  ptx::cluster_sync();                           // the peer's barriers exist before anything targets them
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
+
+  const int num_clusters = static_cast<int>(gridDim.x >> 1);
+  const int first_pair = static_cast<int>(blockIdx.x >> 1);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int pair = first_pair; ok && pair < p.num_pairs; pair += num_clusters) {
+        const int a_row = pair * 2 * BM + static_cast<int>(cta_rank) * BM;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          // both CTAs' bytes are credited to the leader's barrier; only the leader arrives on it
+          const uint32_t lead_full = ptx::map_to_cta(&full_bar[stage], 0);
+          if (cta_rank == 0) ptx::mbar_expect_tx(&full_bar[stage], 2 * S::kStageBytes);
+          ptx::tma_load_3d_pair(sA + stage * S::kABytes, &tmap_a, kb * BK, a_row, 0, lead_full);
+#pragma unroll
+          for (int j = 0; j < kHalves; ++j) {
+            // instruction j covers output columns [j*kNI, (j+1)*kNI): this CTA supplies rows rank*kNI/2 .. of them
+            ptx::tma_load_3d_pair(sB + stage * S::kBBytes + j * S::kBHalfBytes, &tmap_b, kb * BK,
+                                  j * kNI + static_cast<int>(cta_rank) * (kNI / 2), 0, lead_full);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && p.status) atomicOr(p.status, kStatusGemmProducer);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA) -------------------
+    if (lane == 0 && cta_rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int pair = first_pair; ok && pair < p.num_pairs; pair += num_clusters) {
+        if (!ptx::mbar_wait(tempty_bar, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(sA + stage * S::kABytes);
+          const uint32_t b_addr = ptx::smem_u32(sB + stage * S::kBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = ptx::smem_desc_kmajor_sw128(a_addr + k * UMMA_K * 2);
+#pragma unroll
+            for (int j = 0; j < kHalves; ++j) {
+              const uint64_t bdesc = ptx::smem_desc_kmajor_sw128(b_addr + j * S::kBHalfBytes + k * UMMA_K * 2);
+              ptx::umma_f16_pair(tmem_base + j * kNI, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            }
+          }
+          ptx::umma_commit_pair(&empty_bar[stage], 3);    // frees the stage in both CTAs
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::umma_commit_pair(tfull_bar, 3);      // the accumulators of both CTAs are complete
+        acc_phase ^= 1u;
+      }
+      if (!ok && p.status) atomicOr(p.status, kStatusGemmMma);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue: thread = output row ---------------
+    const int ew = warp - 2;                       // epilogue warp index 0..3
+    const int q = warp & 3;                        // TMEM lane quarter this warp may access
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    uint8_t* my_smem = smem + S::kEpiOffset + ew * S::kWarpEpi;
+    uint8_t* fbuf = my_smem;                       // kF32Bufs x 4 KB, 128-byte swizzle (1024-byte aligned)
+    uint8_t* hbuf = my_smem + kF32Bufs * 4096;     // kHBufs x 2 KB, 64-byte swizzle
+    uint64_t* my_rin = rin_bar + ew * kF32Bufs;
+    uint32_t rin_phase = 0;                        // bit b = parity of the next completion of buffer b
+    uint32_t tfull_phase = 0;
+    bool ok = true;
+    const T* bias = static_cast<const T*>(p.bias);
+    const int sw128 = lane & 7;                    // chunk XOR of this thread's row in a 128-byte-swizzled buffer
+    const int sw64 = (lane >> 1) & 3;              // same for the 64-byte-swizzled h buffers
+
+    // this thread's 32 fp32 of buffer b (its row, swizzled)
+    auto f32_row_load = [&](int b, float (&v)[32]) {
+      const uint8_t* row = fbuf + b * 4096 + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 t = *reinterpret_cast<const float4*>(row + ((j ^ sw128) << 4));
+        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+      }
+    };
+    auto f32_row_store = [&](int b, const float (&v)[32]) {
+      uint8_t* row = fbuf + b * 4096 + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(row + ((j ^ sw128) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    };
+    // 32 values rounded to T into h buffer b (this thread's 64-byte row)
+    auto h_row_store = [&](int b, const float (&v)[32]) {
+      uint8_t* row = hbuf + b * 2048 + lane * 64;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(row + ((c ^ sw64) << 4)) =
+            make_uint4(pack2<T>(v[8 * c], v[8 * c + 1]), pack2<T>(v[8 * c + 2], v[8 * c + 3]),
+                       pack2<T>(v[8 * c + 4], v[8 * c + 5]), pack2<T>(v[8 * c + 6], v[8 * c + 7]));
+      }
+    };
+
+    for (int pair = first_pair; ok && pair < p.num_pairs; pair += num_clusters) {
+      const int row0 = pair * 2 * BM + static_cast<int>(cta_rank) * BM + q * 32;   // first row of this warp
+      const bool warp_live = row0 < p.M;           // a warp wholly past M neither loads nor stores (TMA clips partial ones)
+      const uint32_t t_acc = tmem_base + lane_base;
+
+      // residual prefetch for chunks 0 and 1: lands under the main loop
+      auto rin_issue = [&](int c) {
+        if (p.has_res_in && warp_live && lane == 0) {
+          const int b = c % kF32Bufs;
+          ptx::mbar_expect_tx(&my_rin[b], 4096);
+          tma_load_box(fbuf + b * 4096, &tmap_rin, c * kChunk, row0, &my_rin[b]);
+        }
+      };
+      // all earlier TMA stores of this warp have finished reading shared memory (buffers of the previous tile)
+      if (lane == 0) ptx::bulk_wait_group_read<0>();
+      __syncwarp();
+      rin_issue(0);
+      if (kChunks > 1) rin_issue(1);
+
+      if (!ptx::mbar_wait(tfull_bar, tfull_phase, abort_flag)) { ok = false; break; }
+      tfull_phase ^= 1u;
+      ptx::tc_fence_after_sync();
+
+      // ---------------- pass 1: s = res + alpha * (acc + bias), statistics about the first value ----------------
+      float pivot = 0.f, sum = 0.f, sq = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kChunks; ++c) {
+        const int b = c % kF32Bufs;
+        // the buffer chunk c+2 will land in was last stored from by chunk c-2: all but the latest store have been read
+        if (lane == 0) ptx::bulk_wait_group_read<1>();
+        __syncwarp();
+        if (c + 2 < kChunks) rin_issue(c + 2);
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
+        float s[32];
+        if (p.has_res_in && warp_live) {
+          if (!ptx::mbar_wait(&my_rin[b], (rin_phase >> b) & 1u, abort_flag)) { ok = false; break; }
+          rin_phase ^= 1u << b;
+          f32_row_load(b, s);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = 0.f;
+        }
+        ptx::tmem_ld_wait();
+        if (bias) {
+          float bb[32];
+          load_params32(bias + c * kChunk, bb);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = fmaf(p.alpha, u2f(r[i]) + bb[i], s[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = fmaf(p.alpha, u2f(r[i]), s[i]);
+        }
+        if (p.mode == 1) {
+          // affine pre-norm: no statistics, h leaves in this pass
+          float sc[32], sh[32], o[32];
+          load_params32(static_cast<const float*>(p.w_a) + c * kChunk, sc);
+          load_params32(static_cast<const float*>(p.b_a) + c * kChunk, sh);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = fmaf(s[i], sc[i], sh[i]);
+          h_row_store(c % kHBufs, o);
+        } else {
+          if (c == 0) pivot = s[0];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float d = s[i] - pivot;
+            sum += d;
+            sq = fmaf(d, d, sq);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = f2u(s[i]);
+          ptx::tmem_st_32x32(t_acc + c * kChunk, r);
+        }
+        const bool store_res = p.has_res_out && p.mode != 2;
+        if (store_res) f32_row_store(b, s);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && warp_live) {
+          if (store_res) ptx::tma_store_3d(&tmap_rout, fbuf + b * 4096, c * kChunk, row0, 0);
+          if (p.mode == 1) ptx::tma_store_3d(&tmap_h, hbuf + (c % kHBufs) * 2048, c * kChunk, row0, 0);
+        }
+        if (lane == 0) ptx::bulk_commit_group();   // one group per chunk (possibly empty) keeps the wait counts uniform
+      }
+      if (!ok) break;
+
+      if (p.mode != 1) {
+        const float inv_n = 1.f / static_cast<float>(N);
+        ptx::tmem_st_wait();                       // pass 1's writes of s are in TMEM before anything reads them back
+        // LayerNorm of the row held in TMEM: mean / rstd from the sums about the pivot, then gamma / beta.
+        float mean = pivot + sum * inv_n;
+        float rstd = rsqrtf(fmaxf(sq * inv_n - (sum * inv_n) * (sum * inv_n), 0.f) + p.eps);
+        const T* g1 = static_cast<const T*>(p.w_a);
+        const T* b1 = static_cast<const T*>(p.b_a);
+        if (p.mode == 2) {
+          // ---------------- pass 2 (mode 2): res_out = LN_a(s), kept in TMEM, statistics of it ----------------
+          float pivot2 = 0.f, sum2 = 0.f, sq2 = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < kChunks; ++c) {
+            const int b = c % kF32Bufs;
+            if (lane == 0) ptx::bulk_wait_group_read<1>();
+            __syncwarp();
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
+            float gg[32], bb[32], v[32];
+            load_params32(g1 + c * kChunk, gg);
+            load_params32(b1 + c * kChunk, bb);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = fmaf((u2f(r[i]) - mean) * rstd, gg[i], bb[i]);
+            if (c == 0) pivot2 = v[0];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float d = v[i] - pivot2;
+              sum2 += d;
+              sq2 = fmaf(d, d, sq2);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = f2u(v[i]);
+            ptx::tmem_st_32x32(t_acc + c * kChunk, r);
+            if (p.has_res_out) f32_row_store(b, v);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (p.has_res_out && warp_live) ptx::tma_store_3d(&tmap_rout, fbuf + b * 4096, c * kChunk, row0, 0);
+              ptx::bulk_commit_group();
+            }
+          }
+          mean = pivot2 + sum2 * inv_n;
+          rstd = rsqrtf(fmaxf(sq2 * inv_n - (sum2 * inv_n) * (sum2 * inv_n), 0.f) + p.eps);
+          g1 = static_cast<const T*>(p.w_b);
+          b1 = static_cast<const T*>(p.b_b);
+        }
+        ptx::tmem_st_wait();
+        // ---------------- last pass: h = LN(row in TMEM), rounded once, 32 x 32 pieces out by TMA ----------------
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          if (lane == 0) {
+            if (p.split_out) ptx::bulk_wait_group_read<0>();
+            else ptx::bulk_wait_group_read<1>();
+          }
+          __syncwarp();
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
+          float gg[32], bb[32], v[32];
+          load_params32(g1 + c * kChunk, gg);
+          load_params32(b1 + c * kChunk, bb);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaf((u2f(r[i]) - mean) * rstd, gg[i], bb[i]);
+          if (p.split_out) {
+            // h = hi + lo with hi = round16(h), lo = round16(h - hi): rows [hi | hi | lo] of a 3N-wide output
+            float lo[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float hi = Elem<T>::to_f(Elem<T>::from_f(v[i]));
+              lo[i] = v[i] - hi;
+            }
+            h_row_store(0, v);
+            h_row_store(1, lo);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (warp_live) {
+                ptx::tma_store_3d(&tmap_h, hbuf, c * kChunk, row0, 0);
+                ptx::tma_store_3d(&tmap_h, hbuf, N + c * kChunk, row0, 0);
+                ptx::tma_store_3d(&tmap_h, hbuf + 2048, 2 * N + c * kChunk, row0, 0);
+              }
+              ptx::bulk_commit_group();
+            }
+          } else {
+            const int hb = c % kHBufs;
+            h_row_store(hb, v);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (warp_live) ptx::tma_store_3d(&tmap_h, hbuf + hb * 2048, c * kChunk, row0, 0);
+              ptx::bulk_commit_group();
+            }
+          }
+        }
+      }
+      // the accumulator columns are free again: tell the leader's MMA issuer
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar, 0));
+    }
+    if (lane == 0) ptx::bulk_wait_group<0>();      // every output piece has left shared memory and landed
+    if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusGemmEpilogue);
+  }
+
+  // Teardown.  After an abandoned wait, give copies that may still be in flight time to land before shared
+  // memory and TMEM are released.  Neither CTA may leave while the leader's MMAs can still read the peer's
+  // shared memory or the peer can still arrive on the leader's barriers.
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  ptx::tc_fence_before_sync();
+  ptx::cluster_sync();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <int N> struct StagesFor;
+template <> struct StagesFor<512> { static constexpr int v = 3; };   // 48 KB per stage + 80 KB of epilogue staging
+template <> struct StagesFor<256> { static constexpr int v = 4; };   // 32 KB per stage
+template <> struct StagesFor<128> { static constexpr int v = 4; };   // 24 KB per stage
+
+struct Call {
+  void* h_out;
+  float* res_out;
+  const float* res_in;
+  const void *A, *B;
+  int64_t M, N, K;
+  int dtype;
+  Params p;
+};
+
+template <typename T, int N>
+int launch(const Call& c, cudaStream_t s) {
+  constexpr int kStages = StagesFor<N>::v;
+  using S = Smem<N, kStages>;
+  static_assert(S::kDynamic <= 232448, "shared memory budget of one CTA");
+  auto kern = gemm_addnorm_kernel<T, N, kStages>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+    if (e != cudaSuccess) return set_error(OASR_ERR_CUDA, "gemm_add_norm_f32: cannot reserve %d bytes of shared memory: %s",
+                                           S::kDynamic, cudaGetErrorString(e));
+    attr_done = true;
+  }
+  CUtensorMap ta, tb, trin, trout, th;
+  const uint64_t M = static_cast<uint64_t>(c.M), K = static_cast<uint64_t>(c.K);
+  {
+    uint64_t dims[3] = {K, M, 1};
+    uint64_t str[3] = {0, K * 2, K * 2 * M};
+    uint32_t box[3] = {BK, BM, 1};
+    if (int rc = make_tensor_map(&ta, tma_dtype(c.dtype), 3, c.A, dims, str, box)) return rc;
+  }
+  {
+    uint64_t dims[3] = {K, static_cast<uint64_t>(N), 1};
+    uint64_t str[3] = {0, K * 2, K * 2 * N};
+    uint32_t box[3] = {BK, static_cast<uint32_t>(S::kNI / 2), 1};
+    if (int rc = make_tensor_map(&tb, tma_dtype(c.dtype), 3, c.B, dims, str, box)) return rc;
+  }
+  {
+    uint64_t dims[3] = {static_cast<uint64_t>(N), M, 1};
+    uint64_t str[3] = {0, static_cast<uint64_t>(N) * 4, static_cast<uint64_t>(N) * 4 * M};
+    uint32_t box[3] = {kChunk, 32, 1};
+    const void* rin = c.res_in ? static_cast<const void*>(c.res_in) : static_cast<const void*>(c.res_out);
+    const void* rout = c.res_out ? static_cast<const void*>(c.res_out) : rin;
+    if (rin == nullptr) {   // neither residual operand: the maps are never used, but they must be valid objects
+      trin = ta;
+      trout = ta;
+    } else {
+      if (int rc = make_tensor_map(&trin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, rin, dims, str, box)) return rc;
+      if (int rc = make_tensor_map(&trout, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, rout, dims, str, box)) return rc;
+    }
+  }
+  {
+    const uint64_t w = static_cast<uint64_t>(N) * (c.p.split_out ? 3 : 1);
+    uint64_t dims[3] = {w, M, 1};
+    uint64_t str[3] = {0, w * 2, w * 2 * M};
+    uint32_t box[3] = {kChunk, 32, 1};
+    if (int rc = make_tensor_map(&th, tma_dtype(c.dtype), 3, c.h_out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
+  }
+  int64_t clusters = sm_count() / 2;
+  if (c.p.num_pairs < clusters) clusters = c.p.num_pairs;
+  if (clusters < 1) clusters = 1;
+  kern<<<static_cast<unsigned>(2 * clusters), kThreads, S::kDynamic, s>>>(ta, tb, trin, trout, th, c.p);
+  return check_launch("gemm_add_norm_f32 launch");
+}
+
+}  // namespace gan
+}  // namespace ob
+
+extern "C" {
+
+int oasr_b200_gemm_add_norm_supported(int64_t N, int64_t K) {
+  return (N == 128 || N == 256 || N == 512) && K >= 64 && K % 8 == 0 ? 1 : 0;
+}
+
+int oasr_b200_gemm_add_norm_f32(void* h_out, float* res_out, const float* res_in, const void* A, const void* B,
+                                const void* bias, int64_t M, int64_t N, int64_t K, double alpha, int mode,
+                                const void* w_a, const void* b_a, const void* w_b, const void* b_b, double eps,
+                                int split_out, int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gan;
+  OB_REQUIRE(M >= 0 && N > 0 && K > 0, OASR_ERR_INVALID, "gemm_add_norm_f32: bad shape M=%lld N=%lld K=%lld", (long long)M,
+             (long long)N, (long long)K);
+  if (M == 0) return OASR_OK;
+  OB_REQUIRE(oasr_b200_gemm_add_norm_supported(N, K), OASR_ERR_UNSUPPORTED,
+             "gemm_add_norm_f32: the output row must fill tensor memory exactly (N = 128, 256 or 512) and K must be a "
+             "multiple of 8, at least 64 (got N=%lld K=%lld); use gemm + add_norm_f32 for other widths",
+             (long long)N, (long long)K);
+  OB_REQUIRE(h_out && A && B && w_a && b_a, OASR_ERR_INVALID, "gemm_add_norm_f32: null pointer argument");
+  OB_REQUIRE(mode >= 0 && mode <= 2, OASR_ERR_INVALID, "gemm_add_norm_f32: mode must be 0, 1 or 2");
+  OB_REQUIRE(mode != 2 || (res_out && w_b && b_b), OASR_ERR_INVALID, "gemm_add_norm_f32: mode 2 needs res_out and the second norm");
+  OB_REQUIRE(!split_out || mode == 2, OASR_ERR_INVALID, "gemm_add_norm_f32: the [hi | hi | lo] output exists for mode 2 only");
+  OB_REQUIRE(M < (int64_t(1) << 31) && K < (1 << 30), OASR_ERR_INVALID, "gemm_add_norm_f32: extent too large");
+  OB_REQUIRE(is_aligned(h_out, 16) && is_aligned(A, 16) && is_aligned(B, 16) && (!bias || is_aligned(bias, 16)) &&
+                 (!res_in || is_aligned(res_in, 16)) && (!res_out || is_aligned(res_out, 16)) && is_aligned(w_a, 16) &&
+                 is_aligned(b_a, 16) && (!w_b || is_aligned(w_b, 16)) && (!b_b || is_aligned(b_b, 16)),
+             OASR_ERR_ALIGN, "gemm_add_norm_f32: pointers must be 16-byte aligned");
+  Call c{};
+  c.h_out = h_out; c.res_out = res_out; c.res_in = res_in; c.A = A; c.B = B;
+  c.M = M; c.N = N; c.K = K; c.dtype = dtype;
+  Params& p = c.p;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.num_k_blocks = static_cast<int>((K + BK - 1) / BK);
+  p.num_pairs = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
+  p.bias = bias; p.alpha = static_cast<float>(alpha); p.mode = mode; p.split_out = split_out ? 1 : 0;
+  p.has_res_in = res_in != nullptr; p.has_res_out = res_out != nullptr;
+  p.w_a = w_a; p.b_a = b_a; p.w_b = w_b; p.b_b = b_b; p.eps = static_cast<float>(eps);
+  p.status = device_status_ptr();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+    switch (N) {
+      case 512: return launch<T, 512>(c, s);
+      case 256: return launch<T, 256>(c, s);
+      default: return launch<T, 128>(c, s);
+    }
+  });
+}
+
+}  // extern "C"

@@ -272,9 +272,11 @@ class ConformerCTC:
         self._workspace = None
         self._pos_proj = None
 
-    def _encode_packed(self, rows: torch.Tensor, pk: PackedBatch, padded_semantics: bool):
+    def _encode_packed(self, rows: torch.Tensor, pk: PackedBatch, padded_semantics: bool, want_log_probs: bool = True):
         """rows: (total, F'*d) gathered embed-conv outputs -> (log_probs (total, V) fp32, argmax (total,) int32).
-        One call into the native executor (oasr_b200_conformer_encode_packed)."""
+        One call into the native executor (oasr_b200_conformer_encode_packed).  ``want_log_probs=False`` is the
+        token-only form: the head sweeps the vocabulary once, keeps the running first maximum per frame and
+        writes nothing but the argmax (``log_probs`` comes back ``None``)."""
         import ctypes
 
         from . import _lib
@@ -286,7 +288,8 @@ class ConformerCTC:
             self._workspace = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=rows.device)
         ws = self._workspace
         off = (-ws.data_ptr()) % 256
-        log_probs = torch.empty(pk.total, self.cfg.vocab_padded, device=rows.device, dtype=torch.float32)
+        log_probs = torch.empty(pk.total, self.cfg.vocab_padded, device=rows.device, dtype=torch.float32) \
+            if want_log_probs else None
         argmax = torch.empty(pk.total, device=rows.device, dtype=torch.int32)
         _lib.call("oasr_b200_conformer_encode_packed", ctypes.byref(self._native_model), _p(rows), _p(pk.cu_seqlens),
                   _p(pk.fill_frames) if padded_semantics else None, pk.num_segs, pk.total, pk.max_seg,
@@ -391,7 +394,7 @@ class ConformerCTC:
         return (log_probs, argmax) if return_argmax else log_probs
 
     def _forward(self, features: torch.Tensor, lengths, padded_semantics: bool, padded_output: bool,
-                 return_argmax: bool):
+                 return_argmax: bool, tokens_only: bool = False):
         if self.cfg.causal:
             raise NotImplementedError("offline forward with a causal conv module is not wired; use forward_chunk_paged")
         if not features.is_cuda:
@@ -409,8 +412,8 @@ class ConformerCTC:
             lp = torch.zeros(B, Tp, V, device=features.device) if padded_output else torch.zeros(0, V, device=features.device)
             return (lp, out_lengths, None, pk) if return_argmax else (lp, out_lengths, pk)
         rows = self._subsample_packed(features, out_lens, pk.cu_seqlens, pk.total, t1_limit)   # packed before the embed Linear
-        log_probs, argmax = self._encode_packed(rows, pk, padded_semantics)
-        if padded_output:
+        log_probs, argmax = self._encode_packed(rows, pk, padded_semantics, want_log_probs=not tokens_only)
+        if padded_output and log_probs is not None:
             # padded rows carry hidden = 0 in the reference (packing.py:228-232): log_softmax(bias)
             pad_row = torch.log_softmax(self.ctc_b.float(), dim=-1)
             full = pad_row.expand(B * Tp, V).contiguous()
@@ -457,8 +460,10 @@ class ConformerCTC:
         return out
 
     def greedy_search(self, features: torch.Tensor, lengths, packed: bool = True) -> List[List[int]]:
-        """Features -> greedy CTC token lists (argmax per frame in the head's epilogue, collapsed on the host)."""
-        _, _, argmax, pk = self._forward(features, lengths, not packed, False, True)
+        """Features -> greedy CTC token lists: the head keeps the per-frame first maximum in its epilogue and writes
+        no log-probs (the reference's greedy search reads fp32 log-probs back, oasr/functionals/ctc_decode.py:359);
+        the collapse runs on the host."""
+        _, _, argmax, pk = self._forward(features, lengths, not packed, False, True, tokens_only=True)
         if argmax is None:
             return [[] for _ in pk.seg_lengths]
         return self._collapse(argmax.cpu().numpy(), pk.seg_lengths)
@@ -492,7 +497,7 @@ class ConformerCTC:
             staged = stage(nxt) if nxt is not None else None      # next copy goes out before this batch's launches
             main.wait_event(ev)
             f.record_stream(main)
-            _, _, argmax, pk = self._forward(f, lengths, not packed, False, True)
+            _, _, argmax, pk = self._forward(f, lengths, not packed, False, True, tokens_only=True)
             if argmax is None:
                 cur = (None, pk, None)
             else:

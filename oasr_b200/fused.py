@@ -29,6 +29,21 @@ def add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: O
               _stream(h_out))
 
 
+def gemm_add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: Optional[torch.Tensor],
+                      A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor], alpha: float, mode: int, w_a, b_a,
+                      w_b=None, b_b=None, eps: float = 1e-5, split_out: bool = False) -> None:
+    """``add_norm_f32`` with the sub-layer's last Linear folded in: ``y = A @ B.T + bias`` stays fp32 in tensor
+    memory, ``s = res_in + alpha*y``, then the norm of ``mode`` as in :func:`add_norm_f32`.  One kernel instead of
+    ``gemm`` + ``add_layer_norm_residual`` (oasr/models/conformer/model.py:722-751); needs an output width of
+    128, 256 or 512."""
+    _need_cuda(h_out, res_out, res_in, A, B, bias)
+    K, N = A.shape[-1], B.shape[0]
+    M = A.numel() // K
+    _lib.call("oasr_b200_gemm_add_norm_f32", _p(h_out), _p(res_out), _p(res_in), _p(A), _p(B), _p(bias), M, N, K,
+              float(alpha), int(mode), _p(w_a), _p(b_a), _p(w_b), _p(b_b), float(eps), int(bool(split_out)),
+              _DTYPE_ID[A.dtype], _stream(A))
+
+
 def depthwise_conv1d_packed(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                             cu_seqlens: torch.Tensor, max_seg_len: int, *, post_scale=None, post_shift=None,
                             right_fill=None, fill_frames=None, activation: int = -1, out=None) -> torch.Tensor:
@@ -261,3 +276,18 @@ def relshift_bias(bd: torch.Tensor, lengths: torch.Tensor, T: int, scale: float,
               float(scale), int(chunk), int(left_chunks),
               float(floor_value), _DTYPE_ID[bd.dtype], _stream(bd))
     return out[..., :T]
+
+
+def gemm_argmax(A: torch.Tensor, B: torch.Tensor, C: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-row index of the first maximum of ``A @ B.T + C`` (int32) without writing logits or log-probs: the
+    token-only form of the CTC head.  What ``gemm_log_softmax`` followed by the per-frame argmax of a greedy search
+    computes (oasr/layers/ctc.py:48-51, oasr/functionals/ctc_decode.py:359), in one vocabulary sweep."""
+    _need_cuda(A, B, C)
+    K, N = A.shape[-1], B.shape[0]
+    A2 = A.reshape(-1, K)
+    A2 = A2 if A2.is_contiguous() else A2.contiguous()
+    B = B if B.is_contiguous() else B.contiguous()
+    arg = torch.empty(A.shape[:-1], device=A.device, dtype=torch.int32)
+    _lib.call("oasr_b200_gemm_log_softmax", None, _p(A2), _p(B), _p(C), A2.size(0), N, K, _DTYPE_ID[A.dtype],
+              _DTYPE_ID[torch.float32], _p(arg), _stream(A))
+    return arg

@@ -246,3 +246,25 @@ def test_gemm_log_softmax_default_path_at_benchmark_size(M):
     assert out.logsumexp(-1).abs().max().item() < 1e-3
     assert torch.equal(arg.long(), out.argmax(-1))
     assert ob.device_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 300, 4096, BENCH_M])
+def test_token_only_head_equals_the_argmax_of_the_log_probs(M):
+    """out == NULL: one vocabulary sweep, only the first-maximum index per row -- the same index the log-prob form
+    reports, and the argmax of the oracle's log-probs wherever that is not a numerical tie."""
+    from oasr_b200 import fused
+
+    dtype = torch.bfloat16
+    N, K = 5008, 512
+    A, B, C = _rand((M, K), dtype, 21), _rand((N, K), dtype, 22, K ** -0.5), _rand((N,), dtype, 23, 0.1)
+    got = fused.gemm_argmax(A.cuda(), B.cuda(), C.cuda())
+    out, arg = ob.gemm_log_softmax(A.cuda(), B.cuda(), C.cuda(), out_dtype=torch.float32, return_argmax=True)
+    assert got.dtype == torch.int32 and got.shape == (M,)
+    if M > 93 * 128:                                           # both forms ran the same sweep kernel: identical
+        assert torch.equal(got, arg)
+    rows = _sample_rows(M, 512) if M > 2000 else torch.arange(M)
+    want = O.gemm_log_softmax(A[rows], B, C)
+    top2 = want.topk(2, -1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 2e-2
+    assert torch.equal(got[rows.cuda()].cpu().long()[clear], want.argmax(-1)[clear])
+    assert ob.device_status() == 0
