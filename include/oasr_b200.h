@@ -88,6 +88,16 @@ OASR_API int oasr_b200_device_status(uint32_t* word /*host*/, void* stream);
  * roles.  The next oasr_b200_device_status call then returns
  * OASR_ERR_DEVICE_WAIT and clears the word; kernels launched afterwards run
  * normally.  Nothing faults or hangs. */
+/* Diagnostics (no reference counterpart): with a device buffer of 64 uint64
+ * set, the first CTA of every following launch of the instrumented kernels
+ * (the fused Linear+add+norm kernel, the packed relative-position attention
+ * kernel) writes SM clock stamps of its phases there; NULL (the default)
+ * switches it off.  Slots of the Linear+add+norm kernel: 0 start, 1 first
+ * operand load, 2 first operands landed, 3 last MMA committed, 4 accumulator
+ * seen by the epilogue, 5 / 6 / 7 ends of the epilogue passes, 8 stores
+ * drained, 9 exit.  Attention kernel: 0 start, 1 set-up done, 2 first scores
+ * seen, 3 + j end of the softmax of key tile j (j < 40), 60 output written. */
+OASR_API int oasr_b200_trace_buffer(void* device_buffer /*nullable*/);
 OASR_API int oasr_b200_selftest_bounded_wait(int64_t poll_limit, uint32_t* report /*device, nullable*/,
                                              void* stream);
 /* Number of kernels this library has launched in this process so far
@@ -186,7 +196,13 @@ OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
  * oasr/models/conformer/model.py:722-751):
  *   y = A[M,K] . B[N,K]^T + bias (fp32, never rounded), s = res_in + alpha*y,
  * then `mode` / w_a, b_a, w_b, b_b / split_out exactly as oasr_b200_add_norm_f32
- * (h_out 16-bit [M,N] or [M,3N], res_out fp32 [M,N], may alias res_in).
+ * (h_out 16-bit row-major [M,N] or [M,3N]).  The fp32 residual stream
+ * (res_in, res_out; res_out may alias res_in) is NOT row-major here: it is
+ * private to a chain of these calls and uses a blocked layout the kernel can
+ * move without staging -- rows padded to a multiple of 32, blocks of 32 rows x
+ * 32 columns stored band-major ((row/32) * (N/32) + col/32) * 1024 floats,
+ * and inside a block element (row l, column 4j+e) at float (j*32 + l)*4 + e;
+ * the buffers hold roundup32(M) * N floats.
  * The output row must fill tensor memory: N = 128, 256 or 512
  * (oasr_b200_gemm_add_norm_supported); other widths return
  * OASR_ERR_UNSUPPORTED and the caller composes gemm + add_norm_f32. */

@@ -59,6 +59,7 @@ uint32_t* device_status_ptr() {
 namespace gemm { extern int g_force_bn; extern int g_use_pairs; extern int g_lsm_path; }
 extern int g_dw_path;
 extern int g_fmha_relpos_path;
+unsigned long long* g_trace_buffer = nullptr;   // diagnostics: device buffer that instrumented kernels stamp their phases into
 int g_pdl = 0;  // measured neutral on both workloads (offline 7.32 vs 7.36 ms, streaming 3.79 vs 3.71 ms per step): off by default
 extern int g_fmha_chunk_path;
 extern int g_fused_addnorm;
@@ -107,6 +108,11 @@ int oasr_b200_set_tunable(const char* name, int value) {
 }
 
 unsigned long long oasr_b200_launch_count(void) { return ob::g_launches; }
+
+int oasr_b200_trace_buffer(void* device_buffer) {
+  ob::g_trace_buffer = static_cast<unsigned long long*>(device_buffer);
+  return OASR_OK;
+}
 
 const char* oasr_b200_version(void) { return "oasr_b200 0.1.0 sm_100a"; }
 

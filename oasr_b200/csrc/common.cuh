@@ -203,6 +203,7 @@ inline bool act_is_known(int act) {
     }                                                                     \
   }()
 
+extern unsigned long long* g_trace_buffer;  // nullable diagnostics buffer (capi.cu), see oasr_b200_trace_buffer
 int sm_count();  // cached multiprocessor count of the current device (capi.cu)
 
 // Launch with programmatic stream serialisation (the kernel must call grid_dep_wait() before it touches

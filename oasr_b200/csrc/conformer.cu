@@ -96,7 +96,7 @@ Workspace carve(const oasr_b200_conformer_model& m, int64_t M, int64_t max_seg, 
     off += align256(bytes);
     return p;
   };
-  w.res = reinterpret_cast<float*>(take(M * d * 4));
+  w.res = reinterpret_cast<float*>(take((M + 31) / 32 * 32 * d * 4));   // rows padded to whole 32-row bands (blocked layout)
   w.h = take(M * d * 2);
   w.y = take(M * d * 2);
   w.a_ffn = take(M * m.ffn * 2);
@@ -203,10 +203,13 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   } while (0)
   // Last Linear of a sub-layer + residual step + norm: one fused kernel where the width allows it (16-bit GEMMs),
   // else the Linear into w.y followed by add_norm_f32.  `rin` is the residual input (null for the embed).
-  const bool fuse = qk == 0 && g_fused_addnorm != 0 && oasr_b200_gemm_add_norm_supported(d, d) != 0;
+  // The fused kernel keeps the residual stream in its own blocked layout, add_norm_f32 row-major: one or the other
+  // for the whole call.
+  const bool fuse = qk == 0 && g_fused_addnorm != 0 && oasr_b200_gemm_add_norm_supported(d, d) != 0 &&
+                    oasr_b200_gemm_add_norm_supported(d, m.ffn) != 0 && oasr_b200_gemm_add_norm_supported(d, m.embed_in) != 0;
 #define OB_LINEAR_ADDNORM(label, fl, hout, rin, in, wt, bs, lay, qi, K, alpha, mode, wa, ba, wb, bb, eps_, split)       \
   do {                                                                                                              \
-    if (fuse && oasr_b200_gemm_add_norm_supported(d, K)) {                                                          \
+    if (fuse) {                                                                                                     \
       OB_STEP("gemm_addnorm " label, fl, oasr_b200_gemm_add_norm_f32(hout, w.res, rin, in, wt, bs, M, d, K, alpha, mode, wa, ba, \
                                                                     wb, bb, eps_, split, dt, stream));              \
     } else {                                                                                                        \
@@ -214,7 +217,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
       OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(hout, w.res, rin, w.y, alpha, mode, wa, ba, wb, bb, M, d, eps_, split, dt, stream)); \
     }                                                                                                               \
   } while (0)
-  if (fuse && oasr_b200_gemm_add_norm_supported(d, m.embed_in)) {
+  if (fuse) {
     if (m.embed_ln_w) {
       OB_STEP("gemm_addnorm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_add_norm_f32(w.h, w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, 2,
                                      m.embed_ln_w, m.embed_ln_b, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, 1e-5, 0, dt, stream));

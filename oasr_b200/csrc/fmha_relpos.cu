@@ -7,11 +7,17 @@
 // MUFU, barrier hand-offs, 3k clocks before a CTA's first scores arrive), so one CTA per SM leaves every unit
 // under 20 % busy; a second resident CTA fills those gaps.  To fit twice:
 //   keys are walked in tiles of 64 (K | pos 16 KB, V 8 KB per stage, two stages),
-//   P has a single 16 KB buffer (the softmax folds O of tile j-1, which proves P.V of tile j-1 is done, before
-//   it rewrites P for tile j),
-//   TMEM holds S[2] (2 x 64 columns) and O[2] (2 x 64 columns) = 256 columns,
+//   P has a single 16 KB buffer (a softmax thread waits for P.V of tile j-1 before it rewrites P for tile j; by
+//   then that short MMA has long finished, because the exponentials of tile j were computed in between),
+//   TMEM holds S[2] (2 x 64 columns) and ONE O (64 columns) that every P.V accumulates into = 192 of 256 columns,
 // i.e. 96 KB of shared memory and half of TMEM per CTA.
 // 160 threads: warp 4 lane 0 issues TMA loads and MMAs, warps 0-3 own one query row per thread.
+// Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
+// once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
+// are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
+// common case costs nothing -- then exp2 (every fourth one as a degree-3 polynomial on the FMA pipe, because the
+// 16-lane MUFU unit is this kernel's busiest), bf16/fp16 P into swizzled shared memory.  O leaves TMEM once, at
+// the end, scaled by 1 / sum.
 // Only the length mask exists here (keys >= segment length); bias, causal masks, key starts, paged K/V and
 // head_dim 128 stay on the general kernel in fmha.cu.  Every wait is bounded.
 #include <cuda.h>
@@ -36,9 +42,10 @@ constexpr int kVBytes = BKV * 128;
 constexpr int kPBytes = BQ * 128;               // 128 rows x 64 keys
 constexpr int kOffQ = 0, kOffK = kOffQ + kQBytes, kOffV = kOffK + 2 * kKBytes, kOffP = kOffV + 2 * kVBytes;
 constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kNumBars = 12;
+constexpr int kNumBars = 11;
 constexpr int kSmemDynamic = kOffBar + kNumBars * 8 + 16 + 1024;
 constexpr uint32_t kTmemCols = 256, kColS = 0, kColO = 128;
+constexpr float kLazyLog2 = 8.f;   // rescale only when the row maximum grows by more than 2^8
 
 struct Params {
   int H;
@@ -46,12 +53,29 @@ struct Params {
   const int32_t* cu;
   void* out;
   uint32_t* status;
+  unsigned long long* trace;   // nullable diagnostics buffer: the CTA (0, 0, trace_seg) stamps its phases
+  int trace_seg;
 };
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && static_cast<int>(blockIdx.z) == p.trace_seg)
+    p.trace[slot] = static_cast<unsigned long long>(clock64());
+}
 
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x on the FMA / ALU pipes: round x to the nearest integer n with the 1.5 * 2^23 trick, 2^(x - n) by a cubic on
+// [-0.5, 0.5] (relative error 6e-4, below the rounding of a 16-bit P), n added to the exponent field.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float magic = 12582912.f;                      // 0x4B400000
+  const float xr = x + magic;
+  const int n = __float_as_int(xr) - 0x4B400000;
+  const float f = x - (xr - magic);
+  const float pl = fmaf(fmaf(fmaf(0.0555041f, f, 0.2402265f), f, 0.6931472f), f, 1.0f);
+  return __int_as_float(__float_as_int(pl) + (n << 23));
 }
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -76,6 +100,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
   ptx::grid_dep_wait();
+  if (threadIdx.x == 0) stamp(p, 0);
   const int q0 = blockIdx.x * BQ, h = blockIdx.y, seg = blockIdx.z;
   const int row0 = p.cu[seg], kv_len = p.cu[seg + 1] - row0;
   if (q0 >= kv_len) return;  // CTA-uniform (queries and keys of a segment are the same rows)
@@ -97,7 +122,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint64_t* s_full = bars + 5;     // [2]
   uint64_t* s_free = bars + 7;     // [2]
   uint64_t* p_full = bars + 9;     // [1]
-  uint64_t* po_done = bars + 10;   // [2]  P.V into O[b] finished: O[b] is ready and P may be rewritten
+  uint64_t* po_done = bars + 10;   // P.V of a tile has been accumulated into O: O is stable and P may be rewritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -109,8 +134,8 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       ptx::mbar_init(&kv_empty[i], 1);
       ptx::mbar_init(&s_full[i], 1);
       ptx::mbar_init(&s_free[i], BQ);
-      ptx::mbar_init(&po_done[i], 1);
     }
+    ptx::mbar_init(po_done, 1);
     ptx::mbar_init(p_full, BQ);
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -124,6 +149,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) stamp(p, 1);
 
   if (warp == 4) {
     // =================== TMA producer + MMA issuer (one thread) ===================
@@ -149,17 +175,17 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         ptx::umma_commit(&s_full[b]);
       };
-      auto issue_pv = [&](int b) {   // O[b] = P . V_b : K = 64 keys in four steps of 16
+      auto issue_pv = [&](int b, bool first) {   // O (+)= P . V_b : K = 64 keys in four steps of 16
         const uint32_t a_addr = ptx::smem_u32(sP);
         const uint32_t b_addr = ptx::smem_u32(sV + b * kVBytes);
-        const uint32_t d_tmem = tmem_base + kColO + b * D;
+        const uint32_t d_tmem = tmem_base + kColO;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           const uint64_t adesc = ptx::smem_desc_kmajor_sw128(a_addr + kk * 32);
           const uint64_t bdesc = ptx::smem_desc_mnmajor_sw128(b_addr + kk * 2048, BKV * 128, 1024);
-          ptx::umma_f16(d_tmem, adesc, bdesc, kIdescPV, kk != 0 ? 1u : 0u);
+          ptx::umma_f16(d_tmem, adesc, bdesc, kIdescPV, (!first || kk != 0) ? 1u : 0u);
         }
-        ptx::umma_commit(&po_done[b]);
+        ptx::umma_commit(po_done);
         ptx::umma_commit(&kv_empty[b]);
       };
       ptx::mbar_expect_tx(q_full, kQBytes);
@@ -187,7 +213,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(j) & 1u, abort_flag);   // P of tile j written
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        issue_pv(b);
+        issue_pv(b, j == 0);
         if (j + 2 < nkv) {
           ok = ptx::mbar_wait(&kv_empty[b], ph, abort_flag);
           if (!ok) break;
@@ -202,111 +228,113 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int r = threadIdx.x;  // 0..127
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const bool row_ok = r < rows_valid;
-    float m_run = kNegInf, l_run = 0.f, alpha_prev = 1.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    const uint32_t t_o = tmem_base + lane_base + kColO;
+    float m_run = kNegInf, l_run = 0.f;   // m_run: the reference maximum the exponentials, l_run and O are relative to
     bool ok = true;
-    auto fold_o = [&](int t) -> bool {  // o = o * alpha_prev + O_t
-      const int b = t & 1;
-      if (!ptx::mbar_wait(&po_done[b], (t >> 1) & 1u, abort_flag)) return false;
-      ptx::tc_fence_after_sync();
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_base + kColO + b * D + c0, v);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
-      }
-      ptx::tc_fence_before_sync();
-      return true;
-    };
     for (int j = 0; ok && j < nkv; ++j) {
       const int b = j & 1;
       const int key0 = j * BKV;
       if (!ptx::mbar_wait(&s_full[b], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const uint32_t t_s = tmem_base + lane_base + kColS + b * BKV;
-      // ---- pass 1: row max of the raw scores (32-key blocks inside the valid keys need no mask) ----
+      if (j == 0 && r == 0) stamp(p, 2);
+      if (j == 3 && r == 0) stamp(p, 50);
+      uint32_t v[64];
+      ptx::tmem_ld_32x64(tmem_base + lane_base + kColS + b * BKV, v);
+      ptx::tmem_ld_wait();
+      if (j == 3 && r == 0) stamp(p, 51);
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&s_free[b]);          // the scores live in registers now: S[b] may take tile j+2
+      const bool full = key0 + BKV <= kv_len;   // tiles inside the valid keys need no mask
       float tile_max = kNegInf;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        if (key0 + c0 >= kv_len) break;
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(t_s + c0, v);
-        ptx::tmem_ld_wait();
-        if (key0 + c0 + 32 <= kv_len) {
+      if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
-        } else {
+        for (int i = 0; i < 64; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, key0 + c0 + i < kv_len ? __uint_as_float(v[i]) : kNegInf);
-        }
+        for (int i = 0; i < 64; ++i) tile_max = fmaxf(tile_max, key0 + i < kv_len ? __uint_as_float(v[i]) : kNegInf);
       }
       tile_max *= p.scale_log2;   // the scale is positive
-      const float m_new = fmaxf(m_run, tile_max);
-      const float m_use = (m_new == kNegInf) ? 0.f : m_new;  // empty-row clamp
-      const float alpha = (m_run == kNegInf) ? 0.f : ex2_fast(m_run - m_use);
-      // ---- O of tile j-1 (also proves that P.V of tile j-1 has finished reading P) ----
-      if (j >= 1) {
-        if (!fold_o(j - 1)) { ok = false; break; }
+      if (j == 3 && r == 0) stamp(p, 52);
+      // Lazy rescale: the reference maximum moves only when this tile exceeds it by more than 2^kLazyLog2.
+      float rescale = 1.f;
+      bool moved = false;
+      if (m_run == kNegInf) {
+        m_run = (tile_max == kNegInf) ? 0.f : tile_max;      // first tile (empty-row clamp: no valid key -> 0)
+      } else if (tile_max > m_run + kLazyLog2) {
+        rescale = ex2_fast(m_run - tile_max);
+        m_run = tile_max;
+        moved = true;
       }
-      // ---- pass 2: exponentiate, sum, round, write P (K-major, 128-byte swizzle) ----
+      // exponentiate, sum, round: keys 4k+3 of every group of four on the FMA pipe, the others on the MUFU unit
+      uint32_t packed[32];
       float row_sum = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t packed[16];
-        if (key0 + c0 >= kv_len) {   // P of keys past the end is zero (V rows there hold other segments' finite values)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) packed[i] = 0u;
-        } else {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32(t_s + c0, v);
-          ptx::tmem_ld_wait();
-          const bool full = key0 + c0 + 32 <= kv_len;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-            float p1 = ex2_fast(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-            if (!full) {
-              p0 = key0 + c0 + i < kv_len ? p0 : 0.f;
-              p1 = key0 + c0 + i + 1 < kv_len ? p1 : 0.f;
-            }
-            row_sum += p0 + p1;
-            packed[i / 2] = pack2<T>(p0, p1);
-          }
+      for (int i = 0; i < 64; i += 4) {
+        float e0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
+        float e1 = ex2_fast(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run));
+        float e2 = ex2_fast(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m_run));
+        float e3 = ex2_poly(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_run));
+        if (!full) {   // P of keys past the end is zero (V rows there hold other segments' finite values)
+          e0 = key0 + i < kv_len ? e0 : 0.f;
+          e1 = key0 + i + 1 < kv_len ? e1 : 0.f;
+          e2 = key0 + i + 2 < kv_len ? e2 : 0.f;
+          e3 = key0 + i + 3 < kv_len ? e3 : 0.f;
         }
-        // keys c0..c0+31 of row r: 16-byte chunks c0/8 .. +3, XOR-swizzled by r%8
-        uint8_t* row_base = sP + r * 128;
+        row_sum += (e0 + e1) + (e2 + e3);
+        packed[i / 2] = pack2<T>(e0, e1);
+        packed[i / 2 + 1] = pack2<T>(e2, e3);
+      }
+      if (j == 3 && r == 0) stamp(p, 53);
+      // P.V of tile j-1 has finished: P may be rewritten and O is stable (it is only touched here when the maximum moved)
+      if (j >= 1) {
+        if (!ptx::mbar_wait(po_done, static_cast<uint32_t>(j - 1) & 1u, abort_flag)) { ok = false; break; }
+        if (moved) {
+          ptx::tc_fence_after_sync();
+          uint32_t o[64];
+          ptx::tmem_ld_32x64(t_o, o);
+          ptx::tmem_ld_wait();
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c0 / 8 + q4) ^ (r & 7);
-          *reinterpret_cast<uint4*>(row_base + chunk * 16) =
-              make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          for (int i = 0; i < 64; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * rescale);
+          ptx::tmem_st_32x32(t_o, reinterpret_cast<const uint32_t(&)[32]>(o[0]));
+          ptx::tmem_st_32x32(t_o + 32, reinterpret_cast<const uint32_t(&)[32]>(o[32]));
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before_sync();
         }
       }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&s_free[b]);
+      if (j == 3 && r == 0) stamp(p, 54);
+      l_run = l_run * rescale + row_sum;
+      // row r of P, K-major with the 128-byte swizzle: 16-byte chunk c (8 keys) sits at c ^ (r % 8)
+      uint8_t* row_base = sP + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<uint4*>(row_base + ((c ^ (r & 7)) << 4)) =
+            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
+      if (j == 3 && r == 0) stamp(p, 55);
       ptx::fence_proxy_async_smem();
       ptx::mbar_arrive(p_full);
-      l_run = l_run * alpha + row_sum;
-      m_run = m_new;
-      alpha_prev = alpha;
+      if (r == 0 && j < 40) stamp(p, 3 + j);
     }
-    if (ok) ok = fold_o(nkv - 1);
-    if (ok && row_ok) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T* orow = out + static_cast<int64_t>(r) * out_ld;
+    if (ok) ok = ptx::mbar_wait(po_done, static_cast<uint32_t>(nkv - 1) & 1u, abort_flag);
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      uint32_t o[64];
+      ptx::tmem_ld_32x64(t_o, o);
+      ptx::tmem_ld_wait();
+      if (row_ok) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        T* orow = out + static_cast<int64_t>(r) * out_ld;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint4 w;
-        w.x = pack2<T>(o[c] * inv, o[c + 1] * inv);
-        w.y = pack2<T>(o[c + 2] * inv, o[c + 3] * inv);
-        w.z = pack2<T>(o[c + 4] * inv, o[c + 5] * inv);
-        w.w = pack2<T>(o[c + 6] * inv, o[c + 7] * inv);
-        *reinterpret_cast<uint4*>(orow + c) = w;
+        for (int c = 0; c < D; c += 8) {
+          uint4 w;
+          w.x = pack2<T>(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+          w.y = pack2<T>(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+          w.z = pack2<T>(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+          w.w = pack2<T>(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c) = w;
+        }
       }
+      if (r == 0) stamp(p, 60);
     }
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusFmhaSoftmax);
   }
@@ -343,6 +371,7 @@ int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t 
   p.H = (int)H;
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.cu = cu_seqlens; p.out = out; p.status = device_status_ptr();
+  p.trace = g_trace_buffer; p.trace_seg = 0;
   dim3 grid((unsigned)((max_seqlen + BQ - 1) / BQ), (unsigned)H, (unsigned)num_segs);
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
     auto kern = fmha_relpos64_kernel<T>;

@@ -1,7 +1,8 @@
 // Linear + residual add + LayerNorm in ONE kernel for the residual-stream steps of the encoder layer:
 //
 //   y = A[M,K] . B[N,K]^T + bias            (16-bit operands, fp32 accumulate, never rounded)
-//   s = res_in + alpha * y                  (fp32 residual stream; res_in nullable)
+//   s = res_in + alpha * y                  (fp32 residual stream in a blocked layout, see res_block_offset;
+//                                            res_in nullable)
 //   mode 0:  res_out = s,        h = LN_a(s)
 //   mode 1:  res_out = s,        h = s * w_a + b_a          (fp32 per-channel scale/shift: a folded BatchNorm)
 //   mode 2:  res_out = LN_a(s),  h = LN_b(res_out)          (optionally h as [hi | hi | lo], 3N wide)
@@ -18,11 +19,14 @@
 // what limits a single-CTA 128 x 256 tile.  No multicast: every CTA loads its own bytes.
 //   warp 0   TMA producer (A tile + its B rows per 64-wide K block, kStages-deep ring)
 //   warp 1   MMA issuer (leader CTA only; N/256 instructions of N<=256 per K16 step) + TMEM owner
-//   warps 2-5  epilogue, thread = output row (tcgen05.ld 32x32b: lane = row):
-//     pass 1  s = res + alpha*(acc + bias) per 32-column chunk; the residual chunk arrives by TMA into a
-//             swizzled per-warp buffer (prefetched two chunks ahead, the first two under the main loop),
-//             s goes back to the same buffer and out by TMA store, and back into the accumulator's own
-//             TMEM columns; running sums for mean / variance about the row's first value
+//   warps 2-9  epilogue, two threads per output row (tcgen05.ld 32x32b: lane = row; warps w and w+4 share a TMEM
+//             lane quarter and take one half of the row's columns each -- one warp per scheduler is latency-bound):
+//     pass 1  s = res + alpha*(acc + bias) per 32-column chunk; the residual stream lives in HBM in 32 x 32
+//             blocks laid out so that a warp (lane = row) reads and writes a block with eight coalesced 512-byte
+//             accesses straight from registers (the next block is requested before this one is processed, the
+//             first one under the main loop); s also goes back into the accumulator's own TMEM columns; running
+//             sums for mean / variance about the slice's first value, combined across the two slices through
+//             shared memory
 //     pass 2  re-reads s from TMEM, normalises, rounds once, stages 32 x 32 pieces (64-byte swizzle) and
 //             TMA-stores them (mode 2: writes LN_a(s) as fp32 instead, keeps it in TMEM, pass 3 stores h)
 // Every wait is bounded (mbar_wait); on give-up the CTA drains and raises the device status word.
@@ -41,11 +45,12 @@ namespace gan {
 constexpr int BM = 128;      // rows per CTA (= TMEM lanes)
 constexpr int BK = 64;       // K elements per stage (128-byte rows)
 constexpr int UMMA_K = 16;
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;  // two warps per TMEM lane quarter: each handles one half of the row's columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kChunk = 32;   // columns per epilogue step
-constexpr int kF32Bufs = 4;  // per warp: 32 rows x 32 fp32 (4 KB each), residual in / out staging
-constexpr int kHBufs = 2;    // per warp: 32 rows x 32 16-bit (2 KB each), h staging
+constexpr int kSlices = kEpiWarps / 4;   // column slices of a row (threads that share a row)
+// per epilogue warp: two 32 x 32 16-bit staging buffers for h (2 KB each, 64-byte swizzle)
+constexpr int kWarpEpiBytes = 2 * 2048;
 
 struct Params {
   int M, N, K;
@@ -55,12 +60,13 @@ struct Params {
   float alpha;
   int mode;                // 0, 1, 2 as above
   int split_out;           // mode 2: h rows are [hi | hi | lo]
-  int has_res_in;
-  int has_res_out;
+  const float* res_in;     // fp32 residual stream in the blocked layout described at the top, nullable
+  float* res_out;          // same layout, nullable unless mode 2; may alias res_in
   const void *w_a, *b_a;   // T[N] (mode 1: float[N])
   const void *w_b, *b_b;   // T[N], mode 2
   float eps;
   uint32_t* status;
+  unsigned long long* trace;   // nullable: CTA 0 writes clock stamps of its phases here (diagnostics)
 };
 
 template <int N, int kStages>
@@ -72,10 +78,10 @@ struct Smem {
   static constexpr int kBBytes = kHalves * kBHalfBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kRing = kStages * kStageBytes;
-  static constexpr int kWarpEpi = kF32Bufs * 4096 + kHBufs * 2048;
+  static constexpr int kWarpEpi = kWarpEpiBytes;
   static constexpr int kEpiOffset = kRing;
   static constexpr int kBarOffset = kEpiOffset + kEpiWarps * kWarpEpi;
-  static constexpr int kNumBars = 2 * kStages + 2 + kEpiWarps * kF32Bufs;
+  static constexpr int kNumBars = 2 * kStages + 2 + 2;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamic = kTotal + 1024;
 };
@@ -115,15 +121,26 @@ __device__ __forceinline__ void load_params32(const P* p, float (&f)[32]) {
   }
 }
 
-// TMA load of a 2-D fp32 box into this CTA's shared memory (used for the residual chunks).
-__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-  ptx::tma_load_3d(dst, map, c0, c1, 0, bar);
+// Blocked layout of the fp32 residual stream: the matrix is cut into blocks of 32 rows x 32 columns, blocks of a
+// row band back to back (band-major); inside a block the 16-byte piece j (columns 4j..4j+3) of row l sits at
+// float4 index j*32 + l.  A warp whose lane l owns row l of a band then moves a block with eight fully
+// coalesced 512-byte accesses, no staging in shared memory.
+__device__ __forceinline__ int64_t res_block_offset(int band, int chunk, int n_chunks) {
+  return (static_cast<int64_t>(band) * n_chunks + chunk) * 1024;   // in floats
+}
+__device__ __forceinline__ float4 ld_res(const float* p) {
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0) p.trace[slot] = static_cast<unsigned long long>(clock64());
 }
 
 template <typename T, int N, int kStages>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_rin, const __grid_constant__ CUtensorMap tmap_rout,
                     const __grid_constant__ CUtensorMap tmap_h, const Params p) {
   using S = Smem<N, kStages>;
   constexpr int kHalves = S::kHalves;
@@ -142,8 +159,8 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tfull_bar = empty_bar + kStages;
   uint64_t* tempty_bar = tfull_bar + 1;
-  uint64_t* rin_bar = tempty_bar + 1;            // [kEpiWarps][kF32Bufs]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rin_bar + kEpiWarps * kF32Bufs);
+  uint64_t* stat_bar = tempty_bar + 1;           // [2]: every warp has published its slice's row statistics
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -156,14 +173,13 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     ptx::mbar_init(tfull_bar, 1);
     ptx::mbar_init(tempty_bar, kEpiWarps * 2);   // the leader waits for both CTAs' epilogue warps
-    for (int i = 0; i < kEpiWarps * kF32Bufs; ++i) ptx::mbar_init(&rin_bar[i], 1);
+    ptx::mbar_init(&stat_bar[0], kEpiWarps);
+    ptx::mbar_init(&stat_bar[1], kEpiWarps);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
-    ptx::prefetch_tensormap(&tmap_rin);
-    ptx::prefetch_tensormap(&tmap_rout);
     ptx::prefetch_tensormap(&tmap_h);
   }
   if (warp == 1) {
@@ -179,6 +195,7 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int num_clusters = static_cast<int>(gridDim.x >> 1);
   const int first_pair = static_cast<int>(blockIdx.x >> 1);
+  if (threadIdx.x == 0) stamp(p, 0);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -193,6 +210,7 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // both CTAs' bytes are credited to the leader's barrier; only the leader arrives on it
           const uint32_t lead_full = ptx::map_to_cta(&full_bar[stage], 0);
           if (cta_rank == 0) ptx::mbar_expect_tx(&full_bar[stage], 2 * S::kStageBytes);
+          if (kb == 0) stamp(p, 1);
           ptx::tma_load_3d_pair(sA + stage * S::kABytes, &tmap_a, kb * BK, a_row, 0, lead_full);
 #pragma unroll
           for (int j = 0; j < kHalves; ++j) {
@@ -218,6 +236,7 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
+          if (kb == 0) stamp(p, 2);
           const uint32_t a_addr = ptx::smem_u32(sA + stage * S::kABytes);
           const uint32_t b_addr = ptx::smem_u32(sB + stage * S::kBBytes);
 #pragma unroll
@@ -233,45 +252,30 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (ok) ptx::umma_commit_pair(tfull_bar, 3);      // the accumulators of both CTAs are complete
+        stamp(p, 3);
         acc_phase ^= 1u;
       }
       if (!ok && p.status) atomicOr(p.status, kStatusGemmMma);
     }
     __syncwarp();
   } else {
-    // ------------------------------ epilogue: thread = output row ---------------
-    const int ew = warp - 2;                       // epilogue warp index 0..3
+    // ------------------------------ epilogue: thread = (output row, column slice) ---------------
+    const int ew = warp - 2;                       // epilogue warp index 0..7
     const int q = warp & 3;                        // TMEM lane quarter this warp may access
+    const int slice = ew >> 2;                     // which half of the row's columns this warp handles
+    constexpr int kLocal = kChunks / kSlices;      // chunks per warp
+    const int c_lo = slice * kLocal;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
-    uint8_t* my_smem = smem + S::kEpiOffset + ew * S::kWarpEpi;
-    uint8_t* fbuf = my_smem;                       // kF32Bufs x 4 KB, 128-byte swizzle (1024-byte aligned)
-    uint8_t* hbuf = my_smem + kF32Bufs * 4096;     // kHBufs x 2 KB, 64-byte swizzle
-    uint64_t* my_rin = rin_bar + ew * kF32Bufs;
-    uint32_t rin_phase = 0;                        // bit b = parity of the next completion of buffer b
-    uint32_t tfull_phase = 0;
+    uint8_t* hbuf = smem + S::kEpiOffset + ew * S::kWarpEpi;            // 2 x 2 KB h staging; [0] is also the statistics mailbox
+    uint8_t* partner_hbuf = smem + S::kEpiOffset + (ew ^ 4) * S::kWarpEpi;   // same rows, other column slice
+    uint32_t tile_phase = 0;
     bool ok = true;
     const T* bias = static_cast<const T*>(p.bias);
-    const int sw128 = lane & 7;                    // chunk XOR of this thread's row in a 128-byte-swizzled buffer
-    const int sw64 = (lane >> 1) & 3;              // same for the 64-byte-swizzled h buffers
+    const int sw64 = (lane >> 1) & 3;              // chunk XOR of this thread's row in a 64-byte-swizzled buffer
 
-    // this thread's 32 fp32 of buffer b (its row, swizzled)
-    auto f32_row_load = [&](int b, float (&v)[32]) {
-      const uint8_t* row = fbuf + b * 4096 + lane * 128;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 t = *reinterpret_cast<const float4*>(row + ((j ^ sw128) << 4));
-        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-      }
-    };
-    auto f32_row_store = [&](int b, const float (&v)[32]) {
-      uint8_t* row = fbuf + b * 4096 + lane * 128;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<float4*>(row + ((j ^ sw128) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-    };
-    // 32 values rounded to T into h buffer b (this thread's 64-byte row)
-    auto h_row_store = [&](int b, const float (&v)[32]) {
-      uint8_t* row = hbuf + b * 2048 + lane * 64;
+    // 32 values rounded to T into a 64-byte-swizzled buffer (this thread's 64-byte row)
+    auto h_row_store = [&](uint8_t* buf, const float (&v)[32]) {
+      uint8_t* row = buf + lane * 64;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         *reinterpret_cast<uint4*>(row + ((c ^ sw64) << 4)) =
@@ -279,59 +283,105 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                        pack2<T>(v[8 * c + 4], v[8 * c + 5]), pack2<T>(v[8 * c + 6], v[8 * c + 7]));
       }
     };
+    // Before staging buffer `which` is rewritten: the TMA store issued from it two chunks ago has read it.
+    auto h_buffer_free = [&]() {
+      if (lane == 0) ptx::bulk_wait_group_read<1>();
+      __syncwarp();
+    };
+    // Row statistics of the two column slices -> statistics of the whole row.  Every thread mails (mean, M2) of its
+    // slice into its partner's first h buffer (idle at that point: all of the partner's stores have read their
+    // buffers before the tile ends, and no h is staged before the statistics are known), all warps meet on an
+    // mbarrier (bounded wait), and each thread reads its own mailbox.  The combination is symmetric, so both threads of
+    // a row get bit-identical mean / rstd.
+    auto combine_stats = [&](int which, float pivot_, float sum_, float sq_, float& mean_, float& rstd_) -> bool {
+      constexpr float n_s = static_cast<float>(N / kSlices);
+      const float m_s = sum_ / n_s;                              // mean of (x - pivot) over the slice
+      const float mean_s = pivot_ + m_s;
+      const float m2_s = fmaxf(sq_ - sum_ * m_s, 0.f);           // sum of squared deviations from the slice mean
+      *reinterpret_cast<float2*>(partner_hbuf + which * 256 + lane * 8) = make_float2(mean_s, m2_s);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&stat_bar[which]);
+      if (!ptx::mbar_wait(&stat_bar[which], tile_phase, abort_flag)) return false;
+      const float2 o = *reinterpret_cast<const float2*>(hbuf + which * 256 + lane * 8);
+      const float delta = mean_s - o.x;
+      mean_ = 0.5f * (mean_s + o.x);
+      const float m2 = (m2_s + o.y) + delta * delta * (0.5f * n_s);
+      rstd_ = rsqrtf(m2 / static_cast<float>(N) + p.eps);
+      __syncwarp();                                              // every lane has read its mailbox before h is staged over it
+      return true;
+    };
+    // The per-column parameters (bias, gamma / beta or scale / shift) are read by every thread, 32 at a time, from
+    // warp-uniform addresses: pull their lines into L1 once, under the main loop, so that the per-chunk loads hit.
+    {
+      auto prefetch_vec = [&](const void* ptr, int bytes) {
+        if (ptr == nullptr) return;
+        const char* b = static_cast<const char*>(ptr);
+        for (int off = (ew * 32 + lane) * 128; off < bytes; off += kEpiWarps * 32 * 128)
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(b + off));
+      };
+      const int pbytes = N * (p.mode == 1 ? 4 : 2);
+      prefetch_vec(p.bias, N * 2);
+      prefetch_vec(p.w_a, pbytes);
+      prefetch_vec(p.b_a, pbytes);
+      prefetch_vec(p.w_b, N * 2);
+      prefetch_vec(p.b_b, N * 2);
+    }
 
     for (int pair = first_pair; ok && pair < p.num_pairs; pair += num_clusters) {
-      const int row0 = pair * 2 * BM + static_cast<int>(cta_rank) * BM + q * 32;   // first row of this warp
-      const bool warp_live = row0 < p.M;           // a warp wholly past M neither loads nor stores (TMA clips partial ones)
+      const int row0 = pair * 2 * BM + static_cast<int>(cta_rank) * BM + q * 32;   // first row of this warp (a 32-row band)
+      const bool warp_live = row0 < p.M;           // a band wholly past M has no storage: it neither loads nor stores
       const uint32_t t_acc = tmem_base + lane_base;
+      const bool use_rin = p.res_in != nullptr && warp_live;
+      const bool store_res = p.res_out != nullptr && warp_live;
+      const int band = row0 >> 5;
+      // this thread's pieces of residual block (band, c): float4 index j*32 + lane, j = 0..7
+      auto res_ptr = [&](const float* base, int c) { return base + res_block_offset(band, c, kChunks) + lane * 4; };
+      float4 nxt[8];
+      if (use_rin) {                               // the first block travels under the main loop
+        const float* src = res_ptr(p.res_in, c_lo);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) nxt[j] = ld_res(src + j * 128);
+      }
 
-      // residual prefetch for chunks 0 and 1: lands under the main loop
-      auto rin_issue = [&](int c) {
-        if (p.has_res_in && warp_live && lane == 0) {
-          const int b = c % kF32Bufs;
-          ptx::mbar_expect_tx(&my_rin[b], 4096);
-          tma_load_box(fbuf + b * 4096, &tmap_rin, c * kChunk, row0, &my_rin[b]);
-        }
-      };
-      // all earlier TMA stores of this warp have finished reading shared memory (buffers of the previous tile)
-      if (lane == 0) ptx::bulk_wait_group_read<0>();
-      __syncwarp();
-      rin_issue(0);
-      if (kChunks > 1) rin_issue(1);
-
-      if (!ptx::mbar_wait(tfull_bar, tfull_phase, abort_flag)) { ok = false; break; }
-      tfull_phase ^= 1u;
+      if (!ptx::mbar_wait(tfull_bar, tile_phase, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
+      if (ew == 0 && lane == 0) stamp(p, 4);
 
-      // ---------------- pass 1: s = res + alpha * (acc + bias), statistics about the first value ----------------
+      // ---------------- pass 1: s = res + alpha * (acc + bias), statistics about the slice's first value ----------------
       float pivot = 0.f, sum = 0.f, sq = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
-        const int b = c % kF32Bufs;
-        // the buffer chunk c+2 will land in was last stored from by chunk c-2: all but the latest store have been read
-        if (lane == 0) ptx::bulk_wait_group_read<1>();
-        __syncwarp();
-        if (c + 2 < kChunks) rin_issue(c + 2);
+      for (int i = 0; i < kLocal; ++i) {
+        const int c = c_lo + i;
         uint32_t r[32];
         ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
         float s[32];
-        if (p.has_res_in && warp_live) {
-          if (!ptx::mbar_wait(&my_rin[b], (rin_phase >> b) & 1u, abort_flag)) { ok = false; break; }
-          rin_phase ^= 1u << b;
-          f32_row_load(b, s);
+        if (use_rin) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { s[4 * j] = nxt[j].x; s[4 * j + 1] = nxt[j].y; s[4 * j + 2] = nxt[j].z; s[4 * j + 3] = nxt[j].w; }
+          if (i + 1 < kLocal) {                    // the next block is in flight while this one is processed
+            const float* src = res_ptr(p.res_in, c + 1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) nxt[j] = ld_res(src + j * 128);
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[i] = 0.f;
+          for (int k = 0; k < 32; ++k) s[k] = 0.f;
         }
+        float bb[32];
+        if (bias) load_params32(bias + c * kChunk, bb);
         ptx::tmem_ld_wait();
         if (bias) {
-          float bb[32];
-          load_params32(bias + c * kChunk, bb);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[i] = fmaf(p.alpha, u2f(r[i]) + bb[i], s[i]);
+          for (int k = 0; k < 32; ++k) s[k] = fmaf(p.alpha, u2f(r[k]) + bb[k], s[k]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[i] = fmaf(p.alpha, u2f(r[i]), s[i]);
+          for (int k = 0; k < 32; ++k) s[k] = fmaf(p.alpha, u2f(r[k]), s[k]);
+        }
+        if (store_res && p.mode != 2) {
+          float* dst = const_cast<float*>(res_ptr(p.res_out, c));
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(dst + j * 128) = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
         }
         if (p.mode == 1) {
           // affine pre-norm: no statistics, h leaves in this pass
@@ -339,48 +389,43 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           load_params32(static_cast<const float*>(p.w_a) + c * kChunk, sc);
           load_params32(static_cast<const float*>(p.b_a) + c * kChunk, sh);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = fmaf(s[i], sc[i], sh[i]);
-          h_row_store(c % kHBufs, o);
+          for (int k = 0; k < 32; ++k) o[k] = fmaf(s[k], sc[k], sh[k]);
+          uint8_t* hb = hbuf + (i & 1) * 2048;
+          h_buffer_free();
+          h_row_store(hb, o);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (warp_live) ptx::tma_store_3d(&tmap_h, hb, c * kChunk, row0, 0);
+            ptx::bulk_commit_group();
+          }
         } else {
-          if (c == 0) pivot = s[0];
+          if (i == 0) pivot = s[0];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float d = s[i] - pivot;
+          for (int k = 0; k < 32; ++k) {
+            const float d = s[k] - pivot;
             sum += d;
             sq = fmaf(d, d, sq);
           }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = f2u(s[i]);
+          for (int k = 0; k < 32; ++k) r[k] = f2u(s[k]);
           ptx::tmem_st_32x32(t_acc + c * kChunk, r);
         }
-        const bool store_res = p.has_res_out && p.mode != 2;
-        if (store_res) f32_row_store(b, s);
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && warp_live) {
-          if (store_res) ptx::tma_store_3d(&tmap_rout, fbuf + b * 4096, c * kChunk, row0, 0);
-          if (p.mode == 1) ptx::tma_store_3d(&tmap_h, hbuf + (c % kHBufs) * 2048, c * kChunk, row0, 0);
-        }
-        if (lane == 0) ptx::bulk_commit_group();   // one group per chunk (possibly empty) keeps the wait counts uniform
       }
-      if (!ok) break;
+      if (ew == 0 && lane == 0) stamp(p, 5);
 
       if (p.mode != 1) {
-        const float inv_n = 1.f / static_cast<float>(N);
         ptx::tmem_st_wait();                       // pass 1's writes of s are in TMEM before anything reads them back
-        // LayerNorm of the row held in TMEM: mean / rstd from the sums about the pivot, then gamma / beta.
-        float mean = pivot + sum * inv_n;
-        float rstd = rsqrtf(fmaxf(sq * inv_n - (sum * inv_n) * (sum * inv_n), 0.f) + p.eps);
+        float mean, rstd;
+        if (!combine_stats(0, pivot, sum, sq, mean, rstd)) { ok = false; break; }
         const T* g1 = static_cast<const T*>(p.w_a);
         const T* b1 = static_cast<const T*>(p.b_a);
         if (p.mode == 2) {
           // ---------------- pass 2 (mode 2): res_out = LN_a(s), kept in TMEM, statistics of it ----------------
           float pivot2 = 0.f, sum2 = 0.f, sq2 = 0.f;
 #pragma unroll 1
-          for (int c = 0; c < kChunks; ++c) {
-            const int b = c % kF32Bufs;
-            if (lane == 0) ptx::bulk_wait_group_read<1>();
-            __syncwarp();
+          for (int i = 0; i < kLocal; ++i) {
+            const int c = c_lo + i;
             uint32_t r[32];
             ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
             float gg[32], bb[32], v[32];
@@ -388,39 +433,34 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             load_params32(b1 + c * kChunk, bb);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = fmaf((u2f(r[i]) - mean) * rstd, gg[i], bb[i]);
-            if (c == 0) pivot2 = v[0];
+            for (int k = 0; k < 32; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
+            if (i == 0) pivot2 = v[0];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float d = v[i] - pivot2;
+            for (int k = 0; k < 32; ++k) {
+              const float d = v[k] - pivot2;
               sum2 += d;
               sq2 = fmaf(d, d, sq2);
             }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = f2u(v[i]);
+            for (int k = 0; k < 32; ++k) r[k] = f2u(v[k]);
             ptx::tmem_st_32x32(t_acc + c * kChunk, r);
-            if (p.has_res_out) f32_row_store(b, v);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (p.has_res_out && warp_live) ptx::tma_store_3d(&tmap_rout, fbuf + b * 4096, c * kChunk, row0, 0);
-              ptx::bulk_commit_group();
+            if (store_res) {
+              float* dst = const_cast<float*>(res_ptr(p.res_out, c));
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(dst + j * 128) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
           }
-          mean = pivot2 + sum2 * inv_n;
-          rstd = rsqrtf(fmaxf(sq2 * inv_n - (sum2 * inv_n) * (sum2 * inv_n), 0.f) + p.eps);
+          if (ew == 0 && lane == 0) stamp(p, 6);
+          ptx::tmem_st_wait();
+          if (!combine_stats(1, pivot2, sum2, sq2, mean, rstd)) { ok = false; break; }
           g1 = static_cast<const T*>(p.w_b);
           b1 = static_cast<const T*>(p.b_b);
         }
-        ptx::tmem_st_wait();
         // ---------------- last pass: h = LN(row in TMEM), rounded once, 32 x 32 pieces out by TMA ----------------
 #pragma unroll 1
-        for (int c = 0; c < kChunks; ++c) {
-          if (lane == 0) {
-            if (p.split_out) ptx::bulk_wait_group_read<0>();
-            else ptx::bulk_wait_group_read<1>();
-          }
-          __syncwarp();
+        for (int i = 0; i < kLocal; ++i) {
+          const int c = c_lo + i;
           uint32_t r[32];
           ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
           float gg[32], bb[32], v[32];
@@ -428,17 +468,16 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           load_params32(b1 + c * kChunk, bb);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaf((u2f(r[i]) - mean) * rstd, gg[i], bb[i]);
+          for (int k = 0; k < 32; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
           if (p.split_out) {
             // h = hi + lo with hi = round16(h), lo = round16(h - hi): rows [hi | hi | lo] of a 3N-wide output
             float lo[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float hi = Elem<T>::to_f(Elem<T>::from_f(v[i]));
-              lo[i] = v[i] - hi;
-            }
-            h_row_store(0, v);
-            h_row_store(1, lo);
+            for (int k = 0; k < 32; ++k) lo[k] = v[k] - Elem<T>::to_f(Elem<T>::from_f(v[k]));
+            if (lane == 0) ptx::bulk_wait_group_read<0>();
+            __syncwarp();
+            h_row_store(hbuf, v);
+            h_row_store(hbuf + 2048, lo);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -450,23 +489,30 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               ptx::bulk_commit_group();
             }
           } else {
-            const int hb = c % kHBufs;
+            uint8_t* hb = hbuf + (i & 1) * 2048;
+            h_buffer_free();
             h_row_store(hb, v);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              if (warp_live) ptx::tma_store_3d(&tmap_h, hbuf + hb * 2048, c * kChunk, row0, 0);
+              if (warp_live) ptx::tma_store_3d(&tmap_h, hb, c * kChunk, row0, 0);
               ptx::bulk_commit_group();
             }
           }
         }
       }
-      // the accumulator columns are free again: tell the leader's MMA issuer
+      if (ew == 0 && lane == 0) stamp(p, 7);
+      // Tile done.  All of this warp's stores have read their staging buffers (the partner writes statistics into
+      // the first one during the next tile); then the accumulator columns go back to the leader's MMA issuer.
+      if (lane == 0) ptx::bulk_wait_group_read<0>();
+      __syncwarp();
+      tile_phase ^= 1u;
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar, 0));
     }
-    if (lane == 0) ptx::bulk_wait_group<0>();      // every output piece has left shared memory and landed
+    if (lane == 0) ptx::bulk_wait_group<0>();      // every h piece has landed
+    if (ew == 0 && lane == 0) stamp(p, 8);
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusGemmEpilogue);
   }
 
@@ -484,12 +530,13 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) stamp(p, 9);
 }
 
 template <int N> struct StagesFor;
-template <> struct StagesFor<512> { static constexpr int v = 3; };   // 48 KB per stage + 80 KB of epilogue staging
-template <> struct StagesFor<256> { static constexpr int v = 4; };   // 32 KB per stage
-template <> struct StagesFor<128> { static constexpr int v = 4; };   // 24 KB per stage
+template <> struct StagesFor<512> { static constexpr int v = 4; };   // 48 KB per stage + 32 KB of h staging
+template <> struct StagesFor<256> { static constexpr int v = 5; };   // 32 KB per stage
+template <> struct StagesFor<128> { static constexpr int v = 6; };   // 24 KB per stage
 
 struct Call {
   void* h_out;
@@ -514,7 +561,7 @@ int launch(const Call& c, cudaStream_t s) {
                                            S::kDynamic, cudaGetErrorString(e));
     attr_done = true;
   }
-  CUtensorMap ta, tb, trin, trout, th;
+  CUtensorMap ta, tb, th;
   const uint64_t M = static_cast<uint64_t>(c.M), K = static_cast<uint64_t>(c.K);
   {
     uint64_t dims[3] = {K, M, 1};
@@ -529,20 +576,6 @@ int launch(const Call& c, cudaStream_t s) {
     if (int rc = make_tensor_map(&tb, tma_dtype(c.dtype), 3, c.B, dims, str, box)) return rc;
   }
   {
-    uint64_t dims[3] = {static_cast<uint64_t>(N), M, 1};
-    uint64_t str[3] = {0, static_cast<uint64_t>(N) * 4, static_cast<uint64_t>(N) * 4 * M};
-    uint32_t box[3] = {kChunk, 32, 1};
-    const void* rin = c.res_in ? static_cast<const void*>(c.res_in) : static_cast<const void*>(c.res_out);
-    const void* rout = c.res_out ? static_cast<const void*>(c.res_out) : rin;
-    if (rin == nullptr) {   // neither residual operand: the maps are never used, but they must be valid objects
-      trin = ta;
-      trout = ta;
-    } else {
-      if (int rc = make_tensor_map(&trin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, rin, dims, str, box)) return rc;
-      if (int rc = make_tensor_map(&trout, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, rout, dims, str, box)) return rc;
-    }
-  }
-  {
     const uint64_t w = static_cast<uint64_t>(N) * (c.p.split_out ? 3 : 1);
     uint64_t dims[3] = {w, M, 1};
     uint64_t str[3] = {0, w * 2, w * 2 * M};
@@ -552,7 +585,7 @@ int launch(const Call& c, cudaStream_t s) {
   int64_t clusters = sm_count() / 2;
   if (c.p.num_pairs < clusters) clusters = c.p.num_pairs;
   if (clusters < 1) clusters = 1;
-  kern<<<static_cast<unsigned>(2 * clusters), kThreads, S::kDynamic, s>>>(ta, tb, trin, trout, th, c.p);
+  kern<<<static_cast<unsigned>(2 * clusters), kThreads, S::kDynamic, s>>>(ta, tb, th, c.p);
   return check_launch("gemm_add_norm_f32 launch");
 }
 
@@ -560,6 +593,7 @@ int launch(const Call& c, cudaStream_t s) {
 }  // namespace ob
 
 extern "C" {
+
 
 int oasr_b200_gemm_add_norm_supported(int64_t N, int64_t K) {
   return (N == 128 || N == 256 || N == 512) && K >= 64 && K % 8 == 0 ? 1 : 0;
@@ -595,9 +629,10 @@ int oasr_b200_gemm_add_norm_f32(void* h_out, float* res_out, const float* res_in
   p.num_k_blocks = static_cast<int>((K + BK - 1) / BK);
   p.num_pairs = static_cast<int>((M + 2 * BM - 1) / (2 * BM));
   p.bias = bias; p.alpha = static_cast<float>(alpha); p.mode = mode; p.split_out = split_out ? 1 : 0;
-  p.has_res_in = res_in != nullptr; p.has_res_out = res_out != nullptr;
+  p.res_in = res_in; p.res_out = res_out;
   p.w_a = w_a; p.b_a = b_a; p.w_b = w_b; p.b_b = b_b; p.eps = static_cast<float>(eps);
   p.status = device_status_ptr();
+  p.trace = g_trace_buffer;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
     switch (N) {

@@ -35,13 +35,30 @@ def gemm_add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_
     """``add_norm_f32`` with the sub-layer's last Linear folded in: ``y = A @ B.T + bias`` stays fp32 in tensor
     memory, ``s = res_in + alpha*y``, then the norm of ``mode`` as in :func:`add_norm_f32`.  One kernel instead of
     ``gemm`` + ``add_layer_norm_residual`` (oasr/models/conformer/model.py:722-751); needs an output width of
-    128, 256 or 512."""
+    128, 256 or 512.  ``res_in`` / ``res_out`` are fp32 buffers in the kernel's blocked layout
+    (:func:`residual_to_blocked`), ``roundup32(M) * N`` floats."""
     _need_cuda(h_out, res_out, res_in, A, B, bias)
     K, N = A.shape[-1], B.shape[0]
     M = A.numel() // K
     _lib.call("oasr_b200_gemm_add_norm_f32", _p(h_out), _p(res_out), _p(res_in), _p(A), _p(B), _p(bias), M, N, K,
               float(alpha), int(mode), _p(w_a), _p(b_a), _p(w_b), _p(b_b), float(eps), int(bool(split_out)),
               _DTYPE_ID[A.dtype], _stream(A))
+
+
+def residual_to_blocked(res: torch.Tensor) -> torch.Tensor:
+    """Row-major fp32 ``(M, N)`` -> the blocked residual layout of :func:`gemm_add_norm_f32`: rows padded to a
+    multiple of 32, 32 x 32 blocks band-major, element (row l, column 4j+e) of a block at ``(j*32 + l)*4 + e``."""
+    M, N = res.shape
+    Mp = (M + 31) // 32 * 32
+    padded = torch.zeros(Mp, N, device=res.device, dtype=torch.float32)
+    padded[:M] = res
+    return padded.view(Mp // 32, 32, N // 32, 8, 4).permute(0, 2, 3, 1, 4).contiguous().view(-1)
+
+
+def residual_from_blocked(blocked: torch.Tensor, M: int, N: int) -> torch.Tensor:
+    """Inverse of :func:`residual_to_blocked`: the first ``M`` rows as a row-major ``(M, N)`` tensor."""
+    Mp = (M + 31) // 32 * 32
+    return blocked.view(Mp // 32, N // 32, 8, 32, 4).permute(0, 3, 1, 2, 4).reshape(Mp, N)[:M].contiguous()
 
 
 def depthwise_conv1d_packed(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],

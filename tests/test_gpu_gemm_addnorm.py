@@ -12,6 +12,18 @@ from oasr_b200 import _lib, fused
 pytestmark = pytest.mark.gpu
 
 
+def test_blocked_residual_layout_round_trip_and_element_rule():
+    M, N = 70, 128
+    res = torch.arange(M * N, dtype=torch.float32, device="cuda").view(M, N)
+    blk = fused.residual_to_blocked(res)
+    assert blk.numel() == 96 * N
+    assert torch.equal(fused.residual_from_blocked(blk, M, N), res)
+    for row, col in [(0, 0), (33, 5), (69, 127), (31, 96)]:
+        band, l, chunk, j, e = row // 32, row % 32, col // 32, (col % 32) // 4, col % 4
+        off = (band * (N // 32) + chunk) * 1024 + (j * 32 + l) * 4 + e
+        assert blk[off].item() == res[row, col].item()
+
+
 def _case(M, N, K, dtype, seed, with_res=True):
     g = torch.Generator().manual_seed(seed)
     A = torch.randn(M, K, generator=g).to(dtype)
@@ -38,14 +50,16 @@ def _run(A, B, bias, res, alpha, mode, w1, b1, w2, b2, eps, split=False, in_plac
     M, N = A.size(0), B.size(0)
     dev = "cuda"
     h = torch.full((M, N * (3 if split else 1)), float("nan"), device=dev, dtype=A.dtype)
-    res_in = None if res is None else res.to(dev)
-    res_out = res_in if (in_place and res_in is not None) else torch.full((M, N), float("nan"), device=dev)
+    # the residual stream travels in the kernel's blocked layout
+    res_in = None if res is None else fused.residual_to_blocked(res.to(dev))
+    Mp = (M + 31) // 32 * 32
+    res_out = res_in if (in_place and res_in is not None) else torch.full((Mp * N,), float("nan"), device=dev)
     wa, ba = (w1.float().to(dev), b1.float().to(dev)) if mode == 1 else (w1.to(dev), b1.to(dev))
     fused.gemm_add_norm_f32(h, res_out, res_in, A.to(dev), B.to(dev), None if bias is None else bias.to(dev), alpha, mode,
                             wa, ba, w2.to(dev) if mode == 2 else None, b2.to(dev) if mode == 2 else None, eps, split)
     torch.cuda.synchronize()
     assert ob.device_status() == 0
-    return res_out.cpu(), h.float().cpu()
+    return fused.residual_from_blocked(res_out, M, N).cpu(), h.float().cpu()
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -102,7 +116,7 @@ def test_at_benchmark_size_equals_gemm_then_add_norm(N, K, mode):
     torch.testing.assert_close(got_h, want_h.to(dtype).float(), rtol=2e-2, atol=2e-2)
     # the unfused composition on the same inputs
     dev = "cuda"
-    y = ob.gemm(A.to(dev), B.to(dev), bias.to(dev))
+    y = ob.gemm(A.to(dev), B.to(dev), bias.to(dev))   # (this path keeps its residual row-major)
     h2 = torch.empty(M, N, device=dev, dtype=dtype)
     r2 = res.to(dev)
     wa, ba = (w1.float().to(dev), b1.float().to(dev)) if mode == 1 else (w1.to(dev), b1.to(dev))
