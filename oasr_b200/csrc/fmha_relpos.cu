@@ -15,9 +15,10 @@
 // Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
 // once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
 // are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
-// common case costs nothing -- then exp2 (every fourth one as a degree-3 polynomial on the FMA pipe, because the
-// 16-lane MUFU unit is this kernel's busiest), bf16/fp16 P into swizzled shared memory.  O leaves TMEM once, at
-// the end, scaled by 1 / sum.
+// common case costs nothing -- then exp2 (optionally a share of them as a degree-3 polynomial on the FMA pipe,
+// off by default: measured slower), bf16/fp16 P into swizzled shared memory.  O leaves TMEM once, at the end,
+// scaled by 1 / sum.  K | pos of tile j+2 is requested as soon as Q.K^T of tile j has finished, V of tile j+1 when
+// P.V of tile j-1 has: the two have separate stage barriers.
 // Only the length mask exists here (keys >= segment length); bias, causal masks, key starts, paged K/V and
 // head_dim 128 stay on the general kernel in fmha.cu.  Every wait is bounded.
 #include <cuda.h>
@@ -30,7 +31,10 @@
 #include "tma_host.cuh"
 
 namespace ob {
-int g_fmha_relpos_path = 1;  // 1 = this kernel for the packed relative-position form; 0 = the general kernel ("fmha_relpos_path")
+int g_fmha_relpos_path = 1;
+int g_fmha_poly = 0;         // exponentials per four on the FMA pipe in the packed relative-position kernel ("fmha_poly": 0, 1, 2);
+                            // measured on B200 (config-2 batch): 66.0 / 66.9 / 68.9 us per launch for 0 / 1 / 2 -- the kernel is
+                            // bound by instruction issue, not by the MUFU unit, so the extra FMA work does not pay  // 1 = this kernel for the packed relative-position form; 0 = the general kernel ("fmha_relpos_path")
 
 namespace fmha_relpos {
 
@@ -42,7 +46,7 @@ constexpr int kVBytes = BKV * 128;
 constexpr int kPBytes = BQ * 128;               // 128 rows x 64 keys
 constexpr int kOffQ = 0, kOffK = kOffQ + kQBytes, kOffV = kOffK + 2 * kKBytes, kOffP = kOffV + 2 * kVBytes;
 constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kNumBars = 11;
+constexpr int kNumBars = 15;
 constexpr int kSmemDynamic = kOffBar + kNumBars * 8 + 16 + 1024;
 constexpr uint32_t kTmemCols = 256, kColS = 0, kColO = 128;
 constexpr float kLazyLog2 = 8.f;   // rescale only when the row maximum grows by more than 2^8
@@ -88,7 +92,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-template <typename T>
+// kPoly: how many of every four exponentials run as a polynomial on the FMA pipe instead of the MUFU unit (0, 1 or 2)
+template <typename T, int kPoly>
 __global__ void __launch_bounds__(kThreads, 2)
 fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q2,
                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_pos,
@@ -117,12 +122,14 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint8_t* sP = smem + kOffP;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* k_full = bars + 1;     // [2]  K | pos stage landed
+  uint64_t* k_empty = bars + 3;    // [2]  Q.K^T of the stage's tile finished: the stage may be refilled (long before its V)
   uint64_t* s_full = bars + 5;     // [2]
   uint64_t* s_free = bars + 7;     // [2]
   uint64_t* p_full = bars + 9;     // [1]
   uint64_t* po_done = bars + 10;   // P.V of a tile has been accumulated into O: O is stable and P may be rewritten
+  uint64_t* v_full = bars + 11;    // [2]  V stage landed
+  uint64_t* v_empty = bars + 13;   // [2]  P.V of the stage's tile finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -130,8 +137,10 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(&kv_full[i], 1);
-      ptx::mbar_init(&kv_empty[i], 1);
+      ptx::mbar_init(&k_full[i], 1);
+      ptx::mbar_init(&k_empty[i], 1);
+      ptx::mbar_init(&v_full[i], 1);
+      ptx::mbar_init(&v_empty[i], 1);
       ptx::mbar_init(&s_full[i], 1);
       ptx::mbar_init(&s_free[i], BQ);
     }
@@ -155,13 +164,16 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // =================== TMA producer + MMA issuer (one thread) ===================
     if (lane == 0) {
       bool ok = true;
-      auto load_kv = [&](int t, int b) {
+      auto load_k = [&](int t, int b) {
         const int key0 = t * BKV;
-        ptx::mbar_expect_tx(&kv_full[b], kKBytes + kVBytes);
+        ptx::mbar_expect_tx(&k_full[b], kKBytes);
         uint8_t* dk = sK + b * kKBytes;
-        ptx::tma_load_4d(dk, &map_k, 0, row0 + key0, h, 0, &kv_full[b]);
-        ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, h, 0, &kv_full[b]);
-        ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, row0 + key0, h, 0, &kv_full[b]);
+        ptx::tma_load_4d(dk, &map_k, 0, row0 + key0, h, 0, &k_full[b]);
+        ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, h, 0, &k_full[b]);
+      };
+      auto load_v = [&](int t, int b) {
+        ptx::mbar_expect_tx(&v_full[b], kVBytes);
+        ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, row0 + t * BKV, h, 0, &v_full[b]);
       };
       auto issue_qk = [&](int b) {   // S[b] = [q+u | q+v] . [k | pos]^T : K = 128 in eight steps of 16
         const uint32_t a_addr = ptx::smem_u32(sQ);
@@ -174,6 +186,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           ptx::umma_f16(d_tmem, adesc, bdesc, kIdescQK, kk != 0 ? 1u : 0u);
         }
         ptx::umma_commit(&s_full[b]);
+        ptx::umma_commit(&k_empty[b]);
       };
       auto issue_pv = [&](int b, bool first) {   // O (+)= P . V_b : K = 64 keys in four steps of 16
         const uint32_t a_addr = ptx::smem_u32(sP);
@@ -186,39 +199,49 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           ptx::umma_f16(d_tmem, adesc, bdesc, kIdescPV, (!first || kk != 0) ? 1u : 0u);
         }
         ptx::umma_commit(po_done);
-        ptx::umma_commit(&kv_empty[b]);
+        ptx::umma_commit(&v_empty[b]);
       };
       ptx::mbar_expect_tx(q_full, kQBytes);
       ptx::tma_load_4d(sQ, &map_q, 0, row0 + q0, h, 0, q_full);
       ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, row0 + q0, h, 0, q_full);
-      load_kv(0, 0);
-      if (nkv > 1) load_kv(1, 1);
-      ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&kv_full[0], 0, abort_flag);
+      load_k(0, 0);
+      load_v(0, 0);
+      if (nkv > 1) {
+        load_k(1, 1);
+        load_v(1, 1);
+      }
+      ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&k_full[0], 0, abort_flag);
       if (ok) {
         ptx::tc_fence_after_sync();
         issue_qk(0);
       }
+      // Tile j: scores of tile j+1 are issued first (they only need S[nb] back), then the operand refills -- K | pos
+      // of tile j+2 as soon as Q.K^T of tile j has finished (two tiles ahead of its use), V of tile j+1 once P.V of
+      // tile j-1 has -- and last P.V of tile j, which waits for the softmax.
       for (int j = 0; ok && j < nkv; ++j) {
-        const int b = j & 1;
+        const int b = j & 1, nb = b ^ 1;
         const uint32_t ph = (j >> 1) & 1u;
         if (j + 1 < nkv) {
-          const int nb = (j + 1) & 1;
           const uint32_t nph = ((j + 1) >> 1) & 1u;
-          // S[nb] was last read by the softmax of tile j-1
-          ok = ptx::mbar_wait(&kv_full[nb], nph, abort_flag) && ptx::mbar_wait(&s_free[nb], nph ^ 1u, abort_flag);
+          ok = ptx::mbar_wait(&k_full[nb], nph, abort_flag) && ptx::mbar_wait(&s_free[nb], nph ^ 1u, abort_flag);
           if (!ok) break;
           ptx::tc_fence_after_sync();
           issue_qk(nb);
+          if (j >= 1) {   // stage nb held V of tile j-1
+            ok = ptx::mbar_wait(&v_empty[nb], ((j - 1) >> 1) & 1u, abort_flag);
+            if (!ok) break;
+            load_v(j + 1, nb);
+          }
         }
-        ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(j) & 1u, abort_flag);   // P of tile j written
+        if (j + 2 < nkv) {
+          ok = ptx::mbar_wait(&k_empty[b], ph, abort_flag);
+          if (!ok) break;
+          load_k(j + 2, b);
+        }
+        ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(j) & 1u, abort_flag) && ptx::mbar_wait(&v_full[b], ph, abort_flag);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         issue_pv(b, j == 0);
-        if (j + 2 < nkv) {
-          ok = ptx::mbar_wait(&kv_empty[b], ph, abort_flag);
-          if (!ok) break;
-          load_kv(j + 2, b);
-        }
       }
       if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
     }
@@ -245,14 +268,15 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s_free[b]);          // the scores live in registers now: S[b] may take tile j+2
       const bool full = key0 + BKV <= kv_len;   // tiles inside the valid keys need no mask
-      float tile_max = kNegInf;
+      float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};   // four independent chains
       if (full) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) tile_max = fmaxf(tile_max, key0 + i < kv_len ? __uint_as_float(v[i]) : kNegInf);
+        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], key0 + i < kv_len ? __uint_as_float(v[i]) : kNegInf);
       }
+      float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tile_max *= p.scale_log2;   // the scale is positive
       if (j == 3 && r == 0) stamp(p, 52);
       // Lazy rescale: the reference maximum moves only when this tile exceeds it by more than 2^kLazyLog2.
@@ -271,9 +295,11 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
         float e0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
-        float e1 = ex2_fast(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run));
+        const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run);
+        const float x3 = fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_run);
+        float e1 = kPoly >= 2 ? ex2_poly(x1) : ex2_fast(x1);
         float e2 = ex2_fast(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m_run));
-        float e3 = ex2_poly(fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_run));
+        float e3 = kPoly >= 1 ? ex2_poly(x3) : ex2_fast(x3);
         if (!full) {   // P of keys past the end is zero (V rows there hold other segments' finite values)
           e0 = key0 + i < kv_len ? e0 : 0.f;
           e1 = key0 + i + 1 < kv_len ? e1 : 0.f;
@@ -373,19 +399,19 @@ int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t 
   p.cu = cu_seqlens; p.out = out; p.status = device_status_ptr();
   p.trace = g_trace_buffer; p.trace_seg = 0;
   dim3 grid((unsigned)((max_seqlen + BQ - 1) / BQ), (unsigned)H, (unsigned)num_segs);
-  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
-    auto kern = fmha_relpos64_kernel<T>;
-    static bool attr_done = false;
-    if (!attr_done) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDynamic);
-      if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-      if (e != cudaSuccess)
-        return set_error(OASR_ERR_CUDA, "fmha_varlen_relpos: cannot reserve %d bytes of shared memory: %s", kSmemDynamic,
-                         cudaGetErrorString(e));
-      attr_done = true;
-    }
+  auto launch_one = [&](auto kern) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDynamic);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e != cudaSuccess)
+      return set_error(OASR_ERR_CUDA, "fmha_varlen_relpos: cannot reserve %d bytes of shared memory: %s", kSmemDynamic,
+                       cudaGetErrorString(e));
     launch_pdl(kern, grid, dim3(kThreads), kSmemDynamic, stream, mq, mq2, mk, mp, mv, p);
     return check_launch("fmha_varlen_relpos (two CTAs per SM) launch");
+  };
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+    if (g_fmha_poly <= 0) return launch_one(fmha_relpos64_kernel<T, 0>);
+    if (g_fmha_poly == 1) return launch_one(fmha_relpos64_kernel<T, 1>);
+    return launch_one(fmha_relpos64_kernel<T, 2>);
   });
 }
 

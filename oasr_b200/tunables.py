@@ -8,6 +8,8 @@ an in-place row log-softmax kernel (fp32 output only).
 ``fmha_chunk_path``: 1 (default) runs paged rel-pos attention with <= 16 query frames on the warp-per-(stream, head)
 kernel, 0 always on the 128-row tcgen05 kernel.
 ``fmha_relpos_path``: 1 (default) runs packed relative-position attention on the two-CTAs-per-SM kernel, 0 on the general one.
+``fmha_poly``: how many of every four exponentials of the packed relative-position attention kernel run as a cubic on
+the FMA pipe instead of the MUFU unit: 0 (default; measured fastest), 1 or 2.
 ``fused_addnorm``: 1 (default) runs the last Linear of every Conformer sub-layer fused with the residual add and the
 following norm (widths 128 / 256 / 512), 0 as gemm + add_norm_f32.
 ``pdl``: 1 launches the hot kernels with programmatic stream serialisation, 0 (default) in plain stream order.
