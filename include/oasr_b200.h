@@ -611,6 +611,27 @@ OASR_API int oasr_b200_gather_rows(void* out, const void* in, const int64_t* ind
 OASR_API int oasr_b200_scatter_rows(void* out, const void* in, const int64_t* index, int64_t n_in,
                                     int64_t row_bytes, int64_t out_rows, void* stream);
 
+/* ---- feature front end ---------------------------------------------------- */
+/* Kaldi-compatible log-mel FBANK features with optional global CMVN in one
+ * kernel: snip_edges framing, per-frame DC removal, pre-emphasis (first sample
+ * replicated), analysis window, zero-padded n_fft-point power spectrum, mel
+ * filterbank, log(max(., log_floor)), then (x - cmvn_mean) * cmvn_istd.
+ * Replaces the launcher chain stft_frame / rfft_power / mel_log
+ * (csrc/features.cu:39-205, composed in oasr/features/batched.py:171-206) and
+ * cmvn (oasr/functionals/norm.py:338-360).  waveforms (B, T) fp32; lengths (B)
+ * int32 samples (nullable: every row is T long); window (frame_length) fp32;
+ * mel_mat (num_mel, n_fft/2+1) fp32 with mel_lo / mel_hi (num_mel) int32 = the
+ * non-zero bin range [lo, hi) of every filter; out (B, num_frames, num_mel)
+ * fp32, frames that do not lie wholly inside their utterance are zeros.
+ * n_fft: a power of two in [64, 2048], >= frame_length. */
+OASR_API int oasr_b200_fbank(float* out, const float* waveforms, const int32_t* lengths /*nullable*/,
+                             const float* window, const float* mel_mat, const int32_t* mel_lo,
+                             const int32_t* mel_hi, const float* cmvn_mean /*nullable*/,
+                             const float* cmvn_istd /*nullable*/, int64_t B, int64_t T,
+                             int64_t num_frames, int64_t frame_length, int64_t frame_shift,
+                             int64_t n_fft, int64_t num_mel, double preemph, double log_floor,
+                             void* stream);
+
 /* ---- encoder layer stack (native executor) ------------------------------ */
 /* Device pointers to the prepared weights of one Conformer encoder layer
  * (ConformerEncoderLayer, oasr/models/conformer/model.py:499-752).  16-bit
