@@ -555,6 +555,19 @@ OASR_API int oasr_b200_relshift_bias(void* out, const void* bd, const int32_t* l
                                      int64_t T, int64_t ld, int64_t ld_out, int64_t bd_stride_b /*0 = H*T*ld*/,
                                      int64_t bd_stride_h /*0 = T*ld*/, double scale, int64_t chunk,
                                      int64_t left_chunks, double floor_value, int dtype, void* stream);
+/* Streaming form of the same bias (NemotronRelPositionAttention.forward_chunk and NemotronEncoder._streaming_mask,
+ * oasr/models/nemotron/encoder.py:362-410, 680-720): B streams with Tq new query frames each; the keys of stream b
+ * are its cached[b] cached frames followed by the chunk, and offsets[b] encoder frames were emitted before this chunk.
+ * bd (H, B*Tq, ld) holds the position-biased queries against the projected relative table built for Lmax >=
+ * max(cached) + Tq (row p = distance Lmax-1-p; ld >= 2*Lmax-1).  out (B, H, Tq, ld_out) 16-bit: key j < cached[b]+Tq
+ * gets bd[distance cached[b] + i - j] * scale when it lies in the query's chunked-limited window over ABSOLUTE frame
+ * positions, else floor_value; columns past the stream's keys get floor_value.  The reference prefills a window of
+ * constant length with masked placeholders instead; the visible keys and their distances are the same. */
+OASR_API int oasr_b200_relshift_bias_stream(void* out, const void* bd, const int32_t* cached,
+                                            const int32_t* offsets, int64_t B, int64_t H, int64_t Tq,
+                                            int64_t ld, int64_t ld_out, int64_t Lmax, int64_t bd_stride_h,
+                                            double scale, int64_t chunk, int64_t left_chunks,
+                                            double floor_value, int dtype, void* stream);
 
 /* Packed form of the same bias: bd (H, total, ld >= 2T-1) holds the position scores of every packed row (rows
  * [cu_seqlens[s], cu_seqlens[s+1]) are stream s, at most T frames), and segment s of out is (H, len_s, roundup8(len_s))

@@ -153,7 +153,67 @@ __global__ void __launch_bounds__(256) relshift_bias_packed_kernel(T* __restrict
 }  // namespace
 }  // namespace ob
 
+namespace ob {
+// Streaming form of the same bias: B streams, Tq new query frames each, keys = the stream's cached frames followed by
+// the chunk.  One warp per output row (b, h, i).
+template <typename T>
+__global__ void __launch_bounds__(256) relshift_bias_stream_kernel(T* __restrict__ out, const T* __restrict__ bd,
+                                                                   const int32_t* __restrict__ cached,
+                                                                   const int32_t* __restrict__ offsets, int B, int H, int Tq,
+                                                                   int ld, int ld_out, int Lmax, int64_t bd_sh, float scale,
+                                                                   int chunk, int left_chunks, float floor_v) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = static_cast<int64_t>(B) * H * Tq;
+  const int64_t wstride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const T floor_t = Elem<T>::from_f(floor_v);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += wstride) {
+    const int64_t r = row / Tq;               // b * H + h
+    const int i = static_cast<int>(row - r * Tq);
+    const int b = static_cast<int>(r / H);
+    const int h = static_cast<int>(r - static_cast<int64_t>(b) * H);
+    const int c = cached[b];
+    const int keys = c + Tq;
+    const int q_abs = offsets[b] + i;
+    const int k_abs0 = offsets[b] - c;        // absolute frame of key 0 (never negative: only real frames are cached)
+    const int qc = q_abs / chunk;
+    // distance of key j from query i is c + i - j; the projected table has the embedding of distance d at row Lmax - 1 - d
+    const T* src = bd + h * bd_sh + (static_cast<int64_t>(b) * Tq + i) * ld + (Lmax - 1 - c - i);
+    T* dst = out + row * ld_out;
+    for (int j = lane; j < ld_out; j += 32) {
+      T v = floor_t;
+      if (j < keys) {
+        const int diff = qc - (k_abs0 + j) / chunk;
+        if (diff >= 0 && diff <= left_chunks) v = Elem<T>::from_f(Elem<T>::to_f(src[j]) * scale);
+      }
+      dst[j] = v;
+    }
+  }
+}
+}  // namespace ob
+
 extern "C" {
+
+int oasr_b200_relshift_bias_stream(void* out, const void* bd, const int32_t* cached, const int32_t* offsets, int64_t B,
+                                   int64_t H, int64_t Tq, int64_t ld, int64_t ld_out, int64_t Lmax, int64_t bd_stride_h,
+                                   double scale, int64_t chunk, int64_t left_chunks, double floor_value, int dtype,
+                                   void* stream) {
+  using namespace ob;
+  OB_REQUIRE(B >= 0 && H > 0 && Tq > 0 && Lmax >= Tq && ld >= 2 * Lmax - 1 && ld_out > 0 && chunk > 0 && left_chunks >= 0,
+             OASR_ERR_INVALID, "relshift_bias_stream: bad shape");
+  if (B == 0) return OASR_OK;
+  OB_REQUIRE(out && bd && cached && offsets, OASR_ERR_INVALID, "relshift_bias_stream: null pointer argument");
+  const int64_t rows = B * H * Tq;
+  int64_t g = (rows + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (g > cap) g = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return OB_DISPATCH_HALF(dtype, T_, [&]() -> int {
+    relshift_bias_stream_kernel<T_><<<static_cast<unsigned>(g), 256, 0, s>>>(
+        static_cast<T_*>(out), static_cast<const T_*>(bd), cached, offsets, (int)B, (int)H, (int)Tq, (int)ld, (int)ld_out,
+        (int)Lmax, bd_stride_h ? bd_stride_h : B * Tq * ld, (float)scale, (int)chunk, (int)left_chunks, (float)floor_value);
+    return check_launch("relshift_bias_stream launch");
+  });
+}
 
 int oasr_b200_relshift_bias_packed(void* out, const void* bd, const int32_t* cu_seqlens, const int64_t* bias_offsets,
                                    int64_t num_segs, int64_t H, int64_t total, int64_t T, int64_t ld, double scale,

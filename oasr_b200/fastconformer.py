@@ -44,6 +44,7 @@ class FastConformerLayers:
         self.qkind = {None: 0, "fp8": 1, "int8": 2}[quant]
         self._q8 = {}
         self._tables = {}
+        self._stream_tables = {}
         self.C, self.H, self.D, self.F, self.L, self.K = hidden, heads, hidden // heads, ffn, layers, kernel
         self.left, self.right, self.eps = sliding_window - 1, lookahead, eps
         self.device, self.dtype = torch.device(device), dtype
@@ -172,6 +173,98 @@ class FastConformerLayers:
                 out = torch.empty(M, C, device=res.device, dtype=torch.float32)
                 fused.add_norm_f32(h, out, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *lw["norm_out"], eps=self.eps)
         return out
+
+    # ---- streaming: one chunk of B streams over paged keys / values and cached conv tails ----
+    def new_streaming_cache(self, max_streams: int, chunk_frames: int = 16, block_size: int = 16, seed=0):
+        """Page pools, block table and conv-tail buffers for ``max_streams`` concurrent streams.  The cached history is
+        capped at the trained left context rounded up to whole pages."""
+        from .streaming import StreamingCache
+
+        chunk = self.right + 1
+        if chunk_frames % chunk:
+            raise ValueError(f"a streaming step must be a whole number of trained attention chunks ({chunk} frames)")
+        max_past = (max(self.left, 0) + block_size - 1) // block_size * block_size
+        return StreamingCache(self.L, self.H, self.D, self.C, self.K, max_streams, max_past, chunk_frames, block_size,
+                              self.device, self.dtype, seed)
+
+    def _stream_rel_k(self, i: int, lmax: int) -> torch.Tensor:
+        """``relative_k_proj`` of the sinusoid table for ``lmax`` key positions, layer ``i``: constant per cache geometry."""
+        key = (i, lmax)
+        hit = self._stream_tables.get(key)
+        if hit is None:
+            hit = OF.gemm(self._position_table(lmax), self.layers[i]["rel"])          # (roundup8(2*lmax-1), C)
+            self._stream_tables[key] = hit
+        return hit
+
+    def forward_chunk(self, hidden: torch.Tensor, slots, cache) -> torch.Tensor:
+        """One streaming step: ``hidden (B, T_q, C)`` post-subsampling states of the streams in ``slots`` ->
+        ``(B, T_q, C)`` fp32, the layer stack of NemotronEncoder.forward_chunk_paged
+        (oasr/models/nemotron/encoder.py:269-298, 362-410, 585-720).  Keys / values of the chunk are appended to the
+        streams' pages, attention runs over cached frames + chunk with the Transformer-XL bias at the true
+        distances and the chunked-limited window over absolute frame positions, and the conv module continues from
+        each stream's post-GLU tail.  ``cache`` comes from :meth:`new_streaming_cache`; only real frames are cached
+        (the reference's prefilled placeholders are masked keys, which contribute nothing)."""
+        import ctypes
+
+        from . import _lib
+        from .cache import write_kv_chunk
+        from .functional import _DTYPE_ID, _p, _stream
+
+        if not hidden.is_cuda:
+            raise RuntimeError("hidden must be a CUDA tensor (oasr_b200 has no CPU path)")
+        B, Tq, C = hidden.shape
+        slots = list(slots)
+        if Tq != cache.chunk or len(slots) != B:
+            raise RuntimeError(f"expected {len(slots)} streams x {cache.chunk} frames, got {B} x {Tq}")
+        H, D, SL = self.H, self.D, self.K - 1
+        table, cached, total, pos_start, slot_ids = cache.prepare(slots)
+        offsets = pos_start + cached                                   # encoder frames emitted before this chunk
+        lmax = cache.max_past + Tq
+        tk = table.size(1) * cache.block_size
+        chunk = self.right + 1
+        left_chunks = self.left // chunk if self.left >= 0 else lmax
+        M = B * Tq
+        res = hidden.reshape(M, C).to(torch.float32, copy=True).contiguous()
+        h = torch.empty(M, C, device=res.device, dtype=self.dtype)
+        fused.add_norm_f32(h, None, res, None, 0.0, fused.ADD_NORM_LN, *self.layers[0]["norm_feed_forward1"], eps=self.eps)
+        out = None
+        for i, lw in enumerate(self.layers):
+            w1, b1, w2, b2 = lw["feed_forward1"]
+            y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
+            fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN, *lw["norm_self_att"], eps=self.eps)
+            # --- attention over [cached pages ; chunk] ---
+            qkv4 = self._linear(h, *lw["qkv4"]).view(B, Tq, 4, H, D)
+            write_kv_chunk(cache.k_pool[i], cache.v_pool[i], table, qkv4[:, :, 2].permute(0, 2, 1, 3),
+                           qkv4[:, :, 3].permute(0, 2, 1, 3), cached)
+            rel_k = self._stream_rel_k(i, lmax)
+            Pp = rel_k.size(0)
+            bd = fused.bmm_strided(qkv4.view(M, 4, H, D)[:, 1].permute(1, 0, 2), rel_k.view(Pp, H, D).permute(1, 0, 2))   # (H, M, Pp)
+            bias = torch.empty(B, H, Tq, tk, device=res.device, dtype=self.dtype)
+            _lib.call("oasr_b200_relshift_bias_stream", _p(bias), _p(bd), _p(cached), _p(offsets), B, H, Tq, Pp, tk, lmax,
+                      bd.stride(0), D ** -0.5, chunk, left_chunks, MASK_FLOOR, _DTYPE_ID[self.dtype], _stream(bd))
+            att = fmha(qkv4[:, :, 0].permute(0, 2, 1, 3), cache.k_pool[i], cache.v_pool[i], softmax_scale=D ** -0.5,
+                       attn_bias=bias, cache_seqlens=total, block_table=table, token_major=True)
+            y = self._linear(att.reshape(M, C), *lw["o"])
+            fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_conv"], eps=self.eps)
+            # --- conv module continuing from the stream's post-GLU tail ---
+            g = self._linear(h, *lw["pw1"], glu=True)
+            xcat = torch.empty(B, SL + Tq, C, device=res.device, dtype=self.dtype)
+            _lib.call("oasr_b200_conv_state_concat", _p(xcat), ctypes.c_void_p(cache.cnn_state[i].data_ptr()), cache.max_streams,
+                      _p(slot_ids), _p(g), B, SL, Tq, C, _DTYPE_ID[self.dtype], _stream(g))
+            x = OF.depthwise_conv1d(xcat, lw["dw"][0], lw["dw"][1], padding=0)        # valid conv: (B, Tq, C)
+            x = OF.layer_norm_activation(x.reshape(M, C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
+            y = self._linear(x, *lw["pw2"])
+            fused.add_norm_f32(h, res, res, y, 1.0, fused.ADD_NORM_LN, *lw["norm_feed_forward2"], eps=self.eps)
+            w1, b1, w2, b2 = lw["feed_forward2"]
+            y = self._linear(self._linear(h, w1, b1, _SWISH), w2, b2)
+            if i + 1 < self.L:
+                nxt = self.layers[i + 1]["norm_feed_forward1"]
+                fused.add_norm_f32(h, res, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *nxt, eps=self.eps)
+            else:
+                out = torch.empty(M, C, device=res.device, dtype=torch.float32)
+                fused.add_norm_f32(h, out, res, y, 0.5, fused.ADD_NORM_LN_LN, *lw["norm_out"], *lw["norm_out"], eps=self.eps)
+        cache.commit(slots)
+        return out.view(B, Tq, C)
 
     def forward(self, hidden: torch.Tensor, lengths: List[int], packed: bool = True) -> torch.Tensor:
         """``hidden (B, T, C)`` post-subsampling states, host ``lengths`` -> ``(B, T, C)`` fp32: the output of the

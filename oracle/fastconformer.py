@@ -258,3 +258,81 @@ def ctc_head(P, hidden: torch.Tensor) -> torch.Tensor:
     """CtcProjection.forward (oasr/layers/ctc.py:48-51): ``log_softmax(hidden @ W^T + b)`` over the padded vocabulary;
     its torch spelling is torch_gemm_log_softmax (oasr/functionals/gemm_torch.py:64-75)."""
     return torch.log_softmax(F.linear(hidden, P["ctc.ctc_lo.weight"], P["ctc.ctc_lo.bias"]), dim=-1)
+
+
+# ---------------------------------------------------------------------------
+# Streaming: the layer stack chunk by chunk with cached keys / values and conv tails
+# ---------------------------------------------------------------------------
+class FastStreamState:
+    """Per-stream state of the streaming layer stack, kept densely: per layer the keys / values of the frames still
+    inside the trained left context ``(H, cached, D)`` and the conv module's post-GLU tail ``(kernel-1, C)``
+    (zero at stream start: what the offline pass zero-pads), plus the number of encoder frames emitted so far."""
+
+    def __init__(self, cfg: FastConformerConfig):
+        H, D, C = cfg.heads, cfg.head_dim, cfg.hidden
+        self.k = [torch.zeros(H, 0, D) for _ in range(cfg.layers)]
+        self.v = [torch.zeros(H, 0, D) for _ in range(cfg.layers)]
+        self.conv = [torch.zeros(cfg.kernel - 1, C) for _ in range(cfg.layers)]
+        self.offset = 0
+
+
+def layers_forward_chunk(P, cfg: FastConformerConfig, state: FastStreamState, x: torch.Tensor, keep_frames: int = -1):
+    """One chunk ``x (T_q, C)`` of one stream through the layer stack: NemotronEncoderLayer.forward_chunk
+    (oasr/models/nemotron/encoder.py:269-298) for every layer with the streaming attention of
+    NemotronRelPositionAttention.forward_chunk (:362-410), the mask of NemotronEncoder._streaming_mask (:680-720) and the
+    cached conv of NemotronConvolutionModule.forward_chunk (:191-208).
+
+    The reference keeps a prefilled window of exactly ``sliding_window - 1`` cached frames whose not-yet-existing
+    leading columns are masked (``k_abs >= 0``); here only real frames are cached, which gives the same visible keys at
+    the same relative distances.  ``keep_frames`` (default: the trained left context) is how many of the newest cached
+    frames survive into the next chunk; any value >= the left context gives the same result (older keys are masked)."""
+    T_q, C = x.shape
+    H, D = cfg.heads, cfg.head_dim
+    left, chunk = cfg.sliding_window - 1, cfg.lookahead + 1
+    left_chunks = left // chunk
+    keep_frames = left if keep_frames < 0 else keep_frames
+    assert T_q % chunk == 0 and state.offset % chunk == 0, "a streaming step is a whole number of trained attention chunks"
+    cached = state.k[0].shape[1]
+    key_len = cached + T_q
+    q_abs = state.offset + torch.arange(T_q)
+    k_abs = state.offset - cached + torch.arange(key_len)
+    diff = q_abs.div(chunk, rounding_mode="trunc").unsqueeze(1) - k_abs.div(chunk, rounding_mode="trunc").unsqueeze(0)
+    mask = (k_abs >= 0).unsqueeze(0) & (diff >= 0) & (diff <= left_chunks)          # (T_q, key_len)
+    pos_emb = relative_position_embedding(key_len, C)                               # (2*key_len - 1, C)
+    scaling = D ** -0.5
+    x = x.float()
+    for i in range(cfg.layers):
+        p = f"layers.{i}."
+        a, c = p + "self_attn.", p + "conv."
+        residual = x
+        h = _ln(P, p + "norm_feed_forward1", x, cfg.eps)
+        residual = residual + 0.5 * _ffn(P, p + "feed_forward1", h)
+        h = _ln(P, p + "norm_self_att", residual, cfg.eps)
+        # --- attention over [cache ; chunk] ---
+        split = lambda t: t.view(T_q, H, D).transpose(0, 1)                        # (H, T_q, D)
+        q, k, v = split(_lin(P, a + "q_proj", h)), split(_lin(P, a + "k_proj", h)), split(_lin(P, a + "v_proj", h))
+        state.k[i] = torch.cat([state.k[i], k], dim=1)
+        state.v[i] = torch.cat([state.v[i], v], dim=1)
+        rel_k = F.linear(pos_emb, P[a + "relative_k_proj.weight"]).view(-1, H, D)   # (2L-1, H, D)
+        bd = (q + P[a + "bias_v"].unsqueeze(1)) @ rel_k.permute(1, 2, 0)            # (H, T_q, 2L-1)
+        bd = rel_shift(bd.unsqueeze(0))[0][..., :key_len] * scaling
+        bias = bd.masked_fill(mask.logical_not().unsqueeze(0), MASK_FLOOR)
+        scores = ((q + P[a + "bias_u"].unsqueeze(1)) @ state.k[i].transpose(-1, -2)) * scaling + bias
+        out = torch.softmax(scores, dim=-1) @ state.v[i]                            # (H, T_q, D)
+        residual = residual + _lin(P, a + "o_proj", out.transpose(0, 1).reshape(T_q, C))
+        state.k[i] = state.k[i][:, -keep_frames:] if keep_frames > 0 else state.k[i][:, :0]
+        state.v[i] = state.v[i][:, -keep_frames:] if keep_frames > 0 else state.v[i][:, :0]
+        # --- conv module with the cached post-GLU tail ---
+        h = _ln(P, p + "norm_conv", residual, cfg.eps)
+        g = F.glu(F.linear(h, P[c + "pointwise_conv1.weight"].squeeze(-1), P.get(c + "pointwise_conv1.bias")), dim=-1)
+        padded = torch.cat([state.conv[i], g], dim=0)                               # (kernel-1 + T_q, C)
+        state.conv[i] = padded[-(cfg.kernel - 1):].clone()
+        w = P[c + "depthwise_conv.weight"].permute(2, 1, 0)                         # (K,1,C) -> (C,1,K)
+        y = F.conv1d(padded.t().unsqueeze(0), w, P.get(c + "depthwise_conv.bias"), groups=C)[0].t()
+        y = F.silu(_ln(P, c + "norm", y, 1e-5))
+        residual = residual + F.linear(y, P[c + "pointwise_conv2.weight"].squeeze(-1), P.get(c + "pointwise_conv2.bias"))
+        h = _ln(P, p + "norm_feed_forward2", residual, cfg.eps)
+        residual = residual + 0.5 * _ffn(P, p + "feed_forward2", h)
+        x = _ln(P, p + "norm_out", residual, cfg.eps)
+    state.offset += T_q
+    return x

@@ -197,3 +197,48 @@ def test_relshift_bias_packed_equals_padded_per_segment():
         seg = flat[offs[b]:offs[b + 1]].view(H, n, ld8[b])
         assert torch.equal(seg[..., :n], padded[b, :, :n, :n])
         assert (seg[..., n:] == -1.0e4).all()
+
+
+@pytest.mark.parametrize("width", ["tiny", "real"])
+def test_streaming_chunks_match_the_oracle_and_the_offline_pass(width):
+    """FastConformer layer stack chunk by chunk over paged keys / values and cached conv tails: every chunk against the
+    fp32 streaming oracle (itself equal to the offline oracle, tests/test_fastconformer_streaming_oracle.py), streams
+    in scattered slots with different starting times, history longer than the trained left context so that pages are
+    evicted; and the concatenation of a stream's chunks against this package's own offline pass."""
+    if width == "tiny":
+        cfg = OFC.FastConformerConfig(hidden=256, heads=2, ffn=512, layers=2, kernel=9, sliding_window=25, lookahead=3, bias=True)
+        w_std = 0.06
+    else:
+        cfg = OFC.FastConformerConfig(hidden=1024, heads=8, ffn=4096, layers=2, kernel=9, sliding_window=57, lookahead=3, bias=False)
+        w_std = 0.02
+    P = OFC.init_params(cfg, 21, w_std=w_std)
+    model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    step, chunks, streams = 16, 8, 3
+    cache = model.new_streaming_cache(max_streams=5, chunk_frames=step)
+    assert cache.max_past >= cfg.sliding_window - 1
+    g = torch.Generator().manual_seed(3)
+    hidden = torch.randn(streams, step * chunks, cfg.hidden, generator=g)
+    slots = [4, 1, 2]
+    states = [OFC.FastStreamState(cfg) for _ in range(streams)]
+    outs = [[] for _ in range(streams)]
+    worst = 0.0
+    for c in range(chunks + 2):
+        # stream s starts s chunks late: the batch composition changes over time
+        active = [s for s in range(streams) if 0 <= c - s < chunks]
+        if not active:
+            continue
+        xs = torch.stack([hidden[s, (c - s) * step:(c - s + 1) * step] for s in active])
+        got = model.forward_chunk(xs.cuda(), [slots[s] for s in active], cache).cpu()
+        assert ob.device_status() == 0
+        for n, s in enumerate(active):
+            with torch.no_grad():
+                want = OFC.layers_forward_chunk(P, cfg, states[s], hidden[s, (c - s) * step:(c - s + 1) * step], keep_frames=cache.max_past)
+            d = (got[n] - want).abs()
+            worst = max(worst, d.max().item())
+            assert d.max().item() < 6e-2 and d.mean().item() < 6e-3, (c, s, d.max().item(), d.mean().item())
+            outs[s].append(got[n])
+    print(f"fastconformer streaming ({width}): worst chunk max-abs {worst:.3e}")
+    offline = model.forward(hidden.cuda(), [step * chunks] * streams).cpu()
+    for s in range(streams):
+        d = (torch.cat(outs[s]) - offline[s]).abs()
+        assert d.max().item() < 6e-2 and d.mean().item() < 6e-3, (s, d.max().item(), d.mean().item())
