@@ -178,11 +178,12 @@ OASR_API int oasr_b200_add_rms_norm_residual(void* out, void* residual_out, cons
  * It is the reference's `x = residual + alpha*sub(x); x = norm(x)` pairs
  * (oasr/models/conformer/model.py:722-751; fused form :602-663) with the sum
  * never rounded to 16 bits.  res_out may alias res_in.  hidden % 8 == 0,
- * hidden <= 2048.  With split_out = 1, h rows are 3*hidden wide and hold
- * [hi | hi | lo] with hi = round16(h), lo = round16(h - hi): multiplied by a
- * weight laid out as [W_hi | W_lo | W_hi] this gives the product at close to
- * fp32 input precision (used for the CTC head, whose log-probs are compared
- * with an fp32 path). */
+ * hidden <= 2048.  With split_out = 1, h rows are 2*hidden wide and hold
+ * [hi | lo] with hi = round16(h), lo = round16(h - hi): multiplied by a
+ * weight laid out as [W | W] (W in 16 bits, twice) this gives the product with
+ * the INPUT at close to fp32 precision (used for the CTC head, whose log-probs
+ * are compared with an fp32 path: rounding the head's input to bf16 alone costs
+ * 4e-4 mean-abs there, rounding its weight 1e-4). */
 OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
                                     const float* res_in /*nullable*/,
                                     const void* y /*nullable*/, double alpha, int mode,
@@ -196,7 +197,7 @@ OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
  * oasr/models/conformer/model.py:722-751):
  *   y = A[M,K] . B[N,K]^T + bias (fp32, never rounded), s = res_in + alpha*y,
  * then `mode` / w_a, b_a, w_b, b_b / split_out exactly as oasr_b200_add_norm_f32
- * (h_out 16-bit row-major [M,N] or [M,3N]).  The fp32 residual stream
+ * (h_out 16-bit row-major [M,N] or [M,2N]).  The fp32 residual stream
  * (res_in, res_out; res_out may alias res_in) is NOT row-major here: it is
  * private to a chain of these calls and uses a blocked layout the kernel can
  * move without staging -- rows padded to a multiple of 32, blocks of 32 rows x

@@ -56,6 +56,7 @@ uint32_t* device_status_ptr() {
   return ptrs[dev];
 }
 
+namespace conv2_pair { extern int g_enabled; }
 namespace gemm { extern int g_force_bn; extern int g_use_pairs; extern int g_lsm_path; }
 extern int g_dw_path;
 extern int g_fmha_relpos_path;
@@ -100,6 +101,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
   if (name && std::strcmp(name, "fmha_poly") == 0) {
     if (value < 0 || value > 2) return ob::set_error(OASR_ERR_INVALID, "fmha_poly must be 0, 1 or 2 (got %d)", value);
     ob::g_fmha_poly = value;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "conv2_pairs") == 0) {
+    ob::conv2_pair::g_enabled = value != 0;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "fused_addnorm") == 0) {

@@ -21,7 +21,7 @@ struct Workspace {
   uint8_t* att;    // (M, d)
   uint8_t* g;      // (M, d)
   uint8_t* cv;     // (M, d)
-  uint8_t* h3;     // (M, 3d)  after_norm as [hi | hi | lo]
+  uint8_t* h3;     // (M, 2d)  after_norm as [hi | lo]
   uint8_t* pos;    // (max_seg, L*d)
   uint8_t* q8;     // (M, max(ffn, d)) one byte per element: per-token quantised GEMM input (quant_kind != 0)
   float* qs;       // (M) its scales
@@ -54,7 +54,7 @@ ChunkWorkspace carve_chunk(const oasr_b200_conformer_model& m, int64_t B, int64_
   w.xcat = take(MC * d * 2);
   w.g = take(MC * d * 2);
   w.cv = take(M * d * 2);
-  w.h3 = take(M * 3 * d * 2);
+  w.h3 = take(M * 2 * d * 2);
   w.bytes = off;
   return w;
 }
@@ -104,7 +104,7 @@ Workspace carve(const oasr_b200_conformer_model& m, int64_t M, int64_t max_seg, 
   w.att = take(M * d * 2);
   w.g = take(M * d * 2);
   w.cv = take(M * d * 2);
-  w.h3 = take(M * 3 * d * 2);
+  w.h3 = take(M * 2 * d * 2);
   w.pos = take(max_seg * m.num_layers * d * 2);
   if (m.quant_kind != 0) {
     w.q8 = take(M * (m.ffn > d ? m.ffn : d));
@@ -268,7 +268,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
     }
   }
   if (log_probs || argmax) {   // log_probs == NULL: token-only head, one vocabulary sweep, no log-prob write
-    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued at split precision (K = 3d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
+    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued with the input split in two 16-bit terms (K = 2d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 2 * d, dt, OASR_DT_F32,
                                        argmax, stream));
   }
   return OASR_OK;
@@ -425,7 +425,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
     }
   }
   if (log_probs || argmax) {   // log_probs == NULL: token-only head, one vocabulary sweep, no log-prob write
-    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued at split precision (K = 3d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 3 * d, dt, OASR_DT_F32,
+    OB_STEP("gemm_log_softmax", 2.0 * M * m.vocab_padded * d /* algorithmic; issued with the input split in two 16-bit terms (K = 2d) */, oasr_b200_gemm_log_softmax(log_probs, w.h3, m.ctc_w, m.ctc_b, M, m.vocab_padded, 2 * d, dt, OASR_DT_F32,
                                        argmax, stream));
   }
   return OASR_OK;

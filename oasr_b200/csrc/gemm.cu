@@ -1198,6 +1198,13 @@ int run_q8_typed(Params& p, const void* A, const void* B, int64_t M, int64_t N, 
 
 }  // namespace gemm
 
+// The same convolution on CTA pairs over all output channels (conv2_pair.cu).
+namespace conv2_pair {
+bool supported(int64_t C, int64_t N);
+int run(const CUtensorMap& ta, void* out, const void* w2, const void* bias, const int32_t* cu_frames, int64_t B, int64_t C,
+        int64_t N, int64_t F2, int tpt, int64_t total_frames, int dtype, cudaStream_t s);
+}  // namespace conv2_pair
+
 // Internal C++ entry: reference GEMM on CUDA cores (tests compare the
 // tensor-core kernel against it on the device).
 int gemm_simt_reference(void* D, const void* A, const void* B, const void* bias, int64_t M, int64_t N, int64_t K,
@@ -1385,6 +1392,8 @@ int oasr_b200_subsample_conv2(void* out, const void* x1, const void* w2, const v
     uint64_t str[5] = {0, (uint64_t)C * 2, (uint64_t)FH * C * 2, (uint64_t)4 * FH * C * 2, (uint64_t)TH * 4 * FH * C * 2};
     uint32_t box[5] = {BK, (uint32_t)F2, 1, (uint32_t)tpt, 1};
     if (int rc = make_tensor_map(&ta, tma_dtype(dtype), 5, x1, dims, str, box)) return rc;
+    if (g_force_bn == 0 && conv2_pair::supported(C, N))
+      return conv2_pair::run(ta, out, w2, bias, cu_frames, B, C, N, F2, tpt, total_frames, dtype, static_cast<cudaStream_t>(stream));
     uint64_t bdims[3] = {(uint64_t)K, (uint64_t)N, 1};
     uint64_t bstr[3] = {0, (uint64_t)K * 2, (uint64_t)K * 2 * (uint64_t)N};
     uint32_t bbox[3] = {BK, (uint32_t)bn, 1};

@@ -5,7 +5,7 @@
 //                                            res_in nullable)
 //   mode 0:  res_out = s,        h = LN_a(s)
 //   mode 1:  res_out = s,        h = s * w_a + b_a          (fp32 per-channel scale/shift: a folded BatchNorm)
-//   mode 2:  res_out = LN_a(s),  h = LN_b(res_out)          (optionally h as [hi | hi | lo], 3N wide)
+//   mode 2:  res_out = LN_a(s),  h = LN_b(res_out)          (optionally h as [hi | lo], 2N wide)
 //
 // It replaces a GEMM launch, the 16-bit round trip of y through HBM and an add+norm launch
 // (ConformerEncoderLayer.forward_packed: `x = residual + alpha * sub(x); x = norm(x)`,
@@ -59,7 +59,7 @@ struct Params {
   const void* bias;        // T[N], nullable
   float alpha;
   int mode;                // 0, 1, 2 as above
-  int split_out;           // mode 2: h rows are [hi | hi | lo]
+  int split_out;           // mode 2: h rows are [hi | lo]
   const float* res_in;     // fp32 residual stream in the blocked layout described at the top, nullable
   float* res_out;          // same layout, nullable unless mode 2; may alias res_in
   const void *w_a, *b_a;   // T[N] (mode 1: float[N])
@@ -470,7 +470,7 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int k = 0; k < 32; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
           if (p.split_out) {
-            // h = hi + lo with hi = round16(h), lo = round16(h - hi): rows [hi | hi | lo] of a 3N-wide output
+            // h = hi + lo with hi = round16(h), lo = round16(h - hi): rows [hi | lo] of a 2N-wide output
             float lo[32];
 #pragma unroll
             for (int k = 0; k < 32; ++k) lo[k] = v[k] - Elem<T>::to_f(Elem<T>::from_f(v[k]));
@@ -483,8 +483,7 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (lane == 0) {
               if (warp_live) {
                 ptx::tma_store_3d(&tmap_h, hbuf, c * kChunk, row0, 0);
-                ptx::tma_store_3d(&tmap_h, hbuf, N + c * kChunk, row0, 0);
-                ptx::tma_store_3d(&tmap_h, hbuf + 2048, 2 * N + c * kChunk, row0, 0);
+                ptx::tma_store_3d(&tmap_h, hbuf + 2048, N + c * kChunk, row0, 0);
               }
               ptx::bulk_commit_group();
             }
@@ -576,7 +575,7 @@ int launch(const Call& c, cudaStream_t s) {
     if (int rc = make_tensor_map(&tb, tma_dtype(c.dtype), 3, c.B, dims, str, box)) return rc;
   }
   {
-    const uint64_t w = static_cast<uint64_t>(N) * (c.p.split_out ? 3 : 1);
+    const uint64_t w = static_cast<uint64_t>(N) * (c.p.split_out ? 2 : 1);
     uint64_t dims[3] = {w, M, 1};
     uint64_t str[3] = {0, w * 2, w * 2 * M};
     uint32_t box[3] = {kChunk, 32, 1};
@@ -615,7 +614,7 @@ int oasr_b200_gemm_add_norm_f32(void* h_out, float* res_out, const float* res_in
   OB_REQUIRE(h_out && A && B && w_a && b_a, OASR_ERR_INVALID, "gemm_add_norm_f32: null pointer argument");
   OB_REQUIRE(mode >= 0 && mode <= 2, OASR_ERR_INVALID, "gemm_add_norm_f32: mode must be 0, 1 or 2");
   OB_REQUIRE(mode != 2 || (res_out && w_b && b_b), OASR_ERR_INVALID, "gemm_add_norm_f32: mode 2 needs res_out and the second norm");
-  OB_REQUIRE(!split_out || mode == 2, OASR_ERR_INVALID, "gemm_add_norm_f32: the [hi | hi | lo] output exists for mode 2 only");
+  OB_REQUIRE(!split_out || mode == 2, OASR_ERR_INVALID, "gemm_add_norm_f32: the [hi | lo] output exists for mode 2 only");
   OB_REQUIRE(M < (int64_t(1) << 31) && K < (1 << 30), OASR_ERR_INVALID, "gemm_add_norm_f32: extent too large");
   OB_REQUIRE(is_aligned(h_out, 16) && is_aligned(A, 16) && is_aligned(B, 16) && (!bias || is_aligned(bias, 16)) &&
                  (!res_in || is_aligned(res_in, 16)) && (!res_out || is_aligned(res_out, 16)) && is_aligned(w_a, 16) &&

@@ -367,7 +367,7 @@ struct AddNormArgs {
   int64_t rows;
   int hidden;
   float eps;
-  int split_out;        // h rows are [hi | hi | lo] (3*hidden wide): x = hi + lo with both parts 16-bit
+  int split_out;        // h rows are [hi | lo] (2*hidden wide): x = hi + lo with both parts 16-bit
 };
 
 // h row stride and the split store: hi = round(x), lo = round(x - hi).
@@ -384,8 +384,7 @@ __device__ __forceinline__ void store_h(T* h, int e, int H, const float (&v)[kGr
     lo[i] = v[i] - hi[i];
   }
   store8(h + e, hi);
-  store8(h + H + e, hi);
-  store8(h + 2 * H + e, lo);
+  store8(h + H + e, lo);
 }
 
 template <int kChunks>
@@ -452,7 +451,7 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
     }
   }
   const bool split = a.split_out != 0;
-  T* h = static_cast<T*>(a.h_out) + row * H * (split ? 3 : 1);
+  T* h = static_cast<T*>(a.h_out) + row * H * (split ? 2 : 1);
   if constexpr (kMode == 1) {
     const float* sc = static_cast<const float*>(a.w_a);
     const float* sh = static_cast<const float*>(a.b_a);

@@ -277,6 +277,14 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_5d_pair(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1,
+                                                 int32_t c2, int32_t c3, int32_t c4, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+      "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
                "r"(ncols)

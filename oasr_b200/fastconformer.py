@@ -341,13 +341,12 @@ class FastConformerEncoder:
                                     w(params[p + "pointwise_conv.weight"].reshape(sub_channels, sub_channels)),
                                     w(params[p + "pointwise_conv.bias"])))
         self.proj = (w(params[s + "linear.weight"]), w(params[s + "linear.bias"]))
-        # optional CTC projection (CtcProjection, oasr/layers/ctc.py:48-51) at close to fp32 input precision: the
-        # weight split into 16-bit hi + lo parts laid out [W_hi | W_lo | W_hi] against rows [h_hi | h_hi | h_lo]
+        # optional CTC projection (CtcProjection, oasr/layers/ctc.py:48-51) with its input at close to fp32 precision:
+        # rows arrive as two 16-bit terms [h_hi | h_lo] and meet the 16-bit weight twice, [W | W]
         self.ctc = None
         if "ctc.ctc_lo.weight" in params:
             cw = params["ctc.ctc_lo.weight"].detach().float()
-            cw_hi = cw.to(dtype).float()
-            self.ctc = (w(torch.cat([cw_hi, cw - cw_hi, cw_hi], dim=1)), w(params["ctc.ctc_lo.bias"]))
+            self.ctc = (w(torch.cat([cw, cw], dim=1)), w(params["ctc.ctc_lo.bias"]))
             self._one, self._zero = f(torch.ones(hidden)), f(torch.zeros(hidden))
 
     def subsample(self, feats: torch.Tensor, lengths: List[int]):
@@ -391,7 +390,7 @@ class FastConformerEncoder:
         if rows is None:
             lp = torch.zeros((B, T, V) if padded_output else (0, V), device=feats.device)
             return (lp, out_len, None) if return_argmax else (lp, out_len)
-        h3 = torch.empty(rows.size(0), 3 * C, device=rows.device, dtype=self.dtype)
+        h3 = torch.empty(rows.size(0), 2 * C, device=rows.device, dtype=self.dtype)
         fused.add_norm_f32(h3, None, rows, None, 0.0, fused.ADD_NORM_AFFINE, self._one, self._zero, eps=1e-5, split_out=True)
         lp, arg = OF.gemm_log_softmax(h3, self.ctc[0], self.ctc[1], out_dtype=torch.float32, return_argmax=True)
         if padded_output:

@@ -18,11 +18,11 @@ def add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: O
                  eps: float = 1e-5, split_out: bool = False) -> None:
     """``s = res_in + alpha*y`` in fp32, then (mode 0) ``h = LN_a(s)``, (mode 1) ``h = s*w_a + b_a``
     with fp32 per-channel ``w_a/b_a``, or (mode 2) ``res_out = LN_a(s); h = LN_b(res_out)``.
-    With ``split_out`` the rows of ``h_out`` are ``3*hidden`` wide: ``[hi | hi | lo]``, ``h = hi + lo``.
+    With ``split_out`` the rows of ``h_out`` are ``2*hidden`` wide: ``[hi | lo]``, ``h = hi + lo``.
     The ``x = residual + alpha*sub(x)`` / ``norm(x)`` pairs of ConformerEncoderLayer.forward_packed
     (oasr/models/conformer/model.py:722-751) with an fp32 residual stream."""
     _need_cuda(h_out, res_out, res_in, y)
-    hidden = h_out.size(-1) // (3 if split_out else 1)
+    hidden = h_out.size(-1) // (2 if split_out else 1)
     rows = h_out.numel() // h_out.size(-1)
     _lib.call("oasr_b200_add_norm_f32", _p(h_out), _p(res_out), _p(res_in), _p(y), float(alpha), int(mode), _p(w_a),
               _p(b_a), _p(w_b), _p(b_b), rows, hidden, float(eps), int(bool(split_out)), _DTYPE_ID[h_out.dtype],

@@ -49,7 +49,7 @@ def _reference(A, B, bias, res, alpha, mode, w1, b1, w2, b2, eps):
 def _run(A, B, bias, res, alpha, mode, w1, b1, w2, b2, eps, split=False, in_place=True):
     M, N = A.size(0), B.size(0)
     dev = "cuda"
-    h = torch.full((M, N * (3 if split else 1)), float("nan"), device=dev, dtype=A.dtype)
+    h = torch.full((M, N * (2 if split else 1)), float("nan"), device=dev, dtype=A.dtype)
     # the residual stream travels in the kernel's blocked layout
     res_in = None if res is None else fused.residual_to_blocked(res.to(dev))
     Mp = (M + 31) // 32 * 32
@@ -90,14 +90,14 @@ def test_without_residual_input_without_bias_and_out_of_place():
     torch.testing.assert_close(got_h, want_h.to(dtype).float(), rtol=2e-2, atol=2e-2)
 
 
-def test_split_output_rows_are_hi_hi_lo():
+def test_split_output_rows_are_hi_lo():
     dtype = torch.bfloat16
     M, N, K = 333, 512, 2048
     A, B, bias, res, w1, b1, w2, b2 = _case(M, N, K, dtype, 9)
     want_res, want_h = _reference(A, B, bias, res, 0.5, 2, w1, b1, w2, b2, 1e-5)
     got_res, got_h3 = _run(A, B, bias, res, 0.5, 2, w1, b1, w2, b2, 1e-5, split=True)
-    hi, hi2, lo = got_h3[:, :N], got_h3[:, N:2 * N], got_h3[:, 2 * N:]
-    assert torch.equal(hi, hi2)
+    hi, lo = got_h3[:, :N], got_h3[:, N:]
+    assert hi.shape == lo.shape
     # hi + lo carries the fp32 value to ~16 mantissa bits (bf16 GEMM-operand rounding of A / B is common to both sides)
     torch.testing.assert_close(hi + lo, want_h, rtol=1e-3, atol=1e-3)
     torch.testing.assert_close(got_res, want_res, rtol=1e-4, atol=2e-4)
