@@ -557,7 +557,9 @@ def main():
     # thread count is the same at every N (torchrun exports OMP_NUM_THREADS=1, which set_num_threads overrides).
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
+        threads_before = torch.get_num_threads()
         v, a, dt, thr, kind = cpu_throughput(args.batch, repeats=2, threads=os.cpu_count() or 1)
+        torch.set_num_threads(threads_before)   # the GPU arm's small host ops must not wake every core
         cpu = {"value": v, "unit": "audio-s/s", "cores": thr, "kind": kind,
                "sample": f"all {args.batch} utterances of rank 0's batch ({a:.1f} audio-s), fp32 packed path, best of two runs ({dt:.1f} s)"}
     dist = None
@@ -698,11 +700,13 @@ def main():
             got = lp[:rows].float().cpu()
             ocfg = OC.ConformerConfig(d_model=cfg.d_model, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, kernel=cfg.kernel,
                                       vocab=cfg.vocab)
+            threads_before = torch.get_num_threads()
             torch.set_num_threads(os.cpu_count() or 1)
             with torch.no_grad():
                 lens = lengths[:n_chk]
                 want, wl = OC.forward_offline_packed(OC.init_params(ocfg, 1234), ocfg, feats_host[:n_chk, :max(lens)].contiguous(),
                                                      torch.tensor(lens))
+            torch.set_num_threads(threads_before)
             want = want[torch.arange(want.shape[1])[None, :] < wl[:, None]]
             dlt = (got - want)[:, :cfg.vocab].abs()
             same = got[:, :cfg.vocab].argmax(-1) == want[:, :cfg.vocab].argmax(-1)
