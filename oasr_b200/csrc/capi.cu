@@ -108,7 +108,8 @@ int oasr_b200_set_tunable(const char* name, int value) {
     return OASR_OK;
   }
   if (name && std::strcmp(name, "fused_addnorm") == 0) {
-    ob::g_fused_addnorm = value != 0;
+    if (value < 0 || value > 2) return ob::set_error(OASR_ERR_INVALID, "fused_addnorm must be 0, 1 or 2 (got %d)", value);
+    ob::g_fused_addnorm = value;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "dwconv_path") == 0) {

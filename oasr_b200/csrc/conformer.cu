@@ -69,7 +69,8 @@ struct ProfRecord {
 bool g_prof_on = false;
 }  // namespace
 // 1 (default): the last Linear of every sub-layer runs fused with the residual add and the following norm
-// (oasr_b200_gemm_add_norm_f32) where the model width allows it; 0: gemm + add_norm_f32 as two kernels.
+// (oasr_b200_gemm_add_norm_f32) where the model width allows it and the batch fills the GPU; 2: whenever the width
+// allows it; 0: gemm + add_norm_f32 as two kernels.
 int g_fused_addnorm = 1;
 namespace {
 std::vector<ProfRecord> g_prof;
@@ -205,7 +206,13 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   // else the Linear into w.y followed by add_norm_f32.  `rin` is the residual input (null for the embed).
   // The fused kernel keeps the residual stream in its own blocked layout, add_norm_f32 row-major: one or the other
   // for the whole call.
-  const bool fuse = qk == 0 && g_fused_addnorm != 0 && oasr_b200_gemm_add_norm_supported(d, d) != 0 &&
+  // The fused kernel gives one 256-row tile to a pair of SMs and cannot overlap a tile's epilogue with the next main
+  // loop, so it pays only when its tiles fill the GPU: at least 80 % of the SM pairs busy in every round (measured on
+  // B200, d 512: 16.7k rows, 66 of 74 pairs, fused 7.07 against 7.30 ms per step; 8.3k rows, 32 pairs, 4.69 against 4.34).
+  const int64_t pairs = (M + 255) / 256, slots = sm_count() / 2;
+  const int64_t rounds = (pairs + slots - 1) / slots;
+  const bool fills = g_fused_addnorm == 2 || pairs * 5 >= rounds * slots * 4;
+  const bool fuse = qk == 0 && g_fused_addnorm != 0 && fills && oasr_b200_gemm_add_norm_supported(d, d) != 0 &&
                     oasr_b200_gemm_add_norm_supported(d, m.ffn) != 0 && oasr_b200_gemm_add_norm_supported(d, m.embed_in) != 0;
 #define OB_LINEAR_ADDNORM(label, fl, hout, rin, in, wt, bs, lay, qi, K, alpha, mode, wa, ba, wb, bb, eps_, split)       \
   do {                                                                                                              \

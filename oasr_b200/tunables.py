@@ -13,7 +13,8 @@ the FMA pipe instead of the MUFU unit: 0 (default; measured fastest), 1 or 2.
 ``conv2_pairs``: 1 (default) runs the second subsampling convolution on CTA pairs over all output channels (widths
 128 / 256 / 512), 0 on the single-CTA implicit-GEMM kernel.
 ``fused_addnorm``: 1 (default) runs the last Linear of every Conformer sub-layer fused with the residual add and the
-following norm (widths 128 / 256 / 512), 0 as gemm + add_norm_f32.
+following norm (widths 128 / 256 / 512) when the batch's 256-row tiles fill the GPU, 2 whenever the width allows it, 0
+always as gemm + add_norm_f32.
 ``pdl``: 1 launches the hot kernels with programmatic stream serialisation, 0 (default) in plain stream order.
 """
 from __future__ import annotations

@@ -164,3 +164,31 @@ def test_ragged_batch_with_too_short_and_minimal_utterances():
     assert empty_len.tolist() == [0, 0] and empty_lp.shape[0] == 2
     assert model.greedy_search(extra.cuda(), [3, 6]) == [[], []]
     assert ob.device_status() == 0
+
+
+@pytest.mark.parametrize("name", ["tiny", "config1"])
+def test_fused_linear_add_norm_path_meets_the_same_gates(name):
+    """The executor's fused Linear + residual add + norm steps (chosen by default only when the batch fills the GPU) forced
+    on for the small cases: widths 128 and 256, the blocked residual layout, the split head input -- same gates against
+    the fp32 oracle, and within a rounding step of the two-kernel path."""
+    from oasr_b200 import tunables
+
+    case = cases.MODEL_CASES[name]
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats, lengths = cases.make_features(case)
+    model = ConformerCTC(_cfg(cfg), P, device="cuda", dtype=torch.bfloat16)
+    want, want_len = OC.forward_offline_packed(P, cfg, feats, lengths)
+    out = {}
+    try:
+        for mode in (2, 0):
+            tunables.set("fused_addnorm", mode)
+            lp, out_len = model.forward_offline_packed(feats.cuda(), lengths)
+            assert ob.device_status() == 0 and torch.equal(out_len.cpu(), want_len)
+            out[mode] = lp.cpu()
+    finally:
+        tunables.set("fused_addnorm", 1)
+    valid = _valid(out[2], want_len)
+    mx, mean, agree, agree_clear = _report(out[2], want, valid, cfg.vocab, f"{name}/packed, fused Linear+add+norm")
+    assert mx <= MAX_ABS and mean <= MEAN_ABS and agree_clear >= ARGMAX_AGREE
+    assert (out[2] - out[0])[valid][:, :cfg.vocab].abs().max().item() < 2e-2
