@@ -519,6 +519,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the one-off check of this step's log-probs against the CPU oracle")
+    ap.add_argument("--force-fused-addnorm", action="store_true",
+                    help="profiling aid: run the fused Linear+add+norm kernel even when the batch does not fill the GPU (reduced cases)")
     ap.add_argument("--unfused-addnorm", action="store_true",
                     help="comparison run: gemm + add_norm_f32 as two kernels instead of the fused Linear+add+norm kernel")
     ap.add_argument("--pdl", action="store_true", help="launch the hot kernels with programmatic stream serialisation (comparison run)")
@@ -581,9 +583,9 @@ def main():
     if args.pdl:
         from oasr_b200 import tunables
         tunables.set("pdl", 1)
-    if args.unfused_addnorm:
+    if args.unfused_addnorm or args.force_fused_addnorm:
         from oasr_b200 import tunables
-        tunables.set("fused_addnorm", 0)
+        tunables.set("fused_addnorm", 0 if args.unfused_addnorm else 2)
     cfg = model_config(args.layers)
     model = ConformerCTC(cfg, init_params(cfg, 1234), device=f"cuda:{local_rank}", dtype=torch.bfloat16,
                          quant=None if args.quant == "none" else args.quant)
