@@ -333,8 +333,11 @@ OASR_API int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const flo
                                            const float* bias, const int32_t* t1_limit /*nullable*/,
                                            int64_t B, int64_t T, int64_t F, int64_t C, int dtype,
                                            void* stream);
-/* Depthwise 3x3 / stride-2 Conv2d on NHWC 16-bit data (B, T, F, C) with pad_lo zero rows / columns before and
- * pad_hi after on both the time and frequency axes: out (B, To, Fo, C), To = (T+pad_lo+pad_hi-3)/2+1 (Fo alike).
+/* Depthwise 3x3 / stride-2 Conv2d on NHWC 16-bit data (B, T, F, C) with pad_lo zero columns before and pad_hi
+ * after on the frequency axis and time_pad_lo / time_pad_hi zero frames on the time axis (offline: the same (2, 1)
+ * on both axes; a streaming chunk passes (0, 0) in time and prepends its cached two frames instead,
+ * oasr/models/nemotron/subsampling.py:156-189): out (B, To, Fo, C), To = (T+time_pad_lo+time_pad_hi-3)/2+1,
+ * Fo = (F+pad_lo+pad_hi-3)/2+1.
  * weight (C, 3, 3), bias nullable (C); output frames >= out_len[b] (nullable int32[B]) are written as zeros and
  * input frames >= in_len[b] (nullable int32[B]) are read as zeros, whatever the buffer holds there.
  * The depthwise half of a FastConformer subsampling stage (oasr/models/nemotron/subsampling.py:39-53, 204-224);
@@ -342,7 +345,7 @@ OASR_API int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const flo
 OASR_API int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weight,
                                              const void* bias /*nullable*/, const int32_t* out_len /*nullable*/,
                                              const int32_t* in_len /*nullable*/, int64_t B, int64_t T, int64_t F, int64_t C, int64_t pad_lo,
-                                             int64_t pad_hi, int dtype, void* stream);
+                                             int64_t pad_hi, int64_t time_pad_lo, int64_t time_pad_hi, int dtype, void* stream);
 /* Second Conv2d of the subsampling stack (3x3, stride 2, C -> N channels, +
  * bias + ReLU) as an implicit GEMM on the tensor cores, writing only valid
  * output frames, already packed: out (total_frames, F2, N) with utterance b's

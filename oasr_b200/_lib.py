@@ -67,7 +67,7 @@ _SIGNATURES = {
     "oasr_b200_subsample_conv1": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_relshift_bias_stream": [P, P, P, P, I, I, I, I, I, I, I, c_double, I, I, c_double, c_int, P],
     "oasr_b200_relshift_bias": [P, P, P, I, I, I, I, I, I, I, c_double, I, I, c_double, c_int, P],
-    "oasr_b200_depthwise_conv2d_k3s2": [P, P, P, P, P, P, I, I, I, I, I, I, c_int, P],
+    "oasr_b200_depthwise_conv2d_k3s2": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv1_s2d": [P, P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_subsample_conv2": [P, P, P, P, P, I, I, I, I, I, I, c_int, P],
     "oasr_b200_gemm": [P, P, P, P, I, I, I, c_int, c_int, P],

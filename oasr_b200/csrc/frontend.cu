@@ -164,9 +164,11 @@ bool k3s2_applies(const Conv1Args& a) {
          static_cast<size_t>(2 * (256 / groups) + 1) * a.F * sizeof(float) <= 48 * 1024;
 }
 
-// Depthwise 3x3 / stride-2 Conv2d on NHWC 16-bit data with causal-style zero padding (pad_lo rows/columns before,
-// pad_hi after, on both the time and the frequency axis): the depthwise half of a stage of the FastConformer 8x
-// subsampling stack (oasr/models/nemotron/subsampling.py:204-224, padding geometry :39-53).  HBM-bound: a thread
+// Depthwise 3x3 / stride-2 Conv2d on NHWC 16-bit data with causal-style zero padding (pad_lo columns before, pad_hi
+// after on the frequency axis; tpad_lo / tpad_hi frames on the time axis -- equal to the frequency pads offline, zero
+// for a streaming chunk whose left context is the cached tail prepended by the caller): the depthwise half of a stage
+// of the FastConformer 8x subsampling stack (oasr/models/nemotron/subsampling.py:204-224, padding geometry :39-53,
+// streaming form :156-189).  HBM-bound: a thread
 // owns 8 channels of one output position (9 x 16-byte loads, 72 FMAs, one 16-byte store); output frames at or past
 // out_len[b] (nullable) are written as zeros, which is the reference's per-stage time mask.
 struct Dw2dArgs {
@@ -176,7 +178,8 @@ struct Dw2dArgs {
   const void* bias;     // nullable (C)
   const int32_t* out_len;
   const int32_t* in_len;   // nullable: input frames >= in_len[b] count as zeros (whatever the buffer holds there)
-  int B, T, F, C, To, Fo, pad_lo;
+  int B, T, F, C, To, Fo, pad_lo;   // pad_lo: zero columns before the first frequency bin
+  int tpad_lo;                        // zero frames before the first input frame
 };
 
 // kHoist: 256 % (C/8) == 0, so a thread keeps one channel group for its whole grid-stride walk; the weights sit in
@@ -221,7 +224,7 @@ __global__ void __launch_bounds__(256, 2) depthwise_conv2d_k3s2_kernel(Dw2dArgs 
       bool ok[9];
 #pragma unroll
       for (int di = 0; di < 3; ++di) {
-        const int t = 2 * to + di - a.pad_lo;
+        const int t = 2 * to + di - a.tpad_lo;
 #pragma unroll
         for (int dj = 0; dj < 3; ++dj) {
           const int f = 2 * fo + dj - a.pad_lo;
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(256, 2) depthwise_conv2d_k3s2_kernel(Dw2dArgs 
         }
 #pragma unroll
         for (int di = 0; di < 3; ++di) {
-          const int t = 2 * to + di - a.pad_lo;
+          const int t = 2 * to + di - a.tpad_lo;
           if (t < 0 || t >= t_end) continue;
 #pragma unroll
           for (int dj = 0; dj < 3; ++dj) {
@@ -355,18 +358,19 @@ int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const float* weigh
 
 int oasr_b200_depthwise_conv2d_k3s2(void* out, const void* in, const void* weight, const void* bias,
                                     const int32_t* out_len, const int32_t* in_len, int64_t B, int64_t T, int64_t F, int64_t C, int64_t pad_lo,
-                                    int64_t pad_hi, int dtype, void* stream) {
+                                    int64_t pad_hi, int64_t time_pad_lo, int64_t time_pad_hi, int dtype, void* stream) {
   using namespace ob;
-  OB_REQUIRE(B >= 0 && T > 0 && F > 0 && C > 0 && pad_lo >= 0 && pad_hi >= 0, OASR_ERR_INVALID,
-             "depthwise_conv2d_k3s2: bad shape");
-  OB_REQUIRE(T + pad_lo + pad_hi >= 3 && F + pad_lo + pad_hi >= 3, OASR_ERR_INVALID,
+  OB_REQUIRE(B >= 0 && T > 0 && F > 0 && C > 0 && pad_lo >= 0 && pad_hi >= 0 && time_pad_lo >= 0 && time_pad_hi >= 0,
+             OASR_ERR_INVALID, "depthwise_conv2d_k3s2: bad shape");
+  OB_REQUIRE(T + time_pad_lo + time_pad_hi >= 3 && F + pad_lo + pad_hi >= 3, OASR_ERR_INVALID,
              "depthwise_conv2d_k3s2: padded input smaller than the kernel");
   if (B == 0) return OASR_OK;
   OB_REQUIRE(out && in && weight, OASR_ERR_INVALID, "depthwise_conv2d_k3s2: null pointer argument");
   OB_REQUIRE(C % 8 == 0 && is_aligned(out, 16) && is_aligned(in, 16) && (!bias || is_aligned(bias, 16)), OASR_ERR_ALIGN,
              "depthwise_conv2d_k3s2: channels must be a multiple of 8 and the tensors 16-byte aligned");
   Dw2dArgs a{out, in, weight, bias, out_len, in_len, (int)B, (int)T, (int)F, (int)C,
-             (int)((T + pad_lo + pad_hi - 3) / 2 + 1), (int)((F + pad_lo + pad_hi - 3) / 2 + 1), (int)pad_lo};
+             (int)((T + time_pad_lo + time_pad_hi - 3) / 2 + 1), (int)((F + pad_lo + pad_hi - 3) / 2 + 1), (int)pad_lo,
+             (int)time_pad_lo};
   const int groups = (int)(C / 8);
   const bool hoist = 256 % groups == 0 && C <= 1024 && B * a.To * a.Fo < (int64_t(1) << 31);     // 40 bytes of shared memory per channel
   const int64_t total = B * a.To * a.Fo * groups;

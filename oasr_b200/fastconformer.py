@@ -329,6 +329,7 @@ class FastConformerEncoder:
                  dtype: torch.dtype = torch.bfloat16, stages: int = 3):
         self.stack = FastConformerLayers(hidden, heads, ffn, layers, kernel, sliding_window, lookahead, params, device, dtype)
         self.device, self.dtype, self.stages, self.Cs = torch.device(device), dtype, stages, sub_channels
+        self.mels = mels
         w = lambda t: t.detach().to(torch.float32).to(dtype).to(self.device).contiguous()
         f = lambda t: t.detach().to(torch.float32).to(self.device).contiguous()
         s = "subsampling."
@@ -373,6 +374,64 @@ class FastConformerEncoder:
             raise RuntimeError("feats must be a CUDA tensor (oasr_b200 has no CPU path)")
         hidden, out_len = self.subsample(feats, [int(n) for n in lengths])
         return self.stack.forward(hidden, out_len, packed=packed), out_len
+
+    # ------------------------------------------------------------------ streaming
+    def new_streaming_cache(self, max_streams: int, chunk_frames: int = 16, block_size: int = 16, seed=0):
+        """The layer stack's cache plus, per subsampling stage, each stream's last two input frames (``kernel - 1``:
+        NemotronSubsampling.state_specs, oasr/models/nemotron/subsampling.py:130-154): the stem keeps raw fp32 feature
+        frames ``(2, mels)``, every later stage 16-bit NHWC frames ``(2, bins * channels)``, all before frequency padding."""
+        cache = self.stack.new_streaming_cache(max_streams, chunk_frames, block_size, seed)
+        bins = self.mels
+        cache.extra_state.append(torch.zeros(max_streams, 2, bins, device=self.device, dtype=torch.float32))
+        for _ in range(self.stages - 1):
+            bins = (bins + 3 - 3) // 2 + 1
+            cache.extra_state.append(torch.zeros(max_streams, 2, bins * self.Cs, device=self.device, dtype=self.dtype))
+        return cache
+
+    def _stage_input(self, x: torch.Tensor, state: torch.Tensor, slot_ids: torch.Tensor) -> torch.Tensor:
+        """``[cached two frames ; x]`` per stream, and the stream's cache set to the last two frames of that
+        concatenation (NemotronSubsampling._stage_input, subsampling.py:178-189): ``x (B, T, W)`` -> ``(B, T + 2, W)``."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _DTYPE_ID, _p, _stream
+
+        B, T, W = x.shape
+        xcat = torch.empty(B, T + 2, W, device=x.device, dtype=x.dtype)
+        _lib.call("oasr_b200_conv_state_concat", _p(xcat), ctypes.c_void_p(state.data_ptr()), state.size(0), _p(slot_ids),
+                  _p(x), B, 2, T, W, _DTYPE_ID[x.dtype], _stream(x))
+        return xcat
+
+    def subsample_chunk(self, feats: torch.Tensor, slot_ids: torch.Tensor, cache) -> torch.Tensor:
+        """NemotronSubsampling.forward_chunk (subsampling.py:156-176): ``feats (B, T, mels)``, ``T`` a multiple of 8,
+        of the streams in ``slot_ids`` -> ``(B, T / 8, hidden)``.  Every stage reads its cached two frames in place of
+        the offline pass's zero padding on the left and has no padding on the right; no length masks (every frame of a
+        streaming chunk is real audio)."""
+        B, T, mels = feats.shape
+        if T % (1 << self.stages) or mels != self.mels:
+            raise RuntimeError(f"a streaming chunk is (B, multiple of {1 << self.stages}, {self.mels}) feature frames, got {tuple(feats.shape)}")
+        x = self._stage_input(feats.float().contiguous(), cache.extra_state[0], slot_ids)          # (B, T + 2, mels) fp32
+        x = fused.subsample_conv1(torch.nn.functional.pad(x, (2, 1)), *self.conv_in, self.dtype)    # (B, T / 2, F1, Cs)
+        for i, (dw_w, dw_b, pw_w, pw_b) in enumerate(self.sub_stages, start=1):
+            _, Ti, Fd, C = x.shape
+            x = self._stage_input(x.view(B, Ti, Fd * C), cache.extra_state[i], slot_ids).view(B, Ti + 2, Fd, C)
+            x = fused.depthwise_conv2d_k3s2(x, dw_w, dw_b, 2, 1, time_pad=(0, 0))
+            _, To, Fo, C = x.shape
+            x = OF.gemm_activation(x.view(B * To * Fo, C), pw_w, pw_b, 0).view(B, To, Fo, C)
+        B, To, Fo, C = x.shape
+        return OF.gemm(x.reshape(B * To, Fo * C), *self.proj).view(B, To, -1)
+
+    def forward_chunk(self, feats: torch.Tensor, slots, cache) -> torch.Tensor:
+        """One streaming step from feature frames: NemotronEncoder.forward_chunk_paged
+        (oasr/models/nemotron/encoder.py:585-650, ``scale_input`` False).  ``feats (B, 8 * chunk, mels)`` of the streams
+        in ``slots`` -> ``(B, chunk, hidden)`` fp32; ``cache`` from :meth:`new_streaming_cache`."""
+        if not feats.is_cuda:
+            raise RuntimeError("feats must be a CUDA tensor (oasr_b200 has no CPU path)")
+        slots = list(slots)
+        if feats.size(0) != len(slots) or feats.size(1) != cache.chunk << self.stages:
+            raise RuntimeError(f"expected {len(slots)} streams x {cache.chunk << self.stages} feature frames, got {tuple(feats.shape[:2])}")
+        slot_ids = torch.tensor(slots, dtype=torch.int64).to(self.device, non_blocking=True)
+        return self.stack.forward_chunk(self.subsample_chunk(feats, slot_ids, cache), slots, cache)
 
     def forward_ctc(self, feats: torch.Tensor, lengths: List[int], padded_output: bool = True, return_argmax: bool = False):
         """Encoder + CTC head: ``(log_probs fp32, out_lengths[, argmax])``.  The head (fused GEMM + log-softmax with the

@@ -215,17 +215,20 @@ def paged_kv_write_fp8(k_pool: torch.Tensor, v_pool: torch.Tensor, k_new: torch.
 
 
 def depthwise_conv2d_k3s2(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], pad_lo: int, pad_hi: int,
-                          out_len: Optional[torch.Tensor] = None, in_len: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          out_len: Optional[torch.Tensor] = None, in_len: Optional[torch.Tensor] = None,
+                          time_pad: Optional[tuple] = None) -> torch.Tensor:
     """Depthwise 3x3 / stride-2 Conv2d on NHWC ``x (B, T, F, C)`` with ``pad_lo`` zeros before and ``pad_hi`` after on
-    both axes; ``weight (C, 3, 3)``; frames ``>= out_len[b]`` come out as zeros and input frames ``>= in_len[b]`` are read
-    as zeros (the per-stage time masks of oasr/models/nemotron/subsampling.py:26-31, applied at the consumer)."""
+    both axes (``time_pad = (lo, hi)`` overrides the time axis: ``(0, 0)`` for a streaming chunk that carries its own
+    left context); ``weight (C, 3, 3)``; frames ``>= out_len[b]`` come out as zeros and input frames ``>= in_len[b]``
+    are read as zeros (the per-stage time masks of oasr/models/nemotron/subsampling.py:26-31, applied at the consumer)."""
     _need_cuda(x, weight, bias, out_len, in_len)
     x = x.contiguous()
     B, T, Fd, C = x.shape
-    To, Fo = (T + pad_lo + pad_hi - 3) // 2 + 1, (Fd + pad_lo + pad_hi - 3) // 2 + 1
+    tlo, thi = (pad_lo, pad_hi) if time_pad is None else (int(time_pad[0]), int(time_pad[1]))
+    To, Fo = (T + tlo + thi - 3) // 2 + 1, (Fd + pad_lo + pad_hi - 3) // 2 + 1
     out = torch.empty(B, To, Fo, C, device=x.device, dtype=x.dtype)
     _lib.call("oasr_b200_depthwise_conv2d_k3s2", _p(out), _p(x), _p(weight.contiguous()), _p(bias), _p(out_len), _p(in_len), B, T, Fd,
-              C, int(pad_lo), int(pad_hi), _DTYPE_ID[x.dtype], _stream(x))
+              C, int(pad_lo), int(pad_hi), tlo, thi, _DTYPE_ID[x.dtype], _stream(x))
     return out
 
 

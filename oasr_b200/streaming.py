@@ -41,6 +41,8 @@ class StreamingCache:
         self.k_pool = torch.zeros(num_layers, self.num_blocks, block_size, heads, head_dim, device=self.device, dtype=dtype_pool)
         self.v_pool = torch.zeros_like(self.k_pool)
         self.cnn_state = torch.zeros(num_layers, max_streams, conv_kernel - 1, d_model, device=self.device, dtype=dtype)
+        # further per-stream buffers a front end keeps (leading dimension = slot); zeroed with the stream
+        self.extra_state: List[torch.Tensor] = []
         # physical pages are handed out in a random order (a seeded permutation)
         if seed is None:
             order = list(range(self.num_blocks))
@@ -58,6 +60,8 @@ class StreamingCache:
         self._frames[slot] = 0
         self._offset[slot] = 0
         self.cnn_state[:, slot].zero_()
+        for t in self.extra_state:
+            t[slot].zero_()
 
     def prepare(self, slots: Sequence[int]):
         """Evict the oldest pages of every stream over its history cap, then give each stream the

@@ -248,6 +248,46 @@ def subsampling_forward(P, sub: SubsamplingConfig, feats: torch.Tensor, lengths:
     return F.linear(flat, P["subsampling.linear.weight"], P["subsampling.linear.bias"]), lengths
 
 
+class SubsamplingStreamState:
+    """Per-stream state of the streaming front end: every stage's last ``kernel - 1 = 2`` input frames, before
+    frequency padding (NemotronSubsampling.state_specs, oasr/models/nemotron/subsampling.py:130-154); zeros at stream
+    start, which is what the offline pass pads on the left."""
+
+    def __init__(self, sub: SubsamplingConfig):
+        bins, chans = sub.mels, 1
+        self.tails = []
+        for _ in range(sub.stages):
+            self.tails.append(torch.zeros(chans, 2, bins))               # NCHW without the batch axis
+            bins = (bins + 3 - 3) // 2 + 1
+            chans = sub.channels
+
+
+def subsampling_forward_chunk(P, sub: SubsamplingConfig, state: SubsamplingStreamState, feats: torch.Tensor):
+    """NemotronSubsampling.forward_chunk (oasr/models/nemotron/subsampling.py:156-189) for one stream:
+    ``feats (T, mels)``, ``T`` a multiple of 8 -> ``(T / 8, hidden)``.  Each stage prepends its cached two frames
+    instead of zero padding on the left, stores the last two frames of that concatenation, pads the frequency axis
+    (2, 1) only, and has neither a right pad nor a length mask."""
+    assert feats.shape[0] % (1 << sub.stages) == 0
+
+    def stage_input(x, i):                        # x (C, T, F)
+        cat = torch.cat([state.tails[i], x], dim=1)
+        state.tails[i] = cat[:, -2:].clone()
+        return F.pad(cat, (2, 1)).unsqueeze(0)    # frequency only
+
+    x = feats.float().unsqueeze(0)                # (1, T, F)
+    w = P["subsampling.conv_in.weight"].permute(0, 3, 1, 2)
+    x = torch.relu(F.conv2d(stage_input(x, 0), w, P["subsampling.conv_in.bias"], stride=2))[0]
+    for i in range(sub.stages - 1):
+        p = f"subsampling.layers.{i}."
+        x = F.conv2d(stage_input(x, i + 1), P[p + "depthwise_conv.weight"].permute(0, 3, 1, 2), P[p + "depthwise_conv.bias"],
+                     stride=2, groups=sub.channels)
+        pw = P[p + "pointwise_conv.weight"][:, 0, 0, :]
+        x = torch.relu(torch.einsum("bctf,oc->botf", x, pw) + P[p + "pointwise_conv.bias"][None, :, None, None])[0]
+    c, t, f = x.shape
+    flat = x.permute(1, 2, 0).reshape(t, f * c)
+    return F.linear(flat, P["subsampling.linear.weight"], P["subsampling.linear.bias"])
+
+
 def encoder_forward(P, cfg: FastConformerConfig, sub: SubsamplingConfig, feats: torch.Tensor, lengths: List[int]):
     """NemotronEncoder.forward with scale_input False: ``(hidden (B, T', C), out_lengths)``."""
     hidden, out_len = subsampling_forward(P, sub, feats, torch.tensor(lengths))

@@ -24,3 +24,23 @@ def test_chunked_layer_stack_equals_offline(step, keep):
                          for t in range(0, T, step)])
     assert state.offset == T
     assert (got - want).abs().max().item() < 2e-5
+
+
+@pytest.mark.parametrize("step", [8, 16, 64])
+def test_chunked_subsampling_equals_offline(step):
+    """The streaming front end (cached two frames per stage, no right pad, no masks) against the offline one on a
+    whole utterance whose length is a multiple of the 8x factor: identical arithmetic on the first T / 8 frames, so
+    equal to rounding.  The offline pass emits one more frame, the one that reads its right pad; in a stream those
+    inputs arrive with the next chunk."""
+    sub = OFC.SubsamplingConfig(mels=80, channels=32, stages=3)
+    cfg = OFC.FastConformerConfig(hidden=256, heads=2, ffn=512, layers=1, kernel=9, sliding_window=9, lookahead=3, bias=True)
+    P = OFC.init_params(cfg, 5)
+    P.update(OFC.init_subsampling_params(sub, cfg.hidden, 6))
+    T = 192
+    feats = torch.randn(1, T, sub.mels, generator=torch.Generator().manual_seed(8))
+    with torch.no_grad():
+        want, out_len = OFC.subsampling_forward(P, sub, feats, torch.tensor([T]))
+        state = OFC.SubsamplingStreamState(sub)
+        got = torch.cat([OFC.subsampling_forward_chunk(P, sub, state, feats[0, t:t + step]) for t in range(0, T, step)])
+    assert int(out_len[0]) == T // 8 + 1 and got.shape[0] == T // 8
+    assert (got - want[0, :T // 8]).abs().max().item() < 2e-5

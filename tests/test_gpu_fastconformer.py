@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oasr_b200 as ob
-from oasr_b200.fastconformer import FastConformerLayers
+from oasr_b200.fastconformer import FastConformerEncoder, FastConformerLayers
 from oracle import fastconformer as OFC
 from tests.golden import cases
 
@@ -242,3 +242,44 @@ def test_streaming_chunks_match_the_oracle_and_the_offline_pass(width):
     for s in range(streams):
         d = (torch.cat(outs[s]) - offline[s]).abs()
         assert d.max().item() < 6e-2 and d.mean().item() < 6e-3, (s, d.max().item(), d.mean().item())
+
+
+def test_streaming_from_feature_frames_matches_the_oracle():
+    """NemotronEncoder.forward_chunk_paged from mel frames: streaming 8x subsampling (every stage continues from its
+    cached two input frames) feeding the streaming layer stack, streams in scattered slots that start at different
+    times, against the fp32 streaming oracle chunk by chunk; then a slot is reset and reused, which must give the
+    same first chunk again."""
+    sub = OFC.SubsamplingConfig(mels=80, channels=32, stages=3)
+    cfg = OFC.FastConformerConfig(hidden=256, heads=2, ffn=512, layers=2, kernel=9, sliding_window=25, lookahead=3, bias=True)
+    P = OFC.init_params(cfg, 31)
+    P.update(OFC.init_subsampling_params(sub, cfg.hidden, 32))
+    enc = FastConformerEncoder(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead,
+                               sub.mels, sub.channels, P, stages=sub.stages)
+    step, chunks, streams = 16, 5, 3
+    cache = enc.new_streaming_cache(max_streams=6, chunk_frames=step)
+    feats = torch.randn(streams, step * 8 * chunks, sub.mels, generator=torch.Generator().manual_seed(9))
+    slots = [5, 0, 3]
+    front = [OFC.SubsamplingStreamState(sub) for _ in range(streams)]
+    stack = [OFC.FastStreamState(cfg) for _ in range(streams)]
+    first = None
+    worst = worst_mean = 0.0
+    for c in range(chunks + 2):
+        active = [s for s in range(streams) if 0 <= c - s < chunks]
+        if not active:
+            continue
+        win = lambda s: feats[s, (c - s) * step * 8:(c - s + 1) * step * 8]
+        got = enc.forward_chunk(torch.stack([win(s) for s in active]).cuda(), [slots[s] for s in active], cache).cpu()
+        assert ob.device_status() == 0
+        for n, s in enumerate(active):
+            with torch.no_grad():
+                hid = OFC.subsampling_forward_chunk(P, sub, front[s], win(s))
+                want = OFC.layers_forward_chunk(P, cfg, stack[s], hid, keep_frames=cache.max_past)
+            d = (got[n] - want).abs()
+            worst, worst_mean = max(worst, d.max().item()), max(worst_mean, d.mean().item())
+            assert d.max().item() < 8e-2 and d.mean().item() < 8e-3, (c, s, d.max().item(), d.mean().item())
+            if s == 0 and c == 0:
+                first = got[n].clone()
+    print(f"fastconformer streaming from features: worst chunk max-abs {worst:.3e}, mean-abs {worst_mean:.3e}")
+    cache.reset_stream(slots[0])
+    again = enc.forward_chunk(feats[0:1, :step * 8].cuda(), [slots[0]], cache).cpu()[0]
+    assert torch.equal(again, first)
