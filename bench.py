@@ -521,6 +521,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the one-off check of this step's log-probs against the CPU oracle")
     ap.add_argument("--force-fused-addnorm", action="store_true",
                     help="profiling aid: run the fused Linear+add+norm kernel even when the batch does not fill the GPU (reduced cases)")
+    ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
+                    help="comparison runs: set a library tunable (oasr_b200.tunables) before the workload is built; repeatable")
     ap.add_argument("--unfused-addnorm", action="store_true",
                     help="comparison run: gemm + add_norm_f32 as two kernels instead of the fused Linear+add+norm kernel")
     ap.add_argument("--pdl", action="store_true", help="launch the hot kernels with programmatic stream serialisation (comparison run)")
@@ -583,6 +585,10 @@ def main():
     if args.pdl:
         from oasr_b200 import tunables
         tunables.set("pdl", 1)
+    for item in args.tunable:
+        from oasr_b200 import tunables
+        name, _, value = item.partition("=")
+        tunables.set(name, int(value))
     if args.unfused_addnorm or args.force_fused_addnorm:
         from oasr_b200 import tunables
         tunables.set("fused_addnorm", 0 if args.unfused_addnorm else 2)

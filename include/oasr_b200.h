@@ -393,7 +393,8 @@ OASR_API int oasr_b200_quantize_rows(void* q, float* scale, const void* x, int64
  * an operator; it is the reference's `residual + alpha * Linear(x)` pair,
  * oasr/models/conformer/model.py:722-751, with the sum kept in fp32):
  * R_out[M,N] (fp32) = R_in[M,N] (fp32) + alpha * (A . B^T + bias).  R_out may
- * alias R_in. */
+ * alias R_in; R_in == NULL reads as zeros (a plain fp32-output GEMM: how the
+ * embedding projection starts the residual stream without a 16-bit rounding). */
 OASR_API int oasr_b200_gemm_residual_f32(float* R_out, const float* R_in, const void* A,
                                          const void* B, const void* bias /*nullable*/, int64_t M,
                                          int64_t N, int64_t K, double alpha, int dtype,

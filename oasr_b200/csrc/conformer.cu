@@ -233,12 +233,14 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
                                      ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, nullptr, nullptr, m.eps, 0, dt, stream));
     }
   } else {
-  OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm(w.y, rows, m.embed_w, m.embed_b, M, d, m.embed_in, OASR_ACT_NONE, dt, stream));
+  // The embedding is the first value of the fp32 residual stream: it goes there in fp32 straight from the GEMM's
+  // epilogue (a 16-bit round trip here would put a rounding error on every element that all layers then carry).
+  OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_residual_f32(w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, dt, stream));
   if (m.embed_ln_w) {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 2, m.embed_ln_w, m.embed_ln_b,
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, nullptr, 0.0, 2, m.embed_ln_w, m.embed_ln_b,
                                    ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, M, d, 1e-5, 0, dt, stream));
   } else {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b,
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, nullptr, w.res, nullptr, 0.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b,
                                    nullptr, nullptr, M, d, m.eps, 0, dt, stream));
   }
   }
@@ -374,12 +376,13 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
   const double scale = 1.0 / std::sqrt(64.0);
   const oasr_b200_conformer_layer* ly = m.layers;
 
-  OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm(w.y, rows, m.embed_w, m.embed_b, M, d, m.embed_in, OASR_ACT_NONE, dt, stream));
+  // the embedding starts the fp32 residual stream unrounded (see the offline executor)
+  OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_residual_f32(w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, dt, stream));
   if (m.embed_ln_w) {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 2, m.embed_ln_w, m.embed_ln_b,
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, nullptr, 0.0, 2, m.embed_ln_w, m.embed_ln_b,
                                    ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, M, d, 1e-5, 0, dt, stream));
   } else {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, nullptr, w.y, 1.0, 0, ly[0].norm_ff_macaron_w,
+    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, nullptr, w.res, nullptr, 0.0, 0, ly[0].norm_ff_macaron_w,
                                    ly[0].norm_ff_macaron_b, nullptr, nullptr, M, d, m.eps, 0, dt, stream));
   }
   for (int64_t i = 0; i < L; ++i) {

@@ -1272,8 +1272,7 @@ int oasr_b200_gemm_residual_f32(float* R_out, const float* R_in, const void* A, 
   using namespace ob;
   using namespace ob::gemm;
   if (int rc = validate_common("gemm_residual_f32", R_out, A, B, bias, M, N, K)) return rc;
-  OB_REQUIRE(M == 0 || (R_in && is_aligned(R_in, 16)), OASR_ERR_INVALID,
-             "gemm_residual_f32: residual pointer null or unaligned");
+  OB_REQUIRE(M == 0 || !R_in || is_aligned(R_in, 16), OASR_ERR_ALIGN, "gemm_residual_f32: residual pointer unaligned");
   if (M == 0) return OASR_OK;
   Problem pr{};
   pr.sched = kSchedDense; pr.epi = kEpiResid;
