@@ -650,6 +650,22 @@ OASR_API int oasr_b200_fbank(float* out, const float* waveforms, const int32_t* 
                              int64_t n_fft, int64_t num_mel, double preemph, double log_floor,
                              void* stream);
 
+/* ---- greedy CTC decoding -------------------------------------------------- */
+/* Per-frame argmax ids of packed utterances -> token rows: repeated ids are
+ * dropped, then blanks, never across an utterance boundary (the rule of
+ * csrc/decoder/ctc/cpu/ctc_greedy_search.cc:26-55).  The result has the layout
+ * of the reference's GPU decoders for beam 1 (oasr/functionals/ctc_decode.py:
+ * 313-412: tokens (batch, beam, max_len) int32, lengths (batch, beam), optional
+ * emission frames), but is fed by the CTC head's fused argmax, so no log-probs
+ * are written or read.  ids (total) int32 with utterance b at
+ * [cu_seqlens[b], cu_seqlens[b+1]); tokens (batch, max_len) int32, entries past
+ * lengths[b] = blank; lengths (batch) int32 = min(token count, max_len); times
+ * (batch, max_len) int32 nullable: the frame (within its utterance) each token
+ * was emitted at, -1 past the length. */
+OASR_API int oasr_b200_ctc_greedy_collapse(int32_t* tokens, int32_t* lengths, int32_t* times /*nullable*/,
+                                           const int32_t* ids, const int32_t* cu_seqlens, int64_t batch,
+                                           int64_t max_len, int64_t blank, void* stream);
+
 /* ---- encoder layer stack (native executor) ------------------------------ */
 /* Device pointers to the prepared weights of one Conformer encoder layer
  * (ConformerEncoderLayer, oasr/models/conformer/model.py:499-752).  16-bit

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "oasr_b200_add_norm_f32": [P, P, P, P, c_double, c_int, P, P, P, P, I, I, c_double, c_int, c_int, P],
     "oasr_b200_gemm_add_norm_f32": [P, P, P, P, P, P, I, I, I, c_double, c_int, P, P, P, P, c_double, c_int, c_int, P],
     "oasr_b200_gemm_add_norm_supported": [I, I],
+    "oasr_b200_ctc_greedy_collapse": [P, P, P, P, P, I, I, I, P],
     "oasr_b200_fbank": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, c_double, c_double, P],
     "oasr_b200_trace_buffer": [P],
     "oasr_b200_depthwise_conv1d_packed": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_int, c_int, P],

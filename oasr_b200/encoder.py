@@ -101,6 +101,8 @@ def build_packed_batch(out_lengths: List[int], padded_t: int, conv_kernel: int, 
 class ConformerCTC:
     """WeNet-style Conformer encoder + CTC head running on the sm_100a kernels."""
 
+    last_d2h_bytes = 0    # bytes the latest greedy_search_batches step read back (token rows + lengths)
+
     def __init__(self, cfg: ConformerConfig, params: Dict[str, torch.Tensor], device="cuda",
                  dtype: torch.dtype = torch.bfloat16, quant: Optional[str] = None):
         """``quant``: None = 16-bit GEMMs; "fp8" / "int8" = the eight Linear GEMMs of every layer run on
@@ -462,16 +464,22 @@ class ConformerCTC:
     def greedy_search(self, features: torch.Tensor, lengths, packed: bool = True) -> List[List[int]]:
         """Features -> greedy CTC token lists: the head keeps the per-frame first maximum in its epilogue and writes
         no log-probs (the reference's greedy search reads fp32 log-probs back, oasr/functionals/ctc_decode.py:359);
-        the collapse runs on the host."""
+        repeats and blanks are dropped on the device (``ctc_greedy_collapse``), the host only slices the rows."""
         _, _, argmax, pk = self._forward(features, lengths, not packed, False, True, tokens_only=True)
         if argmax is None:
             return [[] for _ in pk.seg_lengths]
-        return self._collapse(argmax.cpu().numpy(), pk.seg_lengths)
+        tokens, counts, _ = fused.ctc_greedy_collapse(argmax, pk.cu_seqlens, max(pk.seg_lengths))
+        return self._rows_to_lists(tokens.cpu(), counts.cpu())
+
+    @staticmethod
+    def _rows_to_lists(tokens: torch.Tensor, counts: torch.Tensor) -> List[List[int]]:
+        rows = tokens.numpy()
+        return [rows[b, :n].tolist() for b, n in enumerate(counts.tolist())]
 
     def greedy_search_batches(self, batches, packed: bool = True):
         """Pipelined greedy search over an iterable of ``(host_features, lengths)`` batches (pinned host
         memory for the copies to overlap): the host-to-device copy of batch i+1 runs on a copy stream
-        under the encoder of batch i, and the device-to-host read and token collapse of batch i run
+        under the encoder of batch i, and the device-to-host read of batch i's collapsed token rows runs
         under the encoder of batch i+1.  Yields one list of token lists per batch, in order."""
         dev = self.device
         main = torch.cuda.current_stream(dev)
@@ -501,11 +509,15 @@ class ConformerCTC:
             if argmax is None:
                 cur = (None, pk, None)
             else:
-                host = torch.empty(argmax.shape, dtype=argmax.dtype, pin_memory=True)
-                host.copy_(argmax, non_blocking=True)
+                tokens, counts, _ = fused.ctc_greedy_collapse(argmax, pk.cu_seqlens, max(pk.seg_lengths))
+                host = (torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True),
+                        torch.empty(counts.shape, dtype=counts.dtype, pin_memory=True))
+                host[0].copy_(tokens, non_blocking=True)
+                host[1].copy_(counts, non_blocking=True)
                 done = torch.cuda.Event()
                 done.record(main)
                 cur = (host, pk, done)
+                self.last_d2h_bytes = tokens.numel() * 4 + counts.numel() * 4
             if pending is not None:
                 yield self._finish(pending)
             pending = cur
@@ -517,4 +529,4 @@ class ConformerCTC:
         if host is None:
             return [[] for _ in pk.seg_lengths]
         done.synchronize()
-        return self._collapse(host.numpy(), pk.seg_lengths)
+        return self._rows_to_lists(host[0], host[1])

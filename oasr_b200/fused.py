@@ -311,3 +311,20 @@ def gemm_argmax(A: torch.Tensor, B: torch.Tensor, C: Optional[torch.Tensor] = No
     _lib.call("oasr_b200_gemm_log_softmax", None, _p(A2), _p(B), _p(C), A2.size(0), N, K, _DTYPE_ID[A.dtype],
               _DTYPE_ID[torch.float32], _p(arg), _stream(A))
     return arg
+
+
+def ctc_greedy_collapse(ids: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int, blank: int = 0, want_times: bool = False):
+    """Greedy CTC decoding on the device: packed per-frame argmax ``ids (total,) int32`` with utterance boundaries
+    ``cu_seqlens (B + 1,) int32`` -> ``(tokens (B, max_len) int32, lengths (B,) int32, times or None)``; repeats are
+    dropped, then blanks, never across an utterance boundary (csrc/decoder/ctc/cpu/ctc_greedy_search.cc:26-55); the beam-1
+    form of the reference's GPU decoder result (oasr/functionals/ctc_decode.py:81-101)."""
+    _need_cuda(ids, cu_seqlens)
+    if ids.dtype != torch.int32 or cu_seqlens.dtype != torch.int32 or not ids.is_contiguous() or not cu_seqlens.is_contiguous():
+        raise ValueError("ids and cu_seqlens must be contiguous int32 tensors")
+    B = cu_seqlens.numel() - 1
+    tokens = torch.empty(B, int(max_len), device=ids.device, dtype=torch.int32)
+    lengths = torch.empty(B, device=ids.device, dtype=torch.int32)
+    times = torch.empty(B, int(max_len), device=ids.device, dtype=torch.int32) if want_times else None
+    _lib.call("oasr_b200_ctc_greedy_collapse", _p(tokens), _p(lengths), _p(times), _p(ids), _p(cu_seqlens), B, int(max_len),
+              int(blank), _stream(ids))
+    return tokens, lengths, times
