@@ -703,7 +703,7 @@ typedef struct oasr_b200_conformer_model {
   const void *pe;                            /* (pe_rows, d) positional table */
   int64_t pe_rows;
   const void *after_norm_w, *after_norm_b;
-  const void *ctc_w, *ctc_b;                 /* (vocab_padded, 3d) split head weight, (vocab_padded) bias */
+  const void *ctc_w, *ctc_b;                 /* (vocab_padded, 2d) head weight [W | W] for the two-term input, (vocab_padded) bias */
   const void *pos_proj;                      /* nullable: (pos_proj_rows, num_layers*d) = pe . pos_w_all^T, streaming */
   int64_t pos_proj_rows;
   int32_t quant_kind;                        /* 0 = 16-bit GEMMs; OASR_Q8_FP8_E4M3 / OASR_Q8_INT8: the eight Linear GEMMs of every
@@ -799,6 +799,54 @@ OASR_API int oasr_b200_profile_enable(int on);
 OASR_API int oasr_b200_profile_count(void);
 OASR_API int oasr_b200_profile_get(int index, const char** label /*host*/, double* ms /*host*/,
                                    double* flops /*host*/);
+
+/* ---- FastConformer / Nemotron layer stack (native executor) ---------------- */
+/* Device pointers to the prepared weights of one NemotronEncoderLayer
+ * (oasr/models/nemotron/encoder.py:217-267): 16-bit tensors in the model
+ * dtype, weight matrices [out_features, in_features] row-major, every bias
+ * nullable.  qkv4_w is [Wq; Wq; Wk; Wv] (4C, C) with qkv4_b = [bq+u; bq+v; bk;
+ * bv] (the two global biases of the Transformer-XL attention folded into two
+ * copies of the query projection); rel_w is relative_k_proj (C, C); dw_w is the
+ * causal depthwise conv as (kernel, C). */
+typedef struct oasr_b200_fastconformer_layer {
+  const void *norm_ff1_w, *norm_ff1_b;
+  const void *ff1_w1, *ff1_b1, *ff1_w2, *ff1_b2;
+  const void *norm_att_w, *norm_att_b;
+  const void *qkv4_w, *qkv4_b, *rel_w, *o_w, *o_b;
+  const void *norm_conv_w, *norm_conv_b;
+  const void *pw1_w, *pw1_b, *dw_w, *dw_b, *conv_norm_w, *conv_norm_b, *pw2_w, *pw2_b;
+  const void *norm_ff2_w, *norm_ff2_b;
+  const void *ff2_w1, *ff2_b1, *ff2_w2, *ff2_b2;
+  const void *norm_out_w, *norm_out_b;
+} oasr_b200_fastconformer_layer;
+
+typedef struct oasr_b200_fastconformer_model {
+  int32_t hidden, heads, ffn, kernel, num_layers, dtype;
+  int32_t left_context;    /* sliding_window - 1 frames; < 0 = unlimited */
+  int32_t right_context;   /* look-ahead frames; the trained attention chunk is right_context + 1 frames */
+  double eps;              /* of the LayerNorms between the sub-layers (the conv module's own norm uses 1e-5) */
+  double mask_floor;       /* finite additive floor of a masked key (-1e4, encoder.py:80) */
+  const oasr_b200_fastconformer_layer* layers;   /* HOST array of num_layers entries */
+} oasr_b200_fastconformer_model;
+
+/* Bytes of device scratch oasr_b200_fastconformer_layers_packed needs for `total` packed frames, a relative-position
+ * table of `table_rows` rows and an attention bias of `bias_numel` elements. */
+OASR_API int64_t oasr_b200_fastconformer_workspace_bytes(const oasr_b200_fastconformer_model* model, int64_t total,
+                                                         int64_t table_rows, int64_t bias_numel);
+/* The layer loop of NemotronEncoder.forward (oasr/models/nemotron/encoder.py:542-583, layer :217-267, attention
+ * :82-149 / 300-359, conv module :150-214) on the valid frames of all utterances back to back, as one fixed sequence
+ * of this library's kernels on `stream`.  res (total, hidden) fp32: the post-subsampling states on entry, overwritten
+ * (it is the residual stream); out (total, hidden) fp32: the stack's output.  rel_table (table_rows, hidden) 16-bit:
+ * sinusoid rows for relative positions max_seg-1 .. -(max_seg-1), then zero rows up to a multiple of 8.  cu_seqlens
+ * int32[num_segs+1]; bias_offsets int64[num_segs+1], segment s = heads * len_s * roundup8(len_s) elements, bias_numel
+ * their sum.  workspace: oasr_b200_fastconformer_workspace_bytes() bytes, 256-byte aligned.  Nothing is allocated and
+ * the host never waits for the device. */
+OASR_API int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* model, float* res, float* out,
+                                                   const void* rel_table, int64_t table_rows,
+                                                   const int32_t* cu_seqlens, const int64_t* bias_offsets,
+                                                   int64_t bias_numel, int64_t num_segs, int64_t total,
+                                                   int64_t max_seg, void* workspace, int64_t workspace_bytes,
+                                                   void* stream);
 
 #ifdef __cplusplus
 }

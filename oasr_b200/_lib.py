@@ -114,6 +114,24 @@ class ConformerModel(ctypes.Structure):
         ("pos_proj", c_void_p), ("pos_proj_rows", c_int64), ("quant_kind", ctypes.c_int32)]
 
 
+class FastConformerLayer(ctypes.Structure):
+    """struct oasr_b200_fastconformer_layer (include/oasr_b200.h)."""
+
+    _fields_ = [(n, c_void_p) for n in (
+        "norm_ff1_w", "norm_ff1_b", "ff1_w1", "ff1_b1", "ff1_w2", "ff1_b2", "norm_att_w", "norm_att_b", "qkv4_w", "qkv4_b",
+        "rel_w", "o_w", "o_b", "norm_conv_w", "norm_conv_b", "pw1_w", "pw1_b", "dw_w", "dw_b", "conv_norm_w", "conv_norm_b",
+        "pw2_w", "pw2_b", "norm_ff2_w", "norm_ff2_b", "ff2_w1", "ff2_b1", "ff2_w2", "ff2_b2", "norm_out_w", "norm_out_b")]
+
+
+class FastConformerModel(ctypes.Structure):
+    """struct oasr_b200_fastconformer_model (include/oasr_b200.h)."""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "hidden", "heads", "ffn", "kernel", "num_layers", "dtype", "left_context", "right_context")] + [
+        ("eps", c_double), ("mask_floor", c_double), ("layers", POINTER(FastConformerLayer))]
+
+
+_SIGNATURES["oasr_b200_fastconformer_layers_packed"] = [POINTER(FastConformerModel), P, P, P, I, P, P, I, I, I, I, P, I, P]
 _SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, I, P, P, P]
 
 _SIGNATURES["oasr_b200_conformer_encode_packed_noalloc"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, P, P]
@@ -155,6 +173,8 @@ def load() -> ctypes.CDLL:
     lib.oasr_b200_profile_count.argtypes = []
     lib.oasr_b200_conformer_workspace_bytes.restype = c_int64
     lib.oasr_b200_conformer_workspace_bytes.argtypes = [POINTER(ConformerModel), I, I]
+    lib.oasr_b200_fastconformer_workspace_bytes.restype = c_int64
+    lib.oasr_b200_fastconformer_workspace_bytes.argtypes = [POINTER(FastConformerModel), I, I, I]
     for name, argtypes in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -167,7 +187,8 @@ def load() -> ctypes.CDLL:
 
 def exported_names() -> list[str]:
     return list(_STRING_FUNCS) + ["oasr_b200_launch_count", "oasr_b200_conformer_workspace_bytes", "oasr_b200_profile_count",
-                                  "oasr_b200_conformer_noalloc_capacity_bytes", "oasr_b200_conformer_chunk_workspace_bytes"] + list(_SIGNATURES)
+                                  "oasr_b200_conformer_noalloc_capacity_bytes", "oasr_b200_conformer_chunk_workspace_bytes",
+                                  "oasr_b200_fastconformer_workspace_bytes"] + list(_SIGNATURES)
 
 
 def launch_count() -> int:

@@ -75,6 +75,63 @@ class FastConformerLayers:
             for n in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
                 lw[n] = (w(params[p + n + ".weight"]), w(params[p + n + ".bias"]))
             self.layers.append(lw)
+        self._workspace = None
+        self.native = self.qkind == 0     # packed 16-bit batches run through the one-call native executor
+        self._build_native_model()
+
+    def _build_native_model(self) -> None:
+        """The host-side description of the stack the native executor takes (struct oasr_b200_fastconformer_model):
+        device pointers of the prepared weights, kept alive by ``self.layers``."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _DTYPE_ID
+
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+        arr = (_lib.FastConformerLayer * self.L)()
+        for i, lw in enumerate(self.layers):
+            c = arr[i]
+            for field, key in (("norm_ff1", "norm_feed_forward1"), ("norm_att", "norm_self_att"), ("norm_conv", "norm_conv"),
+                               ("norm_ff2", "norm_feed_forward2"), ("norm_out", "norm_out"), ("conv_norm", "conv_norm")):
+                setattr(c, field + "_w", ptr(lw[key][0]))
+                setattr(c, field + "_b", ptr(lw[key][1]))
+            for field, key in (("ff1", "feed_forward1"), ("ff2", "feed_forward2")):
+                for n, t in zip(("_w1", "_b1", "_w2", "_b2"), lw[key]):
+                    setattr(c, field + n, ptr(t))
+            c.qkv4_w, c.qkv4_b, c.rel_w = ptr(lw["qkv4"][0]), ptr(lw["qkv4"][1]), ptr(lw["rel"])
+            c.o_w, c.o_b = ptr(lw["o"][0]), ptr(lw["o"][1])
+            c.pw1_w, c.pw1_b = ptr(lw["pw1"][0]), ptr(lw["pw1"][1])
+            c.dw_w, c.dw_b = ptr(lw["dw"][0]), ptr(lw["dw"][1])
+            c.pw2_w, c.pw2_b = ptr(lw["pw2"][0]), ptr(lw["pw2"][1])
+        m = _lib.FastConformerModel()
+        m.hidden, m.heads, m.ffn, m.kernel, m.num_layers = self.C, self.H, self.F, self.K, self.L
+        m.dtype = _DTYPE_ID[self.dtype]
+        m.left_context, m.right_context = self.left, self.right
+        m.eps, m.mask_floor = self.eps, MASK_FLOOR
+        m.layers = ctypes.cast(arr, ctypes.POINTER(_lib.FastConformerLayer))
+        self._native_layers, self._native_model = arr, m      # keep both alive
+
+    def _layers_native(self, res: torch.Tensor, g) -> torch.Tensor:
+        """The packed stack in ONE call into the native executor (oasr_b200_fastconformer_layers_packed): the same
+        kernels in the same order as :meth:`_layers_composed`, enqueued from C++ on the current stream."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _p, _stream
+
+        M, C = res.shape
+        table = self._position_table(g["T"])
+        lib = _lib.load()
+        need = lib.oasr_b200_fastconformer_workspace_bytes(ctypes.byref(self._native_model), M, table.size(0), g["bias_numel"])
+        if self._workspace is None or self._workspace.numel() < need + 256:
+            self._workspace = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=res.device)
+        ws = self._workspace
+        off = (-ws.data_ptr()) % 256
+        out = torch.empty(M, C, device=res.device, dtype=torch.float32)
+        _lib.call("oasr_b200_fastconformer_layers_packed", ctypes.byref(self._native_model), _p(res), _p(out), _p(table),
+                  table.size(0), _p(g["cu"]), _p(g["offsets"]), g["bias_numel"], g["cu"].numel() - 1, M, g["T"],
+                  ctypes.c_void_p(ws.data_ptr() + off), ws.numel() - off, _stream(res))
+        return out
 
     def _linear(self, x: torch.Tensor, w: torch.Tensor, b, act: int = -1, glu: bool = False) -> torch.Tensor:
         """One Linear: 16-bit GEMM, or per-token quantisation + 8-bit GEMM against the cached 8-bit weight."""
@@ -149,6 +206,13 @@ class FastConformerLayers:
 
     def _layers(self, res: torch.Tensor, g) -> torch.Tensor:
         """``res (M, C)`` fp32 rows (overwritten: the residual stream) -> ``(M, C)`` fp32 output of the stack."""
+        if self.native and g["packed"]:
+            return self._layers_native(res, g)
+        return self._layers_composed(res, g)
+
+    def _layers_composed(self, res: torch.Tensor, g) -> torch.Tensor:
+        """The stack operator by operator from Python: padded batches, 8-bit Linear GEMMs, and the check of the native
+        executor (same kernels, same order, so bit-identical results)."""
         M, C = res.shape
         rel_table = self._position_table(g["T"])
         h = torch.empty(M, C, device=res.device, dtype=self.dtype)

@@ -283,3 +283,40 @@ def test_streaming_from_feature_frames_matches_the_oracle():
     cache.reset_stream(slots[0])
     again = enc.forward_chunk(feats[0:1, :step * 8].cuda(), [slots[0]], cache).cpu()[0]
     assert torch.equal(again, first)
+
+
+def test_native_executor_equals_the_operator_by_operator_stack():
+    """oasr_b200_fastconformer_layers_packed enqueues the same kernels in the same order as the Python composition of
+    the packed stack, so the two agree bit for bit; it refuses a workspace that is too small before launching."""
+    import ctypes
+
+    from oasr_b200 import _lib
+
+    cfg = OFC.FastConformerConfig(hidden=256, heads=2, ffn=512, layers=3, kernel=9, sliding_window=25, lookahead=3, bias=True)
+    P = OFC.init_params(cfg, 77)
+    model = FastConformerLayers(cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    assert model.native
+    lengths = [61, 0, 17, 128, 1]
+    hidden = torch.randn(len(lengths), 128, cfg.hidden, generator=torch.Generator().manual_seed(2)).cuda()
+    before = _lib.launch_count()
+    rows_native, index = model.forward_rows(hidden, lengths)
+    launched = _lib.launch_count() - before
+    model.native = False
+    rows_composed, index2 = model.forward_rows(hidden, lengths)
+    model.native = True
+    assert ob.device_status() == 0
+    assert torch.equal(index, index2) and torch.equal(rows_native, rows_composed)
+    assert launched >= 17 * cfg.layers
+    # too small a workspace: refused with a message, nothing launched
+    table = model._position_table(128)
+    before = _lib.launch_count()
+    with pytest.raises(_lib.OasrB200Error, match="workspace"):
+        ws = torch.empty(4096, dtype=torch.uint8, device="cuda")
+        res = torch.zeros(8, cfg.hidden, device="cuda")
+        cu = torch.tensor([0, 8], dtype=torch.int32, device="cuda")
+        offs = torch.tensor([0, cfg.heads * 8 * 8], dtype=torch.int64, device="cuda")
+        _lib.call("oasr_b200_fastconformer_layers_packed", ctypes.byref(model._native_model), ctypes.c_void_p(res.data_ptr()),
+                  ctypes.c_void_p(res.data_ptr()), ctypes.c_void_p(table.data_ptr()), table.size(0), ctypes.c_void_p(cu.data_ptr()),
+                  ctypes.c_void_p(offs.data_ptr()), cfg.heads * 64, 1, 8, 128, ctypes.c_void_p(ws.data_ptr() + (-ws.data_ptr()) % 256),
+                  2048, None)
+    assert _lib.launch_count() == before
