@@ -457,7 +457,8 @@ def run_fastconformer(args):
     """Config-4 style measurement (``--workload fastconformer``): FastConformer encoder (8x subsampling, 24 layers,
     hidden 1024, 8 heads of 128, FFN 4096, kernel 9, 128 mel bins), random-init weights, one step = one padded batch
     of 128 utterances with lengths uniform in 500..3000 frames (the layer stack runs on the valid frames, packed).  ``--quant fp8|int8`` runs the layers' Linear GEMMs on
-    8-bit operands.  The encoder is a Python composition of this package's operators (not a one-call executor)."""
+    8-bit operands.  The 16-bit layer stack is one call into the native executor (oasr_b200_fastconformer_layers_packed);
+    the subsampling front end and the head are separate operator calls."""
     import oasr_b200
     from oasr_b200 import _lib
     from oasr_b200.fastconformer import FastConformerEncoder
@@ -512,7 +513,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="offline", choices=["offline", "streaming", "fastconformer", "sweep"],
                     help="offline = the headline packed batch; streaming = 256 streams x one paged chunk per step; "
-                         "fastconformer = a padded batch through the FastConformer encoder (operator composition)")
+                         "fastconformer = a padded batch through the FastConformer encoder + CTC-1024 head")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
