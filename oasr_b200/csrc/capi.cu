@@ -65,6 +65,7 @@ unsigned long long* g_trace_buffer = nullptr;   // diagnostics: device buffer th
 int g_pdl = 0;  // measured neutral on both workloads (offline 7.32 vs 7.36 ms, streaming 3.79 vs 3.71 ms per step): off by default
 extern int g_fmha_chunk_path;
 extern int g_fused_addnorm;
+namespace conv1_mma { extern int g_enabled; }
 
 }  // namespace ob
 
@@ -110,6 +111,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
   if (name && std::strcmp(name, "fused_addnorm") == 0) {
     if (value < 0 || value > 2) return ob::set_error(OASR_ERR_INVALID, "fused_addnorm must be 0, 1 or 2 (got %d)", value);
     ob::g_fused_addnorm = value;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "conv1_mma") == 0) {
+    ob::conv1_mma::g_enabled = value != 0;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "dwconv_path") == 0) {

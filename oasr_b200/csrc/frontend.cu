@@ -8,6 +8,11 @@
 #include "common.cuh"
 
 namespace ob {
+namespace conv1_mma {   // conv1_mma.cu: the parity-split 3x3 / stride-2 form on the tensor cores
+bool supported(int64_t B, int64_t C);
+int run(void* out, const float* in, const float* weight, const float* bias, const int32_t* t1_limit, int64_t B, int64_t T,
+        int64_t F, int64_t C, int dtype, cudaStream_t s);
+}  // namespace conv1_mma
 namespace {
 
 struct Conv1Args {
@@ -349,6 +354,8 @@ int oasr_b200_subsample_conv1_s2d(void* out, const float* in, const float* weigh
   OB_REQUIRE(C % 8 == 0 && is_aligned(out, 16), OASR_ERR_ALIGN,
              "subsample_conv1_s2d: channels must be a multiple of 8 and out 16-byte aligned");
   OB_REQUIRE(B <= 65535, OASR_ERR_INVALID, "subsample_conv1_s2d: batch too large");
+  if (conv1_mma::supported(B, C) && (dtype == OASR_DT_BF16 || dtype == OASR_DT_F16))
+    return conv1_mma::run(out, in, weight, bias, t1_limit, B, T, F, C, dtype, static_cast<cudaStream_t>(stream));
   Conv1Args a{out, in, weight, bias, t1_limit, (int)B, (int)T, (int)F, (int)C, (int)((T - 3) / 2 + 1),
               (int)((F - 3) / 2 + 1), 3, 2};
   OB_REQUIRE(k3s2_applies(a), OASR_ERR_UNSUPPORTED,
