@@ -19,16 +19,17 @@
 // what limits a single-CTA 128 x 256 tile.  No multicast: every CTA loads its own bytes.
 //   warp 0   TMA producer (A tile + its B rows per 64-wide K block, kStages-deep ring)
 //   warp 1   MMA issuer (leader CTA only; N/256 instructions of N<=256 per K16 step) + TMEM owner
-//   warps 2-9  epilogue, two threads per output row (tcgen05.ld 32x32b: lane = row; warps w and w+4 share a TMEM
-//             lane quarter and take one half of the row's columns each -- one warp per scheduler is latency-bound):
-//     pass 1  s = res + alpha*(acc + bias) per 32-column chunk; the residual stream lives in HBM in 32 x 32
-//             blocks laid out so that a warp (lane = row) reads and writes a block with eight coalesced 512-byte
-//             accesses straight from registers (the next block is requested before this one is processed, the
+//   warps 2-17  epilogue, four threads per output row (tcgen05.ld 32x32b: lane = row; the four warps that share a
+//             TMEM lane quarter take one quarter of the row's columns each -- the passes below are chains of load
+//             latencies, so what they need is warps to switch between; two per scheduler left the SM idle 3/4 of the time):
+//     pass 1  s = res + alpha*(acc + bias) per 16-column chunk; the residual stream lives in HBM in 32 x 32
+//             blocks laid out so that a warp (lane = row) reads and writes half a block with four coalesced 512-byte
+//             accesses straight from registers (the next chunk is requested before this one is processed, the
 //             first one under the main loop); s also goes back into the accumulator's own TMEM columns; running
-//             sums for mean / variance about the slice's first value, combined across the two slices through
+//             sums for mean / variance about the slice's first value, combined across the four slices through
 //             shared memory
-//     pass 2  re-reads s from TMEM, normalises, rounds once, stages 32 x 32 pieces (64-byte swizzle) and
-//             TMA-stores them (mode 2: writes LN_a(s) as fp32 instead, keeps it in TMEM, pass 3 stores h)
+//     pass 2  re-reads s from TMEM, normalises, rounds once, stages 32 x 32 pieces (64-byte swizzle, two chunks each)
+//             and TMA-stores them (mode 2: writes LN_a(s) as fp32 instead, keeps it in TMEM, pass 3 stores h)
 // Every wait is bounded (mbar_wait); on give-up the CTA drains and raises the device status word.
 #include <cuda.h>
 
@@ -45,12 +46,12 @@ namespace gan {
 constexpr int BM = 128;      // rows per CTA (= TMEM lanes)
 constexpr int BK = 64;       // K elements per stage (128-byte rows)
 constexpr int UMMA_K = 16;
-constexpr int kEpiWarps = 8;  // two warps per TMEM lane quarter: each handles one half of the row's columns
+constexpr int kEpiWarps = 16; // four warps per TMEM lane quarter: each handles one quarter of the row's columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr int kChunk = 32;   // columns per epilogue step
+constexpr int kChunk = 16;   // columns per epilogue step (two steps fill one 32 x 32 h piece)
 constexpr int kSlices = kEpiWarps / 4;   // column slices of a row (threads that share a row)
-// per epilogue warp: two 32 x 32 16-bit staging buffers for h (2 KB each, 64-byte swizzle)
-constexpr int kWarpEpiBytes = 2 * 2048;
+// per epilogue warp: one 32 x 32 16-bit staging buffer for h (2 KB, 64-byte swizzle)
+constexpr int kWarpEpiBytes = 2048;
 
 struct Params {
   int M, N, K;
@@ -102,18 +103,18 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// 32 consecutive parameters (16-bit or fp32) starting at p as floats; warp-uniform addresses (broadcast loads).
+// 16 consecutive parameters (16-bit or fp32) starting at p as floats; warp-uniform addresses (broadcast loads).
 template <typename P>
-__device__ __forceinline__ void load_params32(const P* p, float (&f)[32]) {
+__device__ __forceinline__ void load_params16(const P* p, float (&f)[16]) {
   if constexpr (std::is_same<P, float>::value) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
       f[4 * i] = v.x; f[4 * i + 1] = v.y; f[4 * i + 2] = v.z; f[4 * i + 3] = v.w;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       Pack<P> v = ld128_nc(p + 8 * i);
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[8 * i + j] = Elem<P>::to_f(v.v[j]);
@@ -260,57 +261,77 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncwarp();
   } else {
     // ------------------------------ epilogue: thread = (output row, column slice) ---------------
-    const int ew = warp - 2;                       // epilogue warp index 0..7
+    const int ew = warp - 2;                       // epilogue warp index 0..15
     const int q = warp & 3;                        // TMEM lane quarter this warp may access
-    const int slice = ew >> 2;                     // which half of the row's columns this warp handles
-    constexpr int kLocal = kChunks / kSlices;      // chunks per warp
+    const int slice = ew >> 2;                     // which quarter of the row's columns this warp handles
+    constexpr int kLocal = kChunks / kSlices;      // 16-column chunks per thread (even: two chunks make one h piece)
+    static_assert(kLocal >= 2 && kLocal % 2 == 0, "a thread fills whole 32-column h pieces");
     const int c_lo = slice * kLocal;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
-    uint8_t* hbuf = smem + S::kEpiOffset + ew * S::kWarpEpi;            // 2 x 2 KB h staging; [0] is also the statistics mailbox
-    uint8_t* partner_hbuf = smem + S::kEpiOffset + (ew ^ 4) * S::kWarpEpi;   // same rows, other column slice
+    uint8_t* hbuf = smem + S::kEpiOffset + ew * S::kWarpEpi;            // 2 KB: one 32 x 32 h piece; also the statistics mailbox
+    uint8_t* quarter_bufs = smem + S::kEpiOffset + (ew & 3) * S::kWarpEpi;   // + 4 * t * kWarpEpi: the warps of this lane quarter
     uint32_t tile_phase = 0;
     bool ok = true;
     const T* bias = static_cast<const T*>(p.bias);
     const int sw64 = (lane >> 1) & 3;              // chunk XOR of this thread's row in a 64-byte-swizzled buffer
 
-    // 32 values rounded to T into a 64-byte-swizzled buffer (this thread's 64-byte row)
-    auto h_row_store = [&](uint8_t* buf, const float (&v)[32]) {
-      uint8_t* row = buf + lane * 64;
+    // 16 values rounded to T into half `half` of this thread's 64-byte row of the staging buffer
+    auto half_row_store = [&](const float (&v)[16], int half) {
+      uint8_t* row = hbuf + lane * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        *reinterpret_cast<uint4*>(row + ((c ^ sw64) << 4)) =
+      for (int c = 0; c < 2; ++c) {
+        *reinterpret_cast<uint4*>(row + (((2 * half + c) ^ sw64) << 4)) =
             make_uint4(pack2<T>(v[8 * c], v[8 * c + 1]), pack2<T>(v[8 * c + 2], v[8 * c + 3]),
                        pack2<T>(v[8 * c + 4], v[8 * c + 5]), pack2<T>(v[8 * c + 6], v[8 * c + 7]));
       }
     };
-    // Before staging buffer `which` is rewritten: the TMA store issued from it two chunks ago has read it.
+    // Before the staging buffer is rewritten: the TMA store issued from it has read it.
     auto h_buffer_free = [&]() {
-      if (lane == 0) ptx::bulk_wait_group_read<1>();
+      if (lane == 0) ptx::bulk_wait_group_read<0>();
       __syncwarp();
     };
-    // Row statistics of the two column slices -> statistics of the whole row.  Every thread mails (mean, M2) of its
-    // slice into its partner's first h buffer (idle at that point: all of the partner's stores have read their
-    // buffers before the tile ends, and no h is staged before the statistics are known), all warps meet on an
-    // mbarrier (bounded wait), and each thread reads its own mailbox.  The combination is symmetric, so both threads of
-    // a row get bit-identical mean / rstd.
+    // The 32 x 32 piece in the staging buffer leaves for columns [col, col + 32) of the output rows of this warp.
+    auto h_piece_out = [&](int col, int row0_, bool live) {
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (live) ptx::tma_store_3d(&tmap_h, hbuf, col, row0_, 0);
+        ptx::bulk_commit_group();
+      }
+    };
+    // Row statistics of the four column slices -> statistics of the whole row.  Every thread mails (mean, M2) of its
+    // slice to the four warps of its lane quarter (their staging buffers are idle at that point: every store has read
+    // its buffer before the previous tile ended, and no h is staged before the statistics are known), all warps meet
+    // on an mbarrier (bounded wait), and each thread combines the four entries of its own buffer in slice order, so
+    // that the four threads of a row get bit-identical mean / rstd.
     auto combine_stats = [&](int which, float pivot_, float sum_, float sq_, float& mean_, float& rstd_) -> bool {
       constexpr float n_s = static_cast<float>(N / kSlices);
       const float m_s = sum_ / n_s;                              // mean of (x - pivot) over the slice
       const float mean_s = pivot_ + m_s;
       const float m2_s = fmaxf(sq_ - sum_ * m_s, 0.f);           // sum of squared deviations from the slice mean
-      *reinterpret_cast<float2*>(partner_hbuf + which * 256 + lane * 8) = make_float2(mean_s, m2_s);
+#pragma unroll
+      for (int t = 0; t < kSlices; ++t)
+        *reinterpret_cast<float2*>(quarter_bufs + t * 4 * S::kWarpEpi + which * 1024 + (slice * 32 + lane) * 8) =
+            make_float2(mean_s, m2_s);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&stat_bar[which]);
       if (!ptx::mbar_wait(&stat_bar[which], tile_phase, abort_flag)) return false;
-      const float2 o = *reinterpret_cast<const float2*>(hbuf + which * 256 + lane * 8);
-      const float delta = mean_s - o.x;
-      mean_ = 0.5f * (mean_s + o.x);
-      const float m2 = (m2_s + o.y) + delta * delta * (0.5f * n_s);
+      float n = 0.f, mean = 0.f, m2 = 0.f;
+#pragma unroll
+      for (int t = 0; t < kSlices; ++t) {
+        const float2 o = *reinterpret_cast<const float2*>(hbuf + which * 1024 + (t * 32 + lane) * 8);
+        const float delta = o.x - mean;
+        const float n_new = n + n_s;
+        mean += delta * (n_s / n_new);
+        m2 += o.y + delta * delta * (n * n_s / n_new);
+        n = n_new;
+      }
+      mean_ = mean;
       rstd_ = rsqrtf(m2 / static_cast<float>(N) + p.eps);
       __syncwarp();                                              // every lane has read its mailbox before h is staged over it
       return true;
     };
-    // The per-column parameters (bias, gamma / beta or scale / shift) are read by every thread, 32 at a time, from
+    // The per-column parameters (bias, gamma / beta or scale / shift) are read by every thread, 16 at a time, from
     // warp-uniform addresses: pull their lines into L1 once, under the main loop, so that the per-chunk loads hit.
     {
       auto prefetch_vec = [&](const void* ptr, int bytes) {
@@ -334,13 +355,16 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool use_rin = p.res_in != nullptr && warp_live;
       const bool store_res = p.res_out != nullptr && warp_live;
       const int band = row0 >> 5;
-      // this thread's pieces of residual block (band, c): float4 index j*32 + lane, j = 0..7
-      auto res_ptr = [&](const float* base, int c) { return base + res_block_offset(band, c, kChunks) + lane * 4; };
-      float4 nxt[8];
-      if (use_rin) {                               // the first block travels under the main loop
+      // this thread's pieces of 16-column chunk c: the half (c & 1) of residual block (band, c >> 1), float4 index
+      // ((c & 1) * 4 + j) * 32 + lane, j = 0..3
+      auto res_ptr = [&](const float* base, int c) {
+        return base + res_block_offset(band, c >> 1, N / 32) + ((c & 1) * 128 + lane) * 4;
+      };
+      float4 nxt[4];
+      if (use_rin) {                               // the first chunk travels under the main loop
         const float* src = res_ptr(p.res_in, c_lo);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) nxt[j] = ld_res(src + j * 128);
+        for (int j = 0; j < 4; ++j) nxt[j] = ld_res(src + j * 128);
       }
 
       if (!ptx::mbar_wait(tfull_bar, tile_phase, abort_flag)) { ok = false; break; }
@@ -352,64 +376,58 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll 1
       for (int i = 0; i < kLocal; ++i) {
         const int c = c_lo + i;
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
-        float s[32];
+        uint32_t r[16];
+        ptx::tmem_ld_32x16(t_acc + c * kChunk, r);
+        float s[16];
         if (use_rin) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) { s[4 * j] = nxt[j].x; s[4 * j + 1] = nxt[j].y; s[4 * j + 2] = nxt[j].z; s[4 * j + 3] = nxt[j].w; }
-          if (i + 1 < kLocal) {                    // the next block is in flight while this one is processed
+          for (int j = 0; j < 4; ++j) { s[4 * j] = nxt[j].x; s[4 * j + 1] = nxt[j].y; s[4 * j + 2] = nxt[j].z; s[4 * j + 3] = nxt[j].w; }
+          if (i + 1 < kLocal) {                    // the next chunk is in flight while this one is processed
             const float* src = res_ptr(p.res_in, c + 1);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) nxt[j] = ld_res(src + j * 128);
+            for (int j = 0; j < 4; ++j) nxt[j] = ld_res(src + j * 128);
           }
         } else {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) s[k] = 0.f;
+          for (int k = 0; k < 16; ++k) s[k] = 0.f;
         }
-        float bb[32];
-        if (bias) load_params32(bias + c * kChunk, bb);
+        float bb[16];
+        if (bias) load_params16(bias + c * kChunk, bb);
         ptx::tmem_ld_wait();
         if (bias) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) s[k] = fmaf(p.alpha, u2f(r[k]) + bb[k], s[k]);
+          for (int k = 0; k < 16; ++k) s[k] = fmaf(p.alpha, u2f(r[k]) + bb[k], s[k]);
         } else {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) s[k] = fmaf(p.alpha, u2f(r[k]), s[k]);
+          for (int k = 0; k < 16; ++k) s[k] = fmaf(p.alpha, u2f(r[k]), s[k]);
         }
         if (store_res && p.mode != 2) {
           float* dst = const_cast<float*>(res_ptr(p.res_out, c));
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < 4; ++j)
             *reinterpret_cast<float4*>(dst + j * 128) = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
         }
         if (p.mode == 1) {
           // affine pre-norm: no statistics, h leaves in this pass
-          float sc[32], sh[32], o[32];
-          load_params32(static_cast<const float*>(p.w_a) + c * kChunk, sc);
-          load_params32(static_cast<const float*>(p.b_a) + c * kChunk, sh);
+          float sc[16], sh[16], o[16];
+          load_params16(static_cast<const float*>(p.w_a) + c * kChunk, sc);
+          load_params16(static_cast<const float*>(p.b_a) + c * kChunk, sh);
 #pragma unroll
-          for (int k = 0; k < 32; ++k) o[k] = fmaf(s[k], sc[k], sh[k]);
-          uint8_t* hb = hbuf + (i & 1) * 2048;
-          h_buffer_free();
-          h_row_store(hb, o);
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (warp_live) ptx::tma_store_3d(&tmap_h, hb, c * kChunk, row0, 0);
-            ptx::bulk_commit_group();
-          }
+          for (int k = 0; k < 16; ++k) o[k] = fmaf(s[k], sc[k], sh[k]);
+          if ((c & 1) == 0) h_buffer_free();
+          half_row_store(o, c & 1);
+          if (c & 1) h_piece_out((c >> 1) * 32, row0, warp_live);
         } else {
           if (i == 0) pivot = s[0];
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
+          for (int k = 0; k < 16; ++k) {
             const float d = s[k] - pivot;
             sum += d;
             sq = fmaf(d, d, sq);
           }
 #pragma unroll
-          for (int k = 0; k < 32; ++k) r[k] = f2u(s[k]);
-          ptx::tmem_st_32x32(t_acc + c * kChunk, r);
+          for (int k = 0; k < 16; ++k) r[k] = f2u(s[k]);
+          ptx::tmem_st_32x16(t_acc + c * kChunk, r);
         }
       }
       if (ew == 0 && lane == 0) stamp(p, 5);
@@ -426,28 +444,28 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll 1
           for (int i = 0; i < kLocal; ++i) {
             const int c = c_lo + i;
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
-            float gg[32], bb[32], v[32];
-            load_params32(g1 + c * kChunk, gg);
-            load_params32(b1 + c * kChunk, bb);
+            uint32_t r[16];
+            ptx::tmem_ld_32x16(t_acc + c * kChunk, r);
+            float gg[16], bb[16], v[16];
+            load_params16(g1 + c * kChunk, gg);
+            load_params16(b1 + c * kChunk, bb);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
+            for (int k = 0; k < 16; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
             if (i == 0) pivot2 = v[0];
 #pragma unroll
-            for (int k = 0; k < 32; ++k) {
+            for (int k = 0; k < 16; ++k) {
               const float d = v[k] - pivot2;
               sum2 += d;
               sq2 = fmaf(d, d, sq2);
             }
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = f2u(v[k]);
-            ptx::tmem_st_32x32(t_acc + c * kChunk, r);
+            for (int k = 0; k < 16; ++k) r[k] = f2u(v[k]);
+            ptx::tmem_st_32x16(t_acc + c * kChunk, r);
             if (store_res) {
               float* dst = const_cast<float*>(res_ptr(p.res_out, c));
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
+              for (int j = 0; j < 4; ++j)
                 *reinterpret_cast<float4*>(dst + j * 128) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
           }
@@ -458,51 +476,35 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           b1 = static_cast<const T*>(p.b_b);
         }
         // ---------------- last pass: h = LN(row in TMEM), rounded once, 32 x 32 pieces out by TMA ----------------
+        // With split_out the pass runs twice: h = hi + lo with hi = round16(h) into columns [0, N), then
+        // lo = round16(h - hi) into columns [N, 2N).
+        const int parts = p.split_out ? 2 : 1;
 #pragma unroll 1
-        for (int i = 0; i < kLocal; ++i) {
-          const int c = c_lo + i;
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(t_acc + c * kChunk, r);
-          float gg[32], bb[32], v[32];
-          load_params32(g1 + c * kChunk, gg);
-          load_params32(b1 + c * kChunk, bb);
-          ptx::tmem_ld_wait();
+        for (int part = 0; part < parts; ++part) {
+#pragma unroll 1
+          for (int i = 0; i < kLocal; ++i) {
+            const int c = c_lo + i;
+            uint32_t r[16];
+            ptx::tmem_ld_32x16(t_acc + c * kChunk, r);
+            float gg[16], bb[16], v[16];
+            load_params16(g1 + c * kChunk, gg);
+            load_params16(b1 + c * kChunk, bb);
+            ptx::tmem_ld_wait();
 #pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
-          if (p.split_out) {
-            // h = hi + lo with hi = round16(h), lo = round16(h - hi): rows [hi | lo] of a 2N-wide output
-            float lo[32];
+            for (int k = 0; k < 16; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
+            if (part == 1) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) lo[k] = v[k] - Elem<T>::to_f(Elem<T>::from_f(v[k]));
-            if (lane == 0) ptx::bulk_wait_group_read<0>();
-            __syncwarp();
-            h_row_store(hbuf, v);
-            h_row_store(hbuf + 2048, lo);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (warp_live) {
-                ptx::tma_store_3d(&tmap_h, hbuf, c * kChunk, row0, 0);
-                ptx::tma_store_3d(&tmap_h, hbuf + 2048, N + c * kChunk, row0, 0);
-              }
-              ptx::bulk_commit_group();
+              for (int k = 0; k < 16; ++k) v[k] = v[k] - Elem<T>::to_f(Elem<T>::from_f(v[k]));
             }
-          } else {
-            uint8_t* hb = hbuf + (i & 1) * 2048;
-            h_buffer_free();
-            h_row_store(hb, v);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (warp_live) ptx::tma_store_3d(&tmap_h, hb, c * kChunk, row0, 0);
-              ptx::bulk_commit_group();
-            }
+            if ((c & 1) == 0) h_buffer_free();
+            half_row_store(v, c & 1);
+            if (c & 1) h_piece_out(part * N + (c >> 1) * 32, row0, warp_live);
           }
         }
       }
       if (ew == 0 && lane == 0) stamp(p, 7);
-      // Tile done.  All of this warp's stores have read their staging buffers (the partner writes statistics into
-      // the first one during the next tile); then the accumulator columns go back to the leader's MMA issuer.
+      // Tile done.  All of this warp's stores have read the staging buffer (the quarter's warps write statistics into
+      // it during the next tile); then the accumulator columns go back to the leader's MMA issuer.
       if (lane == 0) ptx::bulk_wait_group_read<0>();
       __syncwarp();
       tile_phase ^= 1u;
@@ -578,7 +580,7 @@ int launch(const Call& c, cudaStream_t s) {
     const uint64_t w = static_cast<uint64_t>(N) * (c.p.split_out ? 2 : 1);
     uint64_t dims[3] = {w, M, 1};
     uint64_t str[3] = {0, w * 2, w * 2 * M};
-    uint32_t box[3] = {kChunk, 32, 1};
+    uint32_t box[3] = {32, 32, 1};
     if (int rc = make_tensor_map(&th, tma_dtype(c.dtype), 3, c.h_out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
   }
   int64_t clusters = sm_count() / 2;
