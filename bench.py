@@ -323,21 +323,31 @@ def run_streaming(args):
     assert oasr_b200.device_status() == 0
     time.sleep(1.0)
     sampler.rows.clear()
+    # the step as one CUDA graph (the reference replays its streaming encoder the same way, oasr/engine/graph_cache.py)
+    graphed = None if args.no_graph else model.graphed_chunk_forward(cache, streams, window)
+    run_step = (lambda xs: graphed(xs, slots)) if graphed is not None else \
+        (lambda xs: model.forward_chunk_paged(xs, slots, cache, return_argmax=True))
+    for i in range(3):
+        run_step(dev[i % 8])
+    torch.cuda.synchronize()
+    sampler.rows.clear()
     launches0 = _lib.launch_count()
     evs = []
     for i in range(args.steps):
         flush.fill_(1)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        model.forward_chunk_paged(dev[i % 8], slots, cache, return_argmax=True)
+        run_step(dev[i % 8])
         b.record()
         evs.append((a, b))
     torch.cuda.synchronize()
     launches = _lib.launch_count() - launches0
+    if graphed is not None:
+        launches = graphed.launches_per_replay * args.steps      # replayed launches do not pass through the library's counter
     total_ms = float(sum(a.elapsed_time(b) for a, b in evs))
     t0 = time.perf_counter()
     for i in range(args.steps):
-        _, am = model.forward_chunk_paged(host[i % 8].cuda(non_blocking=True), slots, cache, return_argmax=True)
+        _, am = run_step(host[i % 8].cuda(non_blocking=True))
         toks = am.cpu()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
@@ -358,7 +368,8 @@ def run_streaming(args):
                    "audio_seconds_per_step": audio / args.steps},
         "e2e": {"value": audio / e2e_s, "unit": "audio-s/s", "h2d_bytes_per_step": int(host[0].numel() * 4),
                 "d2h_bytes_per_step": int(toks.numel() * 4),
-                "api": "ConformerCTC.forward_chunk_paged(pinned host windows) -> per-frame argmax on the host"},
+                "api": ("GraphedChunkForward (CUDA-graph replay of the step)" if graphed is not None else "ConformerCTC.forward_chunk_paged")
+                       + "(pinned host windows) -> per-frame argmax on the host"},
         "gpu_launches": int(launches), "clocks": clocks, "kernels_one_step": kernels}), flush=True)
     return 0
 
@@ -527,6 +538,8 @@ def main():
     ap.add_argument("--unfused-addnorm", action="store_true",
                     help="comparison run: gemm + add_norm_f32 as two kernels instead of the fused Linear+add+norm kernel")
     ap.add_argument("--pdl", action="store_true", help="launch the hot kernels with programmatic stream serialisation (comparison run)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="streaming workload: enqueue every step's launches from the host instead of replaying the captured CUDA graph")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"],
                     help="streaming workload: K/V page format (fp8 = e4m3 codes with per-head scales calibrated on four chunks)")
     ap.add_argument("--quant", default="none", choices=["none", "fp8", "int8"],

@@ -345,6 +345,43 @@ class ConformerCTC:
         scales = torch.stack([k, v], dim=1) * (margin / 448.0)
         return torch.clamp(scales, min=1e-8).contiguous()
 
+    def _chunk_launch(self, xs: torch.Tensor, cache, table, cached, total, pos_start, slot_ids):
+        """The device work of one streaming step on the current stream: subsampling convolutions + ONE native call
+        (oasr_b200_conformer_chunk_paged).  No host synchronisation, no host-to-device copy: capturable."""
+        import ctypes
+
+        from . import _lib
+        from .functional import _p
+
+        B = xs.size(0)
+        T = cache.chunk
+        cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=xs.device)
+        rows = self._subsample_packed(xs, [T] * B, cu, B * T)                  # (B * chunk, F'*d)
+        lib = _lib.load()
+        need = lib.oasr_b200_conformer_chunk_workspace_bytes(ctypes.byref(self._native_model), B, T)
+        if self._workspace is None or self._workspace.numel() < need + 256:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the workspace must exist before a capture: run one eager step of this shape first")
+            self._workspace = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=xs.device)
+        ws = self._workspace
+        off = (-ws.data_ptr()) % 256
+        L = self.cfg.layers
+        kp = (ctypes.c_void_p * L)(*[cache.k_pool[i].data_ptr() for i in range(L)])
+        vp = (ctypes.c_void_p * L)(*[cache.v_pool[i].data_ptr() for i in range(L)])
+        log_probs = torch.empty(B, T, self.cfg.vocab_padded, device=xs.device, dtype=torch.float32)
+        argmax = torch.empty(B, T, device=xs.device, dtype=torch.int32)
+        _lib.call("oasr_b200_conformer_chunk_paged", ctypes.byref(self._native_model), _p(rows), B, T, kp, vp, _p(table),
+                  _p(cached), _p(total), _p(pos_start), table.size(1), cache.block_size, cache.num_blocks,
+                  _p(cache.kv_scales), _p(cache.cnn_state), cache.max_streams, _p(slot_ids), ctypes.c_void_p(ws.data_ptr() + off),
+                  ws.numel() - off, _p(log_probs), _p(argmax),
+                  ctypes.c_void_p(torch.cuda.current_stream(xs.device).cuda_stream))
+        return log_probs, argmax
+
+    def graphed_chunk_forward(self, cache, batch: int, window: int):
+        """A streaming step of fixed shape captured once into a CUDA graph (the reference's GraphedEncoderForward,
+        oasr/engine/graph_cache.py:24-29): see :class:`GraphedChunkForward`."""
+        return GraphedChunkForward(self, cache, batch, window)
+
     def forward_chunk_paged(self, xs: torch.Tensor, slots, cache, return_argmax: bool = False):
         """One streaming chunk for the streams in ``slots``: ``xs (B, window, F)`` feature windows ->
         ``log_probs (B, chunk, V)`` fp32 (ConformerEncoder.forward_chunk_paged + head,
@@ -374,24 +411,7 @@ class ConformerCTC:
         if len(slots) != B:
             raise RuntimeError(f"{B} feature windows for {len(slots)} slots")
         table, cached, total, pos_start, slot_ids = cache.prepare(slots)
-        cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=xs.device)
-        rows = self._subsample_packed(xs, [T] * B, cu, B * T)                  # (B * chunk, F'*d)
-        lib = _lib.load()
-        need = lib.oasr_b200_conformer_chunk_workspace_bytes(ctypes.byref(self._native_model), B, T)
-        if self._workspace is None or self._workspace.numel() < need + 256:
-            self._workspace = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=xs.device)
-        ws = self._workspace
-        off = (-ws.data_ptr()) % 256
-        L = self.cfg.layers
-        kp = (ctypes.c_void_p * L)(*[cache.k_pool[i].data_ptr() for i in range(L)])
-        vp = (ctypes.c_void_p * L)(*[cache.v_pool[i].data_ptr() for i in range(L)])
-        log_probs = torch.empty(B, T, self.cfg.vocab_padded, device=xs.device, dtype=torch.float32)
-        argmax = torch.empty(B, T, device=xs.device, dtype=torch.int32)
-        _lib.call("oasr_b200_conformer_chunk_paged", ctypes.byref(self._native_model), _p(rows), B, T, kp, vp, _p(table),
-                  _p(cached), _p(total), _p(pos_start), table.size(1), cache.block_size, cache.num_blocks,
-                  _p(cache.kv_scales), _p(cache.cnn_state), cache.max_streams, _p(slot_ids), ctypes.c_void_p(ws.data_ptr() + off),
-                  ws.numel() - off, _p(log_probs), _p(argmax),
-                  ctypes.c_void_p(torch.cuda.current_stream(xs.device).cuda_stream))
+        log_probs, argmax = self._chunk_launch(xs, cache, table, cached, total, pos_start, slot_ids)
         cache.commit(slots)
         return (log_probs, argmax) if return_argmax else log_probs
 
@@ -530,3 +550,51 @@ class ConformerCTC:
             return [[] for _ in pk.seg_lengths]
         done.synchronize()
         return self._rows_to_lists(host[0], host[1])
+
+
+class GraphedChunkForward:
+    """One streaming step of ``batch`` streams x ``window`` feature frames, captured once into a CUDA graph and
+    replayed per chunk (the reference captures its streaming encoder the same way: ``GraphedEncoderForward``,
+    oasr/engine/graph_cache.py:24-29).  The step is about 170 launches of a few microseconds each, so replaying one
+    graph instead of enqueueing them takes the launch path off the host.  Everything that changes from chunk to chunk
+    is data in fixed device buffers: the feature windows, the block-table rows, the cached / total lengths, the
+    position starts and the slot ids; the page pools and conv states are the cache's own.  Outputs are the graph's
+    static ``log_probs (batch, chunk, V)`` / ``argmax``: read (or copy) them before the next call."""
+
+    def __init__(self, model: "ConformerCTC", cache, batch: int, window: int):
+        if model._pos_proj is None or model._workspace is None:
+            raise RuntimeError("run one eager forward_chunk_paged of this shape first (it sizes the workspace and builds "
+                               "the positional projection)")
+        self.model, self.cache, self.batch = model, cache, batch
+        dev = model.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.xs = torch.zeros(batch, window, model.cfg.input_size, device=dev, dtype=torch.float32)
+        self.table = torch.zeros(batch, cache.max_blocks, **i32)
+        self.cached = torch.zeros(batch, **i32)
+        self.total = torch.full((batch,), cache.chunk, **i32)
+        self.pos_start = torch.zeros(batch, **i32)
+        self.slot_ids = torch.full((batch,), -1, dtype=torch.int64, device=dev)
+        from . import _lib
+
+        self.graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(dev)
+        before = _lib.launch_count()
+        with torch.cuda.graph(self.graph):
+            self.log_probs, self.argmax = model._chunk_launch(self.xs, cache, self.table, self.cached, self.total,
+                                                              self.pos_start, self.slot_ids)
+        self.launches_per_replay = _lib.launch_count() - before     # this library's kernels inside the graph
+
+    def __call__(self, xs: torch.Tensor, slots):
+        slots = list(slots)
+        if len(slots) != self.batch or tuple(xs.shape) != tuple(self.xs.shape):
+            raise RuntimeError(f"this graph was captured for {tuple(self.xs.shape)} windows of {self.batch} streams")
+        table, cached, total, pos_start, slot_ids = self.cache.prepare(slots)
+        self.xs.copy_(xs, non_blocking=True)
+        self.table.copy_(table, non_blocking=True)
+        self.cached.copy_(cached, non_blocking=True)
+        self.total.copy_(total, non_blocking=True)
+        self.pos_start.copy_(pos_start, non_blocking=True)
+        self.slot_ids.copy_(slot_ids, non_blocking=True)
+        self.graph.replay()
+        self.cache.commit(slots)
+        return self.log_probs, self.argmax

@@ -63,6 +63,34 @@ def test_streaming_is_independent_of_batch_composition():
         assert torch.equal(a[1], b[0])
 
 
+def test_graph_replay_equals_the_eager_step():
+    """The streaming step captured once into a CUDA graph and replayed per chunk (GraphedChunkForward) against the
+    eager step on a second cache with the same page order: bit-identical log-probs and argmax on every chunk, with
+    the streams moving between slots of the batch from chunk to chunk."""
+    case = cases.STREAM_CASE
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats = cases.make_stream_features(case).cuda()
+    model = ConformerCTC(_cfg(cfg), P)
+    max_past = case["num_left_chunks"] * case["chunk_size"]
+    eager = model.new_streaming_cache(4, max_past, chunk_frames=case["chunk_size"], seed=3)
+    graphed = model.new_streaming_cache(4, max_past, chunk_frames=case["chunk_size"], seed=3)
+    scratch = model.new_streaming_cache(2, case["chunk_size"], chunk_frames=case["chunk_size"], seed=None)
+    model.forward_chunk_paged(feats[:, :case["window"]], [0, 1], scratch)          # sizes the workspace before the capture
+    step = model.graphed_chunk_forward(graphed, batch=2, window=case["window"])
+    assert step.launches_per_replay > 0
+    for c in range(case["chunks"]):
+        xs = feats[:, c * case["step"]: c * case["step"] + case["window"]]
+        order = [0, 1] if c % 2 == 0 else [1, 0]                                   # row r of the batch is stream order[r]
+        slots = [[2, 0][s] for s in order]
+        want_lp, want_arg = model.forward_chunk_paged(xs[order], slots, eager, return_argmax=True)
+        got_lp, got_arg = step(xs[order], slots)
+        assert torch.equal(got_lp, want_lp) and torch.equal(got_arg, want_arg), c
+    assert ob.device_status() == 0
+    with pytest.raises(RuntimeError, match="captured for"):
+        step(feats[:1, :case["window"]], [0])
+
+
 def test_fp8_page_write_is_bit_exact_and_fp8_attention_matches_the_dequantised_reference():
     from oasr_b200 import fused
     from oracle import ops as O
