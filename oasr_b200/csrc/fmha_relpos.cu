@@ -11,11 +11,14 @@
 //   then that short MMA has long finished, because the exponentials of tile j were computed in between),
 //   TMEM holds S[2] (2 x 64 columns) and ONE O (64 columns) that every P.V accumulates into = 192 of 256 columns,
 // i.e. 96 KB of shared memory and half of TMEM per CTA.
-// 160 threads: warp 4 lane 0 issues TMA loads and MMAs, warps 0-3 own one query row per thread.
+// 192 threads: warp 4 lane 0 issues the MMAs, warp 5 lane 0 the TMA loads (a stage's refill waits for the MMAs that
+// read it; in one thread with the MMA issue those waits made that thread's per-tile path as long as a tile's softmax:
+// 2.7k -> 2.3k clocks per tile once split), warps 0-3 own one query row per thread.
 // Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
 // once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
 // are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
-// common case costs nothing -- then exp2 (optionally a share of them as a degree-3 polynomial on the FMA pipe,
+// common case costs nothing -- then exp2 (scale / subtract and the row sum as packed fp32x2 operations on tiles
+// without masked keys: 1.3k -> 0.8k clocks for the 64 exponentials of a thread; optionally a share of them as a degree-3 polynomial on the FMA pipe,
 // off by default: measured slower), bf16/fp16 P into swizzled shared memory.  O leaves TMEM once, at the end,
 // scaled by 1 / sum.  K | pos of tile j+2 is requested as soon as Q.K^T of tile j has finished, V of tile j+1 when
 // P.V of tile j-1 has: the two have separate stage barriers.
@@ -39,7 +42,7 @@ int g_fmha_poly = 0;         // exponentials per four on the FMA pipe in the pac
 namespace fmha_relpos {
 
 constexpr int BQ = 128, BKV = 64, D = 64;
-constexpr int kThreads = 160;
+constexpr int kThreads = 192;   // 4 softmax warps, the MMA issuer's warp, the TMA producer's warp
 constexpr int kQBytes = 2 * 128 * 128;          // [q+u | q+v]: two atoms of 128 rows x 128 B
 constexpr int kKBytes = 2 * BKV * 128;          // [k | pos] per stage
 constexpr int kVBytes = BKV * 128;
@@ -160,21 +163,36 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) stamp(p, 1);
 
-  if (warp == 4) {
-    // =================== TMA producer + MMA issuer (one thread) ===================
+  if (warp == 5) {
+    // =================== TMA producer (one thread) ===================
+    // Its own warp: the refill of a stage waits for the MMAs that read it, and those waits must not sit in the MMA
+    // issuer's instruction stream (with both roles in one thread that thread's per-tile path, about 2k clocks of
+    // serial waits and issues, was as long as the softmax of a tile and set the pace).
     if (lane == 0) {
       bool ok = true;
-      auto load_k = [&](int t, int b) {
+      ptx::mbar_expect_tx(q_full, kQBytes);
+      ptx::tma_load_4d(sQ, &map_q, 0, row0 + q0, h, 0, q_full);
+      ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, row0 + q0, h, 0, q_full);
+      for (int t = 0; ok && t < nkv; ++t) {
+        const int b = t & 1;
         const int key0 = t * BKV;
+        const uint32_t prev = ((t - 2) >> 1) & 1u;          // parity of the completion by tile t - 2, the stage's last user
+        if (t >= 2 && !ptx::mbar_wait(&k_empty[b], prev, abort_flag)) { ok = false; break; }   // Q.K^T of tile t-2 finished
         ptx::mbar_expect_tx(&k_full[b], kKBytes);
         uint8_t* dk = sK + b * kKBytes;
         ptx::tma_load_4d(dk, &map_k, 0, row0 + key0, h, 0, &k_full[b]);
         ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, h, 0, &k_full[b]);
-      };
-      auto load_v = [&](int t, int b) {
+        if (t >= 2 && !ptx::mbar_wait(&v_empty[b], prev, abort_flag)) { ok = false; break; }   // P.V of tile t-2 finished
         ptx::mbar_expect_tx(&v_full[b], kVBytes);
-        ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, row0 + t * BKV, h, 0, &v_full[b]);
-      };
+        ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, row0 + key0, h, 0, &v_full[b]);
+      }
+      if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
+    }
+    __syncwarp();
+  } else if (warp == 4) {
+    // =================== MMA issuer (one thread) ===================
+    if (lane == 0) {
+      bool ok = true;
       auto issue_qk = [&](int b) {   // S[b] = [q+u | q+v] . [k | pos]^T : K = 128 in eight steps of 16
         const uint32_t a_addr = ptx::smem_u32(sQ);
         const uint32_t b_addr = ptx::smem_u32(sK + b * kKBytes);
@@ -201,23 +219,13 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ptx::umma_commit(po_done);
         ptx::umma_commit(&v_empty[b]);
       };
-      ptx::mbar_expect_tx(q_full, kQBytes);
-      ptx::tma_load_4d(sQ, &map_q, 0, row0 + q0, h, 0, q_full);
-      ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, row0 + q0, h, 0, q_full);
-      load_k(0, 0);
-      load_v(0, 0);
-      if (nkv > 1) {
-        load_k(1, 1);
-        load_v(1, 1);
-      }
       ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&k_full[0], 0, abort_flag);
       if (ok) {
         ptx::tc_fence_after_sync();
         issue_qk(0);
       }
-      // Tile j: scores of tile j+1 are issued first (they only need S[nb] back), then the operand refills -- K | pos
-      // of tile j+2 as soon as Q.K^T of tile j has finished (two tiles ahead of its use), V of tile j+1 once P.V of
-      // tile j-1 has -- and last P.V of tile j, which waits for the softmax.
+      // Tile j: the scores of tile j+1 are issued first (they only need S[nb] back and their K | pos stage), then P.V of
+      // tile j, which waits for the softmax.
       for (int j = 0; ok && j < nkv; ++j) {
         const int b = j & 1, nb = b ^ 1;
         const uint32_t ph = (j >> 1) & 1u;
@@ -227,16 +235,6 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           if (!ok) break;
           ptx::tc_fence_after_sync();
           issue_qk(nb);
-          if (j >= 1) {   // stage nb held V of tile j-1
-            ok = ptx::mbar_wait(&v_empty[nb], ((j - 1) >> 1) & 1u, abort_flag);
-            if (!ok) break;
-            load_v(j + 1, nb);
-          }
-        }
-        if (j + 2 < nkv) {
-          ok = ptx::mbar_wait(&k_empty[b], ph, abort_flag);
-          if (!ok) break;
-          load_k(j + 2, b);
         }
         ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(j) & 1u, abort_flag) && ptx::mbar_wait(&v_full[b], ph, abort_flag);
         if (!ok) break;
@@ -289,26 +287,44 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         m_run = tile_max;
         moved = true;
       }
-      // exponentiate, sum, round: keys 4k+3 of every group of four on the FMA pipe, the others on the MUFU unit
+      // exponentiate, sum, round
       uint32_t packed[32];
       float row_sum = 0.f;
+      if (kPoly == 0 && full) {
+        // the common tile (all keys valid, every exponential on the MUFU unit): scale / subtract and the row sum as
+        // packed fp32x2 operations, no per-key selects
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 nm2 = make_float2(-m_run, -m_run);
+        float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        float e0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
-        const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run);
-        const float x3 = fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_run);
-        float e1 = kPoly >= 2 ? ex2_poly(x1) : ex2_fast(x1);
-        float e2 = ex2_fast(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m_run));
-        float e3 = kPoly >= 1 ? ex2_poly(x3) : ex2_fast(x3);
-        if (!full) {   // P of keys past the end is zero (V rows there hold other segments' finite values)
-          e0 = key0 + i < kv_len ? e0 : 0.f;
-          e1 = key0 + i + 1 < kv_len ? e1 : 0.f;
-          e2 = key0 + i + 2 < kv_len ? e2 : 0.f;
-          e3 = key0 + i + 3 < kv_len ? e3 : 0.f;
+        for (int i = 0; i < 64; i += 2) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
+          const float2 e = make_float2(ex2_fast(x.x), ex2_fast(x.y));
+          acc[(i >> 1) & 1] = __fadd2_rn(acc[(i >> 1) & 1], e);
+          packed[i / 2] = pack2<T>(e.x, e.y);
         }
-        row_sum += (e0 + e1) + (e2 + e3);
-        packed[i / 2] = pack2<T>(e0, e1);
-        packed[i / 2 + 1] = pack2<T>(e2, e3);
+        const float2 a = __fadd2_rn(acc[0], acc[1]);
+        row_sum = a.x + a.y;
+      } else {
+        // keys 4k+3 (and 4k+1) of every group of four optionally on the FMA pipe; keys past the end give P = 0
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          float e0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
+          const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run);
+          const float x3 = fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_run);
+          float e1 = kPoly >= 2 ? ex2_poly(x1) : ex2_fast(x1);
+          float e2 = ex2_fast(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m_run));
+          float e3 = kPoly >= 1 ? ex2_poly(x3) : ex2_fast(x3);
+          if (!full) {   // P of keys past the end is zero (V rows there hold other segments' finite values)
+            e0 = key0 + i < kv_len ? e0 : 0.f;
+            e1 = key0 + i + 1 < kv_len ? e1 : 0.f;
+            e2 = key0 + i + 2 < kv_len ? e2 : 0.f;
+            e3 = key0 + i + 3 < kv_len ? e3 : 0.f;
+          }
+          row_sum += (e0 + e1) + (e2 + e3);
+          packed[i / 2] = pack2<T>(e0, e1);
+          packed[i / 2 + 1] = pack2<T>(e2, e3);
+        }
       }
       if (j == 3 && r == 0) stamp(p, 53);
       // P.V of tile j-1 has finished: P may be rewritten and O is stable (it is only touched here when the maximum moved)
