@@ -519,6 +519,20 @@ OASR_API int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const voi
                                           const int32_t* cu_seqlens, int64_t num_segs,
                                           int64_t max_seqlen, int64_t total, int64_t H,
                                           double scale, int dtype, void* stream);
+/* Work list for oasr_b200_fmha_varlen_relpos_planned: the items (segment, head, 128-row query tile) of a packed
+ * batch, longest segments first, so that the persistent kernel's last items are short ones.  Built on the device
+ * from cu_seqlens (no host synchronisation), once per batch; every layer's attention call reuses it.  plan must hold
+ * oasr_b200_fmha_relpos_plan_bytes(num_segs, H, total) bytes, 16-byte aligned; num_segs <= 1024 (larger batches run
+ * the unplanned entry point, which walks the items in (segment, head, tile) order).  No reference counterpart. */
+OASR_API int64_t oasr_b200_fmha_relpos_plan_bytes(int64_t num_segs, int64_t H, int64_t total);
+OASR_API int oasr_b200_fmha_relpos_plan(void* plan, int64_t plan_bytes, const int32_t* cu_seqlens,
+                                        int64_t num_segs, int64_t H, int64_t total, void* stream);
+/* oasr_b200_fmha_varlen_relpos following a plan (NULL = the unplanned order). */
+OASR_API int oasr_b200_fmha_varlen_relpos_planned(void* out, const void* qkv4, const void* pos, int64_t pos_rows,
+                                                  int64_t pos_stride, const int32_t* cu_seqlens,
+                                                  int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H,
+                                                  double scale, const void* plan /*nullable*/, int dtype,
+                                                  void* stream);
 
 /* Streaming form of the above: the attention of
  * RelPositionMultiHeadedAttention._forward_paged (oasr/layers/attention/attention.py:229-280)

@@ -54,6 +54,8 @@ _SIGNATURES = {
     "oasr_b200_trace_buffer": [P],
     "oasr_b200_depthwise_conv1d_packed": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_int, c_int, P],
     "oasr_b200_fmha_varlen_relpos": [P, P, P, I, I, P, I, I, I, I, c_double, c_int, P],
+    "oasr_b200_fmha_varlen_relpos_planned": [P, P, P, I, I, P, I, I, I, I, c_double, P, c_int, P],
+    "oasr_b200_fmha_relpos_plan": [P, I, P, I, I, I, P],
     "oasr_b200_fmha_paged_relpos": [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, c_double, c_int, P],
     "oasr_b200_depthwise_conv1d_affine": [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P],
     "oasr_b200_conv_state_concat": [P, P, I, P, P, I, I, I, I, c_int, P],
@@ -173,6 +175,8 @@ def load() -> ctypes.CDLL:
     lib.oasr_b200_profile_count.argtypes = []
     lib.oasr_b200_conformer_workspace_bytes.restype = c_int64
     lib.oasr_b200_conformer_workspace_bytes.argtypes = [POINTER(ConformerModel), I, I]
+    lib.oasr_b200_fmha_relpos_plan_bytes.restype = c_int64
+    lib.oasr_b200_fmha_relpos_plan_bytes.argtypes = [I, I, I]
     lib.oasr_b200_fastconformer_workspace_bytes.restype = c_int64
     lib.oasr_b200_fastconformer_workspace_bytes.argtypes = [POINTER(FastConformerModel), I, I, I]
     for name, argtypes in _SIGNATURES.items():
@@ -188,7 +192,7 @@ def load() -> ctypes.CDLL:
 def exported_names() -> list[str]:
     return list(_STRING_FUNCS) + ["oasr_b200_launch_count", "oasr_b200_conformer_workspace_bytes", "oasr_b200_profile_count",
                                   "oasr_b200_conformer_noalloc_capacity_bytes", "oasr_b200_conformer_chunk_workspace_bytes",
-                                  "oasr_b200_fastconformer_workspace_bytes"] + list(_SIGNATURES)
+                                  "oasr_b200_fastconformer_workspace_bytes", "oasr_b200_fmha_relpos_plan_bytes"] + list(_SIGNATURES)
 
 
 def launch_count() -> int:

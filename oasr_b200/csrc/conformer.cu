@@ -23,6 +23,8 @@ struct Workspace {
   uint8_t* cv;     // (M, d)
   uint8_t* h3;     // (M, 2d)  after_norm as [hi | lo]
   uint8_t* pos;    // (max_seg, L*d)
+  uint8_t* att_plan;  // work list of the packed attention kernel (oasr_b200_fmha_relpos_plan)
+  int64_t att_plan_bytes;
   uint8_t* q8;     // (M, max(ffn, d)) one byte per element: per-token quantised GEMM input (quant_kind != 0)
   float* qs;       // (M) its scales
   int64_t bytes;
@@ -107,6 +109,9 @@ Workspace carve(const oasr_b200_conformer_model& m, int64_t M, int64_t max_seg, 
   w.cv = take(M * d * 2);
   w.h3 = take(M * 2 * d * 2);
   w.pos = take(max_seg * m.num_layers * d * 2);
+  // the plan serves at most 1024 segments (beyond that attention runs unplanned), each of at least one frame
+  w.att_plan_bytes = oasr_b200_fmha_relpos_plan_bytes(M < 1024 ? M : 1024, m.heads, M);
+  w.att_plan = take(w.att_plan_bytes);
   if (m.quant_kind != 0) {
     w.q8 = take(M * (m.ffn > d ? m.ffn : d));
     w.qs = reinterpret_cast<float*>(take(M * 4));
@@ -244,6 +249,12 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
                                    nullptr, nullptr, M, d, m.eps, 0, dt, stream));
   }
   }
+  // attention work list (longest segments first), once per batch; every layer reuses it
+  const void* att_plan = nullptr;
+  if (num_segs <= 1024 && oasr_b200_fmha_relpos_plan_bytes(num_segs, m.heads, M) <= w.att_plan_bytes) {
+    OB_STEP("fmha_relpos_plan", 0, oasr_b200_fmha_relpos_plan(w.att_plan, w.att_plan_bytes, cu_seqlens, num_segs, m.heads, M, stream));
+    att_plan = w.att_plan;
+  }
   // linear_pos of every layer in one GEMM: (max_seg, d) x (L*d, d)^T
   OB_STEP("gemm linear_pos", 2.0 * max_seg * L * d * d, oasr_b200_gemm(w.pos, m.pe, m.pos_w_all, nullptr, max_seg, L * d, d, OASR_ACT_NONE, dt, stream));
 
@@ -255,8 +266,8 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
                       l.norm_mha_b, nullptr, nullptr, m.eps, 0);
     // relative-position self-attention
     OB_LINEAR("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, d, OASR_ACT_NONE, 0);
-    OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs, max_seg,
-                                         M, m.heads, scale, dt, stream));
+    OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos_planned(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs,
+                                         max_seg, M, m.heads, scale, att_plan, dt, stream));
     OB_LINEAR_ADDNORM("attn_out", 2.0 * M * d * d, w.h, w.res, w.att, l.out_w, l.out_b, l, 3, d, 1.0, 1, l.norm_conv_scale,
                       l.norm_conv_shift, nullptr, nullptr, m.eps, 0);
     // convolution module

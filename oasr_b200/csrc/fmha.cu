@@ -630,7 +630,11 @@ bool stride_ok(int64_t s) { return s % 8 == 0; }
 
 namespace fmha_relpos {  // fmha_relpos.cu: packed relative-position form, two CTAs per SM
 int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t pos_stride, const int32_t* cu_seqlens,
-        int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype, cudaStream_t stream);
+        int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype, const int2* items,
+        const int32_t* n_items, cudaStream_t stream);
+constexpr int kPlanMaxSegs = 1024;
+int64_t plan_bytes(int64_t num_segs, int64_t H, int64_t total);
+int plan(void* plan_buf, const int32_t* cu_seqlens, int64_t num_segs, int64_t H, cudaStream_t stream);
 }  // namespace fmha_relpos
 extern int g_fmha_relpos_path;
 
@@ -647,10 +651,49 @@ int run(void* out, const void* qkv4, void* k_pool, void* v_pool, const float* k_
 
 extern "C" {
 
+int64_t oasr_b200_fmha_relpos_plan_bytes(int64_t num_segs, int64_t H, int64_t total) {
+  if (num_segs < 0 || H <= 0 || total < 0) return -1;
+  return ob::fmha_relpos::plan_bytes(num_segs, H, total);
+}
+
+int oasr_b200_fmha_relpos_plan(void* plan, int64_t plan_bytes, const int32_t* cu_seqlens, int64_t num_segs, int64_t H,
+                               int64_t total, void* stream) {
+  using namespace ob;
+  OB_REQUIRE(num_segs >= 0 && H > 0 && H <= 32767 && total >= 0, OASR_ERR_INVALID, "fmha_relpos_plan: bad shape");
+  if (num_segs == 0) return OASR_OK;
+  OB_REQUIRE(plan && cu_seqlens && is_aligned(plan, 16), OASR_ERR_INVALID, "fmha_relpos_plan: null or unaligned pointer");
+  OB_REQUIRE(num_segs <= fmha_relpos::kPlanMaxSegs, OASR_ERR_UNSUPPORTED,
+             "fmha_relpos_plan: at most %d segments (got %lld); run oasr_b200_fmha_varlen_relpos without a plan",
+             fmha_relpos::kPlanMaxSegs, (long long)num_segs);
+  OB_REQUIRE(plan_bytes >= fmha_relpos::plan_bytes(num_segs, H, total), OASR_ERR_INVALID,
+             "fmha_relpos_plan: plan buffer of %lld bytes, %lld needed", (long long)plan_bytes,
+             (long long)fmha_relpos::plan_bytes(num_segs, H, total));
+  return fmha_relpos::plan(plan, cu_seqlens, num_segs, H, static_cast<cudaStream_t>(stream));
+}
+
+static int fmha_varlen_relpos_impl(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t pos_stride,
+                                   const int32_t* cu_seqlens, int64_t num_segs, int64_t max_seqlen, int64_t total,
+                                   int64_t H, double scale, const void* plan, int dtype, void* stream_);
+
 int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, int64_t pos_rows,
                                  int64_t pos_stride, const int32_t* cu_seqlens, int64_t num_segs,
                                  int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype,
                                  void* stream_) {
+  return fmha_varlen_relpos_impl(out, qkv4, pos, pos_rows, pos_stride, cu_seqlens, num_segs, max_seqlen, total, H, scale,
+                                 nullptr, dtype, stream_);
+}
+
+int oasr_b200_fmha_varlen_relpos_planned(void* out, const void* qkv4, const void* pos, int64_t pos_rows,
+                                         int64_t pos_stride, const int32_t* cu_seqlens, int64_t num_segs,
+                                         int64_t max_seqlen, int64_t total, int64_t H, double scale, const void* plan,
+                                         int dtype, void* stream_) {
+  return fmha_varlen_relpos_impl(out, qkv4, pos, pos_rows, pos_stride, cu_seqlens, num_segs, max_seqlen, total, H, scale,
+                                 plan, dtype, stream_);
+}
+
+static int fmha_varlen_relpos_impl(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t pos_stride,
+                                   const int32_t* cu_seqlens, int64_t num_segs, int64_t max_seqlen, int64_t total,
+                                   int64_t H, double scale, const void* plan, int dtype, void* stream_) {
   using namespace ob;
   using namespace ob::fmha;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -663,7 +706,9 @@ int oasr_b200_fmha_varlen_relpos(void* out, const void* qkv4, const void* pos, i
              OASR_ERR_ALIGN, "fmha_varlen_relpos: operands must be 16-byte aligned");
   if (num_segs == 0 || max_seqlen == 0 || total == 0) return OASR_OK;
   if (g_fmha_relpos_path)
-    return fmha_relpos::run(out, qkv4, pos, pos_rows, pos_stride, cu_seqlens, num_segs, max_seqlen, total, H, scale, dtype, stream);
+    return fmha_relpos::run(out, qkv4, pos, pos_rows, pos_stride, cu_seqlens, num_segs, max_seqlen, total, H, scale, dtype,
+                            plan ? reinterpret_cast<const int2*>(static_cast<const int32_t*>(plan) + 4) : nullptr,
+                            static_cast<const int32_t*>(plan), stream);
   const int64_t d = H * D, ld = 4 * d;
   const uint8_t* base = static_cast<const uint8_t*>(qkv4);
   Maps maps;

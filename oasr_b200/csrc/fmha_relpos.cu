@@ -49,7 +49,7 @@ constexpr int kVBytes = BKV * 128;
 constexpr int kPBytes = BQ * 128;               // 128 rows x 64 keys
 constexpr int kOffQ = 0, kOffK = kOffQ + kQBytes, kOffV = kOffK + 2 * kKBytes, kOffP = kOffV + 2 * kVBytes;
 constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kNumBars = 15;
+constexpr int kNumBars = 16;
 constexpr int kSmemDynamic = kOffBar + kNumBars * 8 + 16 + 1024;
 constexpr uint32_t kTmemCols = 256, kColS = 0, kColO = 128;
 constexpr float kLazyLog2 = 8.f;   // rescale only when the row maximum grows by more than 2^8
@@ -60,6 +60,10 @@ struct Params {
   const int32_t* cu;
   void* out;
   uint32_t* status;
+  const int2* items;           // nullable: work items (segment, head << 16 | query tile), longest segments first
+  const int32_t* n_items;      // device count of `items`
+  int natural_items;           // items == null: num_segs * H * qtiles, item i = (segment, head, query tile) in that order
+  int qtiles;                  // query tiles of the longest segment
   unsigned long long* trace;   // nullable diagnostics buffer: the CTA (0, 0, trace_seg) stamps its phases
   int trace_seg;
 };
@@ -109,13 +113,28 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
   ptx::grid_dep_wait();
   if (threadIdx.x == 0) stamp(p, 0);
-  const int q0 = blockIdx.x * BQ, h = blockIdx.y, seg = blockIdx.z;
-  const int row0 = p.cu[seg], kv_len = p.cu[seg + 1] - row0;
-  if (q0 >= kv_len) return;  // CTA-uniform (queries and keys of a segment are the same rows)
-  const int nkv = (kv_len + BKV - 1) / BKV;
-  const int rows_valid = min(BQ, kv_len - q0);
+  // Persistent CTA: walks work items blockIdx.x, + gridDim.x, ... of the list (or of the natural enumeration).  All
+  // roles decode the same items in the same order; an item whose query tile lies past its segment is skipped by all.
+  const int n_items = p.items ? *p.n_items : p.natural_items;
   const int64_t out_ld = static_cast<int64_t>(p.H) * D;
-  T* out = static_cast<T*>(p.out) + (static_cast<int64_t>(row0 + q0) * p.H + h) * D;
+  struct Item { int h, q0, row0, kv_len, nkv; };
+  auto decode = [&](int it, Item& w) -> bool {
+    int seg, qt;
+    if (p.items) {
+      const int2 v = p.items[it];
+      seg = v.x; w.h = v.y >> 16; qt = v.y & 0xffff;
+    } else {
+      qt = it % p.qtiles;
+      const int rest = it / p.qtiles;
+      w.h = rest % p.H;
+      seg = rest / p.H;
+    }
+    w.row0 = p.cu[seg];
+    w.kv_len = p.cu[seg + 1] - w.row0;
+    w.q0 = qt * BQ;
+    w.nkv = (w.kv_len + BKV - 1) / BKV;
+    return w.q0 < w.kv_len;
+  };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -133,6 +152,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint64_t* po_done = bars + 10;   // P.V of a tile has been accumulated into O: O is stable and P may be rewritten
   uint64_t* v_full = bars + 11;    // [2]  V stage landed
   uint64_t* v_empty = bars + 13;   // [2]  P.V of the stage's tile finished
+  uint64_t* o_free = bars + 15;    // every softmax thread has read the item's O: the next item's first P.V may overwrite it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -149,6 +169,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     ptx::mbar_init(po_done, 1);
     ptx::mbar_init(p_full, BQ);
+    ptx::mbar_init(o_free, BQ);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -163,6 +184,8 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) stamp(p, 1);
 
+  // Every barrier that completes once per key tile is indexed by the CTA's running tile count g (stage g & 1, phase
+  // g >> 1), which carries on from one item to the next, so the pipeline never drains between items.
   if (warp == 5) {
     // =================== TMA producer (one thread) ===================
     // Its own warp: the refill of a stage waits for the MMAs that read it, and those waits must not sit in the MMA
@@ -170,21 +193,31 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // serial waits and issues, was as long as the softmax of a tile and set the pace).
     if (lane == 0) {
       bool ok = true;
-      ptx::mbar_expect_tx(q_full, kQBytes);
-      ptx::tma_load_4d(sQ, &map_q, 0, row0 + q0, h, 0, q_full);
-      ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, row0 + q0, h, 0, q_full);
-      for (int t = 0; ok && t < nkv; ++t) {
-        const int b = t & 1;
-        const int key0 = t * BKV;
-        const uint32_t prev = ((t - 2) >> 1) & 1u;          // parity of the completion by tile t - 2, the stage's last user
-        if (t >= 2 && !ptx::mbar_wait(&k_empty[b], prev, abort_flag)) { ok = false; break; }   // Q.K^T of tile t-2 finished
-        ptx::mbar_expect_tx(&k_full[b], kKBytes);
-        uint8_t* dk = sK + b * kKBytes;
-        ptx::tma_load_4d(dk, &map_k, 0, row0 + key0, h, 0, &k_full[b]);
-        ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, h, 0, &k_full[b]);
-        if (t >= 2 && !ptx::mbar_wait(&v_empty[b], prev, abort_flag)) { ok = false; break; }   // P.V of tile t-2 finished
-        ptx::mbar_expect_tx(&v_full[b], kVBytes);
-        ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, row0 + key0, h, 0, &v_full[b]);
+      int g = 0, done = 0;
+      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
+        Item w;
+        if (!decode(it, w)) continue;
+        if (done > 0) {   // Q is single-buffered: the previous item's last Q.K^T (tile g-1) has finished
+          if (!ptx::mbar_wait(&k_empty[(g - 1) & 1], ((g - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        }
+        ptx::mbar_expect_tx(q_full, kQBytes);
+        ptx::tma_load_4d(sQ, &map_q, 0, w.row0 + w.q0, w.h, 0, q_full);
+        ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, w.row0 + w.q0, w.h, 0, q_full);
+        for (int t = 0; ok && t < w.nkv; ++t) {
+          const int gg = g + t, b = gg & 1;
+          const int key0 = t * BKV;
+          const uint32_t prev = ((gg - 2) >> 1) & 1u;         // phase of tile gg - 2, the stage's last user
+          if (gg >= 2 && !ptx::mbar_wait(&k_empty[b], prev, abort_flag)) { ok = false; break; }   // its Q.K^T finished
+          ptx::mbar_expect_tx(&k_full[b], kKBytes);
+          uint8_t* dk = sK + b * kKBytes;
+          ptx::tma_load_4d(dk, &map_k, 0, w.row0 + key0, w.h, 0, &k_full[b]);
+          ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, w.h, 0, &k_full[b]);
+          if (gg >= 2 && !ptx::mbar_wait(&v_empty[b], prev, abort_flag)) { ok = false; break; }   // its P.V finished
+          ptx::mbar_expect_tx(&v_full[b], kVBytes);
+          ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, w.row0 + key0, w.h, 0, &v_full[b]);
+        }
+        g += w.nkv;
+        ++done;
       }
       if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
     }
@@ -219,27 +252,33 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ptx::umma_commit(po_done);
         ptx::umma_commit(&v_empty[b]);
       };
-      ok = ptx::mbar_wait(q_full, 0, abort_flag) && ptx::mbar_wait(&k_full[0], 0, abort_flag);
-      if (ok) {
+      // scores of tile gg: its K | pos stage has landed and S[gg & 1] has been read by the softmax of tile gg - 2
+      auto scores = [&](int gg) -> bool {
+        const int b = gg & 1;
+        const uint32_t ph = (gg >> 1) & 1u;
+        if (!ptx::mbar_wait(&k_full[b], ph, abort_flag) || !ptx::mbar_wait(&s_free[b], ph ^ 1u, abort_flag)) return false;
         ptx::tc_fence_after_sync();
-        issue_qk(0);
-      }
-      // Tile j: the scores of tile j+1 are issued first (they only need S[nb] back and their K | pos stage), then P.V of
-      // tile j, which waits for the softmax.
-      for (int j = 0; ok && j < nkv; ++j) {
-        const int b = j & 1, nb = b ^ 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (j + 1 < nkv) {
-          const uint32_t nph = ((j + 1) >> 1) & 1u;
-          ok = ptx::mbar_wait(&k_full[nb], nph, abort_flag) && ptx::mbar_wait(&s_free[nb], nph ^ 1u, abort_flag);
+        issue_qk(b);
+        return true;
+      };
+      int g = 0, done = 0;
+      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
+        Item w;
+        if (!decode(it, w)) continue;
+        ok = ptx::mbar_wait(q_full, static_cast<uint32_t>(done) & 1u, abort_flag) && scores(g);
+        // Tile j: the scores of tile j+1 are issued first, then P.V of tile j, which waits for the softmax.
+        for (int j = 0; ok && j < w.nkv; ++j) {
+          const int gg = g + j, b = gg & 1;
+          if (j + 1 < w.nkv && !scores(gg + 1)) { ok = false; break; }
+          ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(gg) & 1u, abort_flag) &&
+               ptx::mbar_wait(&v_full[b], (gg >> 1) & 1u, abort_flag);
+          if (ok && j == 0 && done > 0) ok = ptx::mbar_wait(o_free, static_cast<uint32_t>(done - 1) & 1u, abort_flag);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          issue_qk(nb);
+          issue_pv(b, j == 0);
         }
-        ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(j) & 1u, abort_flag) && ptx::mbar_wait(&v_full[b], ph, abort_flag);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        issue_pv(b, j == 0);
+        g += w.nkv;
+        ++done;
       }
       if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
     }
@@ -248,14 +287,20 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // =========================== softmax / output (thread = row) ===========================
     const int r = threadIdx.x;  // 0..127
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const bool row_ok = r < rows_valid;
     const uint32_t t_o = tmem_base + lane_base + kColO;
-    float m_run = kNegInf, l_run = 0.f;   // m_run: the reference maximum the exponentials, l_run and O are relative to
     bool ok = true;
+    int g = 0;
+    for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
+    Item w;
+    if (!decode(it, w)) continue;
+    const int kv_len = w.kv_len, nkv = w.nkv;
+    const bool row_ok = r < min(BQ, kv_len - w.q0);
+    T* out = static_cast<T*>(p.out) + (static_cast<int64_t>(w.row0 + w.q0) * p.H + w.h) * D;
+    float m_run = kNegInf, l_run = 0.f;   // m_run: the reference maximum the exponentials, l_run and O are relative to
     for (int j = 0; ok && j < nkv; ++j) {
-      const int b = j & 1;
+      const int gg = g + j, b = gg & 1;
       const int key0 = j * BKV;
-      if (!ptx::mbar_wait(&s_full[b], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      if (!ptx::mbar_wait(&s_full[b], (gg >> 1) & 1u, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       if (j == 0 && r == 0) stamp(p, 2);
       if (j == 3 && r == 0) stamp(p, 50);
@@ -329,7 +374,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (j == 3 && r == 0) stamp(p, 53);
       // P.V of tile j-1 has finished: P may be rewritten and O is stable (it is only touched here when the maximum moved)
       if (j >= 1) {
-        if (!ptx::mbar_wait(po_done, static_cast<uint32_t>(j - 1) & 1u, abort_flag)) { ok = false; break; }
+        if (!ptx::mbar_wait(po_done, static_cast<uint32_t>(gg - 1) & 1u, abort_flag)) { ok = false; break; }
         if (moved) {
           ptx::tc_fence_after_sync();
           uint32_t o[64];
@@ -357,7 +402,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       ptx::mbar_arrive(p_full);
       if (r == 0 && j < 40) stamp(p, 3 + j);
     }
-    if (ok) ok = ptx::mbar_wait(po_done, static_cast<uint32_t>(nkv - 1) & 1u, abort_flag);
+    if (ok) ok = ptx::mbar_wait(po_done, static_cast<uint32_t>(g + nkv - 1) & 1u, abort_flag);
     if (ok) {
       ptx::tc_fence_after_sync();
       uint32_t o[64];
@@ -377,7 +422,11 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
       }
       if (r == 0) stamp(p, 60);
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(o_free);             // O is in registers: the next item's first P.V may overwrite it
     }
+    g += nkv;
+    }   // items
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusFmhaSoftmax);
   }
 
@@ -400,7 +449,8 @@ int make_map(CUtensorMap* m, int dtype, const void* base, int64_t rows, int64_t 
 }
 
 int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t pos_stride, const int32_t* cu_seqlens,
-        int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype, cudaStream_t stream) {
+        int64_t num_segs, int64_t max_seqlen, int64_t total, int64_t H, double scale, int dtype, const int2* items,
+        const int32_t* n_items, cudaStream_t stream) {
   const int64_t d = H * D, ld = 4 * d;
   const uint8_t* base = static_cast<const uint8_t*>(qkv4);
   CUtensorMap mq, mq2, mk, mp, mv;
@@ -414,7 +464,14 @@ int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t 
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.cu = cu_seqlens; p.out = out; p.status = device_status_ptr();
   p.trace = g_trace_buffer; p.trace_seg = 0;
-  dim3 grid((unsigned)((max_seqlen + BQ - 1) / BQ), (unsigned)H, (unsigned)num_segs);
+  p.items = items; p.n_items = n_items;
+  p.qtiles = static_cast<int>((max_seqlen + BQ - 1) / BQ);
+  const int64_t natural = num_segs * H * p.qtiles;
+  OB_REQUIRE(natural < (int64_t(1) << 31), OASR_ERR_INVALID, "fmha_varlen_relpos: too many work items");
+  p.natural_items = static_cast<int>(natural);
+  int64_t ctas = 2 * static_cast<int64_t>(sm_count());     // two resident CTAs per SM, each walking the item list
+  if (natural < ctas) ctas = natural;
+  dim3 grid(static_cast<unsigned>(ctas));
   auto launch_one = [&](auto kern) -> int {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDynamic);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
@@ -429,6 +486,60 @@ int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t 
     if (g_fmha_poly == 1) return launch_one(fmha_relpos64_kernel<T, 1>);
     return launch_one(fmha_relpos64_kernel<T, 2>);
   });
+}
+
+
+// Work list for the persistent kernel: items (segment, head, query tile) with the longest segments first, so that the
+// CTAs that pick up the last items pick up short ones (a tile's cost is proportional to its segment's length).  One
+// block; segments are ranked by counting (num_segs <= 1024), the items of rank r start at the prefix sum of the
+// ranks before it.  plan = [int32 n_items, pad to 16 bytes][int2 items...].
+constexpr int kPlanMaxSegs = 1024;
+__global__ void __launch_bounds__(kPlanMaxSegs) plan_kernel(int32_t* plan, const int32_t* __restrict__ cu, int S, int H) {
+  __shared__ int len[kPlanMaxSegs];
+  __shared__ int seg_of_rank[kPlanMaxSegs];
+  __shared__ int start[kPlanMaxSegs + 1];
+  const int t = threadIdx.x;
+  if (t < S) len[t] = cu[t + 1] - cu[t];
+  __syncthreads();
+  if (t < S) {
+    int rank = 0;
+    const int mine = len[t];
+    for (int k = 0; k < S; ++k) rank += (len[k] > mine || (len[k] == mine && k < t)) ? 1 : 0;
+    seg_of_rank[rank] = t;
+  }
+  __syncthreads();
+  // inclusive scan of the items per rank (Hillis-Steele over S <= 1024 entries)
+  int mine_items = 0;
+  if (t < S) mine_items = ((len[seg_of_rank[t]] + BQ - 1) / BQ) * H;
+  start[t + 1 <= kPlanMaxSegs ? t + 1 : kPlanMaxSegs] = 0;
+  __syncthreads();
+  if (t < S) start[t + 1] = mine_items;
+  if (t == 0) start[0] = 0;
+  __syncthreads();
+  for (int d = 1; d < S; d <<= 1) {
+    int add = 0;
+    if (t < S && t + 1 - d >= 1) add = start[t + 1 - d];
+    __syncthreads();
+    if (t < S) start[t + 1] += add;
+    __syncthreads();
+  }
+  if (t == 0) plan[0] = start[S];
+  if (t < S) {
+    const int seg = seg_of_rank[t];
+    const int qt_n = (len[seg] + BQ - 1) / BQ;
+    int2* items = reinterpret_cast<int2*>(plan + 4) + start[t];
+    for (int qt = 0; qt < qt_n; ++qt)
+      for (int h = 0; h < H; ++h) items[qt * H + h] = make_int2(seg, (h << 16) | qt);
+  }
+}
+
+// every segment contributes H * ceil(len / 128) items: at most H * (total / 128 + num_segs) over all segments
+int64_t plan_bytes(int64_t num_segs, int64_t H, int64_t total) { return 16 + 8 * H * (total / BQ + num_segs); }
+
+int plan(void* plan_buf, const int32_t* cu_seqlens, int64_t num_segs, int64_t H, cudaStream_t stream) {
+  plan_kernel<<<1, kPlanMaxSegs, 0, stream>>>(static_cast<int32_t*>(plan_buf), cu_seqlens, static_cast<int>(num_segs),
+                                              static_cast<int>(H));
+  return check_launch("fmha_relpos_plan launch");
 }
 
 }  // namespace fmha_relpos

@@ -90,21 +90,33 @@ def depthwise_conv1d_packed_causal(x: torch.Tensor, weight: torch.Tensor, bias: 
     return out
 
 
+def fmha_relpos_plan(cu_seqlens: torch.Tensor, heads: int, total: int) -> torch.Tensor:
+    """Work list for :func:`fmha_varlen_relpos` (``plan=``): the (segment, head, query tile) items of a packed batch,
+    longest segments first, built on the device from ``cu_seqlens``; at most 1024 segments.  Build once per batch."""
+    _need_cuda(cu_seqlens)
+    S = cu_seqlens.numel() - 1
+    nbytes = int(_lib.load().oasr_b200_fmha_relpos_plan_bytes(S, heads, int(total)))
+    plan = torch.empty((nbytes + 15) // 16 * 4, device=cu_seqlens.device, dtype=torch.int32)
+    _lib.call("oasr_b200_fmha_relpos_plan", _p(plan), plan.numel() * 4, _p(cu_seqlens), S, heads, int(total), _stream(cu_seqlens))
+    return plan
+
+
 def fmha_varlen_relpos(qkv4: torch.Tensor, pos: torch.Tensor, cu_seqlens: torch.Tensor, max_seg_len: int,
-                       heads: int, scale: float, out=None) -> torch.Tensor:
+                       heads: int, scale: float, out=None, plan: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Conformer relative-position attention over packed rows
     (RelPositionMultiHeadedAttention._forward_packed, oasr/layers/attention/attention.py:323-386).
     ``qkv4`` ``(total, 4*d)`` = ``[q+u | q+v | k | v]``; ``pos`` = ``linear_pos(pe)[:>=max_seg_len]``
-    as a ``(rows, d)`` view with unit inner stride; returns ``(total, d)``."""
-    _need_cuda(qkv4, pos, cu_seqlens)
+    as a ``(rows, d)`` view with unit inner stride; returns ``(total, d)``.  ``plan`` (from :func:`fmha_relpos_plan`)
+    makes the persistent kernel walk the longest segments first; the result does not depend on it."""
+    _need_cuda(qkv4, pos, cu_seqlens, plan)
     total, d4 = qkv4.shape
     d = d4 // 4
     if out is None:
         out = torch.empty(total, d, device=qkv4.device, dtype=qkv4.dtype)
     if pos.stride(1) != 1:
         raise ValueError("pos must have unit stride along the feature axis")
-    _lib.call("oasr_b200_fmha_varlen_relpos", _p(out), _p(qkv4), _p(pos), pos.size(0), pos.stride(0), _p(cu_seqlens),
-              cu_seqlens.numel() - 1, int(max_seg_len), total, heads, float(scale), _DTYPE_ID[qkv4.dtype],
+    _lib.call("oasr_b200_fmha_varlen_relpos_planned", _p(out), _p(qkv4), _p(pos), pos.size(0), pos.stride(0), _p(cu_seqlens),
+              cu_seqlens.numel() - 1, int(max_seg_len), total, heads, float(scale), _p(plan), _DTYPE_ID[qkv4.dtype],
               _stream(qkv4))
     return out
 

@@ -294,3 +294,33 @@ def test_fmha_varlen_relpos_matches_fp32_reference(dtype, path):
         want = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v).reshape(n, d)
         err = (got[a:a + n] - want).abs().max().item()
         assert err < TOL, (s, n, err)
+
+
+def test_planned_relpos_attention_equals_the_unplanned_order():
+    """The persistent packed rel-pos kernel following a longest-first work list (oasr_b200_fmha_relpos_plan) against
+    the same kernel walking (segment, head, tile) order: bit-identical output; the list holds every (segment, head,
+    query tile) exactly once, longest segments first, and skips empty segments; many more items than resident CTAs."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(4)
+    rng = np.random.default_rng(0)
+    lens = [0, 1, 130, 0, 500] + [int(x) for x in rng.integers(1, 400, size=90)]
+    H, D = 8, 64
+    d = H * D
+    total = sum(lens)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32).cuda()
+    qkv4 = (torch.randn(total, 4 * d) * 0.7).bfloat16().cuda()
+    pos = torch.randn(512, d).bfloat16().cuda()
+    plan = fused.fmha_relpos_plan(cu, H, total)
+    want = fused.fmha_varlen_relpos(qkv4, pos, cu, max(lens), H, D ** -0.5)
+    got = fused.fmha_varlen_relpos(qkv4, pos, cu, max(lens), H, D ** -0.5, plan=plan)
+    assert ob.device_status() == 0
+    assert torch.equal(got, want)
+    host = plan.cpu().numpy()
+    n = int(host[0])
+    items = host[4:4 + 2 * n].reshape(n, 2)
+    seg, head, qt = items[:, 0], items[:, 1] >> 16, items[:, 1] & 0xffff
+    expect = {(s, h, q) for s, L in enumerate(lens) for h in range(H) for q in range((L + 127) // 128)}
+    assert n == len(expect) and set(zip(seg.tolist(), head.tolist(), qt.tolist())) == expect
+    item_len = np.asarray(lens)[seg]
+    assert (np.diff(item_len) <= 0).all()
