@@ -206,7 +206,7 @@ class FastConformerLayers:
 
     def _layers(self, res: torch.Tensor, g) -> torch.Tensor:
         """``res (M, C)`` fp32 rows (overwritten: the residual stream) -> ``(M, C)`` fp32 output of the stack."""
-        if self.native and g["packed"]:
+        if self.native and self.qkind == 0 and g["packed"]:      # the native executor runs the 16-bit stack
             return self._layers_native(res, g)
         return self._layers_composed(res, g)
 
