@@ -81,18 +81,21 @@ class PackedBatch:
 def build_packed_batch(out_lengths: List[int], padded_t: int, conv_kernel: int, device) -> PackedBatch:
     """Index tensors from HOST lengths: no device synchronisation (the reference pulls
     ``seg_lengths.tolist()`` from the device, packing.py:143)."""
-    cu = [0]
-    for n in out_lengths:
-        cu.append(cu[-1] + n)
-    total = cu[-1]
+    import numpy as np
+
+    lens = np.asarray(out_lengths, dtype=np.int64).reshape(-1)
+    cu = np.zeros(lens.size + 1, dtype=np.int64)
+    np.cumsum(lens, out=cu[1:])
+    total = int(cu[-1])
     half = (conv_kernel - 1) // 2
-    idx = torch.cat([torch.arange(n, dtype=torch.int64) + b * padded_t for b, n in enumerate(out_lengths)]) \
-        if total else torch.zeros(0, dtype=torch.int64)
-    fill = torch.tensor([min(half, padded_t - n) for n in out_lengths], dtype=torch.int32)
+    # packed row r of utterance b sits at padded row b * padded_t + (r - cu[b]): one vectorised pass, no per-utterance work
+    idx = torch.from_numpy(np.arange(total, dtype=np.int64) +
+                           np.repeat(np.arange(lens.size, dtype=np.int64) * padded_t - cu[:-1], lens))
+    fill = torch.from_numpy(np.minimum(half, padded_t - lens).astype(np.int32))
     return PackedBatch(
-        num_segs=len(out_lengths), total=total, max_seg=max(out_lengths) if out_lengths else 0, padded_t=padded_t,
+        num_segs=int(lens.size), total=total, max_seg=int(lens.max()) if lens.size else 0, padded_t=padded_t,
         seg_lengths=list(out_lengths),
-        cu_seqlens=torch.tensor(cu, dtype=torch.int32).to(device, non_blocking=True),
+        cu_seqlens=torch.from_numpy(cu.astype(np.int32)).to(device, non_blocking=True),
         pack_src_idx=idx.to(device, non_blocking=True),
         fill_frames=fill.to(device, non_blocking=True),
     )
