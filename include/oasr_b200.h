@@ -849,13 +849,15 @@ OASR_API int64_t oasr_b200_fastconformer_workspace_bytes(const oasr_b200_fastcon
                                                          int64_t table_rows, int64_t bias_numel);
 /* The layer loop of NemotronEncoder.forward (oasr/models/nemotron/encoder.py:542-583, layer :217-267, attention
  * :82-149 / 300-359, conv module :150-214) on the valid frames of all utterances back to back, as one fixed sequence
- * of this library's kernels on `stream`.  res (total, hidden) fp32: the post-subsampling states on entry, overwritten
- * (it is the residual stream); out (total, hidden) fp32: the stack's output.  rel_table (table_rows, hidden) 16-bit:
+ * of this library's kernels on `stream`.  rows (total, hidden), 16-bit or (rows_f32 != 0) fp32: the post-subsampling
+ * states of the valid frames (they start the fp32 residual stream, which lives in the workspace; rows is not written); out (total, hidden) fp32: the stack's output.
+ * rel_table (table_rows, hidden) 16-bit:
  * sinusoid rows for relative positions max_seg-1 .. -(max_seg-1), then zero rows up to a multiple of 8.  cu_seqlens
  * int32[num_segs+1]; bias_offsets int64[num_segs+1], segment s = heads * len_s * roundup8(len_s) elements, bias_numel
  * their sum.  workspace: oasr_b200_fastconformer_workspace_bytes() bytes, 256-byte aligned.  Nothing is allocated and
  * the host never waits for the device. */
-OASR_API int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* model, float* res, float* out,
+OASR_API int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* model, const void* rows,
+                                                   int rows_f32, float* out,
                                                    const void* rel_table, int64_t table_rows,
                                                    const int32_t* cu_seqlens, const int64_t* bias_offsets,
                                                    int64_t bias_numel, int64_t num_segs, int64_t total,

@@ -133,7 +133,7 @@ class FastConformerModel(ctypes.Structure):
         ("eps", c_double), ("mask_floor", c_double), ("layers", POINTER(FastConformerLayer))]
 
 
-_SIGNATURES["oasr_b200_fastconformer_layers_packed"] = [POINTER(FastConformerModel), P, P, P, I, P, P, I, I, I, I, P, I, P]
+_SIGNATURES["oasr_b200_fastconformer_layers_packed"] = [POINTER(FastConformerModel), P, c_int, P, P, I, P, P, I, I, I, I, P, I, P]
 _SIGNATURES["oasr_b200_conformer_encode_packed"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, I, P, P, P]
 
 _SIGNATURES["oasr_b200_conformer_encode_packed_noalloc"] = [POINTER(ConformerModel), P, P, P, I, I, I, P, P, P]

@@ -15,6 +15,7 @@ namespace ob {
 namespace {
 
 struct FcWorkspace {
+  float* res;      // (M, C)   fp32 residual stream
   uint8_t* h;      // (M, C)   16-bit normalised activation
   uint8_t* y;      // (M, C)   16-bit sub-layer output
   uint8_t* a_ffn;  // (M, F)
@@ -39,6 +40,7 @@ FcWorkspace fc_carve(const oasr_b200_fastconformer_model& m, int64_t M, int64_t 
     off += fc_align(bytes);
     return p;
   };
+  w.res = reinterpret_cast<float*>(take(M * C * 4));
   w.h = take(M * C * 2);
   w.y = take(M * C * 2);
   w.a_ffn = take(M * m.ffn * 2);
@@ -70,7 +72,7 @@ int64_t oasr_b200_fastconformer_workspace_bytes(const oasr_b200_fastconformer_mo
     if (rc_ != OASR_OK) return rc_;    \
   } while (0)
 
-int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* model, float* res, float* out,
+int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* model, const void* rows, int rows_f32, float* out,
                                           const void* rel_table, int64_t table_rows, const int32_t* cu_seqlens,
                                           const int64_t* bias_offsets, int64_t bias_numel, int64_t num_segs,
                                           int64_t total, int64_t max_seg, void* workspace, int64_t workspace_bytes,
@@ -85,7 +87,7 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
   OB_REQUIRE(m.kernel > 0 && m.ffn > 0 && m.right_context >= 0, OASR_ERR_INVALID, "fastconformer_layers_packed: bad model geometry");
   OB_REQUIRE(num_segs >= 0 && total >= 0 && max_seg >= 0 && bias_numel >= 0, OASR_ERR_INVALID, "fastconformer_layers_packed: bad shape");
   if (total == 0 || num_segs == 0) return OASR_OK;
-  OB_REQUIRE(res && out && rel_table && cu_seqlens && bias_offsets && workspace, OASR_ERR_INVALID,
+  OB_REQUIRE(rows && out && rel_table && cu_seqlens && bias_offsets && workspace, OASR_ERR_INVALID,
              "fastconformer_layers_packed: null pointer argument");
   OB_REQUIRE(table_rows >= 2 * max_seg - 1 && table_rows % 8 == 0, OASR_ERR_INVALID,
              "fastconformer_layers_packed: the position table needs >= 2*max_seg-1 rows, a multiple of 8 (got %lld for %lld frames)",
@@ -103,9 +105,16 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
   const oasr_b200_fastconformer_layer* ly = m.layers;
   const double eps = m.eps;
 
-  // h = LN_ff1(x) of the first layer
-  FC_STEP(oasr_b200_add_norm_f32(w.h, nullptr, res, nullptr, 0.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b, nullptr, nullptr, M, C,
-                                 eps, 0, dt, stream));
+  // the input rows (16-bit, or fp32 when rows_f32) start the fp32 residual stream; h = LN_ff1(x) of the first layer in
+  // the same kernel
+  float* res = w.res;
+  if (rows_f32) {
+    FC_STEP(oasr_b200_add_norm_f32(w.h, res, static_cast<const float*>(rows), nullptr, 0.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b,
+                                   nullptr, nullptr, M, C, eps, 0, dt, stream));
+  } else {
+    FC_STEP(oasr_b200_add_norm_f32(w.h, res, nullptr, rows, 1.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b, nullptr, nullptr, M, C, eps, 0,
+                                   dt, stream));
+  }
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_fastconformer_layer& l = ly[i];
     // macaron feed-forward: x += 0.5 * W2 silu(W1 h)

@@ -111,7 +111,7 @@ class FastConformerLayers:
         m.layers = ctypes.cast(arr, ctypes.POINTER(_lib.FastConformerLayer))
         self._native_layers, self._native_model = arr, m      # keep both alive
 
-    def _layers_native(self, res: torch.Tensor, g) -> torch.Tensor:
+    def _layers_native(self, rows: torch.Tensor, g) -> torch.Tensor:
         """The packed stack in ONE call into the native executor (oasr_b200_fastconformer_layers_packed): the same
         kernels in the same order as :meth:`_layers_composed`, enqueued from C++ on the current stream."""
         import ctypes
@@ -119,7 +119,8 @@ class FastConformerLayers:
         from . import _lib
         from .functional import _p, _stream
 
-        M, C = res.shape
+        M, C = rows.shape
+        res = rows
         table = self._position_table(g["T"])
         lib = _lib.load()
         need = lib.oasr_b200_fastconformer_workspace_bytes(ctypes.byref(self._native_model), M, table.size(0), g["bias_numel"])
@@ -128,7 +129,8 @@ class FastConformerLayers:
         ws = self._workspace
         off = (-ws.data_ptr()) % 256
         out = torch.empty(M, C, device=res.device, dtype=torch.float32)
-        _lib.call("oasr_b200_fastconformer_layers_packed", ctypes.byref(self._native_model), _p(res), _p(out), _p(table),
+        _lib.call("oasr_b200_fastconformer_layers_packed", ctypes.byref(self._native_model), _p(rows),
+                  1 if rows.dtype == torch.float32 else 0, _p(out), _p(table),
                   table.size(0), _p(g["cu"]), _p(g["offsets"]), g["bias_numel"], g["cu"].numel() - 1, M, g["T"],
                   ctypes.c_void_p(ws.data_ptr() + off), ws.numel() - off, _stream(res))
         return out
@@ -204,11 +206,11 @@ class FastConformerLayers:
         x = OF.layer_norm_activation(x.view(-1, self.C), *lw["conv_norm"], eps=1e-5, activation_type=_SWISH)
         return self._linear(x, *lw["pw2"])
 
-    def _layers(self, res: torch.Tensor, g) -> torch.Tensor:
-        """``res (M, C)`` fp32 rows (overwritten: the residual stream) -> ``(M, C)`` fp32 output of the stack."""
-        if self.native and self.qkind == 0 and g["packed"]:      # the native executor runs the 16-bit stack
-            return self._layers_native(res, g)
-        return self._layers_composed(res, g)
+    def _layers(self, rows: torch.Tensor, g) -> torch.Tensor:
+        """``rows (M, C)`` post-subsampling states (fp32 or the model's 16-bit type) -> ``(M, C)`` fp32 output of the stack."""
+        if self.native and self.qkind == 0 and g["packed"] and rows.dtype in (torch.float32, self.dtype):
+            return self._layers_native(rows.contiguous(), g)        # the native executor runs the 16-bit stack
+        return self._layers_composed(rows.to(torch.float32, copy=True).contiguous(), g)   # own copy: updated in place
 
     def _layers_composed(self, res: torch.Tensor, g) -> torch.Tensor:
         """The stack operator by operator from Python: padded batches, 8-bit Linear GEMMs, and the check of the native
@@ -355,7 +357,9 @@ class FastConformerLayers:
         out = torch.zeros(B * T, C, device=dev, dtype=torch.float32)
         rows, rows_dev = self.forward_rows(hidden, lengths)
         if rows is not None:
-            out.index_copy_(0, rows_dev, rows)
+            from .cache import scatter_rows
+
+            scatter_rows(out, rows_dev, rows)
         return out.view(B, T, C)
 
     def forward_rows(self, hidden: torch.Tensor, lengths: List[int]):
@@ -379,8 +383,10 @@ class FastConformerLayers:
              "cu": torch.from_numpy(cu.astype(np.int32)).to(dev, non_blocking=True),
              "offsets": torch.from_numpy(offsets).to(dev, non_blocking=True)}
         rows_dev = torch.from_numpy(rows).to(dev, non_blocking=True)
-        res = hidden.reshape(B * T, C).index_select(0, rows_dev).float()               # (total, C) fp32, own storage
-        return self._layers(res, g), rows_dev
+        from .cache import gather_rows
+
+        rows = gather_rows(hidden.reshape(B * T, C), rows_dev)                          # (total, C), the input's dtype
+        return self._layers(rows, g), rows_dev
 
 
 class FastConformerEncoder:
@@ -518,6 +524,8 @@ class FastConformerEncoder:
         lp, arg = OF.gemm_log_softmax(h3, self.ctc[0], self.ctc[1], out_dtype=torch.float32, return_argmax=True)
         if padded_output:
             full = torch.log_softmax(self.ctc[1].float(), dim=-1).expand(B * T, V).contiguous()
-            full.index_copy_(0, rows_dev, lp)
+            from .cache import scatter_rows
+
+            scatter_rows(full, rows_dev, lp)
             lp = full.view(B, T, V)
         return (lp, out_len, arg) if return_argmax else (lp, out_len)

@@ -307,6 +307,13 @@ def test_native_executor_equals_the_operator_by_operator_stack():
     assert ob.device_status() == 0
     assert torch.equal(index, index2) and torch.equal(rows_native, rows_composed)
     assert launched >= 17 * cfg.layers
+    # 16-bit post-subsampling states (what the front end hands over): the same agreement
+    hidden16 = hidden.bfloat16()
+    native16, _ = model.forward_rows(hidden16, lengths)
+    model.native = False
+    composed16, _ = model.forward_rows(hidden16, lengths)
+    model.native = True
+    assert torch.equal(native16, composed16)
     # too small a workspace: refused with a message, nothing launched
     table = model._position_table(128)
     before = _lib.launch_count()
@@ -315,8 +322,9 @@ def test_native_executor_equals_the_operator_by_operator_stack():
         res = torch.zeros(8, cfg.hidden, device="cuda")
         cu = torch.tensor([0, 8], dtype=torch.int32, device="cuda")
         offs = torch.tensor([0, cfg.heads * 8 * 8], dtype=torch.int64, device="cuda")
-        _lib.call("oasr_b200_fastconformer_layers_packed", ctypes.byref(model._native_model), ctypes.c_void_p(res.data_ptr()),
-                  ctypes.c_void_p(res.data_ptr()), ctypes.c_void_p(table.data_ptr()), table.size(0), ctypes.c_void_p(cu.data_ptr()),
+        out = torch.empty_like(res)
+        _lib.call("oasr_b200_fastconformer_layers_packed", ctypes.byref(model._native_model), ctypes.c_void_p(res.data_ptr()), 1,
+                  ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(table.data_ptr()), table.size(0), ctypes.c_void_p(cu.data_ptr()),
                   ctypes.c_void_p(offs.data_ptr()), cfg.heads * 64, 1, 8, 128, ctypes.c_void_p(ws.data_ptr() + (-ws.data_ptr()) % 256),
                   2048, None)
     assert _lib.launch_count() == before
