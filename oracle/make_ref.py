@@ -1,7 +1,7 @@
 """Recipe for ``oracle/_ref``: an importable copy of the reference's pure-Python package.
 TEST INFRASTRUCTURE ONLY.
 
-    python oracle/make_ref.py [<reference checkout>]        (default: $OASR_REFERENCE or /root/reference)
+    python oracle/make_ref.py [<reference checkout>]        (default: $OASR_REFERENCE, else DEFAULT_CHECKOUT below)
 
 The reference's implementation of this path is Python/PyTorch (``oasr/models``, ``oasr/layers``,
 ``oasr/functionals``, ``oasr/cache``); its CUDA kernels need a CUTLASS submodule that is absent, so
@@ -29,6 +29,8 @@ HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
 
 
+DEFAULT_CHECKOUT = "/root/reference"   # where the build container mounts the reference checkout
+
 def available() -> bool:
     return (DEST / "oasr" / "__init__.py").exists()
 
@@ -36,7 +38,7 @@ def available() -> bool:
 def make(reference: str | None = None) -> Path | None:
     """Copy ``<reference>/oasr`` to ``oracle/_ref/oasr``; returns the destination, or None when the
     checkout is not on this machine (then an existing copy is left as it is)."""
-    src = Path(reference or os.environ.get("OASR_REFERENCE") or "/root/reference") / "oasr"
+    src = Path(reference or os.environ.get("OASR_REFERENCE") or DEFAULT_CHECKOUT) / "oasr"
     if not (src / "__init__.py").exists():
         return None
     dst = DEST / "oasr"
