@@ -87,6 +87,13 @@ struct Smem {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
+// The epilogue passes are bound by their instruction count: the element-wise arithmetic runs two columns per
+// instruction (fp32x2 add / mul / fma, each component rounded exactly as the scalar operation).
+__device__ __forceinline__ float2 f2at(const float* f, int i) { return make_float2(f[2 * i], f[2 * i + 1]); }
+__device__ __forceinline__ float2 pairu(const uint32_t* r, int i) {
+  return make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+}
+__device__ __forceinline__ float2 splat(float x) { return make_float2(x, x); }
 __device__ __forceinline__ float u2f(uint32_t u) { return __uint_as_float(u); }
 __device__ __forceinline__ uint32_t f2u(float f) { return __float_as_uint(f); }
 
@@ -372,7 +379,8 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (ew == 0 && lane == 0) stamp(p, 4);
 
       // ---------------- pass 1: s = res + alpha * (acc + bias), statistics about the slice's first value ----------------
-      float pivot = 0.f, sum = 0.f, sq = 0.f;
+      float pivot = 0.f;
+      float2 sum2 = make_float2(0.f, 0.f), sq2v = make_float2(0.f, 0.f);
 #pragma unroll 1
       for (int i = 0; i < kLocal; ++i) {
         const int c = c_lo + i;
@@ -396,10 +404,16 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ptx::tmem_ld_wait();
         if (bias) {
 #pragma unroll
-          for (int k = 0; k < 16; ++k) s[k] = fmaf(p.alpha, u2f(r[k]) + bb[k], s[k]);
+          for (int k = 0; k < 8; ++k) {
+            const float2 t = __ffma2_rn(splat(p.alpha), __fadd2_rn(pairu(r, k), f2at(bb, k)), f2at(s, k));
+            s[2 * k] = t.x; s[2 * k + 1] = t.y;
+          }
         } else {
 #pragma unroll
-          for (int k = 0; k < 16; ++k) s[k] = fmaf(p.alpha, u2f(r[k]), s[k]);
+          for (int k = 0; k < 8; ++k) {
+            const float2 t = __ffma2_rn(splat(p.alpha), pairu(r, k), f2at(s, k));
+            s[2 * k] = t.x; s[2 * k + 1] = t.y;
+          }
         }
         if (store_res && p.mode != 2) {
           float* dst = const_cast<float*>(res_ptr(p.res_out, c));
@@ -413,17 +427,20 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           load_params16(static_cast<const float*>(p.w_a) + c * kChunk, sc);
           load_params16(static_cast<const float*>(p.b_a) + c * kChunk, sh);
 #pragma unroll
-          for (int k = 0; k < 16; ++k) o[k] = fmaf(s[k], sc[k], sh[k]);
+          for (int k = 0; k < 8; ++k) {
+            const float2 t = __ffma2_rn(f2at(s, k), f2at(sc, k), f2at(sh, k));
+            o[2 * k] = t.x; o[2 * k + 1] = t.y;
+          }
           if ((c & 1) == 0) h_buffer_free();
           half_row_store(o, c & 1);
           if (c & 1) h_piece_out((c >> 1) * 32, row0, warp_live);
         } else {
           if (i == 0) pivot = s[0];
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float d = s[k] - pivot;
-            sum += d;
-            sq = fmaf(d, d, sq);
+          for (int k = 0; k < 8; ++k) {     // even and odd columns keep separate running sums, added at the end
+            const float2 d = __fadd2_rn(f2at(s, k), splat(-pivot));
+            sum2 = __fadd2_rn(sum2, d);
+            sq2v = __ffma2_rn(d, d, sq2v);
           }
 #pragma unroll
           for (int k = 0; k < 16; ++k) r[k] = f2u(s[k]);
@@ -435,12 +452,13 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (p.mode != 1) {
         ptx::tmem_st_wait();                       // pass 1's writes of s are in TMEM before anything reads them back
         float mean, rstd;
-        if (!combine_stats(0, pivot, sum, sq, mean, rstd)) { ok = false; break; }
+        if (!combine_stats(0, pivot, sum2.x + sum2.y, sq2v.x + sq2v.y, mean, rstd)) { ok = false; break; }
         const T* g1 = static_cast<const T*>(p.w_a);
         const T* b1 = static_cast<const T*>(p.b_a);
         if (p.mode == 2) {
           // ---------------- pass 2 (mode 2): res_out = LN_a(s), kept in TMEM, statistics of it ----------------
-          float pivot2 = 0.f, sum2 = 0.f, sq2 = 0.f;
+          float pivot2 = 0.f;
+          float2 sumb = make_float2(0.f, 0.f), sqb = make_float2(0.f, 0.f);
 #pragma unroll 1
           for (int i = 0; i < kLocal; ++i) {
             const int c = c_lo + i;
@@ -451,13 +469,16 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             load_params16(b1 + c * kChunk, bb);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 16; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
+            for (int k = 0; k < 8; ++k) {
+              const float2 t = __ffma2_rn(__fmul2_rn(__fadd2_rn(pairu(r, k), splat(-mean)), splat(rstd)), f2at(gg, k), f2at(bb, k));
+              v[2 * k] = t.x; v[2 * k + 1] = t.y;
+            }
             if (i == 0) pivot2 = v[0];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const float d = v[k] - pivot2;
-              sum2 += d;
-              sq2 = fmaf(d, d, sq2);
+            for (int k = 0; k < 8; ++k) {
+              const float2 d = __fadd2_rn(f2at(v, k), splat(-pivot2));
+              sumb = __fadd2_rn(sumb, d);
+              sqb = __ffma2_rn(d, d, sqb);
             }
 #pragma unroll
             for (int k = 0; k < 16; ++k) r[k] = f2u(v[k]);
@@ -471,7 +492,7 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           if (ew == 0 && lane == 0) stamp(p, 6);
           ptx::tmem_st_wait();
-          if (!combine_stats(1, pivot2, sum2, sq2, mean, rstd)) { ok = false; break; }
+          if (!combine_stats(1, pivot2, sumb.x + sumb.y, sqb.x + sqb.y, mean, rstd)) { ok = false; break; }
           g1 = static_cast<const T*>(p.w_b);
           b1 = static_cast<const T*>(p.b_b);
         }
@@ -491,7 +512,10 @@ gemm_addnorm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             load_params16(b1 + c * kChunk, bb);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 16; ++k) v[k] = fmaf((u2f(r[k]) - mean) * rstd, gg[k], bb[k]);
+            for (int k = 0; k < 8; ++k) {
+              const float2 t = __ffma2_rn(__fmul2_rn(__fadd2_rn(pairu(r, k), splat(-mean)), splat(rstd)), f2at(gg, k), f2at(bb, k));
+              v[2 * k] = t.x; v[2 * k + 1] = t.y;
+            }
             if (part == 1) {
 #pragma unroll
               for (int k = 0; k < 16; ++k) v[k] = v[k] - Elem<T>::to_f(Elem<T>::from_f(v[k]));
