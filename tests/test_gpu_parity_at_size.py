@@ -155,3 +155,55 @@ def test_fastconformer_real_width_with_ctc_head_matches_the_oracle():
     assert agree_clear >= 0.99
     assert torch.equal(arg.cpu().long(), lp[valid].argmax(-1))
     assert lp[valid].logsumexp(-1).abs().max().item() < 1e-3
+
+
+def test_length_sorted_sweep_through_packs_matches_the_fp32_oracle():
+    """The config-5 style path (utterances with log-normal lengths, sorted, packed by the reference's rule, packs dealt
+    to two ranks, greedy search pipelined over a rank's packs) at the headline model: every utterance comes back
+    exactly once and in place, its tokens are the collapse of its own frames' argmax, and its log-probs agree with
+    the fp32 oracle run on the utterance alone (packing restricts attention and the conv to the segment, so an
+    utterance's result does not depend on its pack mates)."""
+    from oasr_b200 import sharding
+
+    cfg = bench.model_config(12)
+    P = init_params(cfg, 1234)
+    model = ConformerCTC(cfg, P, device="cuda", dtype=torch.bfloat16)
+    rng = np.random.default_rng(11)
+    lengths = [int(round(100 * min(max(x, 1.0), 30.0))) for x in rng.lognormal(np.log(6.0), 0.6, size=40)]
+    feats = [torch.randn(n, 80, generator=torch.Generator().manual_seed(100 + i)) for i, n in enumerate(lengths)]
+    packs = sharding.plan_packs(lengths, 2048, 4)
+    assert len(packs) >= 4 and sorted(i for p in packs for i in p) == list(range(len(lengths)))
+    plan = sharding.assign_packs(lengths, packs, 2)
+    results = {}
+    for rank in range(2):                              # both ranks' shares, one after the other on this GPU
+        batches = []
+        for j in plan[rank]:
+            idx = packs[j]
+            T = max(lengths[i] for i in idx)
+            x = torch.zeros(len(idx), T, 80)
+            for r, i in enumerate(idx):
+                x[r, :lengths[i]] = feats[i]
+            batches.append((idx, x.pin_memory(), [lengths[i] for i in idx]))
+        for (idx, _, _), hyps in zip(batches, model.greedy_search_batches((x, ls) for _, x, ls in batches)):
+            assert len(hyps) == len(idx)
+            for i, h in zip(idx, hyps):
+                assert i not in results
+                results[i] = h
+    assert ob.device_status() == 0
+    assert sorted(results) == list(range(len(lengths)))
+    # five utterances spread over the length range, each alone through the oracle
+    order = sorted(range(len(lengths)), key=lambda i: lengths[i])
+    picked = [order[0], order[len(order) // 4], order[len(order) // 2], order[3 * len(order) // 4], order[-1]]
+    PO = OC.init_params(OC.CONFIG2, 1234)
+    worst_mean = 0.0
+    for i in picked:
+        with torch.no_grad():
+            want, want_len = OC.forward_offline_packed(PO, OC.CONFIG2, feats[i][None], torch.tensor([lengths[i]]))
+        n = int(want_len[0])
+        lp, _, _ = model.forward_offline_packed(feats[i][None].cuda(), [lengths[i]], padded_output=False)
+        mx, mean, _, clear = _stats(lp.cpu()[:n], want[0, :n], cfg.vocab, f"sweep utterance {i}, {lengths[i]} frames")
+        worst_mean = max(worst_mean, mean)
+        assert mx <= MAX_ABS and clear >= ARGMAX_AGREE
+        ids = lp[:n, :cfg.vocab].argmax(-1).cpu().numpy()
+        assert results[i] == ConformerCTC._collapse(ids, [n])[0]       # the pack's tokens = this utterance's own tokens
+    assert worst_mean <= 2.0e-3
