@@ -3,25 +3,32 @@
 // (RelPositionMultiHeadedAttention._forward_packed, oasr/layers/attention/attention.py:323-386).
 //
 // Same tcgen05 / TMEM / TMA pipeline as fmha.cu, sized so that TWO CTAs share an SM: at head_dim 64 a tile's
-// tensor work (0.8k clocks) is a fraction of its softmax (3k) and of the latencies around it (TMEM loads,
-// MUFU, barrier hand-offs, 3k clocks before a CTA's first scores arrive), so one CTA per SM leaves every unit
-// under 20 % busy; a second resident CTA fills those gaps.  To fit twice:
+// tensor work (0.4k clocks for 128 queries x 64 keys) is a fraction of its softmax (2k) and of the latencies around it
+// (TMEM loads, MUFU, barrier hand-offs), so one CTA per SM leaves every unit under 20 % busy; a second resident CTA
+// fills those gaps.  To fit twice:
 //   keys are walked in tiles of 64 (K | pos 16 KB, V 8 KB per stage, two stages),
 //   P has a single 16 KB buffer (a softmax thread waits for P.V of tile j-1 before it rewrites P for tile j; by
 //   then that short MMA has long finished, because the exponentials of tile j were computed in between),
 //   TMEM holds S[2] (2 x 64 columns) and ONE O (64 columns) that every P.V accumulates into = 192 of 256 columns,
 // i.e. 96 KB of shared memory and half of TMEM per CTA.
+// PERSISTENT: the grid is two CTAs per SM and every CTA walks work items (segment, head, 128-row query tile) number
+// blockIdx.x, + gridDim.x, ... of a list that holds the longest segments first (plan_kernel below, built on the device
+// once per batch; without a list the items are enumerated in (segment, head, tile) order).  Stages and barriers are
+// indexed by the CTA's running key-tile count, so the pipeline carries on from one item into the next: a fresh CTA
+// needs 3.5-5k clocks before its first scores arrive, which one CTA per item paid 1,300 times per launch of the
+// headline batch (72 -> 55 us per launch).
 // 192 threads: warp 4 lane 0 issues the MMAs, warp 5 lane 0 the TMA loads (a stage's refill waits for the MMAs that
-// read it; in one thread with the MMA issue those waits made that thread's per-tile path as long as a tile's softmax:
-// 2.7k -> 2.3k clocks per tile once split), warps 0-3 own one query row per thread.
+// read it; in one thread with the MMA issue those waits made that thread's per-tile path as long as a tile's softmax),
+// warps 0-3 own one query row per thread.
 // Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
 // once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
 // are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
 // common case costs nothing -- then exp2 (scale / subtract and the row sum as packed fp32x2 operations on tiles
-// without masked keys: 1.3k -> 0.8k clocks for the 64 exponentials of a thread; optionally a share of them as a degree-3 polynomial on the FMA pipe,
-// off by default: measured slower), bf16/fp16 P into swizzled shared memory.  O leaves TMEM once, at the end,
-// scaled by 1 / sum.  K | pos of tile j+2 is requested as soon as Q.K^T of tile j has finished, V of tile j+1 when
-// P.V of tile j-1 has: the two have separate stage barriers.
+// without masked keys: 1.3k -> 0.8k clocks for the 64 exponentials of a thread; optionally a share of them as a
+// degree-3 polynomial on the FMA pipe, off by default: measured slower), bf16/fp16 P into swizzled shared memory.
+// O leaves TMEM once per item, scaled by 1 / sum; the next item's first P.V waits until every row has read it.
+// K | pos of tile j+2 is requested as soon as Q.K^T of tile j has finished, V of tile j+2 when P.V of tile j has: the
+// two have separate stage barriers.
 // Only the length mask exists here (keys >= segment length); bias, causal masks, key starts, paged K/V and
 // head_dim 128 stay on the general kernel in fmha.cu.  Every wait is bounded.
 #include <cuda.h>
@@ -34,10 +41,10 @@
 #include "tma_host.cuh"
 
 namespace ob {
-int g_fmha_relpos_path = 1;
-int g_fmha_poly = 0;         // exponentials per four on the FMA pipe in the packed relative-position kernel ("fmha_poly": 0, 1, 2);
-                            // measured on B200 (config-2 batch): 66.0 / 66.9 / 68.9 us per launch for 0 / 1 / 2 -- the kernel is
-                            // bound by instruction issue, not by the MUFU unit, so the extra FMA work does not pay  // 1 = this kernel for the packed relative-position form; 0 = the general kernel ("fmha_relpos_path")
+int g_fmha_relpos_path = 1;   // 1 = this kernel for the packed relative-position form; 0 = the general kernel ("fmha_relpos_path")
+int g_fmha_poly = 0;          // exponentials per four on the FMA pipe in this kernel ("fmha_poly": 0, 1, 2); measured on B200
+                              // (config-2 batch): 66.0 / 66.9 / 68.9 us per launch for 0 / 1 / 2 -- the softmax is bound by
+                              // instruction issue, not by the MUFU unit, so the extra FMA work does not pay
 
 namespace fmha_relpos {
 
