@@ -120,6 +120,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
   ptx::grid_dep_wait();
   if (threadIdx.x == 0) stamp(p, 0);
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[64 + blockIdx.x * 4] = static_cast<unsigned long long>(clock64());
   // Persistent CTA: walks work items blockIdx.x, + gridDim.x, ... of the list (or of the natural enumeration).  All
   // roles decode the same items in the same order; an item whose query tile lies past its segment is skipped by all.
   const int n_items = p.items ? *p.n_items : p.natural_items;
@@ -268,15 +269,30 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         issue_qk(b);
         return true;
       };
+      // next item of this CTA at or after `it` whose query tile exists (n_items if none)
+      auto next_item = [&](int it, Item& w) {
+        while (it < n_items && !decode(it, w)) it += gridDim.x;
+        return it;
+      };
       int g = 0, done = 0;
-      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
-        Item w;
-        if (!decode(it, w)) continue;
-        ok = ptx::mbar_wait(q_full, static_cast<uint32_t>(done) & 1u, abort_flag) && scores(g);
-        // Tile j: the scores of tile j+1 are issued first, then P.V of tile j, which waits for the softmax.
+      Item w, w2;
+      int it = next_item(blockIdx.x, w);
+      bool first_issued = false;               // the item's first scores were already issued under the previous item
+      while (ok && it < n_items) {
+        if (!first_issued) ok = ptx::mbar_wait(q_full, static_cast<uint32_t>(done) & 1u, abort_flag) && scores(g);
+        first_issued = false;
+        const int it2 = next_item(it + gridDim.x, w2);
+        // Tile j: the scores of tile j+1 are issued first -- at the item's last tile those of the NEXT item's first
+        // tile (its Q was loaded when this item's last Q.K^T finished), so that they are ready when the softmax
+        // threads come out of this item's output -- then P.V of tile j, which waits for the softmax.
         for (int j = 0; ok && j < w.nkv; ++j) {
           const int gg = g + j, b = gg & 1;
-          if (j + 1 < w.nkv && !scores(gg + 1)) { ok = false; break; }
+          if (j + 1 < w.nkv) {
+            if (!scores(gg + 1)) { ok = false; break; }
+          } else if (it2 < n_items) {
+            if (!ptx::mbar_wait(q_full, static_cast<uint32_t>(done + 1) & 1u, abort_flag) || !scores(gg + 1)) { ok = false; break; }
+            first_issued = true;
+          }
           ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(gg) & 1u, abort_flag) &&
                ptx::mbar_wait(&v_full[b], (gg >> 1) & 1u, abort_flag);
           if (ok && j == 0 && done > 0) ok = ptx::mbar_wait(o_free, static_cast<uint32_t>(done - 1) & 1u, abort_flag);
@@ -286,6 +302,8 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         g += w.nkv;
         ++done;
+        it = it2;
+        w = w2;
       }
       if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
     }
@@ -318,14 +336,13 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s_free[b]);          // the scores live in registers now: S[b] may take tile j+2
       const bool full = key0 + BKV <= kv_len;   // tiles inside the valid keys need no mask
-      float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};   // four independent chains
-      if (full) {
+      if (!full) {   // the segment's last tile: keys past its end become -inf scores, i.e. P = exp2(-inf) = 0 below
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], key0 + i < kv_len ? __uint_as_float(v[i]) : kNegInf);
+        for (int i = 0; i < 64; ++i) v[i] = key0 + i < kv_len ? v[i] : 0xff800000u;
       }
+      float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};   // four independent chains
+#pragma unroll
+      for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
       float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tile_max *= p.scale_log2;   // the scale is positive
       if (j == 3 && r == 0) stamp(p, 52);
@@ -342,9 +359,9 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       // exponentiate, sum, round
       uint32_t packed[32];
       float row_sum = 0.f;
-      if (kPoly == 0 && full) {
-        // the common tile (all keys valid, every exponential on the MUFU unit): scale / subtract and the row sum as
-        // packed fp32x2 operations, no per-key selects
+      if (kPoly == 0) {
+        // every exponential on the MUFU unit: scale / subtract and the row sum as packed fp32x2 operations (masked
+        // keys carry -inf and come out as exactly 0)
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
         const float2 nm2 = make_float2(-m_run, -m_run);
         float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
@@ -434,6 +451,13 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     g += nkv;
     }   // items
+    if (p.trace != nullptr && r == 0) {   // diagnostics: this CTA's span and work
+      p.trace[64 + blockIdx.x * 4 + 1] = static_cast<unsigned long long>(clock64());
+      p.trace[64 + blockIdx.x * 4 + 2] = static_cast<unsigned long long>(g);
+      unsigned smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      p.trace[64 + blockIdx.x * 4 + 3] = smid;
+    }
     if (!ok && lane == 0 && p.status) atomicOr(p.status, kStatusFmhaSoftmax);
   }
 
