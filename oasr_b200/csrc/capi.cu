@@ -60,9 +60,10 @@ namespace conv2_pair { extern int g_enabled; }
 namespace gemm { extern int g_force_bn; extern int g_use_pairs; extern int g_lsm_path; }
 extern int g_dw_path;
 extern int g_fmha_relpos_path;
-extern int g_fmha_poly;
 unsigned long long* g_trace_buffer = nullptr;   // diagnostics: device buffer that instrumented kernels stamp their phases into
-int g_pdl = 0;  // measured neutral on both workloads (offline 7.32 vs 7.36 ms, streaming 3.79 vs 3.71 ms per step): off by default
+int g_pdl = 1;  // programmatic stream serialisation for the kernels launched through launch_pdl (a kernel's set-up runs while the
+                // previous one drains): offline step 6.29 against 6.38 ms with every GEMM-shaped kernel on it; neutral on the
+                // graph-replayed streaming step (2.91 ms) and on the FastConformer step (51.5 ms)
 extern int g_fmha_chunk_path;
 extern int g_fused_addnorm;
 namespace conv1_mma { extern int g_enabled; }
@@ -97,11 +98,6 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   if (name && std::strcmp(name, "pdl") == 0) {
     ob::g_pdl = value != 0;
-    return OASR_OK;
-  }
-  if (name && std::strcmp(name, "fmha_poly") == 0) {
-    if (value < 0 || value > 2) return ob::set_error(OASR_ERR_INVALID, "fmha_poly must be 0, 1 or 2 (got %d)", value);
-    ob::g_fmha_poly = value;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "conv2_pairs") == 0) {

@@ -208,7 +208,7 @@ int sm_count();  // cached multiprocessor count of the current device (capi.cu)
 
 // Launch with programmatic stream serialisation (the kernel must call grid_dep_wait() before it touches
 // global memory): its blocks may be scheduled while the previous kernel of the stream drains.  The "pdl"
-// tunable switches the attribute on (default 0: plain stream order).
+// tunable switches the attribute (default 1; 0 = plain stream order).
 extern int g_pdl;
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {

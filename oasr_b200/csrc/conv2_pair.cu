@@ -311,7 +311,7 @@ int launch(const CUtensorMap& ta, const void* w2, int64_t K, const Params& p, in
   const int64_t pairs = (max_items + 1) / 2;
   if (pairs < clusters) clusters = pairs;
   if (clusters < 1) clusters = 1;
-  kern<<<static_cast<unsigned>(2 * clusters), kThreads, S::kDynamic, s>>>(ta, tb, p);
+  launch_pdl(kern, dim3(static_cast<unsigned>(2 * clusters)), dim3(kThreads), S::kDynamic, s, ta, tb, p);
   return check_launch("subsample_conv2 (CTA pairs) launch");
 }
 

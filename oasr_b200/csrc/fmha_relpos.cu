@@ -11,24 +11,26 @@
 //   then that short MMA has long finished, because the exponentials of tile j were computed in between),
 //   TMEM holds S[2] (2 x 64 columns) and ONE O (64 columns) that every P.V accumulates into = 192 of 256 columns,
 // i.e. 96 KB of shared memory and half of TMEM per CTA.
-// PERSISTENT: the grid is two CTAs per SM and every CTA walks work items (segment, head, 128-row query tile) number
-// blockIdx.x, + gridDim.x, ... of a list that holds the longest segments first (plan_kernel below, built on the device
-// once per batch; without a list the items are enumerated in (segment, head, tile) order).  Stages and barriers are
-// indexed by the CTA's running key-tile count, so the pipeline carries on from one item into the next: a fresh CTA
-// needs 3.5-5k clocks before its first scores arrive, which one CTA per item paid 1,300 times per launch of the
-// headline batch (72 -> 55 us per launch).
-// 192 threads: warp 4 lane 0 issues the MMAs, warp 5 lane 0 the TMA loads (a stage's refill waits for the MMAs that
-// read it; in one thread with the MMA issue those waits made that thread's per-tile path as long as a tile's softmax),
-// warps 0-3 own one query row per thread.
+// PERSISTENT: the grid is two CTAs per SM and every CTA walks work items (segment, head, 128-row query tile) of a
+// list that holds the longest segments first (plan_kernel below, built on the device once per batch; without a list the
+// items are enumerated in (segment, head, tile) order), dealt in rounds of gridDim.x items, forwards and backwards in
+// turn.  Stages and barriers are indexed by the CTA's running key-tile count, so the pipeline carries on from one item
+// into the next: a fresh CTA needs 3.5-5k clocks before its first scores arrive, which one CTA per item paid 1,300
+// times per launch of the headline batch (72 -> 55 us per launch).
+// 192 threads: warp 4 lane 0 issues the MMAs, warp 5 lane 0 the TMA loads, warps 0-3 own one query row per thread.
+// The two single-thread roles are event loops over two cursors each (K | pos and V refills; scores and P.V): whichever
+// operation has its inputs ready is issued, so scores run up to two tiles ahead of P.V, into the next item too, and
+// an item's output is written by the softmax threads inside the next item's first tile, while that item's last P.V
+// drains (55 -> 50 us); with the alternating deal (20-28 -> 22-26 key tiles per CTA) 45 us per launch.
 // Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
 // once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
 // are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
 // common case costs nothing -- then exp2 (scale / subtract and the row sum as packed fp32x2 operations on tiles
-// without masked keys: 1.3k -> 0.8k clocks for the 64 exponentials of a thread; optionally a share of them as a
-// degree-3 polynomial on the FMA pipe, off by default: measured slower), bf16/fp16 P into swizzled shared memory.
+// 1.3k -> 0.8k clocks for the 64 exponentials of a thread; a share of them as a cubic on the FMA pipe measured
+// slower: 45.4 / 56.2 / 60.3 us per launch with none / one / two of every four), bf16/fp16 P into swizzled shared memory.
 // O leaves TMEM once per item, scaled by 1 / sum; the next item's first P.V waits until every row has read it.
 // K | pos of tile j+2 is requested as soon as Q.K^T of tile j has finished, V of tile j+2 when P.V of tile j has: the
-// two have separate stage barriers.
+// two have separate stage barriers and separate cursors.
 // Only the length mask exists here (keys >= segment length); bias, causal masks, key starts, paged K/V and
 // head_dim 128 stay on the general kernel in fmha.cu.  Every wait is bounded.
 #include <cuda.h>
@@ -42,9 +44,6 @@
 
 namespace ob {
 int g_fmha_relpos_path = 1;   // 1 = this kernel for the packed relative-position form; 0 = the general kernel ("fmha_relpos_path")
-int g_fmha_poly = 0;          // exponentials per four on the FMA pipe in this kernel ("fmha_poly": 0, 1, 2); measured on B200
-                              // (config-2 batch): 66.0 / 66.9 / 68.9 us per launch for 0 / 1 / 2 -- the softmax is bound by
-                              // instruction issue, not by the MUFU unit, so the extra FMA work does not pay
 
 namespace fmha_relpos {
 
@@ -79,21 +78,15 @@ __device__ __forceinline__ void stamp(const Params& p, int slot) {
     p.trace[slot] = static_cast<unsigned long long>(clock64());
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-// 2^x on the FMA / ALU pipes: round x to the nearest integer n with the 1.5 * 2^23 trick, 2^(x - n) by a cubic on
-// [-0.5, 0.5] (relative error 6e-4, below the rounding of a 16-bit P), n added to the exponent field.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.f);
-  const float magic = 12582912.f;                      // 0x4B400000
-  const float xr = x + magic;
-  const int n = __float_as_int(xr) - 0x4B400000;
-  const float f = x - (xr - magic);
-  const float pl = fmaf(fmaf(fmaf(0.0555041f, f, 0.2402265f), f, 0.6931472f), f, 1.0f);
-  return __int_as_float(__float_as_int(pl) + (n << 23));
 }
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -106,8 +99,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-// kPoly: how many of every four exponentials run as a polynomial on the FMA pipe instead of the MUFU unit (0, 1 or 2)
-template <typename T, int kPoly>
+template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
 fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q2,
                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_pos,
@@ -121,9 +113,16 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   ptx::grid_dep_wait();
   if (threadIdx.x == 0) stamp(p, 0);
   if (p.trace != nullptr && threadIdx.x == 0) p.trace[64 + blockIdx.x * 4] = static_cast<unsigned long long>(clock64());
-  // Persistent CTA: walks work items blockIdx.x, + gridDim.x, ... of the list (or of the natural enumeration).  All
-  // roles decode the same items in the same order; an item whose query tile lies past its segment is skipped by all.
+  // Persistent CTA: the items of the list (or of the natural enumeration) are dealt to the CTAs in rounds of gridDim.x,
+  // forwards in even rounds and backwards in odd ones: the list holds the longest items first, so plain round-robin
+  // would hand CTA 0 the longest item of every round (20 to 28 key tiles per CTA on the headline batch).  All roles
+  // decode the same items in the same order; an item whose query tile lies past its segment is skipped by all.
   const int n_items = p.items ? *p.n_items : p.natural_items;
+  auto item_of_round = [&](int round) -> int {
+    const int G = static_cast<int>(gridDim.x), bid = static_cast<int>(blockIdx.x);
+    const long long it = static_cast<long long>(round) * G + ((round & 1) ? G - 1 - bid : bid);
+    return it < n_items ? static_cast<int>(it) : n_items;
+  };
   const int64_t out_ld = static_cast<int64_t>(p.H) * D;
   struct Item { int h, q0, row0, kv_len, nkv; };
   auto decode = [&](int it, Item& w) -> bool {
@@ -194,38 +193,78 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   // Every barrier that completes once per key tile is indexed by the CTA's running tile count g (stage g & 1, phase
   // g >> 1), which carries on from one item to the next, so the pipeline never drains between items.
+  // The TMA producer and the MMA issuer each follow TWO cursors over the CTA's tile sequence and issue whichever of
+  // their two next operations has its inputs ready (non-blocking barrier tests in a bounded polling loop):
+  // a refill of K | pos never queues behind a V refill that waits for a later P.V, and P.V of a tile never queues
+  // behind scores whose keys are still in flight.
+  struct Cursor { int round, it, j, g, ord; Item w; };   // dealing round, item, key tile within it, running tile count, item ordinal of this CTA
+  auto seek = [&](Cursor& c) {   // from c.round on: the CTA's next item whose query tile exists (c.it = n_items if none)
+    Item w2;
+    for (;; ++c.round) {
+      c.it = item_of_round(c.round);
+      if (c.it >= n_items) { c.it = n_items; return; }
+      if (decode(c.it, w2)) { c.w = w2; return; }
+    }
+  };
+  auto start = [&](Cursor& c) { c.j = 0; c.g = 0; c.ord = 0; c.round = 0; seek(c); };
+  auto advance = [&](Cursor& c) {
+    ++c.g;
+    if (++c.j == c.w.nkv) {
+      c.j = 0;
+      ++c.ord;
+      ++c.round;
+      seek(c);
+    }
+  };
+  constexpr uint32_t kIdleLimit = 1u << 24;   // polls without progress before the role gives up (a sleep between polls
+                                              // measured slower: 45.4 / 46.0 / 46.3 / 46.7 us per launch for 0 / 20 / 40 / 100 ns)
   if (warp == 5) {
     // =================== TMA producer (one thread) ===================
-    // Its own warp: the refill of a stage waits for the MMAs that read it, and those waits must not sit in the MMA
-    // issuer's instruction stream (with both roles in one thread that thread's per-tile path, about 2k clocks of
-    // serial waits and issues, was as long as the softmax of a tile and set the pace).
     if (lane == 0) {
       bool ok = true;
-      int g = 0, done = 0;
-      for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
-        Item w;
-        if (!decode(it, w)) continue;
-        if (done > 0) {   // Q is single-buffered: the previous item's last Q.K^T (tile g-1) has finished
-          if (!ptx::mbar_wait(&k_empty[(g - 1) & 1], ((g - 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+      Cursor ck, cv;
+      start(ck);
+      start(cv);
+      uint32_t idle = 0;
+      while (ok && cv.it < n_items) {
+        bool progress = false;
+        if (ck.it < n_items) {
+          const int gg = ck.g, b = gg & 1;
+          // the stage's last user was Q.K^T of tile gg - 2; Q is single-buffered: a new item's Q waits for the
+          // previous item's last Q.K^T (tile gg - 1)
+          bool ready = gg < 2 || ptx::mbar_test(&k_empty[b], ((gg - 2) >> 1) & 1u);
+          if (ready && ck.j == 0 && ck.ord > 0) ready = ptx::mbar_test(&k_empty[(gg - 1) & 1], ((gg - 1) >> 1) & 1u);
+          if (ready) {
+            const Item& w = ck.w;
+            if (ck.j == 0) {
+              ptx::mbar_expect_tx(q_full, kQBytes);
+              ptx::tma_load_4d(sQ, &map_q, 0, w.row0 + w.q0, w.h, 0, q_full);
+              ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, w.row0 + w.q0, w.h, 0, q_full);
+            }
+            const int key0 = ck.j * BKV;
+            ptx::mbar_expect_tx(&k_full[b], kKBytes);
+            uint8_t* dk = sK + b * kKBytes;
+            ptx::tma_load_4d(dk, &map_k, 0, w.row0 + key0, w.h, 0, &k_full[b]);
+            ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, w.h, 0, &k_full[b]);
+            advance(ck);
+            progress = true;
+          }
         }
-        ptx::mbar_expect_tx(q_full, kQBytes);
-        ptx::tma_load_4d(sQ, &map_q, 0, w.row0 + w.q0, w.h, 0, q_full);
-        ptx::tma_load_4d(sQ + 128 * 128, &map_q2, 0, w.row0 + w.q0, w.h, 0, q_full);
-        for (int t = 0; ok && t < w.nkv; ++t) {
-          const int gg = g + t, b = gg & 1;
-          const int key0 = t * BKV;
-          const uint32_t prev = ((gg - 2) >> 1) & 1u;         // phase of tile gg - 2, the stage's last user
-          if (gg >= 2 && !ptx::mbar_wait(&k_empty[b], prev, abort_flag)) { ok = false; break; }   // its Q.K^T finished
-          ptx::mbar_expect_tx(&k_full[b], kKBytes);
-          uint8_t* dk = sK + b * kKBytes;
-          ptx::tma_load_4d(dk, &map_k, 0, w.row0 + key0, w.h, 0, &k_full[b]);
-          ptx::tma_load_4d(dk + BKV * 128, &map_pos, 0, key0, w.h, 0, &k_full[b]);
-          if (gg >= 2 && !ptx::mbar_wait(&v_empty[b], prev, abort_flag)) { ok = false; break; }   // its P.V finished
-          ptx::mbar_expect_tx(&v_full[b], kVBytes);
-          ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, w.row0 + key0, w.h, 0, &v_full[b]);
+        {
+          const int gg = cv.g, b = gg & 1;
+          if (gg < 2 || ptx::mbar_test(&v_empty[b], ((gg - 2) >> 1) & 1u)) {   // P.V of tile gg - 2 finished
+            ptx::mbar_expect_tx(&v_full[b], kVBytes);
+            ptx::tma_load_4d(sV + b * kVBytes, &map_v, 0, cv.w.row0 + cv.j * BKV, cv.w.h, 0, &v_full[b]);
+            advance(cv);
+            progress = true;
+          }
         }
-        g += w.nkv;
-        ++done;
+        if (progress) {
+          idle = 0;
+        } else {
+          if (++idle >= kIdleLimit) { *abort_flag = 1u; ok = false; }
+          else if ((idle & 63u) == 63u && *abort_flag) ok = false;
+        }
       }
       if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
     }
@@ -260,50 +299,43 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ptx::umma_commit(po_done);
         ptx::umma_commit(&v_empty[b]);
       };
-      // scores of tile gg: its K | pos stage has landed and S[gg & 1] has been read by the softmax of tile gg - 2
-      auto scores = [&](int gg) -> bool {
-        const int b = gg & 1;
-        const uint32_t ph = (gg >> 1) & 1u;
-        if (!ptx::mbar_wait(&k_full[b], ph, abort_flag) || !ptx::mbar_wait(&s_free[b], ph ^ 1u, abort_flag)) return false;
-        ptx::tc_fence_after_sync();
-        issue_qk(b);
-        return true;
-      };
-      // next item of this CTA at or after `it` whose query tile exists (n_items if none)
-      auto next_item = [&](int it, Item& w) {
-        while (it < n_items && !decode(it, w)) it += gridDim.x;
-        return it;
-      };
-      int g = 0, done = 0;
-      Item w, w2;
-      int it = next_item(blockIdx.x, w);
-      bool first_issued = false;               // the item's first scores were already issued under the previous item
-      while (ok && it < n_items) {
-        if (!first_issued) ok = ptx::mbar_wait(q_full, static_cast<uint32_t>(done) & 1u, abort_flag) && scores(g);
-        first_issued = false;
-        const int it2 = next_item(it + gridDim.x, w2);
-        // Tile j: the scores of tile j+1 are issued first -- at the item's last tile those of the NEXT item's first
-        // tile (its Q was loaded when this item's last Q.K^T finished), so that they are ready when the softmax
-        // threads come out of this item's output -- then P.V of tile j, which waits for the softmax.
-        for (int j = 0; ok && j < w.nkv; ++j) {
-          const int gg = g + j, b = gg & 1;
-          if (j + 1 < w.nkv) {
-            if (!scores(gg + 1)) { ok = false; break; }
-          } else if (it2 < n_items) {
-            if (!ptx::mbar_wait(q_full, static_cast<uint32_t>(done + 1) & 1u, abort_flag) || !scores(gg + 1)) { ok = false; break; }
-            first_issued = true;
+      Cursor cq, cp;   // next scores, next P.V
+      start(cq);
+      start(cp);
+      uint32_t idle = 0;
+      while (ok && cp.it < n_items) {
+        bool progress = false;
+        if (cq.it < n_items) {
+          // scores of tile g: its K | pos stage has landed, S[g & 1] has been read by the softmax of tile g - 2, and
+          // (first tile of an item) the item's Q has landed.  They run ahead of P.V by up to two tiles, into the
+          // next item too: its Q was requested when this item's last Q.K^T finished.
+          const int b = cq.g & 1;
+          const uint32_t ph = (cq.g >> 1) & 1u;
+          if (ptx::mbar_test(&k_full[b], ph) && ptx::mbar_test(&s_free[b], ph ^ 1u) &&
+              (cq.j != 0 || ptx::mbar_test(q_full, static_cast<uint32_t>(cq.ord) & 1u))) {
+            ptx::tc_fence_after_sync();
+            issue_qk(b);
+            advance(cq);
+            progress = true;
           }
-          ok = ptx::mbar_wait(p_full, static_cast<uint32_t>(gg) & 1u, abort_flag) &&
-               ptx::mbar_wait(&v_full[b], (gg >> 1) & 1u, abort_flag);
-          if (ok && j == 0 && done > 0) ok = ptx::mbar_wait(o_free, static_cast<uint32_t>(done - 1) & 1u, abort_flag);
-          if (!ok) break;
-          ptx::tc_fence_after_sync();
-          issue_pv(b, j == 0);
         }
-        g += w.nkv;
-        ++done;
-        it = it2;
-        w = w2;
+        if (cp.g < cq.g) {
+          // P.V of tile g: P written, V landed, and (first tile of an item) every row has read the previous item's O
+          const int b = cp.g & 1;
+          if (ptx::mbar_test(p_full, static_cast<uint32_t>(cp.g) & 1u) && ptx::mbar_test(&v_full[b], (cp.g >> 1) & 1u) &&
+              (cp.j != 0 || cp.ord == 0 || ptx::mbar_test(o_free, static_cast<uint32_t>(cp.ord - 1) & 1u))) {
+            ptx::tc_fence_after_sync();
+            issue_pv(b, cp.j == 0);
+            advance(cp);
+            progress = true;
+          }
+        }
+        if (progress) {
+          idle = 0;
+        } else {
+          if (++idle >= kIdleLimit) { *abort_flag = 1u; ok = false; }
+          else if ((idle & 63u) == 63u && *abort_flag) ok = false;
+        }
       }
       if (!ok && p.status) atomicOr(p.status, kStatusFmhaMma);
     }
@@ -315,7 +347,35 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t t_o = tmem_base + lane_base + kColO;
     bool ok = true;
     int g = 0;
-    for (int it = blockIdx.x; ok && it < n_items; it += gridDim.x) {
+    // An item's output leaves TMEM inside the NEXT item's first tile, between that tile's exponentials and its P store
+    // (the last P.V of the item finishes under them); the CTA's last item after the loop.
+    bool pending = false;          // an item whose O has not been written out yet
+    float pending_l = 0.f;
+    T* pending_row = nullptr;      // nullptr: the row lies past the segment's end
+    auto write_out = [&]() {       // O is stable: P.V of the item's last tile has been waited for
+      ptx::tc_fence_after_sync();
+      uint32_t o[64];
+      ptx::tmem_ld_32x64(t_o, o);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(o_free);    // O is in registers: the next item's first P.V may overwrite it
+      if (pending_row != nullptr) {
+        const float inv = pending_l > 0.f ? 1.f / pending_l : 0.f;
+#pragma unroll
+        for (int c = 0; c < D; c += 8) {
+          uint4 w;
+          w.x = pack2<T>(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+          w.y = pack2<T>(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+          w.z = pack2<T>(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+          w.w = pack2<T>(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+          *reinterpret_cast<uint4*>(pending_row + c) = w;
+        }
+      }
+      pending = false;
+    };
+    for (int round = 0; ok; ++round) {
+    const int it = item_of_round(round);
+    if (it >= n_items) break;
     Item w;
     if (!decode(it, w)) continue;
     const int kv_len = w.kv_len, nkv = w.nkv;
@@ -340,10 +400,16 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
         for (int i = 0; i < 64; ++i) v[i] = key0 + i < kv_len ? v[i] : 0xff800000u;
       }
-      float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};   // four independent chains
+      // eight independent chains of three-input maxima (four deep), then a three-level tree
+      float mx[8];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[i]));
-      float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      for (int c = 0; c < 8; ++c) {
+        const float a = max3(__uint_as_float(v[c]), __uint_as_float(v[c + 8]), __uint_as_float(v[c + 16]));
+        const float b2 = max3(a, __uint_as_float(v[c + 24]), __uint_as_float(v[c + 32]));
+        const float c2 = max3(b2, __uint_as_float(v[c + 40]), __uint_as_float(v[c + 48]));
+        mx[c] = fmaxf(c2, __uint_as_float(v[c + 56]));
+      }
+      float tile_max = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
       tile_max *= p.scale_log2;   // the scale is positive
       if (j == 3 && r == 0) stamp(p, 52);
       // Lazy rescale: the reference maximum moves only when this tile exceeds it by more than 2^kLazyLog2.
@@ -359,7 +425,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       // exponentiate, sum, round
       uint32_t packed[32];
       float row_sum = 0.f;
-      if (kPoly == 0) {
+      {
         // every exponential on the MUFU unit: scale / subtract and the row sum as packed fp32x2 operations (masked
         // keys carry -inf and come out as exactly 0)
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
@@ -374,32 +440,14 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         const float2 a = __fadd2_rn(acc[0], acc[1]);
         row_sum = a.x + a.y;
-      } else {
-        // keys 4k+3 (and 4k+1) of every group of four optionally on the FMA pipe; keys past the end give P = 0
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          float e0 = ex2_fast(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
-          const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run);
-          const float x3 = fmaf(__uint_as_float(v[i + 3]), p.scale_log2, -m_run);
-          float e1 = kPoly >= 2 ? ex2_poly(x1) : ex2_fast(x1);
-          float e2 = ex2_fast(fmaf(__uint_as_float(v[i + 2]), p.scale_log2, -m_run));
-          float e3 = kPoly >= 1 ? ex2_poly(x3) : ex2_fast(x3);
-          if (!full) {   // P of keys past the end is zero (V rows there hold other segments' finite values)
-            e0 = key0 + i < kv_len ? e0 : 0.f;
-            e1 = key0 + i + 1 < kv_len ? e1 : 0.f;
-            e2 = key0 + i + 2 < kv_len ? e2 : 0.f;
-            e3 = key0 + i + 3 < kv_len ? e3 : 0.f;
-          }
-          row_sum += (e0 + e1) + (e2 + e3);
-          packed[i / 2] = pack2<T>(e0, e1);
-          packed[i / 2 + 1] = pack2<T>(e2, e3);
-        }
       }
       if (j == 3 && r == 0) stamp(p, 53);
       // P.V of tile j-1 has finished: P may be rewritten and O is stable (it is only touched here when the maximum moved)
-      if (j >= 1) {
+      if (j >= 1 || pending) {
         if (!ptx::mbar_wait(po_done, static_cast<uint32_t>(gg - 1) & 1u, abort_flag)) { ok = false; break; }
-        if (moved) {
+        if (j == 0) {
+          write_out();                 // the previous item's rows (the maximum cannot have moved on a first tile)
+        } else if (moved) {
           ptx::tc_fence_after_sync();
           uint32_t o[64];
           ptx::tmem_ld_32x64(t_o, o);
@@ -426,31 +474,16 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       ptx::mbar_arrive(p_full);
       if (r == 0 && j < 40) stamp(p, 3 + j);
     }
-    if (ok) ok = ptx::mbar_wait(po_done, static_cast<uint32_t>(g + nkv - 1) & 1u, abort_flag);
-    if (ok) {
-      ptx::tc_fence_after_sync();
-      uint32_t o[64];
-      ptx::tmem_ld_32x64(t_o, o);
-      ptx::tmem_ld_wait();
-      if (row_ok) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        T* orow = out + static_cast<int64_t>(r) * out_ld;
-#pragma unroll
-        for (int c = 0; c < D; c += 8) {
-          uint4 w;
-          w.x = pack2<T>(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
-          w.y = pack2<T>(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
-          w.z = pack2<T>(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
-          w.w = pack2<T>(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
-          *reinterpret_cast<uint4*>(orow + c) = w;
-        }
-      }
-      if (r == 0) stamp(p, 60);
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(o_free);             // O is in registers: the next item's first P.V may overwrite it
-    }
+    pending = ok;
+    pending_l = l_run;
+    pending_row = row_ok ? out + static_cast<int64_t>(r) * out_ld : nullptr;
     g += nkv;
     }   // items
+    if (ok && pending) {
+      ok = ptx::mbar_wait(po_done, static_cast<uint32_t>(g - 1) & 1u, abort_flag);
+      if (ok) write_out();
+      if (r == 0) stamp(p, 60);
+    }
     if (p.trace != nullptr && r == 0) {   // diagnostics: this CTA's span and work
       p.trace[64 + blockIdx.x * 4 + 1] = static_cast<unsigned long long>(clock64());
       p.trace[64 + blockIdx.x * 4 + 2] = static_cast<unsigned long long>(g);
@@ -513,9 +546,7 @@ int run(void* out, const void* qkv4, const void* pos, int64_t pos_rows, int64_t 
     return check_launch("fmha_varlen_relpos (two CTAs per SM) launch");
   };
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
-    if (g_fmha_poly <= 0) return launch_one(fmha_relpos64_kernel<T, 0>);
-    if (g_fmha_poly == 1) return launch_one(fmha_relpos64_kernel<T, 1>);
-    return launch_one(fmha_relpos64_kernel<T, 2>);
+    return launch_one(fmha_relpos64_kernel<T>);
   });
 }
 

@@ -610,7 +610,7 @@ int launch(const Call& c, cudaStream_t s) {
   int64_t clusters = sm_count() / 2;
   if (c.p.num_pairs < clusters) clusters = c.p.num_pairs;
   if (clusters < 1) clusters = 1;
-  kern<<<static_cast<unsigned>(2 * clusters), kThreads, S::kDynamic, s>>>(ta, tb, th, c.p);
+  launch_pdl(kern, dim3(static_cast<unsigned>(2 * clusters)), dim3(kThreads), S::kDynamic, s, ta, tb, th, c.p);
   return check_launch("gemm_add_norm_f32 launch");
 }
 

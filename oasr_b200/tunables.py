@@ -8,8 +8,6 @@ an in-place row log-softmax kernel (fp32 output only).
 ``fmha_chunk_path``: 1 (default) runs paged rel-pos attention with <= 16 query frames on the warp-per-(stream, head)
 kernel, 0 always on the 128-row tcgen05 kernel.
 ``fmha_relpos_path``: 1 (default) runs packed relative-position attention on the two-CTAs-per-SM kernel, 0 on the general one.
-``fmha_poly``: how many of every four exponentials of the packed relative-position attention kernel run as a cubic on
-the FMA pipe instead of the MUFU unit: 0 (default; measured fastest), 1 or 2.
 ``conv1_mma``: 1 (default) runs the first subsampling convolution (parity-split output, 256 / 512 channels) as a K = 32
 split-bf16 GEMM on the tensor cores, 0 as the fp32 stencil kernel.
 ``conv2_pairs``: 1 (default) runs the second subsampling convolution on CTA pairs over all output channels (widths
@@ -17,7 +15,7 @@ split-bf16 GEMM on the tensor cores, 0 as the fp32 stencil kernel.
 ``fused_addnorm``: 1 (default) runs the last Linear of every Conformer sub-layer fused with the residual add and the
 following norm (widths 128 / 256 / 512) when the batch's 256-row tiles fill the GPU, 2 whenever the width allows it, 0
 always as gemm + add_norm_f32.
-``pdl``: 1 launches the hot kernels with programmatic stream serialisation, 0 (default) in plain stream order.
+``pdl``: 1 (default) launches the hot kernels with programmatic stream serialisation, 0 in plain stream order.
 """
 from __future__ import annotations
 
