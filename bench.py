@@ -482,7 +482,7 @@ def run_fastconformer(args):
     P = init_fastconformer_params(hidden, heads, ffn, layers, kernel, mels, channels, seed=1234, w_std=0.02, bias=False, vocab=vocab)
     enc = FastConformerEncoder(hidden, heads, ffn, layers, kernel, 57, 3, mels, channels, P)
     if args.quant != "none":
-        enc.stack.qkind = {"fp8": 1, "int8": 2}[args.quant]
+        enc.stack.set_quant(args.quant)
     rng = np.random.default_rng(2024)
     lengths = [int(x) for x in rng.integers(500, 3001, size=batch)]
     feats = torch.randn(batch, max(lengths), mels, generator=torch.Generator().manual_seed(7)).cuda()

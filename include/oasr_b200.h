@@ -832,6 +832,11 @@ typedef struct oasr_b200_fastconformer_layer {
   const void *norm_ff2_w, *norm_ff2_b;
   const void *ff2_w1, *ff2_b1, *ff2_w2, *ff2_b2;
   const void *norm_out_w, *norm_out_b;
+  /* 8-bit kinds (model.quant_kind != 0): the eight Linear weights quantised per output channel
+   * (oasr_b200_quantize_rows of the 16-bit weight) and their fp32 scales, in the order ff1_w1, ff1_w2, qkv4_w, o_w,
+   * pw1_w, pw2_w, ff2_w1, ff2_w2.  rel_w stays 16-bit (it multiplies the small position table).  Unused otherwise. */
+  const void* q_w[8];
+  const float* q_s[8];
 } oasr_b200_fastconformer_layer;
 
 typedef struct oasr_b200_fastconformer_model {
@@ -841,6 +846,7 @@ typedef struct oasr_b200_fastconformer_model {
   double eps;              /* of the LayerNorms between the sub-layers (the conv module's own norm uses 1e-5) */
   double mask_floor;       /* finite additive floor of a masked key (-1e4, encoder.py:80) */
   const oasr_b200_fastconformer_layer* layers;   /* HOST array of num_layers entries */
+  int32_t quant_kind;      /* 0 = 16-bit Linear GEMMs; OASR_Q8_FP8_E4M3 / OASR_Q8_INT8 = per-token quantised inputs x q_w */
 } oasr_b200_fastconformer_model;
 
 /* Bytes of device scratch oasr_b200_fastconformer_layers_packed needs for `total` packed frames, a relative-position

@@ -122,7 +122,8 @@ class FastConformerLayer(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in (
         "norm_ff1_w", "norm_ff1_b", "ff1_w1", "ff1_b1", "ff1_w2", "ff1_b2", "norm_att_w", "norm_att_b", "qkv4_w", "qkv4_b",
         "rel_w", "o_w", "o_b", "norm_conv_w", "norm_conv_b", "pw1_w", "pw1_b", "dw_w", "dw_b", "conv_norm_w", "conv_norm_b",
-        "pw2_w", "pw2_b", "norm_ff2_w", "norm_ff2_b", "ff2_w1", "ff2_b1", "ff2_w2", "ff2_b2", "norm_out_w", "norm_out_b")]
+        "pw2_w", "pw2_b", "norm_ff2_w", "norm_ff2_b", "ff2_w1", "ff2_b1", "ff2_w2", "ff2_b2", "norm_out_w", "norm_out_b")] + [
+        ("q_w", c_void_p * 8), ("q_s", c_void_p * 8)]
 
 
 class FastConformerModel(ctypes.Structure):
@@ -130,7 +131,7 @@ class FastConformerModel(ctypes.Structure):
 
     _fields_ = [(n, ctypes.c_int32) for n in (
         "hidden", "heads", "ffn", "kernel", "num_layers", "dtype", "left_context", "right_context")] + [
-        ("eps", c_double), ("mask_floor", c_double), ("layers", POINTER(FastConformerLayer))]
+        ("eps", c_double), ("mask_floor", c_double), ("layers", POINTER(FastConformerLayer)), ("quant_kind", ctypes.c_int32)]
 
 
 _SIGNATURES["oasr_b200_fastconformer_layers_packed"] = [POINTER(FastConformerModel), P, c_int, P, P, I, P, P, I, I, I, I, P, I, P]

@@ -1,10 +1,11 @@
 // Native executor of the packed FastConformer / Nemotron layer stack: one host call enqueues the whole fixed
 // kernel sequence of NemotronEncoder.forward's layer loop (oasr/models/nemotron/encoder.py:217-267, 542-583) on the
-// caller's stream -- per layer 17 launches of this library's own C-ABI kernels: macaron FFN, Transformer-XL
+// caller's stream -- per layer 17 launches (25 with an 8-bit kind) of this library's own C-ABI kernels: macaron FFN, Transformer-XL
 // relative-position attention (q projected once per global bias, position scores as one batched GEMM over heads,
 // one kernel for the relative shift + scale + chunked-limited window, head_dim 128 attention with that bias),
 // conv module (GLU GEMM, causal depthwise conv per segment, LayerNorm + SiLU, pointwise GEMM), second FFN, with the
-// fp32 residual stream and the fused add + LayerNorm between the sub-layers.  Host code only: no allocation, no host
+// fp32 residual stream and the fused add + LayerNorm between the sub-layers; with an 8-bit kind every Linear is a
+// per-token quantisation of its input followed by the fp8 / int8 GEMM on the pre-quantised weight.  Host code only: no allocation, no host
 // synchronisation; launch order and kernel choice are pure functions of the shapes.  The rows are the valid frames of
 // all utterances back to back (no padding frame is ever computed).
 #include <cmath>
@@ -26,6 +27,8 @@ struct FcWorkspace {
   uint8_t* rel_k;  // (Pp, C)  projected relative-position table of the current layer
   uint8_t* bd;     // (H, M, Pp) position scores
   uint8_t* bias;   // bias_numel elements: block-diagonal attention bias
+  uint8_t* q8;     // (M, max(C, F)) 8-bit kinds: the per-token quantised input of the current Linear
+  float* qs;       // (M) its row scales
   int64_t bytes;
 };
 
@@ -51,6 +54,10 @@ FcWorkspace fc_carve(const oasr_b200_fastconformer_model& m, int64_t M, int64_t 
   w.rel_k = take(table_rows * C * 2);
   w.bd = take(static_cast<int64_t>(m.heads) * M * table_rows * 2);
   w.bias = take(bias_numel * 2);
+  if (m.quant_kind != 0) {
+    w.q8 = take(M * (m.ffn > C ? m.ffn : C));
+    w.qs = reinterpret_cast<float*>(take(M * 4));
+  }
   w.bytes = off;
   return w;
 }
@@ -105,6 +112,22 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
   const oasr_b200_fastconformer_layer* ly = m.layers;
   const double eps = m.eps;
 
+  // One Linear: 16-bit GEMM, or per-token quantisation of the input followed by the 8-bit GEMM on the layer's
+  // pre-quantised weight `qi` (order of oasr_b200_fastconformer_layer::q_w).
+  const int qk = m.quant_kind;
+  OB_REQUIRE(qk == 0 || qk == OASR_Q8_FP8_E4M3 || qk == OASR_Q8_INT8, OASR_ERR_INVALID, "fastconformer_layers_packed: bad quant_kind %d", qk);
+#define FC_LINEAR(out, in, wt, bs, lay, qi, N, K, act, glu)                                                           \
+  do {                                                                                                                \
+    if (qk == 0) {                                                                                                    \
+      if (glu) FC_STEP(oasr_b200_gemm_glu(out, in, wt, bs, M, N, K, dt, stream));                                       \
+      else FC_STEP(oasr_b200_gemm(out, in, wt, bs, M, N, K, act, dt, stream));                                          \
+    } else {                                                                                                          \
+      OB_REQUIRE((lay).q_w[qi] && (lay).q_s[qi], OASR_ERR_INVALID, "fastconformer_layers_packed: layer without 8-bit weight %d", qi); \
+      FC_STEP(oasr_b200_quantize_rows(w.q8, w.qs, in, M, K, qk, dt, stream));                                          \
+      FC_STEP(oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, M, N, K, act, glu, qk, dt, stream)); \
+    }                                                                                                                 \
+  } while (0)
+
   // the input rows (16-bit, or fp32 when rows_f32) start the fp32 residual stream; h = LN_ff1(x) of the first layer in
   // the same kernel
   float* res = w.res;
@@ -118,11 +141,11 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_fastconformer_layer& l = ly[i];
     // macaron feed-forward: x += 0.5 * W2 silu(W1 h)
-    FC_STEP(oasr_b200_gemm(w.a_ffn, w.h, l.ff1_w1, l.ff1_b1, M, F, C, OASR_ACT_SWISH, dt, stream));
-    FC_STEP(oasr_b200_gemm(w.y, w.a_ffn, l.ff1_w2, l.ff1_b2, M, C, F, OASR_ACT_NONE, dt, stream));
+    FC_LINEAR(w.a_ffn, w.h, l.ff1_w1, l.ff1_b1, l, 0, F, C, OASR_ACT_SWISH, 0);
+    FC_LINEAR(w.y, w.a_ffn, l.ff1_w2, l.ff1_b2, l, 1, C, F, OASR_ACT_NONE, 0);
     FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 0.5, 0, l.norm_att_w, l.norm_att_b, nullptr, nullptr, M, C, eps, 0, dt, stream));
     // attention: [q+u | q+v | k | v] of every row, position scores (q+v) . rel_k^T per head, shifted bias, attention
-    FC_STEP(oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * C, C, OASR_ACT_NONE, dt, stream));
+    FC_LINEAR(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * C, C, OASR_ACT_NONE, 0);
     FC_STEP(oasr_b200_gemm(w.rel_k, rel_table, l.rel_w, nullptr, Pp, C, C, OASR_ACT_NONE, dt, stream));
     FC_STEP(oasr_b200_bmm_strided(w.bd, w.qkv4 + C * es, w.rel_k, H, M, Pp, D, 4 * C, D, C, D, dt, stream));
     FC_STEP(oasr_b200_relshift_bias_packed(w.bias, w.bd, cu_seqlens, bias_offsets, num_segs, H, M, max_seg, Pp, scale, chunk,
@@ -130,18 +153,18 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
     FC_STEP(oasr_b200_fmha_varlen_strided(w.att, w.qkv4, w.qkv4 + 2 * C * es, w.qkv4 + 3 * C * es, 4 * C, 4 * C, 4 * C, w.bias,
                                           bias_offsets, 1, 1, cu_seqlens, cu_seqlens, num_segs, M, M, max_seg, H, H, D, scale, dt,
                                           stream));
-    FC_STEP(oasr_b200_gemm(w.y, w.att, l.o_w, l.o_b, M, C, C, OASR_ACT_NONE, dt, stream));
+    FC_LINEAR(w.y, w.att, l.o_w, l.o_b, l, 3, C, C, OASR_ACT_NONE, 0);
     FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 1.0, 0, l.norm_conv_w, l.norm_conv_b, nullptr, nullptr, M, C, eps, 0, dt, stream));
     // conv module: pointwise + GLU, causal depthwise conv per segment, LayerNorm + SiLU, pointwise
-    FC_STEP(oasr_b200_gemm_glu(w.g, w.h, l.pw1_w, l.pw1_b, M, C, C, dt, stream));
+    FC_LINEAR(w.g, w.h, l.pw1_w, l.pw1_b, l, 4, C, C, OASR_ACT_NONE, 1);
     FC_STEP(oasr_b200_depthwise_conv1d_packed_causal(w.cv, w.g, l.dw_w, l.dw_b, cu_seqlens, num_segs, max_seg, C, m.kernel, -1, dt,
                                                      stream));
     FC_STEP(oasr_b200_layer_norm_activation(w.g, w.cv, l.conv_norm_w, l.conv_norm_b, M, C, 1e-5, OASR_ACT_SWISH, dt, stream));
-    FC_STEP(oasr_b200_gemm(w.y, w.g, l.pw2_w, l.pw2_b, M, C, C, OASR_ACT_NONE, dt, stream));
+    FC_LINEAR(w.y, w.g, l.pw2_w, l.pw2_b, l, 5, C, C, OASR_ACT_NONE, 0);
     FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 1.0, 0, l.norm_ff2_w, l.norm_ff2_b, nullptr, nullptr, M, C, eps, 0, dt, stream));
     // second feed-forward, norm_out, then the next layer's first pre-norm in the same kernel
-    FC_STEP(oasr_b200_gemm(w.a_ffn, w.h, l.ff2_w1, l.ff2_b1, M, F, C, OASR_ACT_SWISH, dt, stream));
-    FC_STEP(oasr_b200_gemm(w.y, w.a_ffn, l.ff2_w2, l.ff2_b2, M, C, F, OASR_ACT_NONE, dt, stream));
+    FC_LINEAR(w.a_ffn, w.h, l.ff2_w1, l.ff2_b1, l, 6, F, C, OASR_ACT_SWISH, 0);
+    FC_LINEAR(w.y, w.a_ffn, l.ff2_w2, l.ff2_b2, l, 7, C, F, OASR_ACT_NONE, 0);
     if (i + 1 < L) {
       FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 0.5, 2, l.norm_out_w, l.norm_out_b, ly[i + 1].norm_ff1_w, ly[i + 1].norm_ff1_b,
                                      M, C, eps, 0, dt, stream));

@@ -76,7 +76,15 @@ class FastConformerLayers:
                 lw[n] = (w(params[p + n + ".weight"]), w(params[p + n + ".bias"]))
             self.layers.append(lw)
         self._workspace = None
-        self.native = self.qkind == 0     # packed 16-bit batches run through the one-call native executor
+        self.native = True                # packed batches run through the one-call native executor
+        self._build_native_model()
+
+    def set_quant(self, quant) -> None:
+        """Switch the Linear GEMMs of the stack between 16-bit (``None``) and an 8-bit kind ("fp8" / "int8")."""
+        if quant not in (None, "fp8", "int8"):
+            raise ValueError("quant must be None, 'fp8' or 'int8'")
+        self.qkind = {None: 0, "fp8": 1, "int8": 2}[quant]
+        self._q8 = {}
         self._build_native_model()
 
     def _build_native_model(self) -> None:
@@ -103,12 +111,20 @@ class FastConformerLayers:
             c.pw1_w, c.pw1_b = ptr(lw["pw1"][0]), ptr(lw["pw1"][1])
             c.dw_w, c.dw_b = ptr(lw["dw"][0]), ptr(lw["dw"][1])
             c.pw2_w, c.pw2_b = ptr(lw["pw2"][0]), ptr(lw["pw2"][1])
+            if self.qkind:
+                # the eight Linear weights per output channel in 8 bits, in the order of the struct's q_w / q_s
+                linears = (lw["feed_forward1"][0], lw["feed_forward1"][2], lw["qkv4"][0], lw["o"][0], lw["pw1"][0],
+                           lw["pw2"][0], lw["feed_forward2"][0], lw["feed_forward2"][2])
+                for j, wt in enumerate(linears):
+                    wq, ws = self._weight_q8(wt)
+                    c.q_w[j], c.q_s[j] = wq.data_ptr(), ws.data_ptr()
         m = _lib.FastConformerModel()
         m.hidden, m.heads, m.ffn, m.kernel, m.num_layers = self.C, self.H, self.F, self.K, self.L
         m.dtype = _DTYPE_ID[self.dtype]
         m.left_context, m.right_context = self.left, self.right
         m.eps, m.mask_floor = self.eps, MASK_FLOOR
         m.layers = ctypes.cast(arr, ctypes.POINTER(_lib.FastConformerLayer))
+        m.quant_kind = self.qkind
         self._native_layers, self._native_model = arr, m      # keep both alive
 
     def _layers_native(self, rows: torch.Tensor, g) -> torch.Tensor:
@@ -135,6 +151,14 @@ class FastConformerLayers:
                   ctypes.c_void_p(ws.data_ptr() + off), ws.numel() - off, _stream(res))
         return out
 
+    def _weight_q8(self, w: torch.Tensor):
+        """The 8-bit copy of a Linear weight (per output channel) and its scales, quantised once and kept."""
+        from . import quant
+        key = w.data_ptr()
+        if key not in self._q8:
+            self._q8[key] = quant.quantize_rows(w, self.qkind)
+        return self._q8[key]
+
     def _linear(self, x: torch.Tensor, w: torch.Tensor, b, act: int = -1, glu: bool = False) -> torch.Tensor:
         """One Linear: 16-bit GEMM, or per-token quantisation + 8-bit GEMM against the cached 8-bit weight."""
         if not self.qkind:
@@ -142,10 +166,7 @@ class FastConformerLayers:
                 return OF.gemm_glu(x, w, b)
             return OF.gemm_activation(x, w, b, act) if act >= 0 else OF.gemm(x, w, b)
         from . import quant
-        key = w.data_ptr()
-        if key not in self._q8:
-            self._q8[key] = quant.quantize_rows(w, self.qkind)
-        wq, ws = self._q8[key]
+        wq, ws = self._weight_q8(w)
         xq, xs = quant.quantize_rows(x, self.qkind)
         return quant.gemm_q8(xq, xs, wq, ws, b, kind=self.qkind, activation=act, glu=glu, out_dtype=self.dtype)
 
@@ -208,13 +229,13 @@ class FastConformerLayers:
 
     def _layers(self, rows: torch.Tensor, g) -> torch.Tensor:
         """``rows (M, C)`` post-subsampling states (fp32 or the model's 16-bit type) -> ``(M, C)`` fp32 output of the stack."""
-        if self.native and self.qkind == 0 and g["packed"] and rows.dtype in (torch.float32, self.dtype):
-            return self._layers_native(rows.contiguous(), g)        # the native executor runs the 16-bit stack
+        if self.native and g["packed"] and rows.dtype in (torch.float32, self.dtype):
+            return self._layers_native(rows.contiguous(), g)        # one call: 16-bit or 8-bit Linear GEMMs
         return self._layers_composed(rows.to(torch.float32, copy=True).contiguous(), g)   # own copy: updated in place
 
     def _layers_composed(self, res: torch.Tensor, g) -> torch.Tensor:
-        """The stack operator by operator from Python: padded batches, 8-bit Linear GEMMs, and the check of the native
-        executor (same kernels, same order, so bit-identical results)."""
+        """The stack operator by operator from Python: padded batches, and the check of the native executor (same
+        kernels, same order, so bit-identical results, with 16-bit and with 8-bit Linear GEMMs)."""
         M, C = res.shape
         rel_table = self._position_table(g["T"])
         h = torch.empty(M, C, device=res.device, dtype=self.dtype)

@@ -285,6 +285,35 @@ def test_streaming_from_feature_frames_matches_the_oracle():
     assert torch.equal(again, first)
 
 
+@pytest.mark.parametrize("quant", ["fp8", "int8"])
+def test_native_executor_with_8bit_linears_equals_the_composed_stack(quant):
+    """With an 8-bit kind the native executor quantises every Linear's input per token and runs the fp8 / int8 GEMM on
+    the weight quantised once per output channel -- the same two kernels per Linear as the Python composition, so
+    the results are bit-identical, and they stay within the 8-bit gate (cosine >= 0.999) of the 16-bit stack."""
+    from oasr_b200 import _lib
+
+    cfg = OFC.FastConformerConfig(hidden=256, heads=2, ffn=512, layers=2, kernel=9, sliding_window=25, lookahead=3, bias=True)
+    P = OFC.init_params(cfg, 78, w_std=0.02)     # the benchmark's N(0, 0.02) init, as in the gate test above
+    args = (cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, cfg.kernel, cfg.sliding_window, cfg.lookahead, P)
+    model = FastConformerLayers(*args, quant=quant)
+    assert model.native and model._native_model.quant_kind in (1, 2)
+    lengths = [61, 17, 128, 1]
+    hidden = torch.randn(len(lengths), 128, cfg.hidden, generator=torch.Generator().manual_seed(3)).cuda()
+    before = _lib.launch_count()
+    rows_native, index = model.forward_rows(hidden, lengths)
+    launched = _lib.launch_count() - before
+    model.native = False
+    rows_composed, _ = model.forward_rows(hidden, lengths)
+    model.native = True
+    assert ob.device_status() == 0
+    assert torch.equal(rows_native, rows_composed)
+    assert launched >= 25 * cfg.layers          # 17 + 8 per-token quantisations per layer
+    rows16, _ = FastConformerLayers(*args).forward_rows(hidden, lengths)
+    cos = torch.nn.functional.cosine_similarity(rows_native.flatten(), rows16.flatten(), dim=0).item()
+    print(f"{quant} native stack vs 16-bit stack: cosine {cos:.6f}")
+    assert cos >= 0.999
+
+
 def test_native_executor_equals_the_operator_by_operator_stack():
     """oasr_b200_fastconformer_layers_packed enqueues the same kernels in the same order as the Python composition of
     the packed stack, so the two agree bit for bit; it refuses a workspace that is too small before launching."""
