@@ -306,7 +306,8 @@ def run_streaming(args):
         tunables.set("pdl", 1)
     streams, window, chunk, max_past = args.batch if args.batch != 64 else 256, 67, 16, 256
     cfg = dataclasses.replace(model_config(args.layers), causal=True)
-    model = ConformerCTC(cfg, init_params(cfg, 1234), device="cuda:0", dtype=torch.bfloat16)
+    model = ConformerCTC(cfg, init_params(cfg, 1234), device="cuda:0", dtype=torch.bfloat16,
+                         quant=None if args.quant == "none" else args.quant)
     slots = list(range(streams))
     g = torch.Generator().manual_seed(7)
     host = [torch.randn(streams, window, 80, generator=g).pin_memory() for _ in range(8)]
@@ -361,7 +362,9 @@ def run_streaming(args):
     print(json.dumps({
         "metric": "audio_seconds_per_second", "value": audio / (total_ms * 1e-3), "unit": "audio-s/s", "n_gpus": 1,
         "steps": args.steps, "warmup": warm, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
+        "data": "synthetic",
         "config": {"workload": f"streaming conformer{args.layers}_d512_h8_ffn2048_k15_vocab5002: {streams} streams x 1 chunk "
                                f"(window {window} frames -> {chunk} encoder frames), history {max_past} frames in 16-frame pages, "
                                f"random page order, {'fp8 e4m3 K/V pages with per-head scales' if args.kv == 'fp8' else 'bf16 K/V'}", "l2": "256 MiB flush write between steps",

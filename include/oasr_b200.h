@@ -757,7 +757,10 @@ OASR_API int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* 
  * cache_seqlens[b], and runs the causal conv module on [cnn_state[l, slot_ids[b]] ;
  * chunk], updating cnn_state (num_layers, num_slots, kernel-1, d) in place.  The
  * caller allocated the chunk's pages before the call and advances cache_seqlens
- * after it, as with the reference's AttentionCacheManager.  T <= 128. */
+ * after it, as with the reference's AttentionCacheManager.  T <= 128.  With the
+ * model's quant_kind set, the eight Linear GEMMs of every layer run on 8-bit
+ * operands as in the offline entry point (per-token quantisation of each input,
+ * the layers' q_w / q_s). */
 OASR_API int64_t oasr_b200_conformer_chunk_workspace_bytes(const oasr_b200_conformer_model* model,
                                                            int64_t B, int64_t T);
 OASR_API int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model,

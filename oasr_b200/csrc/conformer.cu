@@ -35,6 +35,8 @@ int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 struct ChunkWorkspace {
   float* res;
   uint8_t *h, *y, *a_ffn, *qkv4, *att, *xcat, *g, *cv, *h3;
+  uint8_t* q8;     // quant_kind != 0: per-token quantised input of the current Linear, one byte per element
+  float* qs;       // its row scales
   int64_t bytes;
 };
 
@@ -57,6 +59,11 @@ ChunkWorkspace carve_chunk(const oasr_b200_conformer_model& m, int64_t B, int64_
   w.g = take(MC * d * 2);
   w.cv = take(M * d * 2);
   w.h3 = take(M * 2 * d * 2);
+  if (m.quant_kind != 0) {
+    const int64_t widest = M * m.ffn > MC * d ? M * m.ffn : MC * d;
+    w.q8 = take(widest);
+    w.qs = reinterpret_cast<float*>(take(MC * 4));
+  }
   w.bytes = off;
   return w;
 }
@@ -378,7 +385,8 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
   OB_REQUIRE(m.pos_proj && m.pos_proj_rows > 0, OASR_ERR_INVALID,
              "conformer_chunk_paged: the model has no projected positional table (pos_proj)");
   OB_REQUIRE(is_aligned(workspace, 256), OASR_ERR_ALIGN, "conformer_chunk_paged: workspace must be 256-byte aligned");
-  OB_REQUIRE(m.quant_kind == 0, OASR_ERR_UNSUPPORTED, "conformer_chunk_paged: 8-bit GEMM kinds are wired into the offline entry point only");
+  const int qk = m.quant_kind;
+  OB_REQUIRE(qk == 0 || qk == OASR_Q8_FP8_E4M3 || qk == OASR_Q8_INT8, OASR_ERR_INVALID, "conformer_chunk_paged: bad quant_kind %d", qk);
   ChunkWorkspace w = carve_chunk(m, B, T, static_cast<uint8_t*>(workspace));
   OB_REQUIRE(workspace_bytes >= w.bytes, OASR_ERR_INVALID, "conformer_chunk_paged: workspace of %lld bytes, %lld needed",
              (long long)workspace_bytes, (long long)w.bytes);
@@ -386,6 +394,19 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
   const int dt = m.dtype;
   const double scale = 1.0 / std::sqrt(64.0);
   const oasr_b200_conformer_layer* ly = m.layers;
+
+  // One Linear over `R` rows: 16-bit GEMM, or per-token quantisation of the input followed by the 8-bit GEMM on the
+  // layer's pre-quantised weight `qi` (order of oasr_b200_conformer_layer::q_w), as in the offline executor.
+#define OB_CHUNK_LINEAR(label, fl, out, in, wt, bs, lay, qi, R, N, K, act, glu)                                       \
+  do {                                                                                                                \
+    if (qk == 0) {                                                                                                    \
+      if (glu) OB_STEP("gemm_glu " label, fl, oasr_b200_gemm_glu(out, in, wt, bs, R, N, K, dt, stream));                \
+      else OB_STEP("gemm " label, fl, oasr_b200_gemm(out, in, wt, bs, R, N, K, act, dt, stream));                      \
+    } else {                                                                                                          \
+      OB_STEP("quantize_rows", 0, oasr_b200_quantize_rows(w.q8, w.qs, in, R, K, qk, dt, stream));                       \
+      OB_STEP("gemm_q8 " label, fl, oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, R, N, K, act, glu, qk, dt, stream)); \
+    }                                                                                                                 \
+  } while (0)
 
   // the embedding starts the fp32 residual stream unrounded (see the offline executor)
   OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_residual_f32(w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, dt, stream));
@@ -398,12 +419,12 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
   }
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_conformer_layer& l = ly[i];
-    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
-    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    OB_CHUNK_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, l, 0, M, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_CHUNK_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, M, d, m.ffn, OASR_ACT_NONE, 0);
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
                                    m.eps, 0, dt, stream));
     // attention: project, append the chunk's keys/values to the pages, attend over cache + chunk
-    OB_STEP("gemm qkv4", 2.0 * M * 3 * d * d, oasr_b200_gemm(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, M, 4 * d, d, OASR_ACT_NONE, dt, stream));
+    OB_CHUNK_LINEAR("qkv4", 2.0 * M * 3 * d * d, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, M, 4 * d, d, OASR_ACT_NONE, 0);
     if (kv_scales) {   // fp8 pages: per-head scales of this layer, K then V
       const float* ks = kv_scales + static_cast<int64_t>(i) * 2 * m.heads;
       const float* vs = ks + m.heads;
@@ -423,20 +444,20 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
                                        pos_start, block_table, total_seqlens, B, T, m.heads, blocks_per_seq, block_size,
                                        num_blocks, scale, dt, stream));
     }
-    OB_STEP("gemm attn_out", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.att, l.out_w, l.out_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_CHUNK_LINEAR("attn_out", 2.0 * M * d * d, w.y, w.att, l.out_w, l.out_b, l, 3, M, d, d, OASR_ACT_NONE, 0);
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
                                    nullptr, M, d, m.eps, 0, dt, stream));
     // convolution module with the cached left context
     OB_STEP("conv_state_concat", 0, oasr_b200_conv_state_concat(w.xcat, static_cast<uint8_t*>(cnn_state) + i * num_slots * SL * d * 2,
                                      num_slots, slot_ids, w.h, B, SL, T, d, dt, stream));
-    OB_STEP("gemm_glu pw1", 2.0 * MC * 2 * d * d, oasr_b200_gemm_glu(w.g, w.xcat, l.pw1_w, l.pw1_b, MC, d, d, dt, stream));
+    OB_CHUNK_LINEAR("pw1", 2.0 * MC * 2 * d * d, w.g, w.xcat, l.pw1_w, l.pw1_b, l, 4, MC, d, d, OASR_ACT_NONE, 1);
     OB_STEP("depthwise_conv1d", 0, oasr_b200_depthwise_conv1d_affine(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
                                      B, T + SL, d, m.kernel, 0, 0, OASR_ACT_SWISH, dt, stream));
-    OB_STEP("gemm pw2", 2.0 * M * d * d, oasr_b200_gemm(w.y, w.cv, l.pw2_w, l.pw2_b, M, d, d, OASR_ACT_NONE, dt, stream));
+    OB_CHUNK_LINEAR("pw2", 2.0 * M * d * d, w.y, w.cv, l.pw2_w, l.pw2_b, l, 5, M, d, d, OASR_ACT_NONE, 0);
     OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, M, d,
                                    m.eps, 0, dt, stream));
-    OB_STEP("gemm ffn_w1", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.a_ffn, w.h, l.ff_w1, l.ff_b1, M, m.ffn, d, OASR_ACT_SWISH, dt, stream));
-    OB_STEP("gemm ffn_w2", 2.0 * M * m.ffn * d, oasr_b200_gemm(w.y, w.a_ffn, l.ff_w2, l.ff_b2, M, d, m.ffn, OASR_ACT_NONE, dt, stream));
+    OB_CHUNK_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ff_w1, l.ff_b1, l, 6, M, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_CHUNK_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, M, d, m.ffn, OASR_ACT_NONE, 0);
     if (i + 1 < L) {
       OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b,
                                      ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, M, d, m.eps, 0, dt, stream));

@@ -398,8 +398,6 @@ class ConformerCTC:
 
         if not self.cfg.causal:
             raise RuntimeError("streaming needs a causal conv module (cfg.causal=True)")
-        if self.quant_kind:
-            raise NotImplementedError("the streaming chunk executor runs 16-bit GEMMs only")
         if not xs.is_cuda:
             raise RuntimeError("xs must be a CUDA tensor (oasr_b200 has no CPU path)")
         if self._pos_proj is None:   # linear_pos of the whole positional table, every layer at once

@@ -159,3 +159,31 @@ def test_streaming_with_fp8_pages_reaches_the_cosine_gate_against_16_bit_pages()
     cos = torch.nn.functional.cosine_similarity(a, b, dim=0).item()
     print(f"fp8 pages vs 16-bit pages: cosine {cos:.6f}, max-abs {(a - b).abs().max().item():.3e}")
     assert cos >= 0.999, cos
+
+
+@pytest.mark.parametrize("mode", ["fp8", "int8"])
+def test_streaming_with_8bit_linears_reaches_the_cosine_gate_against_the_16_bit_run(mode):
+    """The chunk executor with the eight Linear GEMMs of every layer on 8-bit operands (weights per output channel,
+    activations per token, the pointwise_conv1 input over the chunk and its cached left context): cosine >= 0.999
+    against the 16-bit run of the same chunks, through eviction, and the same result from a graph replay."""
+    case = cases.STREAM_CASE
+    cfg = case["cfg"]
+    P = OC.init_params(cfg, case["weight_seed"], case["perturb"])
+    feats = cases.make_stream_features(case).cuda()
+    ref_model = ConformerCTC(_cfg(cfg), P)
+    q_model = ConformerCTC(_cfg(cfg), P, quant=mode)
+    max_past = case["num_left_chunks"] * case["chunk_size"]
+    windows = [feats[:, c * case["step"]: c * case["step"] + case["window"]] for c in range(case["chunks"])]
+    ref_cache = ref_model.new_streaming_cache(2, max_past, seed=1)
+    q_cache = q_model.new_streaming_cache(2, max_past, seed=2)
+    a, b = [], []
+    for xs in windows:
+        a.append(ref_model.forward_chunk_paged(xs, [0, 1], ref_cache)[..., :cfg.vocab].float())
+        b.append(q_model.forward_chunk_paged(xs, [0, 1], q_cache)[..., :cfg.vocab].float())
+    assert ob.device_status() == 0
+    a, b = torch.stack(a), torch.stack(b)
+    assert torch.isfinite(b).all()
+    cos = torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+    agree = (a.argmax(-1) == b.argmax(-1)).float().mean().item()
+    print(f"{mode} streaming Linears vs 16-bit: cosine {cos:.6f}, argmax agreement {agree:.4f}, max-abs {(a - b).abs().max().item():.3e}")
+    assert cos >= 0.999, cos
