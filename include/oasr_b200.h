@@ -190,6 +190,20 @@ OASR_API int oasr_b200_add_norm_f32(void* h_out, float* res_out /*nullable*/,
                                     const void* w_a, const void* b_a, const void* w_b /*mode 2*/,
                                     const void* b_b /*mode 2*/, int64_t rows, int64_t hidden,
                                     double eps, int split_out, int dtype, void* stream);
+/* The same, with the h row also written in 8 bits for a following 8-bit GEMM
+ * (no reference counterpart): q_out (rows, hidden) one byte per element and
+ * q_scale fp32[rows] are what oasr_b200_quantize_rows(h) would produce -- the
+ * scale is amax of the 16-bit h row / 448 (q_kind 1, fp8 e4m3) or / 127
+ * (q_kind 2, int8) -- bit for bit, so the per-token quantisation launch and
+ * its second read of h disappear.  q_out = NULL: exactly
+ * oasr_b200_add_norm_f32.  split_out must be 0 with an 8-bit output. */
+OASR_API int oasr_b200_add_norm_f32_q8(void* h_out, float* res_out /*nullable*/,
+                                       const float* res_in /*nullable*/,
+                                       const void* y /*nullable*/, double alpha, int mode,
+                                       const void* w_a, const void* b_a, const void* w_b /*mode 2*/,
+                                       const void* b_b /*mode 2*/, int64_t rows, int64_t hidden,
+                                       double eps, int split_out, void* q_out /*nullable*/,
+                                       float* q_scale, int q_kind, int dtype, void* stream);
 /* Linear + residual step + norm in one kernel (no single reference
  * counterpart: it replaces gemm (csrc/gemm_jit_binding.cu:9-12) followed by
  * addlayernorm_residual (csrc/norm_jit_binding.cu:18-20, kernel

@@ -226,6 +226,16 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   const bool fills = g_fused_addnorm == 2 || pairs * 5 >= rounds * slots * 4;
   const bool fuse = qk == 0 && g_fused_addnorm != 0 && fills && oasr_b200_gemm_add_norm_supported(d, d) != 0 &&
                     oasr_b200_gemm_add_norm_supported(d, m.ffn) != 0 && oasr_b200_gemm_add_norm_supported(d, m.embed_in) != 0;
+  // add + norm; with an 8-bit kind (and an unsplit h) the kernel also leaves the quantised row of h in w.q8 / w.qs for
+  // the Linear that reads h next, which then skips its own quantisation launch (OB_LINEAR_H)
+#define OB_ADD_NORM(hout, rout, rin, y_, alpha, mode, wa, ba, wb, bb, eps_, split)                                      \
+  OB_STEP("add_norm", 0, oasr_b200_add_norm_f32_q8(hout, rout, rin, y_, alpha, mode, wa, ba, wb, bb, M, d, eps_, split,   \
+                                                   (qk && !(split)) ? w.q8 : nullptr, (qk && !(split)) ? w.qs : nullptr, qk, dt, stream))
+#define OB_LINEAR_H(label, fl, out, wt, bs, lay, qi, N, act, glu)                                                     \
+  do {                                                                                                              \
+    if (qk == 0) OB_LINEAR(label, fl, out, w.h, wt, bs, lay, qi, N, d, act, glu);                                     \
+    else OB_STEP("gemm_q8 " label, fl, oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, M, N, d, act, glu, qk, dt, stream)); \
+  } while (0)
 #define OB_LINEAR_ADDNORM(label, fl, hout, rin, in, wt, bs, lay, qi, K, alpha, mode, wa, ba, wb, bb, eps_, split)       \
   do {                                                                                                              \
     if (fuse) {                                                                                                     \
@@ -233,7 +243,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
                                                                     wb, bb, eps_, split, dt, stream));              \
     } else {                                                                                                        \
       OB_LINEAR(label, fl, w.y, in, wt, bs, lay, qi, d, K, OASR_ACT_NONE, 0);                                        \
-      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(hout, w.res, rin, w.y, alpha, mode, wa, ba, wb, bb, M, d, eps_, split, dt, stream)); \
+      OB_ADD_NORM(hout, w.res, rin, w.y, alpha, mode, wa, ba, wb, bb, eps_, split);                                   \
     }                                                                                                               \
   } while (0)
   if (fuse) {
@@ -249,11 +259,9 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   // epilogue (a 16-bit round trip here would put a rounding error on every element that all layers then carry).
   OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_residual_f32(w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, dt, stream));
   if (m.embed_ln_w) {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, nullptr, 0.0, 2, m.embed_ln_w, m.embed_ln_b,
-                                   ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, M, d, 1e-5, 0, dt, stream));
+    OB_ADD_NORM(w.h, w.res, w.res, nullptr, 0.0, 2, m.embed_ln_w, m.embed_ln_b, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, 1e-5, 0);
   } else {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, nullptr, w.res, nullptr, 0.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b,
-                                   nullptr, nullptr, M, d, m.eps, 0, dt, stream));
+    OB_ADD_NORM(w.h, nullptr, w.res, nullptr, 0.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, nullptr, nullptr, m.eps, 0);
   }
   }
   // attention work list (longest segments first), once per batch; every layer reuses it
@@ -268,24 +276,24 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_conformer_layer& l = ly[i];
     // macaron feed-forward
-    OB_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, l, 0, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_LINEAR_H("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, l.ffm_w1, l.ffm_b1, l, 0, m.ffn, OASR_ACT_SWISH, 0);
     OB_LINEAR_ADDNORM("ffn_w2", 2.0 * M * m.ffn * d, w.h, w.res, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, m.ffn, 0.5, 0, l.norm_mha_w,
                       l.norm_mha_b, nullptr, nullptr, m.eps, 0);
     // relative-position self-attention
-    OB_LINEAR("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, d, OASR_ACT_NONE, 0);
+    OB_LINEAR_H("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, OASR_ACT_NONE, 0);
     OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos_planned(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs,
                                          max_seg, M, m.heads, scale, att_plan, dt, stream));
     OB_LINEAR_ADDNORM("attn_out", 2.0 * M * d * d, w.h, w.res, w.att, l.out_w, l.out_b, l, 3, d, 1.0, 1, l.norm_conv_scale,
                       l.norm_conv_shift, nullptr, nullptr, m.eps, 0);
     // convolution module
-    OB_LINEAR("pw1", 2.0 * M * 2 * d * d, w.g, w.h, l.pw1_w, l.pw1_b, l, 4, d, d, OASR_ACT_NONE, 1);
+    OB_LINEAR_H("pw1", 2.0 * M * 2 * d * d, w.g, l.pw1_w, l.pw1_b, l, 4, d, OASR_ACT_NONE, 1);
     OB_STEP("depthwise_conv1d_packed", 0, oasr_b200_depthwise_conv1d_packed(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
                                               fill_frames ? l.glu_of_bias : nullptr, fill_frames, cu_seqlens, num_segs,
                                               max_seg, d, m.kernel, OASR_ACT_SWISH, dt, stream));
     OB_LINEAR_ADDNORM("pw2", 2.0 * M * d * d, w.h, w.res, w.cv, l.pw2_w, l.pw2_b, l, 5, d, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr,
                       nullptr, m.eps, 0);
     // feed-forward, norm_final, then the next layer's first pre-norm (or after_norm, split for the head)
-    OB_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ff_w1, l.ff_b1, l, 6, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_LINEAR_H("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, l.ff_w1, l.ff_b1, l, 6, m.ffn, OASR_ACT_SWISH, 0);
     if (i + 1 < L) {
       OB_LINEAR_ADDNORM("ffn_w2", 2.0 * M * m.ffn * d, w.h, w.res, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, m.ffn, 0.5, 2, l.norm_final_w,
                         l.norm_final_b, ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, m.eps, 0);
@@ -408,23 +416,26 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
     }                                                                                                                 \
   } while (0)
 
+  // a Linear over the M chunk rows whose input h the add + norm before it has already quantised (8-bit kinds)
+#define OB_CHUNK_LINEAR_H(label, fl, out, wt, bs, lay, qi, N, act)                                                    \
+  do {                                                                                                                \
+    if (qk == 0) OB_CHUNK_LINEAR(label, fl, out, w.h, wt, bs, lay, qi, M, N, d, act, 0);                                \
+    else OB_STEP("gemm_q8 " label, fl, oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, M, N, d, act, 0, qk, dt, stream)); \
+  } while (0)
   // the embedding starts the fp32 residual stream unrounded (see the offline executor)
   OB_STEP("gemm embed", 2.0 * M * d * m.embed_in, oasr_b200_gemm_residual_f32(w.res, nullptr, rows, m.embed_w, m.embed_b, M, d, m.embed_in, 1.0, dt, stream));
   if (m.embed_ln_w) {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, nullptr, 0.0, 2, m.embed_ln_w, m.embed_ln_b,
-                                   ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, M, d, 1e-5, 0, dt, stream));
+    OB_ADD_NORM(w.h, w.res, w.res, nullptr, 0.0, 2, m.embed_ln_w, m.embed_ln_b, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, 1e-5, 0);
   } else {
-    OB_STEP("add_norm embed", 0, oasr_b200_add_norm_f32(w.h, nullptr, w.res, nullptr, 0.0, 0, ly[0].norm_ff_macaron_w,
-                                   ly[0].norm_ff_macaron_b, nullptr, nullptr, M, d, m.eps, 0, dt, stream));
+    OB_ADD_NORM(w.h, nullptr, w.res, nullptr, 0.0, 0, ly[0].norm_ff_macaron_w, ly[0].norm_ff_macaron_b, nullptr, nullptr, m.eps, 0);
   }
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_conformer_layer& l = ly[i];
-    OB_CHUNK_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ffm_w1, l.ffm_b1, l, 0, M, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_CHUNK_LINEAR_H("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, l.ffm_w1, l.ffm_b1, l, 0, m.ffn, OASR_ACT_SWISH);
     OB_CHUNK_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, M, d, m.ffn, OASR_ACT_NONE, 0);
-    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, M, d,
-                                   m.eps, 0, dt, stream));
+    OB_ADD_NORM(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, m.eps, 0);
     // attention: project, append the chunk's keys/values to the pages, attend over cache + chunk
-    OB_CHUNK_LINEAR("qkv4", 2.0 * M * 3 * d * d, w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, M, 4 * d, d, OASR_ACT_NONE, 0);
+    OB_CHUNK_LINEAR_H("qkv4", 2.0 * M * 3 * d * d, w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, OASR_ACT_NONE);
     if (kv_scales) {   // fp8 pages: per-head scales of this layer, K then V
       const float* ks = kv_scales + static_cast<int64_t>(i) * 2 * m.heads;
       const float* vs = ks + m.heads;
@@ -445,8 +456,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
                                        num_blocks, scale, dt, stream));
     }
     OB_CHUNK_LINEAR("attn_out", 2.0 * M * d * d, w.y, w.att, l.out_w, l.out_b, l, 3, M, d, d, OASR_ACT_NONE, 0);
-    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr,
-                                   nullptr, M, d, m.eps, 0, dt, stream));
+    OB_ADD_NORM(w.h, w.res, w.res, w.y, 1.0, 1, l.norm_conv_scale, l.norm_conv_shift, nullptr, nullptr, m.eps, 0);
     // convolution module with the cached left context
     OB_STEP("conv_state_concat", 0, oasr_b200_conv_state_concat(w.xcat, static_cast<uint8_t*>(cnn_state) + i * num_slots * SL * d * 2,
                                      num_slots, slot_ids, w.h, B, SL, T, d, dt, stream));
@@ -454,16 +464,13 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
     OB_STEP("depthwise_conv1d", 0, oasr_b200_depthwise_conv1d_affine(w.cv, w.g, l.dw_w, l.dw_b, l.conv_bn_scale, l.conv_bn_shift,
                                      B, T + SL, d, m.kernel, 0, 0, OASR_ACT_SWISH, dt, stream));
     OB_CHUNK_LINEAR("pw2", 2.0 * M * d * d, w.y, w.cv, l.pw2_w, l.pw2_b, l, 5, M, d, d, OASR_ACT_NONE, 0);
-    OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, M, d,
-                                   m.eps, 0, dt, stream));
-    OB_CHUNK_LINEAR("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, w.h, l.ff_w1, l.ff_b1, l, 6, M, m.ffn, d, OASR_ACT_SWISH, 0);
+    OB_ADD_NORM(w.h, w.res, w.res, w.y, 1.0, 0, l.norm_ff_w, l.norm_ff_b, nullptr, nullptr, m.eps, 0);
+    OB_CHUNK_LINEAR_H("ffn_w1", 2.0 * M * m.ffn * d, w.a_ffn, l.ff_w1, l.ff_b1, l, 6, m.ffn, OASR_ACT_SWISH);
     OB_CHUNK_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ff_w2, l.ff_b2, l, 7, M, d, m.ffn, OASR_ACT_NONE, 0);
     if (i + 1 < L) {
-      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b,
-                                     ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, M, d, m.eps, 0, dt, stream));
+      OB_ADD_NORM(w.h, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b, ly[i + 1].norm_ff_macaron_w, ly[i + 1].norm_ff_macaron_b, m.eps, 0);
     } else {
-      OB_STEP("add_norm", 0, oasr_b200_add_norm_f32(w.h3, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b, m.after_norm_w,
-                                     m.after_norm_b, M, d, m.eps, 1, dt, stream));
+      OB_ADD_NORM(w.h3, w.res, w.res, w.y, 0.5, 2, l.norm_final_w, l.norm_final_b, m.after_norm_w, m.after_norm_b, m.eps, 1);
     }
   }
   if (log_probs || argmax) {   // log_probs == NULL: token-only head, one vocabulary sweep, no log-prob write

@@ -1,6 +1,7 @@
 // Native executor of the packed FastConformer / Nemotron layer stack: one host call enqueues the whole fixed
 // kernel sequence of NemotronEncoder.forward's layer loop (oasr/models/nemotron/encoder.py:217-267, 542-583) on the
-// caller's stream -- per layer 17 launches (25 with an 8-bit kind) of this library's own C-ABI kernels: macaron FFN, Transformer-XL
+// caller's stream -- per layer 17 launches (21 with an 8-bit kind: the add + norm kernels also write the quantised
+// row for the Linear behind them) of this library's own C-ABI kernels: macaron FFN, Transformer-XL
 // relative-position attention (q projected once per global bias, position scores as one batched GEMM over heads,
 // one kernel for the relative shift + scale + chunked-limited window, head_dim 128 attention with that bias),
 // conv module (GLU GEMM, causal depthwise conv per segment, LayerNorm + SiLU, pointwise GEMM), second FFN, with the
@@ -128,24 +129,38 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
     }                                                                                                                 \
   } while (0)
 
+  // A Linear whose input h was produced (and, with an 8-bit kind, already quantised into w.q8 / w.qs) by the add + norm
+  // directly before it.
+#define FC_LINEAR_H(out, wt, bs, lay, qi, N, K, act, glu)                                                            \
+  do {                                                                                                                \
+    if (qk == 0) {                                                                                                    \
+      FC_LINEAR(out, w.h, wt, bs, lay, qi, N, K, act, glu);                                                           \
+    } else {                                                                                                          \
+      OB_REQUIRE((lay).q_w[qi] && (lay).q_s[qi], OASR_ERR_INVALID, "fastconformer_layers_packed: layer without 8-bit weight %d", qi); \
+      FC_STEP(oasr_b200_gemm_q8(out, w.q8, w.qs, (lay).q_w[qi], (lay).q_s[qi], bs, M, N, K, act, glu, qk, dt, stream)); \
+    }                                                                                                                 \
+  } while (0)
+  // add + norm into w.h, and with an 8-bit kind the quantised row for the Linear that follows
+#define FC_ADD_NORM(res_in_, y_, alpha_, mode_, wa, ba, wb, bb)                                                       \
+  FC_STEP(oasr_b200_add_norm_f32_q8(w.h, res, res_in_, y_, alpha_, mode_, wa, ba, wb, bb, M, C, eps, 0,                \
+                                    qk ? w.q8 : nullptr, qk ? w.qs : nullptr, qk, dt, stream))
+
   // the input rows (16-bit, or fp32 when rows_f32) start the fp32 residual stream; h = LN_ff1(x) of the first layer in
   // the same kernel
   float* res = w.res;
   if (rows_f32) {
-    FC_STEP(oasr_b200_add_norm_f32(w.h, res, static_cast<const float*>(rows), nullptr, 0.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b,
-                                   nullptr, nullptr, M, C, eps, 0, dt, stream));
+    FC_ADD_NORM(static_cast<const float*>(rows), nullptr, 0.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b, nullptr, nullptr);
   } else {
-    FC_STEP(oasr_b200_add_norm_f32(w.h, res, nullptr, rows, 1.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b, nullptr, nullptr, M, C, eps, 0,
-                                   dt, stream));
+    FC_ADD_NORM(nullptr, rows, 1.0, 0, ly[0].norm_ff1_w, ly[0].norm_ff1_b, nullptr, nullptr);
   }
   for (int64_t i = 0; i < L; ++i) {
     const oasr_b200_fastconformer_layer& l = ly[i];
     // macaron feed-forward: x += 0.5 * W2 silu(W1 h)
-    FC_LINEAR(w.a_ffn, w.h, l.ff1_w1, l.ff1_b1, l, 0, F, C, OASR_ACT_SWISH, 0);
+    FC_LINEAR_H(w.a_ffn, l.ff1_w1, l.ff1_b1, l, 0, F, C, OASR_ACT_SWISH, 0);
     FC_LINEAR(w.y, w.a_ffn, l.ff1_w2, l.ff1_b2, l, 1, C, F, OASR_ACT_NONE, 0);
-    FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 0.5, 0, l.norm_att_w, l.norm_att_b, nullptr, nullptr, M, C, eps, 0, dt, stream));
+    FC_ADD_NORM(res, w.y, 0.5, 0, l.norm_att_w, l.norm_att_b, nullptr, nullptr);
     // attention: [q+u | q+v | k | v] of every row, position scores (q+v) . rel_k^T per head, shifted bias, attention
-    FC_LINEAR(w.qkv4, w.h, l.qkv4_w, l.qkv4_b, l, 2, 4 * C, C, OASR_ACT_NONE, 0);
+    FC_LINEAR_H(w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * C, C, OASR_ACT_NONE, 0);
     FC_STEP(oasr_b200_gemm(w.rel_k, rel_table, l.rel_w, nullptr, Pp, C, C, OASR_ACT_NONE, dt, stream));
     FC_STEP(oasr_b200_bmm_strided(w.bd, w.qkv4 + C * es, w.rel_k, H, M, Pp, D, 4 * C, D, C, D, dt, stream));
     FC_STEP(oasr_b200_relshift_bias_packed(w.bias, w.bd, cu_seqlens, bias_offsets, num_segs, H, M, max_seg, Pp, scale, chunk,
@@ -154,20 +169,19 @@ int oasr_b200_fastconformer_layers_packed(const oasr_b200_fastconformer_model* m
                                           bias_offsets, 1, 1, cu_seqlens, cu_seqlens, num_segs, M, M, max_seg, H, H, D, scale, dt,
                                           stream));
     FC_LINEAR(w.y, w.att, l.o_w, l.o_b, l, 3, C, C, OASR_ACT_NONE, 0);
-    FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 1.0, 0, l.norm_conv_w, l.norm_conv_b, nullptr, nullptr, M, C, eps, 0, dt, stream));
+    FC_ADD_NORM(res, w.y, 1.0, 0, l.norm_conv_w, l.norm_conv_b, nullptr, nullptr);
     // conv module: pointwise + GLU, causal depthwise conv per segment, LayerNorm + SiLU, pointwise
-    FC_LINEAR(w.g, w.h, l.pw1_w, l.pw1_b, l, 4, C, C, OASR_ACT_NONE, 1);
+    FC_LINEAR_H(w.g, l.pw1_w, l.pw1_b, l, 4, C, C, OASR_ACT_NONE, 1);
     FC_STEP(oasr_b200_depthwise_conv1d_packed_causal(w.cv, w.g, l.dw_w, l.dw_b, cu_seqlens, num_segs, max_seg, C, m.kernel, -1, dt,
                                                      stream));
     FC_STEP(oasr_b200_layer_norm_activation(w.g, w.cv, l.conv_norm_w, l.conv_norm_b, M, C, 1e-5, OASR_ACT_SWISH, dt, stream));
     FC_LINEAR(w.y, w.g, l.pw2_w, l.pw2_b, l, 5, C, C, OASR_ACT_NONE, 0);
-    FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 1.0, 0, l.norm_ff2_w, l.norm_ff2_b, nullptr, nullptr, M, C, eps, 0, dt, stream));
+    FC_ADD_NORM(res, w.y, 1.0, 0, l.norm_ff2_w, l.norm_ff2_b, nullptr, nullptr);
     // second feed-forward, norm_out, then the next layer's first pre-norm in the same kernel
-    FC_LINEAR(w.a_ffn, w.h, l.ff2_w1, l.ff2_b1, l, 6, F, C, OASR_ACT_SWISH, 0);
+    FC_LINEAR_H(w.a_ffn, l.ff2_w1, l.ff2_b1, l, 6, F, C, OASR_ACT_SWISH, 0);
     FC_LINEAR(w.y, w.a_ffn, l.ff2_w2, l.ff2_b2, l, 7, C, F, OASR_ACT_NONE, 0);
     if (i + 1 < L) {
-      FC_STEP(oasr_b200_add_norm_f32(w.h, res, res, w.y, 0.5, 2, l.norm_out_w, l.norm_out_b, ly[i + 1].norm_ff1_w, ly[i + 1].norm_ff1_b,
-                                     M, C, eps, 0, dt, stream));
+      FC_ADD_NORM(res, w.y, 0.5, 2, l.norm_out_w, l.norm_out_b, ly[i + 1].norm_ff1_w, ly[i + 1].norm_ff1_b);
     } else {
       FC_STEP(oasr_b200_add_norm_f32(w.h, out, res, w.y, 0.5, 2, l.norm_out_w, l.norm_out_b, l.norm_out_w, l.norm_out_b, M, C, eps, 0,
                                      dt, stream));

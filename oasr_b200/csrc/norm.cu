@@ -7,6 +7,8 @@
 // [(c*32+l)*8, +8)).  Algorithmic bytes per row of width H in a 16-bit type:
 // LN 4H, add+LN+residual 8H (include/oasr/norm.cuh:28-93,396-484 in the
 // reference make 3-4 passes over the row from global memory instead).
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -368,7 +370,60 @@ struct AddNormArgs {
   int hidden;
   float eps;
   int split_out;        // h rows are [hi | lo] (2*hidden wide): x = hi + lo with both parts 16-bit
+  uint8_t* q_out;       // nullable: the h row once more in 8 bits, quantised per row exactly as quantize_rows(h) would
+  float* q_scale;       // its row scales
+  int q_kind;           // OASR_Q8_FP8_E4M3 / OASR_Q8_INT8
 };
+
+// The per-token quantisation of the row of h this warp has just produced: `v` holds the lane's final values (before
+// their rounding to T); scale = amax(|round_T(v)|) / qmax and q = cvt(round_T(v) / scale), the arithmetic of
+// quantize_rows_kernel (quant.cu) on the stored 16-bit row, so the two routes give the same bytes.
+template <typename T, int kChunks>
+__device__ __forceinline__ void quantise_row(const AddNormArgs& a, int64_t row, int lane, float (&v)[kChunks][kGran]) {
+  const int H = a.hidden;
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    if ((c * 32 + lane) * kGran < H) {
+#pragma unroll
+      for (int i = 0; i < kGran; ++i) {
+        v[c][i] = Elem<T>::to_f(Elem<T>::from_f(v[c][i]));
+        amax = fmaxf(amax, fabsf(v[c][i]));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  const float qmax = a.q_kind == OASR_Q8_FP8_E4M3 ? 448.f : 127.f;
+  const float sc = amax > 0.f ? amax / qmax : 1.f;
+  const float inv = 1.f / sc;
+  if (lane == 0) a.q_scale[row] = sc;
+  uint8_t* qr = a.q_out + row * H;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    const int e = (c * 32 + lane) * kGran;
+    if (e < H) {
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i += 2) {
+          const float x0 = v[c][h * 4 + i] * inv, x1 = v[c][h * 4 + i + 1] * inv;
+          uint32_t two;
+          if (a.q_kind == OASR_Q8_FP8_E4M3) {
+            two = __nv_cvt_float2_to_fp8x2(make_float2(x0, x1), __NV_SATFINITE, __NV_E4M3);
+          } else {
+            const int ia = max(-127, min(127, __float2int_rn(x0))), ib = max(-127, min(127, __float2int_rn(x1)));
+            two = (static_cast<uint32_t>(ia) & 0xffu) | ((static_cast<uint32_t>(ib) & 0xffu) << 8);
+          }
+          packed |= two << (8 * i);
+        }
+        w[h] = packed;
+      }
+      *reinterpret_cast<uint2*>(qr + e) = make_uint2(w[0], w[1]);
+    }
+  }
+}
 
 // h row stride and the split store: hi = round(x), lo = round(x - hi).
 template <typename T>
@@ -459,14 +514,15 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
     for (int c = 0; c < kChunks; ++c) {
       const int e = (c * 32 + lane) * kGran;
       if (e < H) {
-        float s8[kGran], t8[kGran], o8[kGran];
+        float s8[kGran], t8[kGran];
         load8_param(sc + e, s8);
         load8_param(sh + e, t8);
 #pragma unroll
-        for (int i = 0; i < kGran; ++i) o8[i] = fmaf(x[c][i], s8[i], t8[i]);
-        store_h(h, e, H, o8, split);
+        for (int i = 0; i < kGran; ++i) x[c][i] = fmaf(x[c][i], s8[i], t8[i]);
+        store_h(h, e, H, x[c], split);
       }
     }
+    if (a.q_out) quantise_row<T, kChunks>(a, row, lane, x);
     return;
   } else {
     row_layer_norm<kChunks>(x, H, lane, a.eps);
@@ -493,15 +549,16 @@ __global__ void __launch_bounds__(128) add_norm_f32_kernel(AddNormArgs a) {
       for (int c = 0; c < kChunks; ++c) {
         const int e = (c * 32 + lane) * kGran;
         if (e < H) {
-          float g[kGran], bb[kGran], o8[kGran];
+          float g[kGran], bb[kGran];
           load8_param(w2 + e, g);
           load8_param(b2 + e, bb);
 #pragma unroll
-          for (int i = 0; i < kGran; ++i) o8[i] = fmaf(x[c][i], g[i], bb[i]);
-          store_h(h, e, H, o8, split);
+          for (int i = 0; i < kGran; ++i) x[c][i] = fmaf(x[c][i], g[i], bb[i]);
+          store_h(h, e, H, x[c], split);
         }
       }
     }
+    if (a.q_out) quantise_row<T, kChunks>(a, row, lane, x);
   }
 }
 
@@ -528,7 +585,17 @@ extern "C" {
 int oasr_b200_add_norm_f32(void* h_out, float* res_out, const float* res_in, const void* y, double alpha, int mode,
                            const void* w_a, const void* b_a, const void* w_b, const void* b_b, int64_t rows,
                            int64_t hidden, double eps, int split_out, int dtype, void* stream) {
+  return oasr_b200_add_norm_f32_q8(h_out, res_out, res_in, y, alpha, mode, w_a, b_a, w_b, b_b, rows, hidden, eps, split_out,
+                                   nullptr, nullptr, 0, dtype, stream);
+}
+
+int oasr_b200_add_norm_f32_q8(void* h_out, float* res_out, const float* res_in, const void* y, double alpha, int mode,
+                              const void* w_a, const void* b_a, const void* w_b, const void* b_b, int64_t rows,
+                              int64_t hidden, double eps, int split_out, void* q_out, float* q_scale, int q_kind,
+                              int dtype, void* stream) {
   using namespace ob;
+  OB_REQUIRE(!q_out || (q_scale && (q_kind == OASR_Q8_FP8_E4M3 || q_kind == OASR_Q8_INT8) && !split_out && is_aligned(q_out, 16)),
+             OASR_ERR_INVALID, "add_norm_f32_q8: the 8-bit output needs its scales, a kind of 1 (fp8 e4m3) or 2 (int8), 16-byte alignment and split_out = 0");
   OB_REQUIRE(rows >= 0 && hidden > 0, OASR_ERR_INVALID, "add_norm_f32: bad shape");
   if (rows == 0) return OASR_OK;
   OB_REQUIRE(h_out && (res_in || y) && w_a && b_a, OASR_ERR_INVALID, "add_norm_f32: null pointer argument");
@@ -540,7 +607,8 @@ int oasr_b200_add_norm_f32(void* h_out, float* res_out, const float* res_in, con
                  (!y || is_aligned(y, 16)) && is_aligned(w_a, 16) && is_aligned(b_a, 16) &&
                  (!w_b || is_aligned(w_b, 16)) && (!b_b || is_aligned(b_b, 16)),
              OASR_ERR_ALIGN, "add_norm_f32: pointers must be 16-byte aligned");
-  AddNormArgs a{h_out, res_out, res_in, y, (float)alpha, w_a, b_a, w_b, b_b, rows, (int)hidden, (float)eps, split_out};
+  AddNormArgs a{h_out, res_out, res_in, y, (float)alpha, w_a, b_a, w_b, b_b, rows, (int)hidden, (float)eps, split_out,
+                static_cast<uint8_t*>(q_out), q_scale, q_kind};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
     if (mode == 0) return launch_add_norm<T, 0>(a, s);

@@ -29,6 +29,23 @@ def add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: O
               _stream(h_out))
 
 
+def add_norm_f32_q8(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: Optional[torch.Tensor],
+                    y: Optional[torch.Tensor], alpha: float, mode: int, w_a, b_a, w_b=None, b_b=None,
+                    eps: float = 1e-5, kind: int = 1):
+    """:func:`add_norm_f32` that also returns the rows of ``h`` in 8 bits for a following 8-bit GEMM:
+    ``(q uint8 (rows, hidden), scale fp32 (rows,))``, bit for bit what ``quant.quantize_rows(h_out, kind)`` gives
+    (``kind`` 1 = fp8 e4m3, 2 = int8), without the separate quantisation launch."""
+    _need_cuda(h_out, res_out, res_in, y)
+    hidden = h_out.size(-1)
+    rows = h_out.numel() // hidden
+    q = torch.empty(rows, hidden, dtype=torch.uint8, device=h_out.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=h_out.device)
+    _lib.call("oasr_b200_add_norm_f32_q8", _p(h_out), _p(res_out), _p(res_in), _p(y), float(alpha), int(mode), _p(w_a),
+              _p(b_a), _p(w_b), _p(b_b), rows, hidden, float(eps), 0, _p(q), _p(scale), int(kind), _DTYPE_ID[h_out.dtype],
+              _stream(h_out))
+    return q, scale
+
+
 def gemm_add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: Optional[torch.Tensor],
                       A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor], alpha: float, mode: int, w_a, b_a,
                       w_b=None, b_b=None, eps: float = 1e-5, split_out: bool = False) -> None:

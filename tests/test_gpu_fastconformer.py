@@ -307,7 +307,7 @@ def test_native_executor_with_8bit_linears_equals_the_composed_stack(quant):
     model.native = True
     assert ob.device_status() == 0
     assert torch.equal(rows_native, rows_composed)
-    assert launched >= 25 * cfg.layers          # 17 + 8 per-token quantisations per layer
+    assert launched >= 21 * cfg.layers          # 17 + 4 per-token quantisations per layer (the other four ride in add + norm)
     rows16, _ = FastConformerLayers(*args).forward_rows(hidden, lengths)
     cos = torch.nn.functional.cosine_similarity(rows_native.flatten(), rows16.flatten(), dim=0).item()
     print(f"{quant} native stack vs 16-bit stack: cosine {cos:.6f}")

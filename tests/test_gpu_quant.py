@@ -71,3 +71,29 @@ def test_quantised_encoder_reaches_the_cosine_gate_against_the_16_bit_run(mode):
     agree = (got[:, :cfg.vocab].argmax(-1) == ref[:, :cfg.vocab].argmax(-1)).float().mean().item()
     print(f"{mode}: cosine {cos:.6f}, argmax agreement with the bf16 run {agree:.4f}, max-abs {(got - ref)[:, :cfg.vocab].abs().max().item():.3e}")
     assert cos >= 0.999, cos
+
+
+@pytest.mark.parametrize("kind", [1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_add_norm_with_8bit_output_equals_add_norm_then_quantize_rows(kind, mode):
+    """oasr_b200_add_norm_f32_q8 writes, beside h, the row of h in 8 bits with its scale: the same bytes and scales
+    as quantize_rows(h), and h / the residual stream exactly as oasr_b200_add_norm_f32 leaves them."""
+    from oasr_b200 import fused, quant
+
+    rows, hidden = 333, 512
+    g = torch.Generator().manual_seed(5)
+    res = torch.randn(rows, hidden, generator=g).cuda()
+    y = torch.randn(rows, hidden, generator=g).cuda().bfloat16()
+    if mode == 1:
+        w_a, b_a = torch.rand(hidden, generator=g).cuda() + 0.5, torch.randn(hidden, generator=g).cuda()
+    else:
+        w_a, b_a = (torch.rand(hidden, generator=g).cuda() + 0.5).bfloat16(), torch.randn(hidden, generator=g).cuda().bfloat16()
+    w_b, b_b = (torch.rand(hidden, generator=g).cuda() + 0.5).bfloat16(), torch.randn(hidden, generator=g).cuda().bfloat16()
+    h1, r1 = torch.empty(rows, hidden, device="cuda", dtype=torch.bfloat16), torch.empty_like(res)
+    h2, r2 = torch.empty_like(h1), torch.empty_like(res)
+    fused.add_norm_f32(h1, r1, res, y, 0.5, mode, w_a, b_a, w_b if mode == 2 else None, b_b if mode == 2 else None)
+    q, s = fused.add_norm_f32_q8(h2, r2, res, y, 0.5, mode, w_a, b_a, w_b if mode == 2 else None, b_b if mode == 2 else None, kind=kind)
+    assert ob.device_status() == 0
+    assert torch.equal(h1, h2) and torch.equal(r1, r2)
+    q_ref, s_ref = quant.quantize_rows(h1, kind)
+    assert torch.equal(s, s_ref) and torch.equal(q, q_ref)
