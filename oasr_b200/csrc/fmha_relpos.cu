@@ -226,7 +226,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       start(ck);
       start(cv);
       uint32_t idle = 0;
-      while (ok && cv.it < n_items) {
+      while (ok && (ck.it < n_items || cv.it < n_items)) {   // either cursor may finish first
         bool progress = false;
         if (ck.it < n_items) {
           const int gg = ck.g, b = gg & 1;
@@ -250,7 +250,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             progress = true;
           }
         }
-        {
+        if (cv.it < n_items) {
           const int gg = cv.g, b = gg & 1;
           if (gg < 2 || ptx::mbar_test(&v_empty[b], ((gg - 2) >> 1) & 1u)) {   // P.V of tile gg - 2 finished
             ptx::mbar_expect_tx(&v_full[b], kVBytes);

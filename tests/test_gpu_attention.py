@@ -324,3 +324,45 @@ def test_planned_relpos_attention_equals_the_unplanned_order():
     assert n == len(expect) and set(zip(seg.tolist(), head.tolist(), qt.tolist())) == expect
     item_len = np.asarray(lens)[seg]
     assert (np.diff(item_len) <= 0).all()
+
+
+def test_relpos_attention_over_many_single_tile_items():
+    """A pack of short utterances (the sweep's shape): 700 segments of 1-60 frames, 8 heads, so every CTA of the
+    persistent kernel walks about twenty work items of ONE key tile each and its K and V cursors cross item
+    boundaries at every step.  Against the fp32 restatement, with and without the work list, twice (same bits), and
+    the device status stays clean (no role gave up a wait)."""
+    from oasr_b200 import fused
+
+    torch.manual_seed(9)
+    rng = np.random.default_rng(3)
+    lens = [int(x) for x in rng.integers(1, 61, size=700)]
+    H, D = 8, 64
+    d = H * D
+    total = sum(lens)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32).cuda()
+    qkv4 = (torch.randn(total, 4 * d) * 0.7).bfloat16().cuda()
+    pos = torch.randn(64, d).bfloat16().cuda()
+    scale = D ** -0.5
+    plan = fused.fmha_relpos_plan(cu, H, total)
+    outs = []
+    for pl in (plan, None, plan, None):
+        for _ in range(5):
+            outs.append(fused.fmha_varlen_relpos(qkv4, pos, cu, max(lens), H, scale, plan=pl))
+    assert ob.device_status() == 0
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    got = outs[0].float().cpu()
+    x = qkv4.float().cpu()
+    pp = pos.float().cpu()
+    for s in list(range(0, 700, 37)) + [699]:
+        n = lens[s]
+        a = int(cu[s])
+        qu = x[a:a + n, :d].view(n, H, D)
+        qv = x[a:a + n, d:2 * d].view(n, H, D)
+        k = x[a:a + n, 2 * d:3 * d].view(n, H, D)
+        v = x[a:a + n, 3 * d:].view(n, H, D)
+        p = pp[:n].view(n, H, D)
+        sc = (torch.einsum("qhd,khd->hqk", qu, k) + torch.einsum("qhd,khd->hqk", qv, p)) * scale
+        want = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v).reshape(n, d)
+        err = (got[a:a + n] - want).abs().max().item()
+        assert err < TOL, (s, n, err)
