@@ -379,7 +379,7 @@ def run_streaming(args):
 
 def run_sweep(args):
     """Config-5 style measurement (``--workload sweep``): 4096 utterances with log-normal lengths (median 6 s, clipped
-    1-30 s) through the headline Conformer, sorted by length, packed to <= 8192 frames per pack
+    1-30 s) through the headline Conformer, sorted by length, packed to <= ``--pack-frames`` (8192) frames per pack
     (oasr_b200.sharding.plan_packs, the reference's packing rule) and dealt to the ranks by cost
     (assign_packs); no collective on the data path, token lists gathered on the host at the end.  One "step" = the
     whole sweep.  ``--quant int8|fp8`` runs the Linear GEMMs on 8-bit operands (bf16 is the control)."""
@@ -404,7 +404,7 @@ def run_sweep(args):
     n_utts = 4096 if args.batch == 64 else args.batch
     rng = np.random.default_rng(2024)
     lengths = [int(round(100 * min(max(x, 1.0), 30.0))) for x in rng.lognormal(np.log(6.0), 0.6, size=n_utts)]
-    packs = sharding.plan_packs(lengths, 8192, 4)
+    packs = sharding.plan_packs(lengths, args.pack_frames, 4)
     mine = sharding.assign_packs(lengths, packs, world)[rank]
     g = torch.Generator(device=f"cuda:{local_rank}").manual_seed(7 + rank)
     batches = []
@@ -456,7 +456,7 @@ def run_sweep(args):
             "dtype": "bf16" if args.quant == "none" else f"{args.quant} Linear GEMMs (per-token / per-channel scales), bf16 elsewhere",
             "data": "synthetic",
             "config": {"workload": f"sweep of {n_utts} utterances, log-normal lengths (median 6 s, 1-30 s), conformer{args.layers}_d512, "
-                                   f"{len(packs)} packs of <= 8192 frames, cost-balanced over {world} rank(s), no collective",
+                                   f"{len(packs)} packs of <= {args.pack_frames} frames, cost-balanced over {world} rank(s), no collective",
                        "audio_seconds": audio},
             "e2e": {"value": audio / (float(t[1]) * 1e-3), "unit": "audio-s/s",
                     "api": "ConformerCTC.greedy_search_batches over the packs (features resident on the device)"},
@@ -545,6 +545,8 @@ def main():
                     help="streaming workload: enqueue every step's launches from the host instead of replaying the captured CUDA graph")
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"],
                     help="streaming workload: K/V page format (fp8 = e4m3 codes with per-head scales calibrated on four chunks)")
+    ap.add_argument("--pack-frames", type=int, default=8192,
+                    help="sweep workload: post-subsampling frame budget of a pack (the reference's max_packed_frames default is 8192)")
     ap.add_argument("--quant", default="none", choices=["none", "fp8", "int8"],
                     help="run the eight Linear GEMMs of every layer on 8-bit operands (not the headline dtype)")
     ap.add_argument("--batch", type=int, default=64, help="utterances per step (64 = the headline workload)")
