@@ -12,6 +12,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -45,18 +46,39 @@ class StreamingCache:
         self.extra_state: List[torch.Tensor] = []
         # physical pages are handed out in a random order (a seeded permutation)
         if seed is None:
-            order = list(range(self.num_blocks))
+            order = np.arange(self.num_blocks, dtype=np.int32)
         else:
-            order = torch.randperm(self.num_blocks, generator=torch.Generator().manual_seed(seed)).tolist()
-        self._free: List[int] = order[::-1]
-        self._blocks: List[List[int]] = [[] for _ in range(max_streams)]   # logical -> physical, per slot
-        self._frames: List[int] = [0] * max_streams                         # committed (cached) frames per slot
-        self._offset: List[int] = [0] * max_streams                         # encoder frames emitted per slot
+            order = torch.randperm(self.num_blocks, generator=torch.Generator().manual_seed(seed)).numpy().astype(np.int32)
+        # Host bookkeeping as arrays, so that a step over hundreds of streams is a handful of vectorised operations:
+        # a stack of free pages (the top is the next page handed out), per slot the logical -> physical page list
+        # (row of _table, first _nblk entries valid), the committed (cached) frames and the encoder frames emitted.
+        self._free_stack = order[::-1].copy()
+        self._nfree = self.num_blocks
+        self._table = np.zeros((max_streams, self.max_blocks), dtype=np.int32)
+        self._nblk = np.zeros(max_streams, dtype=np.int64)
+        self._frames = np.zeros(max_streams, dtype=np.int64)
+        self._offset = np.zeros(max_streams, dtype=np.int64)
+        self._cols = np.arange(self.max_blocks, dtype=np.int64)[None, :]
 
     # ---- host bookkeeping -------------------------------------------------------------------
+    @property
+    def _free(self) -> List[int]:
+        """The free pages, next one handed out last (introspection)."""
+        return self._free_stack[:self._nfree].tolist()
+
+    @property
+    def _blocks(self) -> List[List[int]]:
+        """Per slot the physical pages in logical order (introspection)."""
+        return [self._table[s, :self._nblk[s]].tolist() for s in range(self.max_streams)]
+
+    def _push_free(self, pages: np.ndarray) -> None:
+        n = pages.size
+        self._free_stack[self._nfree:self._nfree + n] = pages
+        self._nfree += n
+
     def reset_stream(self, slot: int) -> None:
-        self._free.extend(self._blocks[slot])
-        self._blocks[slot] = []
+        self._push_free(self._table[slot, :self._nblk[slot]].copy())
+        self._nblk[slot] = 0
         self._frames[slot] = 0
         self._offset[slot] = 0
         self.cnn_state[:, slot].zero_()
@@ -66,31 +88,49 @@ class StreamingCache:
     def prepare(self, slots: Sequence[int]):
         """Evict the oldest pages of every stream over its history cap, then give each stream the
         pages of the coming chunk.  Returns the device tensors one chunk forward needs:
-        ``(block_table (B, max_blocks) int32, cache_seqlens, total_seqlens, pos_start (B,) int32, slot_ids int64)``."""
-        rows, cached, total, pos = [], [], [], []
-        for s in slots:
-            while self._frames[s] > self.max_past:
-                self._free.append(self._blocks[s].pop(0))
-                self._frames[s] -= self.block_size
-            for _ in range(self.blocks_per_chunk):
-                if not self._free:
-                    raise RuntimeError("page pool exhausted")
-                self._blocks[s].append(self._free.pop())
-            row = self._blocks[s] + [self._blocks[s][-1]] * (self.max_blocks - len(self._blocks[s]))
-            rows.append(row)
-            cached.append(self._frames[s])
-            total.append(self._frames[s] + self.chunk)
-            pos.append(self._offset[s] - self._frames[s])
+        ``(block_table (B, max_blocks) int32, cache_seqlens, total_seqlens, pos_start (B,) int32, slot_ids int64)``.
+        ``slots`` names every stream at most once."""
+        s = np.asarray(slots, dtype=np.int64)
+        n = s.size
+        while True:                                   # oldest whole pages of the streams over their cap
+            over = s[self._frames[s] > self.max_past]
+            if over.size == 0:
+                break
+            self._push_free(self._table[over, 0].copy())
+            self._table[over, :-1] = self._table[over, 1:]
+            self._nblk[over] -= 1
+            self._frames[over] -= self.block_size
+        need = n * self.blocks_per_chunk
+        if need > self._nfree:
+            raise RuntimeError("page pool exhausted")
+        pages = self._free_stack[self._nfree - need:self._nfree][::-1].reshape(n, self.blocks_per_chunk)
+        self._nfree -= need
+        for j in range(self.blocks_per_chunk):
+            self._table[s, self._nblk[s] + j] = pages[:, j]
+        self._nblk[s] += self.blocks_per_chunk
+        # one int32 staging array: the table rows (unused tail entries repeat the stream's last page), then the
+        # cached / total frame counts and the position of the first key
+        mb = self.max_blocks
+        stage = np.empty(n * (mb + 3), dtype=np.int32)
+        last = (self._nblk[s] - 1)[:, None]
+        stage[:n * mb] = np.take_along_axis(self._table[s], np.minimum(self._cols, last), axis=1).reshape(-1)
+        frames = self._frames[s]
+        stage[n * mb:n * mb + n] = frames
+        stage[n * mb + n:n * mb + 2 * n] = frames + self.chunk
+        stage[n * mb + 2 * n:] = self._offset[s] - frames
         dev = self.device
-        i32 = dict(dtype=torch.int32)
-        return (torch.tensor(rows, **i32).to(dev, non_blocking=True), torch.tensor(cached, **i32).to(dev, non_blocking=True),
-                torch.tensor(total, **i32).to(dev, non_blocking=True), torch.tensor(pos, **i32).to(dev, non_blocking=True),
-                torch.tensor(list(slots), dtype=torch.int64).to(dev, non_blocking=True))
+        packed = torch.from_numpy(stage)
+        slot_ids = torch.from_numpy(s)
+        if dev.type == "cuda":
+            packed = packed.pin_memory().to(dev, non_blocking=True)
+            slot_ids = slot_ids.pin_memory().to(dev, non_blocking=True)
+        return (packed[:n * mb].view(n, mb), packed[n * mb:n * mb + n], packed[n * mb + n:n * mb + 2 * n],
+                packed[n * mb + 2 * n:], slot_ids)
 
     def commit(self, slots: Sequence[int]) -> None:
-        for s in slots:
-            self._frames[s] += self.chunk
-            self._offset[s] += self.chunk
+        s = np.asarray(slots, dtype=np.int64)
+        self._frames[s] += self.chunk
+        self._offset[s] += self.chunk
 
     def cached_frames(self, slot: int) -> int:
-        return self._frames[slot]
+        return int(self._frames[slot])
