@@ -114,7 +114,7 @@ int oasr_b200_set_tunable(const char* name, int value) {
     return OASR_OK;
   }
   if (name && std::strcmp(name, "dwconv_path") == 0) {
-    ob::g_dw_path = value != 0;
+    ob::g_dw_path = value;
     return OASR_OK;
   }
   return ob::set_error(OASR_ERR_INVALID, "unknown tunable '%s'", name ? name : "(null)");

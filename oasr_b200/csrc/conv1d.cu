@@ -14,7 +14,8 @@
 #include "sm100_ptx.cuh"
 
 namespace ob {
-int g_dw_path = 0;  // 0 = heuristic (register-streaming kernel where it applies); 1 = shared-memory tiled kernel; set through oasr_b200_set_tunable("dwconv_path")
+int g_dw_path = 2;  // "dwconv_path": 2 (default) = rolling register-window kernel for kernel sizes 9 / 15, the run-at-once streaming
+                    // kernel for the other sizes up to 15; 0 = the run-at-once kernel for all of them; 1 = shared-memory tiled kernel
 namespace {
 
 template <typename T>
@@ -411,6 +412,120 @@ __global__ void __launch_bounds__(256, 2) dwconv_stream_kernel(DwArgs a) {
   }
 }
 
+// Rolling form of the streaming kernel: a thread owns one channel pair over a run of kRollRuns * K consecutive output
+// frames.  The K-deep window of unpacked inputs and a K-deep queue of packed inputs requested K frames ahead both
+// rotate through statically indexed registers (the frame loop is unrolled by K), so a thread keeps 2K + K registers of
+// data instead of the whole run, every input frame is loaded once per run (halo (K - 1) / run instead of (K - 1) / 32),
+// and an output costs its K two-channel FMAs, one load, the unpack / pack, the activation and the store.
+constexpr int kRollRuns = 4;   // 2 and 4 measure the same (0.253-0.256 ms for the 12 launches of a step), 8 is slower (0.349)
+
+template <typename T, int K, bool kAffine, int kAct>
+__global__ void __launch_bounds__(128, 4) dwconv_roll_kernel(DwArgs a) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
+  ptx::grid_dep_wait();
+  constexpr int kRun = kRollRuns * K;
+  const int C = a.channels;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  if (c >= C) return;
+  const int64_t b = blockIdx.z;
+  int64_t in_row0, out_row0;
+  int TL, OL;
+  if (a.cu_seqlens) {
+    const int s0 = a.cu_seqlens[b], s1 = a.cu_seqlens[b + 1];
+    TL = s1 - s0; OL = TL; in_row0 = s0; out_row0 = s0;
+  } else {
+    TL = a.seq_len; OL = a.out_len; in_row0 = b * a.seq_len; out_row0 = b * a.out_len;
+  }
+  const int t0 = blockIdx.x * kRun;
+  if (t0 >= OL) return;
+  int fill_end = TL;
+  uint32_t fill = 0;
+  if (a.right_fill) {
+    fill_end = TL + a.fill_frames[b];
+    fill = pack_pair<T>(a.right_fill[c], a.right_fill[c + 1]);
+  }
+  const uint32_t* __restrict__ in = reinterpret_cast<const uint32_t*>(static_cast<const T*>(a.in) + in_row0 * C + c);
+  const int64_t row_u32 = C / 2;
+  auto fetch = [&](int ti) -> uint32_t {    // input frame ti of the segment: data, the fill value past its end, else zero
+    uint32_t v = 0;
+    if (ti >= 0 && ti < TL) v = __ldg(in + ti * row_u32);
+    else if (ti >= TL && ti < fill_end) v = fill;
+    return v;
+  };
+  float2 w[K];
+  {
+    const uint32_t* __restrict__ wp = reinterpret_cast<const uint32_t*>(static_cast<const T*>(a.weight) + c);
+#pragma unroll
+    for (int k = 0; k < K; ++k) w[k] = unpack_pair<T>(__ldg(wp + k * row_u32));
+  }
+  float2 bias = make_float2(0.f, 0.f);
+  if (a.bias) bias = unpack_pair<T>(__ldg(reinterpret_cast<const uint32_t*>(static_cast<const T*>(a.bias) + c)));
+  if constexpr (kAffine) {   // fold y * scale + shift into the taps and the bias
+    const float2 sc = *reinterpret_cast<const float2*>(a.post_scale + c);
+    const float2 sh = *reinterpret_cast<const float2*>(a.post_shift + c);
+#pragma unroll
+    for (int k = 0; k < K; ++k) w[k] = make_float2(w[k].x * sc.x, w[k].y * sc.y);
+    bias = make_float2(fmaf(bias.x, sc.x, sh.x), fmaf(bias.y, sc.y, sh.y));
+  }
+  const int first = t0 - a.pad_left;          // input frame under tap 0 of output t0
+  float2 x[K];                                 // x[s]: the unpacked frame whose index is congruent to s (mod K) from `first`
+  uint32_t q[K];                               // q[s]: the packed frame K positions after x[s]
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) x[k] = unpack_pair<T>(fetch(first + k));
+  q[K - 1] = fetch(first + K - 1);
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) q[k] = fetch(first + K + k);
+  uint32_t* __restrict__ out = reinterpret_cast<uint32_t*>(static_cast<T*>(a.out) + out_row0 * C + c);
+  const int t_end = min(OL, t0 + kRun);
+#pragma unroll 1
+  for (int base = t0; base < t_end; base += K) {
+#pragma unroll
+    for (int s = 0; s < K; ++s) {
+      // output base + s: window frames (base + s - t0) + 0 .. K-1 from `first`; the newest one sits in slot (s + K - 1) % K
+      const int slot = (s + K - 1) % K;
+      x[slot] = unpack_pair<T>(q[slot]);
+      q[slot] = fetch(first + (base - t0) + s + 2 * K - 1);
+      float2 acc = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) acc = __ffma2_rn(x[(s + k) % K], w[k], acc);
+      if constexpr (kAct == 1) {
+        const float2 h = __fmul2_rn(acc, make_float2(0.5f, 0.5f));
+        acc = __ffma2_rn(h, make_float2(tanh_approx(h.x), tanh_approx(h.y)), h);
+      } else if constexpr (kAct == 2) {
+        acc.x = apply_act_fast(acc.x, a.act);
+        acc.y = apply_act_fast(acc.y, a.act);
+      }
+      if (base + s < t_end) out[(base + s) * row_u32] = pack_pair<T>(acc.x, acc.y);
+    }
+  }
+}
+
+template <typename T, int K>
+int launch_roll(const DwArgs& a, int max_out_len, cudaStream_t s) {
+  if constexpr (sizeof(T) != 2) {
+    return set_error(OASR_ERR_DTYPE, "depthwise_conv1d: rolling kernel is 16-bit only");
+  } else {
+    const int pairs = a.channels / 2;
+    const int threads = pairs >= 128 ? 128 : ((pairs + 31) / 32) * 32;
+    constexpr int kRun = kRollRuns * K;
+    dim3 block(threads);
+    dim3 grid((max_out_len + kRun - 1) / kRun, (pairs + threads - 1) / threads, static_cast<unsigned>(a.batch));
+    const bool affine = a.post_scale != nullptr;
+    const int act = a.act == OASR_ACT_NONE ? 0 : (a.act == OASR_ACT_SWISH ? 1 : 2);
+    if (affine) {
+      if (act == 1) launch_pdl(dwconv_roll_kernel<T, K, true, 1>, grid, block, 0, s, a);
+      else if (act == 0) launch_pdl(dwconv_roll_kernel<T, K, true, 0>, grid, block, 0, s, a);
+      else launch_pdl(dwconv_roll_kernel<T, K, true, 2>, grid, block, 0, s, a);
+    } else {
+      if (act == 1) launch_pdl(dwconv_roll_kernel<T, K, false, 1>, grid, block, 0, s, a);
+      else if (act == 0) launch_pdl(dwconv_roll_kernel<T, K, false, 0>, grid, block, 0, s, a);
+      else launch_pdl(dwconv_roll_kernel<T, K, false, 2>, grid, block, 0, s, a);
+    }
+    return check_launch("depthwise_conv1d (rolling) kernel launch");
+  }
+}
+
 template <typename T, int K>
 int launch_stream(const DwArgs& a, int max_out_len, cudaStream_t s) {
   if constexpr (sizeof(T) != 2) {
@@ -497,7 +612,14 @@ int launch_dw(const DwArgs& a, int max_out_len, cudaStream_t s) {
                      (a.channels + kCB - 1) / kCB <= 65535;
   const bool stream = fast && sizeof(T) == 2 && is_aligned(a.in, 4) && is_aligned(a.out, 4) && is_aligned(a.weight, 4) &&
                       (!a.bias || is_aligned(a.bias, 4)) && (!a.post_scale || (is_aligned(a.post_scale, 8) && is_aligned(a.post_shift, 8))) &&
-                      (max_out_len + kST - 1) / kST <= 65535 && a.kernel_size <= 15 && g_dw_path == 0;
+                      (max_out_len + kST - 1) / kST <= 65535 && a.kernel_size <= 15 && g_dw_path != 1;
+  if (stream && g_dw_path == 2) {
+    switch (a.kernel_size) {
+      case 9: return launch_roll<T, 9>(a, max_out_len, s);
+      case 15: return launch_roll<T, 15>(a, max_out_len, s);
+      default: break;
+    }
+  }
   if (stream) {
     switch (a.kernel_size) {
       case 3: return launch_stream<T, 3>(a, max_out_len, s);

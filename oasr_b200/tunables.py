@@ -4,7 +4,8 @@
 ``lsm_path``: the CTC head - 0 (default) chooses by size, 1 the fused two-sweep kernel, 2 an fp32 logits GEMM followed by
 an in-place row log-softmax kernel (fp32 output only).
 ``gemm_pairs``: 1 runs large dense GEMMs on CTA pairs (tcgen05 cta_group::2), 0 (default) on single-CTA tiles.
-``dwconv_path``: 0 (default) uses the register-streaming depthwise conv kernel where it applies, 1 the shared-memory tiled one.
+``dwconv_path``: 2 (default) runs the depthwise conv of kernel size 9 / 15 on the rolling register-window kernel (other sizes
+up to 15 on the run-at-once register-streaming kernel), 0 all of them on the run-at-once kernel, 1 on the shared-memory tiled one.
 ``fmha_chunk_path``: 1 (default) runs paged rel-pos attention with <= 16 query frames on the warp-per-(stream, head)
 kernel, 0 always on the 128-row tcgen05 kernel.
 ``fmha_relpos_path``: 1 (default) runs packed relative-position attention on the two-CTAs-per-SM kernel, 0 on the general one.

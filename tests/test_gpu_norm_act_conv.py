@@ -230,3 +230,56 @@ def _front_end_case(C, lens, stencil):
     want = torch.cat([y2[b, :, :n].permute(1, 2, 0).reshape(n, -1) for b, n in enumerate(out_lens)])
     err = (got - want).abs().max().item()
     assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("K,causal", [(15, False), (9, True)])
+def test_packed_depthwise_conv_kernels_agree_with_each_other_and_with_fp32(K, causal):
+    """The rolling register-window kernel (default for kernel sizes 9 / 15) against the run-at-once kernel
+    (``dwconv_path`` 0) and an fp32 torch restatement, on ragged segments incl. ones shorter than the kernel, a run
+    boundary inside a segment (60 frames), folded BatchNorm + swish (non-causal form) and the padded-semantics fill."""
+    from oasr_b200 import fused, tunables
+
+    torch.manual_seed(11)
+    lens = [1, 7, 59, 60, 61, 120, 121, 333, 14, 15]
+    C = 512
+    total = sum(lens)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32).cuda()
+    x = torch.randn(total, C).bfloat16().cuda()
+    w = (torch.randn(K, C) * 0.3).bfloat16().cuda()
+    b = torch.randn(C).bfloat16().cuda()
+    sc, sh = (torch.rand(C) + 0.5).cuda(), torch.randn(C).cuda()
+    fill = torch.randn(C).cuda()
+    fill_frames = torch.tensor([min((K - 1) // 2, 3 + i % 5) for i in range(len(lens))], dtype=torch.int32).cuda()
+
+    def run():
+        if causal:
+            return fused.depthwise_conv1d_packed_causal(x, w, b, cu, max(lens), activation=-1).float()
+        return fused.depthwise_conv1d_packed(x, w, b, cu, max(lens), post_scale=sc, post_shift=sh, right_fill=fill,
+                                             fill_frames=fill_frames, activation=2).float()
+
+    outs = {}
+    for path in (2, 0):
+        tunables.set("dwconv_path", path)
+        try:
+            outs[path] = run()
+        finally:
+            tunables.set("dwconv_path", 2)
+    assert ob.device_status() == 0
+    assert (outs[2] - outs[0]).abs().max().item() < 4e-2      # two roundings to bf16 of nearly equal fp32 values
+    xf, wf = x.float().cpu(), w.float().cpu()
+    for s, n in enumerate(lens):
+        a = int(cu[s])
+        seg = xf[a:a + n]
+        if causal:
+            padded = torch.cat([torch.zeros(K - 1, C), seg])
+        else:
+            nf = int(fill_frames[s])
+            right = torch.cat([fill.cpu().bfloat16().float().expand(nf, C), torch.zeros((K - 1) // 2 - nf, C)])
+            padded = torch.cat([torch.zeros((K - 1) // 2, C), seg, right])
+        want = sum(padded[k:k + n] * wf[k] for k in range(K)) + b.float().cpu()
+        if not causal:
+            want = want * sc.cpu() + sh.cpu()
+            want = want * torch.sigmoid(want)
+        for path in (2, 0):
+            err = (outs[path][a:a + n].cpu() - want).abs().max().item()
+            assert err < 3e-2 * max(1.0, want.abs().max().item()), (path, s, n, err)
