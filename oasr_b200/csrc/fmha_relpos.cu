@@ -21,7 +21,8 @@
 // The two single-thread roles are event loops over two cursors each (K | pos and V refills; scores and P.V): whichever
 // operation has its inputs ready is issued, so scores run up to two tiles ahead of P.V, into the next item too, and
 // an item's output is written by the softmax threads inside the next item's first tile, while that item's last P.V
-// drains (55 -> 50 us); with the alternating deal (20-28 -> 22-26 key tiles per CTA) 45 us per launch.
+// drains (55 -> 50 us); with the alternating deal (20-28 -> 22-26 key tiles per CTA) 45 us per launch, 44 us without the
+// per-tile diagnostic stamps the softmax loop used to carry.
 // Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
 // once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
 // are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
@@ -70,7 +71,7 @@ struct Params {
   const int32_t* n_items;      // device count of `items`
   int natural_items;           // items == null: num_segs * H * qtiles, item i = (segment, head, query tile) in that order
   int qtiles;                  // query tiles of the longest segment
-  unsigned long long* trace;   // nullable diagnostics buffer: the CTA (0, 0, trace_seg) stamps its phases
+  unsigned long long* trace;   // nullable diagnostics buffer: CTA 0 stamps its start, every CTA its span, tile count and SM
   int trace_seg;
 };
 __device__ __forceinline__ void stamp(const Params& p, int slot) {
@@ -387,12 +388,9 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const int key0 = j * BKV;
       if (!ptx::mbar_wait(&s_full[b], (gg >> 1) & 1u, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      if (j == 0 && r == 0) stamp(p, 2);
-      if (j == 3 && r == 0) stamp(p, 50);
       uint32_t v[64];
       ptx::tmem_ld_32x64(tmem_base + lane_base + kColS + b * BKV, v);
       ptx::tmem_ld_wait();
-      if (j == 3 && r == 0) stamp(p, 51);
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&s_free[b]);          // the scores live in registers now: S[b] may take tile j+2
       const bool full = key0 + BKV <= kv_len;   // tiles inside the valid keys need no mask
@@ -411,7 +409,6 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       float tile_max = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
       tile_max *= p.scale_log2;   // the scale is positive
-      if (j == 3 && r == 0) stamp(p, 52);
       // Lazy rescale: the reference maximum moves only when this tile exceeds it by more than 2^kLazyLog2.
       float rescale = 1.f;
       bool moved = false;
@@ -441,7 +438,6 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const float2 a = __fadd2_rn(acc[0], acc[1]);
         row_sum = a.x + a.y;
       }
-      if (j == 3 && r == 0) stamp(p, 53);
       // P.V of tile j-1 has finished: P may be rewritten and O is stable (it is only touched here when the maximum moved)
       if (j >= 1 || pending) {
         if (!ptx::mbar_wait(po_done, static_cast<uint32_t>(gg - 1) & 1u, abort_flag)) { ok = false; break; }
@@ -460,7 +456,6 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           ptx::tc_fence_before_sync();
         }
       }
-      if (j == 3 && r == 0) stamp(p, 54);
       l_run = l_run * rescale + row_sum;
       // row r of P, K-major with the 128-byte swizzle: 16-byte chunk c (8 keys) sits at c ^ (r % 8)
       uint8_t* row_base = sP + r * 128;
@@ -469,10 +464,8 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         *reinterpret_cast<uint4*>(row_base + ((c ^ (r & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       }
-      if (j == 3 && r == 0) stamp(p, 55);
       ptx::fence_proxy_async_smem();
       ptx::mbar_arrive(p_full);
-      if (r == 0 && j < 40) stamp(p, 3 + j);
     }
     pending = ok;
     pending_l = l_run;
@@ -482,7 +475,6 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (ok && pending) {
       ok = ptx::mbar_wait(po_done, static_cast<uint32_t>(g - 1) & 1u, abort_flag);
       if (ok) write_out();
-      if (r == 0) stamp(p, 60);
     }
     if (p.trace != nullptr && r == 0) {   // diagnostics: this CTA's span and work
       p.trace[64 + blockIdx.x * 4 + 1] = static_cast<unsigned long long>(clock64());
