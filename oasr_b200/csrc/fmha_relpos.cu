@@ -9,8 +9,9 @@
 //   keys are walked in tiles of 64 (K | pos 16 KB, V 8 KB per stage, two stages),
 //   P has a single 16 KB buffer (a softmax thread waits for P.V of tile j-1 before it rewrites P for tile j; by
 //   then that short MMA has long finished, because the exponentials of tile j were computed in between),
-//   TMEM holds S[2] (2 x 64 columns) and ONE O (64 columns) that every P.V accumulates into = 192 of 256 columns,
-// i.e. 96 KB of shared memory and half of TMEM per CTA.
+//   TMEM holds S[2] (2 x 64 columns) and ONE O (64 columns + 16 that hold the row sum of P, see kIdescPV) that every
+//   P.V accumulates into = 208 of 256 columns,
+// i.e. 104 KB of shared memory (8 KB of it a constant block of ones) and half of TMEM per CTA.
 // PERSISTENT: the grid is two CTAs per SM and every CTA walks work items (segment, head, 128-row query tile) of a
 // list that holds the longest segments first (plan_kernel below, built on the device once per batch; without a list the
 // items are enumerated in (segment, head, tile) order), dealt in rounds of gridDim.x items, forwards and backwards in
@@ -26,9 +27,10 @@
 // Softmax per tile and row: ONE TMEM load of the 64 scores into registers (S is handed back to the MMA issuer at
 // once), running max with a LAZY rescale -- the reference maximum only moves, and O (in TMEM) and the running sum
 // are only rescaled, when the tile's maximum exceeds it by more than 2^8, so exponentials stay below 256 and the
-// common case costs nothing -- then exp2 (scale / subtract and the row sum as packed fp32x2 operations on tiles
-// 1.3k -> 0.8k clocks for the 64 exponentials of a thread; a share of them as a cubic on the FMA pipe measured
-// slower: 45.4 / 56.2 / 60.3 us per launch with none / one / two of every four), bf16/fp16 P into swizzled shared memory.
+// common case costs nothing -- then exp2 (scale / subtract as packed fp32x2 operations: 1.3k -> 0.8k clocks for the 64
+// exponentials of a thread; the row sum is taken by the tensor core: P.V runs with N = 80 against [V | ones],
+// 43.9 -> 43.3 us per launch; a share of the exponentials as a cubic on the FMA pipe measured slower: 45.4 / 56.2 /
+// 60.3 us per launch with none / one / two of every four), bf16/fp16 P into swizzled shared memory.
 // O leaves TMEM once per item, scaled by 1 / sum; the next item's first P.V waits until every row has read it.
 // K | pos of tile j+2 is requested as soon as Q.K^T of tile j has finished, V of tile j+2 when P.V of tile j has: the
 // two have separate stage barriers and separate cursors.
@@ -54,11 +56,13 @@ constexpr int kQBytes = 2 * 128 * 128;          // [q+u | q+v]: two atoms of 128
 constexpr int kKBytes = 2 * BKV * 128;          // [k | pos] per stage
 constexpr int kVBytes = BKV * 128;
 constexpr int kPBytes = BQ * 128;               // 128 rows x 64 keys
+constexpr int kOnesBytes = BKV * 128;           // a V-shaped block of ones: the P.V instruction's second block of 64 columns
 constexpr int kOffQ = 0, kOffK = kOffQ + kQBytes, kOffV = kOffK + 2 * kKBytes, kOffP = kOffV + 2 * kVBytes;
-constexpr int kOffBar = kOffP + kPBytes;
+constexpr int kOffOnes = kOffP + kPBytes;
+constexpr int kOffBar = kOffOnes + kOnesBytes;
 constexpr int kNumBars = 16;
 constexpr int kSmemDynamic = kOffBar + kNumBars * 8 + 16 + 1024;
-constexpr uint32_t kTmemCols = 256, kColS = 0, kColO = 128;
+constexpr uint32_t kTmemCols = 256, kColS = 0, kColO = 128, kColSum = kColO + D;   // O | 16 columns that each hold the row sum of P
 constexpr float kLazyLog2 = 8.f;   // rescale only when the row maximum grows by more than 2^8
 
 struct Params {
@@ -107,7 +111,11 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const __grid_constant__ CUtensorMap map_v, const Params p) {
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr uint32_t kIdescQK = ptx::umma_idesc_f16(kBf16, BQ, BKV, false, false);
-  constexpr uint32_t kIdescPV = ptx::umma_idesc_f16(kBf16, BQ, D, false, true);  // V is MN-major
+  // P.V with N = D + 16: columns D.. of the B operand come from a constant block of ones (the MN-major descriptor's
+  // distance between 64-column blocks points there), so the accumulator's columns D..D+15 each receive the row sum of
+  // the 16-bit P -- the sum the output is divided by leaves the tensor core with O instead of costing every softmax
+  // thread an add per pair of keys.
+  constexpr uint32_t kIdescPV = ptx::umma_idesc_f16(kBf16, BQ, D + 16, false, true);  // V is MN-major
   constexpr float kNegInf = -INFINITY;
 
   ptx::grid_dep_launch();   // no-ops unless launched with programmatic stream serialisation
@@ -150,6 +158,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint8_t* sK = smem + kOffK;
   uint8_t* sV = smem + kOffV;
   uint8_t* sP = smem + kOffP;
+  uint8_t* sOnes = smem + kOffOnes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;     // [2]  K | pos stage landed
@@ -180,6 +189,12 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     ptx::mbar_init(o_free, BQ);
     *abort_flag = 0;
     ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  {
+    const uint32_t one2 = kBf16 ? 0x3F803F80u : 0x3C003C00u;      // 1.0 | 1.0 in T
+    for (int i = threadIdx.x; i < kOnesBytes / 16; i += kThreads)
+      reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(one2, one2, one2, one2);
     ptx::fence_proxy_async_smem();
   }
   if (warp == 4) {
@@ -294,7 +309,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           const uint64_t adesc = ptx::smem_desc_kmajor_sw128(a_addr + kk * 32);
-          const uint64_t bdesc = ptx::smem_desc_mnmajor_sw128(b_addr + kk * 2048, BKV * 128, 1024);
+          const uint64_t bdesc = ptx::smem_desc_mnmajor_sw128(b_addr + kk * 2048, ptx::smem_u32(sOnes) - b_addr, 1024);
           ptx::umma_f16(d_tmem, adesc, bdesc, kIdescPV, (!first || kk != 0) ? 1u : 0u);
         }
         ptx::umma_commit(po_done);
@@ -351,17 +366,18 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // An item's output leaves TMEM inside the NEXT item's first tile, between that tile's exponentials and its P store
     // (the last P.V of the item finishes under them); the CTA's last item after the loop.
     bool pending = false;          // an item whose O has not been written out yet
-    float pending_l = 0.f;
     T* pending_row = nullptr;      // nullptr: the row lies past the segment's end
     auto write_out = [&]() {       // O is stable: P.V of the item's last tile has been waited for
       ptx::tc_fence_after_sync();
-      uint32_t o[64];
+      uint32_t o[64], sm[16];
       ptx::tmem_ld_32x64(t_o, o);
+      ptx::tmem_ld_32x16(t_o + D, sm);
       ptx::tmem_ld_wait();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(o_free);    // O is in registers: the next item's first P.V may overwrite it
+      ptx::mbar_arrive(o_free);    // O and the row sum are in registers: the next item's first P.V may overwrite them
       if (pending_row != nullptr) {
-        const float inv = pending_l > 0.f ? 1.f / pending_l : 0.f;
+        const float l = __uint_as_float(sm[0]);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
         for (int c = 0; c < D; c += 8) {
           uint4 w;
@@ -382,7 +398,7 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int kv_len = w.kv_len, nkv = w.nkv;
     const bool row_ok = r < min(BQ, kv_len - w.q0);
     T* out = static_cast<T*>(p.out) + (static_cast<int64_t>(w.row0 + w.q0) * p.H + w.h) * D;
-    float m_run = kNegInf, l_run = 0.f;   // m_run: the reference maximum the exponentials, l_run and O are relative to
+    float m_run = kNegInf;   // the reference maximum the exponentials, O and the row sums (in TMEM) are relative to
     for (int j = 0; ok && j < nkv; ++j) {
       const int gg = g + j, b = gg & 1;
       const int key0 = j * BKV;
@@ -421,22 +437,16 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       // exponentiate, sum, round
       uint32_t packed[32];
-      float row_sum = 0.f;
       {
-        // every exponential on the MUFU unit: scale / subtract and the row sum as packed fp32x2 operations (masked
-        // keys carry -inf and come out as exactly 0)
+        // every exponential on the MUFU unit, scale / subtract as packed fp32x2 operations (masked keys carry -inf and
+        // come out as exactly 0); the row sums are taken by the tensor core (see kIdescPV)
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
         const float2 nm2 = make_float2(-m_run, -m_run);
-        float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
-          const float2 e = make_float2(ex2_fast(x.x), ex2_fast(x.y));
-          acc[(i >> 1) & 1] = __fadd2_rn(acc[(i >> 1) & 1], e);
-          packed[i / 2] = pack2<T>(e.x, e.y);
+          packed[i / 2] = pack2<T>(ex2_fast(x.x), ex2_fast(x.y));
         }
-        const float2 a = __fadd2_rn(acc[0], acc[1]);
-        row_sum = a.x + a.y;
       }
       // P.V of tile j-1 has finished: P may be rewritten and O is stable (it is only touched here when the maximum moved)
       if (j >= 1 || pending) {
@@ -452,11 +462,16 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           for (int i = 0; i < 64; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * rescale);
           ptx::tmem_st_32x32(t_o, reinterpret_cast<const uint32_t(&)[32]>(o[0]));
           ptx::tmem_st_32x32(t_o + 32, reinterpret_cast<const uint32_t(&)[32]>(o[32]));
+          uint32_t sm[16];                       // the running row sum is relative to the same maximum
+          ptx::tmem_ld_32x16(t_o + D, sm);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sm[i] = __float_as_uint(__uint_as_float(sm[i]) * rescale);
+          ptx::tmem_st_32x16(t_o + D, sm);
           ptx::tmem_st_wait();
           ptx::tc_fence_before_sync();
         }
       }
-      l_run = l_run * rescale + row_sum;
       // row r of P, K-major with the 128-byte swizzle: 16-byte chunk c (8 keys) sits at c ^ (r % 8)
       uint8_t* row_base = sP + r * 128;
 #pragma unroll
@@ -468,7 +483,6 @@ fmha_relpos64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       ptx::mbar_arrive(p_full);
     }
     pending = ok;
-    pending_l = l_run;
     pending_row = row_ok ? out + static_cast<int64_t>(r) * out_ld : nullptr;
     g += nkv;
     }   // items
