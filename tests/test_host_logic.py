@@ -49,3 +49,54 @@ def test_streaming_cache_bookkeeping_on_cpu():
     assert len(c._free) == free_before + 3 and c.cached_frames(2) == 0
     with pytest.raises(ValueError):
         StreamingCache(1, 2, 64, 128, 15, 1, 32, chunk_frames=24, block_size=16, device="cpu")
+
+
+def test_streaming_cache_invariants_under_random_batches_on_cpu():
+    """The vectorised page bookkeeping over random subsets of streams, two pages per chunk, resets in between: every
+    physical page is held by exactly one stream or the free list, a stream holds the pages of its capped history plus
+    the coming chunk in logical order, the returned rows repeat the last page in their unused tail, and an exhausted
+    pool is refused before anything is handed out."""
+    import numpy as np
+    import torch
+
+    from oasr_b200.streaming import StreamingCache
+
+    rng = np.random.default_rng(5)
+    S, bs, chunk, max_past = 12, 8, 16, 40
+    c = StreamingCache(num_layers=1, heads=2, head_dim=64, d_model=128, conv_kernel=15, max_streams=S, max_past_frames=max_past,
+                       chunk_frames=chunk, block_size=bs, device="cpu", dtype=torch.float32, seed=11)
+    assert c.blocks_per_chunk == 2 and c.max_blocks == 5 + 2
+    frames = [0] * S            # a plain-Python model of the committed history and the emitted frames
+    emitted = [0] * S
+    for step in range(200):
+        if step % 17 == 5:
+            s = int(rng.integers(S))
+            c.reset_stream(s)
+            frames[s] = emitted[s] = 0
+        slots = sorted(rng.choice(S, size=int(rng.integers(1, S + 1)), replace=False).tolist())
+        table, cached, total, pos, ids = c.prepare(slots)
+        for s in slots:
+            while frames[s] > max_past:
+                frames[s] -= bs
+        assert ids.tolist() == slots
+        assert cached.tolist() == [frames[s] for s in slots]
+        assert total.tolist() == [frames[s] + chunk for s in slots]
+        assert pos.tolist() == [emitted[s] - frames[s] for s in slots]
+        blocks, free = c._blocks, c._free
+        held = [p for b in blocks for p in b]
+        assert len(set(held)) == len(held) and not (set(held) & set(free)) and len(held) + len(free) == c.num_blocks
+        for row, s in zip(table.tolist(), slots):
+            n = len(blocks[s])
+            assert n == (frames[s] + bs - 1) // bs + c.blocks_per_chunk
+            assert row[:n] == blocks[s] and all(x == blocks[s][-1] for x in row[n:])
+        c.commit(slots)
+        for s in slots:
+            frames[s] += chunk
+            emitted[s] += chunk
+    # exhaustion: a pool with too few pages refuses the step and keeps its state
+    small = StreamingCache(1, 2, 64, 128, 15, 2, max_past, chunk_frames=chunk, block_size=bs, device="cpu", dtype=torch.float32)
+    small._nfree = 3                      # fewer than the four pages two streams need
+    before = (small._nfree, small._nblk.copy())
+    with pytest.raises(RuntimeError, match="exhausted"):
+        small.prepare([0, 1])
+    assert small._nfree == before[0] and (small._nblk == before[1]).all()
