@@ -690,10 +690,12 @@ def main():
                     gemm[f] += v[f]
         step_total = total_ms / args.steps if dist is None else float(np.mean(step_ms))
         achieved = gemm["flops"] / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
-        # flops the kernels issue beyond the algorithmic 2*M*N*K: the query block of the fused projection is computed
-        # twice ([Wq; Wq; Wk; Wv], once per positional bias): 2*M*d*d per layer
+        # flops the kernels issue beyond the algorithmic 2*M*N*K: with the 8-bit kinds (or the qkv_dup tunable off) the
+        # query block of the fused projection is computed twice ([Wq; Wq; Wk; Wv], once per positional bias), 2*M*d*d
+        # per layer; the 16-bit path computes it once and stores it twice (oasr_b200_gemm_dup_first)
         d_model, ffn = cfg.d_model, cfg.ffn
-        issued = gemm["flops"] + 2.0 * pk_rows * d_model * d_model * cfg.layers
+        dup_issued = args.quant != "none" or any(t.startswith("qkv_dup=0") for t in (args.tunable or [])) or d_model % 256 != 0
+        issued = gemm["flops"] + (2.0 * pk_rows * d_model * d_model * cfg.layers if dup_issued else 0.0)
         # peak: the burst figure when the SM clock sampled during the timed region is in the burst regime (>= 0.9 of the
         # maximum), the sustained figure otherwise; both fractions are printed
         burst = bool(clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.9 * clocks["sm_max_mhz"])

@@ -384,6 +384,15 @@ OASR_API int oasr_b200_subsample_conv2(void* out, const void* x1, const void* w2
 OASR_API int oasr_b200_gemm(void* D, const void* A, const void* B, const void* bias /*nullable*/,
                             int64_t M, int64_t N, int64_t K, int activation, int dtype,
                             void* stream);
+/* D[M, N + dup_cols] from A[M,K] . B[N,K]^T (no reference counterpart: it serves the fused q/q/k/v projection,
+ * oasr/layers/attention/attention.py:323-386, whose two query blocks q+u and q+v differ only in their bias): the
+ * first dup_cols columns of the product are stored twice, at output columns [0, dup_cols) and [dup_cols, 2*dup_cols),
+ * the remaining columns after them; bias (16-bit, N + dup_cols entries, nullable) is indexed by OUTPUT column, so the
+ * two copies carry different biases.  The result equals oasr_b200_gemm with the first dup_cols rows of B repeated, bit
+ * for bit, at three quarters of the products.  N and dup_cols multiples of 256 (oasr_b200_gemm_dup_first_supported). */
+OASR_API int oasr_b200_gemm_dup_first_supported(int64_t N, int64_t K, int64_t dup_cols);
+OASR_API int oasr_b200_gemm_dup_first(void* D, const void* A, const void* B, const void* bias /*nullable*/,
+                                      int64_t M, int64_t N, int64_t K, int64_t dup_cols, int dtype, void* stream);
 /* 8-bit operand kinds of the GEMM (no reference counterpart: the reference has no quantised path,
  * oasr/layers/linear.py:7 only names a future one).  D (M,N) 16-bit =
  * act( (A_q . B_q^T) * a_scale[m] * b_scale[n] + bias[n] ), A_q (M,K) and B_q (N,K) one byte per

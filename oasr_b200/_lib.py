@@ -47,9 +47,11 @@ _SIGNATURES = {
     "oasr_b200_add_rms_norm_residual": [P, P, P, P, P, P, I, I, c_double, c_double, c_int, P],
     "oasr_b200_batch_norm": [P, P, P, P, P, P, I, I, c_double, c_int, c_int, P],
     "oasr_b200_add_norm_f32": [P, P, P, P, c_double, c_int, P, P, P, P, I, I, c_double, c_int, c_int, P],
+    "oasr_b200_gemm_dup_first": [P, P, P, P, I, I, I, I, c_int, P],
     "oasr_b200_add_norm_f32_q8": [P, P, P, P, c_double, c_int, P, P, P, P, I, I, c_double, c_int, P, P, c_int, c_int, P],
     "oasr_b200_gemm_add_norm_f32": [P, P, P, P, P, P, I, I, I, c_double, c_int, P, P, P, P, c_double, c_int, c_int, P],
     "oasr_b200_gemm_add_norm_supported": [I, I],
+    "oasr_b200_gemm_dup_first_supported": [I, I, I],
     "oasr_b200_ctc_greedy_collapse": [P, P, P, P, P, I, I, I, P],
     "oasr_b200_fbank": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, c_double, c_double, P],
     "oasr_b200_trace_buffer": [P],

@@ -66,6 +66,7 @@ int g_pdl = 1;  // programmatic stream serialisation for the kernels launched th
                 // graph-replayed streaming step (2.91 ms) and on the FastConformer step (51.5 ms)
 extern int g_fmha_chunk_path;
 extern int g_fused_addnorm;
+extern int g_qkv_dup;
 namespace conv1_mma { extern int g_enabled; }
 
 }  // namespace ob
@@ -94,6 +95,10 @@ int oasr_b200_set_tunable(const char* name, int value) {
   }
   if (name && std::strcmp(name, "fmha_relpos_path") == 0) {
     ob::g_fmha_relpos_path = value != 0;
+    return OASR_OK;
+  }
+  if (name && std::strcmp(name, "qkv_dup") == 0) {
+    ob::g_qkv_dup = value != 0;
     return OASR_OK;
   }
   if (name && std::strcmp(name, "pdl") == 0) {

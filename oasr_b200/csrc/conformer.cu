@@ -81,6 +81,7 @@ bool g_prof_on = false;
 // (oasr_b200_gemm_add_norm_f32) where the model width allows it and the batch fills the GPU; 2: whenever the width
 // allows it; 0: gemm + add_norm_f32 as two kernels.
 int g_fused_addnorm = 1;
+int g_qkv_dup = 1;   // "qkv_dup": 1 = the q/q/k/v projection computes its query block once and stores it twice (two biases)
 namespace {
 std::vector<ProfRecord> g_prof;
 
@@ -221,6 +222,7 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
   // The fused kernel gives one 256-row tile to a pair of SMs and cannot overlap a tile's epilogue with the next main
   // loop, so it pays only when its tiles fill the GPU: at least 80 % of the SM pairs busy in every round (measured on
   // B200, d 512: 16.7k rows, 66 of 74 pairs, fused 7.07 against 7.30 ms per step; 8.3k rows, 32 pairs, 4.69 against 4.34).
+  const bool qkv_dup = qk == 0 && g_qkv_dup != 0 && M >= 128 && oasr_b200_gemm_dup_first_supported(3 * d, d, d) != 0;
   const int64_t pairs = (M + 255) / 256, slots = sm_count() / 2;
   const int64_t rounds = (pairs + slots - 1) / slots;
   const bool fills = g_fused_addnorm == 2 || pairs * 5 >= rounds * slots * 4;
@@ -280,7 +282,11 @@ int oasr_b200_conformer_encode_packed(const oasr_b200_conformer_model* model, co
     OB_LINEAR_ADDNORM("ffn_w2", 2.0 * M * m.ffn * d, w.h, w.res, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, m.ffn, 0.5, 0, l.norm_mha_w,
                       l.norm_mha_b, nullptr, nullptr, m.eps, 0);
     // relative-position self-attention
-    OB_LINEAR_H("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, OASR_ACT_NONE, 0);
+    if (qkv_dup) {   // [Wq;Wk;Wv] are rows d.. of [Wq;Wq;Wk;Wv]: the query block once, stored as q+u and q+v
+      OB_STEP("gemm qkv4", 2.0 * M * 3 * d * d, oasr_b200_gemm_dup_first(w.qkv4, w.h, static_cast<const uint8_t*>(l.qkv4_w) + d * d * 2, l.qkv4_b, M, 3 * d, d, d, dt, stream));
+    } else {
+      OB_LINEAR_H("qkv4", 2.0 * M * 3 * d * d /* algorithmic: the query block is issued twice */, w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, OASR_ACT_NONE, 0);
+    }
     OB_STEP("fmha_varlen_relpos", 0, oasr_b200_fmha_varlen_relpos_planned(w.att, w.qkv4, w.pos + i * d * 2, max_seg, L * d, cu_seqlens, num_segs,
                                          max_seg, M, m.heads, scale, att_plan, dt, stream));
     OB_LINEAR_ADDNORM("attn_out", 2.0 * M * d * d, w.h, w.res, w.att, l.out_w, l.out_b, l, 3, d, 1.0, 1, l.norm_conv_scale,
@@ -403,6 +409,7 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
   const double scale = 1.0 / std::sqrt(64.0);
   const oasr_b200_conformer_layer* ly = m.layers;
 
+  const bool qkv_dup = qk == 0 && g_qkv_dup != 0 && B * T >= 128 && oasr_b200_gemm_dup_first_supported(3 * m.d_model, m.d_model, m.d_model) != 0;
   // One Linear over `R` rows: 16-bit GEMM, or per-token quantisation of the input followed by the 8-bit GEMM on the
   // layer's pre-quantised weight `qi` (order of oasr_b200_conformer_layer::q_w), as in the offline executor.
 #define OB_CHUNK_LINEAR(label, fl, out, in, wt, bs, lay, qi, R, N, K, act, glu)                                       \
@@ -435,7 +442,11 @@ int oasr_b200_conformer_chunk_paged(const oasr_b200_conformer_model* model, cons
     OB_CHUNK_LINEAR("ffn_w2", 2.0 * M * m.ffn * d, w.y, w.a_ffn, l.ffm_w2, l.ffm_b2, l, 1, M, d, m.ffn, OASR_ACT_NONE, 0);
     OB_ADD_NORM(w.h, w.res, w.res, w.y, 0.5, 0, l.norm_mha_w, l.norm_mha_b, nullptr, nullptr, m.eps, 0);
     // attention: project, append the chunk's keys/values to the pages, attend over cache + chunk
-    OB_CHUNK_LINEAR_H("qkv4", 2.0 * M * 3 * d * d, w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, OASR_ACT_NONE);
+    if (qkv_dup) {
+      OB_STEP("gemm qkv4", 2.0 * M * 3 * d * d, oasr_b200_gemm_dup_first(w.qkv4, w.h, static_cast<const uint8_t*>(l.qkv4_w) + d * d * 2, l.qkv4_b, M, 3 * d, d, d, dt, stream));
+    } else {
+      OB_CHUNK_LINEAR_H("qkv4", 2.0 * M * 3 * d * d, w.qkv4, l.qkv4_w, l.qkv4_b, l, 2, 4 * d, OASR_ACT_NONE);
+    }
     if (kv_scales) {   // fp8 pages: per-head scales of this layer, K then V
       const float* ks = kv_scales + static_cast<int64_t>(i) * 2 * m.heads;
       const float* vs = ks + m.heads;

@@ -57,6 +57,7 @@ struct Params {
   int lsm_passes;         // kEpiLsm: 2 = statistics sweep + normalised-output sweep; 1 = statistics only (argmax, no output)
   int32_t* argmax;        // kEpiLsm: nullable
   uint32_t* status;       // device status word (nullable)
+  int dup_cols;           // kDup: output columns [0, dup_cols) of the GEMM are stored twice (see gemm_body)
   // kSchedConv (3x3 / stride-2 convolution as an implicit GEMM over a parity-split NHWC input):
   // 8-bit operand kinds: D = (A_q . B_q^T) * a_scale[row] * b_scale[col] (+ bias)
   const float* a_scale;   // [M] per-row (per-token) scales of A
@@ -245,7 +246,7 @@ constexpr int threads_for() { return 64 + 32 * kEpiWarps * epi_groups<kSched, kE
 // kKind: 0 = 16-bit operands of type T; 1 = fp8 e4m3 operands (kind::f8f6f4, fp32 accumulators); 2 = signed
 // int8 operands (kind::i8, int32 accumulators).  For the 8-bit kinds T is the OUTPUT type, a K block is 128
 // elements (the same 128 bytes per shared-memory row) and the epilogue multiplies by the row and column scales.
-template <typename T, int BN, int kStages, int kSched, int kEpi, int kCtas, int kKind = 0>
+template <typename T, int BN, int kStages, int kSched, int kEpi, int kCtas, int kKind = 0, bool kDup = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                           const CUtensorMap& tmap_d, const Params& p) {
   using S = Smem<BN, kStages, kCtas>;
@@ -520,6 +521,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
         const int nchunks = (min(BN, p.N - t.n0) + 63) / 64;
         // one 64-column TMEM load per chunk; the next chunk's load is issued as soon as this chunk has been
         // converted, under the staging and the stores
+        // kDup (the fused q/q/k/v projection): the first dup_cols columns of the product are stored twice, at output
+        // columns [0, dup_cols) and [dup_cols, 2*dup_cols), each copy with the bias of its OUTPUT column; the other
+        // columns move right by dup_cols.  bias is indexed by output column; tiles do not straddle dup_cols.
+        const int shift = (kDup && t.n0 >= p.dup_cols) ? p.dup_cols : 0;
+        const bool twice = kDup && t.n0 < p.dup_cols;
         auto store_tile = [&](auto act_c) {
           uint32_t r[64], w[32];
           int ci = grp;
@@ -528,12 +534,21 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmap_a, const CUten
           for (; ci < nchunks; ci += kGroups) {
             const int c0 = ci * 64;
             ptx::tmem_ld_wait();
-            finish32(reinterpret_cast<const uint32_t(&)[32]>(r[0]), w, std::integral_constant<int, 0>{}, act_c, t.n0 + c0, bias);
-            finish32(reinterpret_cast<const uint32_t(&)[32]>(r[32]), w, std::integral_constant<int, 1>{}, act_c, t.n0 + c0 + 32, bias);
+            finish32(reinterpret_cast<const uint32_t(&)[32]>(r[0]), w, std::integral_constant<int, 0>{}, act_c, t.n0 + c0, bias ? bias + shift : bias);
+            finish32(reinterpret_cast<const uint32_t(&)[32]>(r[32]), w, std::integral_constant<int, 1>{}, act_c, t.n0 + c0 + 32, bias ? bias + shift : bias);
+            if constexpr (kDup && kGroups == 2) {
+              if (twice) {
+                uint32_t w2[32];
+                finish32(reinterpret_cast<const uint32_t(&)[32]>(r[0]), w2, std::integral_constant<int, 0>{}, act_c, t.n0 + c0, bias ? bias + p.dup_cols : bias);
+                finish32(reinterpret_cast<const uint32_t(&)[32]>(r[32]), w2, std::integral_constant<int, 1>{}, act_c, t.n0 + c0 + 32, bias ? bias + p.dup_cols : bias);
+                stage32_and_store(w2, t.n0 + c0 + p.dup_cols, t);
+                if (t.n0 + c0 + 32 < p.N) stage32_and_store(w2 + 16, t.n0 + c0 + 32 + p.dup_cols, t);
+              }
+            }
             if (ci + kGroups < nchunks) ptx::tmem_ld_32x64(t_acc + (ci + kGroups) * 64, r);
             if constexpr (kGroups == 2) {
-              stage32_and_store(w, t.n0 + c0, t);
-              if (t.n0 + c0 + 32 < p.N) stage32_and_store(w + 16, t.n0 + c0 + 32, t);
+              stage32_and_store(w, t.n0 + c0 + shift, t);
+              if (t.n0 + c0 + 32 < p.N) stage32_and_store(w + 16, t.n0 + c0 + 32 + shift, t);
             } else {
               stage_and_store(w, t.n0 + c0, t);
             }
@@ -825,6 +840,13 @@ __global__ void __launch_bounds__(threads_for<kSched, kEpi>(), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_d, const Params p) {
   gemm_body<T, BN, kStages, kSched, kEpi, 1>(tmap_a, tmap_b, tmap_d, p);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(threads_for<kSchedDense, kEpiStore>(), 1)
+gemm_tcgen05_dup_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_d, const Params p) {
+  gemm_body<T, 256, 4, kSchedDense, kEpiStore, 1, 0, true>(tmap_a, tmap_b, tmap_d, p);
 }
 
 template <typename T, int BN, int kStages, int kEpi, int kKind>
@@ -1233,6 +1255,56 @@ int oasr_b200_gemm(void* D, const void* A, const void* B, const void* bias, int6
   pr.p.M = (int)M; pr.p.N = (int)N; pr.p.K = (int)K; pr.p.batch = 1;
   pr.p.D = D; pr.p.bias = bias; pr.p.act = activation; pr.p.alpha = 1.f;
   return run<kSchedDense, kEpiStore>(pr, dtype, s);
+}
+
+int oasr_b200_gemm_dup_first_supported(int64_t N, int64_t K, int64_t dup_cols) {
+  return N > 0 && K >= 16 && K % 8 == 0 && dup_cols > 0 && dup_cols <= N && N % 256 == 0 && dup_cols % 256 == 0 ? 1 : 0;
+}
+
+int oasr_b200_gemm_dup_first(void* D, const void* A, const void* B, const void* bias, int64_t M, int64_t N, int64_t K,
+                             int64_t dup_cols, int dtype, void* stream) {
+  using namespace ob;
+  using namespace ob::gemm;
+  if (int rc = validate_common("gemm_dup_first", D, A, B, bias, M, N, K)) return rc;
+  OB_REQUIRE(oasr_b200_gemm_dup_first_supported(N, K, dup_cols) != 0, OASR_ERR_UNSUPPORTED,
+             "gemm_dup_first: N and dup_cols must be multiples of 256 with 0 < dup_cols <= N (got N=%lld dup_cols=%lld)",
+             (long long)N, (long long)dup_cols);
+  if (M == 0) return OASR_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Problem pr{};
+  pr.sched = kSchedDense; pr.epi = kEpiStore;
+  pr.M = M; pr.N = N; pr.K = K; pr.batch = 1; pr.A = A; pr.B = B;
+  Params& p = pr.p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
+  p.D = D; p.bias = bias; p.act = OASR_ACT_NONE; p.alpha = 1.f;
+  p.dup_cols = (int)dup_cols;
+  p.status = device_status_ptr();
+  p.num_m_tiles = static_cast<int>((M + BM - 1) / BM);
+  p.num_n_tiles = static_cast<int>(N / 256);
+  p.num_k_blocks = static_cast<int>((K + BK - 1) / BK);
+  return OB_DISPATCH_HALF(dtype, T, [&]() -> int {
+    CUtensorMap ta, tb, td;
+    if (int rc = make_maps<T>(pr, 256, dtype, &ta, &tb, false)) return rc;
+    const uint64_t n_out = static_cast<uint64_t>(N + dup_cols);
+    uint64_t ddims[3] = {n_out, (uint64_t)M, 1};
+    uint64_t dstr[3] = {0, n_out * 2, n_out * 2 * (uint64_t)M};
+    uint32_t dbox[3] = {32u, 32u, 1};                       // the two-group epilogue stores 32 x 32 pieces per warp
+    if (int rc = make_tensor_map(&td, tma_dtype(dtype), 3, D, ddims, dstr, dbox, CU_TENSOR_MAP_SWIZZLE_64B)) return rc;
+    using S = Smem<256, 4>;
+    auto kern = gemm_tcgen05_dup_kernel<T>;
+    static bool attr_done = false;
+    if (!attr_done) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamic);
+      if (e != cudaSuccess) return set_error(OASR_ERR_CUDA, "gemm_dup_first: cannot reserve %d bytes of shared memory: %s",
+                                             S::kDynamic, cudaGetErrorString(e));
+      attr_done = true;
+    }
+    const int64_t work = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
+    int64_t grid = work < sm_count() ? work : sm_count();
+    if (grid < 1) grid = 1;
+    launch_pdl(kern, dim3(static_cast<unsigned>(grid)), dim3(threads_for<kSchedDense, kEpiStore>()), S::kDynamic, s, ta, tb, td, p);
+    return check_launch("tcgen05 gemm (duplicated first block) launch");
+  });
 }
 
 int oasr_b200_gemm_q8(void* D, const void* A_q, const float* a_scale, const void* B_q, const float* b_scale,

@@ -46,6 +46,22 @@ def add_norm_f32_q8(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in
     return q, scale
 
 
+def gemm_dup_first(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor], dup_cols: int,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``A (M, K) @ B (N, K).T`` with the first ``dup_cols`` output columns stored twice: the result is ``(M, N +
+    dup_cols)``, columns ``[0, dup)`` and ``[dup, 2*dup)`` both hold the first block of the product, the rest follows;
+    ``bias`` (``N + dup_cols`` entries) is added per OUTPUT column.  Equal, bit for bit, to ``gemm`` against ``B`` with
+    its first ``dup_cols`` rows repeated -- the fused q/q/k/v projection of the relative-position attention
+    (oasr/layers/attention/attention.py:323-386: q+u and q+v differ only in their bias) at 3/4 of the products."""
+    _need_cuda(A, B, bias, out)
+    M, K = A.shape
+    N = B.size(0)
+    if out is None:
+        out = torch.empty(M, N + dup_cols, device=A.device, dtype=A.dtype)
+    _lib.call("oasr_b200_gemm_dup_first", _p(out), _p(A), _p(B), _p(bias), M, N, K, int(dup_cols), _DTYPE_ID[A.dtype], _stream(A))
+    return out
+
+
 def gemm_add_norm_f32(h_out: torch.Tensor, res_out: Optional[torch.Tensor], res_in: Optional[torch.Tensor],
                       A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor], alpha: float, mode: int, w_a, b_a,
                       w_b=None, b_b=None, eps: float = 1e-5, split_out: bool = False) -> None:

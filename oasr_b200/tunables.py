@@ -16,6 +16,8 @@ split-bf16 GEMM on the tensor cores, 0 as the fp32 stencil kernel.
 ``fused_addnorm``: 1 (default) runs the last Linear of every Conformer sub-layer fused with the residual add and the
 following norm (widths 128 / 256 / 512) when the batch's 256-row tiles fill the GPU, 2 whenever the width allows it, 0
 always as gemm + add_norm_f32.
+``qkv_dup``: 1 (default) computes the query block of the fused q/q/k/v projection once and stores it twice with its two
+biases (widths that are multiples of 256), 0 multiplies by the duplicated weight block.
 ``pdl``: 1 (default) launches the hot kernels with programmatic stream serialisation, 0 in plain stream order.
 """
 from __future__ import annotations

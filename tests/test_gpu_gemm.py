@@ -268,3 +268,25 @@ def test_token_only_head_equals_the_argmax_of_the_log_probs(M):
     clear = (top2[:, 0] - top2[:, 1]) > 2e-2
     assert torch.equal(got[rows.cuda()].cpu().long()[clear], want.argmax(-1)[clear])
     assert ob.device_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 130, 4096, 16722])
+def test_gemm_dup_first_equals_the_gemm_with_the_repeated_weight_block(M):
+    """The fused q/q/k/v projection form: the first d columns of the product are stored twice, each copy with the bias
+    of its output column -- bit for bit the plain GEMM against [Wq; Wq; Wk; Wv], the shape the layer stack runs."""
+    from oasr_b200 import fused
+
+    d = 512
+    g = torch.Generator().manual_seed(M)
+    A = torch.randn(M, d, generator=g).bfloat16().cuda()
+    W3 = (torch.randn(3 * d, d, generator=g) * d ** -0.5).bfloat16().cuda()
+    bias4 = torch.randn(4 * d, generator=g).bfloat16().cuda()
+    W4 = torch.cat([W3[:d], W3], 0).contiguous()
+    want = ob.gemm(A, W4, bias4)
+    got = fused.gemm_dup_first(A, W3, bias4, d)
+    # and reading [Wq; Wk; Wv] in place, as rows d.. of the repeated form
+    got_view = fused.gemm_dup_first(A, W4[d:], bias4, d)
+    assert ob.device_status() == 0
+    assert got.shape == (M, 4 * d) and torch.equal(got, want) and torch.equal(got_view, want)
+    with pytest.raises(Exception, match="multiples of 256"):
+        fused.gemm_dup_first(A, W3[:3 * d - 8], bias4, d)
