@@ -161,3 +161,18 @@ def test_fastconformer_encoder_oracle_matches_reference_fixture():
     out, out_len = OFC.encoder_forward(P, cfg, sub, feats, case["lengths"])
     assert out_len.tolist() == gold["encoder_len"].tolist()
     assert np.abs(out.numpy() - gold["encoder_out"]).max() < 1e-4
+
+
+def test_unshifted_position_term_factorises_in_the_oracle():
+    """The packed relative-position scores carry no relative shift (matrix_bd[i, j] = (q_i + v) . p_j), so
+    (q_i + u) . k_j + (q_i + v) . p_j = q_i . (k_j + p_j) + (u . k_j + v . p_j): one product against k + p plus a
+    per-key, per-head constant.  Checked on the oracle's own tensors in float64 -- the identity a leaner projection /
+    attention pair could use (three output blocks instead of four, half the query bytes per tile)."""
+    torch.manual_seed(0)
+    H, dk, T = 4, 64, 37
+    q, k, p = (torch.randn(H, T, dk, dtype=torch.float64) for _ in range(3))
+    u, v = torch.randn(H, 1, dk, dtype=torch.float64), torch.randn(H, 1, dk, dtype=torch.float64)
+    want = (q + u) @ k.transpose(-1, -2) + (q + v) @ p.transpose(-1, -2)          # the oracle's two terms (conformer.py:219-224)
+    c = (u * k).sum(-1) + (v * p).sum(-1)                                          # (H, T): per key and head
+    got = q @ (k + p).transpose(-1, -2) + c.unsqueeze(1)
+    assert (got - want).abs().max().item() < 1e-10
